@@ -1,0 +1,341 @@
+// Per-token int4 activation quantiser (the runtime half of PermLinear) for sm_100a.
+//
+//   x32 = float(x) * a[k]            fp32 multiply, no contraction
+//   x32 = online Hadamard(x32)       optional (QuaRot R4 "full" / R2 "partial")
+//   s   = absmax(x32) / 7            IEEE division; 1 when the row is all zero; optional fp16 round
+//   q   = clamp(rint(x32 / s), -8, 7)   IEEE division, round-half-even
+//
+// Two kernels, one CTA per token row:
+//   * rows_kernel: row held in registers (no Hadamard) - one global read, one write.
+//   * had_kernel : row staged in shared memory as fp32, butterflies in place, then the same tail.
+// Both are HBM-bound streaming kernels (2 bytes in, 1 byte out per element).
+#include "dq_common.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace dq {
+
+enum { MODE_CODES = 0, MODE_FAKE = 1, MODE_RAW = 2 };
+
+__device__ __forceinline__ float block_max(float v, float* red, int nwarps) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read from a previous use
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float m = red[0];
+  for (int i = 1; i < nwarps; ++i) m = fmaxf(m, red[i]);
+  return m;
+}
+
+__device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
+  float s = __fdiv_rn(amax, 7.0f);
+  if (amax == 0.f) s = 1.0f;
+  if (scale_fp16) {
+    s = __half2float(__float2half_rn(fminf(s, 65504.0f)));
+    if (s == 0.f) s = 1.0f;
+  }
+  return s;
+}
+
+__device__ __forceinline__ float quant_code(float v, float s) {
+  float q = rintf(__fdiv_rn(v, s));
+  return fminf(fmaxf(q, -8.0f), 7.0f);
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void load8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+__device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t* codes_row,
+                                      float* out_row, int idx) {
+  if (mode == MODE_CODES) {
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      lo |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[e], s))) & 0xFFu) << (8 * e);
+      hi |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[4 + e], s))) & 0xFFu) << (8 * e);
+    }
+    *reinterpret_cast<uint2*>(codes_row + idx) = make_uint2(lo, hi);
+  } else {
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = (mode == MODE_FAKE) ? __fmul_rn(quant_code(v[e], s), s) : v[e];
+    *reinterpret_cast<float4*>(out_row + idx) = make_float4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<float4*>(out_row + idx + 4) = make_float4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// register-resident rows (no Hadamard)
+// ---------------------------------------------------------------------------------------------
+template <int THREADS, int VPT, typename XT>
+__global__ void __launch_bounds__(THREADS)
+act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
+                      int8_t* __restrict__ codes, float* __restrict__ sx, float* __restrict__ out,
+                      int mode, int scale_fp16) {
+  __shared__ float red[THREADS / 32];
+  const int row = blockIdx.x;
+  const XT* xr = x + static_cast<int64_t>(row) * ldx;
+  float v[VPT][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = (i * THREADS + threadIdx.x) * 8;
+    if (idx < K) {
+      load8(xr + idx, v[i]);
+      if (a != nullptr) {
+        float av[8];
+        load8(a + idx, av);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = __fmul_rn(v[i][e], av[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[i][e]));
+    }
+  }
+  amax = block_max(amax, red, THREADS / 32);
+  const float s = token_scale(amax, scale_fp16);
+  if (threadIdx.x == 0 && sx != nullptr) sx[row] = s;
+  int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(row) * K : nullptr;
+  float* orow = (out != nullptr) ? out + static_cast<int64_t>(row) * K : nullptr;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = (i * THREADS + threadIdx.x) * 8;
+    if (idx < K) emit8(v[i], s, mode, crow, orow, idx);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// shared-memory rows with the online Hadamard
+// ---------------------------------------------------------------------------------------------
+// One radix-2 stage over the whole row: element index = (hi*2h + lo)*stride + c pairs with
+// + h*stride; (a, b) -> (a + b, a - b).  stride = 1 for the "full" transform (independent
+// contiguous segments whose length is a multiple of 2h), stride = head_dim for the "partial"
+// one (butterflies across the head index).  Stages run in the order h = 1, 2, 4, ... so every
+// sum is formed exactly as in the reference's butterfly loop.
+template <int THREADS>
+__device__ __forceinline__ void wht_stage(float* row, int K, int h, int stride) {
+  for (int b = threadIdx.x; b < K / 2; b += THREADS) {
+    const int c = b % stride;
+    const int hb = b / stride;
+    const int i = ((hb / h) * 2 * h + (hb % h)) * stride + c;
+    const int j = i + h * stride;
+    const float u = row[i], w = row[j];
+    row[i] = __fadd_rn(u, w);
+    row[j] = __fsub_rn(u, w);
+  }
+}
+
+constexpr int kMaxHadK = 32;
+
+template <int THREADS, typename XT>
+__global__ void __launch_bounds__(THREADS)
+act_quant_had_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
+                     int had_kind, int had_k, int had_dim, float had_scale,
+                     const float* __restrict__ had_mat, int8_t* __restrict__ codes,
+                     float* __restrict__ sx, float* __restrict__ out, int mode, int scale_fp16) {
+  extern __shared__ float sm_row[];
+  __shared__ float red[THREADS / 32];
+  float* row = sm_row;
+  float* hm = sm_row + K;  // [had_k, had_k] when had_k > 1
+  const int r = blockIdx.x;
+  const XT* xr = x + static_cast<int64_t>(r) * ldx;
+
+  for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
+    float v[8];
+    load8(xr + idx, v);
+    if (a != nullptr) {
+      float av[8];
+      load8(a + idx, av);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) row[idx + e] = v[e];
+  }
+  if (had_kind == DQ_HAD_FULL && had_k > 1)
+    for (int i = threadIdx.x; i < had_k * had_k; i += THREADS) hm[i] = had_mat[i];
+  __syncthreads();
+
+  if (had_kind == DQ_HAD_FULL) {
+    const int P = K / had_k;  // Walsh-Hadamard length of each contiguous segment
+    for (int h = 1; h < P; h <<= 1) {
+      wht_stage<THREADS>(row, K, h, 1);
+      __syncthreads();
+    }
+    if (had_k > 1) {
+      // out[i][c] = sum_j H[i][j] * (v[j][c] * scale), j ascending, fp32
+      for (int c = threadIdx.x; c < P; c += THREADS) {
+        float v[kMaxHadK];
+#pragma unroll
+        for (int j = 0; j < kMaxHadK; ++j)
+          v[j] = (j < had_k) ? __fmul_rn(row[j * P + c], had_scale) : 0.f;
+        for (int i = 0; i < had_k; ++i) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < kMaxHadK; ++j)
+            if (j < had_k) acc = __fadd_rn(acc, __fmul_rn(hm[i * had_k + j], v[j]));
+          row[i * P + c] = acc;
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < K; i += THREADS) row[i] = __fmul_rn(row[i], had_scale);
+    }
+    __syncthreads();
+  } else if (had_kind == DQ_HAD_PARTIAL) {
+    const int H = K / had_dim;
+    for (int h = 1; h < H; h <<= 1) {
+      wht_stage<THREADS>(row, K, h, had_dim);
+      __syncthreads();
+    }
+    for (int i = threadIdx.x; i < K; i += THREADS) row[i] = __fmul_rn(row[i], had_scale);
+    __syncthreads();
+  }
+
+  float s = 1.f;
+  if (mode != MODE_RAW) {
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < K; i += THREADS) amax = fmaxf(amax, fabsf(row[i]));
+    amax = block_max(amax, red, THREADS / 32);
+    s = token_scale(amax, scale_fp16);
+    if (threadIdx.x == 0 && sx != nullptr) sx[r] = s;
+  }
+  int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(r) * K : nullptr;
+  float* orow = (out != nullptr) ? out + static_cast<int64_t>(r) * K : nullptr;
+  for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = row[idx + e];
+    emit8(v, s, mode, crow, orow, idx);
+  }
+}
+
+constexpr int kHadThreads = 512;
+constexpr int kHadMaxSmem = 200 * 1024;
+
+int init_act_quant_kernels() {
+  cudaError_t e = cudaFuncSetAttribute(act_quant_had_kernel<kHadThreads, __nv_bfloat16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(act_quant_had_kernel<kHadThreads, float>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
+  if (e != cudaSuccess)
+    return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(act_quant_had) failed: %s",
+                     cudaGetErrorString(e));
+  return DQ_OK;
+}
+
+static bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+static int check_had(const dq_hadamard_desc* had, int K) {
+  if (had == nullptr || had->kind == DQ_HAD_NONE) return DQ_OK;
+  if (had->kind == DQ_HAD_FULL) {
+    DQ_REQUIRE(had->had_k >= 1 && had->had_k <= kMaxHadK, DQ_ERR_UNSUPPORTED,
+               "had_k=%d outside [1,%d]", had->had_k, kMaxHadK);
+    DQ_REQUIRE(K % had->had_k == 0 && is_pow2(K / had->had_k), DQ_ERR_SHAPE,
+               "K=%d is not had_k=%d times a power of two", K, had->had_k);
+    DQ_REQUIRE(had->had_k == 1 || had->had_mat != nullptr, DQ_ERR_NULL, "had_mat is null");
+    return DQ_OK;
+  }
+  if (had->kind == DQ_HAD_PARTIAL) {
+    DQ_REQUIRE(had->had_k == 1, DQ_ERR_UNSUPPORTED,
+               "partial Hadamard with a non-power-of-two head count is not implemented");
+    DQ_REQUIRE(had->had_dim >= 1 && K % had->had_dim == 0 && is_pow2(K / had->had_dim),
+               DQ_ERR_SHAPE, "K=%d / had_dim=%d must be a power of two", K, had->had_dim);
+    return DQ_OK;
+  }
+  return set_error(DQ_ERR_UNSUPPORTED, "unknown Hadamard kind %d", had->kind);
+}
+
+template <typename XT>
+static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamard_desc* had, int M,
+                      int K, int8_t* codes, float* sx, float* out, int mode, int scale_fp16,
+                      cudaStream_t stream) {
+  DQ_REQUIRE(x != nullptr, DQ_ERR_NULL, "x is null");
+  DQ_REQUIRE(M >= 0 && K >= 8 && K % 8 == 0, DQ_ERR_SHAPE, "bad shape M=%d K=%d (K %% 8 != 0)", M, K);
+  DQ_REQUIRE(ldx >= K && ldx % 8 == 0, DQ_ERR_ALIGN, "ldx=%lld must be >= K and a multiple of 8",
+             (long long)ldx);
+  DQ_REQUIRE(aligned(x, 16) && (a == nullptr || aligned(a, 16)), DQ_ERR_ALIGN,
+             "x and a must be 16-byte aligned");
+  DQ_REQUIRE((codes == nullptr || aligned(codes, 8)) && (out == nullptr || aligned(out, 16)),
+             DQ_ERR_ALIGN, "outputs must be aligned (codes 8 B, out 16 B)");
+  DQ_REQUIRE(K <= 65536, DQ_ERR_UNSUPPORTED, "K=%d exceeds 65536", K);
+  int rc = check_had(had, K);
+  if (rc != DQ_OK) return rc;
+  if (M == 0) return DQ_OK;
+  const bool use_had = had != nullptr && had->kind != DQ_HAD_NONE;
+  if (use_had || mode == MODE_RAW || K > 32768) {  // longer rows than the register path holds
+    const int hk = use_had ? had->had_k : 1;
+    const size_t smem = static_cast<size_t>(K) * 4 + (hk > 1 ? static_cast<size_t>(hk) * hk * 4 : 0);
+    DQ_REQUIRE(smem <= static_cast<size_t>(kHadMaxSmem), DQ_ERR_UNSUPPORTED,
+               "row of K=%d does not fit in shared memory", K);
+    act_quant_had_kernel<kHadThreads, XT><<<M, kHadThreads, smem, stream>>>(
+        x, ldx, a, K, use_had ? had->kind : DQ_HAD_NONE, hk, use_had ? had->had_dim : 0,
+        use_had ? had->scale : 1.f, use_had ? had->had_mat : nullptr, codes, sx, out, mode,
+        scale_fp16);
+  } else {
+    const int vecs = (K / 8 + 255) / 256;
+    if (vecs <= 1)
+      act_quant_rows_kernel<256, 1, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+    else if (vecs <= 2)
+      act_quant_rows_kernel<256, 2, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+    else if (vecs <= 4)
+      act_quant_rows_kernel<256, 4, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+    else if (vecs <= 8)
+      act_quant_rows_kernel<256, 8, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+    else
+      act_quant_rows_kernel<512, 8, XT><<<M, 512, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+  }
+  DQ_CHECK_CUDA(cudaGetLastError());
+  return DQ_OK;
+}
+
+}  // namespace dq
+
+using namespace dq;
+
+extern "C" int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a,
+                                 const dq_hadamard_desc* had, int M, int K, int8_t* codes,
+                                 float* sx, int scale_fp16, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  DQ_REQUIRE(codes != nullptr && sx != nullptr, DQ_ERR_NULL, "codes / sx is null");
+  return launch_act(static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, had, M, K, codes, sx,
+                    nullptr, MODE_CODES, scale_fp16, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, const float* a,
+                                     const dq_hadamard_desc* had, int M, int K, float* out,
+                                     int scale_fp16, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  DQ_REQUIRE(out != nullptr, DQ_ERR_NULL, "out is null");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (x_is_f32)
+    return launch_act(static_cast<const float*>(x), ldx, a, had, M, K, nullptr, nullptr, out,
+                      MODE_FAKE, scale_fp16, s);
+  return launch_act(static_cast<const __nv_bfloat16*>(x), ldx, a, had, M, K, nullptr, nullptr, out,
+                    MODE_FAKE, scale_fp16, s);
+}
+
+extern "C" int dq_hadamard_f32(const float* x, float* out, int M, int K,
+                               const dq_hadamard_desc* had, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  DQ_REQUIRE(out != nullptr, DQ_ERR_NULL, "out is null");
+  DQ_REQUIRE(had != nullptr && had->kind != DQ_HAD_NONE, DQ_ERR_NULL, "no Hadamard described");
+  return launch_act(x, static_cast<int64_t>(K), nullptr, had, M, K, nullptr, nullptr, out, MODE_RAW,
+                    0, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,59 @@
+// Host-side plumbing shared by the translation units of libdualquant_b200: error reporting,
+// per-device state, argument checks.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/dualquant_b200.h"
+
+namespace dq {
+
+constexpr int kMaxDevices = 16;
+constexpr int kGroup = 128;  // weight-group size = K extent of one pipeline stage
+
+// Per-device state created by dq_init.
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int* status_dev = nullptr;  // device word written by kernels whose bounded waits expire
+};
+
+DeviceState* device_state(int device);
+// State of the current device, or nullptr (and the error text set) if dq_init has not run.
+DeviceState* current_state();
+
+int set_error(int code, const char* fmt, ...);
+
+// cuTensorMapEncodeTiled resolved through the runtime (no link-time libcuda dependency).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// 2-D row-major byte matrix [rows, row_bytes] (row pitch = pitch_bytes), box = box_rows x box_bytes.
+int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
+                    uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows,
+                    CUtensorMapSwizzle swizzle);
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+#define DQ_CHECK_CUDA(expr)                                                                 \
+  do {                                                                                      \
+    cudaError_t _e = (expr);                                                                \
+    if (_e != cudaSuccess)                                                                  \
+      return dq::set_error(DQ_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));    \
+  } while (0)
+
+#define DQ_REQUIRE(cond, code, ...)                          \
+  do {                                                       \
+    if (!(cond)) return dq::set_error((code), __VA_ARGS__);  \
+  } while (0)
+
+// One-time kernel attribute set-up of each translation unit (called from dq_init).
+int init_gemm_int4_kernels();
+int init_act_quant_kernels();
+
+}  // namespace dq

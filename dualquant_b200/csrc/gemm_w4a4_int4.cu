@@ -1,0 +1,464 @@
+// W4A4 int4 dual-scale GEMM for sm_100a.
+//
+//   Y[m,n] = r[n] * sx[m] * sum_g sw[n,g] * ( sum_{k in group g} qx[m,k] * qw[n,k] )
+//
+// Orientation ("swap-AB"): the 128 weight rows of a CTA tile are the UMMA M dimension (TMEM
+// lanes), the token tile TN is the UMMA N dimension (TMEM columns).  One pipeline stage is one
+// weight group (128 k): four tcgen05.mma kind::i8 (K=32) into an int32 TMEM accumulator that is
+// drained once per group, so the per-group partial sums are exact.  Each epilogue thread owns
+// one weight row and therefore one scalar group scale per stage.
+//
+// Warp roles in a 448-thread CTA:
+//   warps 0-3   unpack: packed int4 tile (TMA-staged, 8 KB) -> int8 tile in the 128B-swizzled
+//               K-major layout UMMA reads (16 KB).  Nibbles are two's complement; a byte is
+//               expanded as (w << 4) & 0xF0.. / w & 0xF0.., i.e. 16 * code, and the 1/16 is folded
+//               into the group scale (exact: power of two).
+//   warps 4-11  epilogue: tcgen05.ld of the group accumulator, run += float(acc) * sw, final scale
+//               by r[n]*sx[m], store / split-K reduction.
+//   warp 12     TMA producer (one lane): packed weight tiles and int8 activation tiles.
+//   warp 13     TMEM allocation, UMMA issue (one lane).
+//
+// Split-K (decode shapes): the CTAs that share an output tile form a thread-block cluster along
+// grid z; partial tiles are exchanged through distributed shared memory and summed in rank
+// order, so the result is deterministic and needs no global scratch and no second launch.
+#include "dq_common.h"
+#include "dq_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace dq {
+
+constexpr int kBN = 128;           // weight rows per CTA tile (UMMA M)
+constexpr int kThreads = 448;
+constexpr int kUnpackThreads = 128;
+constexpr int kEpiThreads = 256;
+constexpr int kWpBytes = kBN * kGroup / 2;  // packed stage: 8 KB
+constexpr int kWaBytes = kBN * kGroup;      // unpacked stage: 16 KB
+
+template <int TN>
+struct Cfg {
+  static constexpr int SP = (TN == 16) ? 8 : (TN == 32) ? 6 : (TN == 64) ? 8 : 6;
+  static constexpr int SA = (TN <= 32) ? 2 : 3;
+  static constexpr int SX = (TN == 128) ? 3 : 4;
+  static constexpr int kXBytes = TN * kGroup;
+  static constexpr int kMinCtas = (TN <= 32) ? 2 : 1;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffX = kOffA + SA * kWaBytes;
+  static constexpr int kOffP = kOffX + SX * kXBytes;
+  static constexpr int kOffBar = kOffP + SP * kWpBytes;
+  static constexpr int kNumBars = 2 * SP + 2 * SX + 2 * SA + 4;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + align slack
+  static constexpr int kTmemCols = (2 * TN < 32) ? 32 : 2 * TN;
+  static constexpr int CPW = TN / 2;  // accumulator columns per epilogue warp
+  static_assert(TN * kBN * 4 <= kOffBar, "split-K exchange tile must fit in the stage buffers");
+};
+
+// site codes stored in the status word when a bounded wait expires
+enum { SITE_TMA_P = 1, SITE_TMA_X, SITE_UNPACK_FULL, SITE_UNPACK_EMPTY, SITE_MMA_T, SITE_MMA_A,
+       SITE_MMA_X, SITE_EPI };
+
+template <int TN, bool DUMP>
+__global__ void __launch_bounds__(kThreads, Cfg<TN>::kMinCtas)
+gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
+                      const __grid_constant__ CUtensorMap tm_x,
+                      const __half* __restrict__ sw_t, const float* __restrict__ r,
+                      const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
+                      int32_t* __restrict__ acc_dump, int M, int N, int K, int groups_per_split,
+                      int split_k, int w_stream_once, int* status) {
+  using C = Cfg<TN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint64_t* full_p = bars;
+  uint64_t* empty_p = full_p + C::SP;
+  uint64_t* full_x = empty_p + C::SP;
+  uint64_t* empty_x = full_x + C::SX;
+  uint64_t* full_a = empty_x + C::SX;
+  uint64_t* empty_a = full_a + C::SA;
+  uint64_t* full_t = empty_a + C::SA;
+  uint64_t* empty_t = full_t + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(empty_t + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int n0 = blockIdx.x * kBN;
+  const int t0 = blockIdx.y * TN;
+  const int total_groups = K / kGroup;
+  const int g_begin = blockIdx.z * groups_per_split;
+  int g_end = g_begin + groups_per_split;
+  if (g_end > total_groups) g_end = total_groups;
+  const int ng = (g_end > g_begin) ? (g_end - g_begin) : 0;
+
+  if (tid == 0) {
+    for (int i = 0; i < C::SP; ++i) { mbar_init(&full_p[i], 1); mbar_init(&empty_p[i], kUnpackThreads); }
+    for (int i = 0; i < C::SX; ++i) { mbar_init(&full_x[i], 1); mbar_init(&empty_x[i], 1); }
+    for (int i = 0; i < C::SA; ++i) { mbar_init(&full_a[i], kUnpackThreads); mbar_init(&empty_a[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&full_t[i], 1); mbar_init(&empty_t[i], kEpiThreads); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 13) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 12 && lane == 0) {
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  float run[C::CPW];  // epilogue running sums (only epilogue warps use them)
+#pragma unroll
+  for (int j = 0; j < C::CPW; ++j) run[j] = 0.f;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ unpack warps
+    for (int i = 0; i < ng; ++i) {
+      const int sp = i % C::SP, sa = i % C::SA;
+      if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
+      if (!mbar_wait(&empty_a[sa], ((i / C::SA) & 1) ^ 1, abort_flag, SITE_UNPACK_EMPTY)) break;
+      const uint8_t* src = smem + C::kOffP + sp * kWpBytes;
+      uint8_t* dst = smem + C::kOffA + sa * kWaBytes;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int id = tid + c * kUnpackThreads;  // 16-byte chunk of the packed tile
+        const int row = id >> 2, ch = id & 3;
+        const uint4 w = *reinterpret_cast<const uint4*>(src + id * 16);
+        uint4 lo, hi;
+        lo.x = (w.x << 4) & 0xF0F0F0F0u; hi.x = w.x & 0xF0F0F0F0u;
+        lo.y = (w.y << 4) & 0xF0F0F0F0u; hi.y = w.y & 0xF0F0F0F0u;
+        lo.z = (w.z << 4) & 0xF0F0F0F0u; hi.z = w.z & 0xF0F0F0F0u;
+        lo.w = (w.w << 4) & 0xF0F0F0F0u; hi.w = w.w & 0xF0F0F0F0u;
+        uint8_t* rowp = dst + row * 128;
+        const int sw = row & 7;
+        *reinterpret_cast<uint4*>(rowp + (((2 * ch) ^ sw) << 4)) = lo;
+        *reinterpret_cast<uint4*>(rowp + (((2 * ch + 1) ^ sw) << 4)) = hi;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&full_a[sa]);
+      mbar_arrive(&empty_p[sp]);
+    }
+  } else if (warp < 12) {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;          // TMEM lane quarter this warp may read
+    const int h = (warp - 4) >> 2;   // which half of the token columns
+    const int n = n0 + q * 32 + lane;
+    const bool n_ok = n < N;
+    for (int i = 0; i < ng; ++i) {
+      const int b = i & 1;
+      float s = 0.f;
+      if constexpr (!DUMP) {
+        if (n_ok)
+          s = __half2float(sw_t[static_cast<size_t>(g_begin + i) * N + n]) * 0.0625f;
+      }
+      if (!mbar_wait(&full_t[b], (i >> 1) & 1, abort_flag, SITE_EPI)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(b * TN + h * C::CPW);
+      constexpr int CH = (C::CPW < 32) ? C::CPW : 32;  // columns per tcgen05.ld
+#pragma unroll
+      for (int c0 = 0; c0 < C::CPW; c0 += CH) {
+        uint32_t v[CH];
+        if constexpr (CH == 8) {
+          tmem_ld_x8(taddr + c0, v);
+        } else if constexpr (CH == 16) {
+          tmem_ld_x16(taddr + c0, v);
+        } else {
+          tmem_ld_x32(taddr + c0, v);
+        }
+        tmem_ld_wait();
+        if (c0 + CH == C::CPW) {  // accumulator buffer b is free once its last column is read
+          tc_fence_before();
+          mbar_arrive(&empty_t[b]);
+        }
+        if constexpr (DUMP) {
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int m = t0 + h * C::CPW + c0 + j;
+              if (m < M)
+                acc_dump[(static_cast<size_t>(m) * N + n) * total_groups + (g_begin + i)] =
+                    static_cast<int32_t>(v[j]) >> 4;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CH; ++j)
+            run[c0 + j] = fmaf(static_cast<float>(static_cast<int32_t>(v[j])), s, run[c0 + j]);
+        }
+      }
+    }
+    if constexpr (!DUMP) {
+      if (split_k == 1) {
+        if (n_ok) {
+          const float rn = (r != nullptr) ? r[n] : 1.f;
+#pragma unroll
+          for (int j = 0; j < C::CPW; ++j) {
+            const int m = t0 + h * C::CPW + j;
+            if (m < M) {
+              const float val = run[j] * (rn * sx[m]);
+              if (y_bf16)
+                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
+                    __float2bfloat16_rn(val);
+              else
+                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+            }
+          }
+        }
+      } else {
+        // Partial tile -> this CTA's exchange buffer red[token][row] (aliases the stage buffers:
+        // the last full_t wait above implies every UMMA, hence every smem operand read, is done).
+        float* red = reinterpret_cast<float*>(smem);
+#pragma unroll
+        for (int j = 0; j < C::CPW; ++j) red[(h * C::CPW + j) * kBN + q * 32 + lane] = run[j];
+      }
+    }
+  } else if (warp == 12) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint64_t pol_w, pol_x;
+      if (w_stream_once) pol_w = l2_policy_evict_first(); else pol_w = l2_policy_evict_last();
+      pol_x = l2_policy_evict_last();
+      for (int i = 0; i < ng; ++i) {
+        const int sp = i % C::SP, sxi = i % C::SX;
+        if (!mbar_wait(&empty_p[sp], ((i / C::SP) & 1) ^ 1, abort_flag, SITE_TMA_P)) break;
+        mbar_expect_tx(&full_p[sp], kWpBytes);
+        tma_load_2d(smem + C::kOffP + sp * kWpBytes, &tm_w, (g_begin + i) * (kGroup / 2), n0,
+                    &full_p[sp], pol_w);
+        if (!mbar_wait(&empty_x[sxi], ((i / C::SX) & 1) ^ 1, abort_flag, SITE_TMA_X)) break;
+        mbar_expect_tx(&full_x[sxi], C::kXBytes);
+        tma_load_2d(smem + C::kOffX + sxi * C::kXBytes, &tm_x, (g_begin + i) * kGroup, t0,
+                    &full_x[sxi], pol_x);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_i8(kBN, TN);
+      for (int i = 0; i < ng; ++i) {
+        const int b = i & 1, sa = i % C::SA, sxi = i % C::SX;
+        if (!mbar_wait(&empty_t[b], ((i >> 1) & 1) ^ 1, abort_flag, SITE_MMA_T)) break;
+        if (!mbar_wait(&full_a[sa], (i / C::SA) & 1, abort_flag, SITE_MMA_A)) break;
+        if (!mbar_wait(&full_x[sxi], (i / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
+        tc_fence_after();
+        const uint64_t da = umma_desc_k_sw128(smem_u32(smem + C::kOffA + sa * kWaBytes));
+        const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffX + sxi * C::kXBytes));
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * TN);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // +32 bytes along K inside the swizzle atom = +2 (>>4)
+          umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+        umma_commit(&empty_a[sa]);
+        umma_commit(&empty_x[sxi]);
+        umma_commit(&full_t[b]);
+      }
+    }
+  }
+
+  // -------------------------------------------------------------------- split-K reduction
+  if (!DUMP && split_k > 1) {
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 4 && warp < 12) {
+      const uint32_t rank = cluster_ctarank();
+      const int rows = TN / split_k;  // token rows of the tile this CTA finishes
+      const int e = tid - 4 * 32;     // 0..255
+      const int c4 = e & 31;          // float4 column
+      const uint32_t red_base = smem_u32(smem);
+      for (int rr = e >> 5; rr < rows; rr += 8) {
+        const int tl = static_cast<int>(rank) * rows + rr;
+        const int m = t0 + tl;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t off = static_cast<uint32_t>((tl * kBN + c4 * 4) * 4);
+        for (int p = 0; p < split_k; ++p) {
+          const float4 v = dsmem_ld_f4(dsmem_map(red_base + off, static_cast<uint32_t>(p)));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (m < M) {
+          const float sm = sx[m];
+          const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int n = n0 + c4 * 4 + u;
+            if (n < N) {
+              const float rn = (r != nullptr) ? r[n] : 1.f;
+              const float val = vals[u] * (rn * sm);
+              if (y_bf16)
+                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
+                    __float2bfloat16_rn(val);
+              else
+                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // peers may still be reading this CTA's exchange buffer until here
+  }
+
+  // -------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 13) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+  if (tid == 0 && *abort_flag != 0) atomicCAS(status, 0, *abort_flag);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+template <int TN, bool DUMP>
+static int set_attr() {
+  cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_int4_kernel<TN, DUMP>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg<TN>::kSmemBytes);
+  if (e != cudaSuccess)
+    return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemm TN=%d) failed: %s", TN,
+                     cudaGetErrorString(e));
+  return DQ_OK;
+}
+
+int init_gemm_int4_kernels() {
+  int rc;
+  if ((rc = set_attr<16, false>()) != DQ_OK) return rc;
+  if ((rc = set_attr<32, false>()) != DQ_OK) return rc;
+  if ((rc = set_attr<64, false>()) != DQ_OK) return rc;
+  if ((rc = set_attr<128, false>()) != DQ_OK) return rc;
+  if ((rc = set_attr<16, true>()) != DQ_OK) return rc;
+  if ((rc = set_attr<128, true>()) != DQ_OK) return rc;
+  return DQ_OK;
+}
+
+static int pick_token_tile(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  return 128;
+}
+
+// Smallest power-of-two split (<= 8, <= TN so every rank finishes at least one token row, and
+// leaving at least two groups per CTA) that puts enough CTAs on the machine.
+static int pick_split(int tiles, int total_groups, int tn, int sm_count) {
+  const int target = sm_count * ((tn <= 32) ? 2 : 1);
+  int s = 1;
+  while (s < 8 && tiles * s < target && total_groups / (2 * s) >= 2 && 2 * s <= tn) s *= 2;
+  return s;
+}
+
+template <int TN, bool DUMP>
+static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed, const __half* sw_t,
+                  const float* r, int M, int N, int K, void* y, int y_dtype, int32_t* acc_dump,
+                  int split, cudaStream_t stream, DeviceState* st) {
+  CUtensorMap tm_w, tm_x;
+  int rc = make_tmap_2d_u8(&tm_w, w_packed, static_cast<uint64_t>(K) / 2, N,
+                           static_cast<uint64_t>(K) / 2, kGroup / 2, kBN,
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != DQ_OK) return rc;
+  rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, kGroup, TN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != DQ_OK) return rc;
+
+  const int total_groups = K / kGroup;
+  const int gps = (total_groups + split - 1) / split;
+  const int tok_tiles = (M + TN - 1) / TN;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + kBN - 1) / kBN, tok_tiles, split);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg<TN>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = split;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN, DUMP>, tm_w, tm_x, sw_t, r, sx,
+                                     y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, acc_dump, M, N, K, gps,
+                                     split, w_stream_once, st->status_dev);
+  if (e != cudaSuccess)
+    return set_error(DQ_ERR_CUDA, "gemm_w4a4_int4 launch failed (TN=%d split=%d): %s", TN, split,
+                     cudaGetErrorString(e));
+  return DQ_OK;
+}
+
+static int check_gemm_args(const void* codes, const void* w_packed, int M, int N, int K, int G) {
+  DQ_REQUIRE(codes != nullptr && w_packed != nullptr, DQ_ERR_NULL, "null operand pointer");
+  DQ_REQUIRE(G == kGroup, DQ_ERR_UNSUPPORTED, "weight group size must be %d (got %d)", kGroup, G);
+  DQ_REQUIRE(M >= 1 && N >= 1 && K >= kGroup, DQ_ERR_SHAPE, "bad shape M=%d N=%d K=%d", M, N, K);
+  DQ_REQUIRE(K % kGroup == 0, DQ_ERR_SHAPE, "K=%d must be a multiple of %d", K, kGroup);
+  DQ_REQUIRE(aligned(codes, 16) && aligned(w_packed, 16), DQ_ERR_ALIGN,
+             "codes and w_packed must be 16-byte aligned");
+  return DQ_OK;
+}
+
+}  // namespace dq
+
+using namespace dq;
+
+extern "C" size_t dq_gemm_w4a4_int4_workspace_bytes(int, int, int) { return 0; }
+
+extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                    const void* sw_t, const float* r, int M, int N, int K, int G,
+                                    void* y, int y_dtype, void* /*workspace*/,
+                                    size_t /*workspace_bytes*/, void* stream, int token_tile,
+                                    int split_k) {
+  DeviceState* st = current_state();
+  if (st == nullptr) return DQ_ERR_NOT_INIT;
+  int rc = check_gemm_args(codes, w_packed, M, N, K, G);
+  if (rc != DQ_OK) return rc;
+  DQ_REQUIRE(sx != nullptr && sw_t != nullptr && y != nullptr, DQ_ERR_NULL, "null sx / sw_t / y");
+  DQ_REQUIRE(y_dtype == DQ_DTYPE_F32 || y_dtype == DQ_DTYPE_BF16, DQ_ERR_UNSUPPORTED,
+             "unknown y_dtype %d", y_dtype);
+  const int tn = token_tile ? token_tile : pick_token_tile(M);
+  DQ_REQUIRE(tn == 16 || tn == 32 || tn == 64 || tn == 128, DQ_ERR_SHAPE,
+             "token tile must be 16/32/64/128 (got %d)", tn);
+  const int total_groups = K / kGroup;
+  const int tiles = ((N + kBN - 1) / kBN) * ((M + tn - 1) / tn);
+  int split = split_k ? split_k : pick_split(tiles, total_groups, tn, st->sm_count);
+  DQ_REQUIRE(split == 1 || split == 2 || split == 4 || split == 8, DQ_ERR_SHAPE,
+             "split_k must be 1/2/4/8 (got %d)", split);
+  DQ_REQUIRE(split <= tn && split <= total_groups, DQ_ERR_SHAPE,
+             "split_k=%d too large for token tile %d / %d groups", split, tn, total_groups);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __half* swp = static_cast<const __half*>(sw_t);
+  switch (tn) {
+    case 16: return launch<16, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
+    case 32: return launch<32, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
+    case 64: return launch<64, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
+    default: return launch<128, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
+  }
+}
+
+extern "C" int dq_gemm_w4a4_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                 const void* sw_t, const float* r, int M, int N, int K, int G,
+                                 void* y, int y_dtype, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  return dq_gemm_w4a4_int4_ex(codes, sx, w_packed, sw_t, r, M, N, K, G, y, y_dtype, workspace,
+                              workspace_bytes, stream, 0, 0);
+}
+
+extern "C" int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packed, int M, int N,
+                                     int K, int G, int32_t* acc, void* stream) {
+  DeviceState* st = current_state();
+  if (st == nullptr) return DQ_ERR_NOT_INIT;
+  int rc = check_gemm_args(codes, w_packed, M, N, K, G);
+  if (rc != DQ_OK) return rc;
+  DQ_REQUIRE(acc != nullptr, DQ_ERR_NULL, "null acc");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M <= 16)
+    return launch<16, true>(codes, nullptr, w_packed, nullptr, nullptr, M, N, K, nullptr,
+                            DQ_DTYPE_F32, acc, 1, s, st);
+  return launch<128, true>(codes, nullptr, w_packed, nullptr, nullptr, M, N, K, nullptr,
+                           DQ_DTYPE_F32, acc, 1, s, st);
+}

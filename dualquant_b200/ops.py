@@ -1,0 +1,202 @@
+"""Tensor-level wrappers over the C ABI: torch supplies device memory and the stream, the
+shared library does all the work."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+GROUP = 128
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(dev: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _prep(t: torch.Tensor):
+    if not t.is_cuda:
+        raise RuntimeError("dualquant_b200 runs on CUDA (sm_100a) tensors only; got a CPU tensor")
+    idx = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    if torch.cuda.current_device() != idx:
+        torch.cuda.set_device(idx)
+    _lib.ensure_init(idx)
+    return _lib.load()
+
+
+@dataclass
+class Hadamard:
+    """Online Hadamard description (the had_K / K / had_dim attributes of a PermLinear)."""
+
+    kind: int = _lib.HAD_NONE
+    had_k: int = 1
+    had_dim: int = 0
+    scale: float = 1.0
+    had_mat: Optional[torch.Tensor] = None  # fp32 [had_k, had_k] on the device
+
+    def desc(self):
+        if self.kind == _lib.HAD_NONE:
+            return None
+        d = _lib.HadamardDesc()
+        d.kind, d.had_k, d.had_dim, d.scale = self.kind, self.had_k, self.had_dim, self.scale
+        d.had_mat = self.had_mat.data_ptr() if self.had_mat is not None else None
+        return ctypes.byref(d)
+
+
+@dataclass
+class PackedInt4Weight:
+    """Weight artefact the GEMM consumes: streaming int4 layout + transposed fp16 group scales."""
+
+    w_packed: torch.Tensor  # uint8 [N, K/2]
+    sw_t: torch.Tensor  # fp16 [K/G, N]
+    N: int
+    K: int
+    group: int = GROUP
+
+    def state(self):
+        return {"w_packed": self.w_packed, "sw_t": self.sw_t, "N": self.N, "K": self.K,
+                "group": self.group, "layout_version": 1}
+
+
+def quant_w_int4(w: torch.Tensor, group: int = GROUP):
+    """bf16 [N,K] -> (codes int8 [N,K], sw fp16 [N,K/group])."""
+    lib = _prep(w)
+    w = w.to(torch.bfloat16).contiguous()
+    N, K = w.shape
+    codes = torch.empty(N, K, dtype=torch.int8, device=w.device)
+    sw = torch.empty(N, K // group, dtype=torch.float16, device=w.device)
+    _lib.check(lib.dq_quant_w_int4(_ptr(w), N, K, group, _ptr(codes), _ptr(sw), _stream(w.device)),
+               "dq_quant_w_int4")
+    return codes, sw
+
+
+def pack_w_int4(codes: Optional[torch.Tensor], sw: torch.Tensor, group: int = GROUP,
+                ref_packed: Optional[torch.Tensor] = None) -> PackedInt4Weight:
+    src = codes if codes is not None else ref_packed
+    lib = _prep(src)
+    if codes is not None:
+        codes = codes.contiguous()
+        N, K = codes.shape
+    else:
+        ref_packed = ref_packed.contiguous()
+        N, K = ref_packed.shape[0], ref_packed.shape[1] * 2
+    sw = sw.to(torch.float16).contiguous()
+    w_packed = torch.empty(N, K // 2, dtype=torch.uint8, device=src.device)
+    sw_t = torch.empty(K // group, N, dtype=torch.float16, device=src.device)
+    _lib.check(lib.dq_pack_w_int4(_ptr(codes), _ptr(ref_packed), _ptr(sw), N, K, group, _ptr(w_packed),
+                                  _ptr(sw_t), _stream(src.device)), "dq_pack_w_int4")
+    return PackedInt4Weight(w_packed, sw_t, N, K, group)
+
+
+def unpack_w_int4(pw: PackedInt4Weight) -> torch.Tensor:
+    lib = _prep(pw.w_packed)
+    codes = torch.empty(pw.N, pw.K, dtype=torch.int8, device=pw.w_packed.device)
+    _lib.check(lib.dq_unpack_w_int4(_ptr(pw.w_packed), pw.N, pw.K, _ptr(codes),
+                                    _stream(codes.device)), "dq_unpack_w_int4")
+    return codes
+
+
+def quant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
+                   had: Optional[Hadamard] = None, scale_fp16: bool = False):
+    """bf16 [M,K] -> (codes int8 [M,K], sx fp32 [M])."""
+    lib = _prep(x)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("quant_act_int4 expects bf16 activations")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    M, K = x.shape
+    codes = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    sx = torch.empty(M, dtype=torch.float32, device=x.device)
+    desc = had.desc() if had is not None else None
+    _lib.check(lib.dq_quant_act_int4(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), desc, M, K,
+                                     _ptr(codes), _ptr(sx), int(scale_fp16), _stream(x.device)),
+               "dq_quant_act_int4")
+    return codes, sx
+
+
+def fakequant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
+                       had: Optional[Hadamard] = None, scale_fp16: bool = False) -> torch.Tensor:
+    """[M,K] bf16 or fp32 -> de-quantised fp32 [M,K] (what FormatSpec.cast returns)."""
+    lib = _prep(x)
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("fakequant_act_int4 expects bf16 or fp32")
+    x = x.contiguous()
+    M, K = x.shape
+    out = torch.empty(M, K, dtype=torch.float32, device=x.device)
+    desc = had.desc() if had is not None else None
+    _lib.check(lib.dq_fakequant_act_int4(_ptr(x), int(x.dtype == torch.float32), K, _ptr(a), desc,
+                                         M, K, _ptr(out), int(scale_fp16), _stream(x.device)),
+               "dq_fakequant_act_int4")
+    return out
+
+
+def hadamard_f32(x: torch.Tensor, had: Hadamard) -> torch.Tensor:
+    lib = _prep(x)
+    x = x.to(torch.float32).contiguous()
+    M, K = x.shape
+    out = torch.empty_like(x)
+    _lib.check(lib.dq_hadamard_f32(_ptr(x), _ptr(out), M, K, had.desc(), _stream(x.device)),
+               "dq_hadamard_f32")
+    return out
+
+
+def gemm_w4a4_int4(codes: torch.Tensor, sx: torch.Tensor, pw: PackedInt4Weight,
+                   r: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+                   token_tile: int = 0, split_k: int = 0,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _prep(codes)
+    M, K = codes.shape
+    if K != pw.K:
+        raise ValueError(f"K mismatch: activations {K}, weight {pw.K}")
+    if out is None:
+        out = torch.empty(M, pw.N, dtype=out_dtype, device=codes.device)
+    ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    _lib.check(lib.dq_gemm_w4a4_int4_ex(_ptr(codes), _ptr(sx), _ptr(pw.w_packed), _ptr(pw.sw_t), _ptr(r),
+                                        M, pw.N, K, pw.group, _ptr(out), ydt, None, 0,
+                                        _stream(codes.device), token_tile, split_k),
+               "dq_gemm_w4a4_int4")
+    return out
+
+
+def gemm_w4a4_int4_acc(codes: torch.Tensor, pw: PackedInt4Weight) -> torch.Tensor:
+    """Test hook: raw per-group int32 accumulators [M, N, K/G]."""
+    lib = _prep(codes)
+    M, K = codes.shape
+    acc = torch.zeros(M, pw.N, K // pw.group, dtype=torch.int32, device=codes.device)
+    _lib.check(lib.dq_gemm_w4a4_int4_acc(_ptr(codes), _ptr(pw.w_packed), M, pw.N, K, pw.group,
+                                         _ptr(acc), _stream(codes.device)), "dq_gemm_w4a4_int4_acc")
+    return acc
+
+
+def linear_scratch_bytes(M: int, N: int, K: int) -> int:
+    return int(_lib.load().dq_linear_w4a4_int4_scratch_bytes(M, N, K))
+
+
+def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[Hadamard],
+                     pw: PackedInt4Weight, r: Optional[torch.Tensor], out_dtype=torch.float32,
+                     scale_fp16: bool = False, scratch: Optional[torch.Tensor] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Whole PermLinear.forward on the int4 path in one C call (two launches)."""
+    lib = _prep(x)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    M, K = x.shape
+    need = linear_scratch_bytes(M, pw.N, K)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty(M, pw.N, dtype=out_dtype, device=x.device)
+    ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    desc = had.desc() if had is not None else None
+    _lib.check(lib.dq_linear_w4a4_int4(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), desc,
+                                       _ptr(pw.w_packed), _ptr(pw.sw_t), _ptr(r), M, pw.N, K, pw.group,
+                                       _ptr(out), ydt, int(scale_fp16), _ptr(scratch), scratch.numel(),
+                                       _stream(x.device)), "dq_linear_w4a4_int4")
+    return out

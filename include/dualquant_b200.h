@@ -1,0 +1,184 @@
+/*
+ * dualquant_b200 -- C ABI of the Blackwell (sm_100a) W4A4 inference hot path.
+ *
+ * Every entry point is `extern "C"`, takes raw device pointers plus sizes, launches on the
+ * caller's stream and returns an int status (0 = DQ_OK).  Nothing here allocates, frees,
+ * synchronises or touches the legacy stream; scratch memory is caller-provided.  Pointers are
+ * device pointers unless a comment says "host".  `stream` is a `cudaStream_t` passed as void*.
+ *
+ * The citations name the reference interface (path inside sayehs-dmatrix/dualquant : lines)
+ * whose work the entry point takes over.
+ */
+#ifndef DUALQUANT_B200_H
+#define DUALQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define DQ_API __attribute__((visibility("default")))
+#else
+#define DQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------ */
+enum {
+  DQ_OK = 0,
+  DQ_ERR_SHAPE = 1,       /* a size violates the kernel's divisibility / range rules          */
+  DQ_ERR_ALIGN = 2,       /* a pointer or leading dimension is not aligned as required        */
+  DQ_ERR_NULL = 3,        /* a required pointer is null                                       */
+  DQ_ERR_ARCH = 4,        /* the current device is not compute capability 10.x                */
+  DQ_ERR_CUDA = 5,        /* a CUDA runtime / driver call failed (see dq_last_error_string)   */
+  DQ_ERR_WORKSPACE = 6,   /* caller-provided scratch is too small                             */
+  DQ_ERR_UNSUPPORTED = 7, /* valid request that this build has no kernel for                  */
+  DQ_ERR_NOT_INIT = 8,    /* dq_init was not called for the current device                    */
+  DQ_ERR_TIMEOUT = 9      /* a bounded device-side wait expired (read via dq_device_status)   */
+};
+
+/* element types of the output matrix Y */
+enum { DQ_DTYPE_F32 = 0, DQ_DTYPE_BF16 = 1 };
+
+/* block-scaled FP4 flavours (formats/mx.py:23-31, formats/nvfp4.py:11-19) */
+enum { DQ_FP4_MXFP4 = 0, DQ_FP4_NVFP4 = 1 };
+
+/* online-Hadamard kinds (activations/perm_linear.py:76-106) */
+enum {
+  DQ_HAD_NONE = 0,
+  DQ_HAD_FULL = 1,    /* x.view(-1, had_k, n/had_k): WHT over the last axis, * scale, had_K @   */
+  DQ_HAD_PARTIAL = 2  /* x.view(-1, n/had_dim, had_dim): WHT across the head index, * scale     */
+};
+
+/*
+ * Online Hadamard description.  Mirrors the attributes that
+ * quarot/online_had_install.py:44-58 sets on a PermLinear (had_K, K, had_dim) and the
+ * arithmetic of quarot/vendor/hadamard_utils.py:92-101 + quarot/__init__.py:39-64.
+ */
+typedef struct dq_hadamard_desc {
+  int32_t kind;          /* DQ_HAD_*                                                         */
+  int32_t had_k;         /* FULL: order of the +-1 matrix (1 = pure Walsh-Hadamard)          */
+  int32_t had_dim;       /* PARTIAL: head_dim                                                */
+  float scale;           /* fp32 factor applied after the Walsh-Hadamard butterflies         */
+  const float* had_mat;  /* FULL with had_k > 1: device pointer to [had_k, had_k] fp32       */
+} dq_hadamard_desc;
+
+/* ---- library state ----------------------------------------------------------------------- */
+
+/* One-time per-device set-up (kernel attributes, driver entry points, status word).  Call it
+ * outside stream capture, with the device current.  Replaces the once-only
+ * cudaFuncSetAttribute logic of the reference's launcher patch
+ * (ablation/real_int4_kernel/nunchaku_patches/0001-dualquant-w4a4-modifications.patch:1136-1143). */
+DQ_API int dq_init(int device);
+
+/* Text of the last error raised on the calling thread (host pointer, never null). */
+DQ_API const char* dq_last_error_string(void);
+
+/* Reads (and clears) the device-side status word of `device`: 0, or DQ_ERR_TIMEOUT plus a
+ * site code in the upper 16 bits when a bounded wait inside a kernel expired.  Synchronises
+ * the device. */
+DQ_API int dq_device_status(int device);
+
+DQ_API int dq_abi_version(void);
+
+/* ---- weights ----------------------------------------------------------------------------- */
+
+/* Bytes of the packed weight matrix for (N, K): N*K/2. */
+DQ_API size_t dq_packed_w_bytes(int N, int K);
+
+/*
+ * Re-pack int4 weight codes into the streaming layout the GEMM consumes and transpose the
+ * group scales.  Input is either signed codes (int8 [N,K], values in [-8,7]) or the
+ * reference's packed form (uint8 [N,K/2], low nibble = even k, high nibble = odd k, biased
+ * by +8: vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:156-189); give exactly
+ * one of the two.  sw is fp16 [N, K/G]; sw_t is fp16 [K/G, N].
+ */
+DQ_API int dq_pack_w_int4(const int8_t* codes, const uint8_t* ref_packed, const void* sw,
+                   int N, int K, int G, uint8_t* w_packed, void* sw_t, void* stream);
+
+/* Inverse of dq_pack_w_int4: signed codes int8 [N,K] from the streaming layout. */
+DQ_API int dq_unpack_w_int4(const uint8_t* w_packed, int N, int K, int8_t* codes, void* stream);
+
+/*
+ * Symmetric per-group int4 weight quantiser: W bf16 [N,K] -> codes int8 [N,K] and fp16
+ * scales [N,K/G] (absmax/7, 1 for an all-zero group), the arithmetic of
+ * formats/rtn_int.py:43-69 with the scale rounded to fp16 before the division.
+ */
+DQ_API int dq_quant_w_int4(const void* w_bf16, int N, int K, int G, int8_t* codes, void* sw,
+                    void* stream);
+
+/* ---- activations ------------------------------------------------------------------------- */
+
+/*
+ * Per-token int4 activation quantiser, the runtime half of PermLinear
+ * (activations/perm_linear.py:108-134 with formats/rtn_int.py:43-69, block_size=-1):
+ *   x32 = float(x) * a        (a may be null)
+ *   x32 = hadamard(x32)       (had may be null / DQ_HAD_NONE)
+ *   s   = absmax(x32)/7 (1 if 0), optionally rounded to fp16
+ *   q   = clamp(round_half_even(x32/s), -8, 7)
+ * x is bf16 [M,K] with leading dimension ldx (elements); codes int8 [M,K]; sx fp32 [M].
+ * `a` is fp32 [K].  `had` is a host pointer.
+ */
+DQ_API int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a,
+                      const dq_hadamard_desc* had, int M, int K, int8_t* codes, float* sx,
+                      int scale_fp16, void* stream);
+
+/* Same arithmetic, but writes the de-quantised value q*s as fp32 [M,K] (what
+ * FormatSpec.cast returns, formats/base.py:33-39).  x is fp32 when x_is_f32 != 0. */
+DQ_API int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, const float* a,
+                          const dq_hadamard_desc* had, int M, int K, float* out,
+                          int scale_fp16, void* stream);
+
+/* The online Hadamard alone on fp32 rows: out = hadamard(x) (perm_linear.py:76-106). */
+DQ_API int dq_hadamard_f32(const float* x, float* out, int M, int K, const dq_hadamard_desc* had,
+                    void* stream);
+
+/* ---- int4 dual-scale GEMM ------------------------------------------------------------------ */
+
+/* Scratch bytes dq_gemm_w4a4_int4 needs for (M,N,K); may be 0. */
+DQ_API size_t dq_gemm_w4a4_int4_workspace_bytes(int M, int N, int K);
+
+/*
+ * Y[m,n] = r[n] * sx[m] * sum_g sw[n,g] * (sum_{k in g} qx[m,k] * qw[n,k])
+ * with exact int32 accumulation inside each weight group of G=128 and an fp32 epilogue: the
+ * computation of ablation/real_int4_kernel/fused_w4a4_kernel.py:51-126 with one activation
+ * scale per token, and of dequantise-and-matmul
+ * (vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:192-206, 287-292).
+ *   codes    int8 [M,K] (row stride K), values in [-8,7]
+ *   sx       fp32 [M]
+ *   w_packed, sw_t   from dq_pack_w_int4
+ *   r        fp32 [N] or null (= 1)
+ *   y        [M,N] row-major, fp32 or bf16 (y_dtype)
+ */
+DQ_API int dq_gemm_w4a4_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                      const void* sw_t, const float* r, int M, int N, int K, int G, void* y,
+                      int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* As above with explicit tiling (token tile 16/32/64/128 or 0 = auto, split-K 1/2/4/8 or
+ * 0 = auto); used by tuning sweeps and tests. */
+DQ_API int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                         const void* sw_t, const float* r, int M, int N, int K, int G, void* y,
+                         int y_dtype, void* workspace, size_t workspace_bytes, void* stream,
+                         int token_tile, int split_k);
+
+/* Test hook: the raw per-group int32 accumulators acc[M, N, K/G] (no scales applied). */
+DQ_API int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packed, int M, int N, int K,
+                          int G, int32_t* acc, void* stream);
+
+/*
+ * One call for a whole PermLinear.forward (activations/perm_linear.py:136-141) on the real
+ * int4 path: quantise x (as dq_quant_act_int4) into caller scratch, then the GEMM.
+ * scratch must hold dq_linear_w4a4_int4_scratch_bytes(M,N,K) bytes.
+ */
+DQ_API size_t dq_linear_w4a4_int4_scratch_bytes(int M, int N, int K);
+DQ_API int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float* a,
+                        const dq_hadamard_desc* had, const uint8_t* w_packed, const void* sw_t,
+                        const float* r, int M, int N, int K, int G, void* y, int y_dtype,
+                        int scale_fp16, void* scratch, size_t scratch_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DUALQUANT_B200_H */

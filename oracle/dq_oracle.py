@@ -1,0 +1,285 @@
+"""CPU oracle for the W4A4 hot path -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+Only tests, the smoke check and the CPU-baseline leg of the benchmark may import this module;
+the library itself never does.  Every function restates, in plain torch-on-CPU / numpy, the
+arithmetic of one piece of the reference (sayehs-dmatrix/dualquant); the citation after each
+name is the reference file:line it follows.
+
+Parity status
+-------------
+* int4 path (activation quantiser, weight quantiser / packing, Hadamard, dequantise-and-matmul):
+  pinned against the reference's own code, which is imported in the authoring container to
+  produce the fixtures under tests/golden/ (see tests/golden/make_golden.py).
+* MXFP4 / NVFP4 block casts: PARITY UNPINNED.  The reference delegates them to an external,
+  non-redistributable package (`blockfmt` 0.3.0, formats/mx.py:24-29, formats/nvfp4.py:12-17)
+  that is absent from the reference tree, and ships no test or golden vector at that boundary.
+  The functions here follow the published OCP-MX / NVFP4 definitions and the in-tree statements
+  of intent (legacy_vendor/torch_quant.py:326-375, scale_formats.py:23-45); the element
+  rounding (`float_to_fp4`) *is* pinned against the reference.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+GROUP = 128
+
+
+# ----------------------------------------------------------------------------------------------
+# Hadamard matrices and transforms
+# ----------------------------------------------------------------------------------------------
+def _legendre(a: int, q: int) -> int:
+    a %= q
+    if a == 0:
+        return 0
+    return 1 if pow(a, (q - 1) // 2, q) == 1 else -1
+
+
+def paley2_hadamard(q: int) -> torch.Tensor:
+    """Paley type-II Hadamard matrix of order 2(q+1), q prime, q = 1 mod 4.
+
+    With S the symmetric conference matrix [[0, 1^T], [1, Q]], Q[i][j] = legendre(j - i), the
+    matrix is [[S + I, S - I], [S - I, -S - I]].  For q = 13 this is exactly the 28x28 literal
+    of quarot/vendor/hadamard_utils.py:277-391 (`get_had28`); tests check that equality.
+    """
+    n = q + 1
+    S = torch.zeros(n, n)
+    S[0, 1:] = 1
+    S[1:, 0] = 1
+    for i in range(q):
+        for j in range(q):
+            S[1 + i, 1 + j] = _legendre(j - i, q)
+    eye = torch.eye(n)
+    top = torch.cat([S + eye, S - eye], dim=1)
+    bot = torch.cat([S - eye, -S - eye], dim=1)
+    return torch.cat([top, bot], dim=0).to(torch.float32)
+
+
+def get_hadK(n: int):
+    """(had_K, K) for a transform length n (quarot/vendor/hadamard_utils.py:5-55), restricted to
+    the orders this path needs: 28 * 2^k (Llama-3 intermediate sizes) and powers of two."""
+    if n % 28 == 0 and _is_pow2(n // 28):
+        return paley2_hadamard(13), 28
+    if _is_pow2(n):
+        return None, 1
+    raise NotImplementedError(f"no Hadamard decomposition restated for n={n}")
+
+
+def _is_pow2(n: int) -> bool:
+    return n > 0 and (n & (n - 1)) == 0
+
+
+def wht_last_axis(x: torch.Tensor) -> torch.Tensor:
+    """Unnormalised Walsh-Hadamard butterflies along the last axis, stages h = 1, 2, 4, ...
+    with (a, b) -> (a + b, a - b) (quarot/__init__.py:39-58).  Every output is formed by the same
+    sequence of fp32 additions as the reference, so results are bit-identical."""
+    n = x.shape[-1]
+    assert _is_pow2(n)
+    h = 1
+    while h < n:
+        y = x.reshape(x.shape[:-1] + (n // (2 * h), 2, h))
+        a = y[..., 0, :]
+        b = y[..., 1, :]
+        x = torch.stack([a + b, a - b], dim=-2).reshape(x.shape[:-1] + (n,))
+        h *= 2
+    return x
+
+
+def full_hadamard_scale(n: int) -> float:
+    """The fp32 factor of hadamard_utils.py:97-99: 1.0 / torch.tensor(n).sqrt()."""
+    return float((1.0 / torch.tensor(n).sqrt()).item())
+
+
+def partial_hadamard_scale(num_heads: int) -> float:
+    """perm_linear.py:96-98: python float 1/sqrt(H), applied to an fp32 tensor."""
+    return float(np.float32(1.0 / math.sqrt(num_heads)))
+
+
+def hadamard_full(x32: torch.Tensor, had_mat, had_k: int) -> torch.Tensor:
+    """matmul_hadU_cuda (quarot/vendor/hadamard_utils.py:92-101) on fp32 rows [M, n].
+
+    view(-1, K, n/K) -> WHT over the last axis -> * fp32 scale -> had_K @ .  The K x K stage is
+    summed over j in ascending order in fp32 (the reference calls an fp32 matmul whose summation
+    order is unspecified; codes derived from it may differ at exact rounding ties)."""
+    M, n = x32.shape
+    scale = torch.tensor(full_hadamard_scale(n), dtype=torch.float32)
+    if had_k == 1:
+        return wht_last_axis(x32) * scale
+    v = wht_last_axis(x32.reshape(M, had_k, n // had_k)) * scale
+    out = torch.zeros_like(v)
+    for j in range(had_k):
+        out = out + had_mat[:, j].reshape(1, had_k, 1) * v[:, j : j + 1, :]
+    return out.reshape(M, n)
+
+
+def hadamard_partial(x32: torch.Tensor, had_dim: int) -> torch.Tensor:
+    """Online partial Hadamard of o_proj (activations/perm_linear.py:89-104, K == 1 branch):
+    WHT across the head index for every head-dim lane, times 1/sqrt(H)."""
+    M, n = x32.shape
+    H = n // had_dim
+    y = x32.reshape(M, H, had_dim).transpose(1, 2)
+    y = wht_last_axis(y.contiguous()) * partial_hadamard_scale(H)
+    return y.transpose(1, 2).reshape(M, n)
+
+
+# ----------------------------------------------------------------------------------------------
+# int4 quantisers
+# ----------------------------------------------------------------------------------------------
+def _round_scale_fp16(s: torch.Tensor) -> torch.Tensor:
+    s16 = torch.clamp(s, max=65504.0).to(torch.float16).to(torch.float32)
+    return torch.where(s16 == 0, torch.ones_like(s16), s16)
+
+
+def quant_act_int4(x: torch.Tensor, a=None, had=None, scale_fp16: bool = False):
+    """Per-token int4 quantiser: PermLinear._quantise_act (activations/perm_linear.py:108-134)
+    with act_fmt = rtn_int4, block_size=-1 (formats/rtn_int.py:43-69).
+
+    x: [M, K] bf16 (or fp32).  a: [K] fp32 or None.  had: None, ("full", had_mat, had_k) or
+    ("partial", had_dim).  Returns (codes int8 [M,K], sx fp32 [M], x32 after scale + Hadamard).
+    scale_fp16 rounds the token scale to fp16 before the division (the storage format the
+    benchmark configuration names); False keeps the reference's fp32 scale."""
+    x32 = x.to(torch.float32)
+    if a is not None:
+        x32 = x32 * a.to(torch.float32)
+    if had is not None:
+        if had[0] == "full":
+            x32 = hadamard_full(x32, had[1], had[2])
+        elif had[0] == "partial":
+            x32 = hadamard_partial(x32, had[1])
+        else:
+            raise ValueError(had[0])
+    amax = x32.abs().amax(dim=1, keepdim=True)
+    s = amax / 7
+    s[amax == 0] = 1.0
+    if scale_fp16:
+        s = _round_scale_fp16(s)
+    q = (x32 / s).round().clamp(-8, 7)
+    return q.to(torch.int8), s.reshape(-1).contiguous(), x32
+
+
+def quant_w_int4(w: torch.Tensor, group: int = GROUP):
+    """Symmetric per-group int4 weight quantiser (formats/rtn_int.py:43-69 with block_size =
+    group; same grouping as pack_int4_weights, fused_dual_scale_kernel.py:156-189), with the
+    group scale rounded to fp16 *before* the division so codes and stored scale agree.
+    Returns (codes int8 [N,K], sw fp16 [N, K/group])."""
+    N, K = w.shape
+    wg = w.to(torch.float32).reshape(N, K // group, group)
+    amax = wg.abs().amax(dim=-1, keepdim=True)
+    s = amax / 7
+    s[amax == 0] = 1.0
+    s = _round_scale_fp16(s)
+    q = (wg / s).round().clamp(-8, 7)
+    return q.reshape(N, K).to(torch.int8), s.reshape(N, K // group).to(torch.float16)
+
+
+def ref_pack_int4(codes: torch.Tensor) -> torch.Tensor:
+    """The reference's packed layout (fused_dual_scale_kernel.py:179-186): unsigned code + 8,
+    low nibble = even k, high nibble = odd k; uint8 [N, K/2]."""
+    u = (codes.to(torch.int16) + 8).to(torch.uint8)
+    return ((u[:, 0::2] & 0xF) | ((u[:, 1::2] & 0xF) << 4)).contiguous()
+
+
+def ref_unpack_int4(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of ref_pack_int4 (dequant_int4_reference, fused_dual_scale_kernel.py:192-206,
+    before the scale is applied)."""
+    N, kh = packed.shape
+    out = torch.empty(N, kh * 2, dtype=torch.int16)
+    out[:, 0::2] = (packed & 0xF).to(torch.int16)
+    out[:, 1::2] = ((packed >> 4) & 0xF).to(torch.int16)
+    return (out - 8).to(torch.int8)
+
+
+def stream_pack_int4(codes: torch.Tensor) -> torch.Tensor:
+    """The library's streaming weight layout: per row, 16-byte chunk c covers k in [32c, 32c+32);
+    byte b = (code[32c+b] & 0xF) | ((code[32c+16+b] & 0xF) << 4), two's complement nibbles."""
+    N, K = codes.shape
+    c = codes.to(torch.int16).reshape(N, K // 32, 2, 16)
+    lo = c[:, :, 0, :] & 0xF
+    hi = c[:, :, 1, :] & 0xF
+    return (lo | (hi << 4)).to(torch.uint8).reshape(N, K // 2).contiguous()
+
+
+# ----------------------------------------------------------------------------------------------
+# GEMM
+# ----------------------------------------------------------------------------------------------
+def acc_int32(qx: torch.Tensor, qw: torch.Tensor, group: int = GROUP) -> torch.Tensor:
+    """Exact per-group integer partial sums acc[m, n, g] = sum_{k in g} qx[m,k] * qw[n,k]
+    (the int32 `tl.dot` of ablation/real_int4_kernel/fused_w4a4_kernel.py:116).  |acc| <= 8192,
+    so an fp32 matmul per group is exact."""
+    M, K = qx.shape
+    N = qw.shape[0]
+    G = K // group
+    xa = qx.to(torch.float32).reshape(M, G, group).permute(1, 0, 2)
+    wa = qw.to(torch.float32).reshape(N, G, group).permute(1, 2, 0)
+    acc = torch.bmm(xa, wa)  # [G, M, N]
+    return acc.permute(1, 2, 0).round().to(torch.int32).contiguous()
+
+
+def epilogue(acc: torch.Tensor, sw: torch.Tensor, r, sx: torch.Tensor, dtype=torch.float32):
+    """Y[m,n] = r[n] * sx[m] * sum_g sw[n,g] * acc[m,n,g]  (fused_w4a4_kernel.py:119 with one
+    activation scale per token; r is the DualQuant row scale).  dtype float32 follows the
+    kernel's order (groups ascending, then one scale product); float64 is the tie-breaker."""
+    M, N, G = acc.shape
+    swf = sw.to(dtype)
+    run = torch.zeros(M, N, dtype=dtype)
+    for g in range(G):
+        run = run + acc[:, :, g].to(dtype) * swf[:, g].reshape(1, N)
+    rr = torch.ones(N, dtype=dtype) if r is None else r.to(dtype)
+    return run * (rr.reshape(1, N) * sx.to(dtype).reshape(M, 1))
+
+
+def dequant_w(qw: torch.Tensor, sw: torch.Tensor, r=None, group: int = GROUP, dtype=torch.float32):
+    """De-quantised weight diag(r) * (codes * group scale)  (dequant_int4_reference,
+    fused_dual_scale_kernel.py:192-206)."""
+    N, K = qw.shape
+    w = qw.to(dtype).reshape(N, K // group, group) * sw.to(dtype).reshape(N, K // group, 1)
+    w = w.reshape(N, K)
+    if r is not None:
+        w = w * r.to(dtype).reshape(N, 1)
+    return w
+
+
+def dequant_matmul(qx, sx, qw, sw, r=None, group: int = GROUP, dtype=torch.float64):
+    """The reference's dequantise-and-matmul check (fused_dual_scale_kernel.py:287-292):
+    (de-quantised activations) @ (de-quantised weights)^T."""
+    xd = qx.to(dtype) * sx.to(dtype).reshape(-1, 1)
+    return xd @ dequant_w(qw, sw, r, group, dtype).T
+
+
+def perm_linear_fakequant(x, a, had, w_dq_bf16: torch.Tensor, scale_fp16: bool = False):
+    """The reference's fake-quant forward (activations/perm_linear.py:136-141): de-quantised
+    activations rounded to bf16, bf16 F.linear against the fake-quant weight."""
+    q, s, _ = quant_act_int4(x, a, had, scale_fp16)
+    xq = (q.to(torch.float32) * s.reshape(-1, 1)).to(torch.bfloat16)
+    return torch.nn.functional.linear(xq, w_dq_bf16)
+
+
+# ----------------------------------------------------------------------------------------------
+# FP4 (parity unpinned except float_to_fp4 -- see the module docstring)
+# ----------------------------------------------------------------------------------------------
+_FP4_GRID = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+def float_to_fp4(x: torch.Tensor) -> torch.Tensor:
+    """Round to the nearest E2M1 value, ties to the even mantissa, saturating at 6
+    (legacy_vendor/torch_quant.py:326-356)."""
+    ax = x.abs()
+    out = torch.zeros_like(ax)
+    out = torch.where(ax > 0.25, torch.full_like(ax, 0.5), out)
+    out = torch.where(ax >= 0.75, torch.full_like(ax, 1.0), out)
+    out = torch.where(ax > 1.25, torch.full_like(ax, 1.5), out)
+    out = torch.where(ax >= 1.75, torch.full_like(ax, 2.0), out)
+    out = torch.where(ax > 2.5, torch.full_like(ax, 3.0), out)
+    out = torch.where(ax >= 3.5, torch.full_like(ax, 4.0), out)
+    out = torch.where(ax > 5.0, torch.full_like(ax, 6.0), out)
+    return torch.where(x < 0, -out, out)
+
+
+def fp4_code(v: torch.Tensor) -> torch.Tensor:
+    """E2M1 bit pattern (sign << 3 | magnitude index) of values already on the FP4 grid."""
+    idx = torch.bucketize(v.abs().contiguous(), _FP4_GRID)
+    idx = torch.clamp(idx, max=7)
+    neg = (v < 0) | ((v == 0) & (torch.signbit(v)))
+    return (idx | (neg.to(torch.int64) << 3)).to(torch.uint8)

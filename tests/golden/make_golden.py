@@ -1,0 +1,158 @@
+"""Generates tests/golden/*.npz by running the REFERENCE's own Python code on CPU.
+
+Run in the authoring container only (it needs the reference checkout):
+
+    python tests/golden/make_golden.py /root/reference
+
+The fixtures are small seeded input/output pairs of the reference functions on the W4A4 hot
+path; tests compare the oracle (oracle/dq_oracle.py) and the CUDA library against them.  The
+reference is imported through three shims, none of which touches the arithmetic recorded here:
+  * BLOCKFMT_BACKEND -> an in-memory stub module exposing `Format` (the reference imports
+    blockfmt at module import time even for rtn_int4; MX/NVFP4 casts are NOT recorded);
+  * stub `accelerate` modules (imported, never called, by quarot/vendor/utils.py);
+  * the reference's own pure-torch stand-in for fast_hadamard_transform.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+
+def _install_shims(ref_root: str) -> None:
+    stub = types.ModuleType("_dq_blockfmt_stub")
+
+    class Format:  # never exercised by the fixtures
+        @classmethod
+        def from_shorthand(cls, s):
+            return cls()
+
+        def cast(self, t, axis=-1):
+            raise RuntimeError("blockfmt stub: block casts are not part of the golden fixtures")
+
+    stub.Format = Format
+    sys.modules["_dq_blockfmt_stub"] = stub
+    os.environ["BLOCKFMT_BACKEND"] = "_dq_blockfmt_stub"
+    import transformers  # noqa: F401  (must precede the accelerate stubs)
+
+    acc = types.ModuleType("accelerate")
+    acc_utils = types.ModuleType("accelerate.utils")
+    for name in ("dispatch_model", "infer_auto_device_map"):
+        setattr(acc, name, lambda *a, **k: None)
+    acc_utils.get_balanced_memory = lambda *a, **k: None
+    acc.utils = acc_utils
+    sys.modules.setdefault("accelerate", acc)
+    sys.modules.setdefault("accelerate.utils", acc_utils)
+    sys.path.insert(0, ref_root)
+    sys.path.insert(0, os.path.join(ref_root, "vendor", "dualscale_kernel_benchmark"))
+
+
+def _seeded_x(M, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    out_ch = torch.randperm(K, generator=g)[: max(1, K // 100)]
+    x[:, out_ch] *= 20
+    return x.to(torch.bfloat16)
+
+
+def main(ref_root: str) -> None:
+    _install_shims(ref_root)
+    import torch.nn as nn
+    from activations.perm_linear import PermLinear  # reference
+    from formats import make_format  # reference
+    import hadamard_utils  # reference (vendored QuaRot)
+    from torch_quant import float_to_fp4  # reference
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    out = {}
+
+    # ---- Hadamard matrix and decomposition --------------------------------------------------
+    had28, k28 = hadamard_utils.get_hadK(14336)
+    assert k28 == 28
+    out["had28"] = had28.numpy().astype(np.int8)
+    _, k1 = hadamard_utils.get_hadK(32)
+    assert k1 == 1
+
+    # ---- per-token rtn_int4 cast (formats/rtn_int.py) ---------------------------------------
+    fmt = make_format("rtn_int4", block_size=-1)
+    g = torch.Generator().manual_seed(1)
+    x = _seeded_x(24, 512, 11)
+    a = torch.exp(torch.randn(512, generator=g) * 0.3).to(torch.float16).to(torch.float32)
+    x32 = x.float() * a
+    x32[5] = 0.0  # all-zero token
+    out["cast_in"] = x32.numpy()
+    out["cast_out"] = fmt.cast(x32).numpy()
+
+    # ---- weight cast with groups of 128 -------------------------------------------------------
+    wfmt = make_format("rtn_int4", block_size=128)
+    w = (torch.randn(64, 512, generator=g) * 0.02).to(torch.bfloat16).float()
+    out["wcast_in"] = w.numpy()
+    out["wcast_out"] = wfmt.cast(w).numpy()
+
+    # ---- PermLinear forward: plain, full Hadamard (28 x 32), partial Hadamard -----------------
+    def run_perm(K, N, M, seed, mode):
+        gg = torch.Generator().manual_seed(seed)
+        lin = nn.Linear(K, N, bias=False).to(torch.bfloat16)
+        wq = wfmt.cast((torch.randn(N, K, generator=gg) * 0.02).to(torch.bfloat16).float())
+        lin.weight.data = wq.to(torch.bfloat16)
+        pl = PermLinear(lin, fmt)
+        aa = torch.exp(torch.randn(K, generator=gg) * 0.3).to(torch.float16).to(torch.float32)
+        pl.set_act_scale(aa)
+        if mode == "full":
+            pl.online_full_had = True
+            pl.had_K, pl.K = hadamard_utils.get_hadK(K)
+        elif mode == "partial":
+            pl.online_partial_had = True
+            pl.had_K, pl.K = hadamard_utils.get_hadK(K // 8)
+            pl.had_dim = 8
+        xx = _seeded_x(M, K, seed + 100)
+        with torch.no_grad():
+            xq = pl._quantise_act(xx)
+            y = pl(xx)
+        return {
+            "x": xx.view(torch.int16).numpy(),  # bf16 bit patterns
+            "a": aa.numpy(),
+            "w_bf16": lin.weight.data.view(torch.int16).numpy(),
+            "xq_bf16": xq.view(torch.int16).numpy(),
+            "y_bf16": y.view(torch.int16).numpy(),
+        }
+
+    for tag, (K, N, M, mode) in {
+        "plain": (512, 128, 20, "none"),
+        "full": (896, 128, 12, "full"),  # 896 = 28 * 32
+        "partial": (256, 128, 12, "partial"),  # 32 heads x head_dim 8
+    }.items():
+        for k, v in run_perm(K, N, M, 7, mode).items():
+            out[f"perm_{tag}_{k}"] = v
+
+    # ---- Hadamard alone (fp32) ------------------------------------------------------------------
+    xh = torch.randn(6, 896, generator=g)
+    hk, kk = hadamard_utils.get_hadK(896)
+    out["hadfull_in"] = xh.numpy()
+    out["hadfull_out"] = hadamard_utils.matmul_hadU_cuda(xh.clone(), hk, kk).numpy()
+
+    # ---- reference packing / dequant (vendor kernel directory) ---------------------------------
+    import fused_dual_scale_kernel as fdk  # needs triton importable; no GPU used here
+
+    wp = torch.randn(32, 256, generator=g)
+    packed, scale1 = fdk.pack_int4_weights(wp, 128)
+    out["refpack_w"] = wp.numpy()
+    out["refpack_packed"] = packed.numpy()
+    out["refpack_scale_bf16"] = scale1.view(torch.int16).numpy()
+    out["refpack_dequant"] = fdk.dequant_int4_reference(packed, scale1, 128).numpy()
+
+    # ---- FP4 element rounding ---------------------------------------------------------------------
+    grid = torch.cat([torch.linspace(-7, 7, 449), torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])])
+    out["fp4_in"] = grid.numpy()
+    out["fp4_out"] = float_to_fp4(grid.clone()).numpy()
+
+    path = os.path.join(here, "reference_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

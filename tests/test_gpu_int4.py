@@ -1,0 +1,238 @@
+"""GPU parity tests of the int4 path: every call goes through the C ABI (ctypes) and is compared
+with the CPU oracle on the same seeded inputs.  Integer work is bit-exact; fp32 outputs within
+1e-3 relative (tolerance from the benchmark specification)."""
+import numpy as np
+import pytest
+import torch
+
+from dualquant_b200 import _lib, ops, synthetic
+from oracle import dq_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+REL_TOL = 1e-3
+
+
+def _rel_err(y, ref):
+    return ((y.double() - ref.double()).abs().max() / ref.double().abs().max()).item()
+
+
+def _status_ok():
+    _lib.device_status(0)
+
+
+def _operands(M, N, K, seed=0, scale_fp16=True):
+    x = synthetic.make_x(M, K, seed)
+    w = synthetic.make_w(N, K, seed)
+    r, c = synthetic.make_scales(N, K, seed)
+    a = 1.0 / c
+    qx, sx, _ = O.quant_act_int4(x, a, None, scale_fp16)
+    qw, sw = O.quant_w_int4(w)
+    return x, w, r, a, qx, sx, qw, sw
+
+
+# ------------------------------------------------------------------------------------------
+# weights
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("N,K", [(128, 128), (200, 384), (4096, 4096)])
+def test_quant_and_pack_weights_bit_exact(N, K):
+    w = synthetic.make_w(N, K, 5)
+    w[3, :128] = 0  # an all-zero group
+    qw, sw = O.quant_w_int4(w)
+    codes, sw_g = ops.quant_w_int4(w.to(DEV))
+    assert torch.equal(codes.cpu(), qw)
+    assert torch.equal(sw_g.cpu().view(torch.int16), sw.view(torch.int16))
+    pw = ops.pack_w_int4(codes, sw_g)
+    assert torch.equal(pw.w_packed.cpu(), O.stream_pack_int4(qw))
+    assert torch.equal(pw.sw_t.cpu(), sw.T.contiguous())
+    assert torch.equal(ops.unpack_w_int4(pw).cpu(), qw)
+    # the reference's packed form as the source gives the same artefact
+    pw2 = ops.pack_w_int4(None, sw_g, ref_packed=O.ref_pack_int4(qw).to(DEV))
+    assert torch.equal(pw2.w_packed, pw.w_packed)
+    _status_ok()
+
+
+def test_pack_from_reference_golden(golden):
+    packed = torch.from_numpy(golden["refpack_packed"])
+    codes = O.ref_unpack_int4(packed)
+    sw = torch.ones(32, 2, dtype=torch.float16)
+    pw = ops.pack_w_int4(None, sw.to(DEV), ref_packed=packed.to(DEV))
+    assert torch.equal(ops.unpack_w_int4(pw).cpu(), codes)
+
+
+# ------------------------------------------------------------------------------------------
+# activation quantiser
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,K", [(1, 128), (3, 4096), (17, 14336), (5, 18944), (64, 8), (2, 40000)])
+@pytest.mark.parametrize("scale_fp16", [False, True])
+def test_act_quant_bit_exact(M, K, scale_fp16):
+    x = synthetic.make_x(M, K, 3)
+    if M > 1:
+        x[1] = 0  # all-zero token -> scale 1, codes 0
+    _, c = synthetic.make_scales(8, K, 3)
+    a = 1.0 / c
+    qx, sx, _ = O.quant_act_int4(x, a, None, scale_fp16)
+    codes, sxg = ops.quant_act_int4(x.to(DEV), a.to(DEV), None, scale_fp16)
+    assert torch.equal(sxg.cpu(), sx)
+    assert torch.equal(codes.cpu(), qx)
+    # without a column scale
+    qx0, sx0, _ = O.quant_act_int4(x, None, None, scale_fp16)
+    codes0, sx0g = ops.quant_act_int4(x.to(DEV), None, None, scale_fp16)
+    assert torch.equal(codes0.cpu(), qx0) and torch.equal(sx0g.cpu(), sx0)
+    _status_ok()
+
+
+def test_act_quant_empty_and_strided():
+    x = synthetic.make_x(6, 512, 1).to(DEV)
+    codes, sx = ops.quant_act_int4(x[:0], None, None, False)
+    assert codes.shape == (0, 512) and sx.shape == (0,)
+    wide = torch.zeros(6, 1024, dtype=torch.bfloat16, device=DEV)
+    wide[:, :512] = x
+    c1, s1 = ops.quant_act_int4(wide[:, :512], None, None, False)  # ldx = 1024
+    c2, s2 = ops.quant_act_int4(x, None, None, False)
+    assert torch.equal(c1, c2) and torch.equal(s1, s2)
+
+
+def test_act_quant_golden_reference_cast(golden):
+    x32 = torch.from_numpy(golden["cast_in"])
+    out = ops.fakequant_act_int4(x32.to(DEV), None, None, False)
+    assert torch.equal(out.cpu(), torch.from_numpy(golden["cast_out"]))
+
+
+def test_act_quant_rejects_bad_arguments():
+    x = synthetic.make_x(2, 100, 1).to(DEV)  # K % 8 != 0
+    with pytest.raises(ValueError):
+        ops.quant_act_int4(x, None, None, False)
+    with pytest.raises(RuntimeError):
+        ops.quant_act_int4(synthetic.make_x(2, 128, 1), None, None, False)  # CPU tensor
+
+
+# ------------------------------------------------------------------------------------------
+# Hadamard
+# ------------------------------------------------------------------------------------------
+def _full_had(K):
+    had, k = O.get_hadK(K)
+    return ops.Hadamard(_lib.HAD_FULL, k, 0, O.full_hadamard_scale(K),
+                        None if had is None else had.to(DEV)), ("full", had, k)
+
+
+@pytest.mark.parametrize("M,K", [(3, 896), (2, 14336), (4, 1024)])
+def test_full_hadamard_bit_exact(M, K):
+    hd, ohad = _full_had(K)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(M, K, generator=g)
+    ref = O.hadamard_full(x, ohad[1], ohad[2])
+    got = ops.hadamard_f32(x.to(DEV), hd)
+    assert torch.equal(got.cpu(), ref)
+    xb = synthetic.make_x(M, K, 4)
+    qx, sx, _ = O.quant_act_int4(xb, None, ohad, True)
+    codes, sxg = ops.quant_act_int4(xb.to(DEV), None, hd, True)
+    assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
+    _status_ok()
+
+
+def test_partial_hadamard_bit_exact():
+    M, K, d = 5, 4096, 128
+    hd = ops.Hadamard(_lib.HAD_PARTIAL, 1, d, O.partial_hadamard_scale(K // d), None)
+    xb = synthetic.make_x(M, K, 6)
+    _, c = synthetic.make_scales(8, K, 6)
+    a = 1.0 / c
+    qx, sx, _ = O.quant_act_int4(xb, a, ("partial", d), False)
+    codes, sxg = ops.quant_act_int4(xb.to(DEV), a.to(DEV), hd, False)
+    assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
+
+
+def test_hadamard_golden(golden):
+    x = torch.from_numpy(golden["hadfull_in"])
+    hd, _ = _full_had(896)
+    got = ops.hadamard_f32(x.to(DEV), hd).cpu()
+    ref = torch.from_numpy(golden["hadfull_out"])
+    assert torch.allclose(got, ref, rtol=0, atol=2e-6 * ref.abs().max().item())
+
+
+# ------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------
+def _gpu_weight(qw, sw):
+    return ops.pack_w_int4(qw.to(DEV), sw.to(DEV))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (3, 128, 256), (16, 256, 512), (17, 384, 384),
+                                   (100, 200, 640), (130, 128, 1024)])
+def test_gemm_accumulators_bit_exact(M, N, K):
+    _, _, _, _, qx, sx, qw, sw = _operands(M, N, K, seed=M)
+    pw = _gpu_weight(qw, sw)
+    acc = ops.gemm_w4a4_int4_acc(qx.to(DEV), pw)
+    _status_ok()
+    assert torch.equal(acc.cpu(), O.acc_int32(qx, qw))
+
+
+def test_gemm_accumulators_extreme_codes():
+    # every product at its largest magnitude: (-8) * (-8) * 128 = 8192 per group
+    M, N, K = 16, 128, 256
+    qx = torch.full((M, K), -8, dtype=torch.int8)
+    qw = torch.full((N, K), -8, dtype=torch.int8)
+    qw[::2] = 7
+    pw = _gpu_weight(qw, torch.ones(N, K // 128, dtype=torch.float16))
+    acc = ops.gemm_w4a4_int4_acc(qx.to(DEV), pw)
+    assert torch.equal(acc.cpu(), O.acc_int32(qx, qw))
+
+
+@pytest.mark.parametrize("M,N,K,tn,split", [
+    (1, 128, 128, 0, 0), (1, 256, 1024, 16, 1), (1, 256, 1024, 16, 8), (8, 384, 512, 16, 4),
+    (16, 4096, 4096, 0, 0), (20, 256, 512, 32, 2), (32, 512, 1024, 32, 8), (50, 200, 640, 64, 1),
+    (64, 256, 2048, 64, 4), (128, 256, 512, 128, 1), (128, 384, 1024, 128, 2),
+    (300, 640, 384, 128, 1), (7, 136, 256, 0, 0),
+])
+def test_gemm_output_matches_oracle(M, N, K, tn, split):
+    _, _, r, _, qx, sx, qw, sw = _operands(M, N, K, seed=M + N)
+    pw = _gpu_weight(qw, sw)
+    y = ops.gemm_w4a4_int4(qx.to(DEV), sx.to(DEV), pw, r.to(DEV), token_tile=tn, split_k=split)
+    _status_ok()
+    ref64 = O.dequant_matmul(qx, sx, qw, sw, r)
+    assert _rel_err(y.cpu(), ref64) < REL_TOL
+    ref32 = O.epilogue(O.acc_int32(qx, qw), sw, r, sx)
+    assert _rel_err(y.cpu(), ref32) < 1e-5
+    # bf16 output and no row scale
+    yb = ops.gemm_w4a4_int4(qx.to(DEV), sx.to(DEV), pw, None, out_dtype=torch.bfloat16,
+                            token_tile=tn, split_k=split)
+    refb = O.dequant_matmul(qx, sx, qw, sw, None)
+    assert _rel_err(yb.float().cpu(), refb) < 8e-3  # bf16 rounding of the output
+
+
+def test_gemm_is_deterministic_and_linear_in_scales():
+    M, N, K = 16, 512, 4096
+    _, _, r, _, qx, sx, qw, sw = _operands(M, N, K, seed=9)
+    pw = _gpu_weight(qw, sw)
+    args = (qx.to(DEV), sx.to(DEV), pw, r.to(DEV))
+    y1 = ops.gemm_w4a4_int4(*args)
+    y2 = ops.gemm_w4a4_int4(*args)
+    assert torch.equal(y1, y2)
+    y3 = ops.gemm_w4a4_int4(qx.to(DEV), (2 * sx).to(DEV), pw, (4 * r).to(DEV))
+    assert torch.equal(y3, 8 * y1)  # power-of-two scaling is exact in fp32
+
+
+def test_config0_full_size_against_oracle():
+    # M=2048, K=4096, N=4096, seed 0: the reference's own CPU-runnable configuration
+    M, N, K = 2048, 4096, 4096
+    x, w, r, a, qx, sx, qw, sw = _operands(M, N, K, seed=0)
+    codes, sxg = ops.quant_act_int4(x.to(DEV), a.to(DEV), None, True)
+    assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
+    cw, swg = ops.quant_w_int4(w.to(DEV))
+    assert torch.equal(cw.cpu(), qw)
+    pw = ops.pack_w_int4(cw, swg)
+    y = ops.gemm_w4a4_int4(codes, sxg, pw, r.to(DEV))
+    _status_ok()
+    ref = O.dequant_matmul(qx, sx, qw, sw, r, dtype=torch.float32)
+    assert _rel_err(y.cpu(), ref) < REL_TOL
+    # one-call linear gives the same bits as the two-step path
+    y2 = ops.linear_w4a4_int4(x.to(DEV), a.to(DEV), None, pw, r.to(DEV), scale_fp16=True)
+    assert torch.equal(y2, y)
+
+
+def test_gemm_rejects_bad_arguments():
+    qx = torch.zeros(4, 192, dtype=torch.int8, device=DEV)
+    pw = ops.PackedInt4Weight(torch.zeros(128, 96, dtype=torch.uint8, device=DEV),
+                              torch.ones(1, 128, dtype=torch.float16, device=DEV), 128, 192)
+    with pytest.raises(ValueError):
+        ops.gemm_w4a4_int4(qx, torch.ones(4, device=DEV), pw)  # K % 128 != 0
