@@ -1,0 +1,494 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4 int4 dual-scale hot path (decode-shaped GEMM sweep).
+
+    python bench.py --gpus N --steps K --warmup W            # this library, on the GPU(s)
+    python bench.py --impl reference --steps K --warmup W    # the CPU path, host cores
+
+Workload (N=1): every linear of one Llama-3.1-8B-architecture layer (qkv 4096->6144,
+o 4096->4096, gate+up 4096->28672, down 14336->4096) at M in {1, 8, 16, 32, 64, 128}, int4
+weights in groups of 128 with fp16 group scales, DualQuant row scale r and column scale 1/c,
+per-token int4 activations with an fp16 scale, fp32 output.  One "step" is one pass over all
+24 (linear, M) pairs: activation quantiser + GEMM each.  The metric is decode GB/s: algorithmic
+bytes of the step (packed weights + group scales + r + c + bf16 X + fp32 Y) divided by time.
+Each M value uses its own copy of the four weight matrices (6 x 109 MB = 655 MB in rotation,
+5x the 126 MB L2), so every launch streams its weights from HBM.
+
+With N > 1 ranks each rank owns a contiguous N/ranks slice of the output rows of every weight
+(column-parallel, no collective); the reported value is total bytes over the slowest rank.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from dualquant_b200 import synthetic  # noqa: E402
+
+METRIC = "w4a4_int4_decode_gemm_sweep_GBps"
+UNIT = "GB/s"
+WORKLOAD = "config1: Llama-3.1-8B layer linears (qkv,o,gate_up,down) x M{1,8,16,32,64,128}, int4 dual-scale, G=128"
+
+
+def _step_bytes(n_split: int = 1) -> int:
+    total = 0
+    for _, K, N in synthetic.LLAMA31_8B_LINEARS:
+        for M in synthetic.DECODE_M:
+            total += synthetic.int4_gemm_bytes(M, N // n_split, K) * n_split
+    return total
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            p = [v.strip() for v in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                smax.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, p[5:9]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+class Workload:
+    def __init__(self, dev, rank: int, world: int, seed: int = 0):
+        from dualquant_b200 import ops
+
+        self.ops = ops
+        self.dev = dev
+        self.world = world
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.linears = []  # per linear: dict(name,K,N_local,a,r,weights[copy])
+        n_copies = len(synthetic.DECODE_M)
+        for name, K, N in synthetic.LLAMA31_8B_LINEARS:
+            assert N % world == 0
+            nl = N // world
+            r, c = synthetic.make_scales(N, K, seed)
+            a = (1.0 / c).to(dev)
+            r_local = r[rank * nl:(rank + 1) * nl].contiguous().to(dev)
+            copies = []
+            for _ in range(n_copies):
+                w = (torch.randn(nl, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+                codes, sw = ops.quant_w_int4(w)
+                copies.append(ops.pack_w_int4(codes, sw))
+                del w, codes, sw
+            self.linears.append({"name": name, "K": K, "N": nl, "a": a, "r": r_local, "w": copies})
+        self.x, self.x_host, self.y, self.y_host, self.scratch = {}, {}, {}, {}, {}
+        for M in synthetic.DECODE_M:
+            for lin in self.linears:
+                K, nl = lin["K"], lin["N"]
+                if (M, K) not in self.x:
+                    xh = synthetic.make_x(M, K, seed).pin_memory()
+                    self.x_host[(M, K)] = xh
+                    self.x[(M, K)] = xh.to(dev)
+                self.y[(M, lin["name"])] = torch.empty(M, nl, dtype=torch.float32, device=dev)
+                self.y_host[(M, lin["name"])] = torch.empty(M, nl, dtype=torch.float32).pin_memory()
+                nbytes = ops.linear_scratch_bytes(M, nl, K)
+                self.scratch[(M, lin["name"])] = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize(dev)
+
+    def step(self):
+        """Device-resident pass: quantiser + GEMM for all 24 (linear, M) pairs."""
+        ops = self.ops
+        for mi, M in enumerate(synthetic.DECODE_M):
+            for lin in self.linears:
+                ops.linear_w4a4_int4(self.x[(M, lin["K"])], lin["a"], None, lin["w"][mi], lin["r"],
+                                     scale_fp16=True, scratch=self.scratch[(M, lin["name"])],
+                                     out=self.y[(M, lin["name"])])
+
+    def prequantise(self):
+        ops = self.ops
+        self.q = {}
+        for M in synthetic.DECODE_M:
+            for lin in self.linears:
+                self.q[(M, lin["name"])] = ops.quant_act_int4(self.x[(M, lin["K"])], lin["a"], None, True)
+
+    def gemm_only_step(self):
+        ops = self.ops
+        for mi, M in enumerate(synthetic.DECODE_M):
+            for lin in self.linears:
+                codes, sx = self.q[(M, lin["name"])]
+                ops.gemm_w4a4_int4(codes, sx, lin["w"][mi], lin["r"], out=self.y[(M, lin["name"])])
+
+    def e2e_step(self):
+        """Host buffers in, host buffers out: H2D of X, the one-call linear, D2H of Y."""
+        ops = self.ops
+        for mi, M in enumerate(synthetic.DECODE_M):
+            for lin in self.linears:
+                x = self.x[(M, lin["K"])]
+                x.copy_(self.x_host[(M, lin["K"])], non_blocking=True)
+                y = self.y[(M, lin["name"])]
+                ops.linear_w4a4_int4(x, lin["a"], None, lin["w"][mi], lin["r"], scale_fp16=True,
+                                     scratch=self.scratch[(M, lin["name"])], out=y)
+                self.y_host[(M, lin["name"])].copy_(y, non_blocking=True)
+
+    def e2e_bytes(self):
+        h2d = d2h = 0
+        for M in synthetic.DECODE_M:
+            for lin in self.linears:
+                h2d += M * lin["K"] * 2
+                d2h += M * lin["N"] * 4
+        return h2d, d2h
+
+
+def _capture(fn, dev):
+    """CUDA graph of one call of fn (after a warm-up on a side stream)."""
+    s = torch.cuda.Stream(device=dev)
+    s.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream(dev).wait_stream(s)
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph
+
+
+def _time_loop(run, steps, warmup, dev, barrier):
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize(dev)
+    barrier()
+    torch.cuda.synchronize(dev)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    barrier()
+    return e0.elapsed_time(e1)  # ms
+
+
+def run_gpu(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the library has no CPU path "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    from dualquant_b200 import _lib
+
+    wl = Workload(dev, rank, world, seed=0)
+    step_bytes = _step_bytes(world)
+    launches_per_step = 2 * len(synthetic.DECODE_M) * len(wl.linears)
+
+    # ---- device-resident: CUDA graph of one step ---------------------------------------------
+    graph = _capture(wl.step, dev) if not args.no_graph else None
+    run = graph.replay if graph is not None else wl.step
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = max_over_ranks(_time_loop(run, args.steps, args.warmup, dev, barrier))
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- dominant kernel alone (GEMM launches only) for the roofline -------------------------
+    wl.prequantise()
+    g2 = _capture(wl.gemm_only_step, dev) if not args.no_graph else None
+    run2 = g2.replay if g2 is not None else wl.gemm_only_step
+    ms2 = max_over_ranks(_time_loop(run2, args.steps, args.warmup, dev, barrier)) / args.steps
+    n_gemm = len(synthetic.DECODE_M) * len(wl.linears)
+    peaks, peak_kind = _peaks()
+    achieved = step_bytes / world / (ms2 * 1e-3) / 1e9  # per GPU
+    roofline = {
+        "bound": "hbm", "kernel": "gemm_w4a4_int4_kernel",
+        "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "peak_kind": peak_kind,
+        "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+        "avg_launch_us": round(ms2 * 1e3 / n_gemm, 2),
+        "algorithmic_bytes_per_launch": step_bytes // world // n_gemm,
+        "traffic": None,
+    }
+    prof = os.path.join(ROOT, "profiles", "gemm_w4a4_int4_decode.traffic.json")
+    if os.path.exists(prof):
+        with open(prof) as f:
+            roofline["traffic"] = json.load(f).get("dram_bytes_per_launch")
+
+    # ---- end to end through the C ABI with host buffers -----------------------------------------
+    ms3 = max_over_ranks(_time_loop(wl.e2e_step, args.steps, args.warmup, dev, barrier)) / args.steps
+    h2d, d2h = wl.e2e_bytes()
+    e2e = {"value": round(step_bytes / (ms3 * 1e-3) / 1e9, 1), "unit": UNIT,
+           "ms_per_step": round(ms3, 4), "h2d_bytes_per_step": h2d * world,
+           "d2h_bytes_per_step": d2h * world}
+    _lib.device_status(local_rank)
+
+    detail = None
+    if args.detail:
+        detail = per_shape_detail(wl, dev, args)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4xint4->int32 (kind::i8), fp32 epilogue",
+            "data": "synthetic", "impl": "dualquant_b200",
+            "config": {"workload": WORKLOAD, "parallelism": f"column-parallel over N x{world}, no collective",
+                       "l2": "6 weight copies in rotation (655 MB > 5x L2): inputs larger than L2",
+                       "launch": "CUDA graph replay of one step" if graph is not None else "stream launches",
+                       "step_algorithmic_bytes": step_bytes},
+            "roofline": roofline,
+            "e2e": e2e,
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if not args.skip_cpu and world >= 1:
+            line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_budget)
+        if detail is not None:
+            line["per_shape_GBps"] = detail
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_case(args):
+    """One (linear, M) pair alone, a handful of launches: the small case profilers capture.
+    --case NAME:M[:TN:SPLIT], e.g. gate_up:16 ; --iters launches after 3 warm-up launches."""
+    from dualquant_b200 import _lib, ops
+
+    parts = args.case.split(":")
+    name, M = parts[0], int(parts[1])
+    tn = int(parts[2]) if len(parts) > 2 else 0
+    split = int(parts[3]) if len(parts) > 3 else 0
+    K, N = {n: (k, nn) for n, k, nn in synthetic.LLAMA31_8B_LINEARS}[name]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    copies = []
+    n_copies = max(3, int(300e6 // (N * K // 2)) + 1)
+    for _ in range(n_copies):
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        codes, sw = ops.quant_w_int4(w)
+        copies.append(ops.pack_w_int4(codes, sw))
+        del w, codes, sw
+    r, c = synthetic.make_scales(N, K, 0)
+    x = synthetic.make_x(M, K, 0).to(dev)
+    qx, sx = ops.quant_act_int4(x, (1.0 / c).to(dev), None, True)
+    y = torch.empty(M, N, dtype=torch.float32, device=dev)
+    rr = r.to(dev)
+    for i in range(3):
+        ops.gemm_w4a4_int4(qx, sx, copies[i % n_copies], rr, out=y, token_tile=tn, split_k=split)
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.iters):
+        ops.gemm_w4a4_int4(qx, sx, copies[i % n_copies], rr, out=y, token_tile=tn, split_k=split)
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.device_status(0)
+    ms = e0.elapsed_time(e1) / args.iters
+    b = synthetic.int4_gemm_bytes(M, N, K)
+    print(json.dumps({"case": args.case, "iters": args.iters, "us_per_launch": round(ms * 1e3, 2),
+                      "algorithmic_bytes": b, "GBps": round(b / ms / 1e6, 1),
+                      "weight_copies": n_copies}), flush=True)
+
+
+def per_shape_detail(wl, dev, args):
+    """GEMM-only GB/s of each (linear, M), timed as a graph that cycles through the six weight
+    copies of that linear (so each launch reads weights that left L2)."""
+    ops = wl.ops
+    out = {}
+    for lin in wl.linears:
+        row = []
+        for M in synthetic.DECODE_M:
+            codes, sx = wl.q[(M, lin["name"])]
+            y = wl.y[(M, lin["name"])]
+
+            def fn():
+                for c in range(len(lin["w"])):
+                    ops.gemm_w4a4_int4(codes, sx, lin["w"][c], lin["r"], out=y)
+
+            g = _capture(fn, dev)
+            ms = _time_loop(g.replay, 20, 5, dev, lambda: None) / 20 / len(lin["w"])
+            b = synthetic.int4_gemm_bytes(M, lin["N"], lin["K"])
+            row.append(round(b / (ms * 1e-3) / 1e9, 1))
+        out[lin["name"]] = row
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm (the oracle port of the reference's PyTorch path)
+# ------------------------------------------------------------------------------------------------
+class CpuWorkload:
+    """The reference's CPU path for the same step: PermLinear.forward as fake-quant
+    (activations/perm_linear.py:108-141) - scale, per-token int4 cast, bf16 F.linear against the
+    fake-quant bf16 weight - restated by oracle/dq_oracle.py.  Weights of the sample are built
+    once (untimed), like the reference's offline weight quantisation."""
+
+    def __init__(self, m_values, seed=0):
+        from oracle import dq_oracle as O
+
+        self.O = O
+        self.m_values = m_values
+        self.linears = []
+        for name, K, N in synthetic.LLAMA31_8B_LINEARS:
+            w = synthetic.make_w(N, K, seed)
+            qw, sw = O.quant_w_int4(w)
+            r, c = synthetic.make_scales(N, K, seed)
+            wdq = O.dequant_w(qw, sw, r).to(torch.bfloat16)
+            self.linears.append({"name": name, "K": K, "N": N, "a": 1.0 / c, "w": wdq})
+        self.x = {(M, K): synthetic.make_x(M, K, seed) for M in m_values for _, K, _ in synthetic.LLAMA31_8B_LINEARS}
+
+    def bytes(self):
+        return sum(synthetic.int4_gemm_bytes(M, lin["N"], lin["K"]) for M in self.m_values for lin in self.linears)
+
+    def step(self):
+        O = self.O
+        out = None
+        with torch.no_grad():
+            for M in self.m_values:
+                for lin in self.linears:
+                    out = O.perm_linear_fakequant(self.x[(M, lin["K"])], lin["a"], None, lin["w"], True)
+        return out
+
+
+def cpu_baseline(budget_s: float = 15.0):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    wl = CpuWorkload(synthetic.DECODE_M)
+    wl.step()  # warm-up
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        wl.step()
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 500:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return {"value": round(wl.bytes() / dt / 1e9, 3), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} pass(es) of the full step (24 linears), {dt:.2f} s each, torch {torch.__version__} bf16 F.linear on fake-quant weights",
+            "ms_per_step": round(dt * 1e3, 1)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    wl = CpuWorkload(synthetic.DECODE_M)
+    for _ in range(max(1, min(args.warmup, 2))):
+        wl.step()
+    steps = max(1, min(args.steps, 100))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        wl.step()
+    dt = (time.perf_counter() - t0) / steps
+    value = round(wl.bytes() / dt / 1e9, 3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(dt * 1e3, 2),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 fake-quant (fp32 quantiser)",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "reference CPU path (PermLinear fake-quant) restated by the oracle; the reference is Python and is not present on the GPU box"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{steps} timed pass(es) of the full step (24 linears)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="dualquant_b200", choices=["dualquant_b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--detail", action="store_true", help="add per-(linear, M) GEMM GB/s")
+    ap.add_argument("--case", default=None, help="NAME:M[:TN:SPLIT] - run one (linear, M) GEMM alone")
+    ap.add_argument("--iters", type=int, default=6)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -313,6 +313,7 @@ extern "C" int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a
                                  const dq_hadamard_desc* had, int M, int K, int8_t* codes,
                                  float* sx, int scale_fp16, void* stream) {
   if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
   DQ_REQUIRE(codes != nullptr && sx != nullptr, DQ_ERR_NULL, "codes / sx is null");
   return launch_act(static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, had, M, K, codes, sx,
                     nullptr, MODE_CODES, scale_fp16, static_cast<cudaStream_t>(stream));
@@ -322,6 +323,7 @@ extern "C" int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, c
                                      const dq_hadamard_desc* had, int M, int K, float* out,
                                      int scale_fp16, void* stream) {
   if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
   DQ_REQUIRE(out != nullptr, DQ_ERR_NULL, "out is null");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (x_is_f32)

@@ -415,6 +415,7 @@ extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const 
                                     int split_k) {
   DeviceState* st = current_state();
   if (st == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
   int rc = check_gemm_args(codes, w_packed, M, N, K, G);
   if (rc != DQ_OK) return rc;
   DQ_REQUIRE(sx != nullptr && sw_t != nullptr && y != nullptr, DQ_ERR_NULL, "null sx / sw_t / y");
