@@ -70,7 +70,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu_index), "-lms", "100"],
+                 "-i", str(self.gpu_index), "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -259,7 +259,6 @@ def run_gpu(args):
     if rank == 0:
         sampler.start()
     ms = max_over_ranks(_time_loop(run, args.steps, args.warmup, dev, barrier))
-    clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -290,6 +289,8 @@ def run_gpu(args):
     e2e = {"value": round(step_bytes / (ms3 * 1e-3) / 1e9, 1), "unit": UNIT,
            "ms_per_step": round(ms3, 4), "h2d_bytes_per_step": h2d * world,
            "d2h_bytes_per_step": d2h * world}
+    # clock samples cover the three timed regions above (each is short: tens of ms)
+    clocks = sampler.stop() if rank == 0 else None
     _lib.device_status(local_rank)
 
     detail = None

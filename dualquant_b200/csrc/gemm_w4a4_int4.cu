@@ -15,7 +15,8 @@
 //               into the group scale (exact: power of two).
 //   warps 4-11  epilogue: tcgen05.ld of the group accumulator, run += float(acc) * sw, final scale
 //               by r[n]*sx[m], store / split-K reduction.
-//   warp 12     TMA producer (one lane): packed weight tiles and int8 activation tiles.
+//   warp 12     TMA producer (one lane): packed weight tiles (contiguous 8 KB bulk copies) and
+//               int8 activation tiles (tiled, 128B swizzle).
 //   warp 13     TMEM allocation, UMMA issue (one lane).
 //
 // Split-K (decode shapes): the CTAs that share an output tile form a thread-block cluster along
@@ -27,7 +28,27 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+// Optional timeline instrumentation (development builds only, -DDQ_GEMM_TRACE): CTA (0,0,0)
+// records clock64() at the hand-off points of each role for the first 64 stages.
+#ifdef DQ_GEMM_TRACE
+#define DQ_TR(role, i, k)                                                              \
+  do {                                                                                 \
+    if (trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64) \
+      trace[((role) * 64 + (i)) * 8 + (k)] = clock64();                                \
+  } while (0)
+#define DQ_TRACE_PARAM , long long* trace
+#define DQ_TRACE_ARG , dq::g_trace
+#else
+#define DQ_TR(role, i, k) do {} while (0)
+#define DQ_TRACE_PARAM
+#define DQ_TRACE_ARG
+#endif
+
 namespace dq {
+
+#ifdef DQ_GEMM_TRACE
+long long* g_trace = nullptr;
+#endif
 
 constexpr int kBN = 128;           // weight rows per CTA tile (UMMA M)
 constexpr int kThreads = 448;
@@ -38,11 +59,13 @@ constexpr int kWaBytes = kBN * kGroup;      // unpacked stage: 16 KB
 
 template <int TN>
 struct Cfg {
-  static constexpr int SP = (TN == 16) ? 8 : (TN == 32) ? 6 : (TN == 64) ? 8 : 6;
-  static constexpr int SA = (TN <= 32) ? 2 : 3;
-  static constexpr int SX = (TN == 128) ? 3 : 4;
+  // stage counts: the packed-weight ring is as deep as shared memory allows, because at decode
+  // shapes the kernel is bound by bytes in flight per SM (two CTAs per SM for TN <= 64)
+  static constexpr int SP = (TN == 16) ? 7 : (TN == 128) ? 12 : 6;
+  static constexpr int SA = (TN <= 64) ? 2 : 3;
+  static constexpr int SX = (TN == 16) ? 8 : (TN == 32) ? 6 : (TN == 64) ? 3 : 4;
   static constexpr int kXBytes = TN * kGroup;
-  static constexpr int kMinCtas = (TN <= 32) ? 2 : 1;
+  static constexpr int kMinCtas = (TN <= 64) ? 2 : 1;
   static constexpr int kOffA = 0;
   static constexpr int kOffX = kOffA + SA * kWaBytes;
   static constexpr int kOffP = kOffX + SX * kXBytes;
@@ -60,12 +83,12 @@ enum { SITE_TMA_P = 1, SITE_TMA_X, SITE_UNPACK_FULL, SITE_UNPACK_EMPTY, SITE_MMA
 
 template <int TN, bool DUMP>
 __global__ void __launch_bounds__(kThreads, Cfg<TN>::kMinCtas)
-gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
+gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
                       const __half* __restrict__ sw_t, const float* __restrict__ r,
                       const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
                       int32_t* __restrict__ acc_dump, int M, int N, int K, int groups_per_split,
-                      int split_k, int w_stream_once, int* status) {
+                      int split_k, int w_stream_once, int* status DQ_TRACE_PARAM) {
   using C = Cfg<TN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -87,6 +110,7 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
   const int lane = tid & 31;
   const int n0 = blockIdx.x * kBN;
   const int t0 = blockIdx.y * TN;
+  const int t0_tok = t0;
   const int total_groups = K / kGroup;
   const int g_begin = blockIdx.z * groups_per_split;
   int g_end = g_begin + groups_per_split;
@@ -106,7 +130,6 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
     tmem_relinquish();
   }
   if (warp == 12 && lane == 0) {
-    tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
   }
   tc_fence_before();
@@ -123,7 +146,9 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
     for (int i = 0; i < ng; ++i) {
       const int sp = i % C::SP, sa = i % C::SA;
       if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
+      if (tid == 0) DQ_TR(0, i, 0);
       if (!mbar_wait(&empty_a[sa], ((i / C::SA) & 1) ^ 1, abort_flag, SITE_UNPACK_EMPTY)) break;
+      if (tid == 0) DQ_TR(0, i, 1);
       const uint8_t* src = smem + C::kOffP + sp * kWpBytes;
       uint8_t* dst = smem + C::kOffA + sa * kWaBytes;
 #pragma unroll
@@ -144,6 +169,7 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
       fence_proxy_async_smem();
       mbar_arrive(&full_a[sa]);
       mbar_arrive(&empty_p[sp]);
+      if (tid == 0) DQ_TR(0, i, 2);
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------------ epilogue warps
@@ -151,18 +177,35 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
     const int h = (warp - 4) >> 2;   // which half of the token columns
     const int n = n0 + q * 32 + lane;
     const bool n_ok = n < N;
+    // Group scales of this thread's weight row, [row tile][group][128] in memory.  A new 256-byte
+    // run is touched every stage, so loads are issued kScaleAhead stages early: a load issued
+    // when it is needed would put a DRAM round trip on every stage of the epilogue.
+    constexpr int kScaleAhead = 8;
+    const __half* sw_row = nullptr;
+    float sq[kScaleAhead];
+#pragma unroll
+    for (int d = 0; d < kScaleAhead; ++d) sq[d] = 0.f;
+    if constexpr (!DUMP) {
+      sw_row = sw_t + (static_cast<size_t>(blockIdx.x) * total_groups + g_begin) * kBN + q * 32 + lane;
+#pragma unroll
+      for (int d = 0; d < kScaleAhead; ++d)
+        if (d < ng) sq[d] = __half2float(sw_row[static_cast<size_t>(d) * kBN]);
+    }
     for (int i = 0; i < ng; ++i) {
       const int b = i & 1;
-      float s = 0.f;
+      const float s = sq[0] * 0.0625f;
+#pragma unroll
+      for (int d = 0; d + 1 < kScaleAhead; ++d) sq[d] = sq[d + 1];
       if constexpr (!DUMP) {
-        if (n_ok)
-          s = __half2float(sw_t[static_cast<size_t>(g_begin + i) * N + n]) * 0.0625f;
+        if (i + kScaleAhead < ng)
+          sq[kScaleAhead - 1] = __half2float(sw_row[static_cast<size_t>(i + kScaleAhead) * kBN]);
       }
       if (!mbar_wait(&full_t[b], (i >> 1) & 1, abort_flag, SITE_EPI)) break;
+      if (tid == 128) DQ_TR(1, i, 0);
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(b * TN + h * C::CPW);
-      constexpr int CH = (C::CPW < 32) ? C::CPW : 32;  // columns per tcgen05.ld
+      constexpr int CH = (C::CPW < 32) ? C::CPW : (C::kMinCtas == 2 ? 16 : 32);  // columns per tcgen05.ld
 #pragma unroll
       for (int c0 = 0; c0 < C::CPW; c0 += CH) {
         uint32_t v[CH];
@@ -174,6 +217,7 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
           tmem_ld_x32(taddr + c0, v);
         }
         tmem_ld_wait();
+        if (tid == 128) DQ_TR(1, i, 1);
         if (c0 + CH == C::CPW) {  // accumulator buffer b is free once its last column is read
           tc_fence_before();
           mbar_arrive(&empty_t[b]);
@@ -226,16 +270,49 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
       uint64_t pol_w, pol_x;
       if (w_stream_once) pol_w = l2_policy_evict_first(); else pol_w = l2_policy_evict_last();
       pol_x = l2_policy_evict_last();
-      for (int i = 0; i < ng; ++i) {
-        const int sp = i % C::SP, sxi = i % C::SX;
-        if (!mbar_wait(&empty_p[sp], ((i / C::SP) & 1) ^ 1, abort_flag, SITE_TMA_P)) break;
-        mbar_expect_tx(&full_p[sp], kWpBytes);
-        tma_load_2d(smem + C::kOffP + sp * kWpBytes, &tm_w, (g_begin + i) * (kGroup / 2), n0,
-                    &full_p[sp], pol_w);
-        if (!mbar_wait(&empty_x[sxi], ((i / C::SX) & 1) ^ 1, abort_flag, SITE_TMA_X)) break;
-        mbar_expect_tx(&full_x[sxi], C::kXBytes);
-        tma_load_2d(smem + C::kOffX + sxi * C::kXBytes, &tm_x, (g_begin + i) * kGroup, t0,
-                    &full_x[sxi], pol_x);
+      // packed tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB]
+      const uint8_t* w_tile =
+          w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kWpBytes;
+      // The two rings advance independently (weights run up to SP stages ahead of the MMA,
+      // activations up to SX), so this thread polls both without blocking on either.
+      int iw = 0, ix = 0;
+      long long t0 = clock64();
+      uint32_t idle = 0;
+      while (iw < ng || ix < ng) {
+        bool progress = false;
+        if (iw < ng) {
+          const int sp = iw % C::SP;
+          if (mbar_test_wait(&empty_p[sp], ((iw / C::SP) & 1) ^ 1)) {
+            mbar_expect_tx(&full_p[sp], kWpBytes);
+            bulk_load_1d(smem + C::kOffP + sp * kWpBytes,
+                         w_tile + static_cast<size_t>(g_begin + iw) * kWpBytes, kWpBytes,
+                         &full_p[sp], pol_w);
+            DQ_TR(3, iw, 0);
+            ++iw;
+            progress = true;
+          }
+        }
+        if (ix < ng) {
+          const int sxi = ix % C::SX;
+          if (mbar_test_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1)) {
+            mbar_expect_tx(&full_x[sxi], C::kXBytes);
+            tma_load_2d(smem + C::kOffX + sxi * C::kXBytes, &tm_x, (g_begin + ix) * kGroup, t0_tok,
+                        &full_x[sxi], pol_x);
+            DQ_TR(3, ix, 1);
+            ++ix;
+            progress = true;
+          }
+        }
+        if (progress) {
+          idle = 0;
+          t0 = clock64();
+        } else if ((++idle & 1023u) == 0) {
+          if (*abort_flag != 0) break;
+          if (clock64() - t0 > (1ll << 31)) {
+            *abort_flag = SITE_TMA_P;
+            break;
+          }
+        }
       }
     }
   } else {
@@ -245,18 +322,27 @@ gemm_w4a4_int4_kernel(const __grid_constant__ CUtensorMap tm_w,
       for (int i = 0; i < ng; ++i) {
         const int b = i & 1, sa = i % C::SA, sxi = i % C::SX;
         if (!mbar_wait(&empty_t[b], ((i >> 1) & 1) ^ 1, abort_flag, SITE_MMA_T)) break;
+        DQ_TR(2, i, 0);
         if (!mbar_wait(&full_a[sa], (i / C::SA) & 1, abort_flag, SITE_MMA_A)) break;
+        DQ_TR(2, i, 1);
         if (!mbar_wait(&full_x[sxi], (i / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
+        DQ_TR(2, i, 2);
         tc_fence_after();
         const uint64_t da = umma_desc_k_sw128(smem_u32(smem + C::kOffA + sa * kWaBytes));
         const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffX + sxi * C::kXBytes));
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * TN);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)  // +32 bytes along K inside the swizzle atom = +2 (>>4)
+        for (int kk = 0; kk < 4; ++kk) {  // +32 bytes along K inside the swizzle atom = +2 (>>4)
           umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+          if (kk == 0) DQ_TR(2, i, 3);
+        }
+        DQ_TR(2, i, 4);
         umma_commit(&empty_a[sa]);
+        DQ_TR(2, i, 5);
         umma_commit(&empty_x[sxi]);
+        DQ_TR(2, i, 6);
         umma_commit(&full_t[b]);
+        DQ_TR(2, i, 7);
       }
     }
   }
@@ -349,7 +435,7 @@ static int pick_token_tile(int M) {
 // Smallest power-of-two split (<= 8, <= TN so every rank finishes at least one token row, and
 // leaving at least two groups per CTA) that puts enough CTAs on the machine.
 static int pick_split(int tiles, int total_groups, int tn, int sm_count) {
-  const int target = sm_count * ((tn <= 32) ? 2 : 1);
+  const int target = sm_count * ((tn <= 64) ? 2 : 1);
   int s = 1;
   while (s < 8 && tiles * s < target && total_groups / (2 * s) >= 2 && 2 * s <= tn) s *= 2;
   return s;
@@ -359,12 +445,8 @@ template <int TN, bool DUMP>
 static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed, const __half* sw_t,
                   const float* r, int M, int N, int K, void* y, int y_dtype, int32_t* acc_dump,
                   int split, cudaStream_t stream, DeviceState* st) {
-  CUtensorMap tm_w, tm_x;
-  int rc = make_tmap_2d_u8(&tm_w, w_packed, static_cast<uint64_t>(K) / 2, N,
-                           static_cast<uint64_t>(K) / 2, kGroup / 2, kBN,
-                           CU_TENSOR_MAP_SWIZZLE_NONE);
-  if (rc != DQ_OK) return rc;
-  rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, kGroup, TN, CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tm_x;
+  int rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, kGroup, TN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != DQ_OK) return rc;
 
   const int total_groups = K / kGroup;
@@ -383,9 +465,9 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN, DUMP>, tm_w, tm_x, sw_t, r, sx,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN, DUMP>, w_packed, tm_x, sw_t, r, sx,
                                      y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, acc_dump, M, N, K, gps,
-                                     split, w_stream_once, st->status_dev);
+                                     split, w_stream_once, st->status_dev DQ_TRACE_ARG);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_w4a4_int4 launch failed (TN=%d split=%d): %s", TN, split,
                      cudaGetErrorString(e));
@@ -405,6 +487,12 @@ static int check_gemm_args(const void* codes, const void* w_packed, int M, int N
 }  // namespace dq
 
 using namespace dq;
+
+#ifdef DQ_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) void dq_debug_set_trace(long long* p) {
+  dq::g_trace = p;
+}
+#endif
 
 extern "C" size_t dq_gemm_w4a4_int4_workspace_bytes(int, int, int) { return 0; }
 

@@ -1,13 +1,17 @@
 // Offline weight-side kernels: per-group int4 quantiser, re-packing of int4 codes into the
 // streaming layout the GEMM consumes, and the inverse (test hook).
 //
-// Streaming layout ("w_packed", uint8 [N, K/2]): row n, 16-byte chunk c covers k in
-// [32c, 32c+32); byte b of the chunk holds code[32c + b] in its low nibble and
-// code[32c + 16 + b] in its high nibble, both as two's-complement 4-bit values.  With this
+// Streaming layout ("w_packed", uint8, ceil(N/128)*128*K/2 bytes): the matrix is cut into tiles
+// of 128 rows x 128 k (one GEMM pipeline stage, 8 KB packed) stored contiguously in the order
+// [row tile][k group][row in tile][64 bytes], so a CTA that walks along K for its 128 rows reads
+// one contiguous run of HBM.  Rows past N are zero.  Inside a tile row, 16-byte chunk ch covers
+// k in [32ch, 32ch+32) of the group; byte b of the chunk holds code[32ch + b] in its low nibble
+// and code[32ch + 16 + b] in its high nibble, both as two's-complement 4-bit values.  With this
 // order `(w << 4) & 0xF0F0F0F0` and `w & 0xF0F0F0F0` on a 16-byte chunk yield two 16-byte runs of
 // consecutive k (times 16) - the GEMM's unpack warps need no byte shuffles.
-// Group scales are stored transposed (fp16 [K/G, N]) so an epilogue warp reads 32 consecutive
-// values per group.
+// Group scales ("sw_t", fp16, ceil(N/128)*128*(K/G) values) follow the same tiling:
+// [row tile][k group][row in tile], so the 128 scales a CTA needs per stage are one 256-byte run
+// and consecutive stages are consecutive runs.  Rows past N hold 0.
 #include "dq_common.h"
 
 #include <cuda_bf16.h>
@@ -27,17 +31,25 @@ __device__ __forceinline__ int code_at(const int8_t* codes, const uint8_t* ref_p
 __global__ void pack_w_int4_kernel(const int8_t* __restrict__ codes,
                                    const uint8_t* __restrict__ ref_packed, int N, int K,
                                    uint8_t* __restrict__ w_packed) {
+  // one thread per 16-byte output chunk; chunk index = ((tile * groups + g) * 128 + r) * 4 + ch
   const int64_t chunk = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int chunks_per_row = K / 32;
-  if (chunk >= static_cast<int64_t>(N) * chunks_per_row) return;
-  const int64_t row = chunk / chunks_per_row;
-  const int c = static_cast<int>(chunk % chunks_per_row);
+  const int groups = K / kGroup;
+  const int64_t tiles = (N + 127) / 128;
+  if (chunk >= tiles * groups * 512) return;
+  const int ch = static_cast<int>(chunk & 3);
+  const int r = static_cast<int>((chunk >> 2) & 127);
+  const int64_t tg = chunk >> 9;
+  const int g = static_cast<int>(tg % groups);
+  const int64_t row = (tg / groups) * 128 + r;
+  const int c = g * 4 + ch;  // 32-wide k chunk of the row
   uint32_t w[4] = {0, 0, 0, 0};
+  if (row < N) {
 #pragma unroll
-  for (int b = 0; b < 16; ++b) {
-    const uint32_t lo = static_cast<uint32_t>(code_at(codes, ref_packed, row, K, 32 * c + b)) & 0xFu;
-    const uint32_t hi = static_cast<uint32_t>(code_at(codes, ref_packed, row, K, 32 * c + 16 + b)) & 0xFu;
-    w[b >> 2] |= (lo | (hi << 4)) << (8 * (b & 3));
+    for (int b = 0; b < 16; ++b) {
+      const uint32_t lo = static_cast<uint32_t>(code_at(codes, ref_packed, row, K, 32 * c + b)) & 0xFu;
+      const uint32_t hi = static_cast<uint32_t>(code_at(codes, ref_packed, row, K, 32 * c + 16 + b)) & 0xFu;
+      w[b >> 2] |= (lo | (hi << 4)) << (8 * (b & 3));
+    }
   }
   *reinterpret_cast<uint4*>(w_packed + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
 }
@@ -45,10 +57,16 @@ __global__ void pack_w_int4_kernel(const int8_t* __restrict__ codes,
 __global__ void unpack_w_int4_kernel(const uint8_t* __restrict__ w_packed, int N, int K,
                                      int8_t* __restrict__ codes) {
   const int64_t chunk = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int chunks_per_row = K / 32;
-  if (chunk >= static_cast<int64_t>(N) * chunks_per_row) return;
-  const int64_t row = chunk / chunks_per_row;
-  const int c = static_cast<int>(chunk % chunks_per_row);
+  const int groups = K / kGroup;
+  const int64_t tiles = (N + 127) / 128;
+  if (chunk >= tiles * groups * 512) return;
+  const int ch = static_cast<int>(chunk & 3);
+  const int r = static_cast<int>((chunk >> 2) & 127);
+  const int64_t tg = chunk >> 9;
+  const int g = static_cast<int>(tg % groups);
+  const int64_t row = (tg / groups) * 128 + r;
+  if (row >= N) return;
+  const int c = g * 4 + ch;
   const uint4 raw = *reinterpret_cast<const uint4*>(w_packed + chunk * 16);
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   int8_t* dst = codes + row * K + 32 * c;
@@ -62,11 +80,15 @@ __global__ void unpack_w_int4_kernel(const uint8_t* __restrict__ w_packed, int N
 
 __global__ void transpose_sw_kernel(const __half* __restrict__ sw, int N, int groups,
                                     __half* __restrict__ sw_t) {
+  // output index = (tile * groups + g) * 128 + r
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= static_cast<int64_t>(N) * groups) return;
-  const int g = static_cast<int>(i / N);
-  const int n = static_cast<int>(i % N);
-  sw_t[i] = sw[static_cast<int64_t>(n) * groups + g];
+  const int64_t tiles = (N + 127) / 128;
+  if (i >= tiles * groups * 128) return;
+  const int r = static_cast<int>(i & 127);
+  const int64_t tg = i >> 7;
+  const int g = static_cast<int>(tg % groups);
+  const int64_t n = (tg / groups) * 128 + r;
+  sw_t[i] = (n < N) ? sw[n * groups + g] : __float2half_rn(0.f);
 }
 
 // One warp per (row, group of 128): s = absmax/7 rounded to fp16 (1 for a zero group),
@@ -117,7 +139,8 @@ static int check_w_shape(int N, int K, int G) {
 using namespace dq;
 
 extern "C" size_t dq_packed_w_bytes(int N, int K) {
-  return static_cast<size_t>(N) * static_cast<size_t>(K) / 2;
+  if (N <= 0 || K <= 0) return 0;
+  return (static_cast<size_t>(N) + 127) / 128 * 128 * static_cast<size_t>(K) / 2;
 }
 
 extern "C" int dq_pack_w_int4(const int8_t* codes, const uint8_t* ref_packed, const void* sw, int N,
@@ -130,14 +153,14 @@ extern "C" int dq_pack_w_int4(const int8_t* codes, const uint8_t* ref_packed, co
   DQ_REQUIRE(w_packed != nullptr && aligned(w_packed, 16), DQ_ERR_ALIGN,
              "w_packed must be non-null and 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int64_t chunks = static_cast<int64_t>(N) * (K / 32);
+  const int64_t chunks = static_cast<int64_t>((N + 127) / 128) * (K / kGroup) * 512;
   pack_w_int4_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, s>>>(codes, ref_packed, N,
                                                                                  K, w_packed);
   DQ_CHECK_CUDA(cudaGetLastError());
   if (sw != nullptr || sw_t != nullptr) {
     DQ_REQUIRE(sw != nullptr && sw_t != nullptr, DQ_ERR_NULL, "sw and sw_t must be given together");
     const int groups = K / kGroup;
-    const int64_t total = static_cast<int64_t>(N) * groups;
+    const int64_t total = static_cast<int64_t>((N + 127) / 128) * 128 * groups;
     transpose_sw_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
         static_cast<const __half*>(sw), N, groups, static_cast<__half*>(sw_t));
     DQ_CHECK_CUDA(cudaGetLastError());
@@ -151,7 +174,7 @@ extern "C" int dq_unpack_w_int4(const uint8_t* w_packed, int N, int K, int8_t* c
   if (rc != DQ_OK) return rc;
   DQ_REQUIRE(w_packed != nullptr && codes != nullptr, DQ_ERR_NULL, "null pointer");
   DQ_REQUIRE(aligned(w_packed, 16), DQ_ERR_ALIGN, "w_packed must be 16-byte aligned");
-  const int64_t chunks = static_cast<int64_t>(N) * (K / 32);
+  const int64_t chunks = static_cast<int64_t>((N + 127) / 128) * (K / kGroup) * 512;
   unpack_w_int4_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0,
                          static_cast<cudaStream_t>(stream)>>>(w_packed, N, K, codes);
   DQ_CHECK_CUDA(cudaGetLastError());

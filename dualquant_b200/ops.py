@@ -54,8 +54,8 @@ class Hadamard:
 class PackedInt4Weight:
     """Weight artefact the GEMM consumes: streaming int4 layout + transposed fp16 group scales."""
 
-    w_packed: torch.Tensor  # uint8 [N, K/2]
-    sw_t: torch.Tensor  # fp16 [K/G, N]
+    w_packed: torch.Tensor  # uint8, flat: [row tile][k group][128 rows][64 B]
+    sw_t: torch.Tensor  # fp16, flat: [row tile][k group][128 rows]
     N: int
     K: int
     group: int = GROUP
@@ -88,8 +88,8 @@ def pack_w_int4(codes: Optional[torch.Tensor], sw: torch.Tensor, group: int = GR
         ref_packed = ref_packed.contiguous()
         N, K = ref_packed.shape[0], ref_packed.shape[1] * 2
     sw = sw.to(torch.float16).contiguous()
-    w_packed = torch.empty(N, K // 2, dtype=torch.uint8, device=src.device)
-    sw_t = torch.empty(K // group, N, dtype=torch.float16, device=src.device)
+    w_packed = torch.empty(int(lib.dq_packed_w_bytes(N, K)), dtype=torch.uint8, device=src.device)
+    sw_t = torch.empty((N + 127) // 128 * 128 * (K // group), dtype=torch.float16, device=src.device)
     _lib.check(lib.dq_pack_w_int4(_ptr(codes), _ptr(ref_packed), _ptr(sw), N, K, group, _ptr(w_packed),
                                   _ptr(sw_t), _stream(src.device)), "dq_pack_w_int4")
     return PackedInt4Weight(w_packed, sw_t, N, K, group)

@@ -85,7 +85,7 @@ DQ_API int dq_abi_version(void);
 
 /* ---- weights ----------------------------------------------------------------------------- */
 
-/* Bytes of the packed weight matrix for (N, K): N*K/2. */
+/* Bytes of the packed weight matrix for (N, K): ceil(N/128)*128*K/2 (rows padded to the tile). */
 DQ_API size_t dq_packed_w_bytes(int N, int K);
 
 /*
@@ -93,7 +93,8 @@ DQ_API size_t dq_packed_w_bytes(int N, int K);
  * group scales.  Input is either signed codes (int8 [N,K], values in [-8,7]) or the
  * reference's packed form (uint8 [N,K/2], low nibble = even k, high nibble = odd k, biased
  * by +8: vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:156-189); give exactly
- * one of the two.  sw is fp16 [N, K/G]; sw_t is fp16 [K/G, N].
+ * one of the two.  sw is fp16 [N, K/G]; sw_t receives ceil(N/128)*128*(K/G) fp16 values in the
+ * same tile order as w_packed ([row tile][k group][row in tile]).
  */
 DQ_API int dq_pack_w_int4(const int8_t* codes, const uint8_t* ref_packed, const void* sw,
                    int N, int K, int G, uint8_t* w_packed, void* sw_t, void* stream);

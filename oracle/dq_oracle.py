@@ -191,14 +191,30 @@ def ref_unpack_int4(packed: torch.Tensor) -> torch.Tensor:
     return (out - 8).to(torch.int8)
 
 
-def stream_pack_int4(codes: torch.Tensor) -> torch.Tensor:
-    """The library's streaming weight layout: per row, 16-byte chunk c covers k in [32c, 32c+32);
-    byte b = (code[32c+b] & 0xF) | ((code[32c+16+b] & 0xF) << 4), two's complement nibbles."""
+def stream_pack_int4(codes: torch.Tensor, group: int = GROUP) -> torch.Tensor:
+    """The library's streaming weight layout (flat uint8): tiles of 128 rows x 128 k stored
+    contiguously as [row tile][k group][row in tile][64 bytes], rows past N zero.  Within a
+    tile row, 16-byte chunk ch covers k in [32ch, 32ch+32) of the group and
+    byte b = (code[32ch+b] & 0xF) | ((code[32ch+16+b] & 0xF) << 4), two's complement nibbles."""
     N, K = codes.shape
-    c = codes.to(torch.int16).reshape(N, K // 32, 2, 16)
-    lo = c[:, :, 0, :] & 0xF
-    hi = c[:, :, 1, :] & 0xF
-    return (lo | (hi << 4)).to(torch.uint8).reshape(N, K // 2).contiguous()
+    tiles = (N + 127) // 128
+    padded = torch.zeros(tiles * 128, K, dtype=torch.int16)
+    padded[:N] = codes.to(torch.int16)
+    c = padded.reshape(tiles, 128, K // group, 4, 2, 16)
+    lo = c[..., 0, :] & 0xF
+    hi = c[..., 1, :] & 0xF
+    byt = (lo | (hi << 4)).to(torch.uint8)  # [tiles, 128, groups, 4, 16]
+    return byt.permute(0, 2, 1, 3, 4).contiguous().reshape(-1)
+
+
+def stream_pack_scales(sw: torch.Tensor) -> torch.Tensor:
+    """Group scales in the library's streaming order (flat fp16): [row tile][k group][row in
+    tile], rows past N zero."""
+    N, G = sw.shape
+    tiles = (N + 127) // 128
+    padded = torch.zeros(tiles * 128, G, dtype=torch.float16)
+    padded[:N] = sw
+    return padded.reshape(tiles, 128, G).permute(0, 2, 1).contiguous().reshape(-1)
 
 
 # ----------------------------------------------------------------------------------------------

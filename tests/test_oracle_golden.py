@@ -99,12 +99,20 @@ def test_reference_packing_round_trip(golden):
     scale = _bf16(golden["refpack_scale_bf16"]).float()
     deq = codes.float().reshape(32, 2, 128) * scale.reshape(32, 2, 1)
     assert torch.equal(deq.reshape(32, 256), torch.from_numpy(golden["refpack_dequant"]))
-    # streaming layout: pure permutation of the same nibbles
+    # streaming layout: pure permutation of the same nibbles (tile 0, group 0, row 0, chunk 0)
     sp = O.stream_pack_int4(codes)
-    assert sp.shape == packed.shape
-    lo = (sp & 0xF).to(torch.int16)
+    assert sp.numel() == 128 * 256 // 2  # 32 rows padded to one 128-row tile
+    first = sp[:16].to(torch.int16)
+    lo = first & 0xF
     lo = torch.where(lo > 7, lo - 16, lo)
-    assert torch.equal(lo.reshape(32, 8, 16), codes.to(torch.int16).reshape(32, 8, 2, 16)[:, :, 0, :])
+    hi = first >> 4
+    hi = torch.where(hi > 7, hi - 16, hi)
+    assert torch.equal(lo, codes[0, 0:16].to(torch.int16))
+    assert torch.equal(hi, codes[0, 16:32].to(torch.int16))
+    # second k group of row 0 starts one 8 KB tile later
+    nxt = sp[8192:8192 + 16].to(torch.int16) & 0xF
+    nxt = torch.where(nxt > 7, nxt - 16, nxt)
+    assert torch.equal(nxt, codes[0, 128:144].to(torch.int16))
 
 
 def test_float_to_fp4(golden):
