@@ -15,9 +15,11 @@
 //               into the group scale (exact: power of two).
 //   warps 4-11  epilogue: tcgen05.ld of the group accumulator, run += float(acc) * sw, final scale
 //               by r[n]*sx[m], store / split-K reduction.
-//   warp 12     TMA producer (one lane): packed weight tiles (contiguous 8 KB bulk copies) and
-//               int8 activation tiles (tiled, 128B swizzle).
-//   warp 13     TMEM allocation, UMMA issue (one lane).
+//   warp 12     TMA producer: packed weight tiles (contiguous 8 KB bulk copies) and int8
+//               activation tiles (tiled, 128B swizzle).
+//   warp 13     TMEM allocation, UMMA issue.  Every tcgen05 / mbarrier instruction this warp
+//               executes costs tens of cycles of issue latency and they are all serial, so the
+//               protocol is built to give it one wait, four UMMAs and one commit per group.
 //
 // Split-K (decode shapes): the CTAs that share an output tile form a thread-block cluster along
 // grid z; partial tiles are exchanged through distributed shared memory and summed in rank
@@ -53,24 +55,25 @@ long long* g_trace = nullptr;
 constexpr int kBN = 128;           // weight rows per CTA tile (UMMA M)
 constexpr int kThreads = 448;
 constexpr int kUnpackThreads = 128;
-constexpr int kEpiThreads = 256;
 constexpr int kWpBytes = kBN * kGroup / 2;  // packed stage: 8 KB
 constexpr int kWaBytes = kBN * kGroup;      // unpacked stage: 16 KB
 
 template <int TN>
 struct Cfg {
-  // stage counts: the packed-weight ring is as deep as shared memory allows, because at decode
-  // shapes the kernel is bound by bytes in flight per SM (two CTAs per SM for TN <= 64)
-  static constexpr int SP = (TN == 16) ? 7 : (TN == 128) ? 12 : 6;
-  static constexpr int SA = (TN <= 64) ? 2 : 3;
-  static constexpr int SX = (TN == 16) ? 8 : (TN == 32) ? 6 : (TN == 64) ? 3 : 4;
-  static constexpr int kXBytes = TN * kGroup;
+  // XC: weight groups covered by one activation stage (one barrier round trip per XC groups).
+  static constexpr int XC = (TN <= 32) ? 4 : (TN == 64) ? 2 : 1;
+  // Stage counts.  The packed-weight ring is as deep as shared memory allows: at decode shapes
+  // the kernel is bound by bytes in flight per SM (two CTAs per SM for TN <= 64).
+  static constexpr int SP = (TN == 16) ? 7 : (TN == 128) ? 10 : 5;
+  static constexpr int SX = (TN == 128) ? 4 : 2;
+  static constexpr int kXBytes = TN * kGroup;          // one group of activation codes
+  static constexpr int kXStageBytes = XC * kXBytes;
   static constexpr int kMinCtas = (TN <= 64) ? 2 : 1;
-  static constexpr int kOffA = 0;
-  static constexpr int kOffX = kOffA + SA * kWaBytes;
-  static constexpr int kOffP = kOffX + SX * kXBytes;
+  static constexpr int kOffA = 0;                      // 2 unpacked weight buffers
+  static constexpr int kOffX = kOffA + 2 * kWaBytes;
+  static constexpr int kOffP = kOffX + SX * kXStageBytes;
   static constexpr int kOffBar = kOffP + SP * kWpBytes;
-  static constexpr int kNumBars = 2 * SP + 2 * SX + 2 * SA + 4;
+  static constexpr int kNumBars = 2 * SP + 2 * SX + 4;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + align slack
   static constexpr int kTmemCols = (2 * TN < 32) ? 32 : 2 * TN;
   static constexpr int CPW = TN / 2;  // accumulator columns per epilogue warp
@@ -78,9 +81,17 @@ struct Cfg {
 };
 
 // site codes stored in the status word when a bounded wait expires
-enum { SITE_TMA_P = 1, SITE_TMA_X, SITE_UNPACK_FULL, SITE_UNPACK_EMPTY, SITE_MMA_T, SITE_MMA_A,
-       SITE_MMA_X, SITE_EPI };
+enum { SITE_TMA = 1, SITE_UNPACK_FULL, SITE_UNPACK_FREE, SITE_MMA_READY, SITE_MMA_X, SITE_EPI };
 
+// Barrier protocol (b = i & 1 selects the unpacked-weight buffer and the TMEM accumulator):
+//   full_p / empty_p [SP]  packed weight ring   producer -> unpack warps (one arrival per warp)
+//   full_x / empty_x [SX]  activation ring      producer -> UMMA issuer  (tcgen05.commit)
+//   ready[b]               buffer b written by the 4 unpack warps AND accumulator b drained by the
+//                          8 epilogue warps (12 arrivals; the epilogue pre-arrives once)
+//   done[b]                UMMAs of the group finished (tcgen05.commit): the epilogue may read
+//                          accumulator b, the unpack warps may overwrite buffer b
+// so the single UMMA-issuing thread executes one wait, four UMMAs and one commit per group
+// (plus one wait and one commit per XC groups for the activation ring).
 template <int TN, bool DUMP>
 __global__ void __launch_bounds__(kThreads, Cfg<TN>::kMinCtas)
 gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
@@ -98,11 +109,9 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   uint64_t* empty_p = full_p + C::SP;
   uint64_t* full_x = empty_p + C::SP;
   uint64_t* empty_x = full_x + C::SX;
-  uint64_t* full_a = empty_x + C::SX;
-  uint64_t* empty_a = full_a + C::SA;
-  uint64_t* full_t = empty_a + C::SA;
-  uint64_t* empty_t = full_t + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(empty_t + 2);
+  uint64_t* ready = empty_x + C::SX;
+  uint64_t* done = ready + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
@@ -110,7 +119,6 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   const int lane = tid & 31;
   const int n0 = blockIdx.x * kBN;
   const int t0 = blockIdx.y * TN;
-  const int t0_tok = t0;
   const int total_groups = K / kGroup;
   const int g_begin = blockIdx.z * groups_per_split;
   int g_end = g_begin + groups_per_split;
@@ -118,10 +126,9 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   const int ng = (g_end > g_begin) ? (g_end - g_begin) : 0;
 
   if (tid == 0) {
-    for (int i = 0; i < C::SP; ++i) { mbar_init(&full_p[i], 1); mbar_init(&empty_p[i], kUnpackThreads); }
+    for (int i = 0; i < C::SP; ++i) { mbar_init(&full_p[i], 1); mbar_init(&empty_p[i], 4); }
     for (int i = 0; i < C::SX; ++i) { mbar_init(&full_x[i], 1); mbar_init(&empty_x[i], 1); }
-    for (int i = 0; i < C::SA; ++i) { mbar_init(&full_a[i], kUnpackThreads); mbar_init(&empty_a[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&full_t[i], 1); mbar_init(&empty_t[i], kEpiThreads); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&ready[i], 12); mbar_init(&done[i], 1); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -129,9 +136,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 12 && lane == 0) {
-    tma_prefetch_desc(&tm_x);
-  }
+  if (warp == 12 && lane == 0) tma_prefetch_desc(&tm_x);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -144,13 +149,13 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   if (warp < 4) {
     // ------------------------------------------------------------------ unpack warps
     for (int i = 0; i < ng; ++i) {
-      const int sp = i % C::SP, sa = i % C::SA;
+      const int sp = i % C::SP, b = i & 1;
       if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
       if (tid == 0) DQ_TR(0, i, 0);
-      if (!mbar_wait(&empty_a[sa], ((i / C::SA) & 1) ^ 1, abort_flag, SITE_UNPACK_EMPTY)) break;
+      if (!mbar_wait(&done[b], ((i >> 1) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
       if (tid == 0) DQ_TR(0, i, 1);
       const uint8_t* src = smem + C::kOffP + sp * kWpBytes;
-      uint8_t* dst = smem + C::kOffA + sa * kWaBytes;
+      uint8_t* dst = smem + C::kOffA + b * kWaBytes;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int id = tid + c * kUnpackThreads;  // 16-byte chunk of the packed tile
@@ -166,9 +171,12 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         *reinterpret_cast<uint4*>(rowp + (((2 * ch) ^ sw) << 4)) = lo;
         *reinterpret_cast<uint4*>(rowp + (((2 * ch + 1) ^ sw) << 4)) = hi;
       }
-      fence_proxy_async_smem();
-      mbar_arrive(&full_a[sa]);
-      mbar_arrive(&empty_p[sp]);
+      fence_proxy_async_smem();  // each writer orders its own stores before the UMMA reads
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&ready[b]);
+        mbar_arrive(&empty_p[sp]);
+      }
       if (tid == 0) DQ_TR(0, i, 2);
     }
   } else if (warp < 12) {
@@ -177,9 +185,12 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     const int h = (warp - 4) >> 2;   // which half of the token columns
     const int n = n0 + q * 32 + lane;
     const bool n_ok = n < N;
+    if (lane == 0) {  // both accumulators start out free
+      mbar_arrive(&ready[0]);
+      mbar_arrive(&ready[1]);
+    }
     // Group scales of this thread's weight row, [row tile][group][128] in memory.  A new 256-byte
-    // run is touched every stage, so loads are issued kScaleAhead stages early: a load issued
-    // when it is needed would put a DRAM round trip on every stage of the epilogue.
+    // run is touched every stage, so loads are issued kScaleAhead stages early.
     constexpr int kScaleAhead = 8;
     const __half* sw_row = nullptr;
     float sq[kScaleAhead];
@@ -200,7 +211,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         if (i + kScaleAhead < ng)
           sq[kScaleAhead - 1] = __half2float(sw_row[static_cast<size_t>(i + kScaleAhead) * kBN]);
       }
-      if (!mbar_wait(&full_t[b], (i >> 1) & 1, abort_flag, SITE_EPI)) break;
+      if (!mbar_wait(&done[b], (i >> 1) & 1, abort_flag, SITE_EPI)) break;
       if (tid == 128) DQ_TR(1, i, 0);
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
@@ -218,9 +229,10 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
         tmem_ld_wait();
         if (tid == 128) DQ_TR(1, i, 1);
-        if (c0 + CH == C::CPW) {  // accumulator buffer b is free once its last column is read
+        if (c0 + CH == C::CPW) {  // accumulator b is free once its last column is read
           tc_fence_before();
-          mbar_arrive(&empty_t[b]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ready[b]);
         }
         if constexpr (DUMP) {
           if (n_ok) {
@@ -258,7 +270,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
       } else {
         // Partial tile -> this CTA's exchange buffer red[token][row] (aliases the stage buffers:
-        // the last full_t wait above implies every UMMA, hence every smem operand read, is done).
+        // the last done[] wait above implies every UMMA, hence every smem operand read, is over).
         float* red = reinterpret_cast<float*>(smem);
 #pragma unroll
         for (int j = 0; j < C::CPW; ++j) red[(h * C::CPW + j) * kBN + q * 32 + lane] = run[j];
@@ -266,84 +278,91 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     }
   } else if (warp == 12) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint64_t pol_w, pol_x;
-      if (w_stream_once) pol_w = l2_policy_evict_first(); else pol_w = l2_policy_evict_last();
-      pol_x = l2_policy_evict_last();
-      // packed tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB]
-      const uint8_t* w_tile =
-          w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kWpBytes;
-      // The two rings advance independently (weights run up to SP stages ahead of the MMA,
-      // activations up to SX), so this thread polls both without blocking on either.
-      int iw = 0, ix = 0;
-      long long t0 = clock64();
-      uint32_t idle = 0;
-      while (iw < ng || ix < ng) {
-        bool progress = false;
-        if (iw < ng) {
-          const int sp = iw % C::SP;
-          if (mbar_test_wait(&empty_p[sp], ((iw / C::SP) & 1) ^ 1)) {
+    // The whole warp runs the loop (uniform control flow); lane 0 issues the copies.  The two
+    // rings advance independently - weights up to SP groups ahead of the UMMAs, activations up
+    // to SX stages of XC groups - so both are polled without blocking on either.
+    uint64_t pol_w, pol_x;
+    if (w_stream_once) pol_w = l2_policy_evict_first(); else pol_w = l2_policy_evict_last();
+    pol_x = l2_policy_evict_last();
+    // packed tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB]
+    const uint8_t* w_tile =
+        w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kWpBytes;
+    const int nxc = (ng + C::XC - 1) / C::XC;
+    int iw = 0, ix = 0;
+    long long t_last = clock64();
+    uint32_t idle = 0;
+    while (iw < ng || ix < nxc) {
+      bool progress = false;
+      if (iw < ng) {
+        const int sp = iw % C::SP;
+        if (mbar_test_wait(&empty_p[sp], ((iw / C::SP) & 1) ^ 1)) {
+          if (lane == 0) {
             mbar_expect_tx(&full_p[sp], kWpBytes);
             bulk_load_1d(smem + C::kOffP + sp * kWpBytes,
                          w_tile + static_cast<size_t>(g_begin + iw) * kWpBytes, kWpBytes,
                          &full_p[sp], pol_w);
             DQ_TR(3, iw, 0);
-            ++iw;
-            progress = true;
           }
+          ++iw;
+          progress = true;
         }
-        if (ix < ng) {
-          const int sxi = ix % C::SX;
-          if (mbar_test_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1)) {
-            mbar_expect_tx(&full_x[sxi], C::kXBytes);
-            tma_load_2d(smem + C::kOffX + sxi * C::kXBytes, &tm_x, (g_begin + ix) * kGroup, t0_tok,
-                        &full_x[sxi], pol_x);
+      }
+      if (ix < nxc) {
+        const int sxi = ix % C::SX;
+        if (mbar_test_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1)) {
+          if (lane == 0) {
+            int cnt = ng - ix * C::XC;
+            if (cnt > C::XC) cnt = C::XC;
+            mbar_expect_tx(&full_x[sxi], static_cast<uint32_t>(cnt) * C::kXBytes);
+            for (int j = 0; j < cnt; ++j)
+              tma_load_2d(smem + C::kOffX + sxi * C::kXStageBytes + j * C::kXBytes, &tm_x,
+                          (g_begin + ix * C::XC + j) * kGroup, t0, &full_x[sxi], pol_x);
             DQ_TR(3, ix, 1);
-            ++ix;
-            progress = true;
           }
+          ++ix;
+          progress = true;
         }
-        if (progress) {
-          idle = 0;
-          t0 = clock64();
-        } else if ((++idle & 1023u) == 0) {
-          if (*abort_flag != 0) break;
-          if (clock64() - t0 > (1ll << 31)) {
-            *abort_flag = SITE_TMA_P;
-            break;
-          }
+      }
+      if (progress) {
+        idle = 0;
+        t_last = clock64();
+      } else if ((++idle & 1023u) == 0) {
+        if (*abort_flag != 0) break;
+        if (clock64() - t_last > (1ll << 31)) {
+          *abort_flag = SITE_TMA;
+          break;
         }
       }
     }
   } else {
     // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_i8(kBN, TN);
-      for (int i = 0; i < ng; ++i) {
-        const int b = i & 1, sa = i % C::SA, sxi = i % C::SX;
-        if (!mbar_wait(&empty_t[b], ((i >> 1) & 1) ^ 1, abort_flag, SITE_MMA_T)) break;
-        DQ_TR(2, i, 0);
-        if (!mbar_wait(&full_a[sa], (i / C::SA) & 1, abort_flag, SITE_MMA_A)) break;
-        DQ_TR(2, i, 1);
-        if (!mbar_wait(&full_x[sxi], (i / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
-        DQ_TR(2, i, 2);
-        tc_fence_after();
-        const uint64_t da = umma_desc_k_sw128(smem_u32(smem + C::kOffA + sa * kWaBytes));
-        const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffX + sxi * C::kXBytes));
+    // Whole warp waits (uniform control flow); lane 0 issues tcgen05.mma / tcgen05.commit.
+    constexpr uint32_t idesc = umma_idesc_i8(kBN, TN);
+    const uint32_t a_base = smem_u32(smem + C::kOffA);
+    const uint32_t x_base = smem_u32(smem + C::kOffX);
+    for (int i = 0; i < ng; ++i) {
+      const int b = i & 1;
+      const int xc = i / C::XC, xj = i % C::XC, sxi = xc % C::SX;
+      if (!mbar_wait(&ready[b], (i >> 1) & 1, abort_flag, SITE_MMA_READY)) break;
+      if (lane == 0) DQ_TR(2, i, 0);
+      if (xj == 0) {
+        if (!mbar_wait(&full_x[sxi], (xc / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
+      }
+      if (lane == 0) DQ_TR(2, i, 1);
+      tc_fence_after();
+      if (lane == 0) {
+        const uint64_t da = umma_desc_k_sw128(a_base + b * kWaBytes);
+        const uint64_t db = umma_desc_k_sw128(x_base + sxi * C::kXStageBytes + xj * C::kXBytes);
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * TN);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {  // +32 bytes along K inside the swizzle atom = +2 (>>4)
+        for (int kk = 0; kk < 4; ++kk)  // +32 bytes along K inside the swizzle atom = +2 (>>4)
           umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk > 0 ? 1u : 0u);
-          if (kk == 0) DQ_TR(2, i, 3);
-        }
-        DQ_TR(2, i, 4);
-        umma_commit(&empty_a[sa]);
-        DQ_TR(2, i, 5);
-        umma_commit(&empty_x[sxi]);
-        DQ_TR(2, i, 6);
-        umma_commit(&full_t[b]);
-        DQ_TR(2, i, 7);
+        DQ_TR(2, i, 2);
+        umma_commit(&done[b]);
+        if (xj == C::XC - 1 || i == ng - 1) umma_commit(&empty_x[sxi]);
+        DQ_TR(2, i, 3);
       }
+      __syncwarp();
     }
   }
 
