@@ -31,3 +31,42 @@ extern "C" int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float*
   if (rc != DQ_OK) return rc;
   return dq_gemm_w4a4_int4(codes, sx, w_packed, sw_t, r, M, N, K, G, y, y_dtype, nullptr, 0, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant
+// ---------------------------------------------------------------------------------------------
+// Scratch for dq_linear_w4a4_int4_static lives in the library image itself, so the caller never
+// has to obtain device memory.  Every GPU that loads the library carries these bytes until the
+// process exits.  The array name below is only a host-side handle: the device address that
+// kernels can use is looked up once per device with cudaGetSymbolAddress.
+#define DQ_STATIC_SCRATCH_BYTES (2u * 1024u * 1024u + 16u * 1024u)
+static __device__ __align__(256) unsigned char g_static_scratch[DQ_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[dq::kMaxDevices] = {nullptr};
+
+extern "C" size_t dq_linear_w4a4_int4_static_max_bytes(void) { return DQ_STATIC_SCRATCH_BYTES; }
+
+extern "C" int dq_linear_w4a4_int4_static(const void* x_bf16, int64_t ldx, const float* a,
+                                          const dq_hadamard_desc* had, const uint8_t* w_packed,
+                                          const void* sw_t, const float* r, int M, int N, int K,
+                                          int G, void* y, int y_dtype, int scale_fp16,
+                                          void* stream) {
+  DQ_REQUIRE(M >= 0 && N >= 1 && K >= 1, DQ_ERR_SHAPE, "bad shape M=%d N=%d K=%d", M, N, K);
+  const size_t need = dq_linear_w4a4_int4_scratch_bytes(M, N, K);
+  DQ_REQUIRE(need <= DQ_STATIC_SCRATCH_BYTES, DQ_ERR_WORKSPACE,
+             "M=%d x K=%d needs %zu bytes of scratch; the built-in scratch holds %u "
+             "(use dq_linear_w4a4_int4 with caller-provided scratch for larger batches)",
+             M, K, need, DQ_STATIC_SCRATCH_BYTES);
+  int dev = -1;
+  DQ_CHECK_CUDA(cudaGetDevice(&dev));
+  DQ_REQUIRE(dev >= 0 && dev < dq::kMaxDevices, DQ_ERR_SHAPE, "device index %d out of range", dev);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // one-time set-up for this device (it is the current one): symbol -> device address
+    void* ptr = nullptr;
+    DQ_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    DQ_REQUIRE(ptr != nullptr, DQ_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_scratch_addr[dev] = ptr;
+  }
+  return dq_linear_w4a4_int4(x_bf16, ldx, a, had, w_packed, sw_t, r, M, N, K, G, y, y_dtype,
+                             scale_fp16, g_static_scratch_addr[dev], DQ_STATIC_SCRATCH_BYTES,
+                             stream);
+}

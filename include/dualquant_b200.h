@@ -179,6 +179,37 @@ DQ_API int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float* a,
                         const float* r, int M, int N, int K, int G, void* y, int y_dtype,
                         int scale_fp16, void* scratch, size_t scratch_bytes, void* stream);
 
+/*
+ * dq_linear_w4a4_int4 for callers that cannot hand the library any scratch memory.  (No
+ * counterpart in the reference: its real-kernel path keeps torch-allocated buffers on the
+ * module, ablation/real_int4_kernel/full_model_nunchaku.py:95-104.)
+ *
+ * Who needs it: code that runs where obtaining device memory is off the table - a serving loop
+ * that has already handed every byte of HBM to its own pools, a plugin called from inside
+ * another framework's execution callback where cudaMalloc would synchronise the device, or a
+ * host that is only given input/output pointers.  Same arguments and results as
+ * dq_linear_w4a4_int4 minus the scratch pair; the activation codes and token scales go to a
+ * fixed array inside the library image instead.
+ *
+ * Limits and rules:
+ *  - the array is dq_linear_w4a4_int4_static_max_bytes() = 2 MiB + 16 KiB and is resident on
+ *    every GPU that loads the library for the life of the process; a call whose
+ *    dq_linear_w4a4_int4_scratch_bytes(M,N,K) exceeds it fails with DQ_ERR_WORKSPACE
+ *    (e.g. 128 tokens x K=16384 fits, 256 x 14336 does not);
+ *  - the first call on each device resolves the array's device address (a host-side lookup);
+ *    make that first call outside any stream capture, with the device current;
+ *  - it never calls cudaMalloc / cudaFree or any allocating routine;
+ *  - all calls share the one array and it keeps whatever the last call wrote.  Nothing in it
+ *    has to start at zero: the quantiser overwrites every byte the GEMM later reads.  Two calls
+ *    that overlap on the GPU (different streams, or graphs replayed concurrently) race on it -
+ *    serialise them.
+ */
+DQ_API size_t dq_linear_w4a4_int4_static_max_bytes(void);
+DQ_API int dq_linear_w4a4_int4_static(const void* x_bf16, int64_t ldx, const float* a,
+                                      const dq_hadamard_desc* had, const uint8_t* w_packed,
+                                      const void* sw_t, const float* r, int M, int N, int K,
+                                      int G, void* y, int y_dtype, int scale_fp16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
