@@ -18,6 +18,7 @@ SOURCES = [
     "weights_int4.cu",
     "act_quant_int4.cu",
     "gemm_w4a4_int4.cu",
+    "gemv_w4a4_int4.cu",
     "linear_w4a4.cu",
 ]
 

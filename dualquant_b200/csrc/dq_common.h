@@ -54,6 +54,13 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 
 // One-time kernel attribute set-up of each translation unit (called from dq_init).
 int init_gemm_int4_kernels();
+int init_gemv_int4_kernels();
 int init_act_quant_kernels();
+
+// Decode-batch (register-path) variant of the int4 linear, defined in gemv_w4a4_int4.cu.
+int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count);
+int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                     const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
+                     int tok, int split, cudaStream_t stream, DeviceState* st);
 
 }  // namespace dq

@@ -96,6 +96,8 @@ extern "C" int dq_init(int device) {
 
   int rc = init_gemm_int4_kernels();
   if (rc != DQ_OK) return rc;
+  rc = init_gemv_int4_kernels();
+  if (rc != DQ_OK) return rc;
   rc = init_act_quant_kernels();
   if (rc != DQ_OK) return rc;
   DQ_CHECK_CUDA(cudaDeviceSynchronize());

@@ -528,10 +528,27 @@ extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const 
   DQ_REQUIRE(sx != nullptr && sw_t != nullptr && y != nullptr, DQ_ERR_NULL, "null sx / sw_t / y");
   DQ_REQUIRE(y_dtype == DQ_DTYPE_F32 || y_dtype == DQ_DTYPE_BF16, DQ_ERR_UNSUPPORTED,
              "unknown y_dtype %d", y_dtype);
+  DQ_REQUIRE(aligned(sw_t, 16), DQ_ERR_ALIGN, "sw_t must be 16-byte aligned");
+  const int total_groups = K / kGroup;
+  // token_tile: 0 = choose; 16/32/64/128 = tensor-memory kernel with that token tile;
+  // -8/-16/-32 = register-path decode kernel with that token capacity.
+  const bool decode_path = token_tile < 0 || (token_tile == 0 && M <= 16);
+  if (decode_path) {
+    const int tok = token_tile < 0 ? -token_tile : (M <= 8 ? 8 : 16);
+    DQ_REQUIRE((tok == 8 || tok == 16 || tok == 32) && M <= tok, DQ_ERR_SHAPE,
+               "decode kernel token capacity %d does not cover M=%d", tok, M);
+    const int tiles_n = (N + kBN - 1) / kBN;
+    int split = split_k ? split_k : gemv_pick_split(tiles_n, total_groups, tok, st->sm_count);
+    DQ_REQUIRE(split == 1 || split == 2 || split == 4 || split == 8, DQ_ERR_SHAPE,
+               "split_k must be 1/2/4/8 (got %d)", split);
+    DQ_REQUIRE(split <= tok && split <= total_groups, DQ_ERR_SHAPE,
+               "split_k=%d too large for %d tokens / %d groups", split, tok, total_groups);
+    return launch_gemv_int4(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, tok, split,
+                            static_cast<cudaStream_t>(stream), st);
+  }
   const int tn = token_tile ? token_tile : pick_token_tile(M);
   DQ_REQUIRE(tn == 16 || tn == 32 || tn == 64 || tn == 128, DQ_ERR_SHAPE,
              "token tile must be 16/32/64/128 (got %d)", tn);
-  const int total_groups = K / kGroup;
   const int tiles = ((N + kBN - 1) / kBN) * ((M + tn - 1) / tn);
   int split = split_k ? split_k : pick_split(tiles, total_groups, tn, st->sm_count);
   DQ_REQUIRE(split == 1 || split == 2 || split == 4 || split == 8, DQ_ERR_SHAPE,

@@ -1,0 +1,338 @@
+// W4A4 int4 dual-scale linear for decode batches (M <= 32 tokens) on sm_100a.
+//
+// Same arithmetic and the same weight artefact as gemm_w4a4_int4.cu, different machine mapping.
+// With a handful of tokens the job is to stream the packed weights out of HBM once, so this
+// kernel is built around bytes in flight rather than around the tensor memory pipeline:
+//
+//   * one producer warp keeps a ring of stages full; a stage is one weight group of the CTA's
+//     128 rows: 8 KB of packed int4 (one contiguous bulk copy), its 128 fp16 group scales
+//     (256 B bulk copy) and the int8 activation codes of the group (TMA tile, 128B swizzle);
+//     the ring depth is chosen at launch so that the CTAs sharing an SM together keep
+//     well over 100 KB of weights in flight (throughput = bytes in flight / HBM latency);
+//   * eight compute warps each own 16 weight rows.  A lane reads its packed nibbles straight
+//     from the stage (two 16-byte loads), splits them in registers ((w << 4) & 0xF0.. and
+//     w & 0xF0.., i.e. 16 * code, the 1/16 folded into the group scale) and feeds
+//     mma.sync.m16n8k32.s8 with int32 accumulation per group - no second shared-memory pass,
+//     no cross-warp hand-off on the critical path.  The k order inside a group is permuted
+//     identically for weights and activations (a dot product does not care);
+//   * per group: acc -> fp32, times the group scale, added to a running fp32 sum; at the end
+//     times r[n] * sx[m].  Split-K partial tiles are reduced across the thread-block cluster
+//     through distributed shared memory in rank order (deterministic, no global scratch).
+#include "dq_common.h"
+#include "dq_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace dq {
+
+constexpr int kVBN = 128;                 // weight rows per CTA
+constexpr int kVThreads = 288;            // 8 compute warps + 1 producer warp
+constexpr int kVWBytes = kVBN * kGroup / 2;  // 8 KB packed weights per stage
+constexpr int kVSBytes = kVBN * 2;           // 256 B of fp16 group scales per stage
+
+template <int NT>  // NT = number of 8-token blocks (tokens handled: 8 * NT)
+struct VCfg {
+  static constexpr int TOK = 8 * NT;
+  static constexpr int kXRows = (TOK < 16) ? 16 : TOK;  // rows of the activation tile box
+  static constexpr int kXBytes = kXRows * kGroup;
+  static constexpr int kOffX = 0;
+  static constexpr int kOffW = kXBytes;
+  static constexpr int kOffS = kOffW + kVWBytes;
+  static constexpr int kStage = (kOffS + kVSBytes + 1023) / 1024 * 1024;
+  // The ring depth is a launch parameter: the host gives each CTA as many stages as fit next to
+  // the other CTAs expected on its SM, because throughput here is (bytes in flight) / (HBM latency).
+  static constexpr int kMinStages = 2;
+  static constexpr int kMaxStages = 18;
+  static constexpr int kMinCtas = (NT <= 2) ? 4 : 3;
+  static constexpr int kBarBytes = 2 * kMaxStages * 8 + 16;
+  static constexpr uint32_t kTxBytes = kXBytes + kVWBytes + kVSBytes;
+  static_assert(TOK * kVBN * 4 <= kMinStages * kStage, "split-K exchange tile must fit in the ring");
+  static constexpr int smem_bytes(int stages) { return stages * kStage + kBarBytes + 1024; }
+};
+
+enum { VSITE_PRODUCER = 21, VSITE_COMPUTE = 22 };
+
+__device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kVThreads, VCfg<NT>::kMinCtas)
+gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
+                      const __grid_constant__ CUtensorMap tm_x,
+                      const __half* __restrict__ sw_t, const float* __restrict__ r,
+                      const float* __restrict__ sx, void* __restrict__ y, int y_bf16, int M, int N,
+                      int K, int groups_per_split, int split_k, int stages, int* status) {
+  using C = VCfg<NT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * C::kStage);
+  uint64_t* empty = full + C::kMaxStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + C::kMaxStages);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int n0 = blockIdx.x * kVBN;
+  const int total_groups = K / kGroup;
+  const int g_begin = blockIdx.z * groups_per_split;
+  int g_end = g_begin + groups_per_split;
+  if (g_end > total_groups) g_end = total_groups;
+  const int ng = (g_end > g_begin) ? (g_end - g_begin) : 0;
+
+  if (tid == 0) {
+    for (int i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 8); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 8 && lane == 0) tma_prefetch_desc(&tm_x);
+  __syncthreads();
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ producer warp
+    const uint64_t pol_w = l2_policy_evict_first();
+    const uint64_t pol_x = l2_policy_evict_last();
+    const size_t tile_group0 = static_cast<size_t>(blockIdx.x) * total_groups + g_begin;
+    const uint8_t* w_src = w_packed + tile_group0 * kVWBytes;
+    const uint8_t* s_src = reinterpret_cast<const uint8_t*>(sw_t) + tile_group0 * kVSBytes;
+    int s = 0;
+    uint32_t ph = 1;  // parity of the "stage is free" phase being waited for
+    for (int i = 0; i < ng; ++i) {
+      if (!mbar_wait(&empty[s], ph, abort_flag, VSITE_PRODUCER)) break;
+      if (lane == 0) {
+        uint8_t* st = smem + s * C::kStage;
+        mbar_expect_tx(&full[s], C::kTxBytes);
+        bulk_load_1d(st + C::kOffW, w_src + static_cast<size_t>(i) * kVWBytes, kVWBytes, &full[s],
+                     pol_w);
+        bulk_load_1d(st + C::kOffS, s_src + static_cast<size_t>(i) * kVSBytes, kVSBytes, &full[s],
+                     pol_w);
+        tma_load_2d(st + C::kOffX, &tm_x, (g_begin + i) * kGroup, 0, &full[s], pol_x);
+      }
+      __syncwarp();
+      if (++s == stages) { s = 0; ph ^= 1u; }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int g = lane >> 2;  // fragment row / token index inside an 8-block
+    const int t = lane & 3;
+    const int row = warp * 16 + g;  // local weight row (and row + 8)
+    float run[NT][4];
+#pragma unroll
+    for (int nb = 0; nb < NT; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) run[nb][e] = 0.f;
+
+    int s = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < ng; ++i) {
+      if (!mbar_wait(&full[s], ph, abort_flag, VSITE_COMPUTE)) break;
+      const uint8_t* st = smem + s * C::kStage;
+      const uint4 wa = *reinterpret_cast<const uint4*>(st + C::kOffW + row * 64 + t * 16);
+      const uint4 wb = *reinterpret_cast<const uint4*>(st + C::kOffW + (row + 8) * 64 + t * 16);
+      const __half* sc = reinterpret_cast<const __half*>(st + C::kOffS);
+      const float s0 = __half2float(sc[row]) * 0.0625f;
+      const float s1 = __half2float(sc[row + 8]) * 0.0625f;
+      // Word j of a lane's 16-byte chunk feeds MMA step j: low nibbles are k = 32t + 4j + {0..3}
+      // of the group (fragment slots a0/a1), high nibbles k = 32t + 16 + 4j + {0..3} (a2/a3).
+      const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
+      const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+      uint32_t a0[4], a1[4], a2[4], a3[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a0[j] = (wav[j] << 4) & 0xF0F0F0F0u;
+        a2[j] = wav[j] & 0xF0F0F0F0u;
+        a1[j] = (wbv[j] << 4) & 0xF0F0F0F0u;
+        a3[j] = wbv[j] & 0xF0F0F0F0u;
+      }
+#pragma unroll
+      for (int nb = 0; nb < NT; ++nb) {
+        const int n = nb * 8 + g;  // token row of the activation tile (128B-swizzled rows)
+        const uint8_t* xr = st + C::kOffX + n * 128;
+        const uint4 xlo = *reinterpret_cast<const uint4*>(xr + (((2 * t) ^ (n & 7)) << 4));
+        const uint4 xhi = *reinterpret_cast<const uint4*>(xr + (((2 * t + 1) ^ (n & 7)) << 4));
+        const uint32_t b0[4] = {xlo.x, xlo.y, xlo.z, xlo.w};
+        const uint32_t b1[4] = {xhi.x, xhi.y, xhi.z, xhi.w};
+        int c[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_s8_16x8x32(c, a0[j], a1[j], a2[j], a3[j], b0[j], b1[j]);
+        run[nb][0] = fmaf(static_cast<float>(c[0]), s0, run[nb][0]);
+        run[nb][1] = fmaf(static_cast<float>(c[1]), s0, run[nb][1]);
+        run[nb][2] = fmaf(static_cast<float>(c[2]), s1, run[nb][2]);
+        run[nb][3] = fmaf(static_cast<float>(c[3]), s1, run[nb][3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+      if (++s == stages) { s = 0; ph ^= 1u; }
+    }
+
+    // accumulator fragment: c0/c1 = (row, tokens 2t, 2t+1), c2/c3 = (row + 8, same tokens)
+    if (split_k == 1) {
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        const int n = n0 + row + 8 * hrow;
+        if (n < N) {
+          const float rn = (r != nullptr) ? r[n] : 1.f;
+#pragma unroll
+          for (int nb = 0; nb < NT; ++nb)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int m = nb * 8 + 2 * t + e;
+              if (m < M) {
+                const float val = run[nb][2 * hrow + e] * (rn * sx[m]);
+                if (y_bf16)
+                  reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
+                      __float2bfloat16_rn(val);
+                else
+                  reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+              }
+            }
+        }
+      }
+    } else {
+      // all compute warps are past their last stage before the ring is reused as exchange tile
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      float* red = reinterpret_cast<float*>(smem);
+#pragma unroll
+      for (int nb = 0; nb < NT; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int m = nb * 8 + 2 * t + e;
+          red[m * kVBN + row] = run[nb][e];
+          red[m * kVBN + row + 8] = run[nb][2 + e];
+        }
+    }
+  }
+
+  // -------------------------------------------------------------------- split-K reduction
+  if (split_k > 1) {
+    __syncwarp();
+    cluster_sync_all();
+    if (warp < 8) {
+      const uint32_t rank = cluster_ctarank();
+      const int rows = C::TOK / split_k;  // token rows of the tile this CTA finishes
+      const int c4 = tid & 31;            // float4 column
+      const uint32_t red_base = smem_u32(smem);
+      for (int rr = tid >> 5; rr < rows; rr += 8) {
+        const int m = static_cast<int>(rank) * rows + rr;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t off = static_cast<uint32_t>((m * kVBN + c4 * 4) * 4);
+        for (int p = 0; p < split_k; ++p) {
+          const float4 v = dsmem_ld_f4(dsmem_map(red_base + off, static_cast<uint32_t>(p)));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (m < M) {
+          const float sm = sx[m];
+          const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int n = n0 + c4 * 4 + u;
+            if (n < N) {
+              const float rn = (r != nullptr) ? r[n] : 1.f;
+              const float val = vals[u] * (rn * sm);
+              if (y_bf16)
+                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
+                    __float2bfloat16_rn(val);
+              else
+                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // peers may still be reading this CTA's exchange tile until here
+  }
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0) atomicCAS(status, 0, *abort_flag);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+template <int NT>
+static int set_gemv_attr() {
+  cudaError_t e = cudaFuncSetAttribute(gemv_w4a4_int4_kernel<NT>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess)
+    return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemv NT=%d) failed: %s", NT,
+                     cudaGetErrorString(e));
+  return DQ_OK;
+}
+
+int init_gemv_int4_kernels() {
+  int rc;
+  if ((rc = set_gemv_attr<1>()) != DQ_OK) return rc;
+  if ((rc = set_gemv_attr<2>()) != DQ_OK) return rc;
+  if ((rc = set_gemv_attr<4>()) != DQ_OK) return rc;
+  return DQ_OK;
+}
+
+int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count) {
+  const int target = 3 * sm_count;
+  int s = 1;
+  while (s < 8 && tiles * s < target && total_groups / (2 * s) >= 2 && 2 * s <= tok) s *= 2;
+  return s;
+}
+
+template <int NT>
+static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                         const __half* sw_t, const float* r, int M, int N, int K, void* y,
+                         int y_dtype, int split, cudaStream_t stream, DeviceState* st) {
+  using C = VCfg<NT>;
+  CUtensorMap tm_x;
+  int rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, kGroup, C::kXRows, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != DQ_OK) return rc;
+  const int total_groups = K / kGroup;
+  const int gps = (total_groups + split - 1) / split;
+  const int tiles_n = (N + kVBN - 1) / kVBN;
+  // stages: share the SM's shared memory between the CTAs expected to be co-resident
+  int per_sm = (tiles_n * split + st->sm_count - 1) / st->sm_count;
+  if (per_sm > C::kMinCtas) per_sm = C::kMinCtas;
+  if (per_sm < 1) per_sm = 1;
+  const int avail = (227 * 1024) / per_sm - 1024 - C::kBarBytes - 1024;
+  int stages = avail / C::kStage;
+  if (stages > C::kMaxStages) stages = C::kMaxStages;
+  if (stages > gps) stages = gps;
+  if (stages < C::kMinStages) stages = C::kMinStages;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles_n, 1, split);
+  cfg.blockDim = dim3(kVThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::smem_bytes(stages);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = split;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT>, w_packed, tm_x, sw_t, r, sx, y,
+                                     y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, gps, split,
+                                     stages, st->status_dev);
+  if (e != cudaSuccess)
+    return set_error(DQ_ERR_CUDA, "gemv_w4a4_int4 launch failed (tokens=%d split=%d): %s", C::TOK,
+                     split, cudaGetErrorString(e));
+  return DQ_OK;
+}
+
+// tok: token capacity of the variant (8, 16 or 32) >= M.
+int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                     const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
+                     int tok, int split, cudaStream_t stream, DeviceState* st) {
+  const __half* swp = static_cast<const __half*>(sw_t);
+  switch (tok) {
+    case 8: return launch_gemv_t<1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st);
+    case 16: return launch_gemv_t<2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st);
+    case 32: return launch_gemv_t<4>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st);
+    default: return set_error(DQ_ERR_SHAPE, "register-path token capacity must be 8/16/32 (got %d)", tok);
+  }
+}
+
+}  // namespace dq

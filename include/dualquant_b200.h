@@ -157,8 +157,9 @@ DQ_API int dq_gemm_w4a4_int4(const int8_t* codes, const float* sx, const uint8_t
                       const void* sw_t, const float* r, int M, int N, int K, int G, void* y,
                       int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
-/* As above with explicit tiling (token tile 16/32/64/128 or 0 = auto, split-K 1/2/4/8 or
- * 0 = auto); used by tuning sweeps and tests. */
+/* As above with an explicit kernel choice; used by tuning sweeps and tests.  token_tile: 0 = auto,
+ * 16/32/64/128 = tensor-memory (tcgen05) kernel with that token tile, -8/-16/-32 = decode-batch
+ * kernel with that token capacity (needs M <= capacity).  split_k: 0 = auto, else 1/2/4/8. */
 DQ_API int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                          const void* sw_t, const float* r, int M, int N, int K, int G, void* y,
                          int y_dtype, void* workspace, size_t workspace_bytes, void* stream,

@@ -182,7 +182,11 @@ def test_gemm_accumulators_extreme_codes():
     (1, 128, 128, 0, 0), (1, 256, 1024, 16, 1), (1, 256, 1024, 16, 8), (8, 384, 512, 16, 4),
     (16, 4096, 4096, 0, 0), (20, 256, 512, 32, 2), (32, 512, 1024, 32, 8), (50, 200, 640, 64, 1),
     (64, 256, 2048, 64, 4), (128, 256, 512, 128, 1), (128, 384, 1024, 128, 2),
-    (300, 640, 384, 128, 1), (7, 136, 256, 0, 0),
+    (300, 640, 384, 128, 1), (7, 136, 256, 0, 0), (7, 136, 256, 16, 1),
+    # decode-batch (register-path) kernel: negative token_tile = token capacity
+    (1, 256, 1024, -8, 1), (1, 256, 1024, -8, 8), (8, 384, 512, -8, 4), (5, 200, 384, -8, 2),
+    (16, 4096, 4096, -16, 0), (12, 256, 512, -16, 2), (16, 128, 14336, -16, 8),
+    (20, 256, 512, -32, 2), (32, 512, 1024, -32, 8), (3, 136, 256, -32, 1),
 ])
 def test_gemm_output_matches_oracle(M, N, K, tn, split):
     _, _, r, _, qx, sx, qw, sw = _operands(M, N, K, seed=M + N)
