@@ -1,0 +1,154 @@
+"""PermLinear: drop-in for the reference's runtime wrapper (activations/perm_linear.py:41-141,
+activations/__init__.py:16-27) that runs the real W4A4 path on sm_100a.
+
+Same constructor, attributes and methods as the reference module.  Where the reference
+fake-quantises (quantise, de-quantise to bf16, bf16 F.linear against a fake-quant weight), this
+module packs the wrapped layer's weight to int4 once and calls the library: fused activation
+scale / online Hadamard / per-token int4 quantiser, then the int4 x int4 GEMM with exact int32
+group sums and an fp32 epilogue.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import _lib, ops
+from .quarot import full_hadamard_scale, partial_hadamard_scale
+
+GROUP = 128
+
+
+class PermLinear(nn.Module):
+    def __init__(self, layer: nn.Linear, act_fmt, quantize_bmm_input: bool = False):
+        super().__init__()
+        self.layer = layer
+        self.dtype = layer.weight.dtype
+        self.act_fmt = act_fmt  # FormatSpec
+        self.quantize_bmm_input = quantize_bmm_input
+        self.register_buffer("act_scale", None)
+
+        # QuaRot online-Hadamard state, set by install_online_hadamards
+        self.online_full_had = False
+        self.online_partial_had = False
+        self.had_K = None
+        self.K = 1
+        self.had_dim = 0
+        self.fp32_had = False
+
+        # False: the activation cast is skipped (the online Hadamard still runs)
+        self.act_quant_enabled = True
+
+        # packed weight artefact, built on first use (or by pack())
+        self._packed: Optional[ops.PackedInt4Weight] = None
+        self._hadamard_cache = None
+        self._scratch: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ reference surface
+    def set_act_scale(self, act_scale):
+        if act_scale is not None:
+            act_scale = act_scale.detach().clone().to(torch.float32)
+        self.act_scale = act_scale
+
+    def set_act_quant_enabled(self, enabled: bool) -> None:
+        self.act_quant_enabled = bool(enabled)
+
+    # ------------------------------------------------------------------ weight packing
+    def pack(self, codes: Optional[torch.Tensor] = None, sw: Optional[torch.Tensor] = None) -> None:
+        """Builds the int4 artefact.  Without arguments the wrapped layer's (fake-quant) weight is
+        re-quantised per group of 128 along K, which is how the reference's real-kernel scripts
+        recover codes and scales from `mat_q` (validate_real_kernel.py:95-98 via
+        pack_int4_weights).  `codes` (int8 [N,K]) and `sw` (fp16 [N,K/128]) may be given directly."""
+        w = self.layer.weight
+        if not w.is_cuda:
+            raise RuntimeError("PermLinear.pack needs the layer on a CUDA device (no CPU path)")
+        if codes is None:
+            codes, sw = ops.quant_w_int4(w.detach().to(torch.bfloat16))
+        self._packed = ops.pack_w_int4(codes.to(w.device), sw.to(w.device))
+
+    def _hadamard(self, device) -> Optional[ops.Hadamard]:
+        if not (self.online_full_had or self.online_partial_had):
+            return None
+        if self._hadamard_cache is not None and self._hadamard_cache[0] == device:
+            return self._hadamard_cache[1]
+        K = self.layer.in_features
+        if self.online_full_had:
+            mat = None if self.had_K is None else self.had_K.to(device=device, dtype=torch.float32).contiguous()
+            had = ops.Hadamard(_lib.HAD_FULL, int(self.K), 0, full_hadamard_scale(K), mat)
+        else:
+            if self.K != 1:
+                raise NotImplementedError("partial online Hadamard with a non-power-of-two head count")
+            had = ops.Hadamard(_lib.HAD_PARTIAL, 1, int(self.had_dim),
+                               partial_hadamard_scale(K // int(self.had_dim)), None)
+        self._hadamard_cache = (device, had)
+        return had
+
+    def _int4_path(self) -> bool:
+        return (self.act_quant_enabled and getattr(self.act_fmt, "name", None) == "rtn_int4"
+                and self.act_fmt.block_size == -1 and self.layer.in_features % GROUP == 0)
+
+    # ------------------------------------------------------------------ forward
+    def _quantise_act(self, x):
+        """The reference's activation path as a de-quantised tensor (perm_linear.py:108-134);
+        used when the int4 GEMM does not apply (act quant disabled, other formats)."""
+        x2 = x.reshape(-1, x.shape[-1])
+        had = self._hadamard(x.device)
+        if self.act_quant_enabled:
+            if getattr(self.act_fmt, "name", None) == "rtn_int4" and self.act_fmt.block_size == -1:
+                xin = x2 if x2.dtype in (torch.bfloat16, torch.float32) else x2.float()
+                out = ops.fakequant_act_int4(xin.contiguous(), self.act_scale, had, scale_fp16=False)
+            else:
+                x32 = x2.float()
+                if self.act_scale is not None:
+                    x32 = x32 * self.act_scale
+                if had is not None:
+                    x32 = ops.hadamard_f32(x32, had)
+                out = self.act_fmt.cast(x32)
+        else:
+            x32 = x2.float()
+            if self.act_scale is not None:
+                x32 = x32 * self.act_scale
+            out = ops.hadamard_f32(x32, had) if had is not None else x32
+        return out.to(self.dtype).reshape(x.shape)
+
+    def forward(self, x):
+        if not x.is_cuda:
+            raise RuntimeError("dualquant_b200.PermLinear runs on CUDA (sm_100a) tensors only")
+        if self._int4_path():
+            if self._packed is None:
+                self.pack()
+            pw = self._packed
+            x2 = x.reshape(-1, x.shape[-1])
+            if x2.dtype != torch.bfloat16:
+                x2 = x2.to(torch.bfloat16)
+            M = x2.shape[0]
+            need = ops.linear_scratch_bytes(M, pw.N, pw.K)
+            if self._scratch is None or self._scratch.numel() < need or self._scratch.device != x.device:
+                self._scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+            out_dtype = self.dtype if self.dtype in (torch.bfloat16, torch.float32) else torch.float32
+            out = ops.linear_w4a4_int4(x2, self.act_scale, self._hadamard(x.device), pw, None,
+                                       out_dtype=out_dtype, scale_fp16=False, scratch=self._scratch)
+            out = out.to(self.dtype)
+            if self.layer.bias is not None:
+                out = out + self.layer.bias
+            out = out.reshape(x.shape[:-1] + (pw.N,))
+        else:
+            out = self.layer(self._quantise_act(x))
+        if self.quantize_bmm_input:
+            out = self.act_fmt.cast(out.to(torch.float32)).to(self.dtype)
+        return out
+
+
+def install_perm_linear(parent: nn.Module, attr_name: str, act_fmt, col_scales=None,
+                        quantize_bmm_input: bool = False) -> PermLinear:
+    """Wraps parent.<attr_name> (an nn.Linear) with a PermLinear in place and seeds its
+    activation scale (activations/__init__.py:16-27)."""
+    layer = getattr(parent, attr_name)
+    perm = PermLinear(layer, act_fmt=act_fmt, quantize_bmm_input=quantize_bmm_input)
+    perm.set_act_scale(col_scales)
+    setattr(parent, attr_name, perm)
+    return perm
+
+
+__all__ = ["PermLinear", "install_perm_linear"]

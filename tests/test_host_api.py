@@ -1,0 +1,56 @@
+"""Host-side mirror of the reference API: pieces that need no GPU."""
+import types
+
+import pytest
+import torch
+import torch.nn as nn
+
+from dualquant_b200 import formats, quarot
+from dualquant_b200.activations import PermLinear, install_perm_linear
+
+
+def test_get_hadK_matches_reference_matrix(golden):
+    had, k = quarot.get_hadK(14336)
+    assert k == 28
+    assert torch.equal(had, torch.from_numpy(golden["had28"]).float())
+    assert quarot.get_hadK(4096) == (None, 1)
+    with pytest.raises(NotImplementedError):
+        quarot.get_hadK(12 * 64)
+    assert quarot.full_hadamard_scale(14336) == float((1.0 / torch.tensor(14336).sqrt()).item())
+
+
+def test_make_format_surface():
+    f = formats.make_format("rtn_int4", block_size=-1)
+    assert (f.name, f.block_size, f.max_val) == ("rtn_int4", -1, 7.0)
+    assert torch.equal(f.cast_element_only(torch.tensor([-9.4, 0.5, 1.5, 7.7])),
+                       torch.tensor([-8.0, 0.0, 2.0, 7.0]))
+    with pytest.raises(ValueError):
+        formats.make_format("int3")
+    with pytest.raises(RuntimeError):
+        f.cast(torch.zeros(2, 128))  # CPU tensor: no CPU path
+
+
+def test_perm_linear_attributes_and_install():
+    parent = nn.Module()
+    parent.down_proj = nn.Linear(256, 128, bias=False).to(torch.bfloat16)
+    parent.o_proj = nn.Linear(256, 128, bias=False).to(torch.bfloat16)
+    fmt = formats.make_format("rtn_int4", block_size=-1)
+    pl = install_perm_linear(parent, "down_proj", fmt, col_scales=torch.ones(256, dtype=torch.float64))
+    install_perm_linear(parent, "o_proj", fmt)
+    assert isinstance(parent.down_proj, PermLinear) and parent.down_proj is pl
+    assert pl.act_scale.dtype == torch.float32 and pl.dtype == torch.bfloat16
+    for attr, val in (("online_full_had", False), ("online_partial_had", False), ("had_K", None),
+                      ("K", 1), ("had_dim", 0), ("fp32_had", False), ("act_quant_enabled", True),
+                      ("quantize_bmm_input", False)):
+        assert getattr(pl, attr) == val if val is not None else getattr(pl, attr) is None
+    pl.set_act_quant_enabled(0)
+    assert pl.act_quant_enabled is False
+    model = nn.Module()
+    model.block = parent
+    model.config = types.SimpleNamespace(intermediate_size=28 * 64, num_attention_heads=32,
+                                         hidden_size=256, head_dim=None)
+    quarot.install_online_hadamards(model)
+    assert parent.down_proj.online_full_had and parent.down_proj.K == 28
+    assert parent.o_proj.online_partial_had and parent.o_proj.K == 1 and parent.o_proj.had_dim == 8
+    with pytest.raises(RuntimeError):
+        pl(torch.zeros(2, 256, dtype=torch.bfloat16))  # CPU tensor
