@@ -12,6 +12,10 @@ namespace dq {
 
 constexpr int kMaxDevices = 16;
 constexpr int kGroup = 128;  // weight-group size = K extent of one pipeline stage
+// One streamed weight tile: 128 rows x 128 k of packed int4 (8192 B) followed by the 128 fp16
+// group scales of those rows (256 B).
+constexpr int kTileCodeBytes = 8192;
+constexpr int kTileBytes = kTileCodeBytes + 256;
 
 // Per-device state created by dq_init.
 struct DeviceState {

@@ -284,9 +284,9 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     uint64_t pol_w, pol_x;
     if (w_stream_once) pol_w = l2_policy_evict_first(); else pol_w = l2_policy_evict_last();
     pol_x = l2_policy_evict_last();
-    // packed tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB]
+    // tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB codes + scales]
     const uint8_t* w_tile =
-        w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kWpBytes;
+        w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kTileBytes;
     const int nxc = (ng + C::XC - 1) / C::XC;
     int iw = 0, ix = 0;
     long long t_last = clock64();
@@ -299,7 +299,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
           if (lane == 0) {
             mbar_expect_tx(&full_p[sp], kWpBytes);
             bulk_load_1d(smem + C::kOffP + sp * kWpBytes,
-                         w_tile + static_cast<size_t>(g_begin + iw) * kWpBytes, kWpBytes,
+                         w_tile + static_cast<size_t>(g_begin + iw) * kTileBytes, kWpBytes,
                          &full_p[sp], pol_w);
             DQ_TR(3, iw, 0);
           }

@@ -4,12 +4,13 @@
 // With a handful of tokens the job is to stream the packed weights out of HBM once, so this
 // kernel is built around bytes in flight rather than around the tensor memory pipeline:
 //
-//   * one producer warp keeps a ring of stages full; a stage is one weight group of the CTA's
-//     128 rows: 8 KB of packed int4 (one contiguous bulk copy), its 128 fp16 group scales
-//     (256 B bulk copy) and the int8 activation codes of the group (TMA tile, 128B swizzle);
+//   * one producer warp keeps a ring of stages full; a stage is two consecutive weight groups of
+//     the CTA's 128 rows - 2 x (8 KB of packed int4 + 256 B of fp16 group scales), contiguous in
+//     memory and fetched by ONE bulk copy - plus the int8 activation codes of those groups
+//     (one tiled copy);
 //     the ring depth is chosen at launch so that the CTAs sharing an SM together keep
 //     well over 100 KB of weights in flight (throughput = bytes in flight / HBM latency);
-//   * eight compute warps each own 16 weight rows.  A lane reads its packed nibbles straight
+//   * eight compute warps, each owning 16 weight rows.  A lane reads its packed nibbles straight
 //     from the stage (two 16-byte loads), splits them in registers ((w << 4) & 0xF0.. and
 //     w & 0xF0.., i.e. 16 * code, the 1/16 folded into the group scale) and feeds
 //     mma.sync.m16n8k32.s8 with int32 accumulation per group - no second shared-memory pass,
@@ -26,27 +27,27 @@
 
 namespace dq {
 
-constexpr int kVBN = 128;                 // weight rows per CTA
-constexpr int kVThreads = 288;            // 8 compute warps + 1 producer warp
-constexpr int kVWBytes = kVBN * kGroup / 2;  // 8 KB packed weights per stage
-constexpr int kVSBytes = kVBN * 2;           // 256 B of fp16 group scales per stage
+constexpr int kVBN = 128;       // weight rows per CTA
+constexpr int kVSets = 1;  // warp sets that split the groups of a stage between them (1 or 2)
+constexpr int kVComputeWarps = 8 * kVSets;
+constexpr int kVThreads = (kVComputeWarps + 1) * 32;  // + 1 producer warp
+constexpr int kVGS = 2;         // weight groups per pipeline stage
 
 template <int NT>  // NT = number of 8-token blocks (tokens handled: 8 * NT)
 struct VCfg {
   static constexpr int TOK = 8 * NT;
-  static constexpr int kXRows = (TOK < 16) ? 16 : TOK;  // rows of the activation tile box
-  static constexpr int kXBytes = kXRows * kGroup;
+  static constexpr int kXRows = (TOK < 16) ? 16 : TOK;       // rows of the activation tile box
+  static constexpr int kXPitch = kVGS * kGroup;               // bytes per token row in a stage
+  static constexpr int kXBytes = kXRows * kXPitch;
   static constexpr int kOffX = 0;
-  static constexpr int kOffW = kXBytes;
-  static constexpr int kOffS = kOffW + kVWBytes;
-  static constexpr int kStage = (kOffS + kVSBytes + 1023) / 1024 * 1024;
+  static constexpr int kOffW = kXBytes;                       // kVGS tiles of kTileBytes
+  static constexpr int kStage = (kOffW + kVGS * kTileBytes + 127) / 128 * 128;
   // The ring depth is a launch parameter: the host gives each CTA as many stages as fit next to
   // the other CTAs expected on its SM, because throughput here is (bytes in flight) / (HBM latency).
   static constexpr int kMinStages = 2;
-  static constexpr int kMaxStages = 18;
-  static constexpr int kMinCtas = (NT <= 2) ? 4 : 3;
+  static constexpr int kMaxStages = 10;
+  static constexpr int kMinCtas = (kVSets == 1) ? ((NT == 1) ? 4 : (NT == 2) ? 3 : 2) : ((NT <= 2) ? 2 : 1);
   static constexpr int kBarBytes = 2 * kMaxStages * 8 + 16;
-  static constexpr uint32_t kTxBytes = kXBytes + kVWBytes + kVSBytes;
   static_assert(TOK * kVBN * 4 <= kMinStages * kStage, "split-K exchange tile must fit in the ring");
   static constexpr int smem_bytes(int stages) { return stages * kStage + kBarBytes + 1024; }
 };
@@ -55,8 +56,7 @@ enum { VSITE_PRODUCER = 21, VSITE_COMPUTE = 22 };
 
 __device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -66,9 +66,9 @@ template <int NT>
 __global__ void __launch_bounds__(kVThreads, VCfg<NT>::kMinCtas)
 gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
-                      const __half* __restrict__ sw_t, const float* __restrict__ r,
-                      const float* __restrict__ sx, void* __restrict__ y, int y_bf16, int M, int N,
-                      int K, int groups_per_split, int split_k, int stages, int* status) {
+                      const float* __restrict__ r, const float* __restrict__ sx,
+                      void* __restrict__ y, int y_bf16, int M, int N, int K, int groups_per_split,
+                      int split_k, int stages, int* status) {
   using C = VCfg<NT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -86,34 +86,38 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   int g_end = g_begin + groups_per_split;
   if (g_end > total_groups) g_end = total_groups;
   const int ng = (g_end > g_begin) ? (g_end - g_begin) : 0;
+  const int nst = (ng + kVGS - 1) / kVGS;  // pipeline stages this CTA walks through
 
   if (tid == 0) {
-    for (int i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 8); }
+    for (int i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], kVComputeWarps); }
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 8 && lane == 0) tma_prefetch_desc(&tm_x);
+  if (warp == kVComputeWarps && lane == 0) tma_prefetch_desc(&tm_x);
   __syncthreads();
 
-  if (warp == 8) {
+  if (warp == kVComputeWarps) {
     // ------------------------------------------------------------------ producer warp
+    // Per stage: one bulk copy (codes + scales of up to kVGS consecutive groups, contiguous in
+    // memory) and one tiled copy of the activation codes.  Every asynchronous-copy instruction
+    // costs this warp tens of cycles of issue latency, so a stage is made as large as practical.
     const uint64_t pol_w = l2_policy_evict_first();
     const uint64_t pol_x = l2_policy_evict_last();
-    const size_t tile_group0 = static_cast<size_t>(blockIdx.x) * total_groups + g_begin;
-    const uint8_t* w_src = w_packed + tile_group0 * kVWBytes;
-    const uint8_t* s_src = reinterpret_cast<const uint8_t*>(sw_t) + tile_group0 * kVSBytes;
+    const uint8_t* w_src =
+        w_packed + (static_cast<size_t>(blockIdx.x) * total_groups + g_begin) * kTileBytes;
     int s = 0;
     uint32_t ph = 1;  // parity of the "stage is free" phase being waited for
-    for (int i = 0; i < ng; ++i) {
+    for (int i = 0; i < nst; ++i) {
       if (!mbar_wait(&empty[s], ph, abort_flag, VSITE_PRODUCER)) break;
       if (lane == 0) {
         uint8_t* st = smem + s * C::kStage;
-        mbar_expect_tx(&full[s], C::kTxBytes);
-        bulk_load_1d(st + C::kOffW, w_src + static_cast<size_t>(i) * kVWBytes, kVWBytes, &full[s],
-                     pol_w);
-        bulk_load_1d(st + C::kOffS, s_src + static_cast<size_t>(i) * kVSBytes, kVSBytes, &full[s],
-                     pol_w);
-        tma_load_2d(st + C::kOffX, &tm_x, (g_begin + i) * kGroup, 0, &full[s], pol_x);
+        int cnt = ng - i * kVGS;
+        if (cnt > kVGS) cnt = kVGS;
+        const uint32_t wbytes = static_cast<uint32_t>(cnt) * kTileBytes;
+        mbar_expect_tx(&full[s], wbytes + C::kXBytes);
+        bulk_load_1d(st + C::kOffW, w_src + static_cast<size_t>(i) * kVGS * kTileBytes, wbytes,
+                     &full[s], pol_w);
+        tma_load_2d(st + C::kOffX, &tm_x, (g_begin + i * kVGS) * kGroup, 0, &full[s], pol_x);
       }
       __syncwarp();
       if (++s == stages) { s = 0; ph ^= 1u; }
@@ -122,7 +126,8 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     // ------------------------------------------------------------------ compute warps
     const int g = lane >> 2;  // fragment row / token index inside an 8-block
     const int t = lane & 3;
-    const int row = warp * 16 + g;  // local weight row (and row + 8)
+    const int set = warp >> 3;      // which group of each stage this warp works on
+    const int row = (warp & 7) * 16 + g;  // local weight row (and row + 8)
     float run[NT][4];
 #pragma unroll
     for (int nb = 0; nb < NT; ++nb)
@@ -131,49 +136,99 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 
     int s = 0;
     uint32_t ph = 0;
-    for (int i = 0; i < ng; ++i) {
+    for (int i = 0; i < nst; ++i) {
       if (!mbar_wait(&full[s], ph, abort_flag, VSITE_COMPUTE)) break;
       const uint8_t* st = smem + s * C::kStage;
-      const uint4 wa = *reinterpret_cast<const uint4*>(st + C::kOffW + row * 64 + t * 16);
-      const uint4 wb = *reinterpret_cast<const uint4*>(st + C::kOffW + (row + 8) * 64 + t * 16);
-      const __half* sc = reinterpret_cast<const __half*>(st + C::kOffS);
-      const float s0 = __half2float(sc[row]) * 0.0625f;
-      const float s1 = __half2float(sc[row + 8]) * 0.0625f;
-      // Word j of a lane's 16-byte chunk feeds MMA step j: low nibbles are k = 32t + 4j + {0..3}
-      // of the group (fragment slots a0/a1), high nibbles k = 32t + 16 + 4j + {0..3} (a2/a3).
-      const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
-      const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
-      uint32_t a0[4], a1[4], a2[4], a3[4];
+      int cnt = ng - i * kVGS;
+      if (cnt > kVGS) cnt = kVGS;
+      // with two warp sets, warps 0-7 take the first group of the stage and warps 8-15 the second
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        a0[j] = (wav[j] << 4) & 0xF0F0F0F0u;
-        a2[j] = wav[j] & 0xF0F0F0F0u;
-        a1[j] = (wbv[j] << 4) & 0xF0F0F0F0u;
-        a3[j] = wbv[j] & 0xF0F0F0F0u;
-      }
+      for (int gi = set; gi < kVGS; gi += kVSets) {
+        if (gi >= cnt) break;
+        const uint8_t* tile = st + C::kOffW + gi * kTileBytes;
+        const uint4 wa = *reinterpret_cast<const uint4*>(tile + row * 64 + t * 16);
+        const uint4 wb = *reinterpret_cast<const uint4*>(tile + (row + 8) * 64 + t * 16);
+        const __half* sc = reinterpret_cast<const __half*>(tile + kTileCodeBytes);
+        const float s0 = __half2float(sc[row]) * 0.0625f;
+        const float s1 = __half2float(sc[row + 8]) * 0.0625f;
+        uint4 xlo[NT], xhi[NT];
 #pragma unroll
-      for (int nb = 0; nb < NT; ++nb) {
-        const int n = nb * 8 + g;  // token row of the activation tile (128B-swizzled rows)
-        const uint8_t* xr = st + C::kOffX + n * 128;
-        const uint4 xlo = *reinterpret_cast<const uint4*>(xr + (((2 * t) ^ (n & 7)) << 4));
-        const uint4 xhi = *reinterpret_cast<const uint4*>(xr + (((2 * t + 1) ^ (n & 7)) << 4));
-        const uint32_t b0[4] = {xlo.x, xlo.y, xlo.z, xlo.w};
-        const uint32_t b1[4] = {xhi.x, xhi.y, xhi.z, xhi.w};
-        int c[4] = {0, 0, 0, 0};
+        for (int nb = 0; nb < NT; ++nb) {
+          // activation codes: [token][kVGS * 128] bytes, group gi at byte offset gi * 128
+          const uint8_t* xr = st + C::kOffX + (nb * 8 + g) * C::kXPitch + gi * kGroup + 32 * t;
+          xlo[nb] = *reinterpret_cast<const uint4*>(xr);
+          xhi[nb] = *reinterpret_cast<const uint4*>(xr + 16);
+        }
+        // Word j of a lane's 16-byte chunk feeds MMA step j: low nibbles are
+        // k = 32t + 4j + {0..3} of the group (fragment slots a0/a1), high nibbles
+        // k = 32t + 16 + 4j + {0..3} (a2/a3).
+        const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
+        const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
+        int c[NT][2][4];  // two partial accumulators per token block: dependent chains of 2 MMAs
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma_s8_16x8x32(c, a0[j], a1[j], a2[j], a3[j], b0[j], b1[j]);
-        run[nb][0] = fmaf(static_cast<float>(c[0]), s0, run[nb][0]);
-        run[nb][1] = fmaf(static_cast<float>(c[1]), s0, run[nb][1]);
-        run[nb][2] = fmaf(static_cast<float>(c[2]), s1, run[nb][2]);
-        run[nb][3] = fmaf(static_cast<float>(c[3]), s1, run[nb][3]);
+        for (int nb = 0; nb < NT; ++nb)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { c[nb][0][e] = 0; c[nb][1][e] = 0; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t a0 = (wav[j] << 4) & 0xF0F0F0F0u;
+          const uint32_t a2 = wav[j] & 0xF0F0F0F0u;
+          const uint32_t a1 = (wbv[j] << 4) & 0xF0F0F0F0u;
+          const uint32_t a3 = wbv[j] & 0xF0F0F0F0u;
+#pragma unroll
+          for (int nb = 0; nb < NT; ++nb) {
+            const uint32_t b0 = (j == 0) ? xlo[nb].x : (j == 1) ? xlo[nb].y : (j == 2) ? xlo[nb].z : xlo[nb].w;
+            const uint32_t b1 = (j == 0) ? xhi[nb].x : (j == 1) ? xhi[nb].y : (j == 2) ? xhi[nb].z : xhi[nb].w;
+            mma_s8_16x8x32(c[nb][j & 1], a0, a1, a2, a3, b0, b1);
+          }
+        }
+#pragma unroll
+        for (int nb = 0; nb < NT; ++nb) {
+          run[nb][0] = fmaf(static_cast<float>(c[nb][0][0] + c[nb][1][0]), s0, run[nb][0]);
+          run[nb][1] = fmaf(static_cast<float>(c[nb][0][1] + c[nb][1][1]), s0, run[nb][1]);
+          run[nb][2] = fmaf(static_cast<float>(c[nb][0][2] + c[nb][1][2]), s1, run[nb][2]);
+          run[nb][3] = fmaf(static_cast<float>(c[nb][0][3] + c[nb][1][3]), s1, run[nb][3]);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
       if (++s == stages) { s = 0; ph ^= 1u; }
     }
 
+    // Fold the second warp set's partial sums into the first through shared memory.  All compute
+    // warps are past their last stage at the first barrier, so the ring can be reused.
+    if constexpr (kVSets == 2) {
+      float* red = reinterpret_cast<float*>(smem);
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      if (set == 1) {
+#pragma unroll
+        for (int nb = 0; nb < NT; ++nb)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int m = nb * 8 + 2 * t + e;
+            red[m * kVBN + row] = run[nb][e];
+            red[m * kVBN + row + 8] = run[nb][2 + e];
+          }
+      }
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      if (set == 0) {
+#pragma unroll
+        for (int nb = 0; nb < NT; ++nb)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int m = nb * 8 + 2 * t + e;
+            run[nb][e] += red[m * kVBN + row];
+            run[nb][2 + e] += red[m * kVBN + row + 8];
+          }
+      }
+    }
     // accumulator fragment: c0/c1 = (row, tokens 2t, 2t+1), c2/c3 = (row + 8, same tokens)
-    if (split_k == 1) {
+    if constexpr (kVSets == 1) {
+      if (split_k > 1) asm volatile("bar.sync 1, 256;" ::: "memory");  // ring reused as exchange tile
+    }
+    if (set == 1) {
+      // nothing left to do for the second set
+    } else if (split_k == 1) {
 #pragma unroll
       for (int hrow = 0; hrow < 2; ++hrow) {
         const int n = n0 + row + 8 * hrow;
@@ -196,8 +251,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
       }
     } else {
-      // all compute warps are past their last stage before the ring is reused as exchange tile
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      // each thread overwrites exactly the exchange-tile entries it has just read
       float* red = reinterpret_cast<float*>(smem);
 #pragma unroll
       for (int nb = 0; nb < NT; ++nb)
@@ -214,7 +268,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   if (split_k > 1) {
     __syncwarp();
     cluster_sync_all();
-    if (warp < 8) {
+    if (warp < 8) {  // 256 threads finish this CTA's share of the tile
       const uint32_t rank = cluster_ctarank();
       const int rows = C::TOK / split_k;  // token rows of the tile this CTA finishes
       const int c4 = tid & 31;            // float4 column
@@ -274,10 +328,11 @@ int init_gemv_int4_kernels() {
   return DQ_OK;
 }
 
+// Smallest power-of-two split that gives roughly one CTA per SM (measured optimum on the
+// Llama-3.1-8B decode shapes: more splits cost more in cluster exchange than they win).
 int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count) {
-  const int target = 3 * sm_count;
   int s = 1;
-  while (s < 8 && tiles * s < target && total_groups / (2 * s) >= 2 && 2 * s <= tok) s *= 2;
+  while (s < 8 && tiles * s * 6 < sm_count * 5 && total_groups / (2 * s) >= 2 && 2 * s <= tok) s *= 2;
   return s;
 }
 
@@ -287,7 +342,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
                          int y_dtype, int split, cudaStream_t stream, DeviceState* st) {
   using C = VCfg<NT>;
   CUtensorMap tm_x;
-  int rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, kGroup, C::kXRows, CU_TENSOR_MAP_SWIZZLE_128B);
+  int rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, C::kXPitch, C::kXRows, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != DQ_OK) return rc;
   const int total_groups = K / kGroup;
   const int gps = (total_groups + split - 1) / split;
@@ -299,7 +354,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
   const int avail = (227 * 1024) / per_sm - 1024 - C::kBarBytes - 1024;
   int stages = avail / C::kStage;
   if (stages > C::kMaxStages) stages = C::kMaxStages;
-  if (stages > gps) stages = gps;
+  if (stages > (gps + kVGS - 1) / kVGS) stages = (gps + kVGS - 1) / kVGS;
   if (stages < C::kMinStages) stages = C::kMinStages;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles_n, 1, split);
@@ -313,7 +368,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
   attr[0].val.clusterDim.z = split;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT>, w_packed, tm_x, sw_t, r, sx, y,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT>, w_packed, tm_x, r, sx, y,
                                      y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, gps, split,
                                      stages, st->status_dev);
   if (e != cudaSuccess)

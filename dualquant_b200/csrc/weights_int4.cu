@@ -1,17 +1,19 @@
 // Offline weight-side kernels: per-group int4 quantiser, re-packing of int4 codes into the
 // streaming layout the GEMM consumes, and the inverse (test hook).
 //
-// Streaming layout ("w_packed", uint8, ceil(N/128)*128*K/2 bytes): the matrix is cut into tiles
-// of 128 rows x 128 k (one GEMM pipeline stage, 8 KB packed) stored contiguously in the order
-// [row tile][k group][row in tile][64 bytes], so a CTA that walks along K for its 128 rows reads
-// one contiguous run of HBM.  Rows past N are zero.  Inside a tile row, 16-byte chunk ch covers
+// Streaming layout ("w_packed", uint8, ceil(N/128)*(K/128)*8448 bytes): the matrix is cut into
+// tiles of 128 rows x 128 k (one GEMM pipeline stage).  A tile is 8192 bytes of packed codes
+// ([row in tile][64 bytes]) followed by the 128 fp16 group scales of its rows (256 bytes); tiles
+// are stored in the order [row tile][k group], so a CTA that walks along K for its 128 rows reads
+// one contiguous run of HBM and one bulk copy brings codes and scales of a stage.  Rows past N
+// are zero.  Inside a tile row, 16-byte chunk ch covers
 // k in [32ch, 32ch+32) of the group; byte b of the chunk holds code[32ch + b] in its low nibble
 // and code[32ch + 16 + b] in its high nibble, both as two's-complement 4-bit values.  With this
 // order `(w << 4) & 0xF0F0F0F0` and `w & 0xF0F0F0F0` on a 16-byte chunk yield two 16-byte runs of
 // consecutive k (times 16) - the GEMM's unpack warps need no byte shuffles.
-// Group scales ("sw_t", fp16, ceil(N/128)*128*(K/G) values) follow the same tiling:
-// [row tile][k group][row in tile], so the 128 scales a CTA needs per stage are one 256-byte run
-// and consecutive stages are consecutive runs.  Rows past N hold 0.
+// The group scales are also kept on their own ("sw_t", fp16, ceil(N/128)*128*(K/G) values,
+// [row tile][k group][row in tile], rows past N zero) for the kernel whose epilogue reads them
+// from global memory.
 #include "dq_common.h"
 
 #include <cuda_bf16.h>
@@ -51,7 +53,8 @@ __global__ void pack_w_int4_kernel(const int8_t* __restrict__ codes,
       w[b >> 2] |= (lo | (hi << 4)) << (8 * (b & 3));
     }
   }
-  *reinterpret_cast<uint4*>(w_packed + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(w_packed + tg * kTileBytes + (chunk & 511) * 16) =
+      make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 __global__ void unpack_w_int4_kernel(const uint8_t* __restrict__ w_packed, int N, int K,
@@ -67,7 +70,7 @@ __global__ void unpack_w_int4_kernel(const uint8_t* __restrict__ w_packed, int N
   const int64_t row = (tg / groups) * 128 + r;
   if (row >= N) return;
   const int c = g * 4 + ch;
-  const uint4 raw = *reinterpret_cast<const uint4*>(w_packed + chunk * 16);
+  const uint4 raw = *reinterpret_cast<const uint4*>(w_packed + tg * kTileBytes + (chunk & 511) * 16);
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   int8_t* dst = codes + row * K + 32 * c;
 #pragma unroll
@@ -79,7 +82,7 @@ __global__ void unpack_w_int4_kernel(const uint8_t* __restrict__ w_packed, int N
 }
 
 __global__ void transpose_sw_kernel(const __half* __restrict__ sw, int N, int groups,
-                                    __half* __restrict__ sw_t) {
+                                    __half* __restrict__ sw_t, uint8_t* __restrict__ w_packed) {
   // output index = (tile * groups + g) * 128 + r
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t tiles = (N + 127) / 128;
@@ -88,7 +91,9 @@ __global__ void transpose_sw_kernel(const __half* __restrict__ sw, int N, int gr
   const int64_t tg = i >> 7;
   const int g = static_cast<int>(tg % groups);
   const int64_t n = (tg / groups) * 128 + r;
-  sw_t[i] = (n < N) ? sw[n * groups + g] : __float2half_rn(0.f);
+  const __half v = (n < N) ? sw[n * groups + g] : __float2half_rn(0.f);
+  sw_t[i] = v;
+  reinterpret_cast<__half*>(w_packed + tg * kTileBytes + kTileCodeBytes)[r] = v;
 }
 
 // One warp per (row, group of 128): s = absmax/7 rounded to fp16 (1 for a zero group),
@@ -140,7 +145,7 @@ using namespace dq;
 
 extern "C" size_t dq_packed_w_bytes(int N, int K) {
   if (N <= 0 || K <= 0) return 0;
-  return (static_cast<size_t>(N) + 127) / 128 * 128 * static_cast<size_t>(K) / 2;
+  return (static_cast<size_t>(N) + 127) / 128 * (static_cast<size_t>(K) / kGroup) * kTileBytes;
 }
 
 extern "C" int dq_pack_w_int4(const int8_t* codes, const uint8_t* ref_packed, const void* sw, int N,
@@ -157,12 +162,12 @@ extern "C" int dq_pack_w_int4(const int8_t* codes, const uint8_t* ref_packed, co
   pack_w_int4_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, s>>>(codes, ref_packed, N,
                                                                                  K, w_packed);
   DQ_CHECK_CUDA(cudaGetLastError());
-  if (sw != nullptr || sw_t != nullptr) {
-    DQ_REQUIRE(sw != nullptr && sw_t != nullptr, DQ_ERR_NULL, "sw and sw_t must be given together");
+  {
+    DQ_REQUIRE(sw != nullptr && sw_t != nullptr, DQ_ERR_NULL, "sw and sw_t are required");
     const int groups = K / kGroup;
     const int64_t total = static_cast<int64_t>((N + 127) / 128) * 128 * groups;
     transpose_sw_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
-        static_cast<const __half*>(sw), N, groups, static_cast<__half*>(sw_t));
+        static_cast<const __half*>(sw), N, groups, static_cast<__half*>(sw_t), w_packed);
     DQ_CHECK_CUDA(cudaGetLastError());
   }
   return DQ_OK;

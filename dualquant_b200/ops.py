@@ -54,7 +54,7 @@ class Hadamard:
 class PackedInt4Weight:
     """Weight artefact the GEMM consumes: streaming int4 layout + transposed fp16 group scales."""
 
-    w_packed: torch.Tensor  # uint8, flat: [row tile][k group][128 rows][64 B]
+    w_packed: torch.Tensor  # uint8, flat: [row tile][k group][8192 B codes + 256 B scales]
     sw_t: torch.Tensor  # fp16, flat: [row tile][k group][128 rows]
     N: int
     K: int

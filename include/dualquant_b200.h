@@ -85,7 +85,8 @@ DQ_API int dq_abi_version(void);
 
 /* ---- weights ----------------------------------------------------------------------------- */
 
-/* Bytes of the packed weight matrix for (N, K): ceil(N/128)*128*K/2 (rows padded to the tile). */
+/* Bytes of the packed weight matrix for (N, K): ceil(N/128) * (K/128) tiles of 8448 bytes
+ * (8192 bytes of int4 codes + the tile's 128 fp16 group scales). */
 DQ_API size_t dq_packed_w_bytes(int N, int K);
 
 /*

@@ -191,20 +191,23 @@ def ref_unpack_int4(packed: torch.Tensor) -> torch.Tensor:
     return (out - 8).to(torch.int8)
 
 
-def stream_pack_int4(codes: torch.Tensor, group: int = GROUP) -> torch.Tensor:
-    """The library's streaming weight layout (flat uint8): tiles of 128 rows x 128 k stored
-    contiguously as [row tile][k group][row in tile][64 bytes], rows past N zero.  Within a
-    tile row, 16-byte chunk ch covers k in [32ch, 32ch+32) of the group and
+def stream_pack_int4(codes: torch.Tensor, sw: torch.Tensor, group: int = GROUP) -> torch.Tensor:
+    """The library's streaming weight layout (flat uint8).  Tiles of 128 rows x 128 k in the order
+    [row tile][k group]; a tile is 8192 bytes of codes ([row in tile][64 bytes]) followed by the
+    128 fp16 group scales of its rows (256 bytes); rows past N are zero.  Within a tile row,
+    16-byte chunk ch covers k in [32ch, 32ch+32) of the group and
     byte b = (code[32ch+b] & 0xF) | ((code[32ch+16+b] & 0xF) << 4), two's complement nibbles."""
     N, K = codes.shape
-    tiles = (N + 127) // 128
+    tiles, groups = (N + 127) // 128, K // group
     padded = torch.zeros(tiles * 128, K, dtype=torch.int16)
     padded[:N] = codes.to(torch.int16)
-    c = padded.reshape(tiles, 128, K // group, 4, 2, 16)
+    c = padded.reshape(tiles, 128, groups, 4, 2, 16)
     lo = c[..., 0, :] & 0xF
     hi = c[..., 1, :] & 0xF
     byt = (lo | (hi << 4)).to(torch.uint8)  # [tiles, 128, groups, 4, 16]
-    return byt.permute(0, 2, 1, 3, 4).contiguous().reshape(-1)
+    body = byt.permute(0, 2, 1, 3, 4).contiguous().reshape(tiles, groups, 8192)
+    scales = stream_pack_scales(sw).reshape(tiles, groups, 128).view(torch.uint8).reshape(tiles, groups, 256)
+    return torch.cat([body, scales], dim=2).reshape(-1)
 
 
 def stream_pack_scales(sw: torch.Tensor) -> torch.Tensor:

@@ -43,7 +43,7 @@ def test_quant_and_pack_weights_bit_exact(N, K):
     assert torch.equal(codes.cpu(), qw)
     assert torch.equal(sw_g.cpu().view(torch.int16), sw.view(torch.int16))
     pw = ops.pack_w_int4(codes, sw_g)
-    assert torch.equal(pw.w_packed.cpu(), O.stream_pack_int4(qw))
+    assert torch.equal(pw.w_packed.cpu(), O.stream_pack_int4(qw, sw))
     assert torch.equal(pw.sw_t.cpu(), O.stream_pack_scales(sw))
     assert torch.equal(ops.unpack_w_int4(pw).cpu(), qw)
     # the reference's packed form as the source gives the same artefact
@@ -236,7 +236,7 @@ def test_config0_full_size_against_oracle():
 
 def test_gemm_rejects_bad_arguments():
     qx = torch.zeros(4, 192, dtype=torch.int8, device=DEV)
-    pw = ops.PackedInt4Weight(torch.zeros(128 * 96, dtype=torch.uint8, device=DEV),
+    pw = ops.PackedInt4Weight(torch.zeros(2 * 8448, dtype=torch.uint8, device=DEV),
                               torch.ones(128, dtype=torch.float16, device=DEV), 128, 192)
     with pytest.raises(ValueError):
         ops.gemm_w4a4_int4(qx, torch.ones(4, device=DEV), pw)  # K % 128 != 0

@@ -100,8 +100,8 @@ def test_reference_packing_round_trip(golden):
     deq = codes.float().reshape(32, 2, 128) * scale.reshape(32, 2, 1)
     assert torch.equal(deq.reshape(32, 256), torch.from_numpy(golden["refpack_dequant"]))
     # streaming layout: pure permutation of the same nibbles (tile 0, group 0, row 0, chunk 0)
-    sp = O.stream_pack_int4(codes)
-    assert sp.numel() == 128 * 256 // 2  # 32 rows padded to one 128-row tile
+    sp = O.stream_pack_int4(codes, torch.ones(32, 2, dtype=torch.float16))
+    assert sp.numel() == 2 * 8448  # 32 rows padded to one 128-row tile, two k groups
     first = sp[:16].to(torch.int16)
     lo = first & 0xF
     lo = torch.where(lo > 7, lo - 16, lo)
@@ -109,8 +109,11 @@ def test_reference_packing_round_trip(golden):
     hi = torch.where(hi > 7, hi - 16, hi)
     assert torch.equal(lo, codes[0, 0:16].to(torch.int16))
     assert torch.equal(hi, codes[0, 16:32].to(torch.int16))
-    # second k group of row 0 starts one 8 KB tile later
-    nxt = sp[8192:8192 + 16].to(torch.int16) & 0xF
+    # the tile ends with its 128 fp16 scales (1.0 for real rows, 0 for padding rows)
+    tail = sp[8192:8448].view(torch.float16)
+    assert torch.equal(tail[:32], torch.ones(32, dtype=torch.float16)) and tail[32:].abs().max() == 0
+    # second k group of row 0 starts one tile later
+    nxt = sp[8448:8448 + 16].to(torch.int16) & 0xF
     nxt = torch.where(nxt > 7, nxt - 16, nxt)
     assert torch.equal(nxt, codes[0, 128:144].to(torch.int16))
 
