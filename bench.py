@@ -56,7 +56,9 @@ def _peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """nvidia-smi clock / throttle-reason samples taken while the timed regions run.  A reader
+    thread collects lines; start() returns once the first sample has arrived so that the (short)
+    timed regions are covered."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -65,8 +67,12 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
+        self.lines = []
+        self.thread = None
 
     def start(self):
+        import threading
+
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -74,19 +80,31 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return
+
+        def reader():
+            for line in self.proc.stdout:
+                self.lines.append(line)
+
+        self.thread = threading.Thread(target=reader, daemon=True)
+        self.thread.start()
+        t0 = time.time()
+        while not self.lines and time.time() - t0 < 5.0:
+            time.sleep(0.01)
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
         sm, smax, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in out.strip().splitlines():
+        for line in list(self.lines):
             p = [v.strip() for v in line.split(",")]
             if len(p) < 9:
                 continue
@@ -364,6 +382,56 @@ def run_case(args):
                       "weight_copies": n_copies}), flush=True)
 
 
+PREFILL_SHAPES = (
+    # (label, M, K, N)
+    ("config0 linear", 2048, 4096, 4096),
+    ("qkv", 4096, 4096, 6144),
+    ("gate_up", 4096, 4096, 28672),
+    ("down", 4096, 14336, 4096),
+    ("config2 gate_up", 8192, 4096, 28672),
+    ("config2 down", 8192, 14336, 4096),
+)
+
+
+def run_prefill_suite(args):
+    """Prefill-shaped linears (tensor-core bound): TOPS = 2*M*N*K / time of the GEMM launch and of
+    quantiser + GEMM, against the dense int8 peak (nominal 4500 TOPS; 2x the measured bf16 peak)."""
+    from dualquant_b200 import _lib, ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, kind = _peaks()
+    int8_measured = 2.0 * peaks["bf16_tflops"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    rows = []
+    for label, M, K, N in PREFILL_SHAPES:
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        codes_w, sw = ops.quant_w_int4(w)
+        pw = ops.pack_w_int4(codes_w, sw)
+        del w, codes_w, sw
+        r, c = synthetic.make_scales(N, K, 0)
+        r, a = r.to(dev), (1.0 / c).to(dev)
+        x = (torch.randn(M, K, generator=g, device=dev)).to(torch.bfloat16)
+        qx, sx = ops.quant_act_int4(x, a, None, True)
+        y = torch.empty(M, N, dtype=torch.float32, device=dev)
+        scratch = torch.empty(ops.linear_scratch_bytes(M, N, K), dtype=torch.uint8, device=dev)
+        g_gemm = _capture(lambda: ops.gemm_w4a4_int4(qx, sx, pw, r, out=y), dev)
+        g_full = _capture(lambda: ops.linear_w4a4_int4(x, a, None, pw, r, scale_fp16=True,
+                                                       scratch=scratch, out=y), dev)
+        ms_gemm = _time_loop(g_gemm.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        ms_full = _time_loop(g_full.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        ops_ = 2.0 * M * N * K
+        rows.append({"shape": label, "M": M, "K": K, "N": N,
+                     "gemm_us": round(ms_gemm * 1e3, 1), "gemm_TOPS": round(ops_ / ms_gemm / 1e9, 1),
+                     "linear_us": round(ms_full * 1e3, 1), "linear_TOPS": round(ops_ / ms_full / 1e9, 1),
+                     "frac_int8_nominal": round(ops_ / ms_gemm / 1e9 / 4500.0, 4),
+                     "frac_2x_measured_bf16": round(ops_ / ms_gemm / 1e9 / int8_measured, 4)})
+        del pw, x, qx, sx, y, scratch
+    _lib.device_status(0)
+    print(json.dumps({"suite": "prefill", "unit": "TOPS (2*M*N*K/s)", "peaks": {"int8_nominal": 4500.0,
+                      "int8_2x_bf16_" + kind: int8_measured}, "steps": args.steps, "rows": rows}), flush=True)
+
+
 def per_shape_detail(wl, dev, args):
     """GEMM-only GB/s of each (linear, M), timed as a graph that cycles through the six weight
     copies of that linear (so each launch reads weights that left L2)."""
@@ -481,9 +549,12 @@ def main():
     ap.add_argument("--detail", action="store_true", help="add per-(linear, M) GEMM GB/s")
     ap.add_argument("--case", default=None, help="NAME:M[:TN:SPLIT] - run one (linear, M) GEMM alone")
     ap.add_argument("--iters", type=int, default=6)
+    ap.add_argument("--suite", default=None, choices=["prefill"], help="extra measurement suites")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
-    if args.case:
+    if args.suite == "prefill":
+        run_prefill_suite(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)
