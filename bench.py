@@ -32,7 +32,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from dualquant_b200 import synthetic  # noqa: E402
+from dualquant_b200 import sharding, synthetic  # noqa: E402
 
 METRIC = "w4a4_int4_decode_gemm_sweep_GBps"
 UNIT = "GB/s"
@@ -43,7 +43,9 @@ def _step_bytes(n_split: int = 1) -> int:
     total = 0
     for _, K, N in synthetic.LLAMA31_8B_LINEARS:
         for M in synthetic.DECODE_M:
-            total += synthetic.int4_gemm_bytes(M, N // n_split, K) * n_split
+            for rank in range(n_split):
+                lo, hi = sharding.shard_rows(N, n_split, rank)
+                total += synthetic.int4_gemm_bytes(M, hi - lo, K)
     return total
 
 
@@ -135,11 +137,11 @@ class Workload:
         self.linears = []  # per linear: dict(name,K,N_local,a,r,weights[copy])
         n_copies = len(synthetic.DECODE_M)
         for name, K, N in synthetic.LLAMA31_8B_LINEARS:
-            assert N % world == 0
-            nl = N // world
+            n_lo, n_hi = sharding.shard_rows(N, world, rank)
+            nl = n_hi - n_lo
             r, c = synthetic.make_scales(N, K, seed)
             a = (1.0 / c).to(dev)
-            r_local = r[rank * nl:(rank + 1) * nl].contiguous().to(dev)
+            r_local = r[n_lo:n_hi].contiguous().to(dev)
             copies = []
             for _ in range(n_copies):
                 w = (torch.randn(nl, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
