@@ -16,6 +16,7 @@ DQ_OK = 0
 DQ_ERR_TIMEOUT = 9
 DTYPE_F32, DTYPE_BF16 = 0, 1
 HAD_NONE, HAD_FULL, HAD_PARTIAL = 0, 1, 2
+FP4_MXFP4, FP4_NVFP4 = 0, 1
 
 _ERR_NAMES = {
     1: "DQ_ERR_SHAPE", 2: "DQ_ERR_ALIGN", 3: "DQ_ERR_NULL", 4: "DQ_ERR_ARCH", 5: "DQ_ERR_CUDA",
@@ -53,6 +54,9 @@ SIGNATURES = {
     "dq_quant_act_int4": (_i, [_vp, _i64, _vp, _hp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_fakequant_act_int4": (_i, [_vp, _i, _i64, _vp, _hp, _i, _i, _vp, _i, _vp]),
     "dq_hadamard_f32": (_i, [_vp, _vp, _i, _i, _hp, _vp]),
+    "dq_quant_fp4": (_i, [_vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "dq_fakequant_fp4": (_i, [_vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "dq_nvfp4_tensor_scale": (_i, [_vp, _i, _i64, _vp, _vp]),
     "dq_gemm_w4a4_int4_workspace_bytes": (_sz, [_i, _i, _i]),
     "dq_gemm_w4a4_int4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),

@@ -17,6 +17,7 @@ SOURCES = [
     "dq_runtime.cu",
     "weights_int4.cu",
     "act_quant_int4.cu",
+    "quant_fp4.cu",
     "gemm_w4a4_int4.cu",
     "gemv_w4a4_int4.cu",
     "linear_w4a4.cu",

@@ -57,7 +57,52 @@ def make_rtn_int4(block_size: int = 128, mse: bool = False) -> FormatSpec:
     )
 
 
-_FACTORIES = {"rtn_int4": make_rtn_int4}
+def _fp4_cast(W: torch.Tensor, fmt: int, block: int) -> torch.Tensor:
+    if not W.is_cuda:
+        raise RuntimeError("dualquant_b200 formats cast CUDA tensors only")
+    from . import _lib
+
+    orig_shape, orig_dtype = W.shape, W.dtype
+    x = W.reshape(-1, orig_shape[-1])
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        x = x.to(torch.float32)
+    ts = ops.nvfp4_tensor_scale(x) if fmt == _lib.FP4_NVFP4 else None
+    return ops.fakequant_fp4(x, fmt, None, ts).reshape(orig_shape).to(orig_dtype)
+
+
+def _float_to_fp4(W: torch.Tensor) -> torch.Tensor:
+    """Element-only E2M1 rounding (legacy_vendor/torch_quant.py:326-356): the MXFP4 cast with the
+    block exponent forced to 0 cannot be expressed through the block quantiser, so this is the
+    same threshold table written with torch ops (calibration-time helper, not on the hot path)."""
+    ax = W.abs()
+    out = torch.zeros_like(ax)
+    for thr, val, strict in ((0.25, 0.5, True), (0.75, 1.0, False), (1.25, 1.5, True), (1.75, 2.0, False),
+                             (2.5, 3.0, True), (3.5, 4.0, False), (5.0, 6.0, True)):
+        out = torch.where(ax > thr if strict else ax >= thr, torch.full_like(ax, val), out)
+    return torch.where(W < 0, -out, out)
+
+
+def make_mxfp4(block_size: int = 32) -> FormatSpec:
+    """formats/mx.py:23-31.  Only the OCP block size 32 has a kernel."""
+    from . import _lib
+
+    if block_size != 32:
+        raise NotImplementedError("mxfp4 is built for block_size 32 (the OCP MX block)")
+    return FormatSpec(name="mxfp4", block_size=32, max_val=6.0,
+                      cast=lambda W: _fp4_cast(W, _lib.FP4_MXFP4, 32),
+                      cast_element_only=_float_to_fp4)
+
+
+def make_nvfp4() -> FormatSpec:
+    """formats/nvfp4.py:11-19: block 16, E4M3 block scale, per-tensor fp32 scale."""
+    from . import _lib
+
+    return FormatSpec(name="nvfp4", block_size=16, max_val=6.0,
+                      cast=lambda W: _fp4_cast(W, _lib.FP4_NVFP4, 16),
+                      cast_element_only=_float_to_fp4)
+
+
+_FACTORIES = {"rtn_int4": make_rtn_int4, "mxfp4": make_mxfp4, "nvfp4": make_nvfp4}
 
 
 def register_format(name: str, factory) -> None:

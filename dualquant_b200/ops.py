@@ -200,3 +200,55 @@ def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[H
                                        _ptr(out), ydt, int(scale_fp16), _ptr(scratch), scratch.numel(),
                                        _stream(x.device)), "dq_linear_w4a4_int4")
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# block-scaled FP4
+# ---------------------------------------------------------------------------------------------
+def _fp4_block(fmt: int) -> int:
+    return 32 if fmt == _lib.FP4_MXFP4 else 16
+
+
+def quant_fp4(x: torch.Tensor, fmt: int, a: Optional[torch.Tensor] = None,
+              tensor_scale: Optional[torch.Tensor] = None):
+    """[M,K] bf16/fp32 -> (codes uint8 [M,K/2], sf uint8 [M,K/block], row_scale fp32 [M] or None)."""
+    lib = _prep(x)
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("quant_fp4 expects bf16 or fp32")
+    x = x.contiguous()
+    M, K = x.shape
+    codes = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(M, K // _fp4_block(fmt), dtype=torch.uint8, device=x.device)
+    row_scale = None
+    if fmt == _lib.FP4_NVFP4 and tensor_scale is None:
+        row_scale = torch.empty(M, dtype=torch.float32, device=x.device)
+    _lib.check(lib.dq_quant_fp4(_ptr(x), int(x.dtype == torch.float32), K, _ptr(a), M, K, fmt,
+                                _ptr(tensor_scale), _ptr(codes), _ptr(sf), _ptr(row_scale),
+                                _stream(x.device)), "dq_quant_fp4")
+    return codes, sf, row_scale
+
+
+def fakequant_fp4(x: torch.Tensor, fmt: int, a: Optional[torch.Tensor] = None,
+                  tensor_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _prep(x)
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("fakequant_fp4 expects bf16 or fp32")
+    x = x.contiguous()
+    M, K = x.shape
+    out = torch.empty(M, K, dtype=torch.float32, device=x.device)
+    _lib.check(lib.dq_fakequant_fp4(_ptr(x), int(x.dtype == torch.float32), K, _ptr(a), M, K, fmt,
+                                    _ptr(tensor_scale), _ptr(out), _stream(x.device)),
+               "dq_fakequant_fp4")
+    return out
+
+
+def nvfp4_tensor_scale(x: torch.Tensor) -> torch.Tensor:
+    """absmax(x) / (6 * 448) as a one-element device tensor (1 for an all-zero tensor)."""
+    lib = _prep(x)
+    x = x.contiguous()
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        x = x.float()
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    _lib.check(lib.dq_nvfp4_tensor_scale(_ptr(x), int(x.dtype == torch.float32), x.numel(), _ptr(scale),
+                                         _stream(x.device)), "dq_nvfp4_tensor_scale")
+    return scale

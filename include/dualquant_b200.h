@@ -137,6 +137,32 @@ DQ_API int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, const
 DQ_API int dq_hadamard_f32(const float* x, float* out, int M, int K, const dq_hadamard_desc* had,
                     void* stream);
 
+/* ---- block-scaled FP4 (MXFP4 / NVFP4) quantisers ------------------------------------------ */
+
+/*
+ * Block-scaled FP4 quantiser along K - the work the reference hands to the external `blockfmt`
+ * package (formats/mx.py:23-31 "MXFP4[E2M1]{32}", formats/nvfp4.py:11-19 "NVFP4[E2M1]{16}"),
+ * element rounding as legacy_vendor/torch_quant.py:326-356, MX exponent rule as :359-375,
+ * E4M3 scale rounding as scale_formats.py:39-45.
+ *   x: bf16 or fp32 [M,K] (x_is_f32), optional column scale a fp32 [K]
+ *   fmt: DQ_FP4_MXFP4 (block 32, sf = E8M0 byte) or DQ_FP4_NVFP4 (block 16, sf = E4M3 byte)
+ *   codes: uint8 [M, K/2], element 2j in the low nibble, 2j+1 in the high nibble
+ *   sf:    uint8 [M, K/block]
+ *   NVFP4 second-level scale: tensor_scale (device pointer to one fp32) when given, else one
+ *   scale per row = absmax_row/(6*448) which is written to row_scale[M] (may be null for MXFP4).
+ */
+DQ_API int dq_quant_fp4(const void* x, int x_is_f32, int64_t ldx, const float* a, int M, int K,
+                        int fmt, const float* tensor_scale, uint8_t* codes, uint8_t* sf,
+                        float* row_scale, void* stream);
+
+/* Same arithmetic, de-quantised fp32 [M,K] out: what FormatSpec.cast returns for mxfp4 / nvfp4. */
+DQ_API int dq_fakequant_fp4(const void* x, int x_is_f32, int64_t ldx, const float* a, int M, int K,
+                            int fmt, const float* tensor_scale, float* out, void* stream);
+
+/* Per-tensor NVFP4 second-level scale absmax(x)/(6*448) (1 for a zero tensor) into *scale. */
+DQ_API int dq_nvfp4_tensor_scale(const void* x, int x_is_f32, int64_t numel, float* scale,
+                                 void* stream);
+
 /* ---- int4 dual-scale GEMM ------------------------------------------------------------------ */
 
 /* Scratch bytes dq_gemm_w4a4_int4 needs for (M,N,K); may be 0. */

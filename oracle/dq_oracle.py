@@ -302,3 +302,58 @@ def fp4_code(v: torch.Tensor) -> torch.Tensor:
     idx = torch.clamp(idx, max=7)
     neg = (v < 0) | ((v == 0) & (torch.signbit(v)))
     return (idx | (neg.to(torch.int64) << 3)).to(torch.uint8)
+
+
+# FP4 block formats ------------------------------------------------------------------------------
+# MXFP4: blocks of 32 along the last axis, shared power-of-two scale (E8M0 byte = exponent + 127),
+#        exponent = floor(log2(amax)) - 2 (2 = exponent of the largest E2M1 value 6 = 1.5 * 2^2),
+#        as convert_to_mxfp (legacy_vendor/torch_quant.py:359-375); an all-zero block gets 2^-127.
+# NVFP4: blocks of 16, E4M3 block scale on top of a second-level fp32 scale
+#        ts = amax / (6 * 448) taken per token for activations or given per tensor for weights;
+#        block scale = e4m3(amax_block / 6 / ts) (round to nearest, scale_formats.py:39-45),
+#        element = fp4(x / (ts * block scale)).
+def _floor_log2(amax: torch.Tensor) -> torch.Tensor:
+    bits = amax.contiguous().view(torch.int32)
+    return ((bits >> 23) & 0xFF) - 127  # denormals report -127
+
+
+def quant_mxfp4(x32: torch.Tensor, block: int = 32):
+    """Returns (element values on the FP4 grid [.., K], E8M0 bytes [.., K/block], de-quantised)."""
+    shape = x32.shape
+    xb = x32.reshape(-1, shape[-1] // block, block)
+    amax = xb.abs().amax(dim=-1)
+    e = torch.where(amax == 0, torch.full_like(amax, -127, dtype=torch.int32), _floor_log2(amax) - 2)
+    e = e.clamp(-127, 127)
+    q = float_to_fp4(torch.ldexp(xb, (-e).unsqueeze(-1)))
+    deq = torch.ldexp(q, e.unsqueeze(-1))
+    return q.reshape(shape), (e + 127).to(torch.uint8).reshape(shape[:-1] + (-1,)), deq.reshape(shape)
+
+
+def quant_nvfp4(x32: torch.Tensor, tensor_scale=None, block: int = 16):
+    """Returns (FP4 element values, E4M3 block scales as fp32 [.., K/16], second-level scale
+    [rows] fp32, de-quantised).  tensor_scale None -> one second-level scale per row."""
+    shape = x32.shape
+    x2 = x32.reshape(-1, shape[-1])
+    if tensor_scale is None:
+        amax_row = x2.abs().amax(dim=1, keepdim=True)
+        ts = amax_row / 2688.0
+        ts[amax_row == 0] = 1.0
+    else:
+        ts = torch.full((x2.shape[0], 1), float(tensor_scale), dtype=torch.float32)
+    xb = x2.reshape(x2.shape[0], -1, block)
+    amax = xb.abs().amax(dim=-1)
+    bs = (amax / 6.0 / ts).clamp(max=448.0).to(torch.float8_e4m3fn).to(torch.float32)
+    denom = (ts * bs).unsqueeze(-1)
+    q = torch.where(denom == 0, torch.zeros_like(xb), float_to_fp4(xb / torch.where(denom == 0, torch.ones_like(denom), denom)))
+    deq = q * bs.unsqueeze(-1) * ts.unsqueeze(-1)
+    return q.reshape(shape), bs.reshape(shape[:-1] + (-1,)), ts.reshape(-1), deq.reshape(shape)
+
+
+def pack_fp4(q: torch.Tensor) -> torch.Tensor:
+    """Two E2M1 codes per byte, element 2j in the low nibble, 2j+1 in the high nibble."""
+    c = fp4_code(q).reshape(q.shape[:-1] + (q.shape[-1] // 2, 2))
+    return (c[..., 0] | (c[..., 1] << 4)).to(torch.uint8)
+
+
+def e4m3_byte(v: torch.Tensor) -> torch.Tensor:
+    return v.to(torch.float8_e4m3fn).view(torch.uint8)

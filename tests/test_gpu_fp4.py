@@ -1,0 +1,91 @@
+"""Block-scaled FP4 quantisers (MXFP4 / NVFP4) through the C ABI against the oracle: packed
+E2M1 codes, scale bytes and second-level scales bit-exact, de-quantised values equal."""
+import pytest
+import torch
+
+from dualquant_b200 import _lib, formats, ops, synthetic
+from oracle import dq_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _x(M, K, seed):
+    x = synthetic.make_x(M, K, seed)
+    if M > 2:
+        x[1] = 0  # all-zero row
+        x[2, :64] = 0  # all-zero blocks
+    return x
+
+
+@pytest.mark.parametrize("M,K", [(1, 32), (3, 128), (5, 3584), (2, 18944), (4, 4096)])
+@pytest.mark.parametrize("use_a", [False, True])
+def test_mxfp4_bit_exact(M, K, use_a):
+    x = _x(M, K, 7)
+    a = None
+    x32 = x.float()
+    if use_a:
+        _, c = synthetic.make_scales(8, K, 7)
+        a = 1.0 / c
+        x32 = x32 * a
+    q, e8, deq = O.quant_mxfp4(x32)
+    codes, sf, rs = ops.quant_fp4(x.to(DEV), _lib.FP4_MXFP4, None if a is None else a.to(DEV))
+    assert rs is None
+    assert torch.equal(sf.cpu(), e8)
+    assert torch.equal(codes.cpu(), O.pack_fp4(q))
+    fq = ops.fakequant_fp4(x.to(DEV), _lib.FP4_MXFP4, None if a is None else a.to(DEV))
+    assert torch.equal(fq.cpu(), deq)
+    _lib.device_status(0)
+
+
+@pytest.mark.parametrize("M,K", [(1, 16), (3, 128), (5, 3584), (2, 18944), (4, 4096)])
+@pytest.mark.parametrize("per_tensor", [False, True])
+def test_nvfp4_bit_exact(M, K, per_tensor):
+    x = _x(M, K, 9)
+    x32 = x.float()
+    ts_dev = None
+    ts_val = None
+    if per_tensor:
+        ts_dev = ops.nvfp4_tensor_scale(x.to(DEV))
+        ts_val = float(ts_dev.item())
+        ref_ts = x32.abs().max() / 2688.0
+        assert ts_val == float(ref_ts)
+    q, bs, ts, deq = O.quant_nvfp4(x32, ts_val)
+    codes, sf, rs = ops.quant_fp4(x.to(DEV), _lib.FP4_NVFP4, None, ts_dev)
+    assert torch.equal(sf.cpu(), O.e4m3_byte(bs))
+    assert torch.equal(codes.cpu(), O.pack_fp4(q))
+    if not per_tensor:
+        assert torch.equal(rs.cpu(), ts)
+    fq = ops.fakequant_fp4(x.to(DEV), _lib.FP4_NVFP4, None, ts_dev)
+    assert torch.equal(fq.cpu(), deq)
+    _lib.device_status(0)
+
+
+def test_element_rounding_matches_reference_table(golden):
+    # blocks whose exponent is 0 (absmax in [4, 8)): the MXFP4 element is float_to_fp4(x) itself
+    grid = torch.from_numpy(golden["fp4_in"])
+    want = torch.from_numpy(golden["fp4_out"])
+    keep = grid.abs() <= 6.0
+    vals, ref = grid[keep], want[keep]
+    n = (vals.numel() // 31) * 31
+    rows = vals[:n].reshape(-1, 31)
+    x = torch.cat([rows, torch.full((rows.shape[0], 1), 6.0)], dim=1)  # pin the block exponent to 0
+    fq = ops.fakequant_fp4(x.to(DEV), _lib.FP4_MXFP4).cpu()
+    assert torch.equal(fq[:, :31].reshape(-1), ref[:n])
+    f = formats.make_format("mxfp4")
+    assert torch.equal(f.cast_element_only(grid), want)
+
+
+def test_format_specs():
+    f = formats.make_format("nvfp4")
+    assert (f.name, f.block_size, f.max_val) == ("nvfp4", 16, 6.0)
+    with pytest.raises(ValueError):
+        formats.make_format("nvfp4", block_size=32)
+    w = synthetic.make_w(64, 256, 1).to(DEV)
+    got = f.cast(w)
+    ts = float((w.float().abs().max() / 2688.0).item())
+    _, _, _, deq = O.quant_nvfp4(w.float().cpu(), ts)
+    assert got.dtype == w.dtype and torch.equal(got.float().cpu(), deq.to(torch.bfloat16).float())
+    fm = formats.make_format("mxfp4", block_size=32)
+    _, _, deq2 = O.quant_mxfp4(w.float().cpu())
+    assert torch.equal(fm.cast(w.float()).cpu(), deq2)
