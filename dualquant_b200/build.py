@@ -20,6 +20,7 @@ SOURCES = [
     "quant_fp4.cu",
     "gemm_w4a4_int4.cu",
     "gemv_w4a4_int4.cu",
+    "gemm_fp4.cu",
     "linear_w4a4.cu",
 ]
 

@@ -10,6 +10,7 @@
 //   * had_kernel : row staged in shared memory as fp32, butterflies in place, then the same tail.
 // Both are HBM-bound streaming kernels (2 bytes in, 1 byte out per element).
 #include "dq_common.h"
+#include "dq_ptx.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -89,6 +90,9 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
                       int8_t* __restrict__ codes, float* __restrict__ sx, float* __restrict__ out,
                       int mode, int scale_fp16) {
   __shared__ float red[THREADS / 32];
+  // the GEMM that consumes the codes may be launched programmatically: let it start streaming
+  // its weights now; it waits for this grid before it touches codes / sx
+  grid_dep_launch_dependents();
   const int row = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(row) * ldx;
   float v[VPT][8];
@@ -153,6 +157,7 @@ act_quant_had_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restr
   __shared__ float red[THREADS / 32];
   float* row = sm_row;
   float* hm = sm_row + K;  // [had_k, had_k] when had_k > 1
+  grid_dep_launch_dependents();
   const int r = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(r) * ldx;
 

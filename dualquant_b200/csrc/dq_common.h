@@ -59,6 +59,7 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // One-time kernel attribute set-up of each translation unit (called from dq_init).
 int init_gemm_int4_kernels();
 int init_gemv_int4_kernels();
+int init_gemm_fp4_kernels();
 int init_act_quant_kernels();
 
 // Decode-batch (register-path) variant of the int4 linear, defined in gemv_w4a4_int4.cu.

@@ -224,6 +224,20 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 // ---------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------------------
+// Lets the next kernel of the stream (if it was launched with the programmatic-serialization
+// attribute) start its prologue while this one is still running.
+__device__ __forceinline__ void grid_dep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Blocks until every kernel this one depends on has completed and its writes are visible.
+// A no-op for kernels launched without the attribute.
+__device__ __forceinline__ void grid_dep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------
 // thread-block clusters
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void cluster_sync_all() {

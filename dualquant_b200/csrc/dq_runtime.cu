@@ -98,6 +98,8 @@ extern "C" int dq_init(int device) {
   if (rc != DQ_OK) return rc;
   rc = init_gemv_int4_kernels();
   if (rc != DQ_OK) return rc;
+  rc = init_gemm_fp4_kernels();
+  if (rc != DQ_OK) return rc;
   rc = init_act_quant_kernels();
   if (rc != DQ_OK) return rc;
   DQ_CHECK_CUDA(cudaDeviceSynchronize());

@@ -1,0 +1,308 @@
+// Block-scaled FP4 W4A4 GEMM for sm_100a: tcgen05.mma kind::mxf4nvf4.block_scale.
+//
+//   Y[m,n] = r[n] * tw * tx[m] * sum_k ( qx[m,k] * sfx[m, k/B] ) * ( qw[n,k] * sfw[n, k/B] )
+//
+// MXFP4: B = 32, E8M0 scales, scale_vec::2X, tw = tx = 1.  NVFP4: B = 16, E4M3 scales,
+// scale_vec::4X, tw = per-tensor weight scale, tx[m] = per-token second-level scale.
+// The block scales are applied by the tensor core, so one fp32 accumulator in tensor memory
+// runs over the whole K loop and is drained once.
+//
+// Orientation as in the int4 kernel: 128 weight rows = UMMA M (TMEM lanes), 128 tokens = UMMA N
+// (TMEM columns).  A stage is 256 k: operand tiles of 128 rows x 128 bytes (packed E2M1, 128B
+// swizzle, TMA) and the scale factors of the stage in the 512-byte "32 x 16" atoms
+// tcgen05.cp.32x128b.warpx4 expects (rows r, r+32, r+64, r+96 share a 16-byte line; four scales
+// per row per atom), fetched with contiguous bulk copies and copied to tensor memory by the
+// UMMA-issuing thread ahead of the four K=64 UMMAs of the stage.
+//
+// 192 threads: warp 0 TMA producer, warp 1 TMEM allocation + UMMA issue, warps 2-5 epilogue.
+#include "dq_common.h"
+#include "dq_ptx.cuh"
+
+#include <cuda_bf16.h>
+
+namespace dq {
+
+constexpr int kFBN = 128;      // weight rows per CTA
+constexpr int kFTN = 128;      // tokens per CTA
+constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
+constexpr int kFStages = 4;
+constexpr int kFTileBytes = 128 * 128;  // one operand tile
+constexpr int kFThreads = 192;
+
+struct FCfg {
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kOffA + kFStages * kFTileBytes;
+  static constexpr int kOffSFA = kOffB + kFStages * kFTileBytes;  // up to 2 KB per stage
+  static constexpr int kOffSFB = kOffSFA + kFStages * 2048;
+  static constexpr int kOffBar = kOffSFB + kFStages * 2048;
+  static constexpr int kSmemBytes = kOffBar + (2 * kFStages + 1) * 8 + 16 + 1024;
+  static constexpr int kTmemCols = 256;    // 128 accumulator columns + scale factors
+  static constexpr int kSfColBase = 128;   // scale-factor columns start here: 32 per stage
+};
+
+enum { FSITE_TMA = 31, FSITE_MMA = 32, FSITE_EPI = 33 };
+
+// Shared-memory descriptor of one scale-factor atom for tcgen05.cp: 32 rows x 16 bytes, no
+// swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_atom_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;  // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;         // descriptor version
+  return d;
+}
+
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+// Instruction descriptor, kind::mxf4nvf4: E2M1 operands (format code 1), both K-major.
+//   [4,6) B scale id  [7,10) A format  [10,13) B format  [17,23) N >> 3  [23] scale format
+//   (0 = E4M3, 1 = E8M0)  [24,29) M >> 4  [29,31) A scale id  [31] K size (0 = 64)
+__device__ __forceinline__ uint32_t umma_idesc_fp4(int m, int n, int e8m0, uint32_t sf_id) {
+  return (sf_id << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(e8m0) << 23) | (static_cast<uint32_t>(m >> 4) << 24) | (sf_id << 29);
+}
+
+template <int NVFP4>
+__device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                         uint32_t accumulate) {
+  if constexpr (NVFP4) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::
+            "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::
+            "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+  }
+}
+
+template <int NVFP4>
+__global__ void __launch_bounds__(kFThreads, 1)
+gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx,
+                const float* __restrict__ r, const float* __restrict__ w_scale,
+                const float* __restrict__ x_scale, void* __restrict__ y, int y_bf16, int M, int N,
+                int K, int* status) {
+  using C = FCfg;
+  constexpr int kAtoms = NVFP4 ? 4 : 2;           // scale-factor atoms per operand per stage
+  constexpr uint32_t kSfBytes = kAtoms * 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint64_t* empty = full + kFStages;
+  uint64_t* acc_full = empty + kFStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * kFBN;
+  const int t0 = blockIdx.y * kFTN;
+  const int nst = K / kFKStage;
+
+  if (tid == 0) {
+    for (int i = 0; i < kFStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    const uint64_t pol = l2_policy_evict_last();
+    const uint8_t* sfw_tile = sfw + static_cast<size_t>(blockIdx.x) * nst * kSfBytes;
+    const uint8_t* sfx_tile = sfx + static_cast<size_t>(blockIdx.y) * nst * kSfBytes;
+    for (int i = 0; i < nst; ++i) {
+      const int s = i % kFStages;
+      if (!mbar_wait(&empty[s], ((i / kFStages) & 1) ^ 1, abort_flag, FSITE_TMA)) break;
+      if (lane == 0) {
+        mbar_expect_tx(&full[s], 2 * kFTileBytes + 2 * kSfBytes);
+        tma_load_2d(smem + C::kOffA + s * kFTileBytes, &tm_w, i * 128, n0, &full[s], pol);
+        tma_load_2d(smem + C::kOffB + s * kFTileBytes, &tm_x, i * 128, t0, &full[s], pol);
+        bulk_load_1d(smem + C::kOffSFA + s * 2048, sfw_tile + static_cast<size_t>(i) * kSfBytes,
+                     kSfBytes, &full[s], pol);
+        bulk_load_1d(smem + C::kOffSFB + s * 2048, sfx_tile + static_cast<size_t>(i) * kSfBytes,
+                     kSfBytes, &full[s], pol);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    for (int i = 0; i < nst; ++i) {
+      const int s = i % kFStages;
+      if (!mbar_wait(&full[s], (i / kFStages) & 1, abort_flag, FSITE_MMA)) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t sfa_t = tmem_base + C::kSfColBase + s * 32;
+        const uint32_t sfb_t = sfa_t + 16;
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a) {
+          tmem_cp_32x128b_warpx4(sfa_t + 4 * a, sf_atom_desc(smem_u32(smem + C::kOffSFA + s * 2048 + a * 512)));
+          tmem_cp_32x128b_warpx4(sfb_t + 4 * a, sf_atom_desc(smem_u32(smem + C::kOffSFB + s * 2048 + a * 512)));
+        }
+        const uint64_t da = umma_desc_k_sw128(smem_u32(smem + C::kOffA + s * kFTileBytes));
+        const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + s * kFTileBytes));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // four K=64 UMMAs: +32 bytes along K each
+          const int atom = NVFP4 ? j : (j >> 1);
+          const uint32_t sf_id = NVFP4 ? 0u : static_cast<uint32_t>((j & 1) * 2);
+          const uint32_t idesc = umma_idesc_fp4(kFBN, kFTN, NVFP4 ? 0 : 1, sf_id);
+          umma_fp4<NVFP4>(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa_t + 4 * atom,
+                          sfb_t + 4 * atom, (i > 0 || j > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+        if (i == nst - 1) umma_commit(acc_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;  // TMEM lane quarter of this warp
+    const int n = n0 + q * 32 + lane;
+    if (mbar_wait(acc_full, 0, abort_flag, FSITE_EPI)) {
+      tc_fence_after();
+      float rn = 0.f;
+      if (n < N) {
+        rn = (r != nullptr) ? r[n] : 1.f;
+        if (w_scale != nullptr) rn *= *w_scale;
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < kFTN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = t0 + c0 + j;
+            if (m < M) {
+              const float tx = (x_scale != nullptr) ? x_scale[m] : 1.f;
+              const float val = __uint_as_float(v[j]) * (rn * tx);
+              if (y_bf16)
+                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] = __float2bfloat16_rn(val);
+              else
+                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+  if (tid == 0 && *abort_flag != 0) atomicCAS(status, 0, *abort_flag);
+}
+
+// Scale factors from row-major [rows, nsf] bytes to the atom order the GEMM streams:
+// [row tile of 128][k stage][atom][ (r % 32) * 16 + (r / 32) * 4 + (k % 4) ], rows past `rows` zero.
+__global__ void fp4_sf_to_atoms_kernel(const uint8_t* __restrict__ sf, int rows, int nsf,
+                                       uint8_t* __restrict__ out, int64_t total) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int within = static_cast<int>(i & 511);
+  const int64_t atom = i >> 9;             // global atom index = tile * atoms_per_row_tile + a
+  const int atoms_per_tile = nsf / 4;
+  const int64_t tile = atom / atoms_per_tile;
+  const int a = static_cast<int>(atom % atoms_per_tile);
+  const int r = (within >> 4) + 32 * ((within >> 2) & 3);
+  const int k = a * 4 + (within & 3);
+  const int64_t row = tile * 128 + r;
+  out[i] = (row < rows) ? sf[row * nsf + k] : static_cast<uint8_t>(0);
+}
+
+int init_gemm_fp4_kernels() {
+  cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       FCfg::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             FCfg::kSmemBytes);
+  if (e != cudaSuccess)
+    return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemm_fp4) failed: %s", cudaGetErrorString(e));
+  return DQ_OK;
+}
+
+}  // namespace dq
+
+using namespace dq;
+
+extern "C" size_t dq_fp4_sf_atoms_bytes(int rows, int K, int fmt) {
+  const int blk = (fmt == DQ_FP4_MXFP4) ? 32 : 16;
+  if (rows <= 0 || K <= 0) return 0;
+  return (static_cast<size_t>(rows) + 127) / 128 * 128 * static_cast<size_t>(K / blk);
+}
+
+extern "C" int dq_fp4_sf_to_atoms(const uint8_t* sf, int rows, int K, int fmt, uint8_t* out,
+                                  void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  DQ_REQUIRE(fmt == DQ_FP4_MXFP4 || fmt == DQ_FP4_NVFP4, DQ_ERR_UNSUPPORTED, "unknown FP4 format %d", fmt);
+  DQ_REQUIRE(sf != nullptr && out != nullptr, DQ_ERR_NULL, "null pointer");
+  DQ_REQUIRE(rows >= 1 && K % kFKStage == 0, DQ_ERR_SHAPE, "K=%d must be a multiple of %d", K, kFKStage);
+  const int nsf = K / ((fmt == DQ_FP4_MXFP4) ? 32 : 16);
+  const int64_t total = static_cast<int64_t>(dq_fp4_sf_atoms_bytes(rows, K, fmt));
+  fp4_sf_to_atoms_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0,
+                           static_cast<cudaStream_t>(stream)>>>(sf, rows, nsf, out, total);
+  DQ_CHECK_CUDA(cudaGetLastError());
+  return DQ_OK;
+}
+
+extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atoms,
+                                const float* x_scale, const uint8_t* w_codes,
+                                const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
+                                int M, int N, int K, int fmt, void* y, int y_dtype, void* stream) {
+  DeviceState* st = current_state();
+  if (st == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  DQ_REQUIRE(fmt == DQ_FP4_MXFP4 || fmt == DQ_FP4_NVFP4, DQ_ERR_UNSUPPORTED, "unknown FP4 format %d", fmt);
+  DQ_REQUIRE(x_codes && x_sf_atoms && w_codes && w_sf_atoms && y, DQ_ERR_NULL, "null operand pointer");
+  DQ_REQUIRE(M >= 1 && N >= 1 && K >= kFKStage && K % kFKStage == 0, DQ_ERR_SHAPE,
+             "bad shape M=%d N=%d K=%d (K must be a multiple of %d)", M, N, K, kFKStage);
+  DQ_REQUIRE(aligned(x_codes, 16) && aligned(w_codes, 16) && aligned(x_sf_atoms, 16) &&
+                 aligned(w_sf_atoms, 16),
+             DQ_ERR_ALIGN, "operands must be 16-byte aligned");
+  DQ_REQUIRE(y_dtype == DQ_DTYPE_F32 || y_dtype == DQ_DTYPE_BF16, DQ_ERR_UNSUPPORTED, "unknown y_dtype %d", y_dtype);
+  CUtensorMap tm_w, tm_x;
+  int rc = make_tmap_2d_u8(&tm_w, w_codes, static_cast<uint64_t>(K) / 2, N, static_cast<uint64_t>(K) / 2,
+                           128, kFBN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != DQ_OK) return rc;
+  rc = make_tmap_2d_u8(&tm_x, x_codes, static_cast<uint64_t>(K) / 2, M, static_cast<uint64_t>(K) / 2, 128,
+                       kFTN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != DQ_OK) return rc;
+  const dim3 grid((N + kFBN - 1) / kFBN, (M + kFTN - 1) / kFTN, 1);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int bf = y_dtype == DQ_DTYPE_BF16 ? 1 : 0;
+  if (fmt == DQ_FP4_NVFP4)
+    gemm_fp4_kernel<1><<<grid, kFThreads, FCfg::kSmemBytes, s>>>(tm_w, tm_x, w_sf_atoms, x_sf_atoms, r,
+                                                                  w_scale, x_scale, y, bf, M, N, K,
+                                                                  st->status_dev);
+  else
+    gemm_fp4_kernel<0><<<grid, kFThreads, FCfg::kSmemBytes, s>>>(tm_w, tm_x, w_sf_atoms, x_sf_atoms, r,
+                                                                  w_scale, x_scale, y, bf, M, N, K,
+                                                                  st->status_dev);
+  DQ_CHECK_CUDA(cudaGetLastError());
+  return DQ_OK;
+}

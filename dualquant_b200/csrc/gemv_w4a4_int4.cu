@@ -94,6 +94,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     fence_mbar_init();
   }
   if (warp == kVComputeWarps && lane == 0) tma_prefetch_desc(&tm_x);
+  grid_dep_launch_dependents();
   __syncthreads();
 
   if (warp == kVComputeWarps) {
@@ -105,9 +106,31 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     const uint64_t pol_x = l2_policy_evict_last();
     const uint8_t* w_src =
         w_packed + (static_cast<size_t>(blockIdx.x) * total_groups + g_begin) * kTileBytes;
-    int s = 0;
-    uint32_t ph = 1;  // parity of the "stage is free" phase being waited for
-    for (int i = 0; i < nst; ++i) {
+    // The weights do not depend on the preceding kernel of the stream, the activation codes do
+    // (they come from the quantiser): fill the ring with weights first, then wait for the
+    // prerequisite grid, then fetch the activation tiles of those stages.
+    const int prefill = (nst < stages) ? nst : stages;
+    if (lane == 0) {
+      for (int i = 0; i < prefill; ++i) {
+        uint8_t* st = smem + i * C::kStage;
+        int cnt = ng - i * kVGS;
+        if (cnt > kVGS) cnt = kVGS;
+        const uint32_t wbytes = static_cast<uint32_t>(cnt) * kTileBytes;
+        mbar_expect_tx(&full[i], wbytes + C::kXBytes);
+        bulk_load_1d(st + C::kOffW, w_src + static_cast<size_t>(i) * kVGS * kTileBytes, wbytes,
+                     &full[i], pol_w);
+      }
+    }
+    grid_dep_wait();
+    if (lane == 0) {
+      for (int i = 0; i < prefill; ++i)
+        tma_load_2d(smem + i * C::kStage + C::kOffX, &tm_x, (g_begin + i * kVGS) * kGroup, 0,
+                    &full[i], pol_x);
+    }
+    __syncwarp();
+    int s = (prefill == stages) ? 0 : prefill;
+    uint32_t ph = (prefill == stages) ? 0u : 1u;  // parity of the "stage is free" phase waited for
+    for (int i = prefill; i < nst; ++i) {
       if (!mbar_wait(&empty[s], ph, abort_flag, VSITE_PRODUCER)) break;
       if (lane == 0) {
         uint8_t* st = smem + s * C::kStage;
@@ -361,13 +384,18 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
   cfg.blockDim = dim3(kVThreads, 1, 1);
   cfg.dynamicSmemBytes = C::smem_bytes(stages);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = split;
+  // programmatic dependent launch: the kernel may start (and stream weights) while the kernel
+  // before it in the stream is still running; it executes griddepcontrol.wait before it reads
+  // anything that kernel could have produced
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT>, w_packed, tm_x, r, sx, y,
                                      y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, gps, split,
                                      stages, st->status_dev);

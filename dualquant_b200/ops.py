@@ -252,3 +252,56 @@ def nvfp4_tensor_scale(x: torch.Tensor) -> torch.Tensor:
     _lib.check(lib.dq_nvfp4_tensor_scale(_ptr(x), int(x.dtype == torch.float32), x.numel(), _ptr(scale),
                                          _stream(x.device)), "dq_nvfp4_tensor_scale")
     return scale
+
+
+def fp4_sf_to_atoms(sf: torch.Tensor, K: int, fmt: int) -> torch.Tensor:
+    lib = _prep(sf)
+    rows = sf.shape[0]
+    out = torch.empty(int(lib.dq_fp4_sf_atoms_bytes(rows, K, fmt)), dtype=torch.uint8, device=sf.device)
+    _lib.check(lib.dq_fp4_sf_to_atoms(_ptr(sf.contiguous()), rows, K, fmt, _ptr(out), _stream(sf.device)),
+               "dq_fp4_sf_to_atoms")
+    return out
+
+
+@dataclass
+class PackedFp4Weight:
+    """FP4 weight artefact: packed E2M1 codes, scale factors in GEMM order, NVFP4 tensor scale."""
+
+    codes: torch.Tensor  # uint8 [N, K/2]
+    sf_atoms: torch.Tensor  # uint8, flat
+    tensor_scale: Optional[torch.Tensor]  # fp32 [1] (NVFP4) or None
+    N: int
+    K: int
+    fmt: int
+
+
+def pack_w_fp4(w: torch.Tensor, fmt: int) -> PackedFp4Weight:
+    """bf16/fp32 [N,K] -> FP4 artefact (blocks along K; NVFP4 uses one per-tensor second-level scale)."""
+    w = w.contiguous()
+    if w.dtype not in (torch.bfloat16, torch.float32):
+        w = w.float()
+    N, K = w.shape
+    ts = nvfp4_tensor_scale(w) if fmt == _lib.FP4_NVFP4 else None
+    codes, sf, _ = quant_fp4(w, fmt, None, ts)
+    return PackedFp4Weight(codes, fp4_sf_to_atoms(sf, K, fmt), ts, N, K, fmt)
+
+
+def gemm_w4a4_fp4(x_codes: torch.Tensor, x_sf_atoms: torch.Tensor, x_scale: Optional[torch.Tensor],
+                  pw: PackedFp4Weight, r: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _prep(x_codes)
+    M = x_codes.shape[0]
+    if out is None:
+        out = torch.empty(M, pw.N, dtype=out_dtype, device=x_codes.device)
+    ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    _lib.check(lib.dq_gemm_w4a4_fp4(_ptr(x_codes), _ptr(x_sf_atoms), _ptr(x_scale), _ptr(pw.codes),
+                                    _ptr(pw.sf_atoms), _ptr(pw.tensor_scale), _ptr(r), M, pw.N, pw.K,
+                                    pw.fmt, _ptr(out), ydt, _stream(x_codes.device)), "dq_gemm_w4a4_fp4")
+    return out
+
+
+def linear_w4a4_fp4(x: torch.Tensor, a: Optional[torch.Tensor], pw: PackedFp4Weight,
+                    r: Optional[torch.Tensor] = None, out_dtype=torch.float32) -> torch.Tensor:
+    """Quantise activations (per-token second-level scale for NVFP4) and run the FP4 GEMM."""
+    codes, sf, row_scale = quant_fp4(x, pw.fmt, a, None)
+    return gemm_w4a4_fp4(codes, fp4_sf_to_atoms(sf, pw.K, pw.fmt), row_scale, pw, r, out_dtype)

@@ -163,6 +163,29 @@ DQ_API int dq_fakequant_fp4(const void* x, int x_is_f32, int64_t ldx, const floa
 DQ_API int dq_nvfp4_tensor_scale(const void* x, int x_is_f32, int64_t numel, float* scale,
                                  void* stream);
 
+/* Bytes of the scale factors of a [rows, K] operand in GEMM ("atom") order: rows padded to 128. */
+DQ_API size_t dq_fp4_sf_atoms_bytes(int rows, int K, int fmt);
+
+/* Re-orders row-major scale bytes [rows, K/block] into the order dq_gemm_w4a4_fp4 streams:
+ * [row tile of 128][k][512-byte atom: (r % 32) * 16 + (r / 32) * 4 + (k % 4)], padding rows zero.
+ * K must be a multiple of 256. */
+DQ_API int dq_fp4_sf_to_atoms(const uint8_t* sf, int rows, int K, int fmt, uint8_t* out,
+                              void* stream);
+
+/*
+ * Block-scaled FP4 W4A4 GEMM (tcgen05 kind::mxf4nvf4): the matmul PermLinear performs on
+ * mxfp4 / nvfp4 fake-quantised operands (activations/perm_linear.py:136-141 with the casts of
+ * formats/mx.py:23-31 / formats/nvfp4.py:11-19), computed on the packed operands:
+ *   Y[m,n] = r[n] * w_scale * x_scale[m] * sum_k (qx[m,k]*sfx[m,k/B]) * (qw[n,k]*sfw[n,k/B])
+ * x_codes uint8 [M,K/2], w_codes uint8 [N,K/2] (dq_quant_fp4 output), *_sf_atoms from
+ * dq_fp4_sf_to_atoms, x_scale fp32 [M] / w_scale fp32 [1] (NVFP4 second-level scales; null = 1),
+ * r fp32 [N] or null, y [M,N] fp32 or bf16.  K % 256 == 0.
+ */
+DQ_API int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atoms, const float* x_scale,
+                            const uint8_t* w_codes, const uint8_t* w_sf_atoms, const float* w_scale,
+                            const float* r, int M, int N, int K, int fmt, void* y, int y_dtype,
+                            void* stream);
+
 /* ---- int4 dual-scale GEMM ------------------------------------------------------------------ */
 
 /* Scratch bytes dq_gemm_w4a4_int4 needs for (M,N,K); may be 0. */

@@ -89,3 +89,48 @@ def test_format_specs():
     fm = formats.make_format("mxfp4", block_size=32)
     _, _, deq2 = O.quant_mxfp4(w.float().cpu())
     assert torch.equal(fm.cast(w.float()).cpu(), deq2)
+
+
+# ------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------
+def _fp4_reference(x, a, w, r, fmt):
+    x32 = x.float() * a if a is not None else x.float()
+    if fmt == _lib.FP4_MXFP4:
+        _, _, xd = O.quant_mxfp4(x32)
+        _, _, wd = O.quant_mxfp4(w.float())
+    else:
+        _, _, _, xd = O.quant_nvfp4(x32)
+        ts = float((w.float().abs().max() / 2688.0).item())
+        _, _, _, wd = O.quant_nvfp4(w.float(), ts)
+    y = xd.double() @ wd.double().T
+    return y * r.double().reshape(1, -1) if r is not None else y
+
+
+def test_sf_atom_order():
+    rows, K = 200, 512
+    sf = torch.arange(rows * (K // 16), dtype=torch.int64).remainder(251).to(torch.uint8).reshape(rows, K // 16)
+    out = ops.fp4_sf_to_atoms(sf.to(DEV), K, _lib.FP4_NVFP4).cpu()
+    nsf = K // 16
+    assert out.numel() == 256 * nsf
+    for row, k in ((0, 0), (5, 3), (37, 4), (131, 17), (199, 31)):
+        tile, rr = divmod(row, 128)
+        atom = tile * (nsf // 4) + k // 4
+        idx = atom * 512 + (rr % 32) * 16 + (rr // 32) * 4 + k % 4
+        assert out[idx] == sf[row, k]
+    assert out[(1 * (nsf // 4)) * 512 + (8 % 32) * 16 + 3 * 4] == 0  # row 128+104 = 232 is padding
+
+
+@pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (16, 256, 512), (130, 200, 768), (1, 128, 3584)])
+def test_fp4_gemm_matches_dequant_matmul(fmt, M, N, K):
+    x = synthetic.make_x(M, K, M + 1)
+    w = synthetic.make_w(N, K, N + 2)
+    r, c = synthetic.make_scales(N, K, 3)
+    a = 1.0 / c
+    pw = ops.pack_w_fp4(w.to(DEV), fmt)
+    y = ops.linear_w4a4_fp4(x.to(DEV), a.to(DEV), pw, r.to(DEV))
+    _lib.device_status(0)
+    ref = _fp4_reference(x, a, w, r, fmt)
+    err = ((y.double().cpu() - ref).abs().max() / ref.abs().max()).item()
+    assert err < 1e-3, err
