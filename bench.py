@@ -434,6 +434,54 @@ def run_prefill_suite(args):
                       "int8_2x_bf16_" + kind: int8_measured}, "steps": args.steps, "rows": rows}), flush=True)
 
 
+def run_fp4_suite(args):
+    """Block-scaled FP4 linears on the Qwen2.5-7B-architecture shapes (BASELINE config 3):
+    MXFP4 and NVFP4, M = 16 (GB/s of algorithmic bytes) and M = 4096 (TFLOPS = 2*M*N*K/s)."""
+    from dualquant_b200 import _lib, ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, kind = _peaks()
+    fp4_measured = 4.0 * peaks["bf16_tflops"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    rows = []
+    for fmt_name, fmt in (("mxfp4", _lib.FP4_MXFP4), ("nvfp4", _lib.FP4_NVFP4)):
+        blk = 32 if fmt == _lib.FP4_MXFP4 else 16
+        for name, K, N in synthetic.QWEN25_7B_LINEARS:
+            w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            pw = ops.pack_w_fp4(w, fmt)
+            del w
+            r, c = synthetic.make_scales(N, K, 0)
+            r, a = r.to(dev), (1.0 / c).to(dev)
+            for M in (16, 4096):
+                x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+                codes, sf, rs = ops.quant_fp4(x, fmt, a, None)
+                sfa = ops.fp4_sf_to_atoms(sf, K, fmt)
+                y = torch.empty(M, N, dtype=torch.float32, device=dev)
+                g_gemm = _capture(lambda: ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r, out=y), dev)
+                g_full = _capture(lambda: ops.gemm_w4a4_fp4(*_fp4_prologue(ops, x, a, pw), pw, r, out=y), dev)
+                ms_gemm = _time_loop(g_gemm.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+                ms_full = _time_loop(g_full.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+                flops = 2.0 * M * N * K
+                nbytes = N * K // 2 + N * K // blk + 2 * N + 2 * K + 2 * M * K + 4 * M * N
+                rows.append({"fmt": fmt_name, "linear": name, "M": M, "K": K, "N": N,
+                             "gemm_us": round(ms_gemm * 1e3, 1), "linear_us": round(ms_full * 1e3, 1),
+                             "gemm_TFLOPS": round(flops / ms_gemm / 1e9, 1),
+                             "gemm_GBps": round(nbytes / ms_gemm / 1e6, 1),
+                             "frac_fp4_nominal": round(flops / ms_gemm / 1e9 / 9000.0, 4),
+                             "frac_4x_measured_bf16": round(flops / ms_gemm / 1e9 / fp4_measured, 4),
+                             "frac_hbm_measured": round(nbytes / ms_gemm / 1e6 / peaks["hbm_gbs"], 4)})
+            del pw
+    _lib.device_status(0)
+    print(json.dumps({"suite": "fp4", "peaks": {"fp4_nominal_TFLOPS": 9000.0, "fp4_4x_bf16_" + kind: fp4_measured,
+                      "hbm_GBps_" + kind: peaks["hbm_gbs"]}, "steps": args.steps, "rows": rows}), flush=True)
+
+
+def _fp4_prologue(ops, x, a, pw):
+    codes, sf, rs = ops.quant_fp4(x, pw.fmt, a, None)
+    return codes, ops.fp4_sf_to_atoms(sf, pw.K, pw.fmt), rs
+
+
 def per_shape_detail(wl, dev, args):
     """GEMM-only GB/s of each (linear, M), timed as a graph that cycles through the six weight
     copies of that linear (so each launch reads weights that left L2)."""
@@ -551,11 +599,13 @@ def main():
     ap.add_argument("--detail", action="store_true", help="add per-(linear, M) GEMM GB/s")
     ap.add_argument("--case", default=None, help="NAME:M[:TN:SPLIT] - run one (linear, M) GEMM alone")
     ap.add_argument("--iters", type=int, default=6)
-    ap.add_argument("--suite", default=None, choices=["prefill"], help="extra measurement suites")
+    ap.add_argument("--suite", default=None, choices=["prefill", "fp4"], help="extra measurement suites")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     if args.suite == "prefill":
         run_prefill_suite(args)
+    elif args.suite == "fp4":
+        run_fp4_suite(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

@@ -25,7 +25,7 @@ namespace dq {
 constexpr int kFBN = 128;      // weight rows per CTA
 constexpr int kFTN = 128;      // tokens per CTA
 constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
-constexpr int kFStages = 4;
+constexpr int kFStages = 3;  // 3 x 36 KB: two CTAs fit on one SM, one's epilogue overlaps the other's K loop
 constexpr int kFTileBytes = 128 * 128;  // one operand tile
 constexpr int kFThreads = 192;
 
@@ -84,7 +84,7 @@ __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint6
 }
 
 template <int NVFP4>
-__global__ void __launch_bounds__(kFThreads, 1)
+__global__ void __launch_bounds__(kFThreads, 2)
 gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                 const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx,
                 const float* __restrict__ r, const float* __restrict__ w_scale,
