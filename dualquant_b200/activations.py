@@ -42,6 +42,7 @@ class PermLinear(nn.Module):
 
         # packed weight artefact, built on first use (or by pack())
         self._packed: Optional[ops.PackedInt4Weight] = None
+        self._packed_fp4: Optional[ops.PackedFp4Weight] = None
         self._hadamard_cache = None
         self._scratch: Optional[torch.Tensor] = None
 
@@ -83,6 +84,14 @@ class PermLinear(nn.Module):
                                partial_hadamard_scale(K // int(self.had_dim)), None)
         self._hadamard_cache = (device, had)
         return had
+
+    def _fp4_fmt(self):
+        name = getattr(self.act_fmt, "name", None)
+        if not self.act_quant_enabled or name not in ("mxfp4", "nvfp4"):
+            return None
+        if self.online_full_had or self.online_partial_had or self.layer.in_features % 256 != 0:
+            return None
+        return _lib.FP4_MXFP4 if name == "mxfp4" else _lib.FP4_NVFP4
 
     def _int4_path(self) -> bool:
         return (self.act_quant_enabled and getattr(self.act_fmt, "name", None) == "rtn_int4"
@@ -133,6 +142,19 @@ class PermLinear(nn.Module):
             if self.layer.bias is not None:
                 out = out + self.layer.bias
             out = out.reshape(x.shape[:-1] + (pw.N,))
+        elif self._fp4_fmt() is not None:
+            # block-scaled FP4 activations against the weight packed in the same format
+            fmt = self._fp4_fmt()
+            if self._packed_fp4 is None or self._packed_fp4.fmt != fmt:
+                self._packed_fp4 = ops.pack_w_fp4(self.layer.weight.detach(), fmt)
+            x2 = x.reshape(-1, x.shape[-1])
+            if x2.dtype not in (torch.bfloat16, torch.float32):
+                x2 = x2.to(torch.bfloat16)
+            out_dtype = self.dtype if self.dtype in (torch.bfloat16, torch.float32) else torch.float32
+            out = ops.linear_w4a4_fp4(x2, self.act_scale, self._packed_fp4, None, out_dtype).to(self.dtype)
+            if self.layer.bias is not None:
+                out = out + self.layer.bias
+            out = out.reshape(x.shape[:-1] + (self._packed_fp4.N,))
         else:
             out = self.layer(self._quantise_act(x))
         if self.quantize_bmm_input:

@@ -98,3 +98,29 @@ def test_format_cast_matches_reference(golden):
     fw = formats.make_format("rtn_int4", block_size=128)
     w = torch.from_numpy(golden["wcast_in"]).to(DEV)
     assert torch.equal(fw.cast(w).cpu(), torch.from_numpy(golden["wcast_out"]))
+
+
+@pytest.mark.parametrize("name", ["mxfp4", "nvfp4"])
+def test_fp4_forward_close_to_fakequant_reference(name):
+    # PermLinear with an FP4 activation format runs the packed FP4 GEMM; compare with the
+    # fake-quant formulation (cast both operands, fp64 matmul) the reference computes
+    K, N, M = 512, 256, 9
+    w = synthetic.make_w(N, K, 8)
+    lin = nn.Linear(K, N, bias=False).to(torch.bfloat16)
+    lin.weight.data = w.clone()
+    fmt = formats.make_format(name)
+    pl = PermLinear(lin.to(DEV), fmt)
+    _, c = synthetic.make_scales(N, K, 8)
+    a = 1.0 / c
+    pl.set_act_scale(a)
+    pl = pl.to(DEV)
+    x = synthetic.make_x(M, K, 8)
+    y = pl(x.to(DEV)).double().cpu()
+    x32 = x.float() * a
+    if name == "mxfp4":
+        xd, wd = O.quant_mxfp4(x32)[2], O.quant_mxfp4(w.float())[2]
+    else:
+        xd = O.quant_nvfp4(x32)[3]
+        wd = O.quant_nvfp4(w.float(), float((w.float().abs().max() / 2688.0).item()))[3]
+    ref = xd.double() @ wd.double().T
+    assert ((y - ref).abs().max() / ref.abs().max()).item() < 8e-3  # bf16 output rounding
