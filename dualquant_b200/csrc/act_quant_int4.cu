@@ -93,6 +93,7 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
   // the GEMM that consumes the codes may be launched programmatically: let it start streaming
   // its weights now; it waits for this grid before it touches codes / sx
   grid_dep_launch_dependents();
+  grid_dep_wait();  // x may come from the kernel before this one; codes / sx may still be read by it
   const int row = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(row) * ldx;
   float v[VPT][8];
@@ -158,6 +159,7 @@ act_quant_had_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restr
   float* row = sm_row;
   float* hm = sm_row + K;  // [had_k, had_k] when had_k > 1
   grid_dep_launch_dependents();
+  grid_dep_wait();
   const int r = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(r) * ldx;
 
@@ -289,22 +291,22 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
     const size_t smem = static_cast<size_t>(K) * 4 + (hk > 1 ? static_cast<size_t>(hk) * hk * 4 : 0);
     DQ_REQUIRE(smem <= static_cast<size_t>(kHadMaxSmem), DQ_ERR_UNSUPPORTED,
                "row of K=%d does not fit in shared memory", K);
-    act_quant_had_kernel<kHadThreads, XT><<<M, kHadThreads, smem, stream>>>(
-        x, ldx, a, K, use_had ? had->kind : DQ_HAD_NONE, hk, use_had ? had->had_dim : 0,
-        use_had ? had->scale : 1.f, use_had ? had->had_mat : nullptr, codes, sx, out, mode,
-        scale_fp16);
+    DQ_CHECK_CUDA(launch_pdl(act_quant_had_kernel<kHadThreads, XT>, dim3(M), dim3(kHadThreads), smem,
+                             stream, x, ldx, a, K, use_had ? had->kind : DQ_HAD_NONE, hk,
+                             use_had ? had->had_dim : 0, use_had ? had->scale : 1.f,
+                             use_had ? had->had_mat : nullptr, codes, sx, out, mode, scale_fp16));
   } else {
     const int vecs = (K / 8 + 255) / 256;
     if (vecs <= 1)
-      act_quant_rows_kernel<256, 1, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 1, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
     else if (vecs <= 2)
-      act_quant_rows_kernel<256, 2, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 2, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
     else if (vecs <= 4)
-      act_quant_rows_kernel<256, 4, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 4, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
     else if (vecs <= 8)
-      act_quant_rows_kernel<256, 8, XT><<<M, 256, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 8, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
     else
-      act_quant_rows_kernel<512, 8, XT><<<M, 512, 0, stream>>>(x, ldx, a, K, codes, sx, out, mode, scale_fp16);
+      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<512, 8, XT>, dim3(M), dim3(512), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
   }
   DQ_CHECK_CUDA(cudaGetLastError());
   return DQ_OK;

@@ -56,6 +56,25 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
     if (!(cond)) return dq::set_error((code), __VA_ARGS__);  \
   } while (0)
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may begin while its
+// predecessor in the stream is still running and must execute griddepcontrol.wait before it
+// reads or writes anything the predecessor could touch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // One-time kernel attribute set-up of each translation unit (called from dq_init).
 int init_gemm_int4_kernels();
 int init_gemv_int4_kernels();

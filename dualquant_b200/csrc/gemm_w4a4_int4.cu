@@ -137,6 +137,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     tmem_relinquish();
   }
   if (warp == 12 && lane == 0) tma_prefetch_desc(&tm_x);
+  grid_dep_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -289,6 +290,22 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kTileBytes;
     const int nxc = (ng + C::XC - 1) / C::XC;
     int iw = 0, ix = 0;
+    // Weights do not depend on the preceding kernel of the stream; the activation codes do.
+    // Fill the weight ring first, then wait for the prerequisite grid (programmatic dependent
+    // launch), then start on the activation tiles.
+    {
+      const int pre = (ng < C::SP) ? ng : C::SP;
+      if (lane == 0) {
+        for (; iw < pre; ++iw) {
+          mbar_expect_tx(&full_p[iw], kWpBytes);
+          bulk_load_1d(smem + C::kOffP + iw * kWpBytes,
+                       w_tile + static_cast<size_t>(g_begin + iw) * kTileBytes, kWpBytes,
+                       &full_p[iw], pol_w);
+        }
+      }
+      iw = pre;
+      grid_dep_wait();
+    }
     long long t_last = clock64();
     uint32_t idle = 0;
     while (iw < ng || ix < nxc) {
@@ -478,13 +495,15 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg<TN>::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = split;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN, DUMP>, w_packed, tm_x, sw_t, r, sx,
                                      y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, acc_dump, M, N, K, gps,
