@@ -347,6 +347,30 @@ def run_case(args):
     from dualquant_b200 import _lib, ops
 
     parts = args.case.split(":")
+    if parts[0] == "quant":  # quant:M:K - the int4 activation quantiser alone
+        from dualquant_b200 import ops as _ops
+
+        M, K = int(parts[1]), int(parts[2])
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        n_bufs = max(2, int(400e6 // (M * K * 2)) + 1)
+        xs = [torch.randn(M, K, device=dev).to(torch.bfloat16) for _ in range(n_bufs)]
+        a = torch.rand(K, device=dev) + 0.5
+        for i in range(3):
+            _ops.quant_act_int4(xs[i % n_bufs], a, None, True)
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.iters):
+            _ops.quant_act_int4(xs[i % n_bufs], a, None, True)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.iters
+        b = M * K * 3 + 4 * K + 4 * M
+        print(json.dumps({"case": args.case, "us_per_launch": round(ms * 1e3, 2), "algorithmic_bytes": b,
+                          "GBps": round(b / ms / 1e6, 1)}), flush=True)
+        return
     name, M = parts[0], int(parts[1])
     tn = int(parts[2]) if len(parts) > 2 else 0
     split = int(parts[3]) if len(parts) > 3 else 0

@@ -41,8 +41,16 @@ __device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
   return s;
 }
 
-__device__ __forceinline__ float quant_code(float v, float s) {
-  float q = rintf(__fdiv_rn(v, s));
+// clamp(rint(v / s), -8, 7) with v / s correctly rounded, i.e. bit-identical to the IEEE
+// division, at a fraction of its instruction count: t = v * (1/s) is within 2 ulp of the true
+// quotient, so rint(t) can only differ from rint(v / s) when t lies within a few ulp of a
+// half-integer (|t| <= ~7 here, 4 ulp < 4e-6); only those rare elements take the exact division.
+__device__ __forceinline__ float quant_code(float v, float s, float inv_s) {
+  const float t = __fmul_rn(v, inv_s);
+  float q = rintf(t);
+  const float dist = fabsf(fabsf(__fsub_rn(t, q)) - 0.5f);
+  // the negated comparisons also send NaN / inf (1/s overflowed for a denormal scale) to the exact path
+  if (!(dist >= 1e-5f) || !(fabsf(t) <= 16.0f)) q = rintf(__fdiv_rn(v, s));
   return fminf(fmaxf(q, -8.0f), 7.0f);
 }
 
@@ -62,20 +70,50 @@ __device__ __forceinline__ void load8(const float* p, float* v) {
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+// Eight input elements as loaded (bf16: one 16-byte vector; fp32: two).
+template <typename XT>
+struct Raw8;
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 r;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { r = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void expand(float* v) const {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+};
+template <>
+struct Raw8<float> {
+  float4 lo, hi;
+  __device__ __forceinline__ void load(const float* p) {
+    lo = *reinterpret_cast<const float4*>(p);
+    hi = *reinterpret_cast<const float4*>(p + 4);
+  }
+  __device__ __forceinline__ void expand(float* v) const {
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+    v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+  }
+};
+
 __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t* codes_row,
                                       float* out_row, int idx) {
+  const float inv_s = __fdiv_rn(1.0f, s);
   if (mode == MODE_CODES) {
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      lo |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[e], s))) & 0xFFu) << (8 * e);
-      hi |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[4 + e], s))) & 0xFFu) << (8 * e);
+      lo |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[e], s, inv_s))) & 0xFFu) << (8 * e);
+      hi |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[4 + e], s, inv_s))) & 0xFFu) << (8 * e);
     }
     *reinterpret_cast<uint2*>(codes_row + idx) = make_uint2(lo, hi);
   } else {
     float o[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = (mode == MODE_FAKE) ? __fmul_rn(quant_code(v[e], s), s) : v[e];
+    for (int e = 0; e < 8; ++e) o[e] = (mode == MODE_FAKE) ? __fmul_rn(quant_code(v[e], s, inv_s), s) : v[e];
     *reinterpret_cast<float4*>(out_row + idx) = make_float4(o[0], o[1], o[2], o[3]);
     *reinterpret_cast<float4*>(out_row + idx + 4) = make_float4(o[4], o[5], o[6], o[7]);
   }
@@ -85,7 +123,7 @@ __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t*
 // register-resident rows (no Hadamard)
 // ---------------------------------------------------------------------------------------------
 template <int THREADS, int VPT, typename XT>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, (THREADS >= 512 && VPT <= 2) ? 2048 / THREADS : 1)
 act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
                       int8_t* __restrict__ codes, float* __restrict__ sx, float* __restrict__ out,
                       int mode, int scale_fp16) {
@@ -96,21 +134,26 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
   grid_dep_wait();  // x may come from the kernel before this one; codes / sx may still be read by it
   const int row = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(row) * ldx;
-  float v[VPT][8];
+  // The row is held in registers in its input width (bf16: 4 registers per 8 elements) and
+  // expanded twice - once for the absmax, once for the codes - with identical arithmetic, so
+  // that twice as many rows fit in the register file and more loads are in flight per SM.
+  Raw8<XT> raw[VPT];
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = (i * THREADS + threadIdx.x) * 8;
     if (idx < K) {
-      load8(xr + idx, v[i]);
+      raw[i].load(xr + idx);
+      float v[8];
+      raw[i].expand(v);
       if (a != nullptr) {
         float av[8];
         load8(a + idx, av);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[i][e] = __fmul_rn(v[i][e], av[e]);
+        for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[i][e]));
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
     }
   }
   amax = block_max(amax, red, THREADS / 32);
@@ -121,7 +164,17 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = (i * THREADS + threadIdx.x) * 8;
-    if (idx < K) emit8(v[i], s, mode, crow, orow, idx);
+    if (idx < K) {
+      float v[8];
+      raw[i].expand(v);
+      if (a != nullptr) {
+        float av[8];
+        load8(a + idx, av);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
+      }
+      emit8(v, s, mode, crow, orow, idx);
+    }
   }
 }
 
@@ -296,17 +349,20 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
                              use_had ? had->had_dim : 0, use_had ? had->scale : 1.f,
                              use_had ? had->had_mat : nullptr, codes, sx, out, mode, scale_fp16));
   } else {
-    const int vecs = (K / 8 + 255) / 256;
-    if (vecs <= 1)
-      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 1, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
-    else if (vecs <= 2)
-      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 2, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
-    else if (vecs <= 4)
-      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 4, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
-    else if (vecs <= 8)
-      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<256, 8, XT>, dim3(M), dim3(256), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
-    else
-      DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<512, 8, XT>, dim3(M), dim3(512), 0, stream, x, ldx, a, K, codes, sx, out, mode, scale_fp16));
+    // one CTA per row; as many threads as the row has 16-byte vectors (up to 1024) so that each
+    // thread holds few elements and many warps are resident to hide the load -> reduce -> store
+    // latency chain
+    const int vec = K / 8;
+#define DQ_ROWS_LAUNCH(T, V)                                                                      \
+  DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<T, V, XT>, dim3(M), dim3(T), 0, stream, x, ldx, a, K, \
+                           codes, sx, out, mode, scale_fp16))
+    if (vec <= 128) DQ_ROWS_LAUNCH(128, 1);
+    else if (vec <= 256) DQ_ROWS_LAUNCH(256, 1);
+    else if (vec <= 512) DQ_ROWS_LAUNCH(512, 1);
+    else if (vec <= 1024) DQ_ROWS_LAUNCH(1024, 1);
+    else if (vec <= 2048) DQ_ROWS_LAUNCH(1024, 2);
+    else DQ_ROWS_LAUNCH(1024, 4);
+#undef DQ_ROWS_LAUNCH
   }
   DQ_CHECK_CUDA(cudaGetLastError());
   return DQ_OK;

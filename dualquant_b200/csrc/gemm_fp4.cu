@@ -36,6 +36,7 @@ struct FCfg {
   static constexpr int kOffSFB = kOffSFA + kFStages * 2048;
   static constexpr int kOffBar = kOffSFB + kFStages * 2048;
   static constexpr int kSmemBytes = kOffBar + (2 * kFStages + 1) * 8 + 16 + 1024;
+  static_assert(kFTN * kFBN * 4 <= kOffSFA, "split-K exchange tile must fit in the operand stages");
   static constexpr int kTmemCols = 256;    // 128 accumulator columns + scale factors
   static constexpr int kSfColBase = 128;   // scale-factor columns start here: 32 per stage
 };
@@ -89,7 +90,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx,
                 const float* __restrict__ r, const float* __restrict__ w_scale,
                 const float* __restrict__ x_scale, void* __restrict__ y, int y_bf16, int M, int N,
-                int K, int* status) {
+                int K, int stages_per_split, int split_k, int* status) {
   using C = FCfg;
   constexpr int kAtoms = NVFP4 ? 4 : 2;           // scale-factor atoms per operand per stage
   constexpr uint32_t kSfBytes = kAtoms * 512;
@@ -105,7 +106,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kFBN;
   const int t0 = blockIdx.y * kFTN;
-  const int nst = K / kFKStage;
+  const int total_st = K / kFKStage;
+  const int st_begin = blockIdx.z * stages_per_split;
+  int st_end = st_begin + stages_per_split;
+  if (st_end > total_st) st_end = total_st;
+  const int nst = (st_end > st_begin) ? (st_end - st_begin) : 0;
 
   if (tid == 0) {
     for (int i = 0; i < kFStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
@@ -129,15 +134,15 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     const uint64_t pol = l2_policy_evict_last();
-    const uint8_t* sfw_tile = sfw + static_cast<size_t>(blockIdx.x) * nst * kSfBytes;
-    const uint8_t* sfx_tile = sfx + static_cast<size_t>(blockIdx.y) * nst * kSfBytes;
+    const uint8_t* sfw_tile = sfw + (static_cast<size_t>(blockIdx.x) * total_st + st_begin) * kSfBytes;
+    const uint8_t* sfx_tile = sfx + (static_cast<size_t>(blockIdx.y) * total_st + st_begin) * kSfBytes;
     for (int i = 0; i < nst; ++i) {
       const int s = i % kFStages;
       if (!mbar_wait(&empty[s], ((i / kFStages) & 1) ^ 1, abort_flag, FSITE_TMA)) break;
       if (lane == 0) {
         mbar_expect_tx(&full[s], 2 * kFTileBytes + 2 * kSfBytes);
-        tma_load_2d(smem + C::kOffA + s * kFTileBytes, &tm_w, i * 128, n0, &full[s], pol);
-        tma_load_2d(smem + C::kOffB + s * kFTileBytes, &tm_x, i * 128, t0, &full[s], pol);
+        tma_load_2d(smem + C::kOffA + s * kFTileBytes, &tm_w, (st_begin + i) * 128, n0, &full[s], pol);
+        tma_load_2d(smem + C::kOffB + s * kFTileBytes, &tm_x, (st_begin + i) * 128, t0, &full[s], pol);
         bulk_load_1d(smem + C::kOffSFA + s * 2048, sfw_tile + static_cast<size_t>(i) * kSfBytes,
                      kSfBytes, &full[s], pol);
         bulk_load_1d(smem + C::kOffSFB + s * 2048, sfx_tile + static_cast<size_t>(i) * kSfBytes,
@@ -178,18 +183,28 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter of this warp
     const int n = n0 + q * 32 + lane;
-    if (mbar_wait(acc_full, 0, abort_flag, FSITE_EPI)) {
-      tc_fence_after();
-      float rn = 0.f;
-      if (n < N) {
-        rn = (r != nullptr) ? r[n] : 1.f;
-        if (w_scale != nullptr) rn *= *w_scale;
-      }
+    // token columns that exist in this tile, rounded up to the 32-column granularity of tcgen05.ld
+    int tok_cols = M - t0;
+    if (tok_cols > kFTN) tok_cols = kFTN;
+    const int col_end = (tok_cols + 31) & ~31;
+    const bool have_acc = (nst > 0) && mbar_wait(acc_full, 0, abort_flag, FSITE_EPI);
+    if (have_acc) tc_fence_after();
+    float rn = 0.f;
+    if (n < N) {
+      rn = (r != nullptr) ? r[n] : 1.f;
+      if (w_scale != nullptr) rn *= *w_scale;
+    }
 #pragma unroll 1
-      for (int c0 = 0; c0 < kFTN; c0 += 32) {
-        uint32_t v[32];
+    for (int c0 = 0; c0 < col_end; c0 += 32) {
+      uint32_t v[32];
+      if (have_acc) {
         tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
         tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+      if (split_k == 1) {
         if (n < N) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -204,8 +219,53 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
           }
         }
+      } else {
+        // partial sums -> exchange tile red[token][row] over the (now idle) stage buffers
+        float* red = reinterpret_cast<float*>(smem);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) red[(c0 + j) * kFBN + q * 32 + lane] = __uint_as_float(v[j]);
       }
     }
+  }
+
+  // -------------------------------------------------------------------- split-K reduction
+  if (split_k > 1) {
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      int tok_cols = M - t0;
+      if (tok_cols > kFTN) tok_cols = kFTN;
+      const uint32_t rank = cluster_ctarank();
+      const int e = tid - 64;   // 0..127
+      const int c4 = e & 31;    // float4 column (4 weight rows)
+      const uint32_t red_base = smem_u32(smem);
+      for (int tl = static_cast<int>(rank) + split_k * (e >> 5); tl < tok_cols; tl += split_k * 4) {
+        const int m = t0 + tl;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t off = static_cast<uint32_t>((tl * kFBN + c4 * 4) * 4);
+        for (int p = 0; p < split_k; ++p) {
+          const float4 v = dsmem_ld_f4(dsmem_map(red_base + off, static_cast<uint32_t>(p)));
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const float tx = (x_scale != nullptr) ? x_scale[m] : 1.f;
+        const float ws = (w_scale != nullptr) ? *w_scale : 1.f;
+        const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int nn = n0 + c4 * 4 + u;
+          if (nn < N) {
+            const float rr = ((r != nullptr) ? r[nn] : 1.f) * ws;
+            const float val = vals[u] * (rr * tx);
+            if (y_bf16)
+              reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + nn] = __float2bfloat16_rn(val);
+            else
+              reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + nn] = val;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();  // peers may still be reading this CTA's exchange tile until here
   }
 
   tc_fence_before();
@@ -292,17 +352,34 @@ extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atom
   rc = make_tmap_2d_u8(&tm_x, x_codes, static_cast<uint64_t>(K) / 2, M, static_cast<uint64_t>(K) / 2, 128,
                        kFTN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != DQ_OK) return rc;
-  const dim3 grid((N + kFBN - 1) / kFBN, (M + kFTN - 1) / kFTN, 1);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int total_st = K / kFKStage;
+  const int tiles = ((N + kFBN - 1) / kFBN) * ((M + kFTN - 1) / kFTN);
+  // split K across a cluster when the output tiles alone leave most SMs idle (decode batches)
+  int split = 1;
+  while (split < 8 && tiles * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
+  const int sps = (total_st + split - 1) / split;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + kFBN - 1) / kFBN, (M + kFTN - 1) / kFTN, split);
+  cfg.blockDim = dim3(kFThreads, 1, 1);
+  cfg.dynamicSmemBytes = FCfg::kSmemBytes;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = split;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   const int bf = y_dtype == DQ_DTYPE_BF16 ? 1 : 0;
+  cudaError_t e;
   if (fmt == DQ_FP4_NVFP4)
-    gemm_fp4_kernel<1><<<grid, kFThreads, FCfg::kSmemBytes, s>>>(tm_w, tm_x, w_sf_atoms, x_sf_atoms, r,
-                                                                  w_scale, x_scale, y, bf, M, N, K,
-                                                                  st->status_dev);
+    e = cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<1>, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale,
+                           x_scale, y, bf, M, N, K, sps, split, st->status_dev);
   else
-    gemm_fp4_kernel<0><<<grid, kFThreads, FCfg::kSmemBytes, s>>>(tm_w, tm_x, w_sf_atoms, x_sf_atoms, r,
-                                                                  w_scale, x_scale, y, bf, M, N, K,
-                                                                  st->status_dev);
+    e = cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<0>, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale,
+                           x_scale, y, bf, M, N, K, sps, split, st->status_dev);
+  if (e != cudaSuccess)
+    return set_error(DQ_ERR_CUDA, "gemm_fp4 launch failed (split=%d): %s", split, cudaGetErrorString(e));
   DQ_CHECK_CUDA(cudaGetLastError());
   return DQ_OK;
 }

@@ -32,9 +32,11 @@ __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
 }
 
 __device__ __forceinline__ float e2m1_value(uint32_t code) {
-  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  const float v = mag[code & 7];
-  return (code & 8) ? -v : v;
+  // 1 sign, 2 exponent, 1 mantissa bit: 0, 0.5, then (1 + m/2) * 2^(e-1)
+  const uint32_t e = (code >> 1) & 3u, m = code & 1u;
+  const float frac = 1.0f + 0.5f * static_cast<float>(m);
+  const float v = (e == 0) ? 0.5f * static_cast<float>(m) : frac * __uint_as_float((126u + e) << 23);
+  return (code & 8u) ? -v : v;
 }
 
 __device__ __forceinline__ uint32_t e4m3_byte_of(float v) {
@@ -194,14 +196,15 @@ static int launch_fp4(const XT* x, int64_t ldx, const float* a, int M, int K, in
   DQ_REQUIRE((codes == nullptr || aligned(codes, 4)) && (out == nullptr || aligned(out, 16)), DQ_ERR_ALIGN,
              "outputs misaligned");
   if (M == 0) return DQ_OK;
-  const int vecs = (K / 8 + 255) / 256;
+  const int vec = K / 8;
 #define DQ_FP4_LAUNCH(T, V) \
   quant_fp4_kernel<T, V, XT><<<M, T, 0, stream>>>(x, ldx, a, K, fmt, tensor_scale, codes, sf, row_scale, out, mode)
-  if (vecs <= 1) DQ_FP4_LAUNCH(256, 1);
-  else if (vecs <= 2) DQ_FP4_LAUNCH(256, 2);
-  else if (vecs <= 4) DQ_FP4_LAUNCH(256, 4);
-  else if (vecs <= 8) DQ_FP4_LAUNCH(256, 8);
-  else DQ_FP4_LAUNCH(512, 8);
+  if (vec <= 128) DQ_FP4_LAUNCH(128, 1);
+  else if (vec <= 256) DQ_FP4_LAUNCH(256, 1);
+  else if (vec <= 512) DQ_FP4_LAUNCH(512, 1);
+  else if (vec <= 1024) DQ_FP4_LAUNCH(1024, 1);
+  else if (vec <= 2048) DQ_FP4_LAUNCH(1024, 2);
+  else DQ_FP4_LAUNCH(1024, 4);
 #undef DQ_FP4_LAUNCH
   DQ_CHECK_CUDA(cudaGetLastError());
   return DQ_OK;

@@ -122,7 +122,8 @@ def test_sf_atom_order():
 
 
 @pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (16, 256, 512), (130, 200, 768), (1, 128, 3584)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (16, 256, 512), (130, 200, 768), (1, 128, 3584),
+                                   (16, 384, 2048), (40, 136, 1024), (16, 3584, 18944)])
 def test_fp4_gemm_matches_dequant_matmul(fmt, M, N, K):
     x = synthetic.make_x(M, K, M + 1)
     w = synthetic.make_w(N, K, N + 2)

@@ -240,3 +240,27 @@ def test_gemm_rejects_bad_arguments():
                               torch.ones(128, dtype=torch.float16, device=DEV), 128, 192)
     with pytest.raises(ValueError):
         ops.gemm_w4a4_int4(qx, torch.ones(4, device=DEV), pw)  # K % 128 != 0
+
+
+def test_act_quant_rounding_boundaries_and_tiny_scales():
+    # rows built so that x / s lands exactly on and next to half-integers, plus rows whose scale
+    # is denormal-small (1/s overflows): the fast rounding path must still equal IEEE division
+    K = 1024
+    g = torch.Generator().manual_seed(5)
+    rows = []
+    base = torch.zeros(K)
+    base[0] = 7.0  # absmax 7 -> s = 1 exactly: elements are their own quotients
+    halves = (torch.arange(K - 1) % 15 - 7).float() + 0.5
+    r1 = base.clone(); r1[1:] = halves
+    r2 = base.clone(); r2[1:] = torch.nextafter(halves, torch.full_like(halves, 10.0))
+    r3 = base.clone(); r3[1:] = torch.nextafter(halves, torch.full_like(halves, -10.0))
+    rows += [r1, r2, r3]
+    rows.append(torch.randn(K, generator=g) * 1e-41)   # denormal magnitudes
+    rows.append(torch.randn(K, generator=g) * 3e-39)
+    rows.append(torch.randn(K, generator=g) * 1e30)
+    x = torch.stack(rows)
+    for scale_fp16 in (False, True):
+        q, s, _ = O.quant_act_int4(x, None, None, scale_fp16)
+        ref = q.float() * s.reshape(-1, 1)
+        got = ops.fakequant_act_int4(x.to(DEV), None, None, scale_fp16).cpu()
+        assert torch.equal(got, ref)
