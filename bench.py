@@ -358,23 +358,27 @@ def run_case(args):
     from dualquant_b200 import _lib, ops
 
     parts = args.case.split(":")
-    if parts[0] == "quant":  # quant:M:K - the int4 activation quantiser alone
-        from dualquant_b200 import ops as _ops
+    if parts[0] in ("quant", "quant_had"):  # quant:M:K - the int4 activation quantiser alone
+        from dualquant_b200 import _lib as _l, ops as _ops, quarot as _q
 
         M, K = int(parts[1]), int(parts[2])
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
+        had = None
+        if parts[0] == "quant_had":  # with the full online Hadamard of size K (QuaRot R4)
+            hk, kk = _q.get_hadK(K)
+            had = _ops.Hadamard(_l.HAD_FULL, kk, 0, _q.full_hadamard_scale(K), None if hk is None else hk.to(dev))
         n_bufs = max(2, int(400e6 // (M * K * 2)) + 1)
         xs = [torch.randn(M, K, device=dev).to(torch.bfloat16) for _ in range(n_bufs)]
         a = torch.rand(K, device=dev) + 0.5
         for i in range(3):
-            _ops.quant_act_int4(xs[i % n_bufs], a, None, True)
+            _ops.quant_act_int4(xs[i % n_bufs], a, had, True)
         torch.cuda.synchronize()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(args.iters):
-            _ops.quant_act_int4(xs[i % n_bufs], a, None, True)
+            _ops.quant_act_int4(xs[i % n_bufs], a, had, True)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / args.iters

@@ -285,6 +285,206 @@ act_quant_had_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restr
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// fast online Hadamard: warp-shuffle butterflies inside segments, one thread per column across
+// ---------------------------------------------------------------------------------------------
+// The row is viewed as S segments of P contiguous elements (S <= 32, P = 32 * R).
+//   phase A (wht_inner): Walsh-Hadamard of length P inside every segment; a warp owns a segment,
+//            lane l holds elements l + 32 r: stages h < 32 exchange registers with lane ^ h, stages
+//            h >= 32 are register butterflies.  Same stage order and operand order as
+//            the reference loop (h = 1, 2, 4, ...; (a, b) -> (a + b, a - b)), so bit-identical.
+//   phase B: per column c (0..P-1) across the S segments:
+//            matrix mode   out[i] = sum_j H[i][j] * (v[j] * scale), j ascending  (had_K @ x)
+//            butterfly mode  remaining Walsh-Hadamard stages over the segment index, then * scale
+// Full transform of size 28 * 512: A + matrix.  Full power-of-two size: A + butterflies.
+// Partial (across heads) transform: butterflies only, segments = heads.
+template <int R>
+__device__ __forceinline__ void wht_segment_warp(float* seg, int lane) {
+  // lane l holds elements l + 32 r (r < R): conflict-free shared-memory access; stages h < 32
+  // pair lanes (shuffle), stages h >= 32 pair registers r and r + h/32.  Stage order h = 1, 2, ...
+  float v[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) v[r] = seg[lane + 32 * r];
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[r], m);
+      v[r] = upper ? __fsub_rn(other, v[r]) : __fadd_rn(v[r], other);
+    }
+  }
+#pragma unroll
+  for (int h = 1; h < R; h <<= 1) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if ((r & h) == 0) {
+        const float u = v[r], w = v[r + h];
+        v[r] = __fadd_rn(u, w);
+        v[r + h] = __fsub_rn(u, w);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) seg[lane + 32 * r] = v[r];
+}
+
+// The K x K +-1 matrix of the "full" transform, in constant memory so that an FMA takes its
+// coefficient as an immediate constant-bank operand (one instruction per term instead of a
+// shared-memory load plus an FMA).  Refreshed by the host when a call brings a different matrix.
+__constant__ float c_had_mat[32 * 32];
+
+template <int R, typename XT>
+__global__ void __launch_bounds__(512)
+act_quant_had_fast_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
+                          int S, int inner, int matrix, float had_scale,
+                          const float* __restrict__ had_mat, int8_t* __restrict__ codes,
+                          float* __restrict__ sx, float* __restrict__ out, int mode, int scale_fp16) {
+  constexpr int THREADS = 512;
+  extern __shared__ float sm_row[];
+  __shared__ float red[THREADS / 32];
+  float* row = sm_row;
+  float* hm = sm_row + K;
+  grid_dep_launch_dependents();
+  grid_dep_wait();
+  const int P = K / S;
+  const int rr = blockIdx.x;
+  const XT* xr = x + static_cast<int64_t>(rr) * ldx;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
+    float v[8];
+    load8(xr + idx, v);
+    if (a != nullptr) {
+      float av[8];
+      load8(a + idx, av);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
+    }
+    *reinterpret_cast<float4*>(row + idx) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(row + idx + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  (void)hm;
+  (void)had_mat;
+  __syncthreads();
+
+  if (inner) {
+    for (int sgm = warp; sgm < S; sgm += THREADS / 32) wht_segment_warp<R>(row + sgm * P, lane);
+    __syncthreads();
+  }
+
+  float amax = 0.f;
+  for (int c = threadIdx.x; c < P; c += THREADS) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = (j < S) ? row[j * P + c] : 0.f;
+    if (matrix) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], had_scale);
+      // fully unrolled so that every coefficient is a constant-bank immediate of its FMA and
+      // the S independent accumulation chains can be interleaved
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i < S) {
+          float acc = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)  // rows of c_had_mat are padded to 32 with zeros
+            acc = fmaf(c_had_mat[i * 32 + j], v[j], acc);  // H entries are +-1: same as acc + H*v
+          row[i * P + c] = acc;
+          amax = fmaxf(amax, fabsf(acc));
+        }
+      }
+    } else {
+#pragma unroll
+      for (int hb = 0; hb < 5; ++hb) {
+        constexpr int kOne = 1;
+        const int h = kOne << hb;
+        if (h < S) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if ((j & h) == 0) {
+              const float u = v[j], w = v[j + h];
+              v[j] = __fadd_rn(u, w);
+              v[j + h] = __fsub_rn(u, w);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < S) {
+          const float o = __fmul_rn(v[j], had_scale);
+          row[j * P + c] = o;
+          amax = fmaxf(amax, fabsf(o));
+        }
+      }
+    }
+  }
+  float s = 1.f;
+  if (mode != MODE_RAW) {
+    amax = block_max(amax, red, THREADS / 32);
+    s = token_scale(amax, scale_fp16);
+    if (threadIdx.x == 0 && sx != nullptr) sx[rr] = s;
+  } else {
+    __syncthreads();
+  }
+  int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(rr) * K : nullptr;
+  float* orow = (out != nullptr) ? out + static_cast<int64_t>(rr) * K : nullptr;
+  for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = row[idx + e];
+    emit8(v, s, mode, crow, orow, idx);
+  }
+}
+
+// Copies a device-resident S x S matrix into c_had_mat (rows padded to 32) when it is not the
+// one already there.  The matrix behind a given pointer is assumed immutable (it is the constant
+// Hadamard factor of a layer); the copy is a stream-ordered device-to-device memcpy.
+static int upload_had_matrix(const float* had_mat, int S, cudaStream_t stream) {
+  static const float* cached[kMaxDevices] = {nullptr};
+  static int cached_s[kMaxDevices] = {0};
+  int dev = 0;
+  DQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (cached[dev] == had_mat && cached_s[dev] == S) return DQ_OK;
+  void* sym = nullptr;
+  DQ_CHECK_CUDA(cudaGetSymbolAddress(&sym, c_had_mat));
+  DQ_CHECK_CUDA(cudaMemsetAsync(sym, 0, sizeof(float) * 32 * 32, stream));
+  DQ_CHECK_CUDA(cudaMemcpy2DAsync(sym, 32 * sizeof(float), had_mat, S * sizeof(float), S * sizeof(float), S,
+                                  cudaMemcpyDeviceToDevice, stream));
+  cached[dev] = had_mat;
+  cached_s[dev] = S;
+  return DQ_OK;
+}
+
+// Picks the segmentation for the fast kernel; returns false when the shape is outside its range.
+struct HadPlan {
+  int S, R, inner, matrix;
+};
+static bool plan_fast_hadamard(const dq_hadamard_desc* had, int K, HadPlan* plan) {
+  auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
+  if (had->kind == DQ_HAD_FULL && had->had_k > 1) {
+    const int P = K / had->had_k;
+    if (had->had_k > 32 || !pow2(P) || P < 32 || P > 1024) return false;
+    *plan = {had->had_k, P / 32, 1, 1};
+    return true;
+  }
+  if (had->kind == DQ_HAD_FULL) {  // pure Walsh-Hadamard of length K
+    if (!pow2(K) || K < 64) return false;
+    int P = K / 32 < 32 ? 32 : K / 32;   // S = K / P <= 32
+    if (P > 1024) return false;
+    *plan = {K / P, P / 32, 1, 0};
+    return true;
+  }
+  if (had->kind == DQ_HAD_PARTIAL) {
+    const int H = K / had->had_dim;
+    if (H > 32 || !pow2(H)) return false;
+    *plan = {H, 1, 0, 0};
+    return true;
+  }
+  return false;
+}
+
 constexpr int kHadThreads = 512;
 constexpr int kHadMaxSmem = 200 * 1024;
 
@@ -294,6 +494,15 @@ int init_act_quant_kernels() {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(act_quant_had_kernel<kHadThreads, float>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
+#define DQ_HAD_ATTR(R, T)                                                                     \
+  if (e == cudaSuccess)                                                                       \
+    e = cudaFuncSetAttribute(act_quant_had_fast_kernel<R, T>,                                   \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
+  DQ_HAD_ATTR(1, __nv_bfloat16) DQ_HAD_ATTR(2, __nv_bfloat16) DQ_HAD_ATTR(4, __nv_bfloat16)
+  DQ_HAD_ATTR(8, __nv_bfloat16) DQ_HAD_ATTR(16, __nv_bfloat16) DQ_HAD_ATTR(32, __nv_bfloat16)
+  DQ_HAD_ATTR(1, float) DQ_HAD_ATTR(2, float) DQ_HAD_ATTR(4, float)
+  DQ_HAD_ATTR(8, float) DQ_HAD_ATTR(16, float) DQ_HAD_ATTR(32, float)
+#undef DQ_HAD_ATTR
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(act_quant_had) failed: %s",
                      cudaGetErrorString(e));
@@ -344,6 +553,27 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
     const size_t smem = static_cast<size_t>(K) * 4 + (hk > 1 ? static_cast<size_t>(hk) * hk * 4 : 0);
     DQ_REQUIRE(smem <= static_cast<size_t>(kHadMaxSmem), DQ_ERR_UNSUPPORTED,
                "row of K=%d does not fit in shared memory", K);
+    HadPlan plan;
+    if (use_had && plan_fast_hadamard(had, K, &plan)) {
+      if (plan.matrix) {
+        int rc2 = upload_had_matrix(had->had_mat, plan.S, stream);
+        if (rc2 != DQ_OK) return rc2;
+      }
+#define DQ_HAD_FAST(RR)                                                                          \
+  DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT>, dim3(M), dim3(512), smem, stream, x, ldx, a, \
+                           K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes, sx, out,   \
+                           mode, scale_fp16))
+      switch (plan.R) {
+        case 1: DQ_HAD_FAST(1); break;
+        case 2: DQ_HAD_FAST(2); break;
+        case 4: DQ_HAD_FAST(4); break;
+        case 8: DQ_HAD_FAST(8); break;
+        case 16: DQ_HAD_FAST(16); break;
+        default: DQ_HAD_FAST(32); break;
+      }
+#undef DQ_HAD_FAST
+      return DQ_OK;
+    }
     DQ_CHECK_CUDA(launch_pdl(act_quant_had_kernel<kHadThreads, XT>, dim3(M), dim3(kHadThreads), smem,
                              stream, x, ldx, a, K, use_had ? had->kind : DQ_HAD_NONE, hk,
                              use_had ? had->had_dim : 0, use_had ? had->scale : 1.f,

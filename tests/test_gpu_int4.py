@@ -116,7 +116,8 @@ def _full_had(K):
                         None if had is None else had.to(DEV)), ("full", had, k)
 
 
-@pytest.mark.parametrize("M,K", [(3, 896), (2, 14336), (4, 1024)])
+@pytest.mark.parametrize("M,K", [(3, 896), (2, 14336), (4, 1024), (2, 64), (3, 4096), (1, 2048), (2, 28 * 1024),
+                                 (2, 32768)])
 def test_full_hadamard_bit_exact(M, K):
     hd, ohad = _full_had(K)
     g = torch.Generator().manual_seed(2)
@@ -131,8 +132,9 @@ def test_full_hadamard_bit_exact(M, K):
     _status_ok()
 
 
-def test_partial_hadamard_bit_exact():
-    M, K, d = 5, 4096, 128
+@pytest.mark.parametrize("K,d", [(4096, 128), (256, 8), (1024, 64), (8192, 128)])
+def test_partial_hadamard_bit_exact(K, d):
+    M = 5
     hd = ops.Hadamard(_lib.HAD_PARTIAL, 1, d, O.partial_hadamard_scale(K // d), None)
     xb = synthetic.make_x(M, K, 6)
     _, c = synthetic.make_scales(8, K, 6)
