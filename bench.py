@@ -473,6 +473,71 @@ def run_prefill_suite(args):
                       "int8_2x_bf16_" + kind: int8_measured}, "steps": args.steps, "rows": rows}), flush=True)
 
 
+def run_mlp_suite(args):
+    """BASELINE config 2: prefill MLP, M = 8192 tokens, int4 dual-scale.  gate+up 4096 -> 28672
+    (bf16 out), SiLU(gate) * up in bf16, QuaRot R4 online Hadamard of size 14336 (28 x 512) fused
+    with the activation quantiser, down 14336 -> 4096.  Stage times from CUDA-graph replays."""
+    from dualquant_b200 import _lib, ops, quarot
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    M, H, I = 8192, 4096, 14336
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def packed(N, K):
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        c, sw = ops.quant_w_int4(w)
+        return ops.pack_w_int4(c, sw)
+
+    w_gu, w_down = packed(2 * I, H), packed(H, I)
+    r_gu, c_gu = synthetic.make_scales(2 * I, H, 0)
+    r_dn, c_dn = synthetic.make_scales(H, I, 1)
+    r_gu, a_gu, r_dn, a_dn = r_gu.to(dev), (1.0 / c_gu).to(dev), r_dn.to(dev), (1.0 / c_dn).to(dev)
+    hk, kk = quarot.get_hadK(I)
+    had = ops.Hadamard(_lib.HAD_FULL, kk, 0, quarot.full_hadamard_scale(I), hk.to(dev))
+    x = torch.randn(M, H, generator=g, device=dev).to(torch.bfloat16)
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(M, H, dtype=torch.float32, device=dev)
+    s1 = torch.empty(ops.linear_scratch_bytes(M, 2 * I, H), dtype=torch.uint8, device=dev)
+    state = {}
+
+    def st_gate_up():
+        ops.linear_w4a4_int4(x, a_gu, None, w_gu, r_gu, scale_fp16=True, scratch=s1, out=gu)
+
+    def st_act():
+        state["h"] = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+
+    def st_quant():
+        state["q"] = ops.quant_act_int4(state["h"], a_dn, had, True)
+
+    def st_down():
+        ops.gemm_w4a4_int4(state["q"][0], state["q"][1], w_down, r_dn, out=y)
+
+    def st_fused_quant():
+        state["q"] = ops.quant_act_int4_gated(gu[:, :I], gu[:, I:], a_dn, had, True)
+
+    def whole():
+        st_gate_up(); st_act(); st_quant(); st_down()
+
+    def whole_fused():
+        st_gate_up(); st_fused_quant(); st_down()
+
+    whole()
+    torch.cuda.synchronize()
+    out = {"suite": "mlp", "M": M, "hidden": H, "intermediate": I}
+    for name, fn in (("gate_up_linear", st_gate_up), ("silu_mul_bf16_torch", st_act),
+                     ("hadamard_quant", st_quant), ("silu_mul_hadamard_quant_fused", st_fused_quant),
+                     ("down_gemm", st_down), ("whole_mlp_unfused", whole), ("whole_mlp", whole_fused)):
+        gr = _capture(fn, dev)
+        ms = _time_loop(gr.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        out[name + "_us"] = round(ms * 1e3, 1)
+    ops_total = 2.0 * M * (2 * I * H + H * I)
+    out["whole_mlp_TOPS"] = round(ops_total / (out["whole_mlp_us"] * 1e-6) / 1e12, 1)
+    out["hadamard_quant_GBps"] = round((M * I * 3) / (out["hadamard_quant_us"] * 1e-6) / 1e9, 1)
+    _lib.device_status(0)
+    print(json.dumps(out), flush=True)
+
+
 def run_fp4_suite(args):
     """Block-scaled FP4 linears on the Qwen2.5-7B-architecture shapes (BASELINE config 3):
     MXFP4 and NVFP4, M = 16 (GB/s of algorithmic bytes) and M = 4096 (TFLOPS = 2*M*N*K/s)."""
@@ -638,13 +703,15 @@ def main():
     ap.add_argument("--detail", action="store_true", help="add per-(linear, M) GEMM GB/s")
     ap.add_argument("--case", default=None, help="NAME:M[:TN:SPLIT] - run one (linear, M) GEMM alone")
     ap.add_argument("--iters", type=int, default=6)
-    ap.add_argument("--suite", default=None, choices=["prefill", "fp4"], help="extra measurement suites")
+    ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp"], help="extra measurement suites")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     if args.suite == "prefill":
         run_prefill_suite(args)
     elif args.suite == "fp4":
         run_fp4_suite(args)
+    elif args.suite == "mlp":
+        run_mlp_suite(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

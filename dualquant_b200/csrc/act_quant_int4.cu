@@ -70,6 +70,23 @@ __device__ __forceinline__ void load8(const float* p, float* v) {
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+// SiLU(gate) * up the way a bf16 decoder computes it: SiLU evaluated in fp32 and rounded to
+// bf16, the product rounded to bf16 again.
+__device__ __forceinline__ float silu_mul_bf16(float g, float u) {
+  const float sg = __fdiv_rn(g, 1.0f + expf(-g));
+  const float sgb = __bfloat162float(__float2bfloat16_rn(sg));
+  return __bfloat162float(__float2bfloat16_rn(__fmul_rn(sgb, u)));
+}
+template <typename XT>
+__device__ __forceinline__ void apply_gate(const XT* up_ptr, float* v) {
+  if (up_ptr != nullptr) {
+    float u[8];
+    load8(up_ptr, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = silu_mul_bf16(v[e], u[e]);
+  }
+}
+
 // Eight input elements as loaded (bf16: one 16-byte vector; fp32: two).
 template <typename XT>
 struct Raw8;
@@ -203,7 +220,8 @@ constexpr int kMaxHadK = 32;
 
 template <int THREADS, typename XT>
 __global__ void __launch_bounds__(THREADS)
-act_quant_had_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
+act_quant_had_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_t ldx,
+                     const float* __restrict__ a, int K,
                      int had_kind, int had_k, int had_dim, float had_scale,
                      const float* __restrict__ had_mat, int8_t* __restrict__ codes,
                      float* __restrict__ sx, float* __restrict__ out, int mode, int scale_fp16) {
@@ -215,10 +233,12 @@ act_quant_had_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restr
   grid_dep_wait();
   const int r = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(r) * ldx;
+  const XT* ur = (up != nullptr) ? up + static_cast<int64_t>(r) * ldx : nullptr;
 
   for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
     float v[8];
     load8(xr + idx, v);
+    apply_gate(ur != nullptr ? ur + idx : nullptr, v);
     if (a != nullptr) {
       float av[8];
       load8(a + idx, av);
@@ -336,7 +356,8 @@ __constant__ float c_had_mat[32 * 32];
 
 template <int R, typename XT>
 __global__ void __launch_bounds__(512)
-act_quant_had_fast_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
+act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_t ldx,
+                          const float* __restrict__ a, int K,
                           int S, int inner, int matrix, float had_scale,
                           const float* __restrict__ had_mat, int8_t* __restrict__ codes,
                           float* __restrict__ sx, float* __restrict__ out, int mode, int scale_fp16) {
@@ -350,11 +371,13 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, int64_t ldx, const float* __
   const int P = K / S;
   const int rr = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(rr) * ldx;
+  const XT* ur = (up != nullptr) ? up + static_cast<int64_t>(rr) * ldx : nullptr;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
     float v[8];
     load8(xr + idx, v);
+    apply_gate(ur != nullptr ? ur + idx : nullptr, v);
     if (a != nullptr) {
       float av[8];
       load8(a + idx, av);
@@ -534,7 +557,7 @@ static int check_had(const dq_hadamard_desc* had, int K) {
 template <typename XT>
 static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamard_desc* had, int M,
                       int K, int8_t* codes, float* sx, float* out, int mode, int scale_fp16,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const XT* up = nullptr) {
   DQ_REQUIRE(x != nullptr, DQ_ERR_NULL, "x is null");
   DQ_REQUIRE(M >= 0 && K >= 8 && K % 8 == 0, DQ_ERR_SHAPE, "bad shape M=%d K=%d (K %% 8 != 0)", M, K);
   DQ_REQUIRE(ldx >= K && ldx % 8 == 0, DQ_ERR_ALIGN, "ldx=%lld must be >= K and a multiple of 8",
@@ -548,7 +571,7 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
   if (rc != DQ_OK) return rc;
   if (M == 0) return DQ_OK;
   const bool use_had = had != nullptr && had->kind != DQ_HAD_NONE;
-  if (use_had || mode == MODE_RAW || K > 32768) {  // longer rows than the register path holds
+  if (use_had || mode == MODE_RAW || K > 32768 || up != nullptr) {  // longer rows than the register path holds
     const int hk = use_had ? had->had_k : 1;
     const size_t smem = static_cast<size_t>(K) * 4 + (hk > 1 ? static_cast<size_t>(hk) * hk * 4 : 0);
     DQ_REQUIRE(smem <= static_cast<size_t>(kHadMaxSmem), DQ_ERR_UNSUPPORTED,
@@ -560,7 +583,7 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
         if (rc2 != DQ_OK) return rc2;
       }
 #define DQ_HAD_FAST(RR)                                                                          \
-  DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT>, dim3(M), dim3(512), smem, stream, x, ldx, a, \
+  DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT>, dim3(M), dim3(512), smem, stream, x, up, ldx, a, \
                            K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes, sx, out,   \
                            mode, scale_fp16))
       switch (plan.R) {
@@ -575,7 +598,7 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
       return DQ_OK;
     }
     DQ_CHECK_CUDA(launch_pdl(act_quant_had_kernel<kHadThreads, XT>, dim3(M), dim3(kHadThreads), smem,
-                             stream, x, ldx, a, K, use_had ? had->kind : DQ_HAD_NONE, hk,
+                             stream, x, up, ldx, a, K, use_had ? had->kind : DQ_HAD_NONE, hk,
                              use_had ? had->had_dim : 0, use_had ? had->scale : 1.f,
                              use_had ? had->had_mat : nullptr, codes, sx, out, mode, scale_fp16));
   } else {
@@ -633,4 +656,16 @@ extern "C" int dq_hadamard_f32(const float* x, float* out, int M, int K,
   DQ_REQUIRE(had != nullptr && had->kind != DQ_HAD_NONE, DQ_ERR_NULL, "no Hadamard described");
   return launch_act(x, static_cast<int64_t>(K), nullptr, had, M, K, nullptr, nullptr, out, MODE_RAW,
                     0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dq_quant_act_int4_gated(const void* gate_bf16, const void* up_bf16, int64_t ld,
+                                       const float* a, const dq_hadamard_desc* had, int M, int K,
+                                       int8_t* codes, float* sx, int scale_fp16, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  DQ_REQUIRE(codes != nullptr && sx != nullptr && up_bf16 != nullptr, DQ_ERR_NULL, "codes / sx / up is null");
+  DQ_REQUIRE(aligned(up_bf16, 16), DQ_ERR_ALIGN, "up must be 16-byte aligned");
+  return launch_act(static_cast<const __nv_bfloat16*>(gate_bf16), ld, a, had, M, K, codes, sx, nullptr,
+                    MODE_CODES, scale_fp16, static_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(up_bf16));
 }

@@ -121,6 +121,25 @@ def quant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
     return codes, sx
 
 
+def quant_act_int4_gated(gate: torch.Tensor, up: torch.Tensor, a: Optional[torch.Tensor] = None,
+                         had: Optional[Hadamard] = None, scale_fp16: bool = False):
+    """codes/scales of bf16(bf16(SiLU(gate)) * up); gate and up are bf16 [M,K] views with the same
+    row stride (typically the two halves of a fused gate+up projection output)."""
+    lib = _prep(gate)
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16:
+        raise ValueError("quant_act_int4_gated expects bf16 inputs")
+    if gate.shape != up.shape or gate.stride() != up.stride() or gate.stride(-1) != 1:
+        raise ValueError("gate and up must have the same shape and strides (unit inner stride)")
+    M, K = gate.shape
+    codes = torch.empty(M, K, dtype=torch.int8, device=gate.device)
+    sx = torch.empty(M, dtype=torch.float32, device=gate.device)
+    desc = had.desc() if had is not None else None
+    _lib.check(lib.dq_quant_act_int4_gated(_ptr(gate), _ptr(up), gate.stride(0) if M > 1 else K, _ptr(a),
+                                           desc, M, K, _ptr(codes), _ptr(sx), int(scale_fp16),
+                                           _stream(gate.device)), "dq_quant_act_int4_gated")
+    return codes, sx
+
+
 def fakequant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
                        had: Optional[Hadamard] = None, scale_fp16: bool = False) -> torch.Tensor:
     """[M,K] bf16 or fp32 -> de-quantised fp32 [M,K] (what FormatSpec.cast returns)."""

@@ -127,6 +127,17 @@ DQ_API int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a,
                       const dq_hadamard_desc* had, int M, int K, int8_t* codes, float* sx,
                       int scale_fp16, void* stream);
 
+/*
+ * dq_quant_act_int4 with the MLP activation fused in front: the input row is
+ * bf16(bf16(SiLU(gate)) * up), the bf16 arithmetic of the decoder MLP that feeds down_proj
+ * (the reference leaves it to the HF model: hidden = act_fn(gate_proj(x)) * up_proj(x), then
+ * PermLinear.forward of down_proj, activations/perm_linear.py:136-141).  gate and up are bf16
+ * [M,K] with the same leading dimension ld (e.g. the two halves of a fused gate+up output).
+ */
+DQ_API int dq_quant_act_int4_gated(const void* gate_bf16, const void* up_bf16, int64_t ld,
+                                   const float* a, const dq_hadamard_desc* had, int M, int K,
+                                   int8_t* codes, float* sx, int scale_fp16, void* stream);
+
 /* Same arithmetic, but writes the de-quantised value q*s as fp32 [M,K] (what
  * FormatSpec.cast returns, formats/base.py:33-39).  x is fp32 when x_is_f32 != 0. */
 DQ_API int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, const float* a,

@@ -266,3 +266,23 @@ def test_act_quant_rounding_boundaries_and_tiny_scales():
         ref = q.float() * s.reshape(-1, 1)
         got = ops.fakequant_act_int4(x.to(DEV), None, None, scale_fp16).cpu()
         assert torch.equal(got, ref)
+
+
+def test_gated_quantiser_matches_bf16_silu_mul():
+    # SiLU(gate) * up in bf16 fused in front of the Hadamard quantiser; expf differs in the last
+    # ulp between CPU and GPU, so a handful of bf16 roundings (hence codes) may differ
+    M, K = 6, 14336
+    g = torch.Generator().manual_seed(11)
+    gu = (torch.randn(M, 2 * K, generator=g) * 1.5).to(torch.bfloat16)
+    gate, up = gu[:, :K], gu[:, K:]
+    h = torch.nn.functional.silu(gate) * up
+    _, c = synthetic.make_scales(8, K, 11)
+    a = 1.0 / c
+    hd, ohad = _full_had(K)
+    gud = gu.to(DEV)
+    for had_dev, had_cpu in ((None, None), (hd, ohad)):
+        qx, sx, _ = O.quant_act_int4(h, a, had_cpu, True)
+        codes, sxg = ops.quant_act_int4_gated(gud[:, :K], gud[:, K:], a.to(DEV), had_dev, True)
+        diff = (codes.cpu().int() - qx.int()).abs()
+        assert diff.max() <= 1 and (diff > 0).float().mean() < 2e-3
+        assert torch.allclose(sxg.cpu(), sx, rtol=2e-3)
