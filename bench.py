@@ -538,6 +538,98 @@ def run_mlp_suite(args):
     print(json.dumps(out), flush=True)
 
 
+def run_decoder_suite(args):
+    """BASELINE config 4: random-init Llama-3.1-8B-architecture decoder, every linear W4A4 int4
+    dual-scale with online Hadamards, bf16 attention; prefill batch x seqlen, then decode steps.
+    Tensor-parallel over the ranks of the launch (torch.distributed.run) with an NCCL all-reduce
+    after o_proj and down_proj.  Prints one JSON line on rank 0."""
+    import torch.distributed as dist
+
+    from dualquant_b200 import _lib, decoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    cfg = decoder.DecoderConfig(num_hidden_layers=args.layers)
+    B, S, steps = args.batch, args.seqlen, args.decode_steps
+    model = decoder.Decoder(cfg, dev, tp=world, rank=rank, seed=0, group=group)
+    model.alloc_cache(B, S + steps)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), generator=g).to(dev)
+
+    def sync():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+
+    def timed(fn):
+        sync()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return out, ms
+
+    with torch.no_grad():
+        model.prefill(ids)  # warm-up at full size (allocator, kernel set-up, NCCL communicator)
+        logits, prefill_ms = timed(lambda: model.prefill(ids))
+        tok = logits.argmax(-1)
+        pos_t = torch.tensor([S], dtype=torch.int64, device=dev)
+        static_tok = tok.clone()
+        graph = None
+        if not args.no_graph:
+            try:
+                model.decode_step(static_tok, pos_t)  # warm-up outside capture
+                torch.cuda.synchronize(dev)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    static_logits = model.decode_step(static_tok, pos_t)
+            except Exception as exc:  # capture not possible (e.g. collective): run eagerly
+                graph = None
+                sys.stderr.write(f"decode graph capture failed, running eagerly: {exc}\n")
+
+        def decode_loop():
+            cur = tok
+            for i in range(steps):
+                pos_t.fill_(S + i)
+                if graph is not None:
+                    static_tok.copy_(cur)
+                    graph.replay()
+                    cur = static_logits.argmax(-1)
+                else:
+                    cur = model.decode_step(cur, pos_t).argmax(-1)
+            return cur
+
+        _, decode_ms = timed(decode_loop)
+    _lib.device_status(local_rank)
+    if rank == 0:
+        wbytes = decoder.linear_weight_bytes(cfg)
+        step_ms = decode_ms / steps
+        print(json.dumps({
+            "suite": "decoder", "n_gpus": world, "layers": cfg.num_hidden_layers, "batch": B, "seqlen": S,
+            "decode_steps": steps, "parallelism": f"tp{world}: qkv/gate_up column-parallel, o/down row-parallel + NCCL all-reduce",
+            "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(B * S / prefill_ms * 1e3, 1),
+            "decode_ms_per_step": round(step_ms, 3), "decode_tokens_per_s": round(B / step_ms * 1e3, 1),
+            "decode_launch": "CUDA graph" if graph is not None else "eager",
+            "linear_weight_GB": round(wbytes / 1e9, 3),
+            "decode_weight_stream_GBps": round(wbytes / (step_ms * 1e-3) / 1e9, 1)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_fp4_suite(args):
     """Block-scaled FP4 linears on the Qwen2.5-7B-architecture shapes (BASELINE config 3):
     MXFP4 and NVFP4, M = 16 (GB/s of algorithmic bytes) and M = 4096 (TFLOPS = 2*M*N*K/s)."""
@@ -703,7 +795,11 @@ def main():
     ap.add_argument("--detail", action="store_true", help="add per-(linear, M) GEMM GB/s")
     ap.add_argument("--case", default=None, help="NAME:M[:TN:SPLIT] - run one (linear, M) GEMM alone")
     ap.add_argument("--iters", type=int, default=6)
-    ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp"], help="extra measurement suites")
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seqlen", type=int, default=2048)
+    ap.add_argument("--decode-steps", type=int, default=128)
+    ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp", "decoder"], help="extra measurement suites")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     if args.suite == "prefill":
@@ -712,6 +808,8 @@ def main():
         run_fp4_suite(args)
     elif args.suite == "mlp":
         run_mlp_suite(args)
+    elif args.suite == "decoder":
+        run_decoder_suite(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

@@ -1,0 +1,214 @@
+"""Llama-architecture decoder stack whose linears all run the W4A4 int4 dual-scale path, with
+Megatron-style tensor parallelism over the ranks of one node.
+
+This is the harness for the end-to-end configuration (random-init Llama-3.1-8B architecture,
+prefill + decode, TP 1/2/4/8): the counterpart of the reference's graph_bench_all.prefill/decode
+(ablation/real_int4_kernel/graph_bench_all.py:72-157) around HF's LlamaForCausalLM with every
+linear wrapped by PermLinear and the QuaRot online Hadamards installed
+(quarot/online_had_install.py:44-58).  Attention, RMSNorm and RoPE stay bf16 torch ops (the
+reference leaves them to HF); the seven linears of a layer are four fused W4A4 calls:
+
+    qkv      column-parallel (query/key/value heads split over ranks)
+    o_proj   row-parallel   (online partial Hadamard across the rank's heads), all-reduce
+    gate+up  column-parallel
+    down     row-parallel   (SiLU*up + online Hadamard of the rank's slice + quantiser fused), all-reduce
+
+With tp > 1 the online Hadamards and the per-token activation scales are taken over the rank's
+own slice of the sharded axis (a valid rotation / scaling per shard, no collective); the only
+collectives are the two all-reduces per layer (NCCL).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import _lib, ops, quarot, synthetic
+
+
+@dataclass
+class DecoderConfig:
+    hidden_size: int = 4096
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    vocab_size: int = 128256
+    rope_theta: float = 500000.0
+    rms_norm_eps: float = 1e-5
+    online_hadamard: bool = True
+
+
+LLAMA31_8B = DecoderConfig()
+
+
+class W4A4Linear:
+    """Packed int4 weight + DualQuant scales (+ optional online Hadamard) of one linear shard."""
+
+    def __init__(self, N: int, K: int, device, gen: torch.Generator, had: Optional[ops.Hadamard] = None):
+        w = (torch.randn(N, K, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+        codes, sw = ops.quant_w_int4(w)
+        self.pw = ops.pack_w_int4(codes, sw)
+        del w, codes, sw
+        self.r = torch.exp(torch.randn(N, generator=gen, device=device) * 0.3).half().float()
+        c = torch.exp(torch.randn(K, generator=gen, device=device) * 0.3).half().float()
+        self.a = 1.0 / c
+        self.had = had
+        self.N, self.K = N, K
+        self._scratch = {}
+
+    def _scratch_for(self, M: int, device):
+        buf = self._scratch.get(M)
+        if buf is None:
+            buf = torch.empty(max(ops.linear_scratch_bytes(M, self.N, self.K), 256), dtype=torch.uint8,
+                              device=device)
+            self._scratch[M] = buf
+        return buf
+
+    def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+        return ops.linear_w4a4_int4(x, self.a, self.had, self.pw, self.r, out_dtype=out_dtype,
+                                    scale_fp16=False, scratch=self._scratch_for(x.shape[0], x.device))
+
+    def gated(self, gate: torch.Tensor, up: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+        codes, sx = ops.quant_act_int4_gated(gate, up, self.a, self.had, False)
+        return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype)
+
+
+def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    return F.rms_norm(x, (x.shape[-1],), weight, eps)
+
+
+def _rope_tables(cfg: DecoderConfig, max_pos: int, device):
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device).float() / cfg.head_dim))
+    ang = torch.arange(max_pos, device=device).float()[:, None] * inv[None, :]
+    emb = torch.cat([ang, ang], dim=-1)
+    return emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
+
+
+def _apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    # x [B, H, S, D]; cos/sin [S, D]
+    d = x.shape[-1] // 2
+    rot = torch.cat([-x[..., d:], x[..., :d]], dim=-1)
+    return x * cos + rot * sin
+
+
+class DecoderLayer:
+    def __init__(self, cfg: DecoderConfig, tp: int, device, gen: torch.Generator):
+        self.cfg, self.tp = cfg, tp
+        hd = cfg.head_dim
+        self.hq = cfg.num_attention_heads // tp
+        self.hkv = cfg.num_key_value_heads // tp
+        inter = cfg.intermediate_size // tp
+        had_o = had_d = None
+        if cfg.online_hadamard:
+            if self.hq > 1:
+                had_o = ops.Hadamard(_lib.HAD_PARTIAL, 1, hd, quarot.partial_hadamard_scale(self.hq), None)
+            hk, kk = quarot.get_hadK(inter)
+            had_d = ops.Hadamard(_lib.HAD_FULL, kk, 0, quarot.full_hadamard_scale(inter),
+                                 None if hk is None else hk.to(device))
+        self.qkv = W4A4Linear((self.hq + 2 * self.hkv) * hd, cfg.hidden_size, device, gen)
+        self.o = W4A4Linear(cfg.hidden_size, self.hq * hd, device, gen, had_o)
+        self.gate_up = W4A4Linear(2 * inter, cfg.hidden_size, device, gen)
+        self.down = W4A4Linear(cfg.hidden_size, inter, device, gen, had_d)
+        self.inter = inter
+        self.ln1 = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
+        self.ln2 = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
+        self.k_cache = self.v_cache = None
+
+    def alloc_cache(self, batch: int, max_len: int, device):
+        shape = (batch, self.hkv, max_len, self.cfg.head_dim)
+        self.k_cache = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        self.v_cache = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+
+    def forward(self, x, cos, sin, pos0: int, pos_t: Optional[torch.Tensor], mask, group):
+        """x [B, S, hidden] bf16.  Prefill: pos0 = 0, pos_t None (causal).  Decode: S = 1, the
+        cache position comes from the device tensor pos_t and `mask` hides the unwritten tail."""
+        cfg = self.cfg
+        B, S, Hd = x.shape
+        hd = cfg.head_dim
+        h = _rms_norm(x, self.ln1, cfg.rms_norm_eps)
+        qkv = self.qkv(h.reshape(B * S, Hd)).reshape(B, S, self.hq + 2 * self.hkv, hd)
+        q = qkv[:, :, : self.hq].transpose(1, 2)
+        k = qkv[:, :, self.hq : self.hq + self.hkv].transpose(1, 2)
+        v = qkv[:, :, self.hq + self.hkv :].transpose(1, 2)
+        q, k = _apply_rope(q, cos, sin), _apply_rope(k, cos, sin)
+        rep = self.hq // self.hkv  # grouped-query attention: expand K/V heads for the fused kernels
+        if pos_t is None:
+            self.k_cache[:, :, pos0 : pos0 + S] = k
+            self.v_cache[:, :, pos0 : pos0 + S] = v
+            attn = F.scaled_dot_product_attention(q, k.repeat_interleave(rep, dim=1),
+                                                  v.repeat_interleave(rep, dim=1), is_causal=True)
+        else:
+            self.k_cache.index_copy_(2, pos_t, k)
+            self.v_cache.index_copy_(2, pos_t, v)
+            attn = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask,
+                                                  enable_gqa=True)
+        attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
+        o = self.o(attn)
+        if self.tp > 1:
+            dist.all_reduce(o, group=group)
+        x = x + o.reshape(B, S, Hd)
+        h = _rms_norm(x, self.ln2, cfg.rms_norm_eps)
+        gu = self.gate_up(h.reshape(B * S, Hd))
+        d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :])
+        if self.tp > 1:
+            dist.all_reduce(d, group=group)
+        return x + d.reshape(B, S, Hd)
+
+
+class Decoder:
+    def __init__(self, cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, group=None):
+        assert cfg.num_key_value_heads % tp == 0 and cfg.intermediate_size % (tp * 128) == 0
+        self.cfg, self.tp, self.rank, self.group, self.device = cfg, tp, rank, group, device
+        gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)  # each rank: its own shard
+        shared = torch.Generator(device=device).manual_seed(seed)             # replicated tensors
+        self.embed = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=shared, device=device) * 0.02).to(torch.bfloat16)
+        self.lm_head = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=shared, device=device) * 0.02).to(torch.bfloat16)
+        self.norm = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
+        self.layers = [DecoderLayer(cfg, tp, device, gen) for _ in range(cfg.num_hidden_layers)]
+        self.max_len = 0
+
+    def alloc_cache(self, batch: int, max_len: int):
+        self.max_len = max_len
+        for layer in self.layers:
+            layer.alloc_cache(batch, max_len, self.device)
+        self.cos, self.sin = _rope_tables(self.cfg, max_len, self.device)
+
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [B, S] -> logits of the last position [B, vocab]."""
+        B, S = ids.shape
+        x = self.embed[ids]
+        cos, sin = self.cos[:S], self.sin[:S]
+        for layer in self.layers:
+            x = layer.forward(x, cos, sin, 0, None, None, self.group)
+        x = _rms_norm(x[:, -1], self.norm, self.cfg.rms_norm_eps)
+        return x @ self.lm_head.T
+
+    def decode_step(self, ids: torch.Tensor, pos_t: torch.Tensor) -> torch.Tensor:
+        """ids [B] (one token per sequence), pos_t: int64 device tensor [1] with the cache position.
+        Everything is indexed through pos_t, so the step can be captured in a CUDA graph."""
+        x = self.embed[ids].unsqueeze(1)
+        cos = self.cos.index_select(0, pos_t)
+        sin = self.sin.index_select(0, pos_t)
+        mask = (torch.arange(self.max_len, device=self.device) <= pos_t).view(1, 1, 1, self.max_len)
+        for layer in self.layers:
+            x = layer.forward(x, cos, sin, 0, pos_t, mask, self.group)
+        x = _rms_norm(x[:, 0], self.norm, self.cfg.rms_norm_eps)
+        return x @ self.lm_head.T
+
+
+def linear_weight_bytes(cfg: DecoderConfig) -> int:
+    """Algorithmic int4 weight bytes (codes + fp16 group scales) of all decoder linears."""
+    hd = cfg.head_dim
+    per_layer = 0
+    for N, K in (((cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * hd, cfg.hidden_size),
+                 (cfg.hidden_size, cfg.num_attention_heads * hd),
+                 (2 * cfg.intermediate_size, cfg.hidden_size),
+                 (cfg.hidden_size, cfg.intermediate_size)):
+        per_layer += N * K // 2 + N * (K // 128) * 2
+    return per_layer * cfg.num_hidden_layers
