@@ -590,7 +590,10 @@ def run_decoder_suite(args):
         pos_t = torch.tensor([S], dtype=torch.int64, device=dev)
         static_tok = tok.clone()
         graph = None
-        if not args.no_graph:
+        # With tensor parallelism the step contains NCCL all-reduces; torch.distributed collectives
+        # are not captured here (a first attempt to capture them did not terminate), so the
+        # multi-rank decode loop is launched eagerly.
+        if not args.no_graph and world == 1:
             try:
                 model.decode_step(static_tok, pos_t)  # warm-up outside capture
                 torch.cuda.synchronize(dev)
