@@ -604,6 +604,10 @@ def run_decoder_suite(args):
                 graph = None
                 sys.stderr.write(f"decode graph capture failed, running eagerly: {exc}\n")
 
+        if graph is None:
+            for _ in range(2):  # untimed eager warm-up steps (allocator, lazy NCCL channels)
+                model.decode_step(tok, pos_t)
+
         def decode_loop():
             cur = tok
             for i in range(steps):
