@@ -558,7 +558,8 @@ def run_decoder_suite(args):
         group = dist.group.WORLD
     cfg = decoder.DecoderConfig(num_hidden_layers=args.layers)
     B, S, steps = args.batch, args.seqlen, args.decode_steps
-    model = decoder.Decoder(cfg, dev, tp=world, rank=rank, seed=0, group=group)
+    fused = bool(args.fused_allreduce) and world > 1
+    model = decoder.Decoder(cfg, dev, tp=world, rank=rank, seed=0, group=group, fused_allreduce=fused)
     model.alloc_cache(B, S + steps)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab_size, (B, S), generator=g).to(dev)
@@ -590,11 +591,13 @@ def run_decoder_suite(args):
         pos_t = torch.tensor([S], dtype=torch.int64, device=dev)
         static_tok = tok.clone()
         graph = None
-        # With tensor parallelism the step contains NCCL all-reduces; torch.distributed collectives
-        # are not captured here (a first attempt to capture them did not terminate), so the
-        # multi-rank decode loop is launched eagerly.
-        if not args.no_graph and world == 1:
+        # With tensor parallelism and NCCL the step contains torch.distributed collectives, which
+        # are not captured here (a first attempt to capture them did not terminate), so that
+        # decode loop is launched eagerly.  With the all-reduce fused into the GEMM kernel the step
+        # holds no library collective and is captured like the single-GPU one.
+        if not args.no_graph and (world == 1 or fused):
             try:
+                sync()
                 model.decode_step(static_tok, pos_t)  # warm-up outside capture
                 torch.cuda.synchronize(dev)
                 graph = torch.cuda.CUDAGraph()
@@ -627,7 +630,9 @@ def run_decoder_suite(args):
         step_ms = decode_ms / steps
         print(json.dumps({
             "suite": "decoder", "n_gpus": world, "layers": cfg.num_hidden_layers, "batch": B, "seqlen": S,
-            "decode_steps": steps, "parallelism": f"tp{world}: qkv/gate_up column-parallel, o/down row-parallel + NCCL all-reduce",
+            "decode_steps": steps, "parallelism": f"tp{world}: qkv/gate_up column-parallel, o/down row-parallel + "
+                           + ("all-reduce fused into the decode GEMM over peer memory (NCCL in prefill)" if fused
+                              else "NCCL all-reduce"),
             "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(B * S / prefill_ms * 1e3, 1),
             "decode_ms_per_step": round(step_ms, 3), "decode_tokens_per_s": round(B / step_ms * 1e3, 1),
             "decode_launch": "CUDA graph" if graph is not None else "eager",
@@ -806,6 +811,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seqlen", type=int, default=2048)
     ap.add_argument("--decode-steps", type=int, default=128)
+    ap.add_argument("--fused-allreduce", action="store_true",
+                    help="decoder suite, N>1: sum row-parallel partial outputs inside the decode GEMM over peer memory")
     ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp", "decoder"], help="extra measurement suites")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup

@@ -42,6 +42,14 @@ _vp, _i, _i64, _sz = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_size_t
 _hp = _c.POINTER(HadamardDesc)
 
 # name -> (restype, argtypes); must list every symbol the header declares
+class AllReduceCtx(ctypes.Structure):
+    """dq_allreduce_ctx of the header."""
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("buf_ptrs", ctypes.c_void_p * 8), ("flag_ptrs", ctypes.c_void_p * 8),
+                ("seq", ctypes.c_void_p), ("buf_capacity_floats", ctypes.c_uint64),
+                ("flag_units", ctypes.c_uint64)]
+
+
 SIGNATURES = {
     "dq_init": (_i, [_i]),
     "dq_last_error_string": (_c.c_char_p, []),
@@ -64,6 +72,7 @@ SIGNATURES = {
     "dq_gemm_w4a4_int4_workspace_bytes": (_sz, [_i, _i, _i]),
     "dq_gemm_w4a4_int4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),
+    "dq_gemm_w4a4_int4_ar": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
     "dq_gemm_w4a4_int4_acc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "dq_linear_w4a4_int4_scratch_bytes": (_sz, [_i, _i, _i]),
     "dq_linear_w4a4_int4": (_i, [_vp, _i64, _vp, _hp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _sz, _vp]),

@@ -85,6 +85,7 @@ int init_act_quant_kernels();
 int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count);
 int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                      const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
-                     int tok, int split, cudaStream_t stream, DeviceState* st);
+                     int tok, int split, cudaStream_t stream, DeviceState* st,
+                     const dq_allreduce_ctx* ctx = nullptr);
 
 }  // namespace dq

@@ -608,3 +608,21 @@ extern "C" int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packe
   return launch<128, true>(codes, nullptr, w_packed, nullptr, nullptr, M, N, K, nullptr,
                            DQ_DTYPE_F32, acc, 1, s, st);
 }
+
+extern "C" int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                    const void* sw_t, const float* r, int M, int N, int K, int G,
+                                    void* y, int y_dtype, void* stream,
+                                    const dq_allreduce_ctx* ctx) {
+  DeviceState* st = current_state();
+  if (st == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  int rc = check_gemm_args(codes, w_packed, M, N, K, G);
+  if (rc != DQ_OK) return rc;
+  DQ_REQUIRE(sx != nullptr && sw_t != nullptr && y != nullptr, DQ_ERR_NULL, "null sx / sw_t / y");
+  DQ_REQUIRE(M <= 16, DQ_ERR_UNSUPPORTED, "the fused all-reduce covers decode batches (M <= 16), got M=%d", M);
+  const int tok = (M <= 8) ? 8 : 16;
+  const int total_groups = K / kGroup;
+  const int split = gemv_pick_split((N + kBN - 1) / kBN, total_groups, tok, st->sm_count);
+  return launch_gemv_int4(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, tok, split,
+                          static_cast<cudaStream_t>(stream), st, ctx);
+}

@@ -52,7 +52,42 @@ struct VCfg {
   static constexpr int smem_bytes(int stages) { return stages * kStage + kBarBytes + 1024; }
 };
 
-enum { VSITE_PRODUCER = 21, VSITE_COMPUTE = 22 };
+enum { VSITE_PRODUCER = 21, VSITE_COMPUTE = 22, VSITE_ALLREDUCE = 23 };
+
+// Cross-GPU all-reduce fused into the epilogue (row-parallel linears under tensor parallelism).
+// Every rank runs the same launch on its K slice.  A CTA that has finished its rows of an output
+// tile writes them (already scaled by r[n] * sx[m]) to its rank's exchange buffer, raises a flag
+// on every peer, waits - bounded - for the peers' flags of the same (tile, split) unit, then sums
+// the ranks' contributions in rank order through plain peer loads and stores the final rows.
+// Buffers alternate with the parity of a per-rank call counter that a one-thread kernel bumps
+// after each launch, so a rank that is already in the next call never overwrites data a slower
+// peer is still reading.  No NCCL, no multicast; the waits give up after about half a second.
+struct ArDev {
+  float* bufs[8];        // exchange buffer of every rank (2 * cap floats each), peer-mapped
+  uint32_t* flags[8];    // flag array of every rank: [unit][8]
+  const uint32_t* seq;   // this rank's call counter
+  int rank, world;
+  uint32_t cap;          // floats per parity half
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_relaxed_sys_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__global__ void ar_bump_kernel(uint32_t* seq) { *seq = *seq + 1u; }
 
 __device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -68,7 +103,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
                       const float* __restrict__ r, const float* __restrict__ sx,
                       void* __restrict__ y, int y_bf16, int M, int N, int K, int groups_per_split,
-                      int split_k, int stages, int* status) {
+                      int split_k, int stages, int* status, const ArDev ar) {
   using C = VCfg<NT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -247,11 +282,11 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     }
     // accumulator fragment: c0/c1 = (row, tokens 2t, 2t+1), c2/c3 = (row + 8, same tokens)
     if constexpr (kVSets == 1) {
-      if (split_k > 1) asm volatile("bar.sync 1, 256;" ::: "memory");  // ring reused as exchange tile
+      if (split_k > 1 || ar.world > 1) asm volatile("bar.sync 1, 256;" ::: "memory");  // ring reused as exchange tile
     }
     if (set == 1) {
       // nothing left to do for the second set
-    } else if (split_k == 1) {
+    } else if (split_k == 1 && ar.world <= 1) {
 #pragma unroll
       for (int hrow = 0; hrow < 2; ++hrow) {
         const int n = n0 + row + 8 * hrow;
@@ -287,17 +322,24 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     }
   }
 
-  // -------------------------------------------------------------------- split-K reduction
-  if (split_k > 1) {
+  // -------------------------------------------------------------------- split-K / cross-GPU reduction
+  if (split_k > 1 || ar.world > 1) {
     __syncwarp();
     cluster_sync_all();
     if (warp < 8) {  // 256 threads finish this CTA's share of the tile
-      const uint32_t rank = cluster_ctarank();
+      const uint32_t crank = cluster_ctarank();
       const int rows = C::TOK / split_k;  // token rows of the tile this CTA finishes
       const int c4 = tid & 31;            // float4 column
       const uint32_t red_base = smem_u32(smem);
+      uint32_t seq = 0;
+      float* my_buf = nullptr;
+      if (ar.world > 1) {
+        grid_dep_wait();  // the call counter is bumped by the kernel before this one's prerequisites
+        seq = *ar.seq;
+        my_buf = ar.bufs[ar.rank] + static_cast<size_t>(seq & 1u) * ar.cap;
+      }
       for (int rr = tid >> 5; rr < rows; rr += 8) {
-        const int m = static_cast<int>(rank) * rows + rr;
+        const int m = static_cast<int>(crank) * rows + rr;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         const uint32_t off = static_cast<uint32_t>((m * kVBN + c4 * 4) * 4);
         for (int p = 0; p < split_k; ++p) {
@@ -306,18 +348,74 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
         if (m < M) {
           const float sm = sx[m];
-          const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+          float vals[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int n = n0 + c4 * 4 + u;
-            if (n < N) {
-              const float rn = (r != nullptr) ? r[n] : 1.f;
-              const float val = vals[u] * (rn * sm);
-              if (y_bf16)
-                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                    __float2bfloat16_rn(val);
-              else
-                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+            const float rn = (n < N && r != nullptr) ? r[n] : 1.f;
+            vals[u] = (n < N) ? vals[u] * (rn * sm) : 0.f;
+          }
+          if (ar.world > 1) {
+            // N is a multiple of 4 in this mode (checked on the host): aligned float4 store
+            if (n0 + c4 * 4 < N)
+              *reinterpret_cast<float4*>(my_buf + static_cast<size_t>(m) * N + n0 + c4 * 4) =
+                  make_float4(vals[0], vals[1], vals[2], vals[3]);
+          } else {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int n = n0 + c4 * 4 + u;
+              if (n < N) {
+                if (y_bf16)
+                  reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
+                      __float2bfloat16_rn(vals[u]);
+                else
+                  reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = vals[u];
+              }
+            }
+          }
+        }
+      }
+      if (ar.world > 1) {
+        const uint32_t epoch = seq + 1u;
+        const uint32_t unit = blockIdx.x * static_cast<uint32_t>(split_k) + crank;
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // all rows of this CTA are in the buffer
+        if (tid == 0) {
+          __threadfence_system();
+          for (int p = 0; p < ar.world; ++p)
+            if (p != ar.rank) st_release_sys(ar.flags[p] + unit * 8u + ar.rank, epoch);
+        }
+        if (tid < ar.world && tid != ar.rank) {
+          const uint32_t* f = ar.flags[ar.rank] + unit * 8u + tid;
+          const long long t_start = clock64();
+          while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
+            if (clock64() - t_start > (1ll << 30) || *abort_flag != 0) {
+              *abort_flag = VSITE_ALLREDUCE;
+              break;
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (*abort_flag == 0) {
+          for (int rr = tid >> 5; rr < rows; rr += 8) {
+            const int m = static_cast<int>(crank) * rows + rr;
+            const int nb = n0 + c4 * 4;
+            if (m < M && nb < N) {
+              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int p = 0; p < ar.world; ++p) {  // rank order: every rank forms the same sum
+                const float* src = ar.bufs[p] + static_cast<size_t>(seq & 1u) * ar.cap +
+                                   static_cast<size_t>(m) * N + nb;
+                const float4 v = ld_relaxed_sys_f4(src);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+              }
+              const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                if (y_bf16)
+                  reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + nb + u] =
+                      __float2bfloat16_rn(vals[u]);
+                else
+                  reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + nb + u] = vals[u];
+              }
             }
           }
         }
@@ -362,7 +460,8 @@ int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count) {
 template <int NT>
 static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                          const __half* sw_t, const float* r, int M, int N, int K, void* y,
-                         int y_dtype, int split, cudaStream_t stream, DeviceState* st) {
+                         int y_dtype, int split, cudaStream_t stream, DeviceState* st,
+                         const ArDev& ar) {
   using C = VCfg<NT>;
   CUtensorMap tm_x;
   int rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, C::kXPitch, C::kXRows, CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -398,7 +497,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT>, w_packed, tm_x, r, sx, y,
                                      y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, gps, split,
-                                     stages, st->status_dev);
+                                     stages, st->status_dev, ar);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemv_w4a4_int4 launch failed (tokens=%d split=%d): %s", C::TOK,
                      split, cudaGetErrorString(e));
@@ -408,14 +507,44 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
 // tok: token capacity of the variant (8, 16 or 32) >= M.
 int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                      const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
-                     int tok, int split, cudaStream_t stream, DeviceState* st) {
+                     int tok, int split, cudaStream_t stream, DeviceState* st,
+                     const dq_allreduce_ctx* ctx) {
   const __half* swp = static_cast<const __half*>(sw_t);
+  ArDev ar = {};
+  ar.world = 1;
+  if (ctx != nullptr && ctx->world > 1) {
+    DQ_REQUIRE(ctx->world <= 8 && ctx->rank >= 0 && ctx->rank < ctx->world, DQ_ERR_SHAPE,
+               "bad all-reduce context: rank %d of %d", ctx->rank, ctx->world);
+    DQ_REQUIRE(N % 4 == 0, DQ_ERR_SHAPE, "fused all-reduce needs N %% 4 == 0 (N=%d)", N);
+    DQ_REQUIRE(static_cast<uint64_t>(M) * N <= ctx->buf_capacity_floats, DQ_ERR_WORKSPACE,
+               "M*N=%lld exceeds the exchange buffer capacity %llu", (long long)M * N,
+               (unsigned long long)ctx->buf_capacity_floats);
+    DQ_REQUIRE(static_cast<uint64_t>((N + kVBN - 1) / kVBN) * split <= ctx->flag_units, DQ_ERR_WORKSPACE,
+               "too many (tile, split) units for the flag array");
+    for (int p = 0; p < ctx->world; ++p) {
+      DQ_REQUIRE(ctx->buf_ptrs[p] != nullptr && ctx->flag_ptrs[p] != nullptr, DQ_ERR_NULL,
+                 "null peer pointer for rank %d", p);
+      ar.bufs[p] = static_cast<float*>(ctx->buf_ptrs[p]);
+      ar.flags[p] = static_cast<uint32_t*>(ctx->flag_ptrs[p]);
+    }
+    DQ_REQUIRE(ctx->seq != nullptr, DQ_ERR_NULL, "null call counter");
+    ar.seq = static_cast<const uint32_t*>(ctx->seq);
+    ar.rank = ctx->rank;
+    ar.world = ctx->world;
+    ar.cap = static_cast<uint32_t>(ctx->buf_capacity_floats);
+  }
+  int rc;
   switch (tok) {
-    case 8: return launch_gemv_t<1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st);
-    case 16: return launch_gemv_t<2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st);
-    case 32: return launch_gemv_t<4>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st);
+    case 8: rc = launch_gemv_t<1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar); break;
+    case 16: rc = launch_gemv_t<2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar); break;
+    case 32: rc = launch_gemv_t<4>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar); break;
     default: return set_error(DQ_ERR_SHAPE, "register-path token capacity must be 8/16/32 (got %d)", tok);
   }
+  if (rc == DQ_OK && ar.world > 1) {
+    ar_bump_kernel<<<1, 1, 0, stream>>>(static_cast<uint32_t*>(ctx->seq));
+    DQ_CHECK_CUDA(cudaGetLastError());
+  }
+  return rc;
 }
 
 }  // namespace dq

@@ -15,7 +15,8 @@ reference leaves them to HF); the seven linears of a layer are four fused W4A4 c
 
 With tp > 1 the online Hadamards and the per-token activation scales are taken over the rank's
 own slice of the sharded axis (a valid rotation / scaling per shard, no collective); the only
-collectives are the two all-reduces per layer (NCCL).
+collectives are the two all-reduces per layer: NCCL in prefill; in decode either NCCL or, with
+fused_allreduce, a sum over NVLink peer memory inside the GEMM kernel's epilogue.
 """
 from __future__ import annotations
 
@@ -70,12 +71,18 @@ class W4A4Linear:
             self._scratch[M] = buf
         return buf
 
-    def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16, ar=None) -> torch.Tensor:
+        """ar: an ops.AllReduceContext -> the cross-rank sum happens inside the GEMM (M <= 16)."""
+        if ar is not None:
+            codes, sx = ops.quant_act_int4(x, self.a, self.had, False)
+            return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
         return ops.linear_w4a4_int4(x, self.a, self.had, self.pw, self.r, out_dtype=out_dtype,
                                     scale_fp16=False, scratch=self._scratch_for(x.shape[0], x.device))
 
-    def gated(self, gate: torch.Tensor, up: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+    def gated(self, gate: torch.Tensor, up: torch.Tensor, out_dtype=torch.bfloat16, ar=None) -> torch.Tensor:
         codes, sx = ops.quant_act_int4_gated(gate, up, self.a, self.had, False)
+        if ar is not None:
+            return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
         return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype)
 
 
@@ -125,7 +132,7 @@ class DecoderLayer:
         self.k_cache = torch.zeros(shape, dtype=torch.bfloat16, device=device)
         self.v_cache = torch.zeros(shape, dtype=torch.bfloat16, device=device)
 
-    def forward(self, x, cos, sin, pos0: int, pos_t: Optional[torch.Tensor], mask, group):
+    def forward(self, x, cos, sin, pos0: int, pos_t: Optional[torch.Tensor], mask, group, ar=None):
         """x [B, S, hidden] bf16.  Prefill: pos0 = 0, pos_t None (causal).  Decode: S = 1, the
         cache position comes from the device tensor pos_t and `mask` hides the unwritten tail."""
         cfg = self.cfg
@@ -149,22 +156,30 @@ class DecoderLayer:
             attn = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask,
                                                   enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
-        o = self.o(attn)
-        if self.tp > 1:
+        fused = ar if (ar is not None and self.tp > 1 and B * S <= 16) else None
+        o = self.o(attn, ar=fused)
+        if self.tp > 1 and fused is None:
             dist.all_reduce(o, group=group)
         x = x + o.reshape(B, S, Hd)
         h = _rms_norm(x, self.ln2, cfg.rms_norm_eps)
         gu = self.gate_up(h.reshape(B * S, Hd))
-        d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :])
-        if self.tp > 1:
+        d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :], ar=fused)
+        if self.tp > 1 and fused is None:
             dist.all_reduce(d, group=group)
         return x + d.reshape(B, S, Hd)
 
 
 class Decoder:
-    def __init__(self, cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, group=None):
+    def __init__(self, cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, group=None,
+                 fused_allreduce: bool = False):
+        """fused_allreduce: decode steps sum the row-parallel linears' partial outputs inside the
+        GEMM kernel over NVLink peer memory instead of calling NCCL (prefill keeps NCCL)."""
         assert cfg.num_key_value_heads % tp == 0 and cfg.intermediate_size % (tp * 128) == 0
         self.cfg, self.tp, self.rank, self.group, self.device = cfg, tp, rank, group, device
+        self.ar = None
+        if fused_allreduce and tp > 1:
+            self.ar = ops.AllReduceContext(group if group is not None else dist.group.WORLD, device,
+                                           capacity_floats=16 * cfg.hidden_size)
         gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)  # each rank: its own shard
         shared = torch.Generator(device=device).manual_seed(seed)             # replicated tensors
         self.embed = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=shared, device=device) * 0.02).to(torch.bfloat16)
@@ -197,7 +212,7 @@ class Decoder:
         sin = self.sin.index_select(0, pos_t)
         mask = (torch.arange(self.max_len, device=self.device) <= pos_t).view(1, 1, 1, self.max_len)
         for layer in self.layers:
-            x = layer.forward(x, cos, sin, 0, pos_t, mask, self.group)
+            x = layer.forward(x, cos, sin, 0, pos_t, mask, self.group, self.ar)
         x = _rms_norm(x[:, 0], self.norm, self.cfg.rms_norm_eps)
         return x @ self.lm_head.T
 

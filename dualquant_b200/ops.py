@@ -184,6 +184,65 @@ def gemm_w4a4_int4(codes: torch.Tensor, sx: torch.Tensor, pw: PackedInt4Weight,
     return out
 
 
+class AllReduceContext:
+    """Peer-mapped exchange buffers of the all-reduce fused into the decode GEMM
+    (dq_gemm_w4a4_int4_ar).  Built once per process group from torch symmetric memory: one
+    allocation per rank holding 2 * capacity fp32 (double-buffered partial outputs) followed by
+    the flag array; every rank maps every other rank's allocation over NVLink.  All ranks must
+    construct it collectively and then issue the same sequence of gemm_w4a4_int4_ar calls."""
+
+    FLAG_UNITS = 1024
+
+    def __init__(self, group, device, capacity_floats: int = 16 * 16384):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the fused all-reduce covers one NVLink domain of at most 8 ranks")
+        cap = (int(capacity_floats) + 63) // 64 * 64
+        words = 2 * cap + self.FLAG_UNITS * 8
+        self._mem = symm.empty(words, dtype=torch.float32, device=device)
+        self._mem.zero_()
+        self._handle = symm.rendezvous(self._mem, group)
+        self.seq = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group, device_ids=[device.index])  # every rank's flags are zero from here on
+        ctx = _lib.AllReduceCtx()
+        ctx.world, ctx.rank = self.world, self.rank
+        for p in range(self.world):
+            base = int(self._handle.buffer_ptrs[p])
+            ctx.buf_ptrs[p] = base
+            ctx.flag_ptrs[p] = base + 2 * cap * 4
+        ctx.seq = self.seq.data_ptr()
+        ctx.buf_capacity_floats = cap
+        ctx.flag_units = self.FLAG_UNITS
+        self.capacity = cap
+        self._ctx = ctx
+        self._ref = ctypes.byref(ctx)
+
+
+def gemm_w4a4_int4_ar(codes: torch.Tensor, sx: torch.Tensor, pw: PackedInt4Weight,
+                      r: Optional[torch.Tensor], ctx: AllReduceContext, out_dtype=torch.float32,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-parallel int4 GEMM of a decode batch (M <= 16): this rank's K slice, summed over the
+    ranks of `ctx` inside the kernel; every rank gets the full [M, N] result."""
+    lib = _prep(codes)
+    M, K = codes.shape
+    if K != pw.K:
+        raise ValueError(f"K mismatch: activations {K}, weight {pw.K}")
+    if out is None:
+        out = torch.empty(M, pw.N, dtype=out_dtype, device=codes.device)
+    ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    _lib.check(lib.dq_gemm_w4a4_int4_ar(_ptr(codes), _ptr(sx), _ptr(pw.w_packed), _ptr(pw.sw_t), _ptr(r),
+                                        M, pw.N, K, pw.group, _ptr(out), ydt, _stream(codes.device),
+                                        ctx._ref), "dq_gemm_w4a4_int4_ar")
+    return out
+
+
 def gemm_w4a4_int4_acc(codes: torch.Tensor, pw: PackedInt4Weight) -> torch.Tensor:
     """Test hook: raw per-group int32 accumulators [M, N, K/G]."""
     lib = _prep(codes)

@@ -226,6 +226,34 @@ DQ_API int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const uint
                          int y_dtype, void* workspace, size_t workspace_bytes, void* stream,
                          int token_tile, int split_k);
 
+/*
+ * Peer-memory context of the all-reduce fused into dq_gemm_w4a4_int4_ar (host struct; every
+ * pointer is a device pointer valid in THIS process: rank p's buffers mapped here, e.g. with
+ * torch.distributed._symmetric_memory).  buf_ptrs[p]: 2 * buf_capacity_floats fp32;
+ * flag_ptrs[p]: flag_units * 8 uint32, zero-initialised once; seq: this rank's own uint32 call
+ * counter, zero-initialised.  All ranks must issue the same sequence of _ar calls.
+ */
+typedef struct dq_allreduce_ctx {
+  int32_t world, rank;
+  void* buf_ptrs[8];
+  void* flag_ptrs[8];
+  void* seq;
+  uint64_t buf_capacity_floats;
+  uint64_t flag_units;
+} dq_allreduce_ctx;
+
+/*
+ * Row-parallel linear under tensor parallelism: each rank passes its K slice (codes, weights),
+ * the partial products are summed across ranks inside the kernel's epilogue over NVLink peer
+ * memory (bounded flag waits, sum in rank order, no NCCL, no multicast) and every rank receives
+ * the full Y.  Replaces "F.linear then all-reduce" of a Megatron row-parallel layer; the
+ * reference has no multi-GPU code.  Decode batches only (M <= 16); ctx null or world 1 = plain
+ * GEMM.  Issues one extra one-thread kernel per call (call counter).
+ */
+DQ_API int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                const void* sw_t, const float* r, int M, int N, int K, int G,
+                                void* y, int y_dtype, void* stream, const dq_allreduce_ctx* ctx);
+
 /* Test hook: the raw per-group int32 accumulators acc[M, N, K/G] (no scales applied). */
 DQ_API int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packed, int M, int N, int K,
                           int G, int32_t* acc, void* stream);
