@@ -41,6 +41,8 @@ EncodeTiledFn encode_tiled_fn();
 int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
                     uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows,
                     CUtensorMapSwizzle swizzle);
+int make_tmap_x_groups(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
+                       uint32_t box_rows, uint32_t box_groups);
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

@@ -60,6 +60,29 @@ int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint
   return DQ_OK;
 }
 
+// Activation codes [rows][row_bytes] seen as (128-byte group chunk, row, group): one box is
+// `box_groups` consecutive K groups of `box_rows` rows, laid out in shared memory as
+// [group][row][128 B] (each group block is one 128B-swizzled UMMA operand tile).
+int make_tmap_x_groups(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
+                       uint32_t box_rows, uint32_t box_groups) {
+  if (g_encode == nullptr) return set_error(DQ_ERR_NOT_INIT, "tensor-map encoder not resolved");
+  cuuint64_t dims[3] = {128, rows, row_bytes / 128};
+  cuuint64_t strides[2] = {row_bytes, 128};
+  cuuint32_t box[3] = {128, box_rows, box_groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(DQ_ERR_CUDA,
+                     "cuTensorMapEncodeTiled (3-D) failed (%d): base=%p row_bytes=%llu rows=%llu "
+                     "box=%ux%u",
+                     (int)r, base, (unsigned long long)row_bytes, (unsigned long long)rows,
+                     box_rows, box_groups);
+  return DQ_OK;
+}
+
 }  // namespace dq
 
 using namespace dq;

@@ -8,18 +8,23 @@
 // drained once per group, so the per-group partial sums are exact.  Each epilogue thread owns
 // one weight row and therefore one scalar group scale per stage.
 //
-// Warp roles in a 448-thread CTA:
-//   warps 0-3   unpack: packed int4 tile (TMA-staged, 8 KB) -> int8 tile in the 128B-swizzled
-//               K-major layout UMMA reads (16 KB).  Nibbles are two's complement; a byte is
-//               expanded as (w << 4) & 0xF0.. / w & 0xF0.., i.e. 16 * code, and the 1/16 is folded
-//               into the group scale (exact: power of two).
-//   warps 4-11  epilogue: tcgen05.ld of the group accumulator, run += float(acc) * sw, final scale
-//               by r[n]*sx[m], store / split-K reduction.
-//   warp 12     TMA producer: packed weight tiles (contiguous 8 KB bulk copies) and int8
-//               activation tiles (tiled, 128B swizzle).
-//   warp 13     TMEM allocation, UMMA issue.  Every tcgen05 / mbarrier instruction this warp
-//               executes costs tens of cycles of issue latency and they are all serial, so the
-//               protocol is built to give it one wait, four UMMAs and one commit per group.
+// Warp roles (E = 8 epilogue warps, 16 for the 128-token tile):
+//   warps 0-3        unpack: packed int4 tile (TMA-staged, 8 KB) -> int8 tile in the 128B-swizzled
+//                    K-major layout UMMA reads (16 KB).  Nibbles are two's complement; a byte is
+//                    expanded as (w << 4) & 0xF0.. / w & 0xF0.., i.e. 16 * code, and the 1/16 is
+//                    folded into the group scale (exact: power of two).  One warp expands a whole
+//                    group, so four consecutive groups are in work at once.
+//   warps 4..3+E     epilogue: tcgen05.ld of the group accumulator in two column chunks, the load
+//                    of a chunk overlapping the arithmetic of the one before (also across groups);
+//                    run += float(acc) * sw; final scale by r[n]*sx[m], store / split-K reduction.
+//   warp 4+E         TMA producer: packed weight tiles (contiguous 8 KB bulk copies) and int8
+//                    activation tiles (tiled, 128B swizzle).
+//   warps 5+E(,6+E)  UMMA issue (two warps, even / odd groups, for the 128-token tile; one
+//                    otherwise); warp 5+E also owns the TMEM allocation.
+//                    Every tcgen05 / mbarrier instruction costs tens of cycles of issue latency on
+//                    the thread that executes it; one wait pair, four UMMAs and two commits per
+//                    group come to ~400 cycles, more than the UMMAs of a group take to execute,
+//                    hence two issuing threads.
 //
 // Split-K (decode shapes): the CTAs that share an output tile form a thread-block cluster along
 // grid z; partial tiles are exchanged through distributed shared memory and summed in rank
@@ -53,47 +58,91 @@ long long* g_trace = nullptr;
 #endif
 
 constexpr int kBN = 128;           // weight rows per CTA tile (UMMA M)
-constexpr int kThreads = 448;
-constexpr int kUnpackThreads = 128;
+
 constexpr int kWpBytes = kBN * kGroup / 2;  // packed stage: 8 KB
 constexpr int kWaBytes = kBN * kGroup;      // unpacked stage: 16 KB
 
+// {SP, SX, XC} for token tiles 16 / 32 / 64 / 128
+#ifndef DQ_CFG_16
+#define DQ_CFG_16 4, 2, 4
+#endif
+#ifndef DQ_CFG_32
+#define DQ_CFG_32 4, 2, 2
+#endif
+#ifndef DQ_CFG_64
+#define DQ_CFG_64 4, 2, 1
+#endif
+#ifndef DQ_CFG_128
+#define DQ_CFG_128 12, 4, 1
+#endif
+constexpr int kCfgTab[4][3] = {{DQ_CFG_16}, {DQ_CFG_32}, {DQ_CFG_64}, {DQ_CFG_128}};
+constexpr int kUnpackWarps = 4;
+
 template <int TN>
 struct Cfg {
-  // XC: weight groups covered by one activation stage (one barrier round trip per XC groups).
-  static constexpr int XC = (TN <= 32) ? 4 : (TN == 64) ? 2 : 1;
-  // Stage counts.  The packed-weight ring is as deep as shared memory allows: at decode shapes
-  // the kernel is bound by bytes in flight per SM (two CTAs per SM for TN <= 64).
-  static constexpr int SP = (TN == 16) ? 7 : (TN == 128) ? 10 : 5;
-  static constexpr int SX = (TN == 128) ? 4 : 2;
-  static constexpr int kXBytes = TN * kGroup;          // one group of activation codes
-  static constexpr int kXStageBytes = XC * kXBytes;
+  // NB unpacked weight buffers = TMEM accumulators in flight (buffer b and accumulator b of a
+  // group travel together through the ready/done barriers), SP packed-weight stages, SX
+  // activation stages of XC groups each (one 3-D TMA copy per stage: every instruction the
+  // producer thread issues costs it ~100 cycles).  Two CTAs per SM for TN <= 64.
+  static constexpr int kRow = (TN == 16) ? 0 : (TN == 32) ? 1 : (TN == 64) ? 2 : 3;
+  static constexpr int NB = 4;
+  static constexpr int SP = kCfgTab[kRow][0];
+  static constexpr int SX = kCfgTab[kRow][1];
+  static constexpr int XC = kCfgTab[kRow][2];
+  // A role that is split over several warps by group index must find every barrier it waits on
+  // owned by one warp: waits are by phase parity, so a warp may never be a whole phase ahead of
+  // the barrier's previous user.
+  static_assert(NB % kUnpackWarps == 0 && SP % kUnpackWarps == 0, "stage and buffer rings: multiples of 4");
+  // UMMA-issuing warps: two for the 128-token tile (the issue cost of a group exceeds its UMMA
+  // time there); one otherwise, which keeps two 448-thread CTAs per SM at 72 registers.
+  static constexpr int kIssuers = (TN == 128) ? 2 : 1;
+  static_assert(NB % kIssuers == 0 && SX % kIssuers == 0, "buffer and activation rings: even");
+  static_assert(kIssuers == 1 || XC == 1, "two issuing warps: one group per activation stage");
+  static constexpr int EW = (TN == 128) ? 16 : 8;       // epilogue warps
+  static constexpr int kProducerWarp = kUnpackWarps + EW;
+  static constexpr int kIssuerWarp0 = kProducerWarp + 1;
+  // The 128-token tile runs one CTA per SM and re-balances registers between warpgroups
+  // (unpack 56, epilogue 96, producer/issuers 40 of the 80 the launch grants each thread), which
+  // needs whole warpgroups: the CTA is padded to 24 warps; the last one is a second producer
+  // (activation tiles), so that neither producing thread limits the group rate.
+  static constexpr bool kRebalance = (TN == 128);
+  static constexpr int kThreads = kRebalance ? 768 : 32 * (kIssuerWarp0 + kIssuers);
+  static constexpr int kXProducerWarp = kRebalance ? 23 : kProducerWarp;
+  static_assert(!kRebalance || (kIssuerWarp0 + kIssuers <= 24 && kProducerWarp % 4 == 0), "warpgroup layout");
+  static constexpr int kReadyCount = EW + 1;            // epilogue warps + the unpacking warp
+  static constexpr int kXBytes = TN * kGroup;           // one group of activation codes
   static constexpr int kMinCtas = (TN <= 64) ? 2 : 1;
-  static constexpr int kOffA = 0;                      // 2 unpacked weight buffers
-  static constexpr int kOffX = kOffA + 2 * kWaBytes;
+  static constexpr int kOffA = 0;                       // NB unpacked weight buffers
+  static constexpr int kOffX = kOffA + NB * kWaBytes;
+  static constexpr int kXStageBytes = XC * kXBytes;
   static constexpr int kOffP = kOffX + SX * kXStageBytes;
   static constexpr int kOffBar = kOffP + SP * kWpBytes;
-  static constexpr int kNumBars = 2 * SP + 2 * SX + 4;
-  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;  // + align slack
-  static constexpr int kTmemCols = (2 * TN < 32) ? 32 : 2 * TN;
-  static constexpr int CPW = TN / 2;  // accumulator columns per epilogue warp
+  static constexpr int kNumBars = 2 * SP + 2 * SX + 2 * NB;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static constexpr int kAccCols = NB * TN;
+  static constexpr int kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128
+                                   : kAccCols <= 256 ? 256 : 512;
+  static_assert(kTmemCols * kMinCtas <= 512, "TMEM columns per SM");
+  static_assert((kSmemBytes + 1024) * kMinCtas <= 233472, "shared memory per SM");
+  static constexpr int CPW = TN / (EW / 4);             // accumulator columns per epilogue warp
+  static constexpr int CH = 8;                          // columns per tcgen05.ld
+  static constexpr int NCH = CPW / CH;                  // chunks per group: 1, 2 or 4
   static_assert(TN * kBN * 4 <= kOffBar, "split-K exchange tile must fit in the stage buffers");
 };
 
 // site codes stored in the status word when a bounded wait expires
-enum { SITE_TMA = 1, SITE_UNPACK_FULL, SITE_UNPACK_FREE, SITE_MMA_READY, SITE_MMA_X, SITE_EPI };
+enum { SITE_TMA = 1, SITE_UNPACK_FULL, SITE_UNPACK_FREE, SITE_MMA_READY, SITE_MMA_X, SITE_EPI,
+       SITE_SMEM_ALIGN };
 
-// Barrier protocol (b = i & 1 selects the unpacked-weight buffer and the TMEM accumulator):
-//   full_p / empty_p [SP]  packed weight ring   producer -> unpack warps (one arrival per warp)
+// Barrier protocol (b = i % NB selects the unpacked-weight buffer and the TMEM accumulator):
+//   full_p / empty_p [SP]  packed weight ring   producer -> the unpacking warp of the group
 //   full_x / empty_x [SX]  activation ring      producer -> UMMA issuer  (tcgen05.commit)
-//   ready[b]               buffer b written by the 4 unpack warps AND accumulator b drained by the
-//                          8 epilogue warps (12 arrivals; the epilogue pre-arrives once)
+//   ready[b]               buffer b written by its unpacking warp AND accumulator b drained by
+//                          all epilogue warps (EW + 1 arrivals; the epilogue pre-arrives once)
 //   done[b]                UMMAs of the group finished (tcgen05.commit): the epilogue may read
-//                          accumulator b, the unpack warps may overwrite buffer b
-// so the single UMMA-issuing thread executes one wait, four UMMAs and one commit per group
-// (plus one wait and one commit per XC groups for the activation ring).
+//                          accumulator b, the unpack warp may overwrite buffer b
 template <int TN, bool DUMP>
-__global__ void __launch_bounds__(kThreads, Cfg<TN>::kMinCtas)
+__global__ void __launch_bounds__(Cfg<TN>::kThreads, Cfg<TN>::kMinCtas)
 gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
                       const __half* __restrict__ sw_t, const float* __restrict__ r,
@@ -101,17 +150,23 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       int32_t* __restrict__ acc_dump, int M, int N, int K, int groups_per_split,
                       int split_k, int w_stream_once, int* status DQ_TRACE_PARAM) {
   using C = Cfg<TN>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  // The 128-byte swizzle of the UMMA operands needs the buffers on 1 KB boundaries.  The kernel has
+  // no static shared memory, so the dynamic window starts on one; if it ever does not, every CTA
+  // reports that and leaves before touching a barrier.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, SITE_SMEM_ALIGN);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
   uint64_t* full_p = bars;
   uint64_t* empty_p = full_p + C::SP;
   uint64_t* full_x = empty_p + C::SP;
   uint64_t* empty_x = full_x + C::SX;
   uint64_t* ready = empty_x + C::SX;
-  uint64_t* done = ready + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
+  uint64_t* done = ready + C::NB;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + C::NB);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
@@ -126,17 +181,17 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   const int ng = (g_end > g_begin) ? (g_end - g_begin) : 0;
 
   if (tid == 0) {
-    for (int i = 0; i < C::SP; ++i) { mbar_init(&full_p[i], 1); mbar_init(&empty_p[i], 4); }
+    for (int i = 0; i < C::SP; ++i) { mbar_init(&full_p[i], 1); mbar_init(&empty_p[i], 1); }
     for (int i = 0; i < C::SX; ++i) { mbar_init(&full_x[i], 1); mbar_init(&empty_x[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&ready[i], 12); mbar_init(&done[i], 1); }
+    for (int i = 0; i < C::NB; ++i) { mbar_init(&ready[i], C::kReadyCount); mbar_init(&done[i], 1); }
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 13) {
+  if (warp == C::kIssuerWarp0) {
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 12 && lane == 0) tma_prefetch_desc(&tm_x);
+  if (warp == C::kXProducerWarp && lane == 0) tma_prefetch_desc(&tm_x);
   grid_dep_launch_dependents();
   tc_fence_before();
   __syncthreads();
@@ -147,30 +202,50 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 #pragma unroll
   for (int j = 0; j < C::CPW; ++j) run[j] = 0.f;
 
-  if (warp < 4) {
+  if constexpr (C::kRebalance) {
+    if (warp < kUnpackWarps) {
+      setmaxnreg_dec<56>();
+    } else if (warp < C::kProducerWarp) {
+      setmaxnreg_inc<96>();
+    } else {
+      setmaxnreg_dec<40>();
+    }
+  }
+
+  if (warp < kUnpackWarps) {
     // ------------------------------------------------------------------ unpack warps
-    for (int i = 0; i < ng; ++i) {
-      const int sp = i % C::SP, b = i & 1;
+    // One warp expands a whole group (groups warp, warp + 4, ...): the four warps work on four
+    // consecutive groups at once, so the wait / expand / proxy-fence / arrive chain of a group,
+    // which is latency and not throughput, overlaps with that of its neighbours.
+    for (int i = warp; i < ng; i += kUnpackWarps) {
+      const int sp = i % C::SP, b = i % C::NB;
       if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
-      if (tid == 0) DQ_TR(0, i, 0);
-      if (!mbar_wait(&done[b], ((i >> 1) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
-      if (tid == 0) DQ_TR(0, i, 1);
+      if (lane == 0) DQ_TR(0, i, 0);
+      if (!mbar_wait(&done[b], ((i / C::NB) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
+      if (lane == 0) DQ_TR(0, i, 1);
       const uint8_t* src = smem + C::kOffP + sp * kWpBytes;
       uint8_t* dst = smem + C::kOffA + b * kWaBytes;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int id = tid + c * kUnpackThreads;  // 16-byte chunk of the packed tile
-        const int row = id >> 2, ch = id & 3;
-        const uint4 w = *reinterpret_cast<const uint4*>(src + id * 16);
-        uint4 lo, hi;
-        lo.x = (w.x << 4) & 0xF0F0F0F0u; hi.x = w.x & 0xF0F0F0F0u;
-        lo.y = (w.y << 4) & 0xF0F0F0F0u; hi.y = w.y & 0xF0F0F0F0u;
-        lo.z = (w.z << 4) & 0xF0F0F0F0u; hi.z = w.z & 0xF0F0F0F0u;
-        lo.w = (w.w << 4) & 0xF0F0F0F0u; hi.w = w.w & 0xF0F0F0F0u;
-        uint8_t* rowp = dst + row * 128;
-        const int sw = row & 7;
-        *reinterpret_cast<uint4*>(rowp + (((2 * ch) ^ sw) << 4)) = lo;
-        *reinterpret_cast<uint4*>(rowp + (((2 * ch + 1) ^ sw) << 4)) = hi;
+      for (int c8 = 0; c8 < 16; c8 += 8) {
+        uint4 wv[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          wv[c] = *reinterpret_cast<const uint4*>(src + (lane + (c8 + c) * 32) * 16);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int id = lane + (c8 + c) * 32;  // 16-byte chunk of the packed tile
+          const int row = id >> 2, ch = id & 3;
+          const uint4 w = wv[c];
+          uint4 lo, hi;
+          lo.x = (w.x << 4) & 0xF0F0F0F0u; hi.x = w.x & 0xF0F0F0F0u;
+          lo.y = (w.y << 4) & 0xF0F0F0F0u; hi.y = w.y & 0xF0F0F0F0u;
+          lo.z = (w.z << 4) & 0xF0F0F0F0u; hi.z = w.z & 0xF0F0F0F0u;
+          lo.w = (w.w << 4) & 0xF0F0F0F0u; hi.w = w.w & 0xF0F0F0F0u;
+          uint8_t* rowp = dst + row * 128;
+          const int sw = row & 7;
+          *reinterpret_cast<uint4*>(rowp + (((2 * ch) ^ sw) << 4)) = lo;
+          *reinterpret_cast<uint4*>(rowp + (((2 * ch + 1) ^ sw) << 4)) = hi;
+        }
       }
       fence_proxy_async_smem();  // each writer orders its own stores before the UMMA reads
       __syncwarp();
@@ -178,78 +253,113 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         mbar_arrive(&ready[b]);
         mbar_arrive(&empty_p[sp]);
       }
-      if (tid == 0) DQ_TR(0, i, 2);
+      if (lane == 0) DQ_TR(0, i, 2);
     }
-  } else if (warp < 12) {
+  } else if (warp < C::kProducerWarp) {
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;          // TMEM lane quarter this warp may read
-    const int h = (warp - 4) >> 2;   // which half of the token columns
+    const int h = (warp - kUnpackWarps) >> 2;  // which slice of the token columns
     const int n = n0 + q * 32 + lane;
     const bool n_ok = n < N;
-    if (lane == 0) {  // both accumulators start out free
-      mbar_arrive(&ready[0]);
-      mbar_arrive(&ready[1]);
+    if (lane == 0) {  // every accumulator starts out free
+#pragma unroll
+      for (int b = 0; b < C::NB; ++b) mbar_arrive(&ready[b]);
     }
     // Group scales of this thread's weight row, [row tile][group][128] in memory.  A new 256-byte
     // run is touched every stage, so loads are issued kScaleAhead stages early.
-    constexpr int kScaleAhead = 8;
-    const __half* sw_row = nullptr;
-    float sq[kScaleAhead];
+    // The ring holds the raw fp16 bits: converting at load time would make the warp wait for the
+    // load at once; the conversion happens when the group comes up.
+    constexpr int kScaleAhead = 4;
+    const unsigned short* sw_row = nullptr;
+    unsigned short sq[kScaleAhead];
 #pragma unroll
-    for (int d = 0; d < kScaleAhead; ++d) sq[d] = 0.f;
+    for (int d = 0; d < kScaleAhead; ++d) sq[d] = 0;
     if constexpr (!DUMP) {
-      sw_row = sw_t + (static_cast<size_t>(blockIdx.x) * total_groups + g_begin) * kBN + q * 32 + lane;
+      sw_row = reinterpret_cast<const unsigned short*>(sw_t) +
+               (static_cast<size_t>(blockIdx.x) * total_groups + g_begin) * kBN + q * 32 + lane;
 #pragma unroll
       for (int d = 0; d < kScaleAhead; ++d)
-        if (d < ng) sq[d] = __half2float(sw_row[static_cast<size_t>(d) * kBN]);
+        if (d < ng) sq[d] = __ldg(sw_row + static_cast<size_t>(d) * kBN);
     }
-    for (int i = 0; i < ng; ++i) {
-      const int b = i & 1;
-      const float s = sq[0] * 0.0625f;
-#pragma unroll
-      for (int d = 0; d + 1 < kScaleAhead; ++d) sq[d] = sq[d + 1];
-      if constexpr (!DUMP) {
-        if (i + kScaleAhead < ng)
-          sq[kScaleAhead - 1] = __half2float(sw_row[static_cast<size_t>(i + kScaleAhead) * kBN]);
-      }
-      if (!mbar_wait(&done[b], (i >> 1) & 1, abort_flag, SITE_EPI)) break;
-      if (tid == 128) DQ_TR(1, i, 0);
-      tc_fence_after();
+    auto ld_chunk = [&](int b, int c0, uint32_t* v) {
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                             static_cast<uint32_t>(b * TN + h * C::CPW);
-      constexpr int CH = (C::CPW < 32) ? C::CPW : (C::kMinCtas == 2 ? 16 : 32);  // columns per tcgen05.ld
+                             static_cast<uint32_t>(b * TN + h * C::CPW + c0);
+      tmem_ld_x8(taddr, v);
+    };
+    auto consume = [&](const uint32_t* v, int c0, int i, float s) {
+      if constexpr (DUMP) {
+        if (n_ok) {
 #pragma unroll
-      for (int c0 = 0; c0 < C::CPW; c0 += CH) {
-        uint32_t v[CH];
-        if constexpr (CH == 8) {
-          tmem_ld_x8(taddr + c0, v);
-        } else if constexpr (CH == 16) {
-          tmem_ld_x16(taddr + c0, v);
-        } else {
-          tmem_ld_x32(taddr + c0, v);
+          for (int j = 0; j < C::CH; ++j) {
+            const int m = t0 + h * C::CPW + c0 + j;
+            if (m < M)
+              acc_dump[(static_cast<size_t>(m) * N + n) * total_groups + (g_begin + i)] =
+                  static_cast<int32_t>(v[j]) >> 4;
+          }
         }
-        tmem_ld_wait();
-        if (tid == 128) DQ_TR(1, i, 1);
-        if (c0 + CH == C::CPW) {  // accumulator b is free once its last column is read
+      } else {
+#pragma unroll
+        for (int j = 0; j < C::CH; ++j)
+          run[c0 + j] = fmaf(static_cast<float>(static_cast<int32_t>(v[j])), s, run[c0 + j]);
+      }
+    };
+    // The accumulator of a group is read in chunks of 8 columns.  tcgen05.ld is asynchronous, so
+    // chunk c + 1 is in flight while chunk c is scaled and added, and as soon as the accumulator
+    // is drained the first chunk of the next group is requested (if its UMMAs have finished)
+    // before the last chunk of this one is consumed.
+    uint32_t va[C::CH], vb[C::CH];
+    bool prefetched = false;
+    // One group; `sreg` is this group's slot of the scale ring, refilled for group i + kScaleAhead
+    // right after it is read (the loop below is unrolled by the ring size, so slots are
+    // registers with static indices and no load is waited for before its group comes up).
+    auto group_step = [&](int i, unsigned short& sreg) -> bool {
+      const int b = i % C::NB;
+      const float s = __half2float(__ushort_as_half(sreg)) * 0.0625f;
+      if constexpr (!DUMP) {
+        if (i + kScaleAhead < ng) sreg = __ldg(sw_row + static_cast<size_t>(i + kScaleAhead) * kBN);
+      }
+      if (!prefetched) {
+        if (!mbar_wait(&done[b], (i / C::NB) & 1, abort_flag, SITE_EPI)) return false;
+        tc_fence_after();
+        ld_chunk(b, 0, va);
+      }
+      if (tid == 128) DQ_TR(1, i, 0);
+#pragma unroll
+      for (int c = 0; c < C::NCH; ++c) {  // chunk c lives in va (c even) or vb (c odd)
+        uint32_t* cur = (c & 1) ? vb : va;
+        uint32_t* nxt = (c & 1) ? va : vb;
+        tmem_ld_wait();  // chunk c has landed
+        if (c + 1 < C::NCH) {
+          ld_chunk(b, (c + 1) * C::CH, nxt);
+        } else {
+          if (tid == 128) DQ_TR(1, i, 1);
+          // accumulator b is free once its last column has been read
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&ready[b]);
-        }
-        if constexpr (DUMP) {
-          if (n_ok) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int m = t0 + h * C::CPW + c0 + j;
-              if (m < M)
-                acc_dump[(static_cast<size_t>(m) * N + n) * total_groups + (g_begin + i)] =
-                    static_cast<int32_t>(v[j]) >> 4;
+          if constexpr (C::NCH > 1) {  // NCH is even: the next group's first chunk goes to va
+            prefetched = false;
+            if (i + 1 < ng) {
+              const int b1 = (i + 1) % C::NB;
+              // tcgen05.ld is warp-collective: take the early path only if every lane saw the phase
+              if (__all_sync(0xffffffffu, mbar_test_wait(&done[b1], ((i + 1) / C::NB) & 1) ? 1 : 0)) {
+                tc_fence_after();
+                ld_chunk(b1, 0, nxt);
+                prefetched = true;
+              }
             }
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < CH; ++j)
-            run[c0 + j] = fmaf(static_cast<float>(static_cast<int32_t>(v[j])), s, run[c0 + j]);
         }
+        consume(cur, c * C::CH, i, s);
+      }
+      if (tid == 128) DQ_TR(1, i, 2);
+      return true;
+    };
+    bool ok = true;
+    for (int i0 = 0; i0 < ng && ok; i0 += kScaleAhead) {
+#pragma unroll
+      for (int u = 0; u < kScaleAhead; ++u) {
+        if (ok && i0 + u < ng) ok = group_step(i0 + u, sq[u]);
       }
     }
     if constexpr (!DUMP) {
@@ -277,23 +387,26 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         for (int j = 0; j < C::CPW; ++j) red[(h * C::CPW + j) * kBN + q * 32 + lane] = run[j];
       }
     }
-  } else if (warp == 12) {
-    // ------------------------------------------------------------------ TMA producer
+  } else if (warp == C::kProducerWarp || warp == C::kXProducerWarp) {
+    // ------------------------------------------------------------------ TMA producer(s)
     // The whole warp runs the loop (uniform control flow); lane 0 issues the copies.  The two
     // rings advance independently - weights up to SP groups ahead of the UMMAs, activations up
-    // to SX stages of XC groups - so both are polled without blocking on either.
+    // to SX stages of XC groups - so both are polled without blocking on either.  With two
+    // producer warps each polls its own ring only.
+    const bool do_w = (warp == C::kProducerWarp);
+    const bool do_x = (warp == C::kXProducerWarp);
     uint64_t pol_w, pol_x;
     if (w_stream_once) pol_w = l2_policy_evict_first(); else pol_w = l2_policy_evict_last();
     pol_x = l2_policy_evict_last();
     // tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB codes + scales]
     const uint8_t* w_tile =
         w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kTileBytes;
-    const int nxc = (ng + C::XC - 1) / C::XC;
-    int iw = 0, ix = 0;
+    const int nxs = (ng + C::XC - 1) / C::XC;  // activation stages
+    int iw = do_w ? 0 : ng, ix = do_x ? 0 : nxs;
     // Weights do not depend on the preceding kernel of the stream; the activation codes do.
     // Fill the weight ring first, then wait for the prerequisite grid (programmatic dependent
     // launch), then start on the activation tiles.
-    {
+    if (do_w) {
       const int pre = (ng < C::SP) ? ng : C::SP;
       if (lane == 0) {
         for (; iw < pre; ++iw) {
@@ -304,11 +417,11 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
       }
       iw = pre;
-      grid_dep_wait();
     }
+    if (do_x) grid_dep_wait();
     long long t_last = clock64();
     uint32_t idle = 0;
-    while (iw < ng || ix < nxc) {
+    while (iw < ng || ix < nxs) {
       bool progress = false;
       if (iw < ng) {
         const int sp = iw % C::SP;
@@ -324,16 +437,15 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
           progress = true;
         }
       }
-      if (ix < nxc) {
+      if (ix < nxs) {
         const int sxi = ix % C::SX;
         if (mbar_test_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1)) {
           if (lane == 0) {
-            int cnt = ng - ix * C::XC;
-            if (cnt > C::XC) cnt = C::XC;
-            mbar_expect_tx(&full_x[sxi], static_cast<uint32_t>(cnt) * C::kXBytes);
-            for (int j = 0; j < cnt; ++j)
-              tma_load_2d(smem + C::kOffX + sxi * C::kXStageBytes + j * C::kXBytes, &tm_x,
-                          (g_begin + ix * C::XC + j) * kGroup, t0, &full_x[sxi], pol_x);
+            // one box = XC groups x TN tokens; groups past the end of K are zero-filled and
+            // still counted, so the byte count is always that of the full box
+            mbar_expect_tx(&full_x[sxi], C::kXStageBytes);
+            tma_load_3d(smem + C::kOffX + sxi * C::kXStageBytes, &tm_x, 0, t0,
+                        g_begin + ix * C::XC, &full_x[sxi], pol_x);
             DQ_TR(3, ix, 1);
           }
           ++ix;
@@ -351,19 +463,21 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
       }
     }
-  } else {
+  } else if (warp < C::kIssuerWarp0 + C::kIssuers) {
     // ------------------------------------------------------------------ UMMA issuer
     // Whole warp waits (uniform control flow); lane 0 issues tcgen05.mma / tcgen05.commit.
     constexpr uint32_t idesc = umma_idesc_i8(kBN, TN);
     const uint32_t a_base = smem_u32(smem + C::kOffA);
     const uint32_t x_base = smem_u32(smem + C::kOffX);
-    for (int i = 0; i < ng; ++i) {
-      const int b = i & 1;
-      const int xc = i / C::XC, xj = i % C::XC, sxi = xc % C::SX;
-      if (!mbar_wait(&ready[b], (i >> 1) & 1, abort_flag, SITE_MMA_READY)) break;
+    // The groups alternate between the two issuing warps; accumulator b, buffer b and activation
+    // stage i % SX of a group are always waited for and released by the same warp.
+    for (int i = warp - C::kIssuerWarp0; i < ng; i += C::kIssuers) {
+      const int b = i % C::NB;
+      const int xs = i / C::XC, xj = i % C::XC, sxi = xs % C::SX;
+      if (!mbar_wait(&ready[b], (i / C::NB) & 1, abort_flag, SITE_MMA_READY)) break;
       if (lane == 0) DQ_TR(2, i, 0);
-      if (xj == 0) {
-        if (!mbar_wait(&full_x[sxi], (xc / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
+      if (xj == 0 || C::kIssuers > 1) {
+        if (!mbar_wait(&full_x[sxi], (xs / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
       }
       if (lane == 0) DQ_TR(2, i, 1);
       tc_fence_after();
@@ -387,7 +501,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   if (!DUMP && split_k > 1) {
     __syncwarp();
     cluster_sync_all();
-    if (warp >= 4 && warp < 12) {
+    if (warp >= kUnpackWarps && warp < kUnpackWarps + 8) {
       const uint32_t rank = cluster_ctarank();
       const int rows = TN / split_k;  // token rows of the tile this CTA finishes
       const int e = tid - 4 * 32;     // 0..255
@@ -428,7 +542,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   // -------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == 13) {
+  if (warp == C::kIssuerWarp0) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
@@ -484,7 +598,7 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                   const float* r, int M, int N, int K, void* y, int y_dtype, int32_t* acc_dump,
                   int split, cudaStream_t stream, DeviceState* st) {
   CUtensorMap tm_x;
-  int rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, kGroup, TN, CU_TENSOR_MAP_SWIZZLE_128B);
+  int rc = make_tmap_x_groups(&tm_x, codes, K, M, TN, Cfg<TN>::XC);
   if (rc != DQ_OK) return rc;
 
   const int total_groups = K / kGroup;
@@ -492,7 +606,7 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   const int tok_tiles = (M + TN - 1) / TN;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((N + kBN - 1) / kBN, tok_tiles, split);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(Cfg<TN>::kThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg<TN>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
