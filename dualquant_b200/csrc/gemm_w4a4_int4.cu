@@ -103,11 +103,9 @@ struct Cfg {
   static constexpr int kIssuerWarp0 = kProducerWarp + 1;
   // The 128-token tile runs one CTA per SM and re-balances registers between warpgroups
   // (unpack 56, epilogue 96, producer/issuers 40 of the 80 the launch grants each thread), which
-  // needs whole warpgroups: the CTA is padded to 24 warps; the last one is a second producer
-  // (activation tiles), so that neither producing thread limits the group rate.
+  // needs whole warpgroups: the CTA is padded to 24 warps, the last one idle.
   static constexpr bool kRebalance = (TN == 128);
   static constexpr int kThreads = kRebalance ? 768 : 32 * (kIssuerWarp0 + kIssuers);
-  static constexpr int kXProducerWarp = kRebalance ? 23 : kProducerWarp;
   static_assert(!kRebalance || (kIssuerWarp0 + kIssuers <= 24 && kProducerWarp % 4 == 0), "warpgroup layout");
   static constexpr int kReadyCount = EW + 1;            // epilogue warps + the unpacking warp
   static constexpr int kXBytes = TN * kGroup;           // one group of activation codes
@@ -117,7 +115,7 @@ struct Cfg {
   static constexpr int kXStageBytes = XC * kXBytes;
   static constexpr int kOffP = kOffX + SX * kXStageBytes;
   static constexpr int kOffBar = kOffP + SP * kWpBytes;
-  static constexpr int kNumBars = 2 * SP + 2 * SX + 2 * NB;
+  static constexpr int kNumBars = SP + 2 * SX + 2 * NB;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
   static constexpr int kAccCols = NB * TN;
   static constexpr int kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128
@@ -135,7 +133,8 @@ enum { SITE_TMA = 1, SITE_UNPACK_FULL, SITE_UNPACK_FREE, SITE_MMA_READY, SITE_MM
        SITE_SMEM_ALIGN };
 
 // Barrier protocol (b = i % NB selects the unpacked-weight buffer and the TMEM accumulator):
-//   full_p / empty_p [SP]  packed weight ring   producer -> the unpacking warp of the group
+//   full_p [SP]            packed weight ring   TMA -> the unpacking warp that owns the stage
+//                          (it re-arms the barrier and refills the stage itself)
 //   full_x / empty_x [SX]  activation ring      producer -> UMMA issuer  (tcgen05.commit)
 //   ready[b]               buffer b written by its unpacking warp AND accumulator b drained by
 //                          all epilogue warps (EW + 1 arrivals; the epilogue pre-arrives once)
@@ -161,8 +160,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
   uint64_t* full_p = bars;
-  uint64_t* empty_p = full_p + C::SP;
-  uint64_t* full_x = empty_p + C::SP;
+  uint64_t* full_x = full_p + C::SP;
   uint64_t* empty_x = full_x + C::SX;
   uint64_t* ready = empty_x + C::SX;
   uint64_t* done = ready + C::NB;
@@ -181,7 +179,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   const int ng = (g_end > g_begin) ? (g_end - g_begin) : 0;
 
   if (tid == 0) {
-    for (int i = 0; i < C::SP; ++i) { mbar_init(&full_p[i], 1); mbar_init(&empty_p[i], 1); }
+    for (int i = 0; i < C::SP; ++i) mbar_init(&full_p[i], 1);
     for (int i = 0; i < C::SX; ++i) { mbar_init(&full_x[i], 1); mbar_init(&empty_x[i], 1); }
     for (int i = 0; i < C::NB; ++i) { mbar_init(&ready[i], C::kReadyCount); mbar_init(&done[i], 1); }
     *abort_flag = 0;
@@ -191,12 +189,16 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
-  if (warp == C::kXProducerWarp && lane == 0) tma_prefetch_desc(&tm_x);
+  if (warp == C::kProducerWarp && lane == 0) tma_prefetch_desc(&tm_x);
   grid_dep_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  // tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB codes + scales]
+  const uint8_t* w_tile =
+      w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kTileBytes;
 
   float run[C::CPW];  // epilogue running sums (only epilogue warps use them)
 #pragma unroll
@@ -217,6 +219,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     // One warp expands a whole group (groups warp, warp + 4, ...): the four warps work on four
     // consecutive groups at once, so the wait / expand / proxy-fence / arrive chain of a group,
     // which is latency and not throughput, overlaps with that of its neighbours.
+    const uint64_t pol_w = w_stream_once ? l2_policy_evict_first() : l2_policy_evict_last();
     for (int i = warp; i < ng; i += kUnpackWarps) {
       const int sp = i % C::SP, b = i % C::NB;
       if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
@@ -248,10 +251,18 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
       }
       fence_proxy_async_smem();  // each writer orders its own stores before the UMMA reads
-      __syncwarp();
+      __syncwarp();               // every lane has consumed its loads from the packed stage
       if (lane == 0) {
         mbar_arrive(&ready[b]);
-        mbar_arrive(&empty_p[sp]);
+        // The stage belongs to this warp (SP is a multiple of the unpack warp count): refill it
+        // for group i + SP right away instead of handing it back to the producer warp.
+        if (i + C::SP < ng) {
+          mbar_expect_tx(&full_p[sp], kWpBytes);
+          bulk_load_1d(smem + C::kOffP + sp * kWpBytes,
+                       w_tile + static_cast<size_t>(g_begin + i + C::SP) * kTileBytes, kWpBytes,
+                       &full_p[sp], pol_w);
+          DQ_TR(3, i + C::SP, 0);
+        }
       }
       if (lane == 0) DQ_TR(0, i, 2);
     }
@@ -387,81 +398,38 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         for (int j = 0; j < C::CPW; ++j) red[(h * C::CPW + j) * kBN + q * 32 + lane] = run[j];
       }
     }
-  } else if (warp == C::kProducerWarp || warp == C::kXProducerWarp) {
-    // ------------------------------------------------------------------ TMA producer(s)
-    // The whole warp runs the loop (uniform control flow); lane 0 issues the copies.  The two
-    // rings advance independently - weights up to SP groups ahead of the UMMAs, activations up
-    // to SX stages of XC groups - so both are polled without blocking on either.  With two
-    // producer warps each polls its own ring only.
-    const bool do_w = (warp == C::kProducerWarp);
-    const bool do_x = (warp == C::kXProducerWarp);
-    uint64_t pol_w, pol_x;
-    if (w_stream_once) pol_w = l2_policy_evict_first(); else pol_w = l2_policy_evict_last();
-    pol_x = l2_policy_evict_last();
-    // tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB codes + scales]
-    const uint8_t* w_tile =
-        w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kTileBytes;
-    const int nxs = (ng + C::XC - 1) / C::XC;  // activation stages
-    int iw = do_w ? 0 : ng, ix = do_x ? 0 : nxs;
+  } else if (warp == C::kProducerWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    // The whole warp runs the loop (uniform control flow); lane 0 issues the copies.
     // Weights do not depend on the preceding kernel of the stream; the activation codes do.
-    // Fill the weight ring first, then wait for the prerequisite grid (programmatic dependent
-    // launch), then start on the activation tiles.
-    if (do_w) {
+    // Fill the weight ring first (the unpack warps refill their stages themselves afterwards),
+    // then wait for the prerequisite grid (programmatic dependent launch), then stream the
+    // activation stages, up to SX stages of XC groups ahead of the UMMAs.
+    const uint64_t pol_w = w_stream_once ? l2_policy_evict_first() : l2_policy_evict_last();
+    const uint64_t pol_x = l2_policy_evict_last();
+    if (lane == 0) {
       const int pre = (ng < C::SP) ? ng : C::SP;
-      if (lane == 0) {
-        for (; iw < pre; ++iw) {
-          mbar_expect_tx(&full_p[iw], kWpBytes);
-          bulk_load_1d(smem + C::kOffP + iw * kWpBytes,
-                       w_tile + static_cast<size_t>(g_begin + iw) * kTileBytes, kWpBytes,
-                       &full_p[iw], pol_w);
-        }
+      for (int iw = 0; iw < pre; ++iw) {
+        mbar_expect_tx(&full_p[iw], kWpBytes);
+        bulk_load_1d(smem + C::kOffP + iw * kWpBytes,
+                     w_tile + static_cast<size_t>(g_begin + iw) * kTileBytes, kWpBytes,
+                     &full_p[iw], pol_w);
       }
-      iw = pre;
     }
-    if (do_x) grid_dep_wait();
-    long long t_last = clock64();
-    uint32_t idle = 0;
-    while (iw < ng || ix < nxs) {
-      bool progress = false;
-      if (iw < ng) {
-        const int sp = iw % C::SP;
-        if (mbar_test_wait(&empty_p[sp], ((iw / C::SP) & 1) ^ 1)) {
-          if (lane == 0) {
-            mbar_expect_tx(&full_p[sp], kWpBytes);
-            bulk_load_1d(smem + C::kOffP + sp * kWpBytes,
-                         w_tile + static_cast<size_t>(g_begin + iw) * kTileBytes, kWpBytes,
-                         &full_p[sp], pol_w);
-            DQ_TR(3, iw, 0);
-          }
-          ++iw;
-          progress = true;
-        }
+    grid_dep_wait();
+    const int nxs = (ng + C::XC - 1) / C::XC;  // activation stages
+    for (int ix = 0; ix < nxs; ++ix) {
+      const int sxi = ix % C::SX;
+      if (!mbar_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1, abort_flag, SITE_TMA)) break;
+      if (lane == 0) {
+        // one box = XC groups x TN tokens; groups past the end of K are zero-filled and still
+        // counted, so the byte count is always that of the full box
+        mbar_expect_tx(&full_x[sxi], C::kXStageBytes);
+        tma_load_3d(smem + C::kOffX + sxi * C::kXStageBytes, &tm_x, 0, t0, g_begin + ix * C::XC,
+                    &full_x[sxi], pol_x);
+        DQ_TR(3, ix, 1);
       }
-      if (ix < nxs) {
-        const int sxi = ix % C::SX;
-        if (mbar_test_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1)) {
-          if (lane == 0) {
-            // one box = XC groups x TN tokens; groups past the end of K are zero-filled and
-            // still counted, so the byte count is always that of the full box
-            mbar_expect_tx(&full_x[sxi], C::kXStageBytes);
-            tma_load_3d(smem + C::kOffX + sxi * C::kXStageBytes, &tm_x, 0, t0,
-                        g_begin + ix * C::XC, &full_x[sxi], pol_x);
-            DQ_TR(3, ix, 1);
-          }
-          ++ix;
-          progress = true;
-        }
-      }
-      if (progress) {
-        idle = 0;
-        t_last = clock64();
-      } else if ((++idle & 1023u) == 0) {
-        if (*abort_flag != 0) break;
-        if (clock64() - t_last > (1ll << 31)) {
-          *abort_flag = SITE_TMA;
-          break;
-        }
-      }
+      __syncwarp();
     }
   } else if (warp < C::kIssuerWarp0 + C::kIssuers) {
     // ------------------------------------------------------------------ UMMA issuer
