@@ -461,8 +461,17 @@ def run_prefill_suite(args):
                                                        scratch=scratch, out=y), dev)
         ms_gemm = _time_loop(g_gemm.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
         ms_full = _time_loop(g_full.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        # "reference on this box": what the reference's PermLinear ends in - a bf16 F.linear
+        # (cuBLAS) on de-quantised operands of the same shape; library call, timed for context
+        wb = torch.empty(N, K, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+        yb = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        g_bf16 = _capture(lambda: torch.matmul(x, wb.t(), out=yb), dev)
+        ms_bf16 = _time_loop(g_bf16.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        del wb, yb, g_bf16
         ops_ = 2.0 * M * N * K
         rows.append({"shape": label, "M": M, "K": K, "N": N,
+                     "bf16_matmul_us": round(ms_bf16 * 1e3, 1),
+                     "bf16_matmul_TFLOPS": round(ops_ / ms_bf16 / 1e9, 1),
                      "gemm_us": round(ms_gemm * 1e3, 1), "gemm_TOPS": round(ops_ / ms_gemm / 1e9, 1),
                      "linear_us": round(ms_full * 1e3, 1), "linear_TOPS": round(ops_ / ms_full / 1e9, 1),
                      "frac_int8_nominal": round(ops_ / ms_gemm / 1e9 / 4500.0, 4),
