@@ -19,6 +19,7 @@ SOURCES = [
     "act_quant_int4.cu",
     "quant_fp4.cu",
     "gemm_w4a4_int4.cu",
+    "gemm_w4a4_int4_tm.cu",
     "gemv_w4a4_int4.cu",
     "gemm_fp4.cu",
     "linear_w4a4.cu",

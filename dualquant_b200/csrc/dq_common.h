@@ -80,10 +80,14 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 // One-time kernel attribute set-up of each translation unit (called from dq_init).
 int init_gemm_int4_kernels();
 int init_gemv_int4_kernels();
+int init_gemm_int4_tm_kernels();
 int init_gemm_fp4_kernels();
 int init_act_quant_kernels();
 
 // Decode-batch (register-path) variant of the int4 linear, defined in gemv_w4a4_int4.cu.
+int launch_gemm_int4_tm(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                        const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
+                        int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st);
 int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count);
 int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                      const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,

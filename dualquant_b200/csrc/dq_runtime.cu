@@ -119,6 +119,8 @@ extern "C" int dq_init(int device) {
 
   int rc = init_gemm_int4_kernels();
   if (rc != DQ_OK) return rc;
+  rc = init_gemm_int4_tm_kernels();
+  if (rc != DQ_OK) return rc;
   rc = init_gemv_int4_kernels();
   if (rc != DQ_OK) return rc;
   rc = init_gemm_fp4_kernels();

@@ -400,13 +400,14 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     }
   } else if (warp == C::kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
-    // The whole warp runs the loop (uniform control flow); lane 0 issues the copies.
     // Weights do not depend on the preceding kernel of the stream; the activation codes do.
     // Fill the weight ring first (the unpack warps refill their stages themselves afterwards),
     // then wait for the prerequisite grid (programmatic dependent launch), then stream the
     // activation stages, up to SX stages of XC groups ahead of the UMMAs.
     const uint64_t pol_w = w_stream_once ? l2_policy_evict_first() : l2_policy_evict_last();
     const uint64_t pol_x = l2_policy_evict_last();
+    // Only lane 0 works; the other lanes go straight to the end of the role (a waiting warp of
+    // 32 polling lanes costs the SM issue slots and barrier-unit bandwidth the other roles need).
     if (lane == 0) {
       const int pre = (ng < C::SP) ? ng : C::SP;
       for (int iw = 0; iw < pre; ++iw) {
@@ -415,13 +416,11 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                      w_tile + static_cast<size_t>(g_begin + iw) * kTileBytes, kWpBytes,
                      &full_p[iw], pol_w);
       }
-    }
-    grid_dep_wait();
-    const int nxs = (ng + C::XC - 1) / C::XC;  // activation stages
-    for (int ix = 0; ix < nxs; ++ix) {
-      const int sxi = ix % C::SX;
-      if (!mbar_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1, abort_flag, SITE_TMA)) break;
-      if (lane == 0) {
+      grid_dep_wait();
+      const int nxs = (ng + C::XC - 1) / C::XC;  // activation stages
+      for (int ix = 0; ix < nxs; ++ix) {
+        const int sxi = ix % C::SX;
+        if (!mbar_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1, abort_flag, SITE_TMA)) break;
         // one box = XC groups x TN tokens; groups past the end of K are zero-filled and still
         // counted, so the byte count is always that of the full box
         mbar_expect_tx(&full_x[sxi], C::kXStageBytes);
@@ -429,27 +428,25 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                     &full_x[sxi], pol_x);
         DQ_TR(3, ix, 1);
       }
-      __syncwarp();
     }
   } else if (warp < C::kIssuerWarp0 + C::kIssuers) {
     // ------------------------------------------------------------------ UMMA issuer
-    // Whole warp waits (uniform control flow); lane 0 issues tcgen05.mma / tcgen05.commit.
     constexpr uint32_t idesc = umma_idesc_i8(kBN, TN);
     const uint32_t a_base = smem_u32(smem + C::kOffA);
     const uint32_t x_base = smem_u32(smem + C::kOffX);
     // The groups alternate between the two issuing warps; accumulator b, buffer b and activation
     // stage i % SX of a group are always waited for and released by the same warp.
-    for (int i = warp - C::kIssuerWarp0; i < ng; i += C::kIssuers) {
-      const int b = i % C::NB;
-      const int xs = i / C::XC, xj = i % C::XC, sxi = xs % C::SX;
-      if (!mbar_wait(&ready[b], (i / C::NB) & 1, abort_flag, SITE_MMA_READY)) break;
-      if (lane == 0) DQ_TR(2, i, 0);
-      if (xj == 0 || C::kIssuers > 1) {
-        if (!mbar_wait(&full_x[sxi], (xs / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
-      }
-      if (lane == 0) DQ_TR(2, i, 1);
-      tc_fence_after();
-      if (lane == 0) {
+    if (lane == 0) {  // only lane 0 works (see the producer)
+      for (int i = warp - C::kIssuerWarp0; i < ng; i += C::kIssuers) {
+        const int b = i % C::NB;
+        const int xs = i / C::XC, xj = i % C::XC, sxi = xs % C::SX;
+        if (!mbar_wait(&ready[b], (i / C::NB) & 1, abort_flag, SITE_MMA_READY)) break;
+        DQ_TR(2, i, 0);
+        if (xj == 0 || C::kIssuers > 1) {
+          if (!mbar_wait(&full_x[sxi], (xs / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
+        }
+        DQ_TR(2, i, 1);
+        tc_fence_after();
         const uint64_t da = umma_desc_k_sw128(a_base + b * kWaBytes);
         const uint64_t db = umma_desc_k_sw128(x_base + sxi * C::kXStageBytes + xj * C::kXBytes);
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * TN);
@@ -461,7 +458,6 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         if (xj == C::XC - 1 || i == ng - 1) umma_commit(&empty_x[sxi]);
         DQ_TR(2, i, 3);
       }
-      __syncwarp();
     }
   }
 
@@ -538,8 +534,6 @@ int init_gemm_int4_kernels() {
   if ((rc = set_attr<32, false>()) != DQ_OK) return rc;
   if ((rc = set_attr<64, false>()) != DQ_OK) return rc;
   if ((rc = set_attr<128, false>()) != DQ_OK) return rc;
-  if ((rc = set_attr<16, true>()) != DQ_OK) return rc;
-  if ((rc = set_attr<128, true>()) != DQ_OK) return rc;
   return DQ_OK;
 }
 
@@ -649,6 +643,10 @@ extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const 
     return launch_gemv_int4(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, tok, split,
                             static_cast<cudaStream_t>(stream), st);
   }
+  // 1000 + tile / 2000 + tile force the shared-memory-operand / tensor-memory-operand kernel
+  int forced = 0;
+  if (token_tile >= 2000) { forced = 2; token_tile -= 2000; }
+  else if (token_tile >= 1000) { forced = 1; token_tile -= 1000; }
   const int tn = token_tile ? token_tile : pick_token_tile(M);
   DQ_REQUIRE(tn == 16 || tn == 32 || tn == 64 || tn == 128, DQ_ERR_SHAPE,
              "token tile must be 16/32/64/128 (got %d)", tn);
@@ -660,6 +658,13 @@ extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const 
              "split_k=%d too large for token tile %d / %d groups", split, tn, total_groups);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const __half* swp = static_cast<const __half*>(sw_t);
+  // Two tcgen05 kernels.  Token tiles up to 64 (weight-streaming regime, two CTAs per SM): the
+  // kernel that feeds the weights to the tensor core from tensor memory, which leaves all shared
+  // memory to the copy rings.  Token tile 128 (prefill): the kernel with int8 weight tiles in
+  // shared memory, four accumulators and two issuing warps, measured 10-15 % faster there.
+  const bool use_tm = forced ? (forced == 2) : (tn <= 64);
+  if (use_tm)
+    return launch_gemm_int4_tm(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, nullptr, tn, split, s, st);
   switch (tn) {
     case 16: return launch<16, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
     case 32: return launch<32, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
@@ -684,11 +689,8 @@ extern "C" int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packe
   if (rc != DQ_OK) return rc;
   DQ_REQUIRE(acc != nullptr, DQ_ERR_NULL, "null acc");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (M <= 16)
-    return launch<16, true>(codes, nullptr, w_packed, nullptr, nullptr, M, N, K, nullptr,
-                            DQ_DTYPE_F32, acc, 1, s, st);
-  return launch<128, true>(codes, nullptr, w_packed, nullptr, nullptr, M, N, K, nullptr,
-                           DQ_DTYPE_F32, acc, 1, s, st);
+  return launch_gemm_int4_tm(codes, nullptr, w_packed, nullptr, nullptr, M, N, K, nullptr, DQ_DTYPE_F32,
+                             acc, M <= 16 ? 16 : 128, 1, s, st);
 }
 
 extern "C" int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const uint8_t* w_packed,

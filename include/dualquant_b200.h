@@ -219,8 +219,10 @@ DQ_API int dq_gemm_w4a4_int4(const int8_t* codes, const float* sx, const uint8_t
                       int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* As above with an explicit kernel choice; used by tuning sweeps and tests.  token_tile: 0 = auto,
- * 16/32/64/128 = tensor-memory (tcgen05) kernel with that token tile, -8/-16/-32 = decode-batch
- * kernel with that token capacity (needs M <= capacity).  split_k: 0 = auto, else 1/2/4/8. */
+ * 16/32/64/128 = tcgen05 kernel with that token tile (weights through tensor memory for tiles up
+ * to 64, int8 weight tiles in shared memory for 128; 1000 + tile / 2000 + tile force the
+ * shared-memory / tensor-memory variant), -8/-16/-32 = decode-batch kernel with that token
+ * capacity (needs M <= capacity).  split_k: 0 = auto, else 1/2/4/8. */
 DQ_API int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                          const void* sw_t, const float* r, int M, int N, int K, int G, void* y,
                          int y_dtype, void* workspace, size_t workspace_bytes, void* stream,

@@ -185,6 +185,11 @@ def test_gemm_accumulators_extreme_codes():
     (16, 4096, 4096, 0, 0), (20, 256, 512, 32, 2), (32, 512, 1024, 32, 8), (50, 200, 640, 64, 1),
     (64, 256, 2048, 64, 4), (128, 256, 512, 128, 1), (128, 384, 1024, 128, 2),
     (300, 640, 384, 128, 1), (7, 136, 256, 0, 0), (7, 136, 256, 16, 1),
+    # both tcgen05 kernels at every tile: 1000 + tile = int8 weight tiles in shared memory,
+    # 2000 + tile = weights through tensor memory
+    (9, 256, 640, 1016, 1), (20, 256, 512, 1032, 2), (64, 256, 2048, 1064, 4), (50, 200, 640, 1064, 1),
+    (130, 384, 1024, 2128, 1), (128, 256, 512, 2128, 2), (300, 640, 384, 2128, 1), (40, 136, 384, 2064, 1),
+    (33, 256, 384, 2064, 1), (128, 128, 128, 2128, 1),
     # decode-batch (register-path) kernel: negative token_tile = token capacity
     (1, 256, 1024, -8, 1), (1, 256, 1024, -8, 8), (8, 384, 512, -8, 4), (5, 200, 384, -8, 2),
     (16, 4096, 4096, -16, 0), (12, 256, 512, -16, 2), (16, 128, 14336, -16, 8),
