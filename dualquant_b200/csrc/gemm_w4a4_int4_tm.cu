@@ -297,9 +297,15 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
           }
         }
       } else {
+        // two columns per instruction: packed fp32 FMA (each half rounds like a scalar fmaf)
 #pragma unroll
-        for (int j = 0; j < C::CH; ++j)
-          run[c0 + j] = fmaf(static_cast<float>(static_cast<int32_t>(v[j])), s, run[c0 + j]);
+        for (int j = 0; j < C::CH; j += 2) {
+          const float2 f = make_float2(static_cast<float>(static_cast<int32_t>(v[j])),
+                                       static_cast<float>(static_cast<int32_t>(v[j + 1])));
+          const float2 acc2 = __ffma2_rn(f, make_float2(s, s), make_float2(run[c0 + j], run[c0 + j + 1]));
+          run[c0 + j] = acc2.x;
+          run[c0 + j + 1] = acc2.y;
+        }
       }
     };
     // The accumulator of a group is read in chunks of 8 columns.  tcgen05.ld is asynchronous, so
