@@ -60,6 +60,7 @@ SIGNATURES = {
     "dq_unpack_w_int4": (_i, [_vp, _i, _i, _vp, _vp]),
     "dq_quant_w_int4": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "dq_quant_act_int4": (_i, [_vp, _i64, _vp, _hp, _i, _i, _vp, _vp, _i, _vp]),
+    "dq_quant_act_int4_rmsnorm": (_i, [_vp, _i64, _vp, ctypes.c_float, _vp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_quant_act_int4_gated": (_i, [_vp, _vp, _i64, _vp, _hp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_fakequant_act_int4": (_i, [_vp, _i, _i64, _vp, _hp, _i, _i, _vp, _i, _vp]),
     "dq_hadamard_f32": (_i, [_vp, _vp, _i, _i, _hp, _vp]),

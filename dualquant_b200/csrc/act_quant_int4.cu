@@ -31,6 +31,22 @@ __device__ __forceinline__ float block_max(float v, float* red, int nwarps) {
   return m;
 }
 
+__device__ __forceinline__ float block_sum(float v, float* red, int nwarps) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read from a previous use
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float m = red[0];
+  for (int i = 1; i < nwarps; ++i) m += red[i];
+  return m;
+}
+
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
 __device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
   float s = __fdiv_rn(amax, 7.0f);
   if (amax == 0.f) s = 1.0f;
@@ -139,11 +155,16 @@ __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t*
 // ---------------------------------------------------------------------------------------------
 // register-resident rows (no Hadamard)
 // ---------------------------------------------------------------------------------------------
+// norm_eps >= 0 puts an RMSNorm in front (the reference's _RMSNbf16Safe, quarot/llama_quarot.py:
+// 135-141, and HF's LlamaRMSNorm): v = bf16(x * rsqrt(mean(x^2) + eps)), times the bf16 weight
+// (rounded to bf16 again) when norm_w is given - exactly the bf16 tensor the separate norm would
+// have written and the quantiser read back.
 template <int THREADS, int VPT, typename XT>
 __global__ void __launch_bounds__(THREADS, (THREADS >= 512 && VPT <= 2) ? 2048 / THREADS : 1)
 act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
                       int8_t* __restrict__ codes, float* __restrict__ sx, float* __restrict__ out,
-                      int mode, int scale_fp16) {
+                      int mode, int scale_fp16, const __nv_bfloat16* __restrict__ norm_w,
+                      float norm_eps) {
   __shared__ float red[THREADS / 32];
   // the GEMM that consumes the codes may be launched programmatically: let it start streaming
   // its weights now; it waits for this grid before it touches codes / sx
@@ -152,23 +173,60 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
   const int row = blockIdx.x;
   const XT* xr = x + static_cast<int64_t>(row) * ldx;
   // The row is held in registers in its input width (bf16: 4 registers per 8 elements) and
-  // expanded twice - once for the absmax, once for the codes - with identical arithmetic, so
-  // that twice as many rows fit in the register file and more loads are in flight per SM.
+  // expanded once per pass - sum of squares (with a norm), absmax, codes - with identical
+  // arithmetic, so that twice as many rows fit in the register file and more loads are in
+  // flight per SM.
   Raw8<XT> raw[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = (i * THREADS + threadIdx.x) * 8;
+    if (idx < K) raw[i].load(xr + idx);
+  }
+  const bool norm = norm_eps >= 0.f;
+  float inv_rms = 1.f;
+  if (norm) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = (i * THREADS + threadIdx.x) * 8;
+      if (idx < K) {
+        float v[8];
+        raw[i].expand(v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+      }
+    }
+    ss = block_sum(ss, red, THREADS / 32);
+    inv_rms = rsqrtf(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), norm_eps));
+  }
+  auto prologue = [&](float* v, int idx) {
+    if (norm) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = bf16_round(__fmul_rn(v[e], inv_rms));
+      if (norm_w != nullptr) {
+        Raw8<__nv_bfloat16> wr;
+        wr.load(norm_w + idx);
+        float wv[8];
+        wr.expand(wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = bf16_round(__fmul_rn(wv[e], v[e]));
+      }
+    }
+    if (a != nullptr) {
+      float av[8];
+      load8(a + idx, av);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
+    }
+  };
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = (i * THREADS + threadIdx.x) * 8;
     if (idx < K) {
-      raw[i].load(xr + idx);
       float v[8];
       raw[i].expand(v);
-      if (a != nullptr) {
-        float av[8];
-        load8(a + idx, av);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
-      }
+      prologue(v, idx);
 #pragma unroll
       for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
     }
@@ -184,12 +242,7 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
     if (idx < K) {
       float v[8];
       raw[i].expand(v);
-      if (a != nullptr) {
-        float av[8];
-        load8(a + idx, av);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
-      }
+      prologue(v, idx);
       emit8(v, s, mode, crow, orow, idx);
     }
   }
@@ -557,7 +610,8 @@ static int check_had(const dq_hadamard_desc* had, int K) {
 template <typename XT>
 static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamard_desc* had, int M,
                       int K, int8_t* codes, float* sx, float* out, int mode, int scale_fp16,
-                      cudaStream_t stream, const XT* up = nullptr) {
+                      cudaStream_t stream, const XT* up = nullptr,
+                      const __nv_bfloat16* norm_w = nullptr, float norm_eps = -1.f) {
   DQ_REQUIRE(x != nullptr, DQ_ERR_NULL, "x is null");
   DQ_REQUIRE(M >= 0 && K >= 8 && K % 8 == 0, DQ_ERR_SHAPE, "bad shape M=%d K=%d (K %% 8 != 0)", M, K);
   DQ_REQUIRE(ldx >= K && ldx % 8 == 0, DQ_ERR_ALIGN, "ldx=%lld must be >= K and a multiple of 8",
@@ -571,6 +625,8 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
   if (rc != DQ_OK) return rc;
   if (M == 0) return DQ_OK;
   const bool use_had = had != nullptr && had->kind != DQ_HAD_NONE;
+  DQ_REQUIRE(norm_eps < 0.f || (!use_had && up == nullptr && mode != MODE_RAW && K <= 32768),
+             DQ_ERR_UNSUPPORTED, "the fused RMSNorm covers plain rows of K <= 32768 without a Hadamard");
   if (use_had || mode == MODE_RAW || K > 32768 || up != nullptr) {  // longer rows than the register path holds
     const int hk = use_had ? had->had_k : 1;
     const size_t smem = static_cast<size_t>(K) * 4 + (hk > 1 ? static_cast<size_t>(hk) * hk * 4 : 0);
@@ -608,7 +664,7 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
     const int vec = K / 8;
 #define DQ_ROWS_LAUNCH(T, V)                                                                      \
   DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<T, V, XT>, dim3(M), dim3(T), 0, stream, x, ldx, a, K, \
-                           codes, sx, out, mode, scale_fp16))
+                           codes, sx, out, mode, scale_fp16, norm_w, norm_eps))
     if (vec <= 128) DQ_ROWS_LAUNCH(128, 1);
     else if (vec <= 256) DQ_ROWS_LAUNCH(256, 1);
     else if (vec <= 512) DQ_ROWS_LAUNCH(512, 1);
@@ -633,6 +689,21 @@ extern "C" int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a
   DQ_REQUIRE(codes != nullptr && sx != nullptr, DQ_ERR_NULL, "codes / sx is null");
   return launch_act(static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, had, M, K, codes, sx,
                     nullptr, MODE_CODES, scale_fp16, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dq_quant_act_int4_rmsnorm(const void* x_bf16, int64_t ldx, const void* norm_weight_bf16,
+                                         float eps, const float* a, int M, int K, int8_t* codes,
+                                         float* sx, int scale_fp16, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  DQ_REQUIRE(codes != nullptr && sx != nullptr, DQ_ERR_NULL, "codes / sx is null");
+  DQ_REQUIRE(eps >= 0.f, DQ_ERR_SHAPE, "eps must be >= 0 (got %g)", (double)eps);
+  DQ_REQUIRE(norm_weight_bf16 == nullptr || aligned(norm_weight_bf16, 16), DQ_ERR_ALIGN,
+             "norm weight must be 16-byte aligned");
+  return launch_act(static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, nullptr, M, K, codes, sx,
+                    nullptr, MODE_CODES, scale_fp16, static_cast<cudaStream_t>(stream),
+                    static_cast<const __nv_bfloat16*>(nullptr),
+                    static_cast<const __nv_bfloat16*>(norm_weight_bf16), eps);
 }
 
 extern "C" int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, const float* a,

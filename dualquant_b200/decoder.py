@@ -71,6 +71,12 @@ class W4A4Linear:
             self._scratch[M] = buf
         return buf
 
+    def normed(self, x: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+               out_dtype=torch.bfloat16) -> torch.Tensor:
+        """RMSNorm(x) -> this linear, the norm fused into the activation quantiser."""
+        codes, sx = ops.quant_act_int4_rmsnorm(x, norm_weight, eps, self.a, False)
+        return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype)
+
     def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16, ar=None) -> torch.Tensor:
         """ar: an ops.AllReduceContext -> the cross-rank sum happens inside the GEMM (M <= 16)."""
         if ar is not None:
@@ -138,8 +144,8 @@ class DecoderLayer:
         cfg = self.cfg
         B, S, Hd = x.shape
         hd = cfg.head_dim
-        h = _rms_norm(x, self.ln1, cfg.rms_norm_eps)
-        qkv = self.qkv(h.reshape(B * S, Hd)).reshape(B, S, self.hq + 2 * self.hkv, hd)
+        qkv = self.qkv.normed(x.reshape(B * S, Hd), self.ln1, cfg.rms_norm_eps)
+        qkv = qkv.reshape(B, S, self.hq + 2 * self.hkv, hd)
         q = qkv[:, :, : self.hq].transpose(1, 2)
         k = qkv[:, :, self.hq : self.hq + self.hkv].transpose(1, 2)
         v = qkv[:, :, self.hq + self.hkv :].transpose(1, 2)
@@ -161,8 +167,7 @@ class DecoderLayer:
         if self.tp > 1 and fused is None:
             dist.all_reduce(o, group=group)
         x = x + o.reshape(B, S, Hd)
-        h = _rms_norm(x, self.ln2, cfg.rms_norm_eps)
-        gu = self.gate_up(h.reshape(B * S, Hd))
+        gu = self.gate_up.normed(x.reshape(B * S, Hd), self.ln2, cfg.rms_norm_eps)
         d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :], ar=fused)
         if self.tp > 1 and fused is None:
             dist.all_reduce(d, group=group)

@@ -140,6 +140,25 @@ def quant_act_int4_gated(gate: torch.Tensor, up: torch.Tensor, a: Optional[torch
     return codes, sx
 
 
+def quant_act_int4_rmsnorm(x: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float,
+                           a: Optional[torch.Tensor] = None, scale_fp16: bool = False):
+    """RMSNorm (bf16 result, optional bf16 weight) + column scale + per-token int4 quantiser in
+    one pass: bf16 [M,K] -> (codes int8 [M,K], sx fp32 [M])."""
+    lib = _prep(x)
+    if x.dtype != torch.bfloat16 or x.stride(-1) != 1:
+        raise ValueError("quant_act_int4_rmsnorm expects bf16 rows with unit inner stride")
+    if norm_weight is not None and (norm_weight.dtype != torch.bfloat16 or norm_weight.numel() != x.shape[1]):
+        raise ValueError("norm_weight must be bf16 with one entry per input channel")
+    M, K = x.shape
+    codes = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    sx = torch.empty(M, dtype=torch.float32, device=x.device)
+    _lib.check(lib.dq_quant_act_int4_rmsnorm(_ptr(x), x.stride(0) if M > 1 else K, _ptr(norm_weight),
+                                             float(eps), _ptr(a), M, K, _ptr(codes), _ptr(sx),
+                                             int(scale_fp16), _stream(x.device)),
+               "dq_quant_act_int4_rmsnorm")
+    return codes, sx
+
+
 def fakequant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
                        had: Optional[Hadamard] = None, scale_fp16: bool = False) -> torch.Tensor:
     """[M,K] bf16 or fp32 -> de-quantised fp32 [M,K] (what FormatSpec.cast returns)."""

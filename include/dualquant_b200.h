@@ -140,6 +140,18 @@ DQ_API int dq_quant_act_int4_gated(const void* gate_bf16, const void* up_bf16, i
 
 /* Same arithmetic, but writes the de-quantised value q*s as fp32 [M,K] (what
  * FormatSpec.cast returns, formats/base.py:33-39).  x is fp32 when x_is_f32 != 0. */
+/*
+ * RMSNorm fused in front of dq_quant_act_int4 (no Hadamard): per token
+ * v = bf16(x * rsqrt(mean(x^2) + eps)), times the bf16 norm weight (rounded to bf16 again) when
+ * norm_weight_bf16 is not null, then the column scale a and the per-token int4 quantiser.  This
+ * is the reference's _RMSNbf16Safe (quarot/llama_quarot.py:135-141; HF LlamaRMSNorm when a
+ * weight is given) followed by PermLinear._quantise_act (activations/perm_linear.py:108-134) in
+ * one pass over the row; the bf16 normalised tensor is never written.
+ */
+DQ_API int dq_quant_act_int4_rmsnorm(const void* x_bf16, int64_t ldx, const void* norm_weight_bf16,
+                                     float eps, const float* a, int M, int K, int8_t* codes,
+                                     float* sx, int scale_fp16, void* stream);
+
 DQ_API int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, const float* a,
                           const dq_hadamard_desc* had, int M, int K, float* out,
                           int scale_fp16, void* stream);

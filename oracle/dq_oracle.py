@@ -159,6 +159,18 @@ def quant_act_int4(x: torch.Tensor, a=None, had=None, scale_fp16: bool = False):
     return q.to(torch.int8), s.reshape(-1).contiguous(), x32
 
 
+def rmsnorm_bf16(x: torch.Tensor, weight=None, eps: float = 1e-5) -> torch.Tensor:
+    """_RMSNbf16Safe.forward (quarot/llama_quarot.py:135-141): fp32 variance by .mean(-1),
+    x * rsqrt(var + eps), cast back to the input dtype; with `weight` the HF LlamaRMSNorm form
+    weight * normed.to(input_dtype), the product rounded in the input dtype."""
+    x32 = x.to(torch.float32)
+    var = x32.pow(2).mean(-1, keepdim=True)
+    y = (x32 * torch.rsqrt(var + eps)).to(x.dtype)
+    if weight is not None:
+        y = weight.to(x.dtype) * y
+    return y
+
+
 def quant_w_int4(w: torch.Tensor, group: int = GROUP):
     """Symmetric per-group int4 weight quantiser (formats/rtn_int.py:43-69 with block_size =
     group; same grouping as pack_int4_weights, fused_dual_scale_kernel.py:156-189), with the

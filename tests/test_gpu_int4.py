@@ -291,3 +291,36 @@ def test_gated_quantiser_matches_bf16_silu_mul():
         diff = (codes.cpu().int() - qx.int()).abs()
         assert diff.max() <= 1 and (diff > 0).float().mean() < 2e-3
         assert torch.allclose(sxg.cpu(), sx, rtol=2e-3)
+
+
+# ------------------------------------------------------------------------------------------
+# RMSNorm fused into the quantiser
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,K,with_w", [(1, 4096, False), (8, 4096, True), (33, 1024, True),
+                                        (5, 14336, False), (130, 256, True)])
+def test_quant_act_rmsnorm_matches_norm_then_quant(M, K, with_w):
+    g = torch.Generator().manual_seed(M * 7 + K)
+    x = (torch.randn(M, K, generator=g) * 3.0).bfloat16()
+    x[:, : max(1, K // 100)] *= 20  # outlier channels
+    w = (1.0 + 0.1 * torch.randn(K, generator=g)).bfloat16() if with_w else None
+    a = torch.exp(torch.randn(K, generator=g) * 0.3)
+    codes, sx = ops.quant_act_int4_rmsnorm(x.to(DEV), None if w is None else w.to(DEV), 1e-5, a.to(DEV))
+    _status_ok()
+    normed = O.rmsnorm_bf16(x, w, 1e-5)
+    qref, sref, _ = O.quant_act_int4(normed, a, scale_fp16=False)
+    # the sum of squares is reduced in another order and rsqrt may differ in its last bit:
+    # a normalised value can land on the other side of a bf16 or code rounding boundary
+    diff = (codes.cpu().int() - qref.int()).abs()
+    assert int(diff.max()) <= 1
+    assert float((diff != 0).float().mean()) < 2e-3
+    assert torch.allclose(sx.cpu(), sref, rtol=8e-3, atol=0)
+
+
+def test_quant_act_rmsnorm_rejects_bad_arguments():
+    x = torch.randn(4, 256, device=DEV).bfloat16()
+    with pytest.raises(ValueError):
+        ops.quant_act_int4_rmsnorm(x.float(), None, 1e-5)
+    with pytest.raises(ValueError):
+        ops.quant_act_int4_rmsnorm(x, torch.ones(128, device=DEV).bfloat16(), 1e-5)
+    with pytest.raises(ValueError):
+        ops.quant_act_int4_rmsnorm(x, None, -1.0)
