@@ -90,6 +90,27 @@ __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+// The same bounded wait for a phase that is known to be far away (e.g. an epilogue waiting for a
+// whole K loop): sleeps between probes so that the waiting warps leave the issue slots and the
+// barrier unit to the warps that are working.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity,
+                                                  volatile int* abort_flag, int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(256);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > (1ll << 31)) {
+      *abort_flag = site;
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

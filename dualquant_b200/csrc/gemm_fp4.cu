@@ -136,10 +136,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const uint64_t pol = l2_policy_evict_last();
     const uint8_t* sfw_tile = sfw + (static_cast<size_t>(blockIdx.x) * total_st + st_begin) * kSfBytes;
     const uint8_t* sfx_tile = sfx + (static_cast<size_t>(blockIdx.y) * total_st + st_begin) * kSfBytes;
-    for (int i = 0; i < nst; ++i) {
-      const int s = i % kFStages;
-      if (!mbar_wait(&empty[s], ((i / kFStages) & 1) ^ 1, abort_flag, FSITE_TMA)) break;
-      if (lane == 0) {
+    // Only lane 0 works; the other lanes go straight to the end of the role (32 lanes polling a
+    // barrier cost issue slots and barrier-unit bandwidth that the other warps need).
+    if (lane == 0) {
+      for (int i = 0; i < nst; ++i) {
+        const int s = i % kFStages;
+        if (!mbar_wait(&empty[s], ((i / kFStages) & 1) ^ 1, abort_flag, FSITE_TMA)) break;
         mbar_expect_tx(&full[s], 2 * kFTileBytes + 2 * kSfBytes);
         tma_load_2d(smem + C::kOffA + s * kFTileBytes, &tm_w, (st_begin + i) * 128, n0, &full[s], pol);
         tma_load_2d(smem + C::kOffB + s * kFTileBytes, &tm_x, (st_begin + i) * 128, t0, &full[s], pol);
@@ -148,15 +150,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         bulk_load_1d(smem + C::kOffSFB + s * 2048, sfx_tile + static_cast<size_t>(i) * kSfBytes,
                      kSfBytes, &full[s], pol);
       }
-      __syncwarp();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
-    for (int i = 0; i < nst; ++i) {
-      const int s = i % kFStages;
-      if (!mbar_wait(&full[s], (i / kFStages) & 1, abort_flag, FSITE_MMA)) break;
-      tc_fence_after();
-      if (lane == 0) {
+    if (lane == 0) {  // only lane 0 works (see the producer)
+      for (int i = 0; i < nst; ++i) {
+        const int s = i % kFStages;
+        if (!mbar_wait(&full[s], (i / kFStages) & 1, abort_flag, FSITE_MMA)) break;
+        tc_fence_after();
         const uint32_t sfa_t = tmem_base + C::kSfColBase + s * 32;
         const uint32_t sfb_t = sfa_t + 16;
 #pragma unroll
@@ -177,7 +178,6 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         umma_commit(&empty[s]);
         if (i == nst - 1) umma_commit(acc_full);
       }
-      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -187,7 +187,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     int tok_cols = M - t0;
     if (tok_cols > kFTN) tok_cols = kFTN;
     const int col_end = (tok_cols + 31) & ~31;
-    const bool have_acc = (nst > 0) && mbar_wait(acc_full, 0, abort_flag, FSITE_EPI);
+    const bool have_acc = (nst > 0) && mbar_wait_relaxed(acc_full, 0, abort_flag, FSITE_EPI);
     if (have_acc) tc_fence_after();
     float rn = 0.f;
     if (n < N) {

@@ -145,6 +145,8 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     // (they come from the quantiser): fill the ring with weights first, then wait for the
     // prerequisite grid, then fetch the activation tiles of those stages.
     const int prefill = (nst < stages) ? nst : stages;
+    // Only lane 0 works; the other lanes go straight to the end of the role (32 lanes polling a
+    // barrier cost issue slots and barrier-unit bandwidth that the compute warps need).
     if (lane == 0) {
       for (int i = 0; i < prefill; ++i) {
         uint8_t* st = smem + i * C::kStage;
@@ -155,19 +157,14 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         bulk_load_1d(st + C::kOffW, w_src + static_cast<size_t>(i) * kVGS * kTileBytes, wbytes,
                      &full[i], pol_w);
       }
-    }
-    grid_dep_wait();
-    if (lane == 0) {
+      grid_dep_wait();
       for (int i = 0; i < prefill; ++i)
         tma_load_2d(smem + i * C::kStage + C::kOffX, &tm_x, (g_begin + i * kVGS) * kGroup, 0,
                     &full[i], pol_x);
-    }
-    __syncwarp();
-    int s = (prefill == stages) ? 0 : prefill;
-    uint32_t ph = (prefill == stages) ? 0u : 1u;  // parity of the "stage is free" phase waited for
-    for (int i = prefill; i < nst; ++i) {
-      if (!mbar_wait(&empty[s], ph, abort_flag, VSITE_PRODUCER)) break;
-      if (lane == 0) {
+      int s = (prefill == stages) ? 0 : prefill;
+      uint32_t ph = (prefill == stages) ? 0u : 1u;  // parity of the "stage is free" phase waited for
+      for (int i = prefill; i < nst; ++i) {
+        if (!mbar_wait(&empty[s], ph, abort_flag, VSITE_PRODUCER)) break;
         uint8_t* st = smem + s * C::kStage;
         int cnt = ng - i * kVGS;
         if (cnt > kVGS) cnt = kVGS;
@@ -176,9 +173,8 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         bulk_load_1d(st + C::kOffW, w_src + static_cast<size_t>(i) * kVGS * kTileBytes, wbytes,
                      &full[s], pol_w);
         tma_load_2d(st + C::kOffX, &tm_x, (g_begin + i * kVGS) * kGroup, 0, &full[s], pol_x);
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
-      __syncwarp();
-      if (++s == stages) { s = 0; ph ^= 1u; }
     }
   } else {
     // ------------------------------------------------------------------ compute warps
