@@ -140,13 +140,12 @@ enum { SITE_TMA = 1, SITE_UNPACK_FULL, SITE_UNPACK_FREE, SITE_MMA_READY, SITE_MM
 //                          all epilogue warps (EW + 1 arrivals; the epilogue pre-arrives once)
 //   done[b]                UMMAs of the group finished (tcgen05.commit): the epilogue may read
 //                          accumulator b, the unpack warp may overwrite buffer b
-template <int TN, bool DUMP>
+template <int TN>
 __global__ void __launch_bounds__(Cfg<TN>::kThreads, Cfg<TN>::kMinCtas)
 gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
                       const __half* __restrict__ sw_t, const float* __restrict__ r,
-                      const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
-                      int32_t* __restrict__ acc_dump, int M, int N, int K, int groups_per_split,
+                      const float* __restrict__ sx, void* __restrict__ y, int y_bf16, int M, int N, int K, int groups_per_split,
                       int split_k, int w_stream_once, int* status DQ_TRACE_PARAM) {
   using C = Cfg<TN>;
   // The 128-byte swizzle of the UMMA operands needs the buffers on 1 KB boundaries.  The kernel has
@@ -170,13 +169,32 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int n0 = blockIdx.x * kBN;
-  const int t0 = blockIdx.y * TN;
   const int total_groups = K / kGroup;
   const int g_begin = blockIdx.z * groups_per_split;
   int g_end = g_begin + groups_per_split;
   if (g_end > total_groups) g_end = total_groups;
   const int ng = (g_end > g_begin) ? (g_end - g_begin) : 0;
+  // Tile walk.  Without split-K the grid is persistent: CTA c takes the output tiles c,
+  // c + gridDim.x, ... of the list ordered token tile fastest (CTAs that run together share a
+  // few weight tiles and the activations through L2), and its pipeline runs on from one tile
+  // into the next: the global group counter gi = (tile iteration) * ng + i indexes every ring and
+  // barrier phase.  With split-K every CTA owns one tile (grid x = row tile, y = token tile).
+  const int tok_tiles = (M + TN - 1) / TN;
+  const int n_tiles = ((N + kBN - 1) / kBN) * tok_tiles;
+  const bool persistent = (split_k == 1);
+  const int tile0 = persistent ? static_cast<int>(blockIdx.x)
+                               : static_cast<int>(blockIdx.x) * tok_tiles + static_cast<int>(blockIdx.y);
+  const int tile_step = persistent ? static_cast<int>(gridDim.x) : n_tiles;
+  const int my_tiles = (tile0 < n_tiles) ? (n_tiles - tile0 + tile_step - 1) / tile_step : 0;
+  const int my_groups = my_tiles * ng;
+  const int nxs = (ng + C::XC - 1) / C::XC;  // activation stages per tile
+  auto tile_row = [&](int it) { return (tile0 + it * tile_step) / tok_tiles; };  // 128-row tile index
+  auto tile_tok = [&](int it) { return (tile0 + it * tile_step) % tok_tiles; };  // token tile index
+  // packed tile of global group gi: tiles of a row tile are contiguous along K
+  auto w_group = [&](int gi) {
+    return w_packed + (static_cast<size_t>(tile_row(gi / ng)) * static_cast<size_t>(total_groups) +
+                       static_cast<size_t>(g_begin + gi % ng)) * kTileBytes;
+  };
 
   if (tid == 0) {
     for (int i = 0; i < C::SP; ++i) mbar_init(&full_p[i], 1);
@@ -195,10 +213,6 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-
-  // tiles of this CTA's 128 rows are contiguous along K: [row tile][group][8 KB codes + scales]
-  const uint8_t* w_tile =
-      w_packed + static_cast<size_t>(blockIdx.x) * static_cast<size_t>(total_groups) * kTileBytes;
 
   float run[C::CPW];  // epilogue running sums (only epilogue warps use them)
 #pragma unroll
@@ -220,7 +234,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     // consecutive groups at once, so the wait / expand / proxy-fence / arrive chain of a group,
     // which is latency and not throughput, overlaps with that of its neighbours.
     const uint64_t pol_w = w_stream_once ? l2_policy_evict_first() : l2_policy_evict_last();
-    for (int i = warp; i < ng; i += kUnpackWarps) {
+    for (int i = warp; i < my_groups; i += kUnpackWarps) {  // i: global group index
       const int sp = i % C::SP, b = i % C::NB;
       if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
       if (lane == 0) DQ_TR(0, i, 0);
@@ -256,10 +270,9 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         mbar_arrive(&ready[b]);
         // The stage belongs to this warp (SP is a multiple of the unpack warp count): refill it
         // for group i + SP right away instead of handing it back to the producer warp.
-        if (i + C::SP < ng) {
+        if (i + C::SP < my_groups) {
           mbar_expect_tx(&full_p[sp], kWpBytes);
-          bulk_load_1d(smem + C::kOffP + sp * kWpBytes,
-                       w_tile + static_cast<size_t>(g_begin + i + C::SP) * kTileBytes, kWpBytes,
+          bulk_load_1d(smem + C::kOffP + sp * kWpBytes, w_group(i + C::SP), kWpBytes,
                        &full_p[sp], pol_w);
           DQ_TR(3, i + C::SP, 0);
         }
@@ -270,77 +283,52 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;          // TMEM lane quarter this warp may read
     const int h = (warp - kUnpackWarps) >> 2;  // which slice of the token columns
-    const int n = n0 + q * 32 + lane;
-    const bool n_ok = n < N;
     if (lane == 0) {  // every accumulator starts out free
 #pragma unroll
       for (int b = 0; b < C::NB; ++b) mbar_arrive(&ready[b]);
-    }
-    // Group scales of this thread's weight row, [row tile][group][128] in memory.  A new 256-byte
-    // run is touched every stage, so loads are issued kScaleAhead stages early.
-    // The ring holds the raw fp16 bits: converting at load time would make the warp wait for the
-    // load at once; the conversion happens when the group comes up.
-    constexpr int kScaleAhead = 4;
-    const unsigned short* sw_row = nullptr;
-    unsigned short sq[kScaleAhead];
-#pragma unroll
-    for (int d = 0; d < kScaleAhead; ++d) sq[d] = 0;
-    if constexpr (!DUMP) {
-      sw_row = reinterpret_cast<const unsigned short*>(sw_t) +
-               (static_cast<size_t>(blockIdx.x) * total_groups + g_begin) * kBN + q * 32 + lane;
-#pragma unroll
-      for (int d = 0; d < kScaleAhead; ++d)
-        if (d < ng) sq[d] = __ldg(sw_row + static_cast<size_t>(d) * kBN);
     }
     auto ld_chunk = [&](int b, int c0, uint32_t* v) {
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(b * TN + h * C::CPW + c0);
       tmem_ld_x8(taddr, v);
     };
-    auto consume = [&](const uint32_t* v, int c0, int i, float s) {
-      if constexpr (DUMP) {
-        if (n_ok) {
+    auto consume = [&](const uint32_t* v, int c0, float s) {
+      // two columns per instruction: packed fp32 FMA (each half rounds like a scalar fmaf)
 #pragma unroll
-          for (int j = 0; j < C::CH; ++j) {
-            const int m = t0 + h * C::CPW + c0 + j;
-            if (m < M)
-              acc_dump[(static_cast<size_t>(m) * N + n) * total_groups + (g_begin + i)] =
-                  static_cast<int32_t>(v[j]) >> 4;
-          }
-        }
-      } else {
-        // two columns per instruction: packed fp32 FMA (each half rounds like a scalar fmaf)
-#pragma unroll
-        for (int j = 0; j < C::CH; j += 2) {
-          const float2 f = make_float2(static_cast<float>(static_cast<int32_t>(v[j])),
-                                       static_cast<float>(static_cast<int32_t>(v[j + 1])));
-          const float2 acc2 = __ffma2_rn(f, make_float2(s, s), make_float2(run[c0 + j], run[c0 + j + 1]));
-          run[c0 + j] = acc2.x;
-          run[c0 + j + 1] = acc2.y;
-        }
+      for (int j = 0; j < C::CH; j += 2) {
+        const float2 f = make_float2(static_cast<float>(static_cast<int32_t>(v[j])),
+                                     static_cast<float>(static_cast<int32_t>(v[j + 1])));
+        const float2 acc2 = __ffma2_rn(f, make_float2(s, s), make_float2(run[c0 + j], run[c0 + j + 1]));
+        run[c0 + j] = acc2.x;
+        run[c0 + j + 1] = acc2.y;
       }
     };
+    // Group scales of this thread's weight row, [row tile][group][128] in memory.  A new 256-byte
+    // run is touched every group, so loads are issued kScaleAhead groups early.  The ring holds
+    // the raw fp16 bits: converting at load time would make the warp wait for the load at once;
+    // the conversion happens when the group comes up.
+    constexpr int kScaleAhead = 4;
+    const unsigned short* sw_row = nullptr;
+    unsigned short sq[kScaleAhead];
     // The accumulator of a group is read in chunks of 8 columns.  tcgen05.ld is asynchronous, so
     // chunk c + 1 is in flight while chunk c is scaled and added, and as soon as the accumulator
-    // is drained the first chunk of the next group is requested (if its UMMAs have finished)
-    // before the last chunk of this one is consumed.
+    // is drained the first chunk of the next group (of this tile or the next) is requested, if its
+    // UMMAs have finished, before the last chunk of this one is consumed.
     uint32_t va[C::CH], vb[C::CH];
     bool prefetched = false;
-    // One group; `sreg` is this group's slot of the scale ring, refilled for group i + kScaleAhead
-    // right after it is read (the loop below is unrolled by the ring size, so slots are
-    // registers with static indices and no load is waited for before its group comes up).
-    auto group_step = [&](int i, unsigned short& sreg) -> bool {
-      const int b = i % C::NB;
+    // One group; i = index inside the tile, gi = global index (rings and phases).  `sreg` is this
+    // group's slot of the scale ring, refilled for group i + kScaleAhead right after it is read
+    // (the loop below is unrolled by the ring size, so slots are registers with static indices).
+    auto group_step = [&](int i, int gi, unsigned short& sreg) -> bool {
+      const int b = gi % C::NB;
       const float s = __half2float(__ushort_as_half(sreg)) * 0.0625f;
-      if constexpr (!DUMP) {
-        if (i + kScaleAhead < ng) sreg = __ldg(sw_row + static_cast<size_t>(i + kScaleAhead) * kBN);
-      }
+      if (i + kScaleAhead < ng) sreg = __ldg(sw_row + static_cast<size_t>(i + kScaleAhead) * kBN);
       if (!prefetched) {
-        if (!mbar_wait(&done[b], (i / C::NB) & 1, abort_flag, SITE_EPI)) return false;
+        if (!mbar_wait(&done[b], (gi / C::NB) & 1, abort_flag, SITE_EPI)) return false;
         tc_fence_after();
         ld_chunk(b, 0, va);
       }
-      if (tid == 128) DQ_TR(1, i, 0);
+      if (tid == 128) DQ_TR(1, gi, 0);
 #pragma unroll
       for (int c = 0; c < C::NCH; ++c) {  // chunk c lives in va (c even) or vb (c odd)
         uint32_t* cur = (c & 1) ? vb : va;
@@ -349,17 +337,17 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         if (c + 1 < C::NCH) {
           ld_chunk(b, (c + 1) * C::CH, nxt);
         } else {
-          if (tid == 128) DQ_TR(1, i, 1);
+          if (tid == 128) DQ_TR(1, gi, 1);
           // accumulator b is free once its last column has been read
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&ready[b]);
           if constexpr (C::NCH > 1) {  // NCH is even: the next group's first chunk goes to va
             prefetched = false;
-            if (i + 1 < ng) {
-              const int b1 = (i + 1) % C::NB;
+            if (gi + 1 < my_groups) {
+              const int b1 = (gi + 1) % C::NB;
               // tcgen05.ld is warp-collective: take the early path only if every lane saw the phase
-              if (__all_sync(0xffffffffu, mbar_test_wait(&done[b1], ((i + 1) / C::NB) & 1) ? 1 : 0)) {
+              if (__all_sync(0xffffffffu, mbar_test_wait(&done[b1], ((gi + 1) / C::NB) & 1) ? 1 : 0)) {
                 tc_fence_after();
                 ld_chunk(b1, 0, nxt);
                 prefetched = true;
@@ -367,21 +355,31 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
             }
           }
         }
-        consume(cur, c * C::CH, i, s);
+        consume(cur, c * C::CH, s);
       }
-      if (tid == 128) DQ_TR(1, i, 2);
+      if (tid == 128) DQ_TR(1, gi, 2);
       return true;
     };
     bool ok = true;
-    for (int i0 = 0; i0 < ng && ok; i0 += kScaleAhead) {
+    for (int it = 0; it < my_tiles && ok; ++it) {
+      const int row_tile = tile_row(it);
+      const int n = row_tile * kBN + q * 32 + lane;
+      const int t0 = tile_tok(it) * TN;
 #pragma unroll
-      for (int u = 0; u < kScaleAhead; ++u) {
-        if (ok && i0 + u < ng) ok = group_step(i0 + u, sq[u]);
+      for (int j = 0; j < C::CPW; ++j) run[j] = 0.f;
+      sw_row = reinterpret_cast<const unsigned short*>(sw_t) +
+               (static_cast<size_t>(row_tile) * total_groups + g_begin) * kBN + q * 32 + lane;
+#pragma unroll
+      for (int d = 0; d < kScaleAhead; ++d) sq[d] = (d < ng) ? __ldg(sw_row + static_cast<size_t>(d) * kBN) : 0;
+      for (int i0 = 0; i0 < ng && ok; i0 += kScaleAhead) {
+#pragma unroll
+        for (int u = 0; u < kScaleAhead; ++u) {
+          if (ok && i0 + u < ng) ok = group_step(i0 + u, it * ng + i0 + u, sq[u]);
+        }
       }
-    }
-    if constexpr (!DUMP) {
+      if (!ok) break;
       if (split_k == 1) {
-        if (n_ok) {
+        if (n < N) {
           const float rn = (r != nullptr) ? r[n] : 1.f;
 #pragma unroll
           for (int j = 0; j < C::CPW; ++j) {
@@ -415,24 +413,26 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     // Only lane 0 works; the other lanes go straight to the end of the role (a waiting warp of
     // 32 polling lanes costs the SM issue slots and barrier-unit bandwidth the other roles need).
     if (lane == 0) {
-      const int pre = (ng < C::SP) ? ng : C::SP;
-      for (int iw = 0; iw < pre; ++iw) {
-        mbar_expect_tx(&full_p[iw], kWpBytes);
-        bulk_load_1d(smem + C::kOffP + iw * kWpBytes,
-                     w_tile + static_cast<size_t>(g_begin + iw) * kTileBytes, kWpBytes,
-                     &full_p[iw], pol_w);
+      const int pre = (my_groups < C::SP) ? my_groups : C::SP;
+      for (int gi = 0; gi < pre; ++gi) {
+        mbar_expect_tx(&full_p[gi], kWpBytes);
+        bulk_load_1d(smem + C::kOffP + gi * kWpBytes, w_group(gi), kWpBytes, &full_p[gi], pol_w);
       }
       grid_dep_wait();
-      const int nxs = (ng + C::XC - 1) / C::XC;  // activation stages
-      for (int ix = 0; ix < nxs; ++ix) {
-        const int sxi = ix % C::SX;
-        if (!mbar_wait(&empty_x[sxi], ((ix / C::SX) & 1) ^ 1, abort_flag, SITE_TMA)) break;
-        // one box = XC groups x TN tokens; groups past the end of K are zero-filled and still
-        // counted, so the byte count is always that of the full box
-        mbar_expect_tx(&full_x[sxi], C::kXStageBytes);
-        tma_load_3d(smem + C::kOffX + sxi * C::kXStageBytes, &tm_x, 0, t0, g_begin + ix * C::XC,
-                    &full_x[sxi], pol_x);
-        DQ_TR(3, ix, 1);
+      bool ok = true;
+      for (int it = 0; it < my_tiles && ok; ++it) {
+        const int t0 = tile_tok(it) * TN;
+        for (int ix = 0; ix < nxs; ++ix) {
+          const int xs = it * nxs + ix;  // global activation-stage index
+          const int sxi = xs % C::SX;
+          if (!mbar_wait(&empty_x[sxi], ((xs / C::SX) & 1) ^ 1, abort_flag, SITE_TMA)) { ok = false; break; }
+          // one box = XC groups x TN tokens; groups past the end of K are zero-filled and still
+          // counted, so the byte count is always that of the full box
+          mbar_expect_tx(&full_x[sxi], C::kXStageBytes);
+          tma_load_3d(smem + C::kOffX + sxi * C::kXStageBytes, &tm_x, 0, t0, g_begin + ix * C::XC,
+                      &full_x[sxi], pol_x);
+          DQ_TR(3, xs, 1);
+        }
       }
     }
   } else if (warp < C::kIssuerWarp0 + C::kIssuers) {
@@ -440,18 +440,19 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     constexpr uint32_t idesc = umma_idesc_i8(kBN, TN);
     const uint32_t a_base = smem_u32(smem + C::kOffA);
     const uint32_t x_base = smem_u32(smem + C::kOffX);
-    // The groups alternate between the two issuing warps; accumulator b, buffer b and activation
-    // stage i % SX of a group are always waited for and released by the same warp.
+    // The (global) groups alternate between the two issuing warps; accumulator b, buffer b and
+    // the activation stage of a group are always waited for and released by the same warp.
     if (lane == 0) {  // only lane 0 works (see the producer)
-      for (int i = warp - C::kIssuerWarp0; i < ng; i += C::kIssuers) {
-        const int b = i % C::NB;
-        const int xs = i / C::XC, xj = i % C::XC, sxi = xs % C::SX;
-        if (!mbar_wait(&ready[b], (i / C::NB) & 1, abort_flag, SITE_MMA_READY)) break;
-        DQ_TR(2, i, 0);
+      for (int gi = warp - C::kIssuerWarp0; gi < my_groups; gi += C::kIssuers) {
+        const int it = gi / ng, i = gi % ng;  // tile iteration, group inside the tile
+        const int b = gi % C::NB;
+        const int xs = it * nxs + i / C::XC, xj = i % C::XC, sxi = xs % C::SX;
+        if (!mbar_wait(&ready[b], (gi / C::NB) & 1, abort_flag, SITE_MMA_READY)) break;
+        DQ_TR(2, gi, 0);
         if (xj == 0 || C::kIssuers > 1) {
           if (!mbar_wait(&full_x[sxi], (xs / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
         }
-        DQ_TR(2, i, 1);
+        DQ_TR(2, gi, 1);
         tc_fence_after();
         const uint64_t da = umma_desc_k_sw128(a_base + b * kWaBytes);
         const uint64_t db = umma_desc_k_sw128(x_base + sxi * C::kXStageBytes + xj * C::kXBytes);
@@ -459,19 +460,20 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // +32 bytes along K inside the swizzle atom = +2 (>>4)
           umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk > 0 ? 1u : 0u);
-        DQ_TR(2, i, 2);
+        DQ_TR(2, gi, 2);
         umma_commit(&done[b]);
         if (xj == C::XC - 1 || i == ng - 1) umma_commit(&empty_x[sxi]);
-        DQ_TR(2, i, 3);
+        DQ_TR(2, gi, 3);
       }
     }
   }
 
   // -------------------------------------------------------------------- split-K reduction
-  if (!DUMP && split_k > 1) {
+  if (split_k > 1) {
     __syncwarp();
     cluster_sync_all();
     if (warp >= kUnpackWarps && warp < kUnpackWarps + 8) {
+      const int n0 = tile_row(0) * kBN, t0 = tile_tok(0) * TN;  // split-K: one tile per CTA
       const uint32_t rank = cluster_ctarank();
       const int rows = TN / split_k;  // token rows of the tile this CTA finishes
       const int e = tid - 4 * 32;     // 0..255
@@ -523,9 +525,9 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-template <int TN, bool DUMP>
+template <int TN>
 static int set_attr() {
-  cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_int4_kernel<TN, DUMP>,
+  cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_int4_kernel<TN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<TN>::kSmemBytes);
   if (e != cudaSuccess)
@@ -536,10 +538,10 @@ static int set_attr() {
 
 int init_gemm_int4_kernels() {
   int rc;
-  if ((rc = set_attr<16, false>()) != DQ_OK) return rc;
-  if ((rc = set_attr<32, false>()) != DQ_OK) return rc;
-  if ((rc = set_attr<64, false>()) != DQ_OK) return rc;
-  if ((rc = set_attr<128, false>()) != DQ_OK) return rc;
+  if ((rc = set_attr<16>()) != DQ_OK) return rc;
+  if ((rc = set_attr<32>()) != DQ_OK) return rc;
+  if ((rc = set_attr<64>()) != DQ_OK) return rc;
+  if ((rc = set_attr<128>()) != DQ_OK) return rc;
   return DQ_OK;
 }
 
@@ -561,10 +563,10 @@ static int pick_split(int tiles, int total_groups, int tn, int sm_count) {
   return s;
 }
 
-template <int TN, bool DUMP>
+template <int TN>
 static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed, const __half* sw_t,
-                  const float* r, int M, int N, int K, void* y, int y_dtype, int32_t* acc_dump,
-                  int split, cudaStream_t stream, DeviceState* st) {
+                  const float* r, int M, int N, int K, void* y, int y_dtype, int split,
+                  cudaStream_t stream, DeviceState* st) {
   CUtensorMap tm_x;
   int rc = make_tmap_x_groups(&tm_x, codes, K, M, TN, Cfg<TN>::XC);
   if (rc != DQ_OK) return rc;
@@ -573,7 +575,15 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   const int gps = (total_groups + split - 1) / split;
   const int tok_tiles = (M + TN - 1) / TN;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + kBN - 1) / kBN, tok_tiles, split);
+  const int row_tiles = (N + kBN - 1) / kBN;
+  if (split == 1) {
+    // persistent: one CTA per slot of the machine, each walks the tile list with that stride
+    const int slots = st->sm_count * Cfg<TN>::kMinCtas;
+    const int tiles = row_tiles * tok_tiles;
+    cfg.gridDim = dim3(tiles < slots ? tiles : slots, 1, 1);
+  } else {
+    cfg.gridDim = dim3(row_tiles, tok_tiles, split);
+  }
   cfg.blockDim = dim3(Cfg<TN>::kThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg<TN>::kSmemBytes;
   cfg.stream = stream;
@@ -587,8 +597,8 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN, DUMP>, w_packed, tm_x, sw_t, r, sx,
-                                     y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, acc_dump, M, N, K, gps,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN>, w_packed, tm_x, sw_t, r, sx,
+                                     y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, gps,
                                      split, w_stream_once, st->status_dev DQ_TRACE_ARG);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_w4a4_int4 launch failed (TN=%d split=%d): %s", TN, split,
@@ -672,10 +682,10 @@ extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const 
   if (use_tm)
     return launch_gemm_int4_tm(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, nullptr, tn, split, s, st);
   switch (tn) {
-    case 16: return launch<16, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
-    case 32: return launch<32, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
-    case 64: return launch<64, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
-    default: return launch<128, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
+    case 16: return launch<16>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
+    case 32: return launch<32>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
+    case 64: return launch<64>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
+    default: return launch<128>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
   }
 }
 
