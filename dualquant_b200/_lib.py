@@ -65,6 +65,7 @@ SIGNATURES = {
     "dq_fakequant_act_int4": (_i, [_vp, _i, _i64, _vp, _hp, _i, _i, _vp, _i, _vp]),
     "dq_hadamard_f32": (_i, [_vp, _vp, _i, _i, _hp, _vp]),
     "dq_quant_fp4": (_i, [_vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "dq_quant_fp4_atoms": (_i, [_vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "dq_fakequant_fp4": (_i, [_vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "dq_nvfp4_tensor_scale": (_i, [_vp, _i, _i64, _vp, _vp]),
     "dq_fp4_sf_atoms_bytes": (_sz, [_i, _i, _i]),

@@ -73,9 +73,24 @@ __global__ void __launch_bounds__(THREADS)
 quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K, int fmt,
                  const float* __restrict__ tensor_scale, uint8_t* __restrict__ codes,
                  uint8_t* __restrict__ sf, float* __restrict__ row_scale, float* __restrict__ out,
-                 int mode) {
+                 int mode, int M, int sf_atoms) {
   __shared__ float red[THREADS / 32];
   const int row = blockIdx.x;
+  // sf_atoms: the scale bytes go straight into the order the GEMM streams,
+  // [row tile of 128][k / (4 blocks)][(r % 32) * 16 + (r / 32) * 4 + block % 4]; the grid then
+  // covers the rows up to the next multiple of 128 and the CTAs past M write zero scales.
+  const int blk_sz = (fmt == DQ_FP4_MXFP4) ? 32 : 16;
+  const int nsf = K / blk_sz;
+  auto sf_offset = [&](int ksf) -> int64_t {
+    if (!sf_atoms) return static_cast<int64_t>(row) * nsf + ksf;
+    const int rr = row & 127;
+    return (static_cast<int64_t>(row >> 7) * (nsf >> 2) + (ksf >> 2)) * 512 + (rr & 31) * 16 +
+           (rr >> 5) * 4 + (ksf & 3);
+  };
+  if (row >= M) {
+    for (int ksf = threadIdx.x; ksf < nsf; ksf += THREADS) sf[sf_offset(ksf)] = 0;
+    return;
+  }
   const XT* xr = x + static_cast<int64_t>(row) * ldx;
   float v[VPT][8];
   float bmax[VPT];
@@ -151,7 +166,7 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
     for (int k = 0; k < 4; ++k) packed |= e2m1x2(q[2 * k], q[2 * k + 1]) << (8 * k);
     if (mode == FP4_MODE_CODES) {
       *reinterpret_cast<uint32_t*>(codes + static_cast<int64_t>(row) * (K / 2) + idx / 2) = packed;
-      if ((idx % blk) == 0) sf[static_cast<int64_t>(row) * (K / blk) + idx / blk] = static_cast<uint8_t>(sf_byte);
+      if ((idx % blk) == 0) sf[sf_offset(idx / blk)] = static_cast<uint8_t>(sf_byte);
     } else {
       float o[8];
 #pragma unroll
@@ -185,7 +200,7 @@ __global__ void nvfp4_scale_finalize_kernel(float* scale) {
 template <typename XT>
 static int launch_fp4(const XT* x, int64_t ldx, const float* a, int M, int K, int fmt,
                       const float* tensor_scale, uint8_t* codes, uint8_t* sf, float* row_scale,
-                      float* out, int mode, cudaStream_t stream) {
+                      float* out, int mode, cudaStream_t stream, int sf_atoms = 0) {
   DQ_REQUIRE(fmt == DQ_FP4_MXFP4 || fmt == DQ_FP4_NVFP4, DQ_ERR_UNSUPPORTED, "unknown FP4 format %d", fmt);
   DQ_REQUIRE(x != nullptr, DQ_ERR_NULL, "x is null");
   const int blk = (fmt == DQ_FP4_MXFP4) ? 32 : 16;
@@ -196,9 +211,13 @@ static int launch_fp4(const XT* x, int64_t ldx, const float* a, int M, int K, in
   DQ_REQUIRE((codes == nullptr || aligned(codes, 4)) && (out == nullptr || aligned(out, 16)), DQ_ERR_ALIGN,
              "outputs misaligned");
   if (M == 0) return DQ_OK;
+  DQ_REQUIRE(!sf_atoms || (K / blk) % 4 == 0, DQ_ERR_SHAPE,
+             "scale factors in GEMM order need K %% %d == 0 (K=%d)", 4 * blk, K);
   const int vec = K / 8;
-#define DQ_FP4_LAUNCH(T, V) \
-  quant_fp4_kernel<T, V, XT><<<M, T, 0, stream>>>(x, ldx, a, K, fmt, tensor_scale, codes, sf, row_scale, out, mode)
+  const int rows = sf_atoms ? (M + 127) / 128 * 128 : M;
+#define DQ_FP4_LAUNCH(T, V)                                                                        \
+  quant_fp4_kernel<T, V, XT><<<rows, T, 0, stream>>>(x, ldx, a, K, fmt, tensor_scale, codes, sf, row_scale, \
+                                                     out, mode, M, sf_atoms)
   if (vec <= 128) DQ_FP4_LAUNCH(128, 1);
   else if (vec <= 256) DQ_FP4_LAUNCH(256, 1);
   else if (vec <= 512) DQ_FP4_LAUNCH(512, 1);
@@ -226,6 +245,20 @@ extern "C" int dq_quant_fp4(const void* x, int x_is_f32, int64_t ldx, const floa
                       row_scale, nullptr, FP4_MODE_CODES, s);
   return launch_fp4(static_cast<const __nv_bfloat16*>(x), ldx, a, M, K, fmt, tensor_scale, codes, sf,
                     row_scale, nullptr, FP4_MODE_CODES, s);
+}
+
+extern "C" int dq_quant_fp4_atoms(const void* x, int x_is_f32, int64_t ldx, const float* a, int M,
+                                  int K, int fmt, const float* tensor_scale, uint8_t* codes,
+                                  uint8_t* sf_atoms, float* row_scale, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  DQ_REQUIRE(codes != nullptr && sf_atoms != nullptr, DQ_ERR_NULL, "codes / sf_atoms is null");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (x_is_f32)
+    return launch_fp4(static_cast<const float*>(x), ldx, a, M, K, fmt, tensor_scale, codes, sf_atoms,
+                      row_scale, nullptr, FP4_MODE_CODES, s, 1);
+  return launch_fp4(static_cast<const __nv_bfloat16*>(x), ldx, a, M, K, fmt, tensor_scale, codes,
+                    sf_atoms, row_scale, nullptr, FP4_MODE_CODES, s, 1);
 }
 
 extern "C" int dq_fakequant_fp4(const void* x, int x_is_f32, int64_t ldx, const float* a, int M,

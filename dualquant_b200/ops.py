@@ -307,18 +307,25 @@ def _fp4_block(fmt: int) -> int:
 
 
 def quant_fp4(x: torch.Tensor, fmt: int, a: Optional[torch.Tensor] = None,
-              tensor_scale: Optional[torch.Tensor] = None):
-    """[M,K] bf16/fp32 -> (codes uint8 [M,K/2], sf uint8 [M,K/block], row_scale fp32 [M] or None)."""
+              tensor_scale: Optional[torch.Tensor] = None, atoms: bool = False):
+    """[M,K] bf16/fp32 -> (codes uint8 [M,K/2], sf uint8 [M,K/block], row_scale fp32 [M] or None).
+    atoms=True: the scale bytes come back flat, already in the order the GEMM streams."""
     lib = _prep(x)
     if x.dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("quant_fp4 expects bf16 or fp32")
     x = x.contiguous()
     M, K = x.shape
     codes = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
-    sf = torch.empty(M, K // _fp4_block(fmt), dtype=torch.uint8, device=x.device)
     row_scale = None
     if fmt == _lib.FP4_NVFP4 and tensor_scale is None:
         row_scale = torch.empty(M, dtype=torch.float32, device=x.device)
+    if atoms:
+        sf = torch.empty(int(lib.dq_fp4_sf_atoms_bytes(M, K, fmt)), dtype=torch.uint8, device=x.device)
+        _lib.check(lib.dq_quant_fp4_atoms(_ptr(x), int(x.dtype == torch.float32), K, _ptr(a), M, K, fmt,
+                                          _ptr(tensor_scale), _ptr(codes), _ptr(sf), _ptr(row_scale),
+                                          _stream(x.device)), "dq_quant_fp4_atoms")
+        return codes, sf, row_scale
+    sf = torch.empty(M, K // _fp4_block(fmt), dtype=torch.uint8, device=x.device)
     _lib.check(lib.dq_quant_fp4(_ptr(x), int(x.dtype == torch.float32), K, _ptr(a), M, K, fmt,
                                 _ptr(tensor_scale), _ptr(codes), _ptr(sf), _ptr(row_scale),
                                 _stream(x.device)), "dq_quant_fp4")
@@ -400,5 +407,5 @@ def gemm_w4a4_fp4(x_codes: torch.Tensor, x_sf_atoms: torch.Tensor, x_scale: Opti
 def linear_w4a4_fp4(x: torch.Tensor, a: Optional[torch.Tensor], pw: PackedFp4Weight,
                     r: Optional[torch.Tensor] = None, out_dtype=torch.float32) -> torch.Tensor:
     """Quantise activations (per-token second-level scale for NVFP4) and run the FP4 GEMM."""
-    codes, sf, row_scale = quant_fp4(x, pw.fmt, a, None)
-    return gemm_w4a4_fp4(codes, fp4_sf_to_atoms(sf, pw.K, pw.fmt), row_scale, pw, r, out_dtype)
+    codes, sf_atoms, row_scale = quant_fp4(x, pw.fmt, a, None, atoms=True)
+    return gemm_w4a4_fp4(codes, sf_atoms, row_scale, pw, r, out_dtype)

@@ -178,6 +178,16 @@ DQ_API int dq_quant_fp4(const void* x, int x_is_f32, int64_t ldx, const float* a
                         int fmt, const float* tensor_scale, uint8_t* codes, uint8_t* sf,
                         float* row_scale, void* stream);
 
+/*
+ * dq_quant_fp4 with the scale bytes written straight into the order dq_gemm_w4a4_fp4 streams
+ * (what dq_fp4_sf_to_atoms would produce from the row-major bytes): sf_atoms has
+ * dq_fp4_sf_atoms_bytes(M, K, fmt) bytes, rows past M of the last 128-row tile are written as
+ * zero.  Needs K % 128 == 0 (MXFP4) / K % 64 == 0 (NVFP4).  Saves one pass per activation.
+ */
+DQ_API int dq_quant_fp4_atoms(const void* x, int x_is_f32, int64_t ldx, const float* a, int M, int K,
+                              int fmt, const float* tensor_scale, uint8_t* codes, uint8_t* sf_atoms,
+                              float* row_scale, void* stream);
+
 /* Same arithmetic, de-quantised fp32 [M,K] out: what FormatSpec.cast returns for mxfp4 / nvfp4. */
 DQ_API int dq_fakequant_fp4(const void* x, int x_is_f32, int64_t ldx, const float* a, int M, int K,
                             int fmt, const float* tensor_scale, float* out, void* stream);

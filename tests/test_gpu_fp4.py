@@ -135,3 +135,16 @@ def test_fp4_gemm_matches_dequant_matmul(fmt, M, N, K):
     ref = _fp4_reference(x, a, w, r, fmt)
     err = ((y.double().cpu() - ref).abs().max() / ref.abs().max()).item()
     assert err < 1e-3, err
+
+
+@pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
+@pytest.mark.parametrize("M,K", [(1, 256), (130, 512), (256, 1024), (37, 3584)])
+def test_quantiser_writes_scale_factors_in_gemm_order(fmt, M, K):
+    x = synthetic.make_x(M, K, M + K).to(DEV)
+    a = torch.exp(torch.randn(K, generator=torch.Generator().manual_seed(K)) * 0.3).to(DEV)
+    codes, sf, rs = ops.quant_fp4(x, fmt, a)
+    codes2, sf_atoms, rs2 = ops.quant_fp4(x, fmt, a, atoms=True)
+    assert torch.equal(codes, codes2)
+    assert (rs is None and rs2 is None) or torch.equal(rs, rs2)
+    # identical to the separate re-ordering pass, including the zero rows that pad the last tile
+    assert torch.equal(sf_atoms, ops.fp4_sf_to_atoms(sf, K, fmt).reshape(-1))
