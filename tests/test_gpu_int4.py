@@ -324,3 +324,37 @@ def test_quant_act_rmsnorm_rejects_bad_arguments():
         ops.quant_act_int4_rmsnorm(x, torch.ones(128, device=DEV).bfloat16(), 1e-5)
     with pytest.raises(ValueError):
         ops.quant_act_int4_rmsnorm(x, None, -1.0)
+
+
+# ------------------------------------------------------------------------------------------
+# every GEMM kernel forms the same fp32 sums in the same order
+# ------------------------------------------------------------------------------------------
+def test_all_gemm_kernels_bit_identical_on_random_shapes():
+    """Decode kernel, tensor-memory-operand and shared-memory-operand tcgen05 kernels at every
+    token tile: without split-K each adds float(acc_g) * sw_g in group order, so their outputs
+    must be equal bit for bit (a cheap detector for races in the pipelines)."""
+    import random
+    rnd = random.Random(0)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    for _ in range(60):
+        M = rnd.choice([1, 7, 8, 9, 16, 17, 32, 33, 64, 100, 128, 129, 300, 513])
+        N = rnd.choice([128, 136, 256, 640, 1024, 4096])
+        K = 128 * rnd.choice([1, 2, 3, 5, 8, 13, 32, 56])
+        codes = torch.randint(-8, 8, (M, K), generator=g, device=DEV, dtype=torch.int8)
+        sx = torch.rand(M, generator=g, device=DEV) + 0.5
+        wq = torch.randint(-8, 8, (N, K), generator=g, device=DEV, dtype=torch.int8)
+        sw = (torch.rand(N, K // 128, generator=g, device=DEV) * 0.02 + 0.001).half()
+        r = torch.rand(N, generator=g, device=DEV) + 0.5
+        pw = ops.pack_w_int4(wq, sw)
+        tiles = [t for t in (-8, -16, -32) if M <= -t]
+        for tn in (16, 32, 64, 128):
+            if tn == 16 and M > 64:
+                continue
+            tiles += [1000 + tn, 2000 + tn]
+        outs = [ops.gemm_w4a4_int4(codes, sx, pw, r, token_tile=t, split_k=1) for t in tiles]
+        for t, y in zip(tiles[1:], outs[1:]):
+            assert torch.equal(y, outs[0]), (M, N, K, tiles[0], t)
+        auto1 = ops.gemm_w4a4_int4(codes, sx, pw, r)
+        auto2 = ops.gemm_w4a4_int4(codes, sx, pw, r)
+        assert torch.equal(auto1, auto2), (M, N, K)
+    _status_ok()
