@@ -251,7 +251,8 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const int id = lane + (c8 + c) * 32;  // 16-byte chunk of the packed tile
-          const int row = id >> 2, ch = id & 3;
+          const int row = id >> 2;
+          const int ch = (id & 3) ^ ((row >> 1) & 3);  // position in the row -> k chunk
           const uint4 w = wv[c];
           uint4 lo, hi;
           lo.x = (w.x << 4) & 0xF0F0F0F0u; hi.x = w.x & 0xF0F0F0F0u;

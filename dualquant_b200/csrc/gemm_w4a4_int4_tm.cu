@@ -9,7 +9,8 @@
 //
 // The A operand (weights) never exists as int8 in shared memory.  The packed int4 tile arrives by
 // one bulk copy per pair of groups; each of four unpack warps owns one TMEM lane quarter
-// (32 weight rows), reads its rows from the packed stage (one row of 64 bytes per lane), expands
+// (32 weight rows), reads its rows from the packed stage (one row of 64 bytes per lane; the chunk
+// positions inside a row are swizzled in the artefact so that these loads are conflict-free), expands
 // nibbles to int8 (two's complement: (w << 4) & 0xF0.. / w & 0xF0.. = 16 * code, the 1/16 folded
 // into the group scale) and writes them with tcgen05.st into the operand region of tensor memory:
 // lane = row, 32-bit column j of a group's 32 columns = codes k = 4j .. 4j+3, lowest k in the low
@@ -224,7 +225,7 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
         if (h < cnt) {
           const uint4* src = reinterpret_cast<const uint4*>(stage + h * kTileBytes + row * 64);
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) raw[h][ch] = src[ch];
+          for (int ch = 0; ch < 4; ++ch) raw[h][ch] = src[ch ^ ((row >> 1) & 3)];  // swizzled position
         }
       }
       if (!mbar_wait(&a_free[ab], ((s / C::NA) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;

@@ -37,11 +37,14 @@ template <int NT>  // NT = number of 8-token blocks (tokens handled: 8 * NT)
 struct VCfg {
   static constexpr int TOK = 8 * NT;
   static constexpr int kXRows = (TOK < 16) ? 16 : TOK;       // rows of the activation tile box
-  static constexpr int kXPitch = kVGS * kGroup;               // bytes per token row in a stage
-  static constexpr int kXBytes = kXRows * kXPitch;
+  // Activation codes of a stage: [group][token row][128 B], 128-byte swizzle (one 3-D TMA box).
+  // Swizzled because token rows 128 bytes apart would otherwise put the 16-byte fragment loads
+  // of lanes with different token index on the same banks.
+  static constexpr int kXGroupBytes = kXRows * kGroup;
+  static constexpr int kXBytes = kVGS * kXGroupBytes;
   static constexpr int kOffX = 0;
   static constexpr int kOffW = kXBytes;                       // kVGS tiles of kTileBytes
-  static constexpr int kStage = (kOffW + kVGS * kTileBytes + 127) / 128 * 128;
+  static constexpr int kStage = (kOffW + kVGS * kTileBytes + 1023) / 1024 * 1024;  // swizzle atoms: 1 KB
   // The ring depth is a launch parameter: the host gives each CTA as many stages as fit next to
   // the other CTAs expected on its SM, because throughput here is (bytes in flight) / (HBM latency).
   static constexpr int kMinStages = 2;
@@ -159,8 +162,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
       }
       grid_dep_wait();
       for (int i = 0; i < prefill; ++i)
-        tma_load_2d(smem + i * C::kStage + C::kOffX, &tm_x, (g_begin + i * kVGS) * kGroup, 0,
-                    &full[i], pol_x);
+        tma_load_3d(smem + i * C::kStage + C::kOffX, &tm_x, 0, 0, g_begin + i * kVGS, &full[i], pol_x);
       int s = (prefill == stages) ? 0 : prefill;
       uint32_t ph = (prefill == stages) ? 0u : 1u;  // parity of the "stage is free" phase waited for
       for (int i = prefill; i < nst; ++i) {
@@ -172,7 +174,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         mbar_expect_tx(&full[s], wbytes + C::kXBytes);
         bulk_load_1d(st + C::kOffW, w_src + static_cast<size_t>(i) * kVGS * kTileBytes, wbytes,
                      &full[s], pol_w);
-        tma_load_2d(st + C::kOffX, &tm_x, (g_begin + i * kVGS) * kGroup, 0, &full[s], pol_x);
+        tma_load_3d(st + C::kOffX, &tm_x, 0, 0, g_begin + i * kVGS, &full[s], pol_x);
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }
@@ -200,18 +202,22 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
       for (int gi = set; gi < kVGS; gi += kVSets) {
         if (gi >= cnt) break;
         const uint8_t* tile = st + C::kOffW + gi * kTileBytes;
-        const uint4 wa = *reinterpret_cast<const uint4*>(tile + row * 64 + t * 16);
-        const uint4 wb = *reinterpret_cast<const uint4*>(tile + (row + 8) * 64 + t * 16);
+        // k chunk t of rows `row` and `row + 8` (chunk positions are swizzled by (row >> 1) & 3,
+        // the same value for both rows)
+        const int tp = t ^ ((g >> 1) & 3);
+        const uint4 wa = *reinterpret_cast<const uint4*>(tile + row * 64 + tp * 16);
+        const uint4 wb = *reinterpret_cast<const uint4*>(tile + (row + 8) * 64 + tp * 16);
         const __half* sc = reinterpret_cast<const __half*>(tile + kTileCodeBytes);
         const float s0 = __half2float(sc[row]) * 0.0625f;
         const float s1 = __half2float(sc[row + 8]) * 0.0625f;
         uint4 xlo[NT], xhi[NT];
 #pragma unroll
         for (int nb = 0; nb < NT; ++nb) {
-          // activation codes: [token][kVGS * 128] bytes, group gi at byte offset gi * 128
-          const uint8_t* xr = st + C::kOffX + (nb * 8 + g) * C::kXPitch + gi * kGroup + 32 * t;
-          xlo[nb] = *reinterpret_cast<const uint4*>(xr);
-          xhi[nb] = *reinterpret_cast<const uint4*>(xr + 16);
+          // activation codes: [group][token][128 B]; 16-byte chunk c of token row m sits at
+          // chunk position c ^ (m & 7) (128-byte swizzle); this lane needs chunks 2t and 2t + 1
+          const uint8_t* xr = st + C::kOffX + gi * C::kXGroupBytes + (nb * 8 + g) * kGroup;
+          xlo[nb] = *reinterpret_cast<const uint4*>(xr + (((2 * t) ^ g) << 4));
+          xhi[nb] = *reinterpret_cast<const uint4*>(xr + (((2 * t + 1) ^ g) << 4));
         }
         // Word j of a lane's 16-byte chunk feeds MMA step j: low nibbles are
         // k = 32t + 4j + {0..3} of the group (fragment slots a0/a1), high nibbles
@@ -460,7 +466,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
                          const ArDev& ar) {
   using C = VCfg<NT>;
   CUtensorMap tm_x;
-  int rc = make_tmap_2d_u8(&tm_x, codes, K, M, K, C::kXPitch, C::kXRows, CU_TENSOR_MAP_SWIZZLE_NONE);
+  int rc = make_tmap_x_groups(&tm_x, codes, K, M, C::kXRows, kVGS);
   if (rc != DQ_OK) return rc;
   const int total_groups = K / kGroup;
   const int gps = (total_groups + split - 1) / split;

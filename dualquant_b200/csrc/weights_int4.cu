@@ -38,8 +38,9 @@ __global__ void pack_w_int4_kernel(const int8_t* __restrict__ codes,
   const int groups = K / kGroup;
   const int64_t tiles = (N + 127) / 128;
   if (chunk >= tiles * groups * 512) return;
-  const int ch = static_cast<int>(chunk & 3);
   const int r = static_cast<int>((chunk >> 2) & 127);
+  // chunk position inside the 64-byte row is swizzled: position p holds k chunk p ^ ((r >> 1) & 3)
+  const int ch = static_cast<int>(chunk & 3) ^ ((r >> 1) & 3);
   const int64_t tg = chunk >> 9;
   const int g = static_cast<int>(tg % groups);
   const int64_t row = (tg / groups) * 128 + r;
@@ -63,8 +64,8 @@ __global__ void unpack_w_int4_kernel(const uint8_t* __restrict__ w_packed, int N
   const int groups = K / kGroup;
   const int64_t tiles = (N + 127) / 128;
   if (chunk >= tiles * groups * 512) return;
-  const int ch = static_cast<int>(chunk & 3);
   const int r = static_cast<int>((chunk >> 2) & 127);
+  const int ch = static_cast<int>(chunk & 3) ^ ((r >> 1) & 3);
   const int64_t tg = chunk >> 9;
   const int g = static_cast<int>(tg % groups);
   const int64_t row = (tg / groups) * 128 + r;

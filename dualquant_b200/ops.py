@@ -62,7 +62,7 @@ class PackedInt4Weight:
 
     def state(self):
         return {"w_packed": self.w_packed, "sw_t": self.sw_t, "N": self.N, "K": self.K,
-                "group": self.group, "layout_version": 1}
+                "group": self.group, "layout_version": 2}
 
 
 def quant_w_int4(w: torch.Tensor, group: int = GROUP):

@@ -207,8 +207,9 @@ def stream_pack_int4(codes: torch.Tensor, sw: torch.Tensor, group: int = GROUP) 
     """The library's streaming weight layout (flat uint8).  Tiles of 128 rows x 128 k in the order
     [row tile][k group]; a tile is 8192 bytes of codes ([row in tile][64 bytes]) followed by the
     128 fp16 group scales of its rows (256 bytes); rows past N are zero.  Within a tile row,
-    16-byte chunk ch covers k in [32ch, 32ch+32) of the group and
-    byte b = (code[32ch+b] & 0xF) | ((code[32ch+16+b] & 0xF) << 4), two's complement nibbles."""
+    k chunk ch covers k in [32ch, 32ch+32) of the group, its 16 bytes are
+    byte b = (code[32ch+b] & 0xF) | ((code[32ch+16+b] & 0xF) << 4), two's complement nibbles,
+    and it sits at chunk position ch ^ ((row_in_tile >> 1) & 3) of the 64-byte row."""
     N, K = codes.shape
     tiles, groups = (N + 127) // 128, K // group
     padded = torch.zeros(tiles * 128, K, dtype=torch.int16)
@@ -217,6 +218,10 @@ def stream_pack_int4(codes: torch.Tensor, sw: torch.Tensor, group: int = GROUP) 
     lo = c[..., 0, :] & 0xF
     hi = c[..., 1, :] & 0xF
     byt = (lo | (hi << 4)).to(torch.uint8)  # [tiles, 128, groups, 4, 16]
+    rows = torch.arange(128)
+    src = torch.arange(4)[None, :] ^ ((rows >> 1) & 3)[:, None]  # [128, 4]: k chunk at each position
+    idx = src.reshape(1, 128, 1, 4, 1).expand(tiles, 128, groups, 4, 16)
+    byt = torch.gather(byt, 3, idx)  # position p of row r now holds k chunk p ^ ((r >> 1) & 3)
     body = byt.permute(0, 2, 1, 3, 4).contiguous().reshape(tiles, groups, 8192)
     scales = stream_pack_scales(sw).reshape(tiles, groups, 128).view(torch.uint8).reshape(tiles, groups, 256)
     return torch.cat([body, scales], dim=2).reshape(-1)
