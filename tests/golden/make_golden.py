@@ -2,7 +2,7 @@
 
 Run in the authoring container only (it needs the reference checkout):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 The fixtures are small seeded input/output pairs of the reference functions on the W4A4 hot
 path; tests compare the oracle (oracle/dq_oracle.py) and the CUDA library against them.  The
@@ -155,4 +155,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path of the reference checkout>")
+    main(sys.argv[1])
