@@ -21,7 +21,7 @@
 // barrier round trip per role per step): every mbarrier / tcgen05 / TMA instruction costs the
 // issuing thread 70-100 cycles, and those serial chains, not bandwidth, bound this kernel.
 //
-// Warp roles (E = 8 epilogue warps, 16 for the 128-token tile):
+// Warp roles (E = 4 epilogue warps, 16 for the 128-token tile):
 //   warps 0-3      unpack (lane quarter = warp index)
 //   warps 4..3+E   epilogue: chunked tcgen05.ld of the group accumulator, run += float(acc) * sw;
 //                  final scale by r[n] * sx[m], store / split-K reduction over the cluster
@@ -58,7 +58,9 @@ struct Cfg {
   static constexpr int SX = kCfgTab[kRow][1];
   static constexpr int NB = kCfgTab[kRow][2];
   static constexpr int NA = kCfgTab[kRow][3];
-  static constexpr int EW = (TN == 128) ? 16 : 8;       // epilogue warps
+  // epilogue warps: few warps with more columns each for the small tiles (every waiting warp
+  // polls its barrier and costs issue slots)
+  static constexpr int EW = (TN == 128) ? 16 : 4;
   static constexpr int kProducerWarp = kUnpackWarps + EW;
   static constexpr int kIssuerWarp = kProducerWarp + 1;
   // The 128-token tile runs one CTA per SM and re-balances registers between warpgroups, which
@@ -476,10 +478,10 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
   if (!DUMP && split_k > 1) {
     __syncwarp();
     cluster_sync_all();
-    if (warp >= kUnpackWarps && warp < kUnpackWarps + 8) {
+    if (warp < 8) {  // 256 threads (unpack warps and the first epilogue warps; all roles are done)
       const uint32_t rank = cluster_ctarank();
       const int rows = TN / split_k;  // token rows of the tile this CTA finishes
-      const int e = tid - kUnpackWarps * 32;  // 0..255
+      const int e = tid;              // 0..255
       const int c4 = e & 31;                  // float4 column
       const uint32_t red_base = smem_u32(smem);
       for (int rr = e >> 5; rr < rows; rr += 8) {
