@@ -665,7 +665,15 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
 #define DQ_ROWS_LAUNCH(T, V)                                                                      \
   DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<T, V, XT>, dim3(M), dim3(T), 0, stream, x, ldx, a, K, \
                            codes, sx, out, mode, scale_fp16, norm_w, norm_eps))
-    if (vec <= 128) DQ_ROWS_LAUNCH(128, 1);
+#ifndef DQ_QUANT_BIG_M
+#define DQ_QUANT_BIG_M (1 << 30)
+#endif
+    // Many rows (prefill): fewer threads per row, each with four 16-byte loads in flight - the
+    // kernel is then bound by bytes in flight per SM, not by the per-row latency chain.
+    if (M >= DQ_QUANT_BIG_M && vec > 128 && vec <= 512) DQ_ROWS_LAUNCH(128, 4);
+    else if (M >= DQ_QUANT_BIG_M && vec > 512 && vec <= 1024) DQ_ROWS_LAUNCH(256, 4);
+    else if (M >= DQ_QUANT_BIG_M && vec > 1024 && vec <= 2048) DQ_ROWS_LAUNCH(512, 4);
+    else if (vec <= 128) DQ_ROWS_LAUNCH(128, 1);
     else if (vec <= 256) DQ_ROWS_LAUNCH(256, 1);
     else if (vec <= 512) DQ_ROWS_LAUNCH(512, 1);
     else if (vec <= 1024) DQ_ROWS_LAUNCH(1024, 1);
