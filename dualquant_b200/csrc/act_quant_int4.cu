@@ -61,13 +61,26 @@ __device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
 // division, at a fraction of its instruction count: t = v * (1/s) is within 2 ulp of the true
 // quotient, so rint(t) can only differ from rint(v / s) when t lies within a few ulp of a
 // half-integer (|t| <= ~7 here, 4 ulp < 4e-6); only those rare elements take the exact division.
+// Rounding and the float -> int step avoid the conversion instructions (quarter-rate pipe; at
+// prefill sizes this kernel is bound by instruction issue, not by memory): adding and subtracting
+// 1.5 * 2^23 rounds to the nearest integer, ties to even, for |t| < 2^22, and the low byte of the
+// bit pattern of (q + 1.5 * 2^23) is q as a two's-complement int8.
+constexpr float kRoundMagic = 12582912.0f;
 __device__ __forceinline__ float quant_code(float v, float s, float inv_s) {
   const float t = __fmul_rn(v, inv_s);
-  float q = rintf(t);
+  float q = __fsub_rn(__fadd_rn(t, kRoundMagic), kRoundMagic);
   const float dist = fabsf(fabsf(__fsub_rn(t, q)) - 0.5f);
   // the negated comparisons also send NaN / inf (1/s overflowed for a denormal scale) to the exact path
   if (!(dist >= 1e-5f) || !(fabsf(t) <= 16.0f)) q = rintf(__fdiv_rn(v, s));
   return fminf(fmaxf(q, -8.0f), 7.0f);
+}
+// four codes in [-8, 7] (as floats) -> four int8 in one word, first code in the low byte
+__device__ __forceinline__ uint32_t pack_codes4(float q0, float q1, float q2, float q3) {
+  const uint32_t u0 = __float_as_uint(__fadd_rn(q0, kRoundMagic));
+  const uint32_t u1 = __float_as_uint(__fadd_rn(q1, kRoundMagic));
+  const uint32_t u2 = __float_as_uint(__fadd_rn(q2, kRoundMagic));
+  const uint32_t u3 = __float_as_uint(__fadd_rn(q3, kRoundMagic));
+  return __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
 }
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
@@ -136,12 +149,10 @@ __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t*
                                       float* out_row, int idx) {
   const float inv_s = __fdiv_rn(1.0f, s);
   if (mode == MODE_CODES) {
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      lo |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[e], s, inv_s))) & 0xFFu) << (8 * e);
-      hi |= (static_cast<uint32_t>(static_cast<int>(quant_code(v[4 + e], s, inv_s))) & 0xFFu) << (8 * e);
-    }
+    const uint32_t lo = pack_codes4(quant_code(v[0], s, inv_s), quant_code(v[1], s, inv_s),
+                                    quant_code(v[2], s, inv_s), quant_code(v[3], s, inv_s));
+    const uint32_t hi = pack_codes4(quant_code(v[4], s, inv_s), quant_code(v[5], s, inv_s),
+                                    quant_code(v[6], s, inv_s), quant_code(v[7], s, inv_s));
     *reinterpret_cast<uint2*>(codes_row + idx) = make_uint2(lo, hi);
   } else {
     float o[8];
@@ -665,14 +676,12 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
 #define DQ_ROWS_LAUNCH(T, V)                                                                      \
   DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<T, V, XT>, dim3(M), dim3(T), 0, stream, x, ldx, a, K, \
                            codes, sx, out, mode, scale_fp16, norm_w, norm_eps))
-#ifndef DQ_QUANT_BIG_M
-#define DQ_QUANT_BIG_M (1 << 30)
-#endif
+    constexpr int kBigM = 1024;
     // Many rows (prefill): fewer threads per row, each with four 16-byte loads in flight - the
     // kernel is then bound by bytes in flight per SM, not by the per-row latency chain.
-    if (M >= DQ_QUANT_BIG_M && vec > 128 && vec <= 512) DQ_ROWS_LAUNCH(128, 4);
-    else if (M >= DQ_QUANT_BIG_M && vec > 512 && vec <= 1024) DQ_ROWS_LAUNCH(256, 4);
-    else if (M >= DQ_QUANT_BIG_M && vec > 1024 && vec <= 2048) DQ_ROWS_LAUNCH(512, 4);
+    if (M >= kBigM && vec > 128 && vec <= 512) DQ_ROWS_LAUNCH(128, 4);
+    else if (M >= kBigM && vec > 512 && vec <= 1024) DQ_ROWS_LAUNCH(256, 4);
+    else if (M >= kBigM && vec > 1024 && vec <= 2048) DQ_ROWS_LAUNCH(512, 4);
     else if (vec <= 128) DQ_ROWS_LAUNCH(128, 1);
     else if (vec <= 256) DQ_ROWS_LAUNCH(256, 1);
     else if (vec <= 512) DQ_ROWS_LAUNCH(512, 1);

@@ -358,3 +358,15 @@ def test_all_gemm_kernels_bit_identical_on_random_shapes():
         auto2 = ops.gemm_w4a4_int4(codes, sx, pw, r)
         assert torch.equal(auto1, auto2), (M, N, K)
     _status_ok()
+
+
+@pytest.mark.parametrize("M,K", [(1024, 2048), (1100, 4096), (1024, 14336)])
+def test_quant_act_many_rows_bit_exact(M, K):
+    """Row counts at which the quantiser switches to its many-rows launch shape."""
+    x = synthetic.make_x(M, K, K)
+    a = torch.exp(torch.randn(K, generator=torch.Generator().manual_seed(K)) * 0.3)
+    codes, sx = ops.quant_act_int4(x.to(DEV), a.to(DEV), None, True)
+    _status_ok()
+    q, s, _ = O.quant_act_int4(x, a, None, scale_fp16=True)
+    assert torch.equal(codes.cpu(), q)
+    assert torch.equal(sx.cpu(), s)
