@@ -66,13 +66,25 @@ __device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
 // 1.5 * 2^23 rounds to the nearest integer, ties to even, for |t| < 2^22, and the low byte of the
 // bit pattern of (q + 1.5 * 2^23) is q as a two's-complement int8.
 constexpr float kRoundMagic = 12582912.0f;
-__device__ __forceinline__ float quant_code(float v, float s, float inv_s) {
-  const float t = __fmul_rn(v, inv_s);
-  float q = __fsub_rn(__fadd_rn(t, kRoundMagic), kRoundMagic);
-  const float dist = fabsf(fabsf(__fsub_rn(t, q)) - 0.5f);
-  // the negated comparisons also send NaN / inf (1/s overflowed for a denormal scale) to the exact path
-  if (!(dist >= 1e-5f) || !(fabsf(t) <= 16.0f)) q = rintf(__fdiv_rn(v, s));
-  return fminf(fmaxf(q, -8.0f), 7.0f);
+// Eight codes at once.  The fast estimate runs for all of them; only if one of them lies within
+// reach of a rounding boundary (or the estimate is not finite) does the thread redo all eight with
+// the IEEE division - in a branch of its own, so that the division sequence stays out of the
+// common path instead of being predicated into it.
+__device__ __forceinline__ void quant_codes8(const float* v, float s, float inv_s, float* q) {
+  bool exact = false;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float t = __fmul_rn(v[e], inv_s);
+    const float qe = __fsub_rn(__fadd_rn(t, kRoundMagic), kRoundMagic);
+    const float dist = fabsf(fabsf(__fsub_rn(t, qe)) - 0.5f);
+    // the negated comparisons also catch NaN / inf (1/s overflowed for a denormal scale)
+    exact |= !(dist >= 1e-5f) || !(fabsf(t) <= 16.0f);
+    q[e] = fminf(fmaxf(qe, -8.0f), 7.0f);
+  }
+  if (exact) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) q[e] = fminf(fmaxf(rintf(__fdiv_rn(v[e], s)), -8.0f), 7.0f);
+  }
 }
 // four codes in [-8, 7] (as floats) -> four int8 in one word, first code in the low byte
 __device__ __forceinline__ uint32_t pack_codes4(float q0, float q1, float q2, float q3) {
@@ -149,15 +161,21 @@ __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t*
                                       float* out_row, int idx) {
   const float inv_s = __fdiv_rn(1.0f, s);
   if (mode == MODE_CODES) {
-    const uint32_t lo = pack_codes4(quant_code(v[0], s, inv_s), quant_code(v[1], s, inv_s),
-                                    quant_code(v[2], s, inv_s), quant_code(v[3], s, inv_s));
-    const uint32_t hi = pack_codes4(quant_code(v[4], s, inv_s), quant_code(v[5], s, inv_s),
-                                    quant_code(v[6], s, inv_s), quant_code(v[7], s, inv_s));
+    float q[8];
+    quant_codes8(v, s, inv_s, q);
+    const uint32_t lo = pack_codes4(q[0], q[1], q[2], q[3]);
+    const uint32_t hi = pack_codes4(q[4], q[5], q[6], q[7]);
     *reinterpret_cast<uint2*>(codes_row + idx) = make_uint2(lo, hi);
   } else {
     float o[8];
+    if (mode == MODE_FAKE) {
+      quant_codes8(v, s, inv_s, o);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = (mode == MODE_FAKE) ? __fmul_rn(quant_code(v[e], s, inv_s), s) : v[e];
+      for (int e = 0; e < 8; ++e) o[e] = __fmul_rn(o[e], s);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = v[e];
+    }
     *reinterpret_cast<float4*>(out_row + idx) = make_float4(o[0], o[1], o[2], o[3]);
     *reinterpret_cast<float4*>(out_row + idx + 4) = make_float4(o[4], o[5], o[6], o[7]);
   }
@@ -170,7 +188,10 @@ __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t*
 // 135-141, and HF's LlamaRMSNorm): v = bf16(x * rsqrt(mean(x^2) + eps)), times the bf16 weight
 // (rounded to bf16 again) when norm_w is given - exactly the bf16 tensor the separate norm would
 // have written and the quantiser read back.
-template <int THREADS, int VPT, typename XT>
+// KEEP: the scaled values of the absmax pass stay in registers for the code pass (many-rows launch
+// shape, where the kernel is bound by instruction issue and registers are plentiful) instead of
+// being re-expanded from the raw row (few-rows shape, where occupancy hides latency).
+template <int THREADS, int VPT, typename XT, bool KEEP = false>
 __global__ void __launch_bounds__(THREADS, (THREADS >= 512 && VPT <= 2) ? 2048 / THREADS : 1)
 act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
                       int8_t* __restrict__ codes, float* __restrict__ sx, float* __restrict__ out,
@@ -231,6 +252,7 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
     }
   };
   float amax = 0.f;
+  float kept[KEEP ? VPT : 1][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = (i * THREADS + threadIdx.x) * 8;
@@ -240,6 +262,10 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
       prologue(v, idx);
 #pragma unroll
       for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+      if constexpr (KEEP) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kept[i][e] = v[e];
+      }
     }
   }
   amax = block_max(amax, red, THREADS / 32);
@@ -251,10 +277,14 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
   for (int i = 0; i < VPT; ++i) {
     const int idx = (i * THREADS + threadIdx.x) * 8;
     if (idx < K) {
-      float v[8];
-      raw[i].expand(v);
-      prologue(v, idx);
-      emit8(v, s, mode, crow, orow, idx);
+      if constexpr (KEEP) {
+        emit8(kept[i], s, mode, crow, orow, idx);
+      } else {
+        float v[8];
+        raw[i].expand(v);
+        prologue(v, idx);
+        emit8(v, s, mode, crow, orow, idx);
+      }
     }
   }
 }
@@ -673,15 +703,16 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
     // thread holds few elements and many warps are resident to hide the load -> reduce -> store
     // latency chain
     const int vec = K / 8;
-#define DQ_ROWS_LAUNCH(T, V)                                                                      \
-  DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<T, V, XT>, dim3(M), dim3(T), 0, stream, x, ldx, a, K, \
+#define DQ_ROWS_LAUNCH_K(T, V, KP)                                                                \
+  DQ_CHECK_CUDA(launch_pdl(act_quant_rows_kernel<T, V, XT, KP>, dim3(M), dim3(T), 0, stream, x, ldx, a, K, \
                            codes, sx, out, mode, scale_fp16, norm_w, norm_eps))
+#define DQ_ROWS_LAUNCH(T, V) DQ_ROWS_LAUNCH_K(T, V, false)
     constexpr int kBigM = 1024;
     // Many rows (prefill): fewer threads per row, each with four 16-byte loads in flight - the
     // kernel is then bound by bytes in flight per SM, not by the per-row latency chain.
-    if (M >= kBigM && vec > 128 && vec <= 512) DQ_ROWS_LAUNCH(128, 4);
-    else if (M >= kBigM && vec > 512 && vec <= 1024) DQ_ROWS_LAUNCH(256, 4);
-    else if (M >= kBigM && vec > 1024 && vec <= 2048) DQ_ROWS_LAUNCH(512, 4);
+    if (M >= kBigM && vec > 128 && vec <= 512) DQ_ROWS_LAUNCH_K(128, 4, true);
+    else if (M >= kBigM && vec > 512 && vec <= 1024) DQ_ROWS_LAUNCH_K(256, 4, true);
+    else if (M >= kBigM && vec > 1024 && vec <= 2048) DQ_ROWS_LAUNCH_K(512, 4, true);
     else if (vec <= 128) DQ_ROWS_LAUNCH(128, 1);
     else if (vec <= 256) DQ_ROWS_LAUNCH(256, 1);
     else if (vec <= 512) DQ_ROWS_LAUNCH(512, 1);
@@ -689,6 +720,7 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
     else if (vec <= 2048) DQ_ROWS_LAUNCH(1024, 2);
     else DQ_ROWS_LAUNCH(1024, 4);
 #undef DQ_ROWS_LAUNCH
+#undef DQ_ROWS_LAUNCH_K
   }
   DQ_CHECK_CUDA(cudaGetLastError());
   return DQ_OK;
