@@ -148,18 +148,52 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
         e = max(-127, min(127, e));
       }
       sf_byte = static_cast<uint32_t>(e + 127);
+      // 2^-e is representable (as a subnormal at the far end), so one multiplication rounds
+      // exactly like scalbnf(v, -e) would
+      const float down = scalbnf(1.0f, -e);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = scalbnf(v[i][k], -e);
+      for (int k = 0; k < 8; ++k) q[k] = __fmul_rn(v[i][k], down);
       deq_scale = scalbnf(1.0f, e);
     } else {
       const float want = __fdiv_rn(__fdiv_rn(bmax[i], 6.0f), ts);
       sf_byte = e4m3_byte_of(fminf(want, 448.0f));
       const float bs = e4m3_value(sf_byte);
       const float denom = __fmul_rn(ts, bs);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = (denom == 0.f) ? 0.f : __fdiv_rn(v[i][k], denom);
       deq_scale = denom;
       if (mode == FP4_MODE_FAKE) deq_scale = bs;  // applied as (q * bs) * ts below
+      if (denom == 0.f) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) q[k] = 0.f;
+      } else {
+        // v / denom rounded to E2M1 without eight IEEE divisions: t = v * (1 / denom) is within
+        // 2^-22 |t| of the quotient; if t (1 - 2^-21) and t (1 + 2^-21) convert to the same codes,
+        // so does everything between them, the correctly rounded quotient included.  Otherwise
+        // (an element sits on a rounding boundary, or t is not finite) the thread takes the exact
+        // divisions, in a branch of its own.
+        const float inv = __fdiv_rn(1.0f, denom);
+        float lo[8], hi[8];
+        bool exact = false;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float t = __fmul_rn(v[i][k], inv);
+          exact |= !(fabsf(t) <= 1e30f);
+          lo[k] = __fmul_rn(t, 0.99999952316284179688f);  // 1 - 2^-21
+          hi[k] = __fmul_rn(t, 1.00000047683715820312f);  // 1 + 2^-21
+        }
+        uint32_t plo = 0, phi = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          plo |= e2m1x2(lo[2 * k], lo[2 * k + 1]) << (8 * k);
+          phi |= e2m1x2(hi[2 * k], hi[2 * k + 1]) << (8 * k);
+        }
+        if (exact || plo != phi) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) q[k] = __fdiv_rn(v[i][k], denom);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) q[k] = lo[k];
+        }
+      }
     }
     uint32_t packed = 0;
 #pragma unroll
