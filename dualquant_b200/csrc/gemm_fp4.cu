@@ -27,7 +27,7 @@ constexpr int kFTN = 128;      // tokens per CTA
 constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
 constexpr int kFStages = 3;  // 3 x 36 KB: two CTAs fit on one SM, one's epilogue overlaps the other's K loop
 constexpr int kFTileBytes = 128 * 128;  // one operand tile
-constexpr int kFThreads = 192;
+constexpr int kFThreads = 256;  // producer, UMMA issuer, 4 epilogue warps, 2 scale-factor copiers
 
 struct FCfg {
   static constexpr int kOffA = 0;
@@ -35,13 +35,13 @@ struct FCfg {
   static constexpr int kOffSFA = kOffB + kFStages * kFTileBytes;  // up to 2 KB per stage
   static constexpr int kOffSFB = kOffSFA + kFStages * 2048;
   static constexpr int kOffBar = kOffSFB + kFStages * 2048;
-  static constexpr int kSmemBytes = kOffBar + (2 * kFStages + 1) * 8 + 16 + 1024;
+  static constexpr int kSmemBytes = kOffBar + (3 * kFStages + 1) * 8 + 16 + 1024;
   static_assert(kFTN * kFBN * 4 <= kOffSFA, "split-K exchange tile must fit in the operand stages");
   static constexpr int kTmemCols = 256;    // 128 accumulator columns + scale factors
   static constexpr int kSfColBase = 128;   // scale-factor columns start here: 32 per stage
 };
 
-enum { FSITE_TMA = 31, FSITE_MMA = 32, FSITE_EPI = 33 };
+enum { FSITE_TMA = 31, FSITE_MMA = 32, FSITE_EPI = 33, FSITE_SF = 34 };
 
 // Shared-memory descriptor of one scale-factor atom for tcgen05.cp: 32 rows x 16 bytes, no
 // swizzle, 8-row groups 128 bytes apart.
@@ -99,7 +99,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
   uint64_t* empty = full + kFStages;
-  uint64_t* acc_full = empty + kFStages;
+  uint64_t* sf_ready = empty + kFStages;
+  uint64_t* acc_full = sf_ready + kFStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -113,7 +114,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const int nst = (st_end > st_begin) ? (st_end - st_begin) : 0;
 
   if (tid == 0) {
-    for (int i = 0; i < kFStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < kFStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+      mbar_init(&sf_ready[i], 2);  // one tcgen05.commit from each scale-factor copier
+    }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -156,15 +161,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     if (lane == 0) {  // only lane 0 works (see the producer)
       for (int i = 0; i < nst; ++i) {
         const int s = i % kFStages;
+        // operands landed (full) and their scale factors copied into tensor memory (sf_ready)
         if (!mbar_wait(&full[s], (i / kFStages) & 1, abort_flag, FSITE_MMA)) break;
+        if (!mbar_wait(&sf_ready[s], (i / kFStages) & 1, abort_flag, FSITE_MMA)) break;
         tc_fence_after();
         const uint32_t sfa_t = tmem_base + C::kSfColBase + s * 32;
         const uint32_t sfb_t = sfa_t + 16;
-#pragma unroll
-        for (int a = 0; a < kAtoms; ++a) {
-          tmem_cp_32x128b_warpx4(sfa_t + 4 * a, sf_atom_desc(smem_u32(smem + C::kOffSFA + s * 2048 + a * 512)));
-          tmem_cp_32x128b_warpx4(sfb_t + 4 * a, sf_atom_desc(smem_u32(smem + C::kOffSFB + s * 2048 + a * 512)));
-        }
         const uint64_t da = umma_desc_k_sw128(smem_u32(smem + C::kOffA + s * kFTileBytes));
         const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + s * kFTileBytes));
 #pragma unroll
@@ -177,6 +179,28 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         }
         umma_commit(&empty[s]);
         if (i == nst - 1) umma_commit(acc_full);
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ scale-factor copiers
+    // Warp 6 moves the weight scale factors of each stage from shared to tensor memory
+    // (tcgen05.cp, one per 512-byte atom), warp 7 the activation scale factors.  They used to be
+    // issued by the UMMA thread: 4-8 copies + 4 UMMAs + commits per stage, at ~70 cycles of issue
+    // latency each, took that one thread several times the 271 cycles the UMMAs need to execute.
+    // The stage's columns are free again once its previous UMMAs have finished, which the
+    // producer has already waited for before refilling the stage (full implies it).
+    if (lane == 0) {
+      const bool is_b = (warp == 7);
+      const int sf_off = is_b ? C::kOffSFB : C::kOffSFA;
+      for (int i = 0; i < nst; ++i) {
+        const int s = i % kFStages;
+        if (!mbar_wait(&full[s], (i / kFStages) & 1, abort_flag, FSITE_SF)) break;
+        tc_fence_after();
+        const uint32_t sf_t = tmem_base + C::kSfColBase + s * 32 + (is_b ? 16 : 0);
+#pragma unroll
+        for (int at = 0; at < kAtoms; ++at)
+          tmem_cp_32x128b_warpx4(sf_t + 4 * at, sf_atom_desc(smem_u32(smem + sf_off + s * 2048 + at * 512)));
+        umma_commit(&sf_ready[s]);
       }
     }
   } else {
@@ -232,7 +256,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   if (split_k > 1) {
     __syncwarp();
     cluster_sync_all();
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       int tok_cols = M - t0;
       if (tok_cols > kFTN) tok_cols = kFTN;
       const uint32_t rank = cluster_ctarank();
