@@ -90,7 +90,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx,
                 const float* __restrict__ r, const float* __restrict__ w_scale,
                 const float* __restrict__ x_scale, void* __restrict__ y, int y_bf16, int M, int N,
-                int K, int stages_per_split, int split_k, int* status) {
+                int K, int stages_per_split, int split_k, int tok_fast, int* status) {
   using C = FCfg;
   constexpr int kAtoms = NVFP4 ? 4 : 2;           // scale-factor atoms per operand per stage
   constexpr uint32_t kSfBytes = kAtoms * 512;
@@ -105,8 +105,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * kFBN;
-  const int t0 = blockIdx.y * kFTN;
+  // tok_fast: grid x walks the token tiles (CTAs that run together share one weight tile and the
+  // whole, smaller, activation matrix stays in L2); otherwise grid x walks the row tiles
+  const int n0 = (tok_fast ? blockIdx.y : blockIdx.x) * kFBN;
+  const int t0 = (tok_fast ? blockIdx.x : blockIdx.y) * kFTN;
   const int total_st = K / kFKStage;
   const int st_begin = blockIdx.z * stages_per_split;
   int st_end = st_begin + stages_per_split;
@@ -139,8 +141,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     const uint64_t pol = l2_policy_evict_last();
-    const uint8_t* sfw_tile = sfw + (static_cast<size_t>(blockIdx.x) * total_st + st_begin) * kSfBytes;
-    const uint8_t* sfx_tile = sfx + (static_cast<size_t>(blockIdx.y) * total_st + st_begin) * kSfBytes;
+    const uint8_t* sfw_tile = sfw + (static_cast<size_t>(n0 / kFBN) * total_st + st_begin) * kSfBytes;
+    const uint8_t* sfx_tile = sfx + (static_cast<size_t>(t0 / kFTN) * total_st + st_begin) * kSfBytes;
     // Only lane 0 works; the other lanes go straight to the end of the role (32 lanes polling a
     // barrier cost issue slots and barrier-unit bandwidth that the other warps need).
     if (lane == 0) {
@@ -383,7 +385,10 @@ extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atom
   while (split < 8 && tiles * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
   const int sps = (total_st + split - 1) / split;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + kFBN - 1) / kFBN, (M + kFTN - 1) / kFTN, split);
+  const int row_tiles = (N + kFBN - 1) / kFBN, tok_tiles = (M + kFTN - 1) / kFTN;
+  // the smaller operand is the one every CTA wave re-reads; it stays in L2 when grid x walks its tiles
+  const int tok_fast = (tok_tiles > 1 && M < N && row_tiles <= 65535) ? 1 : 0;
+  cfg.gridDim = tok_fast ? dim3(tok_tiles, row_tiles, split) : dim3(row_tiles, tok_tiles, split);
   cfg.blockDim = dim3(kFThreads, 1, 1);
   cfg.dynamicSmemBytes = FCfg::kSmemBytes;
   cfg.stream = static_cast<cudaStream_t>(stream);
@@ -398,10 +403,10 @@ extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atom
   cudaError_t e;
   if (fmt == DQ_FP4_NVFP4)
     e = cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<1>, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale,
-                           x_scale, y, bf, M, N, K, sps, split, st->status_dev);
+                           x_scale, y, bf, M, N, K, sps, split, tok_fast, st->status_dev);
   else
     e = cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<0>, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale,
-                           x_scale, y, bf, M, N, K, sps, split, st->status_dev);
+                           x_scale, y, bf, M, N, K, sps, split, tok_fast, st->status_dev);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_fp4 launch failed (split=%d): %s", split, cudaGetErrorString(e));
   DQ_CHECK_CUDA(cudaGetLastError());
