@@ -832,7 +832,8 @@ def run_reference(args):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     wl = CpuWorkload(synthetic.DECODE_M)
-    for _ in range(max(1, min(args.warmup, 2))):
+    warmup = max(3, min(args.warmup, 20))
+    for _ in range(warmup):
         wl.step()
     steps = max(1, min(args.steps, 100))
     t0 = time.perf_counter()
@@ -842,7 +843,7 @@ def run_reference(args):
     value = round(wl.bytes() / dt / 1e9, 3)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(dt * 1e3, 2),
+        "steps": steps, "warmup": warmup, "ms_per_step": round(dt * 1e3, 2),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 fake-quant (fp32 quantiser)",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "note": "reference CPU path (PermLinear fake-quant) restated by the oracle; the reference is Python and is not present on the GPU box"},
