@@ -430,6 +430,39 @@ def run_case(args):
         print(json.dumps({"case": args.case, "us_per_launch": round(ms * 1e3, 2), "algorithmic_bytes": b,
                           "GBps": round(b / ms / 1e6, 1)}), flush=True)
         return
+    if parts[0] == "fp4":  # fp4:FMT:LINEAR:M - one block-scaled FP4 GEMM of the Qwen2.5-7B shapes alone
+        fmt = {"mxfp4": _lib.FP4_MXFP4, "nvfp4": _lib.FP4_NVFP4}[parts[1]]
+        K, N = {n: (k, nn) for n, k, nn in synthetic.QWEN25_7B_LINEARS}[parts[2]]
+        M = int(parts[3])
+        blk = 32 if fmt == _lib.FP4_MXFP4 else 16
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        g = torch.Generator(device=dev).manual_seed(0)
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        pw = ops.pack_w_fp4(w, fmt)
+        del w
+        r, c = synthetic.make_scales(N, K, 0)
+        r, a = r.to(dev), (1.0 / c).to(dev)
+        x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        codes, sfa, rs = _fp4_prologue(ops, x, a, pw)
+        y = torch.empty(M, N, dtype=torch.float32, device=dev)
+        for _ in range(3):
+            ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r, out=y)
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        _lib.device_status(0)
+        ms = e0.elapsed_time(e1) / args.iters
+        nbytes = N * K // 2 + N * K // blk + 2 * N + 2 * K + 2 * M * K + 4 * M * N
+        print(json.dumps({"case": args.case, "iters": args.iters, "us_per_launch": round(ms * 1e3, 2),
+                          "TFLOPS": round(2.0 * M * N * K / ms / 1e9, 1), "algorithmic_bytes": nbytes,
+                          "GBps": round(nbytes / ms / 1e6, 1)}), flush=True)
+        return
     name, M = parts[0], int(parts[1])
     tn = int(parts[2]) if len(parts) > 2 else 0
     split = int(parts[3]) if len(parts) > 3 else 0
