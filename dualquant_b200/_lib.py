@@ -71,6 +71,7 @@ SIGNATURES = {
     "dq_fp4_sf_atoms_bytes": (_sz, [_i, _i, _i]),
     "dq_fp4_sf_to_atoms": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "dq_gemm_w4a4_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
+    "dq_gemm_w4a4_fp4_tiled": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "dq_gemm_w4a4_int4_workspace_bytes": (_sz, [_i, _i, _i]),
     "dq_gemm_w4a4_int4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),

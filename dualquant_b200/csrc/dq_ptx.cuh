@@ -79,17 +79,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// Warp-level form of the bounded wait for warps whose 32 lanes all need the phase: lane 0 waits,
-// the result is broadcast with a shuffle (which is also the warp-level synchronisation that
-// orders the other lanes' later accesses after lane 0's acquire of the barrier).  One thread
-// probing instead of 32 leaves the barrier unit to the roles that are working.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
-                                               volatile int* abort_flag, int site, int lane) {
-  int ok = 1;
-  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, site) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
 // Register re-balancing between warpgroups (4 consecutive warps): every thread of the warpgroup
 // executes the same instruction; dec returns registers to the CTA's pool, inc takes from it.
 template <int N>

@@ -25,20 +25,34 @@ namespace dq {
 constexpr int kFBN = 128;      // weight rows per CTA
 constexpr int kFTN = 128;      // tokens per CTA
 constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
-constexpr int kFStages = 3;  // 3 x 36 KB: two CTAs fit on one SM, one's epilogue overlaps the other's K loop
-constexpr int kFTileBytes = 128 * 128;  // one operand tile
+constexpr int kFp4WideMinK = 8192;  // automatic choice of the 256-token tile: K at least this
+constexpr int kFTileBytes = 128 * 128;  // one operand tile of 128 rows
 constexpr int kFThreads = 256;  // producer, UMMA issuer, 4 epilogue warps, 2 scale-factor copiers
 
+// NT = token blocks of 128 per CTA.
+//   NT = 1: 3 stages of 36 KB and 256 tensor-memory columns, so two CTAs share an SM and one's
+//           epilogue overlaps the other's K loop.
+//   NT = 2: 128 weight rows x 256 tokens.  The weight tile of a stage is fetched once for two
+//           token blocks (24 KB of operands per 128x128x256 block product instead of 32 KB): the
+//           shape for long K loops, where the stream of operand tiles out of L2 is what bounds
+//           the 128x128 tile.  4 stages of 54 KB, one CTA per SM, two fp32 accumulators.
+template <int NT>
 struct FCfg {
+  static constexpr int kStages = (NT == 1) ? 3 : 4;
   static constexpr int kOffA = 0;
-  static constexpr int kOffB = kOffA + kFStages * kFTileBytes;
-  static constexpr int kOffSFA = kOffB + kFStages * kFTileBytes;  // up to 2 KB per stage
-  static constexpr int kOffSFB = kOffSFA + kFStages * 2048;
-  static constexpr int kOffBar = kOffSFB + kFStages * 2048;
-  static constexpr int kSmemBytes = kOffBar + (3 * kFStages + 1) * 8 + 16 + 1024;
+  static constexpr int kOffB = kOffA + kStages * kFTileBytes;
+  static constexpr int kOffSFA = kOffB + kStages * NT * kFTileBytes;  // up to 2 KB per stage
+  static constexpr int kOffSFB = kOffSFA + kStages * 2048;            // up to NT x 2 KB per stage
+  static constexpr int kOffBar = kOffSFB + kStages * NT * 2048;
+  static constexpr int kSmemBytes = kOffBar + (3 * kStages + 1) * 8 + 16 + 1024;
   static_assert(kFTN * kFBN * 4 <= kOffSFA, "split-K exchange tile must fit in the operand stages");
-  static constexpr int kTmemCols = 256;    // 128 accumulator columns + scale factors
-  static constexpr int kSfColBase = 128;   // scale-factor columns start here: 32 per stage
+  static_assert(kSmemBytes <= 227 * 1024, "stages exceed the shared memory of an SM");
+  static constexpr int kAccCols = NT * kFTN;          // fp32 accumulator columns
+  static constexpr int kSfColsStage = 16 + NT * 16;   // scale-factor columns per stage: A, then B per block
+  static constexpr int kSfColBase = kAccCols;
+  static constexpr int kTmemCols = (NT == 1) ? 256 : 512;
+  static_assert(kSfColBase + kStages * kSfColsStage <= kTmemCols, "tensor memory columns");
+  static constexpr int kMinCtas = (NT == 1) ? 2 : 1;
 };
 
 enum { FSITE_TMA = 31, FSITE_MMA = 32, FSITE_EPI = 33, FSITE_SF = 34 };
@@ -84,14 +98,15 @@ __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint6
   }
 }
 
-template <int NVFP4>
-__global__ void __launch_bounds__(kFThreads, 2)
+template <int NVFP4, int NT>
+__global__ void __launch_bounds__(kFThreads, FCfg<NT>::kMinCtas)
 gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                 const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx,
                 const float* __restrict__ r, const float* __restrict__ w_scale,
                 const float* __restrict__ x_scale, void* __restrict__ y, int y_bf16, int M, int N,
                 int K, int stages_per_split, int split_k, int tok_fast, int* status) {
-  using C = FCfg;
+  using C = FCfg<NT>;
+  constexpr int kFStages = C::kStages;
   constexpr int kAtoms = NVFP4 ? 4 : 2;           // scale-factor atoms per operand per stage
   constexpr uint32_t kSfBytes = kAtoms * 512;
   extern __shared__ uint8_t smem_raw[];
@@ -108,7 +123,9 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   // tok_fast: grid x walks the token tiles (CTAs that run together share one weight tile and the
   // whole, smaller, activation matrix stays in L2); otherwise grid x walks the row tiles
   const int n0 = (tok_fast ? blockIdx.y : blockIdx.x) * kFBN;
-  const int t0 = (tok_fast ? blockIdx.x : blockIdx.y) * kFTN;
+  const int t0 = (tok_fast ? blockIdx.x : blockIdx.y) * (NT * kFTN);
+  // token blocks of this CTA that hold tokens (the last CTA of a ragged M may own only one)
+  const int nblk = (NT == 2 && M - t0 > kFTN) ? 2 : 1;
   const int total_st = K / kFKStage;
   const int st_begin = blockIdx.z * stages_per_split;
   int st_end = st_begin + stages_per_split;
@@ -143,19 +160,22 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const uint64_t pol = l2_policy_evict_last();
     const uint8_t* sfw_tile = sfw + (static_cast<size_t>(n0 / kFBN) * total_st + st_begin) * kSfBytes;
     const uint8_t* sfx_tile = sfx + (static_cast<size_t>(t0 / kFTN) * total_st + st_begin) * kSfBytes;
+    const size_t sfx_block = static_cast<size_t>(total_st) * kSfBytes;  // next token block of 128
     // Only lane 0 works; the other lanes go straight to the end of the role (32 lanes polling a
     // barrier cost issue slots and barrier-unit bandwidth that the other warps need).
     if (lane == 0) {
       for (int i = 0; i < nst; ++i) {
         const int s = i % kFStages;
         if (!mbar_wait(&empty[s], ((i / kFStages) & 1) ^ 1, abort_flag, FSITE_TMA)) break;
-        mbar_expect_tx(&full[s], 2 * kFTileBytes + 2 * kSfBytes);
+        // the activation box is NT x 128 token rows (rows past M arrive as zeros and count)
+        mbar_expect_tx(&full[s], (1 + NT) * kFTileBytes + (1 + nblk) * kSfBytes);
         tma_load_2d(smem + C::kOffA + s * kFTileBytes, &tm_w, (st_begin + i) * 128, n0, &full[s], pol);
-        tma_load_2d(smem + C::kOffB + s * kFTileBytes, &tm_x, (st_begin + i) * 128, t0, &full[s], pol);
+        tma_load_2d(smem + C::kOffB + s * NT * kFTileBytes, &tm_x, (st_begin + i) * 128, t0, &full[s], pol);
         bulk_load_1d(smem + C::kOffSFA + s * 2048, sfw_tile + static_cast<size_t>(i) * kSfBytes,
                      kSfBytes, &full[s], pol);
-        bulk_load_1d(smem + C::kOffSFB + s * 2048, sfx_tile + static_cast<size_t>(i) * kSfBytes,
-                     kSfBytes, &full[s], pol);
+        for (int b = 0; b < nblk; ++b)
+          bulk_load_1d(smem + C::kOffSFB + (s * NT + b) * 2048,
+                       sfx_tile + b * sfx_block + static_cast<size_t>(i) * kSfBytes, kSfBytes, &full[s], pol);
       }
     }
   } else if (warp == 1) {
@@ -167,17 +187,22 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         if (!mbar_wait(&full[s], (i / kFStages) & 1, abort_flag, FSITE_MMA)) break;
         if (!mbar_wait(&sf_ready[s], (i / kFStages) & 1, abort_flag, FSITE_MMA)) break;
         tc_fence_after();
-        const uint32_t sfa_t = tmem_base + C::kSfColBase + s * 32;
-        const uint32_t sfb_t = sfa_t + 16;
+        const uint32_t sfa_t = tmem_base + C::kSfColBase + s * C::kSfColsStage;
         const uint64_t da = umma_desc_k_sw128(smem_u32(smem + C::kOffA + s * kFTileBytes));
-        const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + s * kFTileBytes));
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {  // four K=64 UMMAs: +32 bytes along K each
-          const int atom = NVFP4 ? j : (j >> 1);
-          const uint32_t sf_id = NVFP4 ? 0u : static_cast<uint32_t>((j & 1) * 2);
-          const uint32_t idesc = umma_idesc_fp4(kFBN, kFTN, NVFP4 ? 0 : 1, sf_id);
-          umma_fp4<NVFP4>(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa_t + 4 * atom,
-                          sfb_t + 4 * atom, (i > 0 || j > 0) ? 1u : 0u);
+        for (int b = 0; b < NT; ++b) {  // token block b: its own accumulator and scale-factor columns
+          if (b < nblk) {
+            const uint32_t sfb_t = sfa_t + 16 + b * 16;
+            const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + (s * NT + b) * kFTileBytes));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // four K=64 UMMAs: +32 bytes along K each
+              const int atom = NVFP4 ? j : (j >> 1);
+              const uint32_t sf_id = NVFP4 ? 0u : static_cast<uint32_t>((j & 1) * 2);
+              const uint32_t idesc = umma_idesc_fp4(kFBN, kFTN, NVFP4 ? 0 : 1, sf_id);
+              umma_fp4<NVFP4>(tmem_base + b * kFTN, da + 2 * j, db + 2 * j, idesc, sfa_t + 4 * atom,
+                              sfb_t + 4 * atom, (i > 0 || j > 0) ? 1u : 0u);
+            }
+          }
         }
         umma_commit(&empty[s]);
         if (i == nst - 1) umma_commit(acc_full);
@@ -198,10 +223,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         const int s = i % kFStages;
         if (!mbar_wait(&full[s], (i / kFStages) & 1, abort_flag, FSITE_SF)) break;
         tc_fence_after();
-        const uint32_t sf_t = tmem_base + C::kSfColBase + s * 32 + (is_b ? 16 : 0);
+        const uint32_t sf_t = tmem_base + C::kSfColBase + s * C::kSfColsStage + (is_b ? 16 : 0);
+        const int blocks = is_b ? nblk : 1;
+        for (int b = 0; b < blocks; ++b) {
+          const uint32_t src = smem_u32(smem + sf_off + (s * (is_b ? NT : 1) + b) * 2048);
 #pragma unroll
-        for (int at = 0; at < kAtoms; ++at)
-          tmem_cp_32x128b_warpx4(sf_t + 4 * at, sf_atom_desc(smem_u32(smem + sf_off + s * 2048 + at * 512)));
+          for (int at = 0; at < kAtoms; ++at)
+            tmem_cp_32x128b_warpx4(sf_t + b * 16 + 4 * at, sf_atom_desc(src + at * 512));
+        }
         umma_commit(&sf_ready[s]);
       }
     }
@@ -211,7 +240,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const int n = n0 + q * 32 + lane;
     // token columns that exist in this tile, rounded up to the 32-column granularity of tcgen05.ld
     int tok_cols = M - t0;
-    if (tok_cols > kFTN) tok_cols = kFTN;
+    if (tok_cols > NT * kFTN) tok_cols = NT * kFTN;
     const int col_end = (tok_cols + 31) & ~31;
     const bool have_acc = (nst > 0) && mbar_wait_relaxed(acc_full, 0, abort_flag, FSITE_EPI);
     if (have_acc) tc_fence_after();
@@ -322,11 +351,17 @@ __global__ void fp4_sf_to_atoms_kernel(const uint8_t* __restrict__ sf, int rows,
 }
 
 int init_gemm_fp4_kernels() {
-  cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       FCfg::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       FCfg<1>::kSmemBytes);
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(gemm_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             FCfg::kSmemBytes);
+    e = cudaFuncSetAttribute(gemm_fp4_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             FCfg<1>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_fp4_kernel<0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             FCfg<2>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_fp4_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             FCfg<2>::kSmemBytes);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemm_fp4) failed: %s", cudaGetErrorString(e));
   return DQ_OK;
@@ -360,6 +395,15 @@ extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atom
                                 const float* x_scale, const uint8_t* w_codes,
                                 const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
                                 int M, int N, int K, int fmt, void* y, int y_dtype, void* stream) {
+  return dq_gemm_w4a4_fp4_tiled(x_codes, x_sf_atoms, x_scale, w_codes, w_sf_atoms, w_scale, r, M, N, K,
+                                fmt, y, y_dtype, 0, stream);
+}
+
+extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_sf_atoms,
+                                      const float* x_scale, const uint8_t* w_codes,
+                                      const uint8_t* w_sf_atoms, const float* w_scale,
+                                      const float* r, int M, int N, int K, int fmt, void* y,
+                                      int y_dtype, int token_blocks, void* stream) {
   DeviceState* st = current_state();
   if (st == nullptr) return DQ_ERR_NOT_INIT;
   if (M == 0) return DQ_OK;
@@ -371,26 +415,39 @@ extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atom
                  aligned(w_sf_atoms, 16),
              DQ_ERR_ALIGN, "operands must be 16-byte aligned");
   DQ_REQUIRE(y_dtype == DQ_DTYPE_F32 || y_dtype == DQ_DTYPE_BF16, DQ_ERR_UNSUPPORTED, "unknown y_dtype %d", y_dtype);
+  DQ_REQUIRE(token_blocks >= 0 && token_blocks <= 2, DQ_ERR_SHAPE, "token_blocks must be 0 (auto), 1 or 2, got %d",
+             token_blocks);
+  const int total_st = K / kFKStage;
+  // split K across a cluster when the output tiles alone leave most SMs idle (decode batches)
+  int split = 1;
+  {
+    const int tiles1 = ((N + kFBN - 1) / kFBN) * ((M + kFTN - 1) / kFTN);
+    while (split < 8 && tiles1 * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
+  }
+  // 256-token tiles: for long K loops with enough tiles to fill the SMs at one CTA each
+  int nt = token_blocks;
+  if (nt == 0) {
+    const int tiles2 = ((N + kFBN - 1) / kFBN) * ((M + 2 * kFTN - 1) / (2 * kFTN));
+    nt = (split == 1 && K >= kFp4WideMinK && tiles2 >= 2 * st->sm_count) ? 2 : 1;
+  }
+  DQ_REQUIRE(nt == 1 || split == 1, DQ_ERR_UNSUPPORTED,
+             "256-token tiles have no split-K path (M=%d N=%d K=%d would split %d ways)", M, N, K, split);
+  const int tile_tok = nt * kFTN;
   CUtensorMap tm_w, tm_x;
   int rc = make_tmap_2d_u8(&tm_w, w_codes, static_cast<uint64_t>(K) / 2, N, static_cast<uint64_t>(K) / 2,
                            128, kFBN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != DQ_OK) return rc;
   rc = make_tmap_2d_u8(&tm_x, x_codes, static_cast<uint64_t>(K) / 2, M, static_cast<uint64_t>(K) / 2, 128,
-                       kFTN, CU_TENSOR_MAP_SWIZZLE_128B);
+                       tile_tok, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != DQ_OK) return rc;
-  const int total_st = K / kFKStage;
-  const int tiles = ((N + kFBN - 1) / kFBN) * ((M + kFTN - 1) / kFTN);
-  // split K across a cluster when the output tiles alone leave most SMs idle (decode batches)
-  int split = 1;
-  while (split < 8 && tiles * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
   const int sps = (total_st + split - 1) / split;
   cudaLaunchConfig_t cfg = {};
-  const int row_tiles = (N + kFBN - 1) / kFBN, tok_tiles = (M + kFTN - 1) / kFTN;
+  const int row_tiles = (N + kFBN - 1) / kFBN, tok_tiles = (M + tile_tok - 1) / tile_tok;
   // the smaller operand is the one every CTA wave re-reads; it stays in L2 when grid x walks its tiles
   const int tok_fast = (tok_tiles > 1 && M < N && row_tiles <= 65535) ? 1 : 0;
   cfg.gridDim = tok_fast ? dim3(tok_tiles, row_tiles, split) : dim3(row_tiles, tok_tiles, split);
   cfg.blockDim = dim3(kFThreads, 1, 1);
-  cfg.dynamicSmemBytes = FCfg::kSmemBytes;
+  cfg.dynamicSmemBytes = (nt == 2) ? FCfg<2>::kSmemBytes : FCfg<1>::kSmemBytes;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -401,12 +458,10 @@ extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atom
   cfg.numAttrs = 1;
   const int bf = y_dtype == DQ_DTYPE_BF16 ? 1 : 0;
   cudaError_t e;
-  if (fmt == DQ_FP4_NVFP4)
-    e = cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<1>, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale,
-                           x_scale, y, bf, M, N, K, sps, split, tok_fast, st->status_dev);
-  else
-    e = cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<0>, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale,
-                           x_scale, y, bf, M, N, K, sps, split, tok_fast, st->status_dev);
+  auto kern = (fmt == DQ_FP4_NVFP4) ? (nt == 2 ? gemm_fp4_kernel<1, 2> : gemm_fp4_kernel<1, 1>)
+                                    : (nt == 2 ? gemm_fp4_kernel<0, 2> : gemm_fp4_kernel<0, 1>);
+  e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale, x_scale, y, bf, M, N,
+                         K, sps, split, tok_fast, st->status_dev);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_fp4 launch failed (split=%d): %s", split, cudaGetErrorString(e));
   DQ_CHECK_CUDA(cudaGetLastError());

@@ -32,12 +32,6 @@
 #include "dq_common.h"
 #include "dq_ptx.cuh"
 
-#ifdef DQ_LANE0_WAIT
-#define DQ_WAIT_W(bar, par, flag, site) mbar_wait_warp(bar, par, flag, site, lane)
-#else
-#define DQ_WAIT_W(bar, par, flag, site) mbar_wait(bar, par, flag, site)
-#endif
-
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -244,7 +238,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
       const int sp = i % C::SP, b = i % C::NB;
       if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
       if (lane == 0) DQ_TR(0, i, 0);
-      if (!DQ_WAIT_W(&done[b], ((i / C::NB) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
+      if (!mbar_wait(&done[b], ((i / C::NB) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
       if (lane == 0) DQ_TR(0, i, 1);
       const uint8_t* src = smem + C::kOffP + sp * kWpBytes;
       uint8_t* dst = smem + C::kOffA + b * kWaBytes;
@@ -331,7 +325,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
       const float s = __half2float(__ushort_as_half(sreg)) * 0.0625f;
       if (i + kScaleAhead < ng) sreg = __ldg(sw_row + static_cast<size_t>(i + kScaleAhead) * kBN);
       if (!prefetched) {
-        if (!DQ_WAIT_W(&done[b], (gi / C::NB) & 1, abort_flag, SITE_EPI)) return false;
+        if (!mbar_wait(&done[b], (gi / C::NB) & 1, abort_flag, SITE_EPI)) return false;
         tc_fence_after();
         ld_chunk(b, 0, va);
       }

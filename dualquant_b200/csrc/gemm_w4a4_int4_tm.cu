@@ -34,12 +34,6 @@
 #include "dq_common.h"
 #include "dq_ptx.cuh"
 
-#ifdef DQ_LANE0_WAIT
-#define DQ_WAIT_W(bar, par, flag, site) mbar_wait_warp(bar, par, flag, site, lane)
-#else
-#define DQ_WAIT_W(bar, par, flag, site) mbar_wait(bar, par, flag, site)
-#endif
-
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -236,7 +230,7 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
           for (int ch = 0; ch < 4; ++ch) raw[h][ch] = src[ch ^ ((row >> 1) & 3)];  // swizzled position
         }
       }
-      if (!DQ_WAIT_W(&a_free[ab], ((s / C::NA) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
+      if (!mbar_wait(&a_free[ab], ((s / C::NA) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
       tc_fence_after();
 #pragma unroll
       for (int h = 0; h < kStepGroups; ++h) {
@@ -330,7 +324,7 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
         if (i + kScaleAhead < ng) sreg = __ldg(sw_row + static_cast<size_t>(i + kScaleAhead) * kBN);
       }
       if (!prefetched) {
-        if (!DQ_WAIT_W(&acc_done[b], (i / C::NB) & 1, abort_flag, SITE_EPI)) return false;
+        if (!mbar_wait(&acc_done[b], (i / C::NB) & 1, abort_flag, SITE_EPI)) return false;
         tc_fence_after();
         ld_chunk(b, 0, va);
       }

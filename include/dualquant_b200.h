@@ -219,6 +219,20 @@ DQ_API int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atoms, c
                             const float* r, int M, int N, int K, int fmt, void* y, int y_dtype,
                             void* stream);
 
+/*
+ * dq_gemm_w4a4_fp4 with the token tile chosen by the caller (same reference citation; the
+ * reference has no tile notion).  token_blocks = 1: 128 weight rows x 128 tokens per CTA, two
+ * CTAs per SM, split-K over a cluster for decode batches.  token_blocks = 2: 128 x 256, one CTA
+ * per SM, the weight tile of a stage fetched once for two token blocks (no split-K: fails with
+ * DQ_ERR_UNSUPPORTED where the 128-token path would split).  0 = the library's own choice, which
+ * is what dq_gemm_w4a4_fp4 passes.  Results are identical for every choice.
+ */
+DQ_API int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_sf_atoms,
+                                  const float* x_scale, const uint8_t* w_codes,
+                                  const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
+                                  int M, int N, int K, int fmt, void* y, int y_dtype,
+                                  int token_blocks, void* stream);
+
 /* ---- int4 dual-scale GEMM ------------------------------------------------------------------ */
 
 /* Scratch bytes dq_gemm_w4a4_int4 needs for (M,N,K); may be 0. */

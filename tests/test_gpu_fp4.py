@@ -138,6 +138,42 @@ def test_fp4_gemm_matches_dequant_matmul(fmt, M, N, K):
 
 
 @pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
+@pytest.mark.parametrize("M,N,K", [(256, 128, 256), (130, 200, 768), (257, 384, 512), (384, 136, 768),
+                                   (1000, 4096, 1024), (70, 128, 512)])
+def test_fp4_gemm_token_tiles_agree(fmt, M, N, K):
+    """The 128- and the 256-token tile give the same output bit for bit (same products, same
+    K order in one fp32 accumulator), full, ragged and single-block tiles alike, and both match
+    the de-quantised fp32 matmul."""
+    x = synthetic.make_x(M, K, M + 5)
+    w = synthetic.make_w(N, K, N + 6)
+    r, c = synthetic.make_scales(N, K, 7)
+    a = (1.0 / c).to(DEV)
+    pw = ops.pack_w_fp4(w.to(DEV), fmt)
+    codes, sf, rs = ops.quant_fp4(x.to(DEV), fmt, a, None)
+    sfa = ops.fp4_sf_to_atoms(sf, K, fmt)
+    y1 = ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r.to(DEV), token_blocks=1)
+    y2 = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r.to(DEV), out=y2, token_blocks=2)
+    _lib.device_status(0)
+    assert torch.equal(y1, y2)
+    ref = _fp4_reference(x, a.cpu(), w, r, fmt)
+    err = ((y2.double().cpu() - ref).abs().max() / ref.abs().max()).item()
+    assert err < 1e-3, err
+
+
+def test_fp4_wide_tile_rejects_split_k_shapes():
+    M, N, K = 16, 256, 2048  # a decode batch: the 128-token path splits K over a cluster
+    x = synthetic.make_x(M, K, 1).to(DEV)
+    pw = ops.pack_w_fp4(synthetic.make_w(N, K, 2).to(DEV), _lib.FP4_MXFP4)
+    codes, sf, rs = ops.quant_fp4(x, _lib.FP4_MXFP4, None, None)
+    sfa = ops.fp4_sf_to_atoms(sf, K, _lib.FP4_MXFP4)
+    with pytest.raises((RuntimeError, ValueError)):
+        ops.gemm_w4a4_fp4(codes, sfa, rs, pw, None, token_blocks=2)
+    with pytest.raises((RuntimeError, ValueError)):
+        ops.gemm_w4a4_fp4(codes, sfa, rs, pw, None, token_blocks=3)
+
+
+@pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
 @pytest.mark.parametrize("M,K", [(1, 256), (130, 512), (256, 1024), (37, 3584)])
 def test_quantiser_writes_scale_factors_in_gemm_order(fmt, M, K):
     x = synthetic.make_x(M, K, M + K).to(DEV)
