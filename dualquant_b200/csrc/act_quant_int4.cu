@@ -448,14 +448,16 @@ __device__ __forceinline__ void wht_segment_warp(float* seg, int lane) {
 // shared-memory load plus an FMA).  Refreshed by the host when a call brings a different matrix.
 __constant__ float c_had_mat[32 * 32];
 
-template <int R, typename XT>
-__global__ void __launch_bounds__(512)
+// THREADS = 512: one CTA per SM, the shortest time per row (decode batches, one row per SM at most).
+// THREADS = 256: three CTAs per SM; with many rows one row's load, barrier and store phases overlap
+// another row's arithmetic.
+template <int R, typename XT, int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 3 : 1)
 act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_t ldx,
                           const float* __restrict__ a, int K,
                           int S, int inner, int matrix, float had_scale,
                           const float* __restrict__ had_mat, int8_t* __restrict__ codes,
                           float* __restrict__ sx, float* __restrict__ out, int mode, int scale_fp16) {
-  constexpr int THREADS = 512;
   extern __shared__ float sm_row[];
   __shared__ float red[THREADS / 32];
   float* row = sm_row;
@@ -613,7 +615,10 @@ int init_act_quant_kernels() {
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
 #define DQ_HAD_ATTR(R, T)                                                                     \
   if (e == cudaSuccess)                                                                       \
-    e = cudaFuncSetAttribute(act_quant_had_fast_kernel<R, T>,                                   \
+    e = cudaFuncSetAttribute(act_quant_had_fast_kernel<R, T, 512>,                              \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);        \
+  if (e == cudaSuccess)                                                                       \
+    e = cudaFuncSetAttribute(act_quant_had_fast_kernel<R, T, 256>,                              \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
   DQ_HAD_ATTR(1, __nv_bfloat16) DQ_HAD_ATTR(2, __nv_bfloat16) DQ_HAD_ATTR(4, __nv_bfloat16)
   DQ_HAD_ATTR(8, __nv_bfloat16) DQ_HAD_ATTR(16, __nv_bfloat16) DQ_HAD_ATTR(32, __nv_bfloat16)
@@ -679,10 +684,18 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
         int rc2 = upload_had_matrix(had->had_mat, plan.S, stream);
         if (rc2 != DQ_OK) return rc2;
       }
+      // many rows: smaller CTAs, several per SM (the row must leave room for three of them)
+      const DeviceState* dst = current_state();
+      const bool small_cta = dst != nullptr && M > 2 * dst->sm_count && smem <= 72 * 1024;
 #define DQ_HAD_FAST(RR)                                                                          \
-  DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT>, dim3(M), dim3(512), smem, stream, x, up, ldx, a, \
-                           K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes, sx, out,   \
-                           mode, scale_fp16))
+  if (small_cta)                                                                                 \
+    DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT, 256>, dim3(M), dim3(256), smem, stream, x, up, \
+                             ldx, a, K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes,   \
+                             sx, out, mode, scale_fp16));                                                    \
+  else                                                                                           \
+    DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT, 512>, dim3(M), dim3(512), smem, stream, x, up, \
+                             ldx, a, K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes,   \
+                             sx, out, mode, scale_fp16))
       switch (plan.R) {
         case 1: DQ_HAD_FAST(1); break;
         case 2: DQ_HAD_FAST(2); break;
