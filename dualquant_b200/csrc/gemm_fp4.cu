@@ -25,7 +25,6 @@ namespace dq {
 constexpr int kFBN = 128;      // weight rows per CTA
 constexpr int kFTN = 128;      // tokens per CTA
 constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
-constexpr int kFp4WideMinK = 8192;  // automatic choice of the 256-token tile: K at least this
 constexpr int kFTileBytes = 128 * 128;  // one operand tile of 128 rows
 constexpr int kFThreads = 256;  // producer, UMMA issuer, 4 epilogue warps, 2 scale-factor copiers
 
@@ -424,12 +423,10 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
     const int tiles1 = ((N + kFBN - 1) / kFBN) * ((M + kFTN - 1) / kFTN);
     while (split < 8 && tiles1 * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
   }
-  // 256-token tiles: for long K loops with enough tiles to fill the SMs at one CTA each
-  int nt = token_blocks;
-  if (nt == 0) {
-    const int tiles2 = ((N + kFBN - 1) / kFBN) * ((M + 2 * kFTN - 1) / (2 * kFTN));
-    nt = (split == 1 && K >= kFp4WideMinK && tiles2 >= 2 * st->sm_count) ? 2 : 1;
-  }
+  // The library's own choice is the 128-token tile: measured on every BASELINE config 3 shape at
+  // M = 4096 the 256-token tile is 18-35 % slower (one CTA and one UMMA-issuing thread per SM
+  // instead of two), although it pulls a quarter less operand data out of L2.
+  const int nt = (token_blocks == 0) ? 1 : token_blocks;
   DQ_REQUIRE(nt == 1 || split == 1, DQ_ERR_UNSUPPORTED,
              "256-token tiles have no split-K path (M=%d N=%d K=%d would split %d ways)", M, N, K, split);
   const int tile_tok = nt * kFTN;
