@@ -41,6 +41,9 @@ EncodeTiledFn encode_tiled_fn();
 int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
                     uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows,
                     CUtensorMapSwizzle swizzle);
+// 2-D row-major fp32 / bf16 output matrix for tiled bulk stores (no swizzle).
+int make_tmap_2d_out(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
+                     uint32_t box_cols, uint32_t box_rows);
 int make_tmap_x_groups(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
                        uint32_t box_rows, uint32_t box_groups);
 

@@ -141,6 +141,23 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       : "memory");
 }
 
+// Tiled bulk store shared -> global (never a reduce, never at a negative coordinate; x * element
+// size must be a multiple of 16 bytes).  Rows and columns of the box that fall outside the tensor
+// are not written.  The issuing thread tracks completion with a bulk group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::
+                   "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until every committed bulk store of this thread has finished READING shared memory (the
+// global writes themselves complete by the end of the grid).
+__device__ __forceinline__ void bulk_wait_group_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tm, int x, int y,
                                             int z, uint64_t* bar, uint64_t policy) {
   asm volatile(

@@ -60,6 +60,25 @@ int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint
   return DQ_OK;
 }
 
+// 2-D row-major output matrix [rows, cols] of fp32 (elem_bytes 4) or bf16 (2), row pitch
+// cols * elem_bytes, box = box_rows x box_cols elements, no swizzle: the map of a tiled bulk store.
+int make_tmap_2d_out(CUtensorMap* out, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
+                     uint32_t box_cols, uint32_t box_rows) {
+  if (g_encode == nullptr) return set_error(DQ_ERR_NOT_INIT, "tensor-map encoder not resolved");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                        2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(DQ_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed (%d): base=%p cols=%llu rows=%llu box=%ux%u",
+                     (int)r, base, (unsigned long long)cols, (unsigned long long)rows, box_cols, box_rows);
+  return DQ_OK;
+}
+
 // Activation codes [rows][row_bytes] seen as (128-byte group chunk, row, group): one box is
 // `box_groups` consecutive K groups of `box_rows` rows, laid out in shared memory as
 // [group][row][128 B] (each group block is one 128B-swizzled UMMA operand tile).

@@ -100,6 +100,7 @@ __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint6
 template <int NVFP4, int NT>
 __global__ void __launch_bounds__(kFThreads, FCfg<NT>::kMinCtas)
 gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                const __grid_constant__ CUtensorMap tm_y, int bulk_store,
                 const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx,
                 const float* __restrict__ r, const float* __restrict__ w_scale,
                 const float* __restrict__ x_scale, void* __restrict__ y, int y_bf16, int M, int N,
@@ -148,6 +149,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
+    if (bulk_store) tma_prefetch_desc(&tm_y);
   }
   tc_fence_before();
   __syncthreads();
@@ -188,19 +190,20 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         tc_fence_after();
         const uint32_t sfa_t = tmem_base + C::kSfColBase + s * C::kSfColsStage;
         const uint64_t da = umma_desc_k_sw128(smem_u32(smem + C::kOffA + s * kFTileBytes));
+        // One instruction per K = 64 step covers every token block of the CTA (UMMA N = 128 or
+        // 256): the weight slice is read from shared memory once per step.  Scale factors of the
+        // token rows: 4 columns per block of 128 rows, blocks side by side (rows 128..255 follow
+        // rows 0..127), 4 * NT columns per atom.
+        {
+          const uint32_t sfb_t = sfa_t + 16;
+          const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + s * NT * kFTileBytes));
 #pragma unroll
-        for (int b = 0; b < NT; ++b) {  // token block b: its own accumulator and scale-factor columns
-          if (b < nblk) {
-            const uint32_t sfb_t = sfa_t + 16 + b * 16;
-            const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + (s * NT + b) * kFTileBytes));
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {  // four K=64 UMMAs: +32 bytes along K each
-              const int atom = NVFP4 ? j : (j >> 1);
-              const uint32_t sf_id = NVFP4 ? 0u : static_cast<uint32_t>((j & 1) * 2);
-              const uint32_t idesc = umma_idesc_fp4(kFBN, kFTN, NVFP4 ? 0 : 1, sf_id);
-              umma_fp4<NVFP4>(tmem_base + b * kFTN, da + 2 * j, db + 2 * j, idesc, sfa_t + 4 * atom,
-                              sfb_t + 4 * atom, (i > 0 || j > 0) ? 1u : 0u);
-            }
+          for (int j = 0; j < 4; ++j) {  // four K=64 UMMAs: +32 bytes along K each
+            const int atom = NVFP4 ? j : (j >> 1);
+            const uint32_t sf_id = NVFP4 ? 0u : static_cast<uint32_t>((j & 1) * 2);
+            const uint32_t idesc = umma_idesc_fp4(kFBN, nblk * kFTN, NVFP4 ? 0 : 1, sf_id);
+            umma_fp4<NVFP4>(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa_t + 4 * atom,
+                            sfb_t + 4 * NT * atom, (i > 0 || j > 0) ? 1u : 0u);
           }
         }
         umma_commit(&empty[s]);
@@ -228,7 +231,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
           const uint32_t src = smem_u32(smem + sf_off + (s * (is_b ? NT : 1) + b) * 2048);
 #pragma unroll
           for (int at = 0; at < kAtoms; ++at)
-            tmem_cp_32x128b_warpx4(sf_t + b * 16 + 4 * at, sf_atom_desc(src + at * 512));
+            tmem_cp_32x128b_warpx4(sf_t + (is_b ? 4 * NT * at + 4 * b : 4 * at), sf_atom_desc(src + at * 512));
         }
         umma_commit(&sf_ready[s]);
       }
@@ -258,7 +261,30 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = 0u;
       }
-      if (split_k == 1) {
+      if (split_k == 1 && bulk_store) {
+        // Through shared memory and out with one tiled bulk store per 32 tokens: the chunk is
+        // laid out [token][128 weight rows] (a lane writes its row's column: conflict-free), the
+        // copy engine writes 512-byte (fp32) runs per token and skips rows / tokens that do not
+        // exist.  The operand stages are idle by now; every chunk has its own 16 KB of them, so no
+        // chunk waits for an earlier store to have been read.
+        uint8_t* buf = smem + (c0 >> 5) * (32 * kFBN * 4);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int m = t0 + c0 + j;
+          const float tx = (x_scale != nullptr && m < M) ? x_scale[m] : 1.f;
+          const float val = __uint_as_float(v[j]) * (rn * tx);
+          if (y_bf16)
+            reinterpret_cast<__nv_bfloat16*>(buf)[j * kFBN + q * 32 + lane] = __float2bfloat16_rn(val);
+          else
+            reinterpret_cast<float*>(buf)[j * kFBN + q * 32 + lane] = val;
+        }
+        fence_proxy_async_smem();  // generic-proxy writes before the async-proxy read of the store
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (warp == 2 && lane == 0) {
+          tma_store_2d(&tm_y, buf, n0, t0 + c0);
+          bulk_commit_group();
+        }
+      } else if (split_k == 1) {
         if (n < N) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -280,6 +306,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         for (int j = 0; j < 32; ++j) red[(c0 + j) * kFBN + q * 32 + lane] = __uint_as_float(v[j]);
       }
     }
+    // shared memory must outlive the copy engine's reads of the staged chunks
+    if (split_k == 1 && bulk_store && warp == 2 && lane == 0) bulk_wait_group_read0();
   }
 
   // -------------------------------------------------------------------- split-K reduction
@@ -437,6 +465,15 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   rc = make_tmap_2d_u8(&tm_x, x_codes, static_cast<uint64_t>(K) / 2, M, static_cast<uint64_t>(K) / 2, 128,
                        tile_tok, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != DQ_OK) return rc;
+  // Output through tiled bulk stores when the copy engine can address it (16-byte pitch and
+  // base); the split-K path reduces through distributed shared memory and stores directly.
+  const int esz = (y_dtype == DQ_DTYPE_BF16) ? 2 : 4;
+  const int bulk_store = (split == 1 && (static_cast<size_t>(N) * esz) % 16 == 0 && aligned(y, 16)) ? 1 : 0;
+  CUtensorMap tm_y = tm_w;  // a valid map is passed either way; unused without bulk_store
+  if (bulk_store) {
+    rc = make_tmap_2d_out(&tm_y, y, esz, static_cast<uint64_t>(N), static_cast<uint64_t>(M), kFBN, 32);
+    if (rc != DQ_OK) return rc;
+  }
   const int sps = (total_st + split - 1) / split;
   cudaLaunchConfig_t cfg = {};
   const int row_tiles = (N + kFBN - 1) / kFBN, tok_tiles = (M + tile_tok - 1) / tile_tok;
@@ -457,7 +494,7 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   cudaError_t e;
   auto kern = (fmt == DQ_FP4_NVFP4) ? (nt == 2 ? gemm_fp4_kernel<1, 2> : gemm_fp4_kernel<1, 1>)
                                     : (nt == 2 ? gemm_fp4_kernel<0, 2> : gemm_fp4_kernel<0, 1>);
-  e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, w_sf_atoms, x_sf_atoms, r, w_scale, x_scale, y, bf, M, N,
+  e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, tm_y, bulk_store, w_sf_atoms, x_sf_atoms, r, w_scale, x_scale, y, bf, M, N,
                          K, sps, split, tok_fast, st->status_dev);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_fp4 launch failed (split=%d): %s", split, cudaGetErrorString(e));

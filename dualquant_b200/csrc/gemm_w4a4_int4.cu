@@ -381,17 +381,25 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
       if (!ok) break;
       if (split_k == 1) {
         if (n < N) {
+          // One running pointer per thread (a 64-bit add per token instead of a multiply and the
+          // m < M / dtype tests per element): these stores are on the epilogue warps' own chain.
           const float rn = (r != nullptr) ? r[n] : 1.f;
+          const int m0 = t0 + h * C::CPW;
+          const int cnt = (M - m0 < C::CPW) ? (M - m0) : C::CPW;  // tokens of this slice that exist
+          const float* sxp = sx + m0;
+          if (y_bf16) {
+            __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(y) + static_cast<size_t>(m0) * N + n;
 #pragma unroll
-          for (int j = 0; j < C::CPW; ++j) {
-            const int m = t0 + h * C::CPW + j;
-            if (m < M) {
-              const float val = run[j] * (rn * sx[m]);
-              if (y_bf16)
-                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                    __float2bfloat16_rn(val);
-              else
-                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+            for (int j = 0; j < C::CPW; ++j) {
+              if (j < cnt) *yp = __float2bfloat16_rn(run[j] * (rn * __ldg(sxp + j)));
+              yp += N;
+            }
+          } else {
+            float* yp = reinterpret_cast<float*>(y) + static_cast<size_t>(m0) * N + n;
+#pragma unroll
+            for (int j = 0; j < C::CPW; ++j) {
+              if (j < cnt) *yp = run[j] * (rn * __ldg(sxp + j));
+              yp += N;
             }
           }
         }
