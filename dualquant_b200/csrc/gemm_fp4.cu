@@ -236,8 +236,16 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         umma_commit(&sf_ready[s]);
       }
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue warps
+  }
+  __syncwarp();  // the role warps' lane 0 rejoins its warp
+  // -------------------------------------------------------------------- epilogue
+  // Two teams of four warps, one warp per TMEM lane quarter in each: warps 2-5, which have no
+  // other role, and - when the output goes through bulk stores - the producer, issuer and copier
+  // warps once their loops are over (four warps alone are too few to hide the latency of their own
+  // instruction chains).  The teams take alternate 32-token chunks.
+  const int team = (warp >= 2 && warp < 6) ? 0 : 1;
+  const int nteams = (split_k == 1 && bulk_store) ? 2 : 1;
+  if (team < nteams) {
     const int q = warp & 3;  // TMEM lane quarter of this warp
     const int n = n0 + q * 32 + lane;
     // token columns that exist in this tile, rounded up to the 32-column granularity of tcgen05.ld
@@ -252,7 +260,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       if (w_scale != nullptr) rn *= *w_scale;
     }
 #pragma unroll 1
-    for (int c0 = 0; c0 < col_end; c0 += 32) {
+    for (int c0 = team * 32; c0 < col_end; c0 += 32 * nteams) {
       uint32_t v[32];
       if (have_acc) {
         tmem_ld_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
@@ -279,8 +287,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             reinterpret_cast<float*>(buf)[j * kFBN + q * 32 + lane] = val;
         }
         fence_proxy_async_smem();  // generic-proxy writes before the async-proxy read of the store
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-        if (warp == 2 && lane == 0) {
+        if (team == 0)  // the four warps of the team
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        else
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+        if ((warp == 2 || warp == 0) && lane == 0) {
           tma_store_2d(&tm_y, buf, n0, t0 + c0);
           bulk_commit_group();
         }
@@ -307,7 +318,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       }
     }
     // shared memory must outlive the copy engine's reads of the staged chunks
-    if (split_k == 1 && bulk_store && warp == 2 && lane == 0) bulk_wait_group_read0();
+    if (split_k == 1 && bulk_store && (warp == 2 || warp == 0) && lane == 0) bulk_wait_group_read0();
   }
 
   // -------------------------------------------------------------------- split-K reduction
