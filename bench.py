@@ -777,8 +777,9 @@ def run_fp4_suite(args):
 
 
 def _fp4_prologue(ops, x, a, pw):
-    codes, sf, rs = ops.quant_fp4(x, pw.fmt, a, None)
-    return codes, ops.fp4_sf_to_atoms(sf, pw.K, pw.fmt), rs
+    """Activation quantiser of the FP4 linear, as ops.linear_w4a4_fp4 runs it: one launch that
+    writes the scale bytes in the order the GEMM streams."""
+    return ops.quant_fp4(x, pw.fmt, a, None, atoms=True)
 
 
 def per_shape_detail(wl, dev, args):

@@ -25,10 +25,14 @@ namespace dq {
 constexpr int kFBN = 128;      // weight rows per CTA
 constexpr int kFTN = 128;      // tokens per CTA
 constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
+constexpr int kFp4DecodeTokens = 0;  // library's choice of the 32-token tile: M up to this
 constexpr int kFTileBytes = 128 * 128;  // one operand tile of 128 rows
 constexpr int kFThreads = 256;  // producer, UMMA issuer, 4 epilogue warps, 2 scale-factor copiers
 
-// NT = token blocks of 128 per CTA.
+// NT = token blocks of 128 per CTA; NT = 0 is the decode tile of 32 tokens.
+//   NT = 0: 128 weight rows x 32 tokens (UMMA N = 32): a stage is 24 KB instead of 36 KB, of which
+//           only the 16 KB weight tile comes from HBM, so four stages fit where three did and more
+//           weight bytes are in flight per SM.  Two CTAs per SM, split-K over a cluster.
 //   NT = 1: 3 stages of 36 KB and 256 tensor-memory columns, so two CTAs share an SM and one's
 //           epilogue overlaps the other's K loop.
 //   NT = 2: 128 weight rows x 256 tokens.  The weight tile of a stage is fetched once for two
@@ -37,21 +41,24 @@ constexpr int kFThreads = 256;  // producer, UMMA issuer, 4 epilogue warps, 2 sc
 //           the 128x128 tile.  4 stages of 54 KB, one CTA per SM, two fp32 accumulators.
 template <int NT>
 struct FCfg {
+  static constexpr int kTok = (NT == 0) ? 32 : NT * kFTN;   // tokens per CTA
+  static constexpr int kSfBlocks = (NT == 0) ? 1 : NT;      // blocks of 128 token rows whose scale factors a stage holds
+  static constexpr int kBTileBytes = kTok * 128;            // activation tile of a stage
   static constexpr int kStages = (NT == 1) ? 3 : 4;
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + kStages * kFTileBytes;
-  static constexpr int kOffSFA = kOffB + kStages * NT * kFTileBytes;  // up to 2 KB per stage
-  static constexpr int kOffSFB = kOffSFA + kStages * 2048;            // up to NT x 2 KB per stage
-  static constexpr int kOffBar = kOffSFB + kStages * NT * 2048;
+  static constexpr int kOffSFA = kOffB + kStages * kBTileBytes;       // up to 2 KB per stage
+  static constexpr int kOffSFB = kOffSFA + kStages * 2048;            // up to 2 KB per block and stage
+  static constexpr int kOffBar = kOffSFB + kStages * kSfBlocks * 2048;
   static constexpr int kSmemBytes = kOffBar + (3 * kStages + 1) * 8 + 16 + 1024;
-  static_assert(kFTN * kFBN * 4 <= kOffSFA, "split-K exchange tile must fit in the operand stages");
+  static_assert(((kTok < kFTN) ? kTok : kFTN) * kFBN * 4 <= kOffSFA, "split-K exchange tile must fit in the operand stages");
   static_assert(kSmemBytes <= 227 * 1024, "stages exceed the shared memory of an SM");
-  static constexpr int kAccCols = NT * kFTN;          // fp32 accumulator columns
-  static constexpr int kSfColsStage = 16 + NT * 16;   // scale-factor columns per stage: A, then B per block
+  static constexpr int kAccCols = (NT == 0) ? 32 : NT * kFTN;  // fp32 accumulator columns
+  static constexpr int kSfColsStage = 16 + kSfBlocks * 16;  // scale-factor columns per stage: A, then B per block
   static constexpr int kSfColBase = kAccCols;
-  static constexpr int kTmemCols = (NT == 1) ? 256 : 512;
+  static constexpr int kTmemCols = (NT == 2) ? 512 : 256;
   static_assert(kSfColBase + kStages * kSfColsStage <= kTmemCols, "tensor memory columns");
-  static constexpr int kMinCtas = (NT == 1) ? 2 : 1;
+  static constexpr int kMinCtas = (NT == 2) ? 1 : 2;
 };
 
 enum { FSITE_TMA = 31, FSITE_MMA = 32, FSITE_EPI = 33, FSITE_SF = 34 };
@@ -123,7 +130,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   // tok_fast: grid x walks the token tiles (CTAs that run together share one weight tile and the
   // whole, smaller, activation matrix stays in L2); otherwise grid x walks the row tiles
   const int n0 = (tok_fast ? blockIdx.y : blockIdx.x) * kFBN;
-  const int t0 = (tok_fast ? blockIdx.x : blockIdx.y) * (NT * kFTN);
+  const int t0 = (tok_fast ? blockIdx.x : blockIdx.y) * C::kTok;
   // token blocks of this CTA that hold tokens (the last CTA of a ragged M may own only one)
   const int nblk = (NT == 2 && M - t0 > kFTN) ? 2 : 1;
   const int total_st = K / kFKStage;
@@ -168,14 +175,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       for (int i = 0; i < nst; ++i) {
         const int s = i % kFStages;
         if (!mbar_wait(&empty[s], ((i / kFStages) & 1) ^ 1, abort_flag, FSITE_TMA)) break;
-        // the activation box is NT x 128 token rows (rows past M arrive as zeros and count)
-        mbar_expect_tx(&full[s], (1 + NT) * kFTileBytes + (1 + nblk) * kSfBytes);
+        // the activation box is the CTA's whole token tile (rows past M arrive as zeros and count)
+        mbar_expect_tx(&full[s], kFTileBytes + C::kBTileBytes + (1 + nblk) * kSfBytes);
         tma_load_2d(smem + C::kOffA + s * kFTileBytes, &tm_w, (st_begin + i) * 128, n0, &full[s], pol);
-        tma_load_2d(smem + C::kOffB + s * NT * kFTileBytes, &tm_x, (st_begin + i) * 128, t0, &full[s], pol);
+        tma_load_2d(smem + C::kOffB + s * C::kBTileBytes, &tm_x, (st_begin + i) * 128, t0, &full[s], pol);
         bulk_load_1d(smem + C::kOffSFA + s * 2048, sfw_tile + static_cast<size_t>(i) * kSfBytes,
                      kSfBytes, &full[s], pol);
         for (int b = 0; b < nblk; ++b)
-          bulk_load_1d(smem + C::kOffSFB + (s * NT + b) * 2048,
+          bulk_load_1d(smem + C::kOffSFB + (s * C::kSfBlocks + b) * 2048,
                        sfx_tile + b * sfx_block + static_cast<size_t>(i) * kSfBytes, kSfBytes, &full[s], pol);
       }
     }
@@ -195,15 +202,17 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         // token rows: 4 columns per block of 128 rows, blocks side by side (rows 128..255 follow
         // rows 0..127), 4 * NT columns per atom.
         {
-          const uint32_t sfb_t = sfa_t + 16;
-          const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + s * NT * kFTileBytes));
+          // a 32-token tile is one quarter of a 128-row scale-factor block: rows 32 q .. 32 q + 31 of
+          // the block sit in column q of each atom
+          const uint32_t sfb_t = sfa_t + 16 + ((NT == 0) ? static_cast<uint32_t>((t0 % kFTN) / 32) : 0u);
+          const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + s * C::kBTileBytes));
 #pragma unroll
           for (int j = 0; j < 4; ++j) {  // four K=64 UMMAs: +32 bytes along K each
             const int atom = NVFP4 ? j : (j >> 1);
             const uint32_t sf_id = NVFP4 ? 0u : static_cast<uint32_t>((j & 1) * 2);
-            const uint32_t idesc = umma_idesc_fp4(kFBN, nblk * kFTN, NVFP4 ? 0 : 1, sf_id);
+            const uint32_t idesc = umma_idesc_fp4(kFBN, (NT == 0) ? 32 : nblk * kFTN, NVFP4 ? 0 : 1, sf_id);
             umma_fp4<NVFP4>(tmem_base, da + 2 * j, db + 2 * j, idesc, sfa_t + 4 * atom,
-                            sfb_t + 4 * NT * atom, (i > 0 || j > 0) ? 1u : 0u);
+                            sfb_t + 4 * C::kSfBlocks * atom, (i > 0 || j > 0) ? 1u : 0u);
           }
         }
         umma_commit(&empty[s]);
@@ -228,10 +237,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         const uint32_t sf_t = tmem_base + C::kSfColBase + s * C::kSfColsStage + (is_b ? 16 : 0);
         const int blocks = is_b ? nblk : 1;
         for (int b = 0; b < blocks; ++b) {
-          const uint32_t src = smem_u32(smem + sf_off + (s * (is_b ? NT : 1) + b) * 2048);
+          const uint32_t src = smem_u32(smem + sf_off + (s * (is_b ? C::kSfBlocks : 1) + b) * 2048);
 #pragma unroll
           for (int at = 0; at < kAtoms; ++at)
-            tmem_cp_32x128b_warpx4(sf_t + (is_b ? 4 * NT * at + 4 * b : 4 * at), sf_atom_desc(src + at * 512));
+            tmem_cp_32x128b_warpx4(sf_t + (is_b ? 4 * C::kSfBlocks * at + 4 * b : 4 * at),
+                                   sf_atom_desc(src + at * 512));
         }
         umma_commit(&sf_ready[s]);
       }
@@ -250,7 +260,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const int n = n0 + q * 32 + lane;
     // token columns that exist in this tile, rounded up to the 32-column granularity of tcgen05.ld
     int tok_cols = M - t0;
-    if (tok_cols > NT * kFTN) tok_cols = NT * kFTN;
+    if (tok_cols > C::kTok) tok_cols = C::kTok;
     const int col_end = (tok_cols + 31) & ~31;
     const bool have_acc = (nst > 0) && mbar_wait_relaxed(acc_full, 0, abort_flag, FSITE_EPI);
     if (have_acc) tc_fence_after();
@@ -327,7 +337,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     cluster_sync_all();
     if (warp >= 2 && warp < 6) {
       int tok_cols = M - t0;
-      if (tok_cols > kFTN) tok_cols = kFTN;
+      if (tok_cols > C::kTok) tok_cols = C::kTok;
       const uint32_t rank = cluster_ctarank();
       const int e = tid - 64;   // 0..127
       const int c4 = e & 31;    // float4 column (4 weight rows)
@@ -395,6 +405,12 @@ int init_gemm_fp4_kernels() {
     e = cudaFuncSetAttribute(gemm_fp4_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              FCfg<1>::kSmemBytes);
   if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_fp4_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             FCfg<0>::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_fp4_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             FCfg<0>::kSmemBytes);
+  if (e == cudaSuccess)
     e = cudaFuncSetAttribute(gemm_fp4_kernel<0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              FCfg<2>::kSmemBytes);
   if (e == cudaSuccess)
@@ -434,14 +450,14 @@ extern "C" int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atom
                                 const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
                                 int M, int N, int K, int fmt, void* y, int y_dtype, void* stream) {
   return dq_gemm_w4a4_fp4_tiled(x_codes, x_sf_atoms, x_scale, w_codes, w_sf_atoms, w_scale, r, M, N, K,
-                                fmt, y, y_dtype, 0, stream);
+                                fmt, y, y_dtype, 0, stream);  // 0: the library picks the token tile
 }
 
 extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_sf_atoms,
                                       const float* x_scale, const uint8_t* w_codes,
                                       const uint8_t* w_sf_atoms, const float* w_scale,
                                       const float* r, int M, int N, int K, int fmt, void* y,
-                                      int y_dtype, int token_blocks, void* stream) {
+                                      int y_dtype, int token_tile, void* stream) {
   DeviceState* st = current_state();
   if (st == nullptr) return DQ_ERR_NOT_INIT;
   if (M == 0) return DQ_OK;
@@ -453,22 +469,22 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
                  aligned(w_sf_atoms, 16),
              DQ_ERR_ALIGN, "operands must be 16-byte aligned");
   DQ_REQUIRE(y_dtype == DQ_DTYPE_F32 || y_dtype == DQ_DTYPE_BF16, DQ_ERR_UNSUPPORTED, "unknown y_dtype %d", y_dtype);
-  DQ_REQUIRE(token_blocks >= 0 && token_blocks <= 2, DQ_ERR_SHAPE, "token_blocks must be 0 (auto), 1 or 2, got %d",
-             token_blocks);
+  DQ_REQUIRE(token_tile == 0 || token_tile == 32 || token_tile == 128 || token_tile == 256, DQ_ERR_SHAPE,
+             "token_tile must be 0 (library's choice), 32, 128 or 256, got %d", token_tile);
   const int total_st = K / kFKStage;
+  // The library's own choice: 32-token tiles for decode batches, else 128.  The 256-token tile is
+  // not chosen: measured on the BASELINE config 3 shapes at M = 4096 it is 3 % faster on the
+  // longest K loop and 2-15 % slower elsewhere (one CTA and one UMMA-issuing thread per SM).
+  const int tile_tok = token_tile ? token_tile : (M <= kFp4DecodeTokens ? 32 : kFTN);
+  const int nt = tile_tok == 32 ? 0 : tile_tok / kFTN;
   // split K across a cluster when the output tiles alone leave most SMs idle (decode batches)
   int split = 1;
   {
-    const int tiles1 = ((N + kFBN - 1) / kFBN) * ((M + kFTN - 1) / kFTN);
+    const int tiles1 = ((N + kFBN - 1) / kFBN) * ((M + tile_tok - 1) / tile_tok);
     while (split < 8 && tiles1 * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
   }
-  // The library's own choice is the 128-token tile: measured on every BASELINE config 3 shape at
-  // M = 4096 the 256-token tile is 18-35 % slower (one CTA and one UMMA-issuing thread per SM
-  // instead of two), although it pulls a quarter less operand data out of L2.
-  const int nt = (token_blocks == 0) ? 1 : token_blocks;
-  DQ_REQUIRE(nt == 1 || split == 1, DQ_ERR_UNSUPPORTED,
+  DQ_REQUIRE(nt != 2 || split == 1, DQ_ERR_UNSUPPORTED,
              "256-token tiles have no split-K path (M=%d N=%d K=%d would split %d ways)", M, N, K, split);
-  const int tile_tok = nt * kFTN;
   CUtensorMap tm_w, tm_x;
   int rc = make_tmap_2d_u8(&tm_w, w_codes, static_cast<uint64_t>(K) / 2, N, static_cast<uint64_t>(K) / 2,
                            128, kFBN, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -492,7 +508,7 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   const int tok_fast = (tok_tiles > 1 && M < N && row_tiles <= 65535) ? 1 : 0;
   cfg.gridDim = tok_fast ? dim3(tok_tiles, row_tiles, split) : dim3(row_tiles, tok_tiles, split);
   cfg.blockDim = dim3(kFThreads, 1, 1);
-  cfg.dynamicSmemBytes = (nt == 2) ? FCfg<2>::kSmemBytes : FCfg<1>::kSmemBytes;
+  cfg.dynamicSmemBytes = (nt == 2) ? FCfg<2>::kSmemBytes : (nt == 1) ? FCfg<1>::kSmemBytes : FCfg<0>::kSmemBytes;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -503,8 +519,9 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   cfg.numAttrs = 1;
   const int bf = y_dtype == DQ_DTYPE_BF16 ? 1 : 0;
   cudaError_t e;
-  auto kern = (fmt == DQ_FP4_NVFP4) ? (nt == 2 ? gemm_fp4_kernel<1, 2> : gemm_fp4_kernel<1, 1>)
-                                    : (nt == 2 ? gemm_fp4_kernel<0, 2> : gemm_fp4_kernel<0, 1>);
+  auto kern = (fmt == DQ_FP4_NVFP4)
+                  ? (nt == 2 ? gemm_fp4_kernel<1, 2> : nt == 1 ? gemm_fp4_kernel<1, 1> : gemm_fp4_kernel<1, 0>)
+                  : (nt == 2 ? gemm_fp4_kernel<0, 2> : nt == 1 ? gemm_fp4_kernel<0, 1> : gemm_fp4_kernel<0, 0>);
   e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, tm_y, bulk_store, w_sf_atoms, x_sf_atoms, r, w_scale, x_scale, y, bf, M, N,
                          K, sps, split, tok_fast, st->status_dev);
   if (e != cudaSuccess)

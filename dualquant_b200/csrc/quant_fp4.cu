@@ -74,7 +74,10 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
                  const float* __restrict__ tensor_scale, uint8_t* __restrict__ codes,
                  uint8_t* __restrict__ sf, float* __restrict__ row_scale, float* __restrict__ out,
                  int mode, int M, int sf_atoms) {
+  // THREADS bounds the launch; the CTA may be smaller (a multiple of 32): vectors are dealt out
+  // with the launched size as the stride, so that a row of K/8 vectors leaves few idle slots.
   __shared__ float red[THREADS / 32];
+  const int nthreads = static_cast<int>(blockDim.x);
   const int row = blockIdx.x;
   // sf_atoms: the scale bytes go straight into the order the GEMM streams,
   // [row tile of 128][k / (4 blocks)][(r % 32) * 16 + (r / 32) * 4 + block % 4]; the grid then
@@ -88,7 +91,7 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
            (rr >> 5) * 4 + (ksf & 3);
   };
   if (row >= M) {
-    for (int ksf = threadIdx.x; ksf < nsf; ksf += THREADS) sf[sf_offset(ksf)] = 0;
+    for (int ksf = threadIdx.x; ksf < nsf; ksf += nthreads) sf[sf_offset(ksf)] = 0;
     return;
   }
   const XT* xr = x + static_cast<int64_t>(row) * ldx;
@@ -97,7 +100,7 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
   float rmax = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int idx = (i * THREADS + threadIdx.x) * 8;
+    const int idx = (i * nthreads + threadIdx.x) * 8;
     bmax[i] = 0.f;
     if (idx < K) {
       fp4_load8(xr + idx, v[i]);
@@ -128,7 +131,7 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
       if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = rmax;
       __syncthreads();
       float m = red[0];
-      for (int i = 1; i < THREADS / 32; ++i) m = fmaxf(m, red[i]);
+      for (int i = 1; i < nthreads / 32; ++i) m = fmaxf(m, red[i]);
       ts = (m == 0.f) ? 1.f : __fdiv_rn(m, 2688.0f);
     }
     if (threadIdx.x == 0 && row_scale != nullptr) row_scale[row] = ts;
@@ -136,7 +139,7 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
   const int blk = (fmt == DQ_FP4_MXFP4) ? 32 : 16;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int idx = (i * THREADS + threadIdx.x) * 8;
+    const int idx = (i * nthreads + threadIdx.x) * 8;
     if (idx >= K) continue;
     float q[8];
     float deq_scale;
@@ -249,14 +252,18 @@ static int launch_fp4(const XT* x, int64_t ldx, const float* a, int M, int K, in
              "scale factors in GEMM order need K %% %d == 0 (K=%d)", 4 * blk, K);
   const int vec = K / 8;
   const int rows = sf_atoms ? (M + 127) / 128 * 128 : M;
+  // T bounds the CTA, V = vectors of 8 per thread; the CTA launched is the smallest multiple of
+  // 32 threads that covers the row with V vectors each.
 #define DQ_FP4_LAUNCH(T, V)                                                                        \
-  quant_fp4_kernel<T, V, XT><<<rows, T, 0, stream>>>(x, ldx, a, K, fmt, tensor_scale, codes, sf, row_scale, \
-                                                     out, mode, M, sf_atoms)
+  quant_fp4_kernel<T, V, XT><<<rows, ((vec + (V) - 1) / (V) + 31) / 32 * 32, 0, stream>>>(        \
+      x, ldx, a, K, fmt, tensor_scale, codes, sf, row_scale, out, mode, M, sf_atoms)
   if (vec <= 128) DQ_FP4_LAUNCH(128, 1);
   else if (vec <= 256) DQ_FP4_LAUNCH(256, 1);
   else if (vec <= 512) DQ_FP4_LAUNCH(512, 1);
-  else if (vec <= 1024) DQ_FP4_LAUNCH(1024, 1);
-  else if (vec <= 2048) DQ_FP4_LAUNCH(1024, 2);
+  else if (vec <= 1024) DQ_FP4_LAUNCH(512, 2);
+  else if (vec <= 1536) DQ_FP4_LAUNCH(512, 3);
+  else if (vec <= 2048) DQ_FP4_LAUNCH(512, 4);
+  else if (vec <= 3072) DQ_FP4_LAUNCH(1024, 3);
   else DQ_FP4_LAUNCH(1024, 4);
 #undef DQ_FP4_LAUNCH
   DQ_CHECK_CUDA(cudaGetLastError());

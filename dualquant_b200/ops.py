@@ -392,8 +392,8 @@ def pack_w_fp4(w: torch.Tensor, fmt: int) -> PackedFp4Weight:
 
 def gemm_w4a4_fp4(x_codes: torch.Tensor, x_sf_atoms: torch.Tensor, x_scale: Optional[torch.Tensor],
                   pw: PackedFp4Weight, r: Optional[torch.Tensor] = None, out_dtype=torch.float32,
-                  out: Optional[torch.Tensor] = None, token_blocks: int = 0) -> torch.Tensor:
-    """token_blocks: 0 = library's choice, 1 = 128-token tiles, 2 = 256-token tiles (no split-K)."""
+                  out: Optional[torch.Tensor] = None, token_tile: int = 0) -> torch.Tensor:
+    """token_tile: 0 = library's choice, 32 / 128 / 256 tokens per CTA (256 has no split-K)."""
     lib = _prep(x_codes)
     M = x_codes.shape[0]
     if out is None:
@@ -401,7 +401,7 @@ def gemm_w4a4_fp4(x_codes: torch.Tensor, x_sf_atoms: torch.Tensor, x_scale: Opti
     ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
     _lib.check(lib.dq_gemm_w4a4_fp4_tiled(_ptr(x_codes), _ptr(x_sf_atoms), _ptr(x_scale), _ptr(pw.codes),
                                           _ptr(pw.sf_atoms), _ptr(pw.tensor_scale), _ptr(r), M, pw.N,
-                                          pw.K, pw.fmt, _ptr(out), ydt, token_blocks,
+                                          pw.K, pw.fmt, _ptr(out), ydt, token_tile,
                                           _stream(x_codes.device)), "dq_gemm_w4a4_fp4_tiled")
     return out
 

@@ -221,17 +221,19 @@ DQ_API int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atoms, c
 
 /*
  * dq_gemm_w4a4_fp4 with the token tile chosen by the caller (same reference citation; the
- * reference has no tile notion).  token_blocks = 1: 128 weight rows x 128 tokens per CTA, two
- * CTAs per SM, split-K over a cluster for decode batches.  token_blocks = 2: 128 x 256, one CTA
- * per SM, the weight tile of a stage fetched once for two token blocks (no split-K: fails with
- * DQ_ERR_UNSUPPORTED where the 128-token path would split).  0 = the library's own choice, which
- * is what dq_gemm_w4a4_fp4 passes.  Results are identical for every choice.
+ * reference has no tile notion).  token_tile = 32: 128 weight rows x 32 tokens per CTA (decode
+ * batches: smaller stages, more weight bytes in flight).  128: 128 x 128, two CTAs per SM.  Both
+ * split K over a cluster when the tiles alone leave SMs idle.  256: 128 x 256, one CTA per SM, the
+ * weight tile of a stage fetched once for two token blocks (no split-K: fails with
+ * DQ_ERR_UNSUPPORTED where the other tiles would split).  0 = the library's own choice, which is
+ * what dq_gemm_w4a4_fp4 passes.  Results are identical for every choice that does not change
+ * the split of K.
  */
 DQ_API int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_sf_atoms,
                                   const float* x_scale, const uint8_t* w_codes,
                                   const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
                                   int M, int N, int K, int fmt, void* y, int y_dtype,
-                                  int token_blocks, void* stream);
+                                  int token_tile, void* stream);
 
 /* ---- int4 dual-scale GEMM ------------------------------------------------------------------ */
 
