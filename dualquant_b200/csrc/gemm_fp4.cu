@@ -25,7 +25,7 @@ namespace dq {
 constexpr int kFBN = 128;      // weight rows per CTA
 constexpr int kFTN = 128;      // tokens per CTA
 constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
-constexpr int kFp4DecodeTokens = 0;  // library's choice of the 32-token tile: M up to this
+constexpr int kFp4DecodeTokens = 32;  // library's choice of the 32-token tile: M up to this
 constexpr int kFTileBytes = 128 * 128;  // one operand tile of 128 rows
 constexpr int kFThreads = 256;  // producer, UMMA issuer, 4 epilogue warps, 2 scale-factor copiers
 
@@ -202,9 +202,9 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         // token rows: 4 columns per block of 128 rows, blocks side by side (rows 128..255 follow
         // rows 0..127), 4 * NT columns per atom.
         {
-          // a 32-token tile is one quarter of a 128-row scale-factor block: rows 32 q .. 32 q + 31 of
-          // the block sit in column q of each atom
-          const uint32_t sfb_t = sfa_t + 16 + ((NT == 0) ? static_cast<uint32_t>((t0 % kFTN) / 32) : 0u);
+          // (the 32-token tile is only launched for M <= 32: its rows are rows 0..31 of the first
+          // scale-factor block, the first column of each atom)
+          const uint32_t sfb_t = sfa_t + 16;
           const uint64_t db = umma_desc_k_sw128(smem_u32(smem + C::kOffB + s * C::kBTileBytes));
 #pragma unroll
           for (int j = 0; j < 4; ++j) {  // four K=64 UMMAs: +32 bytes along K each
@@ -480,9 +480,11 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   // split K across a cluster when the output tiles alone leave most SMs idle (decode batches)
   int split = 1;
   {
-    const int tiles1 = ((N + kFBN - 1) / kFBN) * ((M + tile_tok - 1) / tile_tok);
+    const int split_tok = (tile_tok == 32) ? 32 : kFTN;  // the 256-token tile never splits: judged as 128
+    const int tiles1 = ((N + kFBN - 1) / kFBN) * ((M + split_tok - 1) / split_tok);
     while (split < 8 && tiles1 * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
   }
+  DQ_REQUIRE(nt != 0 || M <= 32, DQ_ERR_UNSUPPORTED, "the 32-token tile covers batches of up to 32 tokens, got M=%d", M);
   DQ_REQUIRE(nt != 2 || split == 1, DQ_ERR_UNSUPPORTED,
              "256-token tiles have no split-K path (M=%d N=%d K=%d would split %d ways)", M, N, K, split);
   CUtensorMap tm_w, tm_x;

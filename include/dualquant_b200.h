@@ -222,7 +222,7 @@ DQ_API int dq_gemm_w4a4_fp4(const uint8_t* x_codes, const uint8_t* x_sf_atoms, c
 /*
  * dq_gemm_w4a4_fp4 with the token tile chosen by the caller (same reference citation; the
  * reference has no tile notion).  token_tile = 32: 128 weight rows x 32 tokens per CTA (decode
- * batches: smaller stages, more weight bytes in flight).  128: 128 x 128, two CTAs per SM.  Both
+ * batches, M <= 32 only: smaller stages, more weight bytes in flight).  128: 128 x 128, two CTAs per SM.  Both
  * split K over a cluster when the tiles alone leave SMs idle.  256: 128 x 256, one CTA per SM, the
  * weight tile of a stage fetched once for two token blocks (no split-K: fails with
  * DQ_ERR_UNSUPPORTED where the other tiles would split).  0 = the library's own choice, which is
