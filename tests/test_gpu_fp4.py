@@ -38,6 +38,26 @@ def test_mxfp4_bit_exact(M, K, use_a):
     _lib.device_status(0)
 
 
+@pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
+@pytest.mark.parametrize("M,K", [(520, 3584), (512, 18944), (600, 2048), (513, 8192)])
+def test_fp4_quant_many_rows_bit_exact(fmt, M, K):
+    """The launch shape for many rows (small CTAs, four vectors per thread) against the oracle."""
+    x = _x(M, K, 11)
+    _, c = synthetic.make_scales(8, K, 11)
+    a = 1.0 / c
+    x32 = x.float() * a
+    codes, sf, rs = ops.quant_fp4(x.to(DEV), fmt, a.to(DEV))
+    if fmt == _lib.FP4_MXFP4:
+        q, e8, _ = O.quant_mxfp4(x32)
+        assert torch.equal(sf.cpu(), e8)
+    else:
+        q, bs, ts, _ = O.quant_nvfp4(x32, None)
+        assert torch.equal(sf.cpu(), O.e4m3_byte(bs))
+        assert torch.equal(rs.cpu(), ts)
+    assert torch.equal(codes.cpu(), O.pack_fp4(q))
+    _lib.device_status(0)
+
+
 @pytest.mark.parametrize("M,K", [(1, 16), (3, 128), (5, 3584), (2, 18944), (4, 4096)])
 @pytest.mark.parametrize("per_tensor", [False, True])
 def test_nvfp4_bit_exact(M, K, per_tensor):
