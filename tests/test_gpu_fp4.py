@@ -41,7 +41,7 @@ def test_mxfp4_bit_exact(M, K, use_a):
 @pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
 @pytest.mark.parametrize("M,K", [(520, 3584), (512, 18944), (600, 2048), (513, 8192)])
 def test_fp4_quant_many_rows_bit_exact(fmt, M, K):
-    """The launch shape for many rows (small CTAs, four vectors per thread) against the oracle."""
+    """Hundreds of rows, every launch shape of the quantiser (1-4 vectors per thread) against the oracle."""
     x = _x(M, K, 11)
     _, c = synthetic.make_scales(8, K, 11)
     a = 1.0 / c
@@ -179,6 +179,29 @@ def test_fp4_gemm_token_tiles_agree(fmt, M, N, K):
     ref = _fp4_reference(x, a.cpu(), w, r, fmt)
     err = ((y2.double().cpu() - ref).abs().max() / ref.abs().max()).item()
     assert err < 1e-3, err
+
+
+@pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
+@pytest.mark.parametrize("M,N,K,dtype", [(130, 130, 768, torch.float32), (257, 204, 512, torch.bfloat16),
+                                         (40, 136, 768, torch.bfloat16), (129, 200, 512, torch.bfloat16)])
+def test_fp4_gemm_output_pitches_and_dtypes(fmt, M, N, K, dtype):
+    """Outputs whose row pitch is not a multiple of 16 bytes take the direct-store epilogue, the
+    others the bulk-store one; fp32 and bf16, ragged M and N."""
+    x = synthetic.make_x(M, K, M + 21)
+    w = synthetic.make_w(N, K, N + 22)
+    r, c = synthetic.make_scales(N, K, 23)
+    a = (1.0 / c).to(DEV)
+    pw = ops.pack_w_fp4(w.to(DEV), fmt)
+    codes, sf, rs = ops.quant_fp4(x.to(DEV), fmt, a, None)
+    sfa = ops.fp4_sf_to_atoms(sf, K, fmt)
+    y = torch.full((M + 1, N), 7.0, dtype=dtype, device=DEV)  # one guard row behind the output
+    ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r.to(DEV), out=y[:M])
+    _lib.device_status(0)
+    assert torch.all(y[M] == 7.0)
+    ref = _fp4_reference(x, a.cpu(), w, r, fmt)
+    tol = 1e-3 if dtype == torch.float32 else 8e-3  # bf16 output rounding: 2^-8 relative
+    err = ((y[:M].double().cpu() - ref).abs().max() / ref.abs().max()).item()
+    assert err < tol, err
 
 
 def test_fp4_wide_tile_rejects_split_k_shapes():
