@@ -431,6 +431,30 @@ def run_case(args):
         print(json.dumps({"case": args.case, "us_per_launch": round(ms * 1e3, 2), "algorithmic_bytes": b,
                           "GBps": round(b / ms / 1e6, 1)}), flush=True)
         return
+    if parts[0] == "quant_fp4":  # quant_fp4:FMT:M:K - the FP4 activation quantiser alone
+        fmt = {"mxfp4": _lib.FP4_MXFP4, "nvfp4": _lib.FP4_NVFP4}[parts[1]]
+        M, K = int(parts[2]), int(parts[3])
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        n_bufs = max(2, int(400e6 // (M * K * 2)) + 1)
+        xs = [torch.randn(M, K, device=dev).to(torch.bfloat16) for _ in range(n_bufs)]
+        a = torch.rand(K, device=dev) + 0.5
+        for i in range(3):
+            ops.quant_fp4(xs[i % n_bufs], fmt, a, None, atoms=True)
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.iters):
+            ops.quant_fp4(xs[i % n_bufs], fmt, a, None, atoms=True)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.iters
+        blk = 32 if fmt == _lib.FP4_MXFP4 else 16
+        b = M * K * 2 + M * K // 2 + M * K // blk + 4 * K
+        print(json.dumps({"case": args.case, "us_per_launch": round(ms * 1e3, 2), "algorithmic_bytes": b,
+                          "GBps": round(b / ms / 1e6, 1)}), flush=True)
+        return
     if parts[0] == "fp4":  # fp4:FMT:LINEAR:M - one block-scaled FP4 GEMM of the Qwen2.5-7B shapes alone
         fmt = {"mxfp4": _lib.FP4_MXFP4, "nvfp4": _lib.FP4_NVFP4}[parts[1]]
         K, N = {n: (k, nn) for n, k, nn in synthetic.QWEN25_7B_LINEARS}[parts[2]]
