@@ -18,6 +18,9 @@
 namespace dq {
 
 enum { FP4_MODE_CODES = 0, FP4_MODE_FAKE = 1 };
+// the streaming kernel (several small CTAs per SM) takes over from the row-in-registers kernel
+constexpr int kFp4StreamMinRows = 512;  // rows: enough CTAs to fill the SMs several times
+constexpr int kFp4StreamMinVec = 1024;  // vectors of 8 per row (K >= 8192): shorter rows are faster in registers
 
 __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
   uint16_t out;
@@ -66,6 +69,89 @@ __device__ __forceinline__ void fp4_load8(const float* p, float* v) {
   const float4 b = *reinterpret_cast<const float4*>(p + 4);
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// One vector of 8 consecutive elements (already scaled by the column scale) whose block absmax is
+// known: block scale, element codes, stores.  sf_off = where this vector's block scale byte goes
+// (used by the first vector of a block only).
+__device__ __forceinline__ void fp4_emit_vector(const float* v, float bmax, float ts, int fmt, int mode,
+                                                int row, int K, int idx, int blk, int64_t sf_off,
+                                                uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
+                                                float* __restrict__ out) {
+    float q[8];
+    float deq_scale;
+    uint32_t sf_byte;
+    if (fmt == DQ_FP4_MXFP4) {
+      int e = -127;
+      if (bmax != 0.f) {
+        e = static_cast<int>((__float_as_uint(bmax) >> 23) & 0xFFu) - 127 - 2;
+        e = max(-127, min(127, e));
+      }
+      sf_byte = static_cast<uint32_t>(e + 127);
+      // 2^-e is representable (as a subnormal at the far end), so one multiplication rounds
+      // exactly like scalbnf(v, -e) would
+      const float down = scalbnf(1.0f, -e);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q[k] = __fmul_rn(v[k], down);
+      deq_scale = scalbnf(1.0f, e);
+    } else {
+      const float want = __fdiv_rn(__fdiv_rn(bmax, 6.0f), ts);
+      sf_byte = e4m3_byte_of(fminf(want, 448.0f));
+      const float bs = e4m3_value(sf_byte);
+      const float denom = __fmul_rn(ts, bs);
+      deq_scale = denom;
+      if (mode == FP4_MODE_FAKE) deq_scale = bs;  // applied as (q * bs) * ts below
+      if (denom == 0.f) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) q[k] = 0.f;
+      } else {
+        // v / denom rounded to E2M1 without eight IEEE divisions: t = v * (1 / denom) is within
+        // 2^-22 |t| of the quotient; if t (1 - 2^-21) and t (1 + 2^-21) convert to the same codes,
+        // so does everything between them, the correctly rounded quotient included.  Otherwise
+        // (an element sits on a rounding boundary, or t is not finite) the thread takes the exact
+        // divisions, in a branch of its own.
+        const float inv = __fdiv_rn(1.0f, denom);
+        float lo[8], hi[8];
+        bool exact = false;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float t = __fmul_rn(v[k], inv);
+          exact |= !(fabsf(t) <= 1e30f);
+          lo[k] = __fmul_rn(t, 0.99999952316284179688f);  // 1 - 2^-21
+          hi[k] = __fmul_rn(t, 1.00000047683715820312f);  // 1 + 2^-21
+        }
+        uint32_t plo = 0, phi = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          plo |= e2m1x2(lo[2 * k], lo[2 * k + 1]) << (8 * k);
+          phi |= e2m1x2(hi[2 * k], hi[2 * k + 1]) << (8 * k);
+        }
+        if (exact || plo != phi) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) q[k] = __fdiv_rn(v[k], denom);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) q[k] = lo[k];
+        }
+      }
+    }
+    uint32_t packed = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) packed |= e2m1x2(q[2 * k], q[2 * k + 1]) << (8 * k);
+    if (mode == FP4_MODE_CODES) {
+      *reinterpret_cast<uint32_t*>(codes + static_cast<int64_t>(row) * (K / 2) + idx / 2) = packed;
+      if ((idx % blk) == 0) sf[sf_off] = static_cast<uint8_t>(sf_byte);
+    } else {
+      float o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float qv = e2m1_value((packed >> (4 * k)) & 0xFu);
+        o[k] = (fmt == DQ_FP4_MXFP4) ? __fmul_rn(qv, deq_scale) : __fmul_rn(__fmul_rn(qv, deq_scale), ts);
+      }
+      float* orow = out + static_cast<int64_t>(row) * K + idx;
+      *reinterpret_cast<float4*>(orow) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4*>(orow + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
 }
 
 template <int THREADS, int VPT, typename XT>
@@ -141,80 +227,92 @@ quant_fp4_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict_
   for (int i = 0; i < VPT; ++i) {
     const int idx = (i * nthreads + threadIdx.x) * 8;
     if (idx >= K) continue;
-    float q[8];
-    float deq_scale;
-    uint32_t sf_byte;
-    if (fmt == DQ_FP4_MXFP4) {
-      int e = -127;
-      if (bmax[i] != 0.f) {
-        e = static_cast<int>((__float_as_uint(bmax[i]) >> 23) & 0xFFu) - 127 - 2;
-        e = max(-127, min(127, e));
-      }
-      sf_byte = static_cast<uint32_t>(e + 127);
-      // 2^-e is representable (as a subnormal at the far end), so one multiplication rounds
-      // exactly like scalbnf(v, -e) would
-      const float down = scalbnf(1.0f, -e);
+    fp4_emit_vector(v[i], bmax[i], ts, fmt, mode, row, K, idx, blk, sf_offset(idx / blk), codes, sf, out);
+  }
+}
+
+// The same quantiser for many long rows: a CTA of 256 threads walks its row in steps of 256
+// vectors instead of holding it in registers, so that several CTAs share an SM and one row's loads
+// overlap another row's arithmetic (the register version runs one 800-thread CTA per SM at
+// K = 18944).  NVFP4 without a given tensor scale needs the row's absmax first: a first pass over
+// the row, which the second pass then finds in L2.  Same per-vector arithmetic (fp4_emit_vector),
+// same results.
+template <typename XT>
+__global__ void __launch_bounds__(256, 6)  // 39 registers: six CTAs per SM (four measured 12 % slower)
+quant_fp4_stream_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K, int fmt,
+                        const float* __restrict__ tensor_scale, uint8_t* __restrict__ codes,
+                        uint8_t* __restrict__ sf, float* __restrict__ row_scale, float* __restrict__ out,
+                        int mode, int M, int sf_atoms) {
+  constexpr int T = 256;
+  __shared__ float red[T / 32];
+  const int row = blockIdx.x;
+  const int blk = (fmt == DQ_FP4_MXFP4) ? 32 : 16;
+  const int nsf = K / blk;
+  auto sf_offset = [&](int ksf) -> int64_t {
+    if (!sf_atoms) return static_cast<int64_t>(row) * nsf + ksf;
+    const int rr = row & 127;
+    return (static_cast<int64_t>(row >> 7) * (nsf >> 2) + (ksf >> 2)) * 512 + (rr & 31) * 16 +
+           (rr >> 5) * 4 + (ksf & 3);
+  };
+  if (row >= M) {
+    for (int ksf = threadIdx.x; ksf < nsf; ksf += T) sf[sf_offset(ksf)] = 0;
+    return;
+  }
+  const XT* xr = x + static_cast<int64_t>(row) * ldx;
+  const int nvec = K / 8;
+  const int iters = (nvec + T - 1) / T;
+  auto load_scaled = [&](int idx, float* v) {
+    fp4_load8(xr + idx, v);
+    if (a != nullptr) {
+      float av[8];
+      fp4_load8(a + idx, av);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) q[k] = __fmul_rn(v[i][k], down);
-      deq_scale = scalbnf(1.0f, e);
-    } else {
-      const float want = __fdiv_rn(__fdiv_rn(bmax[i], 6.0f), ts);
-      sf_byte = e4m3_byte_of(fminf(want, 448.0f));
-      const float bs = e4m3_value(sf_byte);
-      const float denom = __fmul_rn(ts, bs);
-      deq_scale = denom;
-      if (mode == FP4_MODE_FAKE) deq_scale = bs;  // applied as (q * bs) * ts below
-      if (denom == 0.f) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) q[k] = 0.f;
-      } else {
-        // v / denom rounded to E2M1 without eight IEEE divisions: t = v * (1 / denom) is within
-        // 2^-22 |t| of the quotient; if t (1 - 2^-21) and t (1 + 2^-21) convert to the same codes,
-        // so does everything between them, the correctly rounded quotient included.  Otherwise
-        // (an element sits on a rounding boundary, or t is not finite) the thread takes the exact
-        // divisions, in a branch of its own.
-        const float inv = __fdiv_rn(1.0f, denom);
-        float lo[8], hi[8];
-        bool exact = false;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float t = __fmul_rn(v[i][k], inv);
-          exact |= !(fabsf(t) <= 1e30f);
-          lo[k] = __fmul_rn(t, 0.99999952316284179688f);  // 1 - 2^-21
-          hi[k] = __fmul_rn(t, 1.00000047683715820312f);  // 1 + 2^-21
-        }
-        uint32_t plo = 0, phi = 0;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          plo |= e2m1x2(lo[2 * k], lo[2 * k + 1]) << (8 * k);
-          phi |= e2m1x2(hi[2 * k], hi[2 * k + 1]) << (8 * k);
-        }
-        if (exact || plo != phi) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) q[k] = __fdiv_rn(v[i][k], denom);
-        } else {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) q[k] = lo[k];
-        }
-      }
+      for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
     }
-    uint32_t packed = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) packed |= e2m1x2(q[2 * k], q[2 * k + 1]) << (8 * k);
-    if (mode == FP4_MODE_CODES) {
-      *reinterpret_cast<uint32_t*>(codes + static_cast<int64_t>(row) * (K / 2) + idx / 2) = packed;
-      if ((idx % blk) == 0) sf[sf_offset(idx / blk)] = static_cast<uint8_t>(sf_byte);
+  };
+  float ts = 1.f;
+  if (fmt == DQ_FP4_NVFP4) {
+    if (tensor_scale != nullptr) {
+      ts = *tensor_scale;
     } else {
-      float o[8];
+      float rmax = 0.f;
+      for (int it = 0; it < iters; ++it) {
+        const int idx = (it * T + threadIdx.x) * 8;
+        if (idx < K) {
+          float v[8];
+          load_scaled(idx, v);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float qv = e2m1_value((packed >> (4 * k)) & 0xFu);
-        o[k] = (fmt == DQ_FP4_MXFP4) ? __fmul_rn(qv, deq_scale) : __fmul_rn(__fmul_rn(qv, deq_scale), ts);
+          for (int e = 0; e < 8; ++e) rmax = fmaxf(rmax, fabsf(v[e]));
+        }
       }
-      float* orow = out + static_cast<int64_t>(row) * K + idx;
-      *reinterpret_cast<float4*>(orow) = make_float4(o[0], o[1], o[2], o[3]);
-      *reinterpret_cast<float4*>(orow + 4) = make_float4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = rmax;
+      __syncthreads();
+      float m = red[0];
+#pragma unroll
+      for (int i = 1; i < T / 32; ++i) m = fmaxf(m, red[i]);
+      ts = (m == 0.f) ? 1.f : __fdiv_rn(m, 2688.0f);
     }
+    if (threadIdx.x == 0 && row_scale != nullptr) row_scale[row] = ts;
+  }
+  for (int it = 0; it < iters; ++it) {  // every lane runs every iteration: the shuffles need the warp
+    const int idx = (it * T + threadIdx.x) * 8;
+    float v[8];
+    float bmax = 0.f;
+    if (idx < K) {
+      load_scaled(idx, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) bmax = fmaxf(bmax, fabsf(v[e]));
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    }
+    // block absmax: 16 elements = 2 adjacent lanes, 32 elements = 4 adjacent lanes
+    bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+    if (fmt == DQ_FP4_MXFP4) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+    if (idx < K)
+      fp4_emit_vector(v, bmax, ts, fmt, mode, row, K, idx, blk, sf_offset(idx / blk), codes, sf, out);
   }
 }
 
@@ -259,7 +357,10 @@ static int launch_fp4(const XT* x, int64_t ldx, const float* a, int M, int K, in
       x, ldx, a, K, fmt, tensor_scale, codes, sf, row_scale, out, mode, M, sf_atoms)
   // (four vectors per thread in smaller CTAs for many rows measured no faster: 126 vs 107 us at
   // M = 4096, K = 18944)
-  if (vec <= 128) DQ_FP4_LAUNCH(128, 1);
+  if (M >= kFp4StreamMinRows && vec >= kFp4StreamMinVec) {
+    quant_fp4_stream_kernel<XT><<<rows, 256, 0, stream>>>(x, ldx, a, K, fmt, tensor_scale, codes, sf,
+                                                          row_scale, out, mode, M, sf_atoms);
+  } else if (vec <= 128) DQ_FP4_LAUNCH(128, 1);
   else if (vec <= 256) DQ_FP4_LAUNCH(256, 1);
   else if (vec <= 512) DQ_FP4_LAUNCH(512, 1);
   else if (vec <= 1024) DQ_FP4_LAUNCH(512, 2);

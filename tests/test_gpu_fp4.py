@@ -48,13 +48,19 @@ def test_fp4_quant_many_rows_bit_exact(fmt, M, K):
     x32 = x.float() * a
     codes, sf, rs = ops.quant_fp4(x.to(DEV), fmt, a.to(DEV))
     if fmt == _lib.FP4_MXFP4:
-        q, e8, _ = O.quant_mxfp4(x32)
+        q, e8, deq = O.quant_mxfp4(x32)
         assert torch.equal(sf.cpu(), e8)
     else:
-        q, bs, ts, _ = O.quant_nvfp4(x32, None)
+        q, bs, ts, deq = O.quant_nvfp4(x32, None)
         assert torch.equal(sf.cpu(), O.e4m3_byte(bs))
         assert torch.equal(rs.cpu(), ts)
     assert torch.equal(codes.cpu(), O.pack_fp4(q))
+    fq = ops.fakequant_fp4(x.to(DEV), fmt, a.to(DEV))
+    assert torch.equal(fq.cpu(), deq)
+    # scale bytes written straight in the order the GEMM streams = the re-ordered row-major bytes
+    codes2, sfa, rs2 = ops.quant_fp4(x.to(DEV), fmt, a.to(DEV), None, atoms=True)
+    assert torch.equal(codes2, codes)
+    assert torch.equal(sfa.reshape(-1), ops.fp4_sf_to_atoms(sf, K, fmt).reshape(-1))
     _lib.device_status(0)
 
 
