@@ -189,7 +189,8 @@ def test_fp4_gemm_token_tiles_agree(fmt, M, N, K):
 
 @pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
 @pytest.mark.parametrize("M,N,K,dtype", [(130, 130, 768, torch.float32), (257, 204, 512, torch.bfloat16),
-                                         (40, 136, 768, torch.bfloat16), (129, 200, 512, torch.bfloat16)])
+                                         (40, 136, 768, torch.bfloat16), (129, 200, 512, torch.bfloat16),
+                                         (40, 64, 512, torch.float32), (3, 8, 256, torch.bfloat16)])
 def test_fp4_gemm_output_pitches_and_dtypes(fmt, M, N, K, dtype):
     """Outputs whose row pitch is not a multiple of 16 bytes take the direct-store epilogue, the
     others the bulk-store one; fp32 and bf16, ragged M and N."""
