@@ -590,7 +590,7 @@ def run_prefill_suite(args):
 
 
 def run_mlp_suite(args):
-    """BASELINE config 2: prefill MLP, M = 8192 tokens, int4 dual-scale.  gate+up 4096 -> 28672
+    """Benchmark configuration 2: prefill MLP, M = 8192 tokens, int4 dual-scale.  gate+up 4096 -> 28672
     (bf16 out), SiLU(gate) * up in bf16, QuaRot R4 online Hadamard of size 14336 (28 x 512) fused
     with the activation quantiser, down 14336 -> 4096.  Stage times from CUDA-graph replays."""
     from dualquant_b200 import _lib, ops, quarot
@@ -655,7 +655,7 @@ def run_mlp_suite(args):
 
 
 def run_decoder_suite(args):
-    """BASELINE config 4: random-init Llama-3.1-8B-architecture decoder, every linear W4A4 int4
+    """Benchmark configuration 4: random-init Llama-3.1-8B-architecture decoder, every linear W4A4 int4
     dual-scale with online Hadamards, bf16 attention; prefill batch x seqlen, then decode steps.
     Tensor-parallel over the ranks of the launch (torch.distributed.run) with an NCCL all-reduce
     after o_proj and down_proj.  Prints one JSON line on rank 0."""
@@ -759,7 +759,7 @@ def run_decoder_suite(args):
 
 
 def run_fp4_suite(args):
-    """Block-scaled FP4 linears on the Qwen2.5-7B-architecture shapes (BASELINE config 3):
+    """Block-scaled FP4 linears on the Qwen2.5-7B-architecture shapes (benchmark configuration 3):
     MXFP4 and NVFP4, M = 16 (GB/s of algorithmic bytes) and M = 4096 (TFLOPS = 2*M*N*K/s)."""
     from dualquant_b200 import _lib, ops
 
