@@ -20,7 +20,8 @@ namespace dq {
 enum { FP4_MODE_CODES = 0, FP4_MODE_FAKE = 1 };
 // the streaming kernel (several small CTAs per SM) takes over from the row-in-registers kernel
 constexpr int kFp4StreamMinRows = 512;  // rows: enough CTAs to fill the SMs several times
-constexpr int kFp4StreamMinVec = 1024;  // vectors of 8 per row (K >= 8192): shorter rows are faster in registers
+constexpr int kFp4StreamMinVec = 1024;  // MXFP4: vectors of 8 per row (K >= 8192); shorter rows are as fast in registers
+constexpr int kFp4StreamMinVecNv = 256;  // NVFP4 (two phases per row): from K = 2048 (6-10 % at K = 3584-4096)
 
 __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
   uint16_t out;
@@ -357,7 +358,7 @@ static int launch_fp4(const XT* x, int64_t ldx, const float* a, int M, int K, in
       x, ldx, a, K, fmt, tensor_scale, codes, sf, row_scale, out, mode, M, sf_atoms)
   // (four vectors per thread in smaller CTAs for many rows measured no faster: 126 vs 107 us at
   // M = 4096, K = 18944)
-  if (M >= kFp4StreamMinRows && vec >= kFp4StreamMinVec) {
+  if (M >= kFp4StreamMinRows && vec >= (fmt == DQ_FP4_NVFP4 ? kFp4StreamMinVecNv : kFp4StreamMinVec)) {
     quant_fp4_stream_kernel<XT><<<rows, 256, 0, stream>>>(x, ldx, a, K, fmt, tensor_scale, codes, sf,
                                                           row_scale, out, mode, M, sf_atoms);
   } else if (vec <= 128) DQ_FP4_LAUNCH(128, 1);
