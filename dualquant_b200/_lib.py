@@ -55,11 +55,13 @@ SIGNATURES = {
     "dq_last_error_string": (_c.c_char_p, []),
     "dq_device_status": (_i, [_i]),
     "dq_abi_version": (_i, []),
+    "dq_set_tuning": (_i, [_c.c_char_p, _i]),
     "dq_packed_w_bytes": (_sz, [_i, _i]),
     "dq_pack_w_int4": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "dq_unpack_w_int4": (_i, [_vp, _i, _i, _vp, _vp]),
     "dq_quant_w_int4": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "dq_quant_act_int4": (_i, [_vp, _i64, _vp, _hp, _i, _i, _vp, _vp, _i, _vp]),
+    "dq_quant_act_int4_f32": (_i, [_vp, _i64, _vp, _hp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_quant_act_int4_rmsnorm": (_i, [_vp, _i64, _vp, ctypes.c_float, _vp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_quant_act_int4_gated": (_i, [_vp, _vp, _i64, _vp, _hp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_fakequant_act_int4": (_i, [_vp, _i, _i64, _vp, _hp, _i, _i, _vp, _i, _vp]),
@@ -131,6 +133,11 @@ def ensure_init(device_index: int) -> None:
     lib = load()
     check(lib.dq_init(int(device_index)), f"dq_init({device_index})")
     _inited.add(device_index)
+
+
+def set_tuning(name: str, value: int) -> None:
+    """Launch-shape override (see dq_set_tuning in the header); for sweeps and tests."""
+    check(load().dq_set_tuning(name.encode(), int(value)), f"dq_set_tuning({name})")
 
 
 def device_status(device_index: int) -> None:

@@ -45,6 +45,10 @@ class PermLinear(nn.Module):
         self._packed_fp4: Optional[ops.PackedFp4Weight] = None
         self._hadamard_cache = None
         self._scratch: Optional[torch.Tensor] = None
+        # None = not examined yet; False = the weight is not on the W4 grid of the activation
+        # format, the layer keeps the reference's fake-quant formulation
+        self._weight_on_grid: Optional[bool] = None
+        self._weight_on_grid_fp4: Optional[bool] = None
 
     # ------------------------------------------------------------------ reference surface
     def set_act_scale(self, act_scale):
@@ -56,17 +60,53 @@ class PermLinear(nn.Module):
         self.act_quant_enabled = bool(enabled)
 
     # ------------------------------------------------------------------ weight packing
-    def pack(self, codes: Optional[torch.Tensor] = None, sw: Optional[torch.Tensor] = None) -> None:
+    def pack(self, codes: Optional[torch.Tensor] = None, sw: Optional[torch.Tensor] = None,
+             force: bool = False) -> bool:
         """Builds the int4 artefact.  Without arguments the wrapped layer's (fake-quant) weight is
         re-quantised per group of 128 along K, which is how the reference's real-kernel scripts
         recover codes and scales from `mat_q` (validate_real_kernel.py:95-98 via
-        pack_int4_weights).  `codes` (int8 [N,K]) and `sw` (fp16 [N,K/128]) may be given directly."""
+        pack_int4_weights).  `codes` (int8 [N,K]) and `sw` (fp16 [N,K/128]) may be given directly.
+
+        The reference's PermLinear never touches the weight (activations/perm_linear.py:136-141), so
+        the real int4 GEMM may stand in for `F.linear(x_q, W)` only when W already lies on the int4
+        group-of-128 grid.  After re-quantising, codes * scale must reproduce the stored weight to
+        within the rounding of its storage type (1/128 of the group maximum); otherwise the weight is
+        not W4-g128 (a 16-bit weight, per-row or GPTQ scales off this grid, another format) and the
+        layer keeps the reference's formulation - fake-quantised activations into the wrapped
+        layer's own F.linear.  `force=True` packs regardless (an explicit opt-in to quantising the
+        weight here).  Returns True when the int4 artefact is in use."""
         w = self.layer.weight
         if not w.is_cuda:
             raise RuntimeError("PermLinear.pack needs the layer on a CUDA device (no CPU path)")
         if codes is None:
-            codes, sw = ops.quant_w_int4(w.detach().to(torch.bfloat16))
+            w16 = w.detach().to(torch.bfloat16)
+            codes, sw = ops.quant_w_int4(w16)
+            if not force and not _reproduces(codes, sw, w.detach(), GROUP):
+                self._packed = None
+                self._weight_on_grid = False
+                return False
         self._packed = ops.pack_w_int4(codes.to(w.device), sw.to(w.device))
+        self._weight_on_grid = True
+        return True
+
+    def pack_fp4(self, fmt: int, force: bool = False) -> bool:
+        """FP4 counterpart of pack(): the weight is packed in the activation format only when it
+        already lies on that format's grid (its cast reproduces it), or with force=True."""
+        w = self.layer.weight.detach()
+        if not w.is_cuda:
+            raise RuntimeError("PermLinear.pack_fp4 needs the layer on a CUDA device (no CPU path)")
+        if not force:
+            cast = self.act_fmt.cast(w.float())
+            blk = 32 if fmt == _lib.FP4_MXFP4 else 16
+            wb = w.float().reshape(w.shape[0], -1, blk)
+            tol = wb.abs().amax(-1, keepdim=True) * (1.0 / 128.0)
+            if not bool(((cast.reshape(wb.shape) - wb).abs() <= tol).all()):
+                self._packed_fp4 = None
+                self._weight_on_grid_fp4 = False
+                return False
+        self._packed_fp4 = ops.pack_w_fp4(w, fmt)
+        self._weight_on_grid_fp4 = True
+        return True
 
     def _hadamard(self, device) -> Optional[ops.Hadamard]:
         if not (self.online_full_had or self.online_partial_had):
@@ -124,32 +164,39 @@ class PermLinear(nn.Module):
     def forward(self, x):
         if not x.is_cuda:
             raise RuntimeError("dualquant_b200.PermLinear runs on CUDA (sm_100a) tensors only")
-        if self._int4_path():
-            if self._packed is None:
-                self.pack()
+        use_int4 = self._int4_path()
+        if use_int4 and self._packed is None and self._weight_on_grid is None:
+            self.pack()
+        fmt4 = None if use_int4 else self._fp4_fmt()
+        if fmt4 is not None and (self._packed_fp4 is None or self._packed_fp4.fmt != fmt4) \
+                and self._weight_on_grid_fp4 is None:
+            self.pack_fp4(fmt4)
+        if use_int4 and self._packed is not None:
             pw = self._packed
             x2 = x.reshape(-1, x.shape[-1])
-            if x2.dtype != torch.bfloat16:
-                x2 = x2.to(torch.bfloat16)
             M = x2.shape[0]
             need = ops.linear_scratch_bytes(M, pw.N, pw.K)
             if self._scratch is None or self._scratch.numel() < need or self._scratch.device != x.device:
                 self._scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
             out_dtype = self.dtype if self.dtype in (torch.bfloat16, torch.float32) else torch.float32
-            out = ops.linear_w4a4_int4(x2, self.act_scale, self._hadamard(x.device), pw, None,
-                                       out_dtype=out_dtype, scale_fp16=False, scratch=self._scratch)
+            if x2.dtype == torch.bfloat16:
+                out = ops.linear_w4a4_int4(x2, self.act_scale, self._hadamard(x.device), pw, None,
+                                           out_dtype=out_dtype, scale_fp16=False, scratch=self._scratch)
+            else:
+                # the reference upcasts to fp32 before scaling and quantising (perm_linear.py:119-125):
+                # fp32 / fp16 inputs go through the fp32 quantiser, not through a bf16 rounding
+                codes, sx = ops.quant_act_int4(x2.float(), self.act_scale, self._hadamard(x.device),
+                                               scale_fp16=False)
+                out = ops.gemm_w4a4_int4(codes, sx, pw, None, out_dtype=out_dtype)
             out = out.to(self.dtype)
             if self.layer.bias is not None:
                 out = out + self.layer.bias
             out = out.reshape(x.shape[:-1] + (pw.N,))
-        elif self._fp4_fmt() is not None:
+        elif fmt4 is not None and self._packed_fp4 is not None and self._packed_fp4.fmt == fmt4:
             # block-scaled FP4 activations against the weight packed in the same format
-            fmt = self._fp4_fmt()
-            if self._packed_fp4 is None or self._packed_fp4.fmt != fmt:
-                self._packed_fp4 = ops.pack_w_fp4(self.layer.weight.detach(), fmt)
             x2 = x.reshape(-1, x.shape[-1])
             if x2.dtype not in (torch.bfloat16, torch.float32):
-                x2 = x2.to(torch.bfloat16)
+                x2 = x2.float()
             out_dtype = self.dtype if self.dtype in (torch.bfloat16, torch.float32) else torch.float32
             out = ops.linear_w4a4_fp4(x2, self.act_scale, self._packed_fp4, None, out_dtype).to(self.dtype)
             if self.layer.bias is not None:
@@ -160,6 +207,15 @@ class PermLinear(nn.Module):
         if self.quantize_bmm_input:
             out = self.act_fmt.cast(out.to(torch.float32)).to(self.dtype)
         return out
+
+
+def _reproduces(codes: torch.Tensor, sw: torch.Tensor, w: torch.Tensor, group: int) -> bool:
+    """True when codes * group scale gives back `w` up to the rounding of w's storage type."""
+    N, K = codes.shape
+    deq = codes.float().reshape(N, K // group, group) * sw.float().unsqueeze(-1)
+    wg = w.float().reshape(N, K // group, group)
+    tol = wg.abs().amax(-1, keepdim=True) * (1.0 / 128.0)
+    return bool(((deq - wg).abs() <= tol).all())
 
 
 def install_perm_linear(parent: nn.Module, attr_name: str, act_fmt, col_scales=None,

@@ -21,6 +21,7 @@ SOURCES = [
     "gemm_w4a4_int4.cu",
     "gemm_w4a4_int4_tm.cu",
     "gemv_w4a4_int4.cu",
+    "gemv_w4a4_int4_fused.cu",
     "gemm_fp4.cu",
     "linear_w4a4.cu",
 ]

@@ -11,6 +11,7 @@
 // Both are HBM-bound streaming kernels (2 bytes in, 1 byte out per element).
 #include "dq_common.h"
 #include "dq_ptx.cuh"
+#include "dq_quant.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -45,54 +46,6 @@ __device__ __forceinline__ float block_sum(float v, float* red, int nwarps) {
 
 __device__ __forceinline__ float bf16_round(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
-}
-
-__device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
-  float s = __fdiv_rn(amax, 7.0f);
-  if (amax == 0.f) s = 1.0f;
-  if (scale_fp16) {
-    s = __half2float(__float2half_rn(fminf(s, 65504.0f)));
-    if (s == 0.f) s = 1.0f;
-  }
-  return s;
-}
-
-// clamp(rint(v / s), -8, 7) with v / s correctly rounded, i.e. bit-identical to the IEEE
-// division, at a fraction of its instruction count: t = v * (1/s) is within 2 ulp of the true
-// quotient, so rint(t) can only differ from rint(v / s) when t lies within a few ulp of a
-// half-integer (|t| <= ~7 here, 4 ulp < 4e-6); only those rare elements take the exact division.
-// Rounding and the float -> int step avoid the conversion instructions (quarter-rate pipe; at
-// prefill sizes this kernel is bound by instruction issue, not by memory): adding and subtracting
-// 1.5 * 2^23 rounds to the nearest integer, ties to even, for |t| < 2^22, and the low byte of the
-// bit pattern of (q + 1.5 * 2^23) is q as a two's-complement int8.
-constexpr float kRoundMagic = 12582912.0f;
-// Eight codes at once.  The fast estimate runs for all of them; only if one of them lies within
-// reach of a rounding boundary (or the estimate is not finite) does the thread redo all eight with
-// the IEEE division - in a branch of its own, so that the division sequence stays out of the
-// common path instead of being predicated into it.
-__device__ __forceinline__ void quant_codes8(const float* v, float s, float inv_s, float* q) {
-  bool exact = false;
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const float t = __fmul_rn(v[e], inv_s);
-    const float qe = __fsub_rn(__fadd_rn(t, kRoundMagic), kRoundMagic);
-    const float dist = fabsf(fabsf(__fsub_rn(t, qe)) - 0.5f);
-    // the negated comparisons also catch NaN / inf (1/s overflowed for a denormal scale)
-    exact |= !(dist >= 1e-5f) || !(fabsf(t) <= 16.0f);
-    q[e] = fminf(fmaxf(qe, -8.0f), 7.0f);
-  }
-  if (exact) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) q[e] = fminf(fmaxf(rintf(__fdiv_rn(v[e], s)), -8.0f), 7.0f);
-  }
-}
-// four codes in [-8, 7] (as floats) -> four int8 in one word, first code in the low byte
-__device__ __forceinline__ uint32_t pack_codes4(float q0, float q1, float q2, float q3) {
-  const uint32_t u0 = __float_as_uint(__fadd_rn(q0, kRoundMagic));
-  const uint32_t u1 = __float_as_uint(__fadd_rn(q1, kRoundMagic));
-  const uint32_t u2 = __float_as_uint(__fadd_rn(q2, kRoundMagic));
-  const uint32_t u3 = __float_as_uint(__fadd_rn(q3, kRoundMagic));
-  return __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
 }
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
@@ -565,14 +518,27 @@ static int upload_had_matrix(const float* had_mat, int S, cudaStream_t stream) {
   static int cached_s[kMaxDevices] = {0};
   int dev = 0;
   DQ_CHECK_CUDA(cudaGetDevice(&dev));
-  if (cached[dev] == had_mat && cached_s[dev] == S) return DQ_OK;
+  // While the stream is being captured the copy is always recorded, so that a replayed graph
+  // carries its own matrix whatever was uploaded between capture and replay.  Outside capture
+  // the copy is skipped when the same pointer was uploaded last; the upload is ordered on the
+  // caller's stream only, so calls that bring a Hadamard matrix must share one stream per
+  // device (or be ordered by the caller).
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  DQ_CHECK_CUDA(cudaStreamIsCapturing(stream, &cap));
+  const bool capturing = cap != cudaStreamCaptureStatusNone;
+  // Once an upload sits inside a graph, a replay can rewrite the table at any time behind the
+  // back of this cache: from then on every call uploads.
+  static bool seen_capture[kMaxDevices] = {false};
+  if (capturing) seen_capture[dev] = true;
+  if (!seen_capture[dev] && cached[dev] == had_mat && cached_s[dev] == S) return DQ_OK;
   void* sym = nullptr;
   DQ_CHECK_CUDA(cudaGetSymbolAddress(&sym, c_had_mat));
   DQ_CHECK_CUDA(cudaMemsetAsync(sym, 0, sizeof(float) * 32 * 32, stream));
   DQ_CHECK_CUDA(cudaMemcpy2DAsync(sym, 32 * sizeof(float), had_mat, S * sizeof(float), S * sizeof(float), S,
                                   cudaMemcpyDeviceToDevice, stream));
-  cached[dev] = had_mat;
-  cached_s[dev] = S;
+  // a captured copy has not run yet: whatever is cached no longer describes the table
+  cached[dev] = capturing ? nullptr : had_mat;
+  cached_s[dev] = capturing ? 0 : S;
   return DQ_OK;
 }
 
@@ -751,6 +717,16 @@ extern "C" int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a
   DQ_REQUIRE(codes != nullptr && sx != nullptr, DQ_ERR_NULL, "codes / sx is null");
   return launch_act(static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, had, M, K, codes, sx,
                     nullptr, MODE_CODES, scale_fp16, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dq_quant_act_int4_f32(const float* x_f32, int64_t ldx, const float* a,
+                                     const dq_hadamard_desc* had, int M, int K, int8_t* codes,
+                                     float* sx, int scale_fp16, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  DQ_REQUIRE(codes != nullptr && sx != nullptr, DQ_ERR_NULL, "codes / sx is null");
+  return launch_act(x_f32, ldx, a, had, M, K, codes, sx, nullptr, MODE_CODES, scale_fp16,
+                    static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dq_quant_act_int4_rmsnorm(const void* x_bf16, int64_t ldx, const void* norm_weight_bf16,

@@ -80,12 +80,30 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Tuning knobs (dq_set_tuning): launch-shape overrides for measurement sweeps and tests.  0 means
+// "the library's own choice" for every knob except DQ_TUNE_LINEAR_FUSED (1 = on).
+enum {
+  DQ_TUNE_LINEAR_FUSED = 0,     // dq_linear_w4a4_int4 may take the one-launch decode kernel
+  DQ_TUNE_FUSED_STAGES = 1,     // ring depth of the one-launch decode kernel
+  DQ_TUNE_FUSED_SPLIT = 2,      // its split of K
+  DQ_TUNE_FUSED_EXTRA_CTA = 3,  // CTAs' worth of shared memory left free per SM for the next launch
+  DQ_TUNE_COUNT = 4
+};
+int tuning(int key);
+
 // One-time kernel attribute set-up of each translation unit (called from dq_init).
 int init_gemm_int4_kernels();
 int init_gemv_int4_kernels();
 int init_gemm_int4_tm_kernels();
 int init_gemm_fp4_kernels();
 int init_act_quant_kernels();
+int init_gemv_fused_kernels();
+
+// One-launch decode linear (quantiser inside the GEMM kernel), defined in gemv_w4a4_int4_fused.cu.
+bool gemv_fused_covers(int M, int N, int K, const DeviceState* st);
+int launch_gemv_fused(const void* x_bf16, int64_t ldx, const float* a, const uint8_t* w_packed,
+                      const float* r, int M, int N, int K, void* y, int y_dtype, int scale_fp16,
+                      cudaStream_t stream, DeviceState* st);
 
 // Decode-batch (register-path) variant of the int4 linear, defined in gemv_w4a4_int4.cu.
 int launch_gemm_int4_tm(const int8_t* codes, const float* sx, const uint8_t* w_packed,

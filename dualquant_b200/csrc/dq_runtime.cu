@@ -40,6 +40,9 @@ int set_error(int code, const char* fmt, ...) {
 
 EncodeTiledFn encode_tiled_fn() { return g_encode; }
 
+static int g_tuning[DQ_TUNE_COUNT] = {1, 0, 0, 1};
+int tuning(int key) { return (key >= 0 && key < DQ_TUNE_COUNT) ? g_tuning[key] : 0; }
+
 int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
                     uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows,
                     CUtensorMapSwizzle swizzle) {
@@ -106,7 +109,20 @@ int make_tmap_x_groups(CUtensorMap* out, const void* base, uint64_t row_bytes, u
 
 using namespace dq;
 
-extern "C" int dq_abi_version(void) { return 1; }
+extern "C" int dq_abi_version(void) { return 2; }
+
+extern "C" int dq_set_tuning(const char* name, int value) {
+  static const char* const names[DQ_TUNE_COUNT] = {"linear_fused", "fused_stages", "fused_split",
+                                                   "fused_extra_cta"};
+  DQ_REQUIRE(name != nullptr, DQ_ERR_NULL, "null tuning name");
+  for (int i = 0; i < DQ_TUNE_COUNT; ++i) {
+    if (strcmp(name, names[i]) == 0) {
+      g_tuning[i] = value;
+      return DQ_OK;
+    }
+  }
+  return set_error(DQ_ERR_UNSUPPORTED, "unknown tuning knob '%s'", name);
+}
 
 extern "C" const char* dq_last_error_string(void) { return g_err; }
 
@@ -145,6 +161,8 @@ extern "C" int dq_init(int device) {
   rc = init_gemm_fp4_kernels();
   if (rc != DQ_OK) return rc;
   rc = init_act_quant_kernels();
+  if (rc != DQ_OK) return rc;
+  rc = init_gemv_fused_kernels();
   if (rc != DQ_OK) return rc;
   DQ_CHECK_CUDA(cudaDeviceSynchronize());
   st->ready = true;

@@ -1,5 +1,6 @@
-// One-call PermLinear.forward on the real int4 path: activation quantiser + GEMM on the
-// caller's stream, intermediates in caller-provided scratch.
+// One-call PermLinear.forward on the real int4 path.  Decode batches (M <= 16, no online Hadamard)
+// run as ONE kernel that quantises in its prologue; everything else is activation quantiser + GEMM
+// on the caller's stream with the intermediates in caller-provided scratch.
 #include "dq_common.h"
 
 namespace {
@@ -24,6 +25,19 @@ extern "C" int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float*
              "scratch of %zu bytes is smaller than the %zu required", scratch_bytes,
              dq_linear_w4a4_int4_scratch_bytes(M, N, K));
   if (M == 0) return DQ_OK;
+  // Decode batches without an online Hadamard: one launch, the quantiser runs inside the GEMM
+  // kernel and the scratch stays untouched.  Same codes, scales and sums as the two launches below.
+  if ((had == nullptr || had->kind == DQ_HAD_NONE) && G == dq::kGroup &&
+      dq::tuning(dq::DQ_TUNE_LINEAR_FUSED) != 0) {
+    dq::DeviceState* st = dq::current_state();
+    if (st == nullptr) return DQ_ERR_NOT_INIT;
+    if (dq::gemv_fused_covers(M, N, K, st)) {
+      DQ_REQUIRE(y_dtype == DQ_DTYPE_F32 || y_dtype == DQ_DTYPE_BF16, DQ_ERR_UNSUPPORTED,
+                 "unknown y_dtype %d", y_dtype);
+      return dq::launch_gemv_fused(x_bf16, ldx, a, w_packed, r, M, N, K, y, y_dtype, scale_fp16,
+                                   static_cast<cudaStream_t>(stream), st);
+    }
+  }
   int8_t* codes = static_cast<int8_t*>(scratch);
   float* sx = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) +
                                        round_up(static_cast<size_t>(M) * K, 256));

@@ -5,7 +5,7 @@
 //   MXFP4: e = floor(log2(absmax_block)) - 2 clamped to [-127, 127] (-127 for a zero block);
 //          q = e2m1(x32 * 2^-e)                 scale byte = e + 127
 //   NVFP4: ts = absmax_row / (6 * 448) (1 for a zero row), or a given per-tensor value;
-//          bs = e4m3(absmax_block / 6 / ts);    q = e2m1(x32 / (ts * bs)), 0 when bs == 0
+//          bs = e4m3(clamp(absmax_block / 6 / ts, 2^-6, 448));    q = e2m1(x32 / (ts * bs))
 // Element and scale conversions use the hardware converters (cvt.rn.satfinite.e2m1x2.f32 /
 // .e4m3x2.f32: round to nearest even, saturating), divisions are IEEE.  One CTA per row, the row
 // in registers, 8 consecutive elements per thread; a block spans 2 (NVFP4) or 4 (MXFP4) lanes.
@@ -97,7 +97,9 @@ __device__ __forceinline__ void fp4_emit_vector(const float* v, float bmax, floa
       deq_scale = scalbnf(1.0f, e);
     } else {
       const float want = __fdiv_rn(__fdiv_rn(bmax, 6.0f), ts);
-      sf_byte = e4m3_byte_of(fminf(want, 448.0f));
+      // clamped to the normal range of E4M3 [2^-6, 448] before the cast, as the reference's scale
+      // quantiser does (scale_formats.py:39-45): an all-zero or tiny block gets the scale 2^-6
+      sf_byte = e4m3_byte_of(fmaxf(fminf(want, 448.0f), 0.015625f));
       const float bs = e4m3_value(sf_byte);
       const float denom = __fmul_rn(ts, bs);
       deq_scale = denom;

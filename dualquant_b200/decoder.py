@@ -110,6 +110,20 @@ def _apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.
     return x * cos + rot * sin
 
 
+_HAD_MATRICES = {}
+
+
+def _shared_hadamard_matrix(hk, kk: int, device):
+    """One device copy of the K x K Hadamard factor per (order, device), shared by all layers: the
+    quantiser skips its table upload when consecutive calls bring the same matrix pointer."""
+    if hk is None:
+        return None
+    key = (int(kk), str(device))
+    if key not in _HAD_MATRICES:
+        _HAD_MATRICES[key] = hk.to(device=device, dtype=torch.float32).contiguous()
+    return _HAD_MATRICES[key]
+
+
 class DecoderLayer:
     def __init__(self, cfg: DecoderConfig, tp: int, device, gen: torch.Generator):
         self.cfg, self.tp = cfg, tp
@@ -123,7 +137,7 @@ class DecoderLayer:
                 had_o = ops.Hadamard(_lib.HAD_PARTIAL, 1, hd, quarot.partial_hadamard_scale(self.hq), None)
             hk, kk = quarot.get_hadK(inter)
             had_d = ops.Hadamard(_lib.HAD_FULL, kk, 0, quarot.full_hadamard_scale(inter),
-                                 None if hk is None else hk.to(device))
+                                 _shared_hadamard_matrix(hk, kk, device))
         self.qkv = W4A4Linear((self.hq + 2 * self.hkv) * hd, cfg.hidden_size, device, gen)
         self.o = W4A4Linear(cfg.hidden_size, self.hq * hd, device, gen, had_o)
         self.gate_up = W4A4Linear(2 * inter, cfg.hidden_size, device, gen)

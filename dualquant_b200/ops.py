@@ -105,19 +105,20 @@ def unpack_w_int4(pw: PackedInt4Weight) -> torch.Tensor:
 
 def quant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
                    had: Optional[Hadamard] = None, scale_fp16: bool = False):
-    """bf16 [M,K] -> (codes int8 [M,K], sx fp32 [M])."""
+    """bf16 or fp32 [M,K] -> (codes int8 [M,K], sx fp32 [M])."""
     lib = _prep(x)
-    if x.dtype != torch.bfloat16:
-        raise ValueError("quant_act_int4 expects bf16 activations")
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("quant_act_int4 expects bf16 or fp32 activations")
     if x.stride(-1) != 1:
         x = x.contiguous()
     M, K = x.shape
     codes = torch.empty(M, K, dtype=torch.int8, device=x.device)
     sx = torch.empty(M, dtype=torch.float32, device=x.device)
     desc = had.desc() if had is not None else None
-    _lib.check(lib.dq_quant_act_int4(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), desc, M, K,
-                                     _ptr(codes), _ptr(sx), int(scale_fp16), _stream(x.device)),
-               "dq_quant_act_int4")
+    fn, what = ((lib.dq_quant_act_int4, "dq_quant_act_int4") if x.dtype == torch.bfloat16
+                else (lib.dq_quant_act_int4_f32, "dq_quant_act_int4_f32"))
+    _lib.check(fn(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), desc, M, K, _ptr(codes), _ptr(sx),
+                  int(scale_fp16), _stream(x.device)), what)
     return codes, sx
 
 
@@ -280,8 +281,11 @@ def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[H
                      pw: PackedInt4Weight, r: Optional[torch.Tensor], out_dtype=torch.float32,
                      scale_fp16: bool = False, scratch: Optional[torch.Tensor] = None,
                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Whole PermLinear.forward on the int4 path in one C call (two launches)."""
+    """Whole PermLinear.forward on the int4 path in one C call."""
     lib = _prep(x)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("linear_w4a4_int4 expects bf16 activations (quantise fp32 rows with "
+                         "quant_act_int4 and call gemm_w4a4_int4)")
     if x.stride(-1) != 1:
         x = x.contiguous()
     M, K = x.shape

@@ -83,6 +83,13 @@ DQ_API int dq_device_status(int device);
 
 DQ_API int dq_abi_version(void);
 
+/* Launch-shape overrides for measurement sweeps and tests (no counterpart in the reference, whose
+ * Triton kernels autotune instead: vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:26-53).
+ * name (host string): "linear_fused" (1 = dq_linear_w4a4_int4 may run decode batches as one
+ * launch, 0 = always quantiser + GEMM), "fused_stages", "fused_split", "fused_extra_cta"
+ * (0 = the library's own choice).  Process-wide, not thread-safe against concurrent launches. */
+DQ_API int dq_set_tuning(const char* name, int value);
+
 /* ---- weights ----------------------------------------------------------------------------- */
 
 /* Bytes of the packed weight matrix for (N, K): ceil(N/128) * (K/128) tiles of 8448 bytes
@@ -126,6 +133,13 @@ DQ_API int dq_quant_w_int4(const void* w_bf16, int N, int K, int G, int8_t* code
 DQ_API int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a,
                       const dq_hadamard_desc* had, int M, int K, int8_t* codes, float* sx,
                       int scale_fp16, void* stream);
+
+/* dq_quant_act_int4 for fp32 rows: the reference upcasts every input to fp32 before it scales
+ * and quantises (activations/perm_linear.py:119-125), so fp32 (and fp16, widened by the caller)
+ * activations are quantised from their fp32 values rather than through a bf16 rounding. */
+DQ_API int dq_quant_act_int4_f32(const float* x_f32, int64_t ldx, const float* a,
+                                 const dq_hadamard_desc* had, int M, int K, int8_t* codes,
+                                 float* sx, int scale_fp16, void* stream);
 
 /*
  * dq_quant_act_int4 with the MLP activation fused in front: the input row is

@@ -296,6 +296,7 @@ def perm_linear_fakequant(x, a, had, w_dq_bf16: torch.Tensor, scale_fp16: bool =
 # FP4 (parity unpinned except float_to_fp4 -- see the module docstring)
 # ----------------------------------------------------------------------------------------------
 _FP4_GRID = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+_E4M3_TINY = 0.015625  # torch.finfo(torch.float8_e4m3fn).tiny = 2^-6
 
 
 def float_to_fp4(x: torch.Tensor) -> torch.Tensor:
@@ -327,7 +328,8 @@ def fp4_code(v: torch.Tensor) -> torch.Tensor:
 #        as convert_to_mxfp (legacy_vendor/torch_quant.py:359-375); an all-zero block gets 2^-127.
 # NVFP4: blocks of 16, E4M3 block scale on top of a second-level fp32 scale
 #        ts = amax / (6 * 448) taken per token for activations or given per tensor for weights;
-#        block scale = e4m3(amax_block / 6 / ts) (round to nearest, scale_formats.py:39-45),
+#        block scale = e4m3(clamp(amax_block / 6 / ts, 2^-6, 448)) (round to nearest; the clamp to
+#        the normal E4M3 range is quantize_scale_e4m3's, scale_formats.py:39-45),
 #        element = fp4(x / (ts * block scale)).
 def _floor_log2(amax: torch.Tensor) -> torch.Tensor:
     bits = amax.contiguous().view(torch.int32)
@@ -359,7 +361,7 @@ def quant_nvfp4(x32: torch.Tensor, tensor_scale=None, block: int = 16):
         ts = torch.full((x2.shape[0], 1), float(tensor_scale), dtype=torch.float32)
     xb = x2.reshape(x2.shape[0], -1, block)
     amax = xb.abs().amax(dim=-1)
-    bs = (amax / 6.0 / ts).clamp(max=448.0).to(torch.float8_e4m3fn).to(torch.float32)
+    bs = (amax / 6.0 / ts).clamp(min=_E4M3_TINY, max=448.0).to(torch.float8_e4m3fn).to(torch.float32)
     denom = (ts * bs).unsqueeze(-1)
     q = torch.where(denom == 0, torch.zeros_like(xb), float_to_fp4(xb / torch.where(denom == 0, torch.ones_like(denom), denom)))
     deq = q * bs.unsqueeze(-1) * ts.unsqueeze(-1)

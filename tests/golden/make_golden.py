@@ -8,7 +8,8 @@ The fixtures are small seeded input/output pairs of the reference functions on t
 path; tests compare the oracle (oracle/dq_oracle.py) and the CUDA library against them.  The
 reference is imported through three shims, none of which touches the arithmetic recorded here:
   * BLOCKFMT_BACKEND -> an in-memory stub module exposing `Format` (the reference imports
-    blockfmt at module import time even for rtn_int4; MX/NVFP4 casts are NOT recorded);
+    blockfmt at module import time even for rtn_int4; the external package's own MX/NVFP4 casts
+    are NOT recorded - the MXFP4 fixture comes from the reference's in-tree convert_to_mxfp);
   * stub `accelerate` modules (imported, never called, by quarot/vendor/utils.py);
   * the reference's own pure-torch stand-in for fast_hadamard_transform.
 """
@@ -148,6 +149,42 @@ def main(ref_root: str) -> None:
     grid = torch.cat([torch.linspace(-7, 7, 449), torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])])
     out["fp4_in"] = grid.numpy()
     out["fp4_out"] = float_to_fp4(grid.clone()).numpy()
+
+    # ---- MXFP4 block cast: the reference's in-tree statement (legacy_vendor/torch_quant.py:359-375)
+    # convert_to_mxfp moves its input to 'cuda:0'; there is no GPU where this script runs, so the
+    # device argument is dropped for the duration of the call (the arithmetic is untouched).
+    from torch_quant import convert_to_mxfp  # reference
+
+    xm = _seeded_x(16, 512, 23).float()
+    am = torch.exp(torch.randn(512, generator=g) * 0.3).to(torch.float16).to(torch.float32)
+    xm = xm * am
+    xm[3, 64:96] = 0.0            # an all-zero block
+    xm[4, :] *= 2.0 ** -20        # small magnitudes
+    xm[5, :] *= 2.0 ** 30         # large magnitudes
+    xm[6, 0:32] = torch.tensor([6.0, -6.0, 3.0, 1.5] * 8)  # block maximum exactly on the grid
+    xm[7, 0:32] = torch.tensor([4.0, 2.5, 1.25, 0.25] * 8) * 0.5  # elements on rounding ties
+    orig_to = torch.Tensor.to
+
+    def _to_without_cuda(self, *args, **kwargs):
+        args = tuple(v for v in args if not (isinstance(v, str) and v.startswith("cuda")))
+        kwargs = {k: v for k, v in kwargs.items() if not (k == "device" and str(v).startswith("cuda"))}
+        return orig_to(self, *args, **kwargs) if (args or kwargs) else self
+
+    torch.Tensor.to = _to_without_cuda
+    try:
+        out["mxfp4_in"] = xm.numpy().copy()
+        out["mxfp4_out"] = convert_to_mxfp(xm.clone(), block_size=32).numpy()
+    finally:
+        torch.Tensor.to = orig_to
+
+    # ---- E4M3 scale quantiser used for NVFP4-style block scales (scale_formats.py:39-45) -----------
+    import scale_formats  # reference
+
+    sgrid = torch.cat([torch.tensor([0.0, 1e-9, 2.0 ** -10, 2.0 ** -7, 2.0 ** -6, 0.0165, 447.0, 448.0, 449.0,
+                                     500.0, 1e6]),
+                       torch.exp(torch.linspace(-8.0, 7.0, 600))])
+    out["e4m3_scale_in"] = sgrid.numpy()
+    out["e4m3_scale_out"] = scale_formats.quantize_scale_e4m3(sgrid.clone()).numpy()
 
     path = os.path.join(here, "reference_vectors.npz")
     np.savez_compressed(path, **out)

@@ -35,7 +35,7 @@ def test_library_exports_every_declared_symbol():
 def test_ctypes_table_covers_the_header():
     assert sorted(_lib.SIGNATURES) == _declared()
     lib = _lib.load()
-    assert lib.dq_abi_version() == 1
+    assert lib.dq_abi_version() == 2
     assert lib.dq_packed_w_bytes(200, 256) == 2 * 2 * 8448  # 2 row tiles x 2 k groups
     assert lib.dq_linear_w4a4_int4_scratch_bytes(16, 128, 4096) == 16 * 4096 + 256
 

@@ -87,6 +87,33 @@ def test_nvfp4_bit_exact(M, K, per_tensor):
     _lib.device_status(0)
 
 
+def test_mxfp4_cast_matches_reference_convert_to_mxfp(golden):
+    """The library's MXFP4 cast against the output of the reference's own convert_to_mxfp
+    (legacy_vendor/torch_quant.py:359-375, block 32) recorded in the golden fixtures: zero block,
+    tiny and huge magnitudes, block maxima on the grid, elements on rounding ties."""
+    x = torch.from_numpy(golden["mxfp4_in"])
+    want = torch.from_numpy(golden["mxfp4_out"])
+    fq = ops.fakequant_fp4(x.to(DEV), _lib.FP4_MXFP4)
+    assert torch.equal(fq.cpu(), want)
+    assert torch.equal(formats.make_format("mxfp4").cast(x.to(DEV)).cpu(), want)
+    _lib.device_status(0)
+
+
+def test_nvfp4_block_scale_matches_reference_e4m3_quantiser(golden):
+    """NVFP4 block-scale bytes against the reference's quantize_scale_e4m3 (scale_formats.py:39-45:
+    clamp to [2^-6, 448], E4M3 round-to-nearest-even) on a grid of scale values."""
+    want = torch.from_numpy(golden["e4m3_scale_in"])
+    x = torch.zeros(want.numel(), 16)
+    x[:, 0] = want * 6.0
+    exact = (x[:, 0] / 6.0) == want
+    one = torch.ones(1, device=DEV)
+    _, sf, _ = ops.quant_fp4(x.to(DEV), _lib.FP4_NVFP4, None, one)
+    got = sf.cpu().view(torch.float8_e4m3fn).float().reshape(-1)
+    ref = torch.from_numpy(golden["e4m3_scale_out"])
+    assert torch.equal(got[exact], ref[exact])
+    _lib.device_status(0)
+
+
 def test_element_rounding_matches_reference_table(golden):
     # blocks whose exponent is 0 (absmax in [4, 8)): the MXFP4 element is float_to_fp4(x) itself
     grid = torch.from_numpy(golden["fp4_in"])

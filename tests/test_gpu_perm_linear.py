@@ -56,7 +56,8 @@ def test_forward_against_reference_outputs(golden, tag):
 
 def test_forward_matches_oracle_and_handles_leading_dims():
     K, N = 1024, 384
-    w = synthetic.make_w(N, K, 4)
+    # a W4 checkpoint: the stored weight is the bf16 fake-quant of the raw one (group 128)
+    w = O.dequant_w(*O.quant_w_int4(synthetic.make_w(N, K, 4))).to(torch.bfloat16)
     lin = nn.Linear(K, N, bias=True).to(torch.bfloat16)
     lin.weight.data = w.clone()
     pl = PermLinear(lin.to(DEV), formats.make_format("rtn_int4", block_size=-1))
@@ -67,6 +68,7 @@ def test_forward_matches_oracle_and_handles_leading_dims():
     x = synthetic.make_x(6, K, 4).reshape(2, 3, K)
     y = pl(x.to(DEV))
     assert y.shape == (2, 3, N) and y.dtype == torch.bfloat16
+    assert pl._packed is not None and pl._weight_on_grid is True  # the real int4 GEMM ran
     qx, sx, _ = O.quant_act_int4(x.reshape(6, K), a, None, False)
     qw, sw = O.quant_w_int4(w)
     ref = O.dequant_matmul(qx, sx, qw, sw) + lin.bias.detach().double().cpu()
@@ -100,12 +102,69 @@ def test_format_cast_matches_reference(golden):
     assert torch.equal(fw.cast(w).cpu(), torch.from_numpy(golden["wcast_out"]))
 
 
+def test_weight_off_the_int4_grid_keeps_the_reference_formulation():
+    """The reference's PermLinear never quantises the weight (activations/perm_linear.py:136-141).
+    A 16-bit weight (W16A4) must therefore not be pushed through the W4 GEMM: the layer runs
+    fake-quantised activations into the wrapped layer's own F.linear, exactly the reference's
+    formulation; force=True is the explicit opt-in to quantising the weight here."""
+    K, N, M = 512, 256, 7
+    lin = nn.Linear(K, N, bias=False).to(torch.bfloat16)
+    lin.weight.data = synthetic.make_w(N, K, 5).clone()  # raw bf16 weight, not on the int4 grid
+    fmt = formats.make_format("rtn_int4", block_size=-1)
+    pl = PermLinear(lin.to(DEV), fmt)
+    _, c = synthetic.make_scales(N, K, 5)
+    pl.set_act_scale((1.0 / c).to(DEV))
+    x = synthetic.make_x(M, K, 5).to(DEV)
+    y = pl(x)
+    assert pl._packed is None and pl._weight_on_grid is False
+    assert torch.equal(y, pl.layer(pl._quantise_act(x)))
+    xq, _, _ = O.quant_act_int4(x.cpu(), 1.0 / c, None, False)
+    # opt-in: quantise the weight here and run the int4 GEMM
+    assert pl.pack(force=True) is True
+    y4 = pl(x)
+    assert pl._packed is not None
+    rel = (y4.float() - y.float()).abs().max() / y.float().abs().max()
+    assert 1e-3 < rel < 0.2  # a different (W4) result, which is why it must be asked for
+
+
+def test_fp32_inputs_are_quantised_from_fp32():
+    """fp32 activations take the fp32 quantiser (the reference upcasts, perm_linear.py:119-125):
+    codes equal the oracle's on the fp32 values, which differ from the codes of the bf16-rounded
+    input on some elements."""
+    K, N, M = 1024, 256, 5
+    w = O.dequant_w(*O.quant_w_int4(synthetic.make_w(N, K, 6))).to(torch.bfloat16)
+    lin = nn.Linear(K, N, bias=False).to(torch.bfloat16)
+    lin.weight.data = w.clone()
+    pl = PermLinear(lin.to(DEV), formats.make_format("rtn_int4", block_size=-1))
+    _, c = synthetic.make_scales(N, K, 6)
+    a = 1.0 / c
+    pl.set_act_scale(a.to(DEV))
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(M, K, generator=g)  # fp32 values that are not bf16-representable
+    y = pl(x.to(DEV))
+    qx, sx, _ = O.quant_act_int4(x, a, None, False)
+    qw, sw = O.quant_w_int4(w)
+    ref = O.dequant_matmul(qx, sx, qw, sw)
+    err = (y.double().cpu() - ref).abs().max() / ref.abs().max()
+    assert err < 8e-3  # bf16 output rounding only
+    from dualquant_b200 import ops
+    codes, s_dev = ops.quant_act_int4(x.to(DEV), a.to(DEV), None, False)
+    assert torch.equal(codes.cpu(), qx) and torch.equal(s_dev.cpu(), sx)
+    qx_bf16, _, _ = O.quant_act_int4(x.to(torch.bfloat16), a, None, False)
+    assert not torch.equal(qx_bf16, qx)
+
+
 @pytest.mark.parametrize("name", ["mxfp4", "nvfp4"])
 def test_fp4_forward_close_to_fakequant_reference(name):
-    # PermLinear with an FP4 activation format runs the packed FP4 GEMM; compare with the
-    # fake-quant formulation (cast both operands, fp64 matmul) the reference computes
+    # PermLinear with an FP4 activation format and a weight already on that format's grid runs the
+    # packed FP4 GEMM; compare with the fake-quant formulation (cast both operands, fp64 matmul)
+    # the reference computes
     K, N, M = 512, 256, 9
     w = synthetic.make_w(N, K, 8)
+    if name == "mxfp4":
+        w = O.quant_mxfp4(w.float())[2].to(torch.bfloat16)  # exact in bf16
+    else:
+        w = O.quant_nvfp4(w.float(), float((w.float().abs().max() / 2688.0).item()))[3].to(torch.bfloat16)
     lin = nn.Linear(K, N, bias=False).to(torch.bfloat16)
     lin.weight.data = w.clone()
     fmt = formats.make_format(name)
@@ -116,6 +175,7 @@ def test_fp4_forward_close_to_fakequant_reference(name):
     pl = pl.to(DEV)
     x = synthetic.make_x(M, K, 8)
     y = pl(x.to(DEV)).double().cpu()
+    assert pl._packed_fp4 is not None and pl._weight_on_grid_fp4 is True
     x32 = x.float() * a
     if name == "mxfp4":
         xd, wd = O.quant_mxfp4(x32)[2], O.quant_mxfp4(w.float())[2]

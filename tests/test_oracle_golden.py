@@ -137,3 +137,25 @@ def test_acc_and_epilogue_agree_with_dequant_matmul():
     y32 = O.epilogue(acc, sw, r, sx)
     y64 = O.dequant_matmul(qx, sx, qw, sw, r)
     assert torch.allclose(y32.double(), y64, rtol=1e-5, atol=1e-6 * y64.abs().max().item())
+
+
+def test_mxfp4_block_cast_matches_convert_to_mxfp(golden):
+    # legacy_vendor/torch_quant.py:359-375 run on CPU by the fixture generator, block 32
+    x = torch.from_numpy(golden["mxfp4_in"])
+    _, e8m0, deq = O.quant_mxfp4(x, 32)
+    assert torch.equal(deq, torch.from_numpy(golden["mxfp4_out"]))
+    assert int(e8m0.reshape(16, -1)[3, 2]) == 0  # the all-zero block carries the smallest exponent
+
+
+def test_nvfp4_block_scale_rounding_matches_quantize_scale_e4m3(golden):
+    # scale_formats.py:39-45: clamp to [2^-6, 448], cast to E4M3 (round to nearest even) and back.
+    # Feed each grid value as "amax / 6 / ts" of a block of 16 and read the block scale back.
+    want = torch.from_numpy(golden["e4m3_scale_in"])
+    x = torch.zeros(want.numel(), 16)
+    x[:, 0] = want * 6.0
+    exact = (x[:, 0] / 6.0) == want  # keep only grid points that survive the *6 /6 round trip
+    _, bs, _, _ = O.quant_nvfp4(x, tensor_scale=1.0)
+    ref = torch.from_numpy(golden["e4m3_scale_out"])
+    assert int(exact.sum()) > 500
+    assert torch.equal(bs.reshape(-1)[exact], ref[exact])
+    assert float(bs.min()) == 2.0 ** -6  # zero / tiny blocks are clamped to the smallest normal
