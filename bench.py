@@ -50,6 +50,22 @@ def _step_bytes(n_split: int = 1) -> int:
     return total
 
 
+def bench_config(world: int) -> dict:
+    """The workload description; both arms (this library and --impl reference) print exactly
+    this object."""
+    return {
+        "workload": WORKLOAD,
+        "linears": {name: [K, N] for name, K, N in synthetic.LLAMA31_8B_LINEARS},
+        "M": list(synthetic.DECODE_M),
+        "step": "one pass over all 24 (linear, M) pairs: per-token activation quantisation + dual-scale GEMM, "
+                "bf16 X in, fp32 Y out",
+        "seed": 0,
+        "n_split": world,
+        "parallelism": f"column-parallel over N x{world}, no collective",
+        "step_algorithmic_bytes": _step_bytes(world),
+    }
+
+
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -71,6 +87,7 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.lines = []
+        self.stamps = []
         self.thread = None
 
     def start(self):
@@ -88,12 +105,25 @@ class ClockSampler:
         def reader():
             for line in self.proc.stdout:
                 self.lines.append(line)
+                self.stamps.append(time.time())
 
         self.thread = threading.Thread(target=reader, daemon=True)
         self.thread.start()
         t0 = time.time()
         while not self.lines and time.time() - t0 < 5.0:
             time.sleep(0.01)
+
+    def median_sm_mhz(self, t0: float, t1: float):
+        """Median SM clock of the samples that arrived in the wall-clock window [t0, t1]."""
+        vals = []
+        for line, ts in zip(list(self.lines), list(self.stamps)):
+            if t0 <= ts <= t1:
+                p = [v.strip() for v in line.split(",")]
+                try:
+                    vals.append(float(p[1]))
+                except (ValueError, IndexError):
+                    pass
+        return statistics.median(vals) if vals else None
 
     def stop(self):
         if self.proc is None:
@@ -284,6 +314,43 @@ def _time_loop(run, steps, warmup, dev, barrier):
     return e0.elapsed_time(e1)  # ms
 
 
+def _kernel_class(M: int) -> str:
+    """Which GEMM kernel dq_gemm_w4a4_int4 runs for a batch of M tokens."""
+    if M <= 8:
+        return "gemv_w4a4_int4_kernel<1> (mma.sync.s8, 8-token capacity)"
+    if M <= 16:
+        return "gemv_w4a4_int4_kernel<2> (mma.sync.s8, 16-token capacity)"
+    if M <= 32:
+        return "gemm_w4a4_int4_tm_kernel<32> (tcgen05 kind::i8, weights via tensor memory)"
+    if M <= 64:
+        return "gemm_w4a4_int4_tm_kernel<64> (tcgen05 kind::i8, weights via tensor memory)"
+    return "gemm_w4a4_int4_kernel<128> (tcgen05 kind::i8, int8 weight tiles in shared memory)"
+
+
+def _traffic_table():
+    """ncu DRAM traffic per launch of each decode kernel class (profiles/decode_kernel_traffic.json,
+    written from ncu captures of `bench.py --case NAME:M`); {} when the file is absent."""
+    path = os.path.join(ROOT, "profiles", "decode_kernel_traffic.json")
+    if not os.path.exists(path):
+        return {}
+    with open(path) as f:
+        return json.load(f)
+
+
+def _sustained(run, ms_per_step, dev, barrier, max_over_ranks, sampler, reps=5, target_s=0.2):
+    """`reps` timed loops of at least `target_s` seconds of GPU time each (the K-step loop of the
+    contract lasts a few milliseconds): ms/step of every repeat and the SM clock sampled during it."""
+    n = max(10, int(target_s * 1e3 / max(ms_per_step, 1e-3)) + 1)
+    out, clocks = [], []
+    for _ in range(reps):
+        t0 = time.time()
+        ms = max_over_ranks(_time_loop(run, n, 1, dev, barrier)) / n
+        t1 = time.time()
+        out.append(ms)
+        clocks.append(sampler.median_sm_mhz(t0, t1) if sampler is not None else None)
+    return n, out, clocks
+
+
 def run_gpu(args):
     import torch.distributed as dist
 
@@ -316,47 +383,84 @@ def run_gpu(args):
 
     wl = Workload(dev, rank, world, seed=0)
     step_bytes = _step_bytes(world)
-    launches_per_step = 2 * len(synthetic.DECODE_M) * len(wl.linears)
+    n_lin = len(wl.linears)
+    n_m = len(synthetic.DECODE_M)
+    launches_per_step = 2 * n_m * n_lin  # activation quantiser + GEMM per linear
+    peaks, peak_kind = _peaks()
+    hbm = peaks["hbm_gbs"]
 
     # ---- device-resident: CUDA graph of one step ---------------------------------------------
     graph = _capture(wl.step, dev) if not args.no_graph else None
     run = graph.replay if graph is not None else wl.step
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler is not None:
         sampler.start()
     ms = max_over_ranks(_time_loop(run, args.steps, args.warmup, dev, barrier))
     ms_per_step = ms / args.steps
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
-
-    # ---- dominant kernel alone (GEMM launches only) for the roofline -------------------------
-    wl.prequantise()
-    g2 = _capture(wl.gemm_only_step, dev) if not args.no_graph else None
-    run2 = g2.replay if g2 is not None else wl.gemm_only_step
-    ms2 = max_over_ranks(_time_loop(run2, args.steps, args.warmup, dev, barrier)) / args.steps
-    n_gemm = len(synthetic.DECODE_M) * len(wl.linears)
-    peaks, peak_kind = _peaks()
-    achieved = step_bytes / world / (ms2 * 1e-3) / 1e9  # per GPU
-    roofline = {
-        "bound": "hbm", "kernel": "gemm_w4a4_int4_kernel",
-        "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "peak_kind": peak_kind,
-        "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-        "avg_launch_us": round(ms2 * 1e3 / n_gemm, 2),
-        "algorithmic_bytes_per_launch": step_bytes // world // n_gemm,
-        "traffic": None,
+    n_rep, rep_ms, rep_clk = _sustained(run, ms_per_step, dev, barrier, max_over_ranks, sampler)
+    sustained = {
+        "steps_per_repeat": n_rep, "repeats": len(rep_ms),
+        "value_median": round(step_bytes / (statistics.median(rep_ms) * 1e-3) / 1e9, 1),
+        "value_min": round(step_bytes / (max(rep_ms) * 1e-3) / 1e9, 1),
+        "value_max": round(step_bytes / (min(rep_ms) * 1e-3) / 1e9, 1),
+        "ms_per_step": [round(v, 4) for v in rep_ms], "sm_mhz": rep_clk,
     }
-    prof = os.path.join(ROOT, "profiles", "gemm_w4a4_int4_decode.traffic.json")
-    if os.path.exists(prof):
-        with open(prof) as f:
-            prof_data = json.load(f)
-            roofline["traffic"] = prof_data.get("dram_bytes_per_launch")
-            roofline["traffic_case"] = (f"ncu capture of {prof_data.get('kernel')} on {prof_data.get('case')}: "
-                                        f"{prof_data.get('algorithmic_bytes_per_launch')} algorithmic bytes per launch")
+
+    # ---- GEMM launches alone, per kernel class (one class per batch size) ---------------------
+    wl.prequantise()
+    traffic = _traffic_table()
+    classes = []
+    gemm_ms_total = 0.0
+    for mi, M in enumerate(synthetic.DECODE_M):
+        def gemm_m(mi=mi, M=M):
+            for c in range(len(wl.linears[0]["w"])):  # cycle the weight copies: every launch reads HBM
+                for lin in wl.linears:
+                    codes, sx = wl.q[(M, lin["name"])]
+                    wl.ops.gemm_w4a4_int4(codes, sx, lin["w"][(mi + c) % n_m], lin["r"], out=wl.y[(M, lin["name"])])
+        gm = _capture(gemm_m, dev) if not args.no_graph else None
+        n_launch = n_lin * n_m
+        ms_m = max_over_ranks(_time_loop(gm.replay if gm is not None else gemm_m, max(args.steps // 2, 5),
+                                         args.warmup, dev, barrier)) / max(args.steps // 2, 5)
+        bytes_m = sum(synthetic.int4_gemm_bytes(M, lin["N"], lin["K"]) for lin in wl.linears)  # this rank, 4 launches
+        us = ms_m * 1e3 / n_launch
+        ach = bytes_m / n_lin / (us * 1e-6) / 1e9
+        gemm_ms_total += ms_m / n_m  # one pass over the four linears of this M
+        rec = {"kernel": _kernel_class(M), "M": M, "launches_per_step": n_lin,
+               "algorithmic_bytes_per_launch": bytes_m // n_lin, "us_per_launch": round(us, 2),
+               "achieved": round(ach, 1), "frac": round(ach / hbm, 4)}
+        t = traffic.get(f"M{M}")
+        if t is not None and world == 1:
+            rec["traffic"] = t.get("dram_bytes_per_launch")
+            rec["traffic_case"] = t.get("case")
+            rec["traffic_case_algorithmic_bytes"] = t.get("algorithmic_bytes_per_launch")
+        classes.append(rec)
+        del gm
+    n_gemm = n_m * n_lin
+    achieved = step_bytes / world / (gemm_ms_total * 1e-3) / 1e9  # per GPU, all GEMM launches of a step
+    dom = max(classes, key=lambda r: r["us_per_launch"] * r["launches_per_step"])
+    roofline = {
+        "bound": "hbm", "kernel": dom["kernel"], "achieved": dom["achieved"], "peak": hbm,
+        "peak_kind": peak_kind, "unit": "GB/s", "frac": dom["frac"],
+        "traffic": dom.get("traffic"), "traffic_case": dom.get("traffic_case"),
+        "traffic_case_algorithmic_bytes": dom.get("traffic_case_algorithmic_bytes"),
+        "algorithmic_bytes_per_launch": dom["algorithmic_bytes_per_launch"],
+        "avg_launch_us": dom["us_per_launch"],
+        "note": "the class with the largest share of the step's GEMM time; every class is listed in `classes`",
+        "all_gemm_launches": {"achieved": round(achieved, 1), "frac": round(achieved / hbm, 4),
+                              "avg_launch_us": round(gemm_ms_total * 1e3 / n_gemm, 2),
+                              "algorithmic_bytes_per_launch": step_bytes // world // n_gemm},
+        "quantiser": {"kernel": "act_quant_rows_kernel", "launches_per_step": n_gemm,
+                      "us_per_launch": round(max(ms_per_step - gemm_ms_total, 0.0) * 1e3 / n_gemm, 2),
+                      "note": "step time minus GEMM-only time, per launch (latency-bound at decode sizes)"},
+        "classes": classes,
+    }
 
     # ---- end to end through the C ABI with host buffers -----------------------------------------
     if args.no_graph:
-        run_m = [(lambda mi=mi: wl.step_m(mi)) for mi in range(len(synthetic.DECODE_M))]
+        run_m = [(lambda mi=mi: wl.step_m(mi)) for mi in range(n_m)]
     else:
-        graphs_m = [_capture(lambda mi=mi: wl.step_m(mi), dev) for mi in range(len(synthetic.DECODE_M))]
+        graphs_m = [_capture(lambda mi=mi: wl.step_m(mi), dev) for mi in range(n_m)]
         run_m = [gm.replay for gm in graphs_m]
     wl.e2e_setup(run_m)
     ms3 = max_over_ranks(_time_loop(wl.e2e_step, args.steps, args.warmup, dev, barrier)) / args.steps
@@ -365,36 +469,74 @@ def run_gpu(args):
            "ms_per_step": round(ms3, 4), "h2d_bytes_per_step": h2d * world,
            "d2h_bytes_per_step": d2h * world,
            "copies": "per batch size, on two copy streams, overlapped with the other batch sizes' linears"}
-    # clock samples cover the three timed regions above (each is short: tens of ms)
-    clocks = sampler.stop() if rank == 0 else None
+    # clock samples cover the timed regions above
+    clocks = sampler.stop() if sampler is not None else None
     _lib.device_status(local_rank)
 
-    detail = None
-    if args.detail:
-        detail = per_shape_detail(wl, dev, args)
+    per_shape = per_shape_detail(wl, dev, args) if (world == 1 and not args.no_detail) else None
+    del wl, graph
+    torch.cuda.empty_cache()
+
+    # ---- the other benchmark configurations, as sub-records of the same line -------------------
+    extras = {}
+    if not args.no_extras:
+        extras = run_extras(args, world, rank, local_rank, dev)
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4xint4->int32 (kind::i8), fp32 epilogue",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int4xint4->int32 (kind::i8 / mma.sync.s8), fp32 epilogue",
             "data": "synthetic", "impl": "dualquant_b200",
-            "config": {"workload": WORKLOAD, "parallelism": f"column-parallel over N x{world}, no collective",
-                       "l2": "6 weight copies in rotation (655 MB > 5x L2): inputs larger than L2",
-                       "launch": "CUDA graph replay of one step" if graph is not None else "stream launches",
-                       "step_algorithmic_bytes": step_bytes},
+            "config": bench_config(world),
+            "arm": {"l2": "6 weight copies in rotation (655 MB > 5x L2): inputs larger than L2",
+                    "launch": "CUDA graph replay of one step" if not args.no_graph else "stream launches"},
+            "sustained": sustained,
             "roofline": roofline,
             "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
-        if not args.skip_cpu and world >= 1:
+        if per_shape is not None:
+            line["per_shape_gemm_GBps"] = per_shape
+            line["per_shape_frac_of_hbm"] = {k: [round(v / hbm, 3) for v in row] for k, row in per_shape.items()}
+        line.update(extras)
+        if not args.skip_cpu:
             line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_budget)
-        if detail is not None:
-            line["per_shape_GBps"] = detail
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_extras(args, world, rank, local_rank, dev):
+    """Benchmark configurations 0, 2, 3 and 4 measured in the same run.  One GPU: prefill int4
+    (TOPS), the config-2 MLP, block-scaled FP4 and the 32-layer decoder.  N GPUs: the decoder,
+    tensor-parallel over the N ranks with the all-reduce fused into the decode GEMM.  A suite that
+    fails reports its error text instead of numbers."""
+    out = {}
+
+    def guarded(name, fn):
+        try:
+            out[name] = fn()
+        except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
+
+    sub = argparse.Namespace(**vars(args))
+    sub.steps = max(5, min(args.steps, 10))
+    if world == 1:
+        guarded("peaks_mma_only", lambda: run_peak_suite(sub, emit=False))
+        guarded("prefill", lambda: run_prefill_suite(sub, emit=False))
+        guarded("mlp", lambda: run_mlp_suite(sub, emit=False))
+        guarded("fp4", lambda: run_fp4_suite(sub, emit=False))
+        guarded("reference_gpu_kernels", lambda: run_reference_gpu(sub, emit=False))
+    sub.fused_allreduce = True
+    try:
+        out["decoder"] = run_decoder_suite(sub, emit=False, init_pg=False)
+    except Exception as exc:  # noqa: BLE001
+        out["decoder"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    return out if rank == 0 else {}
 
 
 def run_case(args):
@@ -536,7 +678,7 @@ PREFILL_SHAPES = (
 )
 
 
-def run_prefill_suite(args):
+def run_prefill_suite(args, emit=True):
     """Prefill-shaped linears (tensor-core bound): TOPS = 2*M*N*K / time of the GEMM launch and of
     quantiser + GEMM, against the dense int8 peak (nominal 4500 TOPS; 2x the measured bf16 peak)."""
     from dualquant_b200 import _lib, ops
@@ -585,11 +727,20 @@ def run_prefill_suite(args):
         row["bf16_matmul_us"] = round(ms_bf16 * 1e3, 1)
         row["bf16_matmul_TFLOPS"] = round(2.0 * M * N * K / ms_bf16 / 1e9, 1)
         del xb, wb, yb, g_bf16
-    print(json.dumps({"suite": "prefill", "unit": "TOPS (2*M*N*K/s)", "peaks": {"int8_nominal": 4500.0,
-                      "int8_2x_bf16_" + kind: int8_measured}, "steps": args.steps, "rows": rows}), flush=True)
+    mma = _mma_peaks(args)
+    if mma is not None and mma.get("int8_TOPS"):
+        for row in rows:
+            row["frac_int8_mma_only_measured"] = round(row["gemm_TOPS"] / mma["int8_TOPS"], 4)
+    rec = {"suite": "prefill", "unit": "TOPS (2*M*N*K/s)",
+           "peaks": {"int8_nominal": 4500.0, "int8_2x_bf16_" + kind: int8_measured,
+                     "int8_mma_only_measured": None if mma is None else mma.get("int8_TOPS")},
+           "steps": args.steps, "rows": rows}
+    if emit:
+        print(json.dumps(rec), flush=True)
+    return rec
 
 
-def run_mlp_suite(args):
+def run_mlp_suite(args, emit=True):
     """Benchmark configuration 2: prefill MLP, M = 8192 tokens, int4 dual-scale.  gate+up 4096 -> 28672
     (bf16 out), SiLU(gate) * up in bf16, QuaRot R4 online Hadamard of size 14336 (28 x 512) fused
     with the activation quantiser, down 14336 -> 4096.  Stage times from CUDA-graph replays."""
@@ -651,10 +802,12 @@ def run_mlp_suite(args):
     out["whole_mlp_TOPS"] = round(ops_total / (out["whole_mlp_us"] * 1e-6) / 1e12, 1)
     out["hadamard_quant_GBps"] = round((M * I * 3) / (out["hadamard_quant_us"] * 1e-6) / 1e9, 1)
     _lib.device_status(0)
-    print(json.dumps(out), flush=True)
+    if emit:
+        print(json.dumps(out), flush=True)
+    return out
 
 
-def run_decoder_suite(args):
+def run_decoder_suite(args, emit=True, init_pg=True):
     """Benchmark configuration 4: random-init Llama-3.1-8B-architecture decoder, every linear W4A4 int4
     dual-scale with online Hadamards, bf16 attention; prefill batch x seqlen, then decode steps.
     Tensor-parallel over the ranks of the launch (torch.distributed.run) with an NCCL all-reduce
@@ -670,7 +823,8 @@ def run_decoder_suite(args):
     dev = torch.device("cuda", local_rank)
     group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        if init_pg:
+            dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     cfg = decoder.DecoderConfig(num_hidden_layers=args.layers)
     B, S, steps = args.batch, args.seqlen, args.decode_steps
@@ -723,6 +877,25 @@ def run_decoder_suite(args):
                 graph = None
                 sys.stderr.write(f"decode graph capture failed, running eagerly: {exc}\n")
 
+        # Correctness gate before any decode time is reported (the reference's harness does the same,
+        # ablation/real_int4_kernel/graph_bench_all.py:84-92,142-153): the captured step must
+        # reproduce the eagerly launched step on the same token and cache position.
+        checks = {"graph_equals_eager": None}
+        if graph is not None:
+            pos_t.fill_(S)
+            static_tok.copy_(tok)
+            eager_logits = model.decode_step(static_tok, pos_t).clone()
+            graph.replay()
+            torch.cuda.synchronize(dev)
+            diff = (static_logits.float() - eager_logits.float()).abs().max().item()
+            ok = bool(torch.equal(static_logits, eager_logits))
+            if world > 1:
+                t = torch.tensor([0.0 if ok else 1.0], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ok = t.item() == 0.0
+            checks = {"graph_equals_eager": ok, "max_abs_logit_diff": diff}
+        checks["prefill_logits_finite"] = bool(torch.isfinite(logits).all().item())
+
         if graph is None:
             for _ in range(2):  # untimed eager warm-up steps (allocator, lazy NCCL channels)
                 model.decode_step(tok, pos_t)
@@ -741,24 +914,34 @@ def run_decoder_suite(args):
 
         _, decode_ms = timed(decode_loop)
     _lib.device_status(local_rank)
-    if rank == 0:
+    rec = None
+    if True:
         wbytes = decoder.linear_weight_bytes(cfg)
         step_ms = decode_ms / steps
-        print(json.dumps({
+        peaks, kind = _peaks()
+        rec = ({
             "suite": "decoder", "n_gpus": world, "layers": cfg.num_hidden_layers, "batch": B, "seqlen": S,
             "decode_steps": steps, "parallelism": f"tp{world}: qkv/gate_up column-parallel, o/down row-parallel + "
                            + ("all-reduce fused into the decode GEMM over peer memory (NCCL in prefill)" if fused
                               else "NCCL all-reduce"),
             "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(B * S / prefill_ms * 1e3, 1),
-            "decode_ms_per_step": round(step_ms, 3), "decode_tokens_per_s": round(B / step_ms * 1e3, 1),
+            "decode_ms_per_step": round(step_ms, 3) if checks.get("graph_equals_eager") is not False else None,
+            "decode_tokens_per_s": round(B / step_ms * 1e3, 1),
             "decode_launch": "CUDA graph" if graph is not None else "eager",
             "linear_weight_GB": round(wbytes / 1e9, 3),
-            "decode_weight_stream_GBps": round(wbytes / (step_ms * 1e-3) / 1e9, 1)}), flush=True)
-    if world > 1:
+            "decode_weight_stream_GBps": round(wbytes / (step_ms * 1e-3) / 1e9, 1),
+            "decode_weight_stream_frac_of_hbm_per_gpu": round(wbytes / world / (step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+            "checks": checks})
+    del model
+    torch.cuda.empty_cache()
+    if emit and rank == 0:
+        print(json.dumps(rec), flush=True)
+    if world > 1 and init_pg:
         dist.destroy_process_group()
+    return rec
 
 
-def run_fp4_suite(args):
+def run_fp4_suite(args, emit=True):
     """Block-scaled FP4 linears on the Qwen2.5-7B-architecture shapes (benchmark configuration 3):
     MXFP4 and NVFP4, M = 16 (GB/s of algorithmic bytes) and M = 4096 (TFLOPS = 2*M*N*K/s)."""
     from dualquant_b200 import _lib, ops
@@ -814,8 +997,19 @@ def run_fp4_suite(args):
                              "frac_hbm_measured": round(nbytes / ms_gemm / 1e6 / peaks["hbm_gbs"], 4)})
             del pw
     _lib.device_status(0)
-    print(json.dumps({"suite": "fp4", "peaks": {"fp4_nominal_TFLOPS": 9000.0, "fp4_4x_bf16_" + kind: fp4_measured,
-                      "hbm_GBps_" + kind: peaks["hbm_gbs"]}, "steps": args.steps, "rows": rows}), flush=True)
+    mma = _mma_peaks(args)
+    if mma is not None:
+        for row in rows:
+            pk = mma.get(row["fmt"] + "_TFLOPS")
+            if pk and row["M"] > 128:
+                row["frac_fp4_mma_only_measured"] = round(row["gemm_TFLOPS"] / pk, 4)
+    rec = {"suite": "fp4", "peaks": {"fp4_nominal_TFLOPS": 9000.0, "fp4_4x_bf16_" + kind: fp4_measured,
+                                     "hbm_GBps_" + kind: peaks["hbm_gbs"],
+                                     "mma_only_measured": mma},
+           "steps": args.steps, "rows": rows}
+    if emit:
+        print(json.dumps(rec), flush=True)
+    return rec
 
 
 def _fp4_prologue(ops, x, a, pw):
@@ -853,25 +1047,50 @@ def per_shape_detail(wl, dev, args):
 class CpuWorkload:
     """The reference's CPU path for the same step: PermLinear.forward as fake-quant
     (activations/perm_linear.py:108-141) - scale, per-token int4 cast, bf16 F.linear against the
-    fake-quant bf16 weight - restated by oracle/dq_oracle.py.  Weights of the sample are built
-    once (untimed), like the reference's offline weight quantisation."""
+    fake-quant bf16 weight.  When the reference's own modules are staged under oracle/_ref
+    (oracle/stage_reference.py) the step runs the reference's unmodified PermLinear
+    (kind "reference"); otherwise the restatement in oracle/dq_oracle.py (kind "port").  Weights
+    of the sample are built once (untimed), like the reference's offline weight quantisation."""
 
     def __init__(self, m_values, seed=0):
         from oracle import dq_oracle as O
+        from oracle import stage_reference as SR
 
         self.O = O
         self.m_values = m_values
+        self.kind = "port"
+        ref = None
+        if SR.available():
+            try:
+                ref = SR.import_reference()
+                self.kind = "reference"
+            except Exception as exc:  # noqa: BLE001 - fall back to the port, say why
+                sys.stderr.write(f"staged reference not importable ({exc}); using the oracle port\n")
         self.linears = []
         for name, K, N in synthetic.LLAMA31_8B_LINEARS:
             w = synthetic.make_w(N, K, seed)
             qw, sw = O.quant_w_int4(w)
             r, c = synthetic.make_scales(N, K, seed)
             wdq = O.dequant_w(qw, sw, r).to(torch.bfloat16)
-            self.linears.append({"name": name, "K": K, "N": N, "a": 1.0 / c, "w": wdq})
+            entry = {"name": name, "K": K, "N": N, "a": 1.0 / c, "w": wdq, "module": None}
+            if ref is not None:
+                lin = torch.nn.Linear(K, N, bias=False).to(torch.bfloat16)
+                lin.weight.data = wdq
+                pl = ref.PermLinear(lin, ref.make_format("rtn_int4", block_size=-1))
+                pl.set_act_scale(1.0 / c)
+                entry["module"] = pl
+            self.linears.append(entry)
         self.x = {(M, K): synthetic.make_x(M, K, seed) for M in m_values for _, K, _ in synthetic.LLAMA31_8B_LINEARS}
 
     def bytes(self):
         return sum(synthetic.int4_gemm_bytes(M, lin["N"], lin["K"]) for M in self.m_values for lin in self.linears)
+
+    def describe(self):
+        if self.kind == "reference":
+            return ("the reference's own PermLinear (activations/perm_linear.py, staged unmodified under oracle/_ref) "
+                    f"on CPU, torch {torch.__version__}")
+        return ("oracle restatement of PermLinear's fake-quant forward (the staged reference is absent), "
+                f"torch {torch.__version__} bf16 F.linear")
 
     def step(self):
         O = self.O
@@ -879,7 +1098,10 @@ class CpuWorkload:
         with torch.no_grad():
             for M in self.m_values:
                 for lin in self.linears:
-                    out = O.perm_linear_fakequant(self.x[(M, lin["K"])], lin["a"], None, lin["w"], True)
+                    if lin["module"] is not None:
+                        out = lin["module"](self.x[(M, lin["K"])])
+                    else:
+                        out = O.perm_linear_fakequant(self.x[(M, lin["K"])], lin["a"], None, lin["w"], False)
         return out
 
 
@@ -896,8 +1118,8 @@ def cpu_baseline(budget_s: float = 15.0):
         if time.perf_counter() - t0 > budget_s or n >= 500:
             break
     dt = (time.perf_counter() - t0) / n
-    return {"value": round(wl.bytes() / dt / 1e9, 3), "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{n} pass(es) of the full step (24 linears), {dt:.2f} s each, torch {torch.__version__} bf16 F.linear on fake-quant weights",
+    return {"value": round(wl.bytes() / dt / 1e9, 3), "unit": UNIT, "cores": cores, "kind": wl.kind,
+            "sample": f"{n} pass(es) of the full step (24 linears), {dt:.3f} s each; {wl.describe()}",
             "ms_per_step": round(dt * 1e3, 1)}
 
 
@@ -920,14 +1142,129 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": round(dt * 1e3, 2),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 fake-quant (fp32 quantiser)",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "reference CPU path (PermLinear fake-quant) restated by the oracle; the reference is Python and is not present on the GPU box"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 fake-quant (fp32 quantiser)", "data": "synthetic",
+        "config": bench_config(args.gpus),
+        "arm": {"path": wl.describe(), "threads": cores,
+                "note": "the whole step on rank 0's host cores (the CPU path does not shard)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": wl.kind,
                          "sample": f"{steps} timed pass(es) of the full step (24 linears)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# The reference's own GPU kernels (Triton) on this GPU: context rows, never on the product path
+# ------------------------------------------------------------------------------------------------
+def run_reference_gpu(args, emit=True):
+    """Times the reference's two Triton kernels on the same GPU with the same CUDA-event harness:
+    `fused_w4a4_gemm` (ablation/real_int4_kernel/fused_w4a4_kernel.py:129-161, group 64, autotuned)
+    and `fused_beta_int4_gemm` (vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:220-262,
+    group 32), imported unmodified from oracle/_ref.  A kernel that cannot be imported, compiled or
+    run reports its error text."""
+    from oracle import stage_reference as SR
+
+    rec = {"suite": "reference_gpu_kernels", "rows": []}
+    if not SR.available():
+        rec["unavailable"] = "oracle/_ref is not staged (run python oracle/stage_reference.py <reference checkout>)"
+        if emit:
+            print(json.dumps(rec), flush=True)
+        return rec
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        SR.import_reference()
+        import fused_dual_scale_kernel as fdk
+        import fused_w4a4_kernel as fwk
+    except Exception as exc:  # noqa: BLE001
+        rec["unavailable"] = f"import failed: {type(exc).__name__}: {exc}"[:300]
+        if emit:
+            print(json.dumps(rec), flush=True)
+        return rec
+    from dualquant_b200 import ops
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    cases = (("gate_up M=16", 16, 4096, 28672), ("o M=16", 16, 4096, 4096), ("config0 M=2048", 2048, 4096, 4096))
+    for label, M, K, N in cases:
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02)
+        x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+        beta = torch.exp(torch.randn(K, generator=g, device=dev) * 0.3).to(torch.bfloat16)
+        row = {"shape": label, "M": M, "K": K, "N": N}
+        # this library on the same shape (quantiser + GEMM), for the ratio
+        codes, sw = ops.quant_w_int4(w.to(torch.bfloat16))
+        pw = ops.pack_w_int4(codes, sw)
+        a32 = beta.float()
+        y = torch.empty(M, N, dtype=torch.float32, device=dev)
+        scratch = torch.empty(max(256, ops.linear_scratch_bytes(M, N, K)), dtype=torch.uint8, device=dev)
+        g_own = _capture(lambda: ops.linear_w4a4_int4(x, a32, None, pw, None, scratch=scratch, out=y), dev)
+        row["dualquant_b200_linear_us"] = round(_time_loop(g_own.replay, 20, 5, dev, lambda: None) / 20 * 1e3, 1)
+        for kname, fn, gs, mod in (("triton_fused_w4a4_gemm_g64", "fused_w4a4_gemm", 64, fwk),
+                                   ("triton_fused_beta_int4_gemm_g32", "fused_beta_int4_gemm", 32, fdk)):
+            try:
+                wp, s1 = fdk.pack_int4_weights(w, gs)
+                call = getattr(mod, fn)
+                if fn == "fused_beta_int4_gemm":
+                    run = lambda: call(x, beta, wp, s1, group_size=gs)  # noqa: E731
+                else:
+                    run = lambda: call(x, beta, wp, s1, group_size=gs)  # noqa: E731
+                run()  # compile / autotune
+                torch.cuda.synchronize()
+                ms = _time_loop(run, 10, 3, dev, lambda: None) / 10
+                row[kname + "_us"] = round(ms * 1e3, 1)
+                row[kname + "_TOPS"] = round(2.0 * M * N * K / ms / 1e9, 1)
+            except Exception as exc:  # noqa: BLE001
+                row[kname + "_unavailable"] = f"{type(exc).__name__}: {exc}"[:200]
+            torch.cuda.empty_cache()
+        rec["rows"].append(row)
+        del w, x, pw
+    if emit:
+        print(json.dumps(rec), flush=True)
+    return rec
+
+
+# ------------------------------------------------------------------------------------------------
+# MMA-only tensor-core peaks (tcgen05 issue loops with resident operands)
+# ------------------------------------------------------------------------------------------------
+_MMA_PEAKS = {}
+
+
+def _mma_peaks(args):
+    """Measured once per process: {"int8_TOPS", "mxfp4_TFLOPS", "nvfp4_TFLOPS"} or None."""
+    if "v" not in _MMA_PEAKS:
+        try:
+            _MMA_PEAKS["v"] = run_peak_suite(args, emit=False)
+        except Exception as exc:  # noqa: BLE001
+            sys.stderr.write(f"MMA-only peak measurement failed: {exc}\n")
+            _MMA_PEAKS["v"] = None
+    return _MMA_PEAKS["v"]
+
+
+def run_peak_suite(args, emit=True):
+    """tcgen05.mma issue loops on operands that never leave shared / tensor memory: the rate the
+    tensor pipe sustains with nothing else going on, for kind::i8 (128x256x32 per instruction)
+    and kind::mxf4nvf4.block_scale (128x256x64, E8M0 block 32 and E4M3 block 16)."""
+    from dualquant_b200 import _lib, ops
+
+    if "v" in _MMA_PEAKS and _MMA_PEAKS["v"] is not None:
+        rec = _MMA_PEAKS["v"]
+    else:
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        rec = {"suite": "peaks_mma_only"}
+        for key, kind in (("int8_TOPS", 0), ("mxfp4_TFLOPS", 1), ("nvfp4_TFLOPS", 2)):
+            best = 0.0
+            for _ in range(3):
+                best = max(best, ops.mma_peak(kind, iters=4096))
+            rec[key] = round(best, 1)
+        rec["how"] = ("one CTA per SM, one thread issuing back-to-back tcgen05.mma (UMMA 128x256, K = 32 bytes "
+                      "per instruction for int8, 64 elements for FP4) on shared-memory operands that are never "
+                      "reloaded; CUDA events; best of 3")
+        _lib.device_status(0)
+        _MMA_PEAKS["v"] = rec
+    if emit:
+        print(json.dumps(rec), flush=True)
+    return rec
 
 
 def main():
@@ -939,7 +1276,6 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
-    ap.add_argument("--detail", action="store_true", help="add per-(linear, M) GEMM GB/s")
     ap.add_argument("--case", default=None, help="NAME:M[:TN:SPLIT] - run one (linear, M) GEMM alone")
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--layers", type=int, default=32)
@@ -948,9 +1284,21 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=128)
     ap.add_argument("--fused-allreduce", action="store_true",
                     help="decoder suite, N>1: sum row-parallel partial outputs inside the decode GEMM over peer memory")
-    ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp", "decoder"], help="extra measurement suites")
+    ap.add_argument("--tune", action="append", default=[], metavar="NAME=VALUE",
+                    help="launch-shape override passed to dq_set_tuning (measurement sweeps)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the decode sweep (skip the prefill / MLP / FP4 / decoder sub-records)")
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-(linear, M) GEMM table")
+    ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp", "decoder", "peaks", "reference_gpu"],
+                    help="one measurement suite alone")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    if args.tune:
+        from dualquant_b200 import _lib as _tl
+
+        for item in args.tune:
+            name, _, val = item.partition("=")
+            _tl.set_tuning(name, int(val))
     if args.suite == "prefill":
         run_prefill_suite(args)
     elif args.suite == "fp4":
@@ -959,6 +1307,10 @@ def main():
         run_mlp_suite(args)
     elif args.suite == "decoder":
         run_decoder_suite(args)
+    elif args.suite == "peaks":
+        run_peak_suite(args)
+    elif args.suite == "reference_gpu":
+        run_reference_gpu(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

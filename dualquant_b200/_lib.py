@@ -56,6 +56,7 @@ SIGNATURES = {
     "dq_device_status": (_i, [_i]),
     "dq_abi_version": (_i, []),
     "dq_set_tuning": (_i, [_c.c_char_p, _i]),
+    "dq_mma_peak_probe": (_i, [_i, _i, _c.POINTER(_c.c_double), _vp]),
     "dq_packed_w_bytes": (_sz, [_i, _i]),
     "dq_pack_w_int4": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "dq_unpack_w_int4": (_i, [_vp, _i, _i, _vp, _vp]),

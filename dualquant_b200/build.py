@@ -24,6 +24,7 @@ SOURCES = [
     "gemv_w4a4_int4_fused.cu",
     "gemm_fp4.cu",
     "linear_w4a4.cu",
+    "mma_peak.cu",
 ]
 
 NVCC_FLAGS = [

@@ -81,7 +81,9 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 // Tuning knobs (dq_set_tuning): launch-shape overrides for measurement sweeps and tests.  0 means
-// "the library's own choice" for every knob except DQ_TUNE_LINEAR_FUSED (1 = on).
+// "the library's own choice" for every knob except DQ_TUNE_LINEAR_FUSED (1 = on, 0 = off, the default:
+// measured on B200 the one-launch kernel is not faster than quantiser + GEMM chained by programmatic
+// dependent launch, see the note at the top of gemv_w4a4_int4_fused.cu).
 enum {
   DQ_TUNE_LINEAR_FUSED = 0,     // dq_linear_w4a4_int4 may take the one-launch decode kernel
   DQ_TUNE_FUSED_STAGES = 1,     // ring depth of the one-launch decode kernel
@@ -98,6 +100,7 @@ int init_gemm_int4_tm_kernels();
 int init_gemm_fp4_kernels();
 int init_act_quant_kernels();
 int init_gemv_fused_kernels();
+int init_mma_peak_kernels();
 
 // One-launch decode linear (quantiser inside the GEMM kernel), defined in gemv_w4a4_int4_fused.cu.
 bool gemv_fused_covers(int M, int N, int K, const DeviceState* st);

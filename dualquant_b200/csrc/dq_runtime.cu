@@ -40,7 +40,7 @@ int set_error(int code, const char* fmt, ...) {
 
 EncodeTiledFn encode_tiled_fn() { return g_encode; }
 
-static int g_tuning[DQ_TUNE_COUNT] = {1, 0, 0, 1};
+static int g_tuning[DQ_TUNE_COUNT] = {0, 0, 0, 1};
 int tuning(int key) { return (key >= 0 && key < DQ_TUNE_COUNT) ? g_tuning[key] : 0; }
 
 int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
@@ -163,6 +163,8 @@ extern "C" int dq_init(int device) {
   rc = init_act_quant_kernels();
   if (rc != DQ_OK) return rc;
   rc = init_gemv_fused_kernels();
+  if (rc != DQ_OK) return rc;
+  rc = init_mma_peak_kernels();
   if (rc != DQ_OK) return rc;
   DQ_CHECK_CUDA(cudaDeviceSynchronize());
   st->ready = true;

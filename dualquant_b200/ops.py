@@ -415,3 +415,22 @@ def linear_w4a4_fp4(x: torch.Tensor, a: Optional[torch.Tensor], pw: PackedFp4Wei
     """Quantise activations (per-token second-level scale for NVFP4) and run the FP4 GEMM."""
     codes, sf_atoms, row_scale = quant_fp4(x, pw.fmt, a, None, atoms=True)
     return gemm_w4a4_fp4(codes, sf_atoms, row_scale, pw, r, out_dtype)
+
+
+def mma_peak(kind: int, iters: int = 4096, device=None) -> float:
+    """Tensor-pipe ceiling probe (dq_mma_peak_probe): tera-operations per second of a pure
+    tcgen05.mma issue loop on every SM.  kind 0 = int8, 1 = MXFP4, 2 = NVFP4."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    _lib.ensure_init(idx)
+    lib = _lib.load()
+    n_ops = ctypes.c_double(0.0)
+    stream = _stream(dev)
+    _lib.check(lib.dq_mma_peak_probe(kind, 64, None, stream), "dq_mma_peak_probe")  # warm-up
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    _lib.check(lib.dq_mma_peak_probe(kind, iters, ctypes.byref(n_ops), stream), "dq_mma_peak_probe")
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return n_ops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12

@@ -85,10 +85,19 @@ DQ_API int dq_abi_version(void);
 
 /* Launch-shape overrides for measurement sweeps and tests (no counterpart in the reference, whose
  * Triton kernels autotune instead: vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:26-53).
- * name (host string): "linear_fused" (1 = dq_linear_w4a4_int4 may run decode batches as one
- * launch, 0 = always quantiser + GEMM), "fused_stages", "fused_split", "fused_extra_cta"
+ * name (host string): "linear_fused" (1 = dq_linear_w4a4_int4 runs decode batches, M <= 16, as one
+ * launch that quantises inside the GEMM kernel; 0 = quantiser + GEMM, the default), "fused_stages", "fused_split", "fused_extra_cta"
  * (0 = the library's own choice).  Process-wide, not thread-safe against concurrent launches. */
 DQ_API int dq_set_tuning(const char* name, int value);
+
+/* Tensor-core ceiling probe: launches, on every SM, a loop of `iters` x 4 tcgen05.mma instructions
+ * (UMMA 128 x 256, 32 bytes of K each) on operands resident in shared / tensor memory; kind 0 =
+ * kind::i8, 1 = kind::mxf4nvf4 with E8M0 block-32 scales, 2 = with E4M3 block-16 scales.  *ops_out
+ * (host, may be null) receives the arithmetic operations the launch performs (2 per multiply-add);
+ * the caller times the launch with events.  Measurement helper in the spirit of the reference's
+ * roofline estimate (ablation/real_int4_kernel/verification/ceiling_analysis.py:55-63), which
+ * measures a cuBLAS bf16 GEMM and quotes datasheet figures for the integer rates. */
+DQ_API int dq_mma_peak_probe(int kind, int iters, double* ops_out, void* stream);
 
 /* ---- weights ----------------------------------------------------------------------------- */
 

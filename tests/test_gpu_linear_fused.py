@@ -23,9 +23,13 @@ def _two_launch(x, a, pw, r, scale_fp16, out_dtype):
 
 
 @pytest.fixture(autouse=True)
-def _reset_tuning():
+def _fused_on():
+    """The one-launch kernel is opt-in (dq_set_tuning("linear_fused", 1)); switch it on for these
+    tests and restore the library defaults afterwards."""
+    _lib.ensure_init(0)
+    _lib.set_tuning("linear_fused", 1)
     yield
-    for k, v in (("linear_fused", 1), ("fused_stages", 0), ("fused_split", 0), ("fused_extra_cta", 1)):
+    for k, v in (("linear_fused", 0), ("fused_stages", 0), ("fused_split", 0), ("fused_extra_cta", 1)):
         _lib.set_tuning(k, v)
 
 
