@@ -66,6 +66,7 @@ SIGNATURES = {
     "dq_quant_act_int4_rmsnorm": (_i, [_vp, _i64, _vp, ctypes.c_float, _vp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_quant_act_int4_gated": (_i, [_vp, _vp, _i64, _vp, _hp, _i, _i, _vp, _vp, _i, _vp]),
     "dq_fakequant_act_int4": (_i, [_vp, _i, _i64, _vp, _hp, _i, _i, _vp, _i, _vp]),
+    "dq_fakequant_act_int4_bf16": (_i, [_vp, _i64, _i, _i, _vp, _vp]),
     "dq_hadamard_f32": (_i, [_vp, _vp, _i, _i, _hp, _vp]),
     "dq_quant_fp4": (_i, [_vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "dq_quant_fp4_atoms": (_i, [_vp, _i, _i64, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
@@ -77,6 +78,7 @@ SIGNATURES = {
     "dq_gemm_w4a4_fp4_tiled": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "dq_gemm_w4a4_int4_workspace_bytes": (_sz, [_i, _i, _i]),
     "dq_gemm_w4a4_int4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "dq_gemm_w4a4_int4_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),
     "dq_gemm_w4a4_int4_ar": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
     "dq_gemm_w4a4_int4_acc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),

@@ -205,7 +205,12 @@ class PermLinear(nn.Module):
         else:
             out = self.layer(self._quantise_act(x))
         if self.quantize_bmm_input:
-            out = self.act_fmt.cast(out.to(torch.float32)).to(self.dtype)
+            if (out.dtype == torch.bfloat16 and getattr(self.act_fmt, "name", None) == "rtn_int4"
+                    and self.act_fmt.block_size == -1 and out.shape[-1] % 8 == 0):
+                # one pass, bf16 in and out: same values as cast(out.float()).to(bf16)
+                out = ops.fakequant_act_int4_bf16(out.reshape(-1, out.shape[-1])).reshape(out.shape)
+            else:
+                out = self.act_fmt.cast(out.to(torch.float32)).to(self.dtype)
         return out
 
 

@@ -18,7 +18,16 @@
 
 namespace dq {
 
-enum { MODE_CODES = 0, MODE_FAKE = 1, MODE_RAW = 2 };
+enum { MODE_CODES = 0, MODE_FAKE = 1, MODE_RAW = 2, MODE_FAKE_BF16 = 3 };
+
+// Row `row` of the de-quantised output: fp32 elements, or bf16 elements for MODE_FAKE_BF16 (the
+// pointer type stays float*; emit8 casts it back).
+__device__ __forceinline__ float* out_row_ptr(float* out, int64_t row, int K, int mode) {
+  if (out == nullptr) return nullptr;
+  if (mode == MODE_FAKE_BF16)
+    return reinterpret_cast<float*>(reinterpret_cast<__nv_bfloat16*>(out) + row * K);
+  return out + row * K;
+}
 
 __device__ __forceinline__ float block_max(float v, float* red, int nwarps) {
 #pragma unroll
@@ -119,6 +128,16 @@ __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t*
     const uint32_t lo = pack_codes4(q[0], q[1], q[2], q[3]);
     const uint32_t hi = pack_codes4(q[4], q[5], q[6], q[7]);
     *reinterpret_cast<uint2*>(codes_row + idx) = make_uint2(lo, hi);
+  } else if (mode == MODE_FAKE_BF16) {
+    float o[8];
+    quant_codes8(v, s, inv_s, o);
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(o[2 * e], s), __fmul_rn(o[2 * e + 1], s));
+      w[e] = *reinterpret_cast<const uint32_t*>(&pr);
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out_row) + idx) = make_uint4(w[0], w[1], w[2], w[3]);
   } else {
     float o[8];
     if (mode == MODE_FAKE) {
@@ -225,7 +244,7 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
   const float s = token_scale(amax, scale_fp16);
   if (threadIdx.x == 0 && sx != nullptr) sx[row] = s;
   int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(row) * K : nullptr;
-  float* orow = (out != nullptr) ? out + static_cast<int64_t>(row) * K : nullptr;
+  float* orow = out_row_ptr(out, row, K, mode);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = (i * THREADS + threadIdx.x) * 8;
@@ -343,7 +362,7 @@ act_quant_had_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_
     if (threadIdx.x == 0 && sx != nullptr) sx[r] = s;
   }
   int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(r) * K : nullptr;
-  float* orow = (out != nullptr) ? out + static_cast<int64_t>(r) * K : nullptr;
+  float* orow = out_row_ptr(out, r, K, mode);
   for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
     float v[8];
 #pragma unroll
@@ -501,7 +520,7 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
     __syncthreads();
   }
   int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(rr) * K : nullptr;
-  float* orow = (out != nullptr) ? out + static_cast<int64_t>(rr) * K : nullptr;
+  float* orow = out_row_ptr(out, rr, K, mode);
   for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
     float v[8];
 #pragma unroll
@@ -756,6 +775,16 @@ extern "C" int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, c
                       MODE_FAKE, scale_fp16, s);
   return launch_act(static_cast<const __nv_bfloat16*>(x), ldx, a, had, M, K, nullptr, nullptr, out,
                     MODE_FAKE, scale_fp16, s);
+}
+
+extern "C" int dq_fakequant_act_int4_bf16(const void* x_bf16, int64_t ldx, int M, int K,
+                                          void* out_bf16, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  DQ_REQUIRE(out_bf16 != nullptr, DQ_ERR_NULL, "out is null");
+  return launch_act(static_cast<const __nv_bfloat16*>(x_bf16), ldx, nullptr, nullptr, M, K, nullptr,
+                    nullptr, static_cast<float*>(out_bf16), MODE_FAKE_BF16, 0,
+                    static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int dq_hadamard_f32(const float* x, float* out, int M, int K,

@@ -106,16 +106,17 @@ int init_mma_peak_kernels();
 bool gemv_fused_covers(int M, int N, int K, const DeviceState* st);
 int launch_gemv_fused(const void* x_bf16, int64_t ldx, const float* a, const uint8_t* w_packed,
                       const float* r, int M, int N, int K, void* y, int y_dtype, int scale_fp16,
-                      cudaStream_t stream, DeviceState* st);
+                      cudaStream_t stream, DeviceState* st, const void* residual = nullptr);
 
 // Decode-batch (register-path) variant of the int4 linear, defined in gemv_w4a4_int4.cu.
 int launch_gemm_int4_tm(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                         const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
-                        int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st);
+                        int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st,
+                        const void* residual = nullptr);
 int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count);
 int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                      const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
                      int tok, int split, cudaStream_t stream, DeviceState* st,
-                     const dq_allreduce_ctx* ctx = nullptr);
+                     const dq_allreduce_ctx* ctx = nullptr, const void* residual = nullptr);
 
 }  // namespace dq

@@ -283,6 +283,28 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 // ---------------------------------------------------------------------------------------
+// output element with the optional fused residual
+// ---------------------------------------------------------------------------------------
+// Stores Y[idx] = val, or, with a residual matrix of Y's own element type, Y[idx] = residual[idx]
+// + the value a plain store would have written (for bf16 outputs the linear's result is rounded
+// to bf16 first and the sum rounded again: what a bf16 "x = x + linear(h)" computes).
+__device__ __forceinline__ void store_y(void* y, const void* residual, int y_bf16, size_t idx, float val) {
+  if (y_bf16) {
+    unsigned short bits;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(bits) : "f"(val));
+    if (residual != nullptr) {
+      const float lin = __uint_as_float(static_cast<uint32_t>(bits) << 16);
+      const float res = __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(residual)[idx]) << 16);
+      asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(bits) : "f"(lin + res));
+    }
+    reinterpret_cast<unsigned short*>(y)[idx] = bits;
+  } else {
+    if (residual != nullptr) val += reinterpret_cast<const float*>(residual)[idx];
+    reinterpret_cast<float*>(y)[idx] = val;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // programmatic dependent launch
 // ---------------------------------------------------------------------------------------
 // Lets the next kernel of the stream (if it was launched with the programmatic-serialization

@@ -145,7 +145,8 @@ __global__ void __launch_bounds__(Cfg<TN>::kThreads, Cfg<TN>::kMinCtas)
 gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
                       const __half* __restrict__ sw_t, const float* __restrict__ r,
-                      const float* __restrict__ sx, void* __restrict__ y, int y_bf16, int M, int N, int K, int groups_per_split,
+                      const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
+                      const void* __restrict__ residual, int M, int N, int K, int groups_per_split,
                       int split_k, int w_stream_once, int* status DQ_TRACE_PARAM) {
   using C = Cfg<TN>;
   // The 128-byte swizzle of the UMMA operands needs the buffers on 1 KB boundaries.  The kernel has
@@ -387,7 +388,14 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
           const int m0 = t0 + h * C::CPW;
           const int cnt = (M - m0 < C::CPW) ? (M - m0) : C::CPW;  // tokens of this slice that exist
           const float* sxp = sx + m0;
-          if (y_bf16) {
+          if (residual != nullptr) {
+            size_t idx = static_cast<size_t>(m0) * N + n;
+#pragma unroll
+            for (int j = 0; j < C::CPW; ++j) {
+              if (j < cnt) store_y(y, residual, y_bf16, idx, run[j] * (rn * __ldg(sxp + j)));
+              idx += N;
+            }
+          } else if (y_bf16) {
             __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(y) + static_cast<size_t>(m0) * N + n;
 #pragma unroll
             for (int j = 0; j < C::CPW; ++j) {
@@ -505,12 +513,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
             const int n = n0 + c4 * 4 + u;
             if (n < N) {
               const float rn = (r != nullptr) ? r[n] : 1.f;
-              const float val = vals[u] * (rn * sm);
-              if (y_bf16)
-                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                    __float2bfloat16_rn(val);
-              else
-                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+              store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, vals[u] * (rn * sm));
             }
           }
         }
@@ -575,7 +578,7 @@ static int pick_split(int tiles, int total_groups, int tn, int sm_count) {
 template <int TN>
 static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed, const __half* sw_t,
                   const float* r, int M, int N, int K, void* y, int y_dtype, int split,
-                  cudaStream_t stream, DeviceState* st) {
+                  cudaStream_t stream, DeviceState* st, const void* residual) {
   CUtensorMap tm_x;
   int rc = make_tmap_x_groups(&tm_x, codes, K, M, TN, Cfg<TN>::XC);
   if (rc != DQ_OK) return rc;
@@ -607,7 +610,7 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   cfg.numAttrs = 2;
   const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN>, w_packed, tm_x, sw_t, r, sx,
-                                     y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, gps,
+                                     y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, M, N, K, gps,
                                      split, w_stream_once, st->status_dev DQ_TRACE_ARG);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_w4a4_int4 launch failed (TN=%d split=%d): %s", TN, split,
@@ -637,11 +640,10 @@ extern "C" __attribute__((visibility("default"))) void dq_debug_set_trace(long l
 
 extern "C" size_t dq_gemm_w4a4_int4_workspace_bytes(int, int, int) { return 0; }
 
-extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const uint8_t* w_packed,
-                                    const void* sw_t, const float* r, int M, int N, int K, int G,
-                                    void* y, int y_dtype, void* /*workspace*/,
-                                    size_t /*workspace_bytes*/, void* stream, int token_tile,
-                                    int split_k) {
+static int gemm_int4_dispatch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                              const void* sw_t, const float* r, const void* residual, int M, int N,
+                              int K, int G, void* y, int y_dtype, void* stream, int token_tile,
+                              int split_k) {
   DeviceState* st = current_state();
   if (st == nullptr) return DQ_ERR_NOT_INIT;
   if (M == 0) return DQ_OK;
@@ -666,7 +668,7 @@ extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const 
     DQ_REQUIRE(split <= tok && split <= total_groups, DQ_ERR_SHAPE,
                "split_k=%d too large for %d tokens / %d groups", split, tok, total_groups);
     return launch_gemv_int4(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, tok, split,
-                            static_cast<cudaStream_t>(stream), st);
+                            static_cast<cudaStream_t>(stream), st, nullptr, residual);
   }
   // 1000 + tile / 2000 + tile force the shared-memory-operand / tensor-memory-operand kernel
   int forced = 0;
@@ -689,13 +691,32 @@ extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const 
   // shared memory, four accumulators and two issuing warps, measured 10-15 % faster there.
   const bool use_tm = forced ? (forced == 2) : (tn <= 64);
   if (use_tm)
-    return launch_gemm_int4_tm(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, nullptr, tn, split, s, st);
+    return launch_gemm_int4_tm(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, nullptr, tn, split, s, st,
+                               residual);
   switch (tn) {
-    case 16: return launch<16>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
-    case 32: return launch<32>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
-    case 64: return launch<64>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
-    default: return launch<128>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st);
+    case 16: return launch<16>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st, residual);
+    case 32: return launch<32>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st, residual);
+    case 64: return launch<64>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st, residual);
+    default: return launch<128>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st, residual);
   }
+}
+
+extern "C" int dq_gemm_w4a4_int4_ex(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                    const void* sw_t, const float* r, int M, int N, int K, int G,
+                                    void* y, int y_dtype, void* /*workspace*/,
+                                    size_t /*workspace_bytes*/, void* stream, int token_tile,
+                                    int split_k) {
+  return gemm_int4_dispatch(codes, sx, w_packed, sw_t, r, nullptr, M, N, K, G, y, y_dtype, stream,
+                            token_tile, split_k);
+}
+
+extern "C" int dq_gemm_w4a4_int4_residual(const int8_t* codes, const float* sx,
+                                          const uint8_t* w_packed, const void* sw_t, const float* r,
+                                          const void* residual, int M, int N, int K, int G, void* y,
+                                          int y_dtype, void* stream) {
+  DQ_REQUIRE(residual != nullptr, DQ_ERR_NULL, "null residual");
+  DQ_REQUIRE(aligned(residual, y_dtype == DQ_DTYPE_BF16 ? 2 : 4), DQ_ERR_ALIGN, "misaligned residual");
+  return gemm_int4_dispatch(codes, sx, w_packed, sw_t, r, residual, M, N, K, G, y, y_dtype, stream, 0, 0);
 }
 
 extern "C" int dq_gemm_w4a4_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,

@@ -137,6 +137,7 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
                          const __grid_constant__ CUtensorMap tm_x,
                          const __half* __restrict__ sw_t, const float* __restrict__ r,
                          const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
+                         const void* __restrict__ residual,
                          int32_t* __restrict__ acc_dump, int M, int N, int K,
                          int groups_per_split, int split_k, int w_stream_once, int* status) {
   using C = Cfg<TN>;
@@ -373,7 +374,14 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
           const int m0 = t0 + h * C::CPW;
           const int cnt = (M - m0 < C::CPW) ? (M - m0) : C::CPW;  // tokens of this slice that exist
           const float* sxp = sx + m0;
-          if (y_bf16) {
+          if (residual != nullptr) {
+            size_t idx = static_cast<size_t>(m0) * N + n;
+#pragma unroll
+            for (int j = 0; j < C::CPW; ++j) {
+              if (j < cnt) store_y(y, residual, y_bf16, idx, run[j] * (rn * __ldg(sxp + j)));
+              idx += N;
+            }
+          } else if (y_bf16) {
             __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(y) + static_cast<size_t>(m0) * N + n;
 #pragma unroll
             for (int j = 0; j < C::CPW; ++j) {
@@ -508,12 +516,7 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
             const int n = n0 + c4 * 4 + u;
             if (n < N) {
               const float rn = (r != nullptr) ? r[n] : 1.f;
-              const float val = vals[u] * (rn * sm);
-              if (y_bf16)
-                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                    __float2bfloat16_rn(val);
-              else
-                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+              store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, vals[u] * (rn * sm));
             }
           }
         }
@@ -548,7 +551,7 @@ static int set_attr() {
 template <int TN, bool DUMP>
 static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed, const __half* sw_t,
                   const float* r, int M, int N, int K, void* y, int y_dtype, int32_t* acc_dump,
-                  int split, cudaStream_t stream, DeviceState* st) {
+                  int split, cudaStream_t stream, DeviceState* st, const void* residual) {
   CUtensorMap tm_x;
   int rc = make_tmap_x_groups(&tm_x, codes, K, M, TN, kStepGroups);
   if (rc != DQ_OK) return rc;
@@ -571,7 +574,7 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   cfg.numAttrs = 2;
   const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_tm_kernel<TN, DUMP>, w_packed, tm_x, sw_t,
-                                     r, sx, y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, acc_dump, M, N, K,
+                                     r, sx, y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, acc_dump, M, N, K,
                                      gps, split, w_stream_once, st->status_dev);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_w4a4_int4 (tm) launch failed (TN=%d split=%d): %s", TN,
@@ -595,18 +598,18 @@ int init_gemm_int4_tm_kernels() {
 // tn: 16 / 32 / 64 / 128; acc_dump != nullptr selects the accumulator-dump variant (tn 16 or 128).
 int launch_gemm_int4_tm(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                         const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
-                        int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st) {
+                        int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st, const void* residual) {
   const __half* swp = static_cast<const __half*>(sw_t);
   if (acc_dump != nullptr) {
     if (tn == 16)
-      return tm::launch<16, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st);
-    return tm::launch<128, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st);
+      return tm::launch<16, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st, residual);
+    return tm::launch<128, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st, residual);
   }
   switch (tn) {
-    case 16: return tm::launch<16, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
-    case 32: return tm::launch<32, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
-    case 64: return tm::launch<64, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
-    default: return tm::launch<128, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st);
+    case 16: return tm::launch<16, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    case 32: return tm::launch<32, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    case 64: return tm::launch<64, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    default: return tm::launch<128, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
   }
 }
 

@@ -105,8 +105,8 @@ __global__ void __launch_bounds__(kVThreads, VCfg<NT>::kMinCtas)
 gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
                       const float* __restrict__ r, const float* __restrict__ sx,
-                      void* __restrict__ y, int y_bf16, int M, int N, int K, int groups_per_split,
-                      int split_k, int stages, int* status, const ArDev ar) {
+                      void* __restrict__ y, int y_bf16, const void* __restrict__ residual, int M, int N,
+                      int K, int groups_per_split, int split_k, int stages, int* status, const ArDev ar) {
   using C = VCfg<NT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -300,12 +300,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
             for (int e = 0; e < 2; ++e) {
               const int m = nb * 8 + 2 * t + e;
               if (m < M) {
-                const float val = run[nb][2 * hrow + e] * (rn * sx[m]);
-                if (y_bf16)
-                  reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                      __float2bfloat16_rn(val);
-                else
-                  reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+                store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, run[nb][2 * hrow + e] * (rn * sx[m]));
               }
             }
         }
@@ -366,13 +361,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               const int n = n0 + c4 * 4 + u;
-              if (n < N) {
-                if (y_bf16)
-                  reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                      __float2bfloat16_rn(vals[u]);
-                else
-                  reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = vals[u];
-              }
+              if (n < N) store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, vals[u]);
             }
           }
         }
@@ -411,13 +400,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
               }
               const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                if (y_bf16)
-                  reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + nb + u] =
-                      __float2bfloat16_rn(vals[u]);
-                else
-                  reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + nb + u] = vals[u];
-              }
+              for (int u = 0; u < 4; ++u) store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + nb + u, vals[u]);
             }
           }
         }
@@ -463,7 +446,7 @@ template <int NT>
 static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                          const __half* sw_t, const float* r, int M, int N, int K, void* y,
                          int y_dtype, int split, cudaStream_t stream, DeviceState* st,
-                         const ArDev& ar) {
+                         const ArDev& ar, const void* residual) {
   using C = VCfg<NT>;
   CUtensorMap tm_x;
   int rc = make_tmap_x_groups(&tm_x, codes, K, M, C::kXRows, kVGS);
@@ -498,7 +481,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT>, w_packed, tm_x, r, sx, y,
-                                     y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, gps, split,
+                                     y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, M, N, K, gps, split,
                                      stages, st->status_dev, ar);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemv_w4a4_int4 launch failed (tokens=%d split=%d): %s", C::TOK,
@@ -510,7 +493,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
 int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                      const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
                      int tok, int split, cudaStream_t stream, DeviceState* st,
-                     const dq_allreduce_ctx* ctx) {
+                     const dq_allreduce_ctx* ctx, const void* residual) {
   const __half* swp = static_cast<const __half*>(sw_t);
   ArDev ar = {};
   ar.world = 1;
@@ -537,9 +520,9 @@ int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_pack
   }
   int rc;
   switch (tok) {
-    case 8: rc = launch_gemv_t<1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar); break;
-    case 16: rc = launch_gemv_t<2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar); break;
-    case 32: rc = launch_gemv_t<4>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar); break;
+    case 8: rc = launch_gemv_t<1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual); break;
+    case 16: rc = launch_gemv_t<2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual); break;
+    case 32: rc = launch_gemv_t<4>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual); break;
     default: return set_error(DQ_ERR_SHAPE, "register-path token capacity must be 8/16/32 (got %d)", tok);
   }
   if (rc == DQ_OK && ar.world > 1) {

@@ -118,8 +118,9 @@ template <int NT, int U>
 __global__ void __launch_bounds__(kThreads, (U <= 2) ? 3 : 2)
 gemv_fused_kernel(const uint8_t* __restrict__ w_packed, const __nv_bfloat16* __restrict__ x,
                   int64_t ldx, const float* __restrict__ a, const float* __restrict__ r,
-                  void* __restrict__ y, int y_bf16, int M, int N, int K, int groups_per_split,
-                  int split_k, int cx, int stages, int scale_fp16, int* status) {
+                  void* __restrict__ y, int y_bf16, const void* __restrict__ residual, int M, int N,
+                  int K, int groups_per_split, int split_k, int cx, int stages, int scale_fp16,
+                  int* status) {
   using C = FCfg<NT>;
   constexpr int TOK = C::TOK;
   constexpr int TPR = C::kThreadsPerRow;
@@ -359,12 +360,7 @@ gemv_fused_kernel(const uint8_t* __restrict__ w_packed, const __nv_bfloat16* __r
               for (int e = 0; e < 2; ++e) {
                 const int m = nb * 8 + 2 * t + e;
                 if (m < M) {
-                  const float val = run[nb][2 * hrow + e] * (rn * sxs[m]);
-                  if (y_bf16)
-                    reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                        __float2bfloat16_rn(val);
-                  else
-                    reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+                  store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, run[nb][2 * hrow + e] * (rn * sxs[m]));
                 }
               }
           }
@@ -409,12 +405,7 @@ gemv_fused_kernel(const uint8_t* __restrict__ w_packed, const __nv_bfloat16* __r
             const int n = n0 + c4 * 4 + u;
             if (n < N) {
               const float rn = (r != nullptr) ? r[n] : 1.f;
-              const float val = vals[u] * (rn * sm);
-              if (y_bf16)
-                reinterpret_cast<__nv_bfloat16*>(y)[static_cast<size_t>(m) * N + n] =
-                    __float2bfloat16_rn(val);
-              else
-                reinterpret_cast<float*>(y)[static_cast<size_t>(m) * N + n] = val;
+              store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, vals[u] * (rn * sm));
             }
           }
         }
@@ -513,7 +504,8 @@ bool gemv_fused_covers(int M, int N, int K, const DeviceState* st) {
 template <int NT, int U>
 static int launch_fused_t(const FusedPlan& p, const void* x, int64_t ldx, const float* a,
                           const uint8_t* w_packed, const float* r, int M, int N, int K, void* y,
-                          int y_dtype, int scale_fp16, cudaStream_t stream, DeviceState* st) {
+                          int y_dtype, int scale_fp16, cudaStream_t stream, DeviceState* st,
+                          const void* residual) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.tiles_x, 1, p.split);
   cfg.blockDim = dim3(fused::kThreads, 1, 1);
@@ -530,7 +522,7 @@ static int launch_fused_t(const FusedPlan& p, const void* x, int64_t ldx, const 
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, fused::gemv_fused_kernel<NT, U>, w_packed,
                                      static_cast<const __nv_bfloat16*>(x), ldx, a, r, y,
-                                     y_dtype == DQ_DTYPE_BF16 ? 1 : 0, M, N, K, p.gps, p.split, p.cx,
+                                     y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, M, N, K, p.gps, p.split, p.cx,
                                      p.stages, scale_fp16, st->status_dev);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemv_fused launch failed (tokens=%d split=%d cx=%d stages=%d): %s",
@@ -540,7 +532,7 @@ static int launch_fused_t(const FusedPlan& p, const void* x, int64_t ldx, const 
 
 int launch_gemv_fused(const void* x_bf16, int64_t ldx, const float* a, const uint8_t* w_packed,
                       const float* r, int M, int N, int K, void* y, int y_dtype, int scale_fp16,
-                      cudaStream_t stream, DeviceState* st) {
+                      cudaStream_t stream, DeviceState* st, const void* residual) {
   const FusedPlan p = plan_fused(M, N, K, st->sm_count);
   DQ_REQUIRE(p.ok, DQ_ERR_UNSUPPORTED, "one-launch decode linear does not cover M=%d N=%d K=%d", M, N, K);
   DQ_REQUIRE(x_bf16 != nullptr && w_packed != nullptr && y != nullptr, DQ_ERR_NULL, "null x / w_packed / y");
@@ -551,7 +543,7 @@ int launch_gemv_fused(const void* x_bf16, int64_t ldx, const float* a, const uin
 #define DQ_FUSED_CASE(NTV, UV)                                                                     \
   if (p.nt == NTV && p.units == UV)                                                                \
     return launch_fused_t<NTV, UV>(p, x_bf16, ldx, a, w_packed, r, M, N, K, y, y_dtype, scale_fp16, \
-                                   stream, st)
+                                   stream, st, residual)
   DQ_FUSED_CASE(1, 1);
   DQ_FUSED_CASE(1, 2);
   DQ_FUSED_CASE(1, 4);

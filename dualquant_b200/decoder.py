@@ -51,10 +51,13 @@ LLAMA31_8B = DecoderConfig()
 class W4A4Linear:
     """Packed int4 weight + DualQuant scales (+ optional online Hadamard) of one linear shard."""
 
-    def __init__(self, N: int, K: int, device, gen: torch.Generator, had: Optional[ops.Hadamard] = None):
+    def __init__(self, N: int, K: int, device, gen: torch.Generator, had: Optional[ops.Hadamard] = None,
+                 keep_codes: bool = False):
         w = (torch.randn(N, K, generator=gen, device=device) * 0.02).to(torch.bfloat16)
         codes, sw = ops.quant_w_int4(w)
         self.pw = ops.pack_w_int4(codes, sw)
+        # checkers rebuild the layer on the CPU from the unpacked codes and group scales
+        self.codes, self.sw = (codes, sw) if keep_codes else (None, None)
         del w, codes, sw
         self.r = torch.exp(torch.randn(N, generator=gen, device=device) * 0.3).half().float()
         c = torch.exp(torch.randn(K, generator=gen, device=device) * 0.3).half().float()
@@ -77,19 +80,24 @@ class W4A4Linear:
         codes, sx = ops.quant_act_int4_rmsnorm(x, norm_weight, eps, self.a, False)
         return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype)
 
-    def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16, ar=None) -> torch.Tensor:
-        """ar: an ops.AllReduceContext -> the cross-rank sum happens inside the GEMM (M <= 16)."""
+    def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16, ar=None, residual=None) -> torch.Tensor:
+        """ar: an ops.AllReduceContext -> the cross-rank sum happens inside the GEMM (M <= 16).
+        residual: [M, N] bf16 -> returns residual + linear, the sum formed in the GEMM epilogue."""
         if ar is not None:
             codes, sx = ops.quant_act_int4(x, self.a, self.had, False)
             return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
+        if residual is not None:
+            codes, sx = ops.quant_act_int4(x, self.a, self.had, False)
+            return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, residual=residual)
         return ops.linear_w4a4_int4(x, self.a, self.had, self.pw, self.r, out_dtype=out_dtype,
                                     scale_fp16=False, scratch=self._scratch_for(x.shape[0], x.device))
 
-    def gated(self, gate: torch.Tensor, up: torch.Tensor, out_dtype=torch.bfloat16, ar=None) -> torch.Tensor:
+    def gated(self, gate: torch.Tensor, up: torch.Tensor, out_dtype=torch.bfloat16, ar=None,
+              residual=None) -> torch.Tensor:
         codes, sx = ops.quant_act_int4_gated(gate, up, self.a, self.had, False)
         if ar is not None:
             return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
-        return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype)
+        return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype, residual=residual)
 
 
 def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -125,7 +133,7 @@ def _shared_hadamard_matrix(hk, kk: int, device):
 
 
 class DecoderLayer:
-    def __init__(self, cfg: DecoderConfig, tp: int, device, gen: torch.Generator):
+    def __init__(self, cfg: DecoderConfig, tp: int, device, gen: torch.Generator, keep_codes: bool = False):
         self.cfg, self.tp = cfg, tp
         hd = cfg.head_dim
         self.hq = cfg.num_attention_heads // tp
@@ -138,10 +146,10 @@ class DecoderLayer:
             hk, kk = quarot.get_hadK(inter)
             had_d = ops.Hadamard(_lib.HAD_FULL, kk, 0, quarot.full_hadamard_scale(inter),
                                  _shared_hadamard_matrix(hk, kk, device))
-        self.qkv = W4A4Linear((self.hq + 2 * self.hkv) * hd, cfg.hidden_size, device, gen)
-        self.o = W4A4Linear(cfg.hidden_size, self.hq * hd, device, gen, had_o)
-        self.gate_up = W4A4Linear(2 * inter, cfg.hidden_size, device, gen)
-        self.down = W4A4Linear(cfg.hidden_size, inter, device, gen, had_d)
+        self.qkv = W4A4Linear((self.hq + 2 * self.hkv) * hd, cfg.hidden_size, device, gen, None, keep_codes)
+        self.o = W4A4Linear(cfg.hidden_size, self.hq * hd, device, gen, had_o, keep_codes)
+        self.gate_up = W4A4Linear(2 * inter, cfg.hidden_size, device, gen, None, keep_codes)
+        self.down = W4A4Linear(cfg.hidden_size, inter, device, gen, had_d, keep_codes)
         self.inter = inter
         self.ln1 = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
         self.ln2 = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
@@ -177,20 +185,26 @@ class DecoderLayer:
                                                   enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
         fused = ar if (ar is not None and self.tp > 1 and B * S <= 16) else None
+        if self.tp == 1:
+            # one GPU: the residual additions ride in the epilogues of o_proj and down_proj
+            x = self.o(attn, residual=x.reshape(B * S, Hd).contiguous()).reshape(B, S, Hd)
+            gu = self.gate_up.normed(x.reshape(B * S, Hd), self.ln2, cfg.rms_norm_eps)
+            return self.down.gated(gu[:, : self.inter], gu[:, self.inter :],
+                                   residual=x.reshape(B * S, Hd)).reshape(B, S, Hd)
         o = self.o(attn, ar=fused)
-        if self.tp > 1 and fused is None:
+        if fused is None:
             dist.all_reduce(o, group=group)
         x = x + o.reshape(B, S, Hd)
         gu = self.gate_up.normed(x.reshape(B * S, Hd), self.ln2, cfg.rms_norm_eps)
         d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :], ar=fused)
-        if self.tp > 1 and fused is None:
+        if fused is None:
             dist.all_reduce(d, group=group)
         return x + d.reshape(B, S, Hd)
 
 
 class Decoder:
     def __init__(self, cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, group=None,
-                 fused_allreduce: bool = False):
+                 fused_allreduce: bool = False, keep_codes: bool = False):
         """fused_allreduce: decode steps sum the row-parallel linears' partial outputs inside the
         GEMM kernel over NVLink peer memory instead of calling NCCL (prefill keeps NCCL)."""
         assert cfg.num_key_value_heads % tp == 0 and cfg.intermediate_size % (tp * 128) == 0
@@ -204,7 +218,7 @@ class Decoder:
         self.embed = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=shared, device=device) * 0.02).to(torch.bfloat16)
         self.lm_head = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=shared, device=device) * 0.02).to(torch.bfloat16)
         self.norm = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
-        self.layers = [DecoderLayer(cfg, tp, device, gen) for _ in range(cfg.num_hidden_layers)]
+        self.layers = [DecoderLayer(cfg, tp, device, gen, keep_codes) for _ in range(cfg.num_hidden_layers)]
         self.max_len = 0
 
     def alloc_cache(self, batch: int, max_len: int):

@@ -186,17 +186,43 @@ def hadamard_f32(x: torch.Tensor, had: Hadamard) -> torch.Tensor:
     return out
 
 
+def fakequant_act_int4_bf16(x: torch.Tensor) -> torch.Tensor:
+    """bf16 [M,K] -> bf16 [M,K]: per-token int4 fake-quantisation in one pass (the
+    quantize_bmm_input step of PermLinear)."""
+    lib = _prep(x)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("fakequant_act_int4_bf16 expects bf16 rows")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    M, K = x.shape
+    out = torch.empty(M, K, dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.dq_fakequant_act_int4_bf16(_ptr(x), x.stride(0) if M > 1 else K, M, K, _ptr(out),
+                                              _stream(x.device)), "dq_fakequant_act_int4_bf16")
+    return out
+
+
 def gemm_w4a4_int4(codes: torch.Tensor, sx: torch.Tensor, pw: PackedInt4Weight,
                    r: Optional[torch.Tensor] = None, out_dtype=torch.float32,
                    token_tile: int = 0, split_k: int = 0,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out: Optional[torch.Tensor] = None,
+                   residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual: [M, N] of the output's dtype -> out = residual + linear (fused into the epilogue;
+    may be the output tensor itself)."""
     lib = _prep(codes)
     M, K = codes.shape
     if K != pw.K:
         raise ValueError(f"K mismatch: activations {K}, weight {pw.K}")
     if out is None:
-        out = torch.empty(M, pw.N, dtype=out_dtype, device=codes.device)
+        out = torch.empty(M, pw.N, dtype=residual.dtype if residual is not None else out_dtype,
+                          device=codes.device)
     ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    if residual is not None:
+        if residual.dtype != out.dtype or tuple(residual.shape) != (M, pw.N) or not residual.is_contiguous():
+            raise ValueError("residual must be a contiguous [M, N] tensor of the output's dtype")
+        _lib.check(lib.dq_gemm_w4a4_int4_residual(_ptr(codes), _ptr(sx), _ptr(pw.w_packed), _ptr(pw.sw_t),
+                                                  _ptr(r), _ptr(residual), M, pw.N, K, pw.group, _ptr(out),
+                                                  ydt, _stream(codes.device)), "dq_gemm_w4a4_int4_residual")
+        return out
     _lib.check(lib.dq_gemm_w4a4_int4_ex(_ptr(codes), _ptr(sx), _ptr(pw.w_packed), _ptr(pw.sw_t), _ptr(r),
                                         M, pw.N, K, pw.group, _ptr(out), ydt, None, 0,
                                         _stream(codes.device), token_tile, split_k),

@@ -179,6 +179,12 @@ DQ_API int dq_fakequant_act_int4(const void* x, int x_is_f32, int64_t ldx, const
                           const dq_hadamard_desc* had, int M, int K, float* out,
                           int scale_fp16, void* stream);
 
+/* Per-token int4 fake-quantisation of bf16 rows with a bf16 result, in one pass: what PermLinear
+ * does to its own output when quantize_bmm_input is set - act_fmt.cast(out.float()).to(bf16),
+ * activations/perm_linear.py:139-140 - without the fp32 round trip through memory. */
+DQ_API int dq_fakequant_act_int4_bf16(const void* x_bf16, int64_t ldx, int M, int K, void* out_bf16,
+                                      void* stream);
+
 /* The online Hadamard alone on fp32 rows: out = hadamard(x) (perm_linear.py:76-106). */
 DQ_API int dq_hadamard_f32(const float* x, float* out, int M, int K, const dq_hadamard_desc* had,
                     void* stream);
@@ -278,6 +284,17 @@ DQ_API size_t dq_gemm_w4a4_int4_workspace_bytes(int M, int N, int K);
 DQ_API int dq_gemm_w4a4_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                       const void* sw_t, const float* r, int M, int N, int K, int G, void* y,
                       int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * dq_gemm_w4a4_int4 with the decoder's residual connection fused into the epilogue:
+ * Y = residual + linear.  residual is [M,N] of Y's element type and may be Y itself (in place).
+ * For bf16 the linear's result is rounded to bf16 before the sum and the sum rounded again -
+ * bit-identical to the separate `hidden = residual + o_proj(...)` of the HF decoder layer the
+ * reference wraps (ablation/real_int4_kernel/full_model_nunchaku.py:81-114 leaves that add to HF).
+ */
+DQ_API int dq_gemm_w4a4_int4_residual(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                      const void* sw_t, const float* r, const void* residual, int M,
+                                      int N, int K, int G, void* y, int y_dtype, void* stream);
 
 /* As above with an explicit kernel choice; used by tuning sweeps and tests.  token_tile: 0 = auto,
  * 16/32/64/128 = tcgen05 kernel with that token tile (weights through tensor memory for tiles up
