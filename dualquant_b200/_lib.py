@@ -78,6 +78,8 @@ SIGNATURES = {
     "dq_gemm_w4a4_fp4_tiled": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "dq_gemm_w4a4_int4_workspace_bytes": (_sz, [_i, _i, _i]),
     "dq_gemm_w4a4_int4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "dq_quant_act_int4_grouped": (_i, [_vp, _i64, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
+    "dq_gemm_w4a4_int4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "dq_gemm_w4a4_int4_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),
     "dq_gemm_w4a4_int4_ar": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),

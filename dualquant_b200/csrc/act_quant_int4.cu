@@ -724,9 +724,75 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
   return DQ_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// one activation scale per (token, group of 128): the quantiser of the reference's fused W4A4
+// Triton kernel (per row and K tile) as a stand-alone pass
+// ---------------------------------------------------------------------------------------------
+// One warp per (token, group); a lane holds four consecutive elements.  IEEE divisions (this
+// variant is not on the measured path).  round_away = 1 rounds halves away from zero like the
+// Triton kernel's libdevice.round, 0 rounds them to even like torch.round.
+__global__ void __launch_bounds__(256)
+act_quant_grouped_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const float* __restrict__ a,
+                         int M, int K, int8_t* __restrict__ codes, float* __restrict__ sxg,
+                         int scale_fp16, int round_away) {
+  grid_dep_launch_dependents();
+  grid_dep_wait();
+  const int groups = K / kGroup;
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (token, group)
+  if (unit >= M * groups) return;
+  const int m = unit / groups, g = unit % groups;
+  const int lane = threadIdx.x & 31;
+  const int k0 = g * kGroup + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + static_cast<int64_t>(m) * ldx + k0);
+  float v[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
+  if (a != nullptr) {
+    const float4 av = *reinterpret_cast<const float4*>(a + k0);
+    v[0] = __fmul_rn(v[0], av.x); v[1] = __fmul_rn(v[1], av.y);
+    v[2] = __fmul_rn(v[2], av.z); v[3] = __fmul_rn(v[3], av.w);
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float s = token_scale(amax, scale_fp16);
+  if (lane == 0) sxg[static_cast<size_t>(g) * M + m] = s;
+  int q[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float t = __fdiv_rn(v[e], s);
+    const float rq = round_away ? roundf(t) : rintf(t);
+    q[e] = static_cast<int>(fminf(fmaxf(rq, -8.0f), 7.0f));
+  }
+  const uint32_t packed = (static_cast<uint32_t>(q[0]) & 0xFFu) | ((static_cast<uint32_t>(q[1]) & 0xFFu) << 8) |
+                          ((static_cast<uint32_t>(q[2]) & 0xFFu) << 16) | ((static_cast<uint32_t>(q[3]) & 0xFFu) << 24);
+  *reinterpret_cast<uint32_t*>(codes + static_cast<int64_t>(m) * K + k0) = packed;
+}
+
 }  // namespace dq
 
 using namespace dq;
+
+extern "C" int dq_quant_act_int4_grouped(const void* x_bf16, int64_t ldx, const float* a, int M, int K,
+                                         int G, int8_t* codes, float* sx_groups, int scale_fp16,
+                                         int round_away, void* stream) {
+  if (current_state() == nullptr) return DQ_ERR_NOT_INIT;
+  if (M == 0) return DQ_OK;
+  DQ_REQUIRE(x_bf16 != nullptr && codes != nullptr && sx_groups != nullptr, DQ_ERR_NULL, "null x / codes / sx_groups");
+  DQ_REQUIRE(G == kGroup, DQ_ERR_UNSUPPORTED, "activation group size must be %d (got %d)", kGroup, G);
+  DQ_REQUIRE(M >= 0 && K >= kGroup && K % kGroup == 0, DQ_ERR_SHAPE, "bad shape M=%d K=%d", M, K);
+  DQ_REQUIRE(ldx >= K && ldx % 4 == 0, DQ_ERR_ALIGN, "ldx=%lld must be >= K and a multiple of 4", (long long)ldx);
+  DQ_REQUIRE(aligned(x_bf16, 8) && (a == nullptr || aligned(a, 16)) && aligned(codes, 4), DQ_ERR_ALIGN,
+             "x (8 B), a (16 B) and codes (4 B) must be aligned");
+  const int64_t units = static_cast<int64_t>(M) * (K / kGroup);
+  DQ_REQUIRE(units < (1ll << 31), DQ_ERR_SHAPE, "too many (token, group) units");
+  const int per_cta = 8;
+  DQ_CHECK_CUDA(launch_pdl(act_quant_grouped_kernel, dim3(static_cast<unsigned>((units + per_cta - 1) / per_cta)),
+                           dim3(per_cta * 32), 0, static_cast<cudaStream_t>(stream),
+                           static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, M, K, codes, sx_groups,
+                           scale_fp16, round_away));
+  DQ_CHECK_CUDA(cudaGetLastError());
+  return DQ_OK;
+}
 
 extern "C" int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a,
                                  const dq_hadamard_desc* had, int M, int K, int8_t* codes,

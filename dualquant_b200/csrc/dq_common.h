@@ -112,11 +112,12 @@ int launch_gemv_fused(const void* x_bf16, int64_t ldx, const float* a, const uin
 int launch_gemm_int4_tm(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                         const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
                         int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st,
-                        const void* residual = nullptr);
+                        const void* residual = nullptr, bool grouped_sx = false);
 int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count);
 int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                      const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
                      int tok, int split, cudaStream_t stream, DeviceState* st,
-                     const dq_allreduce_ctx* ctx = nullptr, const void* residual = nullptr);
+                     const dq_allreduce_ctx* ctx = nullptr, const void* residual = nullptr,
+                     bool grouped_sx = false);
 
 }  // namespace dq

@@ -643,7 +643,7 @@ extern "C" size_t dq_gemm_w4a4_int4_workspace_bytes(int, int, int) { return 0; }
 static int gemm_int4_dispatch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                               const void* sw_t, const float* r, const void* residual, int M, int N,
                               int K, int G, void* y, int y_dtype, void* stream, int token_tile,
-                              int split_k) {
+                              int split_k, bool grouped_sx = false) {
   DeviceState* st = current_state();
   if (st == nullptr) return DQ_ERR_NOT_INIT;
   if (M == 0) return DQ_OK;
@@ -668,7 +668,7 @@ static int gemm_int4_dispatch(const int8_t* codes, const float* sx, const uint8_
     DQ_REQUIRE(split <= tok && split <= total_groups, DQ_ERR_SHAPE,
                "split_k=%d too large for %d tokens / %d groups", split, tok, total_groups);
     return launch_gemv_int4(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, tok, split,
-                            static_cast<cudaStream_t>(stream), st, nullptr, residual);
+                            static_cast<cudaStream_t>(stream), st, nullptr, residual, grouped_sx);
   }
   // 1000 + tile / 2000 + tile force the shared-memory-operand / tensor-memory-operand kernel
   int forced = 0;
@@ -689,10 +689,11 @@ static int gemm_int4_dispatch(const int8_t* codes, const float* sx, const uint8_
   // kernel that feeds the weights to the tensor core from tensor memory, which leaves all shared
   // memory to the copy rings.  Token tile 128 (prefill): the kernel with int8 weight tiles in
   // shared memory, four accumulators and two issuing warps, measured 10-15 % faster there.
-  const bool use_tm = forced ? (forced == 2) : (tn <= 64);
+  // (the per-group activation-scale variant exists in the tensor-memory-operand kernel only)
+  const bool use_tm = grouped_sx || (forced ? (forced == 2) : (tn <= 64));
   if (use_tm)
     return launch_gemm_int4_tm(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, nullptr, tn, split, s, st,
-                               residual);
+                               residual, grouped_sx);
   switch (tn) {
     case 16: return launch<16>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st, residual);
     case 32: return launch<32>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, s, st, residual);
@@ -717,6 +718,14 @@ extern "C" int dq_gemm_w4a4_int4_residual(const int8_t* codes, const float* sx,
   DQ_REQUIRE(residual != nullptr, DQ_ERR_NULL, "null residual");
   DQ_REQUIRE(aligned(residual, y_dtype == DQ_DTYPE_BF16 ? 2 : 4), DQ_ERR_ALIGN, "misaligned residual");
   return gemm_int4_dispatch(codes, sx, w_packed, sw_t, r, residual, M, N, K, G, y, y_dtype, stream, 0, 0);
+}
+
+extern "C" int dq_gemm_w4a4_int4_grouped(const int8_t* codes, const float* sx_groups,
+                                         const uint8_t* w_packed, const void* sw_t, const float* r,
+                                         int M, int N, int K, int G, void* y, int y_dtype,
+                                         void* stream) {
+  return gemm_int4_dispatch(codes, sx_groups, w_packed, sw_t, r, nullptr, M, N, K, G, y, y_dtype, stream,
+                            0, 0, true);
 }
 
 extern "C" int dq_gemm_w4a4_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,

@@ -131,7 +131,7 @@ namespace tm {
 //   acc_done / acc_free [NB] accumulators         issuer (tcgen05.commit) -> EW epilogue warps
 // Every barrier is waited on by one role whose warps all pass every phase in order, so a waiter
 // is never a whole phase ahead of the barrier (waits are by phase parity).
-template <int TN, bool DUMP>
+template <int TN, int MODE>
 __global__ void __launch_bounds__(Cfg<TN>::kThreads, Cfg<TN>::kMinCtas)
 gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
                          const __grid_constant__ CUtensorMap tm_x,
@@ -141,6 +141,10 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
                          int32_t* __restrict__ acc_dump, int M, int N, int K,
                          int groups_per_split, int split_k, int w_stream_once, int* status) {
   using C = Cfg<TN>;
+  // MODE 0: Y with one activation scale per token; 1: dump the raw int32 group sums; 2: Y with one
+  // activation scale per (token, weight group): sx is then [K / 128][M], group-major
+  constexpr bool DUMP = (MODE == 1);
+  constexpr bool GS = (MODE == 2);
   // The 128-byte swizzle of the activation tiles needs them on 1 KB boundaries.  The kernel has
   // no static shared memory, so the dynamic window starts on one; if it ever does not, every CTA
   // reports that and leaves before touching a barrier.
@@ -302,11 +306,20 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
         }
       } else {
         // two columns per instruction: packed fp32 FMA (each half rounds like a scalar fmaf)
+        const float* sg = nullptr;
+        if constexpr (GS) sg = sx + static_cast<size_t>(g_begin + i) * M;  // this group's token scales
 #pragma unroll
         for (int j = 0; j < C::CH; j += 2) {
           const float2 f = make_float2(static_cast<float>(static_cast<int32_t>(v[j])),
                                        static_cast<float>(static_cast<int32_t>(v[j + 1])));
-          const float2 acc2 = __ffma2_rn(f, make_float2(s, s), make_float2(run[c0 + j], run[c0 + j + 1]));
+          float2 p = make_float2(s, s);
+          if constexpr (GS) {
+            // warp-uniform addresses (every lane of a warp holds the same token columns)
+            const int m0 = t0 + h * C::CPW + c0 + j;
+            p.x = __fmul_rn(s, __ldg(sg + (m0 < M ? m0 : M - 1)));
+            p.y = __fmul_rn(s, __ldg(sg + (m0 + 1 < M ? m0 + 1 : M - 1)));
+          }
+          const float2 acc2 = __ffma2_rn(f, p, make_float2(run[c0 + j], run[c0 + j + 1]));
           run[c0 + j] = acc2.x;
           run[c0 + j + 1] = acc2.y;
         }
@@ -374,25 +387,29 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
           const int m0 = t0 + h * C::CPW;
           const int cnt = (M - m0 < C::CPW) ? (M - m0) : C::CPW;  // tokens of this slice that exist
           const float* sxp = sx + m0;
+          auto tok_scale = [&](int j) -> float {  // per-token scale; already applied per group in GS mode
+            if constexpr (GS) return 1.f;
+            return __ldg(sxp + j);
+          };
           if (residual != nullptr) {
             size_t idx = static_cast<size_t>(m0) * N + n;
 #pragma unroll
             for (int j = 0; j < C::CPW; ++j) {
-              if (j < cnt) store_y(y, residual, y_bf16, idx, run[j] * (rn * __ldg(sxp + j)));
+              if (j < cnt) store_y(y, residual, y_bf16, idx, run[j] * (rn * tok_scale(j)));
               idx += N;
             }
           } else if (y_bf16) {
             __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(y) + static_cast<size_t>(m0) * N + n;
 #pragma unroll
             for (int j = 0; j < C::CPW; ++j) {
-              if (j < cnt) *yp = __float2bfloat16_rn(run[j] * (rn * __ldg(sxp + j)));
+              if (j < cnt) *yp = __float2bfloat16_rn(run[j] * (rn * tok_scale(j)));
               yp += N;
             }
           } else {
             float* yp = reinterpret_cast<float*>(y) + static_cast<size_t>(m0) * N + n;
 #pragma unroll
             for (int j = 0; j < C::CPW; ++j) {
-              if (j < cnt) *yp = run[j] * (rn * __ldg(sxp + j));
+              if (j < cnt) *yp = run[j] * (rn * tok_scale(j));
               yp += N;
             }
           }
@@ -509,7 +526,7 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         if (m < M) {
-          const float sm = sx[m];
+          const float sm = GS ? 1.f : sx[m];
           const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -537,9 +554,9 @@ gemm_w4a4_int4_tm_kernel(const uint8_t* __restrict__ w_packed,
   if (tid == 0 && *abort_flag != 0) atomicCAS(status, 0, *abort_flag);
 }
 
-template <int TN, bool DUMP>
+template <int TN, int MODE>
 static int set_attr() {
-  cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_int4_tm_kernel<TN, DUMP>,
+  cudaError_t e = cudaFuncSetAttribute(gemm_w4a4_int4_tm_kernel<TN, MODE>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<TN>::kSmemBytes);
   if (e != cudaSuccess)
@@ -548,7 +565,7 @@ static int set_attr() {
   return DQ_OK;
 }
 
-template <int TN, bool DUMP>
+template <int TN, int MODE>
 static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed, const __half* sw_t,
                   const float* r, int M, int N, int K, void* y, int y_dtype, int32_t* acc_dump,
                   int split, cudaStream_t stream, DeviceState* st, const void* residual) {
@@ -573,7 +590,7 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_tm_kernel<TN, DUMP>, w_packed, tm_x, sw_t,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_tm_kernel<TN, MODE>, w_packed, tm_x, sw_t,
                                      r, sx, y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, acc_dump, M, N, K,
                                      gps, split, w_stream_once, st->status_dev);
   if (e != cudaSuccess)
@@ -586,30 +603,43 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
 
 int init_gemm_int4_tm_kernels() {
   int rc;
-  if ((rc = tm::set_attr<16, false>()) != DQ_OK) return rc;
-  if ((rc = tm::set_attr<32, false>()) != DQ_OK) return rc;
-  if ((rc = tm::set_attr<64, false>()) != DQ_OK) return rc;
-  if ((rc = tm::set_attr<128, false>()) != DQ_OK) return rc;
-  if ((rc = tm::set_attr<16, true>()) != DQ_OK) return rc;
-  if ((rc = tm::set_attr<128, true>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<16, 0>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<32, 0>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<64, 0>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<128, 0>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<16, 1>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<128, 1>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<16, 2>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<32, 2>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<64, 2>()) != DQ_OK) return rc;
+  if ((rc = tm::set_attr<128, 2>()) != DQ_OK) return rc;
   return DQ_OK;
 }
 
 // tn: 16 / 32 / 64 / 128; acc_dump != nullptr selects the accumulator-dump variant (tn 16 or 128).
 int launch_gemm_int4_tm(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                         const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
-                        int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st, const void* residual) {
+                        int32_t* acc_dump, int tn, int split, cudaStream_t s, DeviceState* st,
+                        const void* residual, bool grouped_sx) {
   const __half* swp = static_cast<const __half*>(sw_t);
+  if (grouped_sx && acc_dump == nullptr) {
+    switch (tn) {
+      case 16: return tm::launch<16, 2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+      case 32: return tm::launch<32, 2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+      case 64: return tm::launch<64, 2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+      default: return tm::launch<128, 2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    }
+  }
   if (acc_dump != nullptr) {
     if (tn == 16)
-      return tm::launch<16, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st, residual);
-    return tm::launch<128, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st, residual);
+      return tm::launch<16, 1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st, residual);
+    return tm::launch<128, 1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, acc_dump, 1, s, st, residual);
   }
   switch (tn) {
-    case 16: return tm::launch<16, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
-    case 32: return tm::launch<32, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
-    case 64: return tm::launch<64, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
-    default: return tm::launch<128, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    case 16: return tm::launch<16, 0>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    case 32: return tm::launch<32, 0>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    case 64: return tm::launch<64, 0>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
+    default: return tm::launch<128, 0>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, nullptr, split, s, st, residual);
   }
 }
 

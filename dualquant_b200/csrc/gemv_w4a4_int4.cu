@@ -100,7 +100,9 @@ __device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], uint32_t a0, uint32_
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT>
+// GS: one activation scale per (token, weight group) - sx is then [K / 128][M], group-major - instead
+// of one per token.
+template <int NT, bool GS>
 __global__ void __launch_bounds__(kVThreads, VCfg<NT>::kMinCtas)
 gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __grid_constant__ CUtensorMap tm_x,
@@ -244,10 +246,17 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
 #pragma unroll
         for (int nb = 0; nb < NT; ++nb) {
-          run[nb][0] = fmaf(static_cast<float>(c[nb][0][0] + c[nb][1][0]), s0, run[nb][0]);
-          run[nb][1] = fmaf(static_cast<float>(c[nb][0][1] + c[nb][1][1]), s0, run[nb][1]);
-          run[nb][2] = fmaf(static_cast<float>(c[nb][0][2] + c[nb][1][2]), s1, run[nb][2]);
-          run[nb][3] = fmaf(static_cast<float>(c[nb][0][3] + c[nb][1][3]), s1, run[nb][3]);
+          float xa = 1.f, xb = 1.f;  // activation scales of tokens 2t, 2t + 1 of this block
+          if constexpr (GS) {
+            const float* sg = sx + static_cast<size_t>(g_begin + i * kVGS + gi) * M;
+            const int m = nb * 8 + 2 * t;
+            xa = __ldg(sg + (m < M ? m : M - 1));
+            xb = __ldg(sg + (m + 1 < M ? m + 1 : M - 1));
+          }
+          run[nb][0] = fmaf(static_cast<float>(c[nb][0][0] + c[nb][1][0]), GS ? __fmul_rn(s0, xa) : s0, run[nb][0]);
+          run[nb][1] = fmaf(static_cast<float>(c[nb][0][1] + c[nb][1][1]), GS ? __fmul_rn(s0, xb) : s0, run[nb][1]);
+          run[nb][2] = fmaf(static_cast<float>(c[nb][0][2] + c[nb][1][2]), GS ? __fmul_rn(s1, xa) : s1, run[nb][2]);
+          run[nb][3] = fmaf(static_cast<float>(c[nb][0][3] + c[nb][1][3]), GS ? __fmul_rn(s1, xb) : s1, run[nb][3]);
         }
       }
       __syncwarp();
@@ -300,7 +309,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
             for (int e = 0; e < 2; ++e) {
               const int m = nb * 8 + 2 * t + e;
               if (m < M) {
-                store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, run[nb][2 * hrow + e] * (rn * sx[m]));
+                store_y(y, residual, y_bf16, static_cast<size_t>(m) * N + n, run[nb][2 * hrow + e] * (GS ? rn : rn * sx[m]));
               }
             }
         }
@@ -344,7 +353,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         if (m < M) {
-          const float sm = sx[m];
+          const float sm = GS ? 1.f : sx[m];
           float vals[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -418,8 +427,11 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 // ---------------------------------------------------------------------------------------------
 template <int NT>
 static int set_gemv_attr() {
-  cudaError_t e = cudaFuncSetAttribute(gemv_w4a4_int4_kernel<NT>,
+  cudaError_t e = cudaFuncSetAttribute(gemv_w4a4_int4_kernel<NT, false>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemv_w4a4_int4_kernel<NT, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemv NT=%d) failed: %s", NT,
                      cudaGetErrorString(e));
@@ -442,7 +454,7 @@ int gemv_pick_split(int tiles, int total_groups, int tok, int sm_count) {
   return s;
 }
 
-template <int NT>
+template <int NT, bool GS>
 static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                          const __half* sw_t, const float* r, int M, int N, int K, void* y,
                          int y_dtype, int split, cudaStream_t stream, DeviceState* st,
@@ -480,7 +492,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT>, w_packed, tm_x, r, sx, y,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a4_int4_kernel<NT, GS>, w_packed, tm_x, r, sx, y,
                                      y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, M, N, K, gps, split,
                                      stages, st->status_dev, ar);
   if (e != cudaSuccess)
@@ -493,7 +505,7 @@ static int launch_gemv_t(const int8_t* codes, const float* sx, const uint8_t* w_
 int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                      const void* sw_t, const float* r, int M, int N, int K, void* y, int y_dtype,
                      int tok, int split, cudaStream_t stream, DeviceState* st,
-                     const dq_allreduce_ctx* ctx, const void* residual) {
+                     const dq_allreduce_ctx* ctx, const void* residual, bool grouped_sx) {
   const __half* swp = static_cast<const __half*>(sw_t);
   ArDev ar = {};
   ar.world = 1;
@@ -519,11 +531,16 @@ int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_pack
     ar.cap = static_cast<uint32_t>(ctx->buf_capacity_floats);
   }
   int rc;
-  switch (tok) {
-    case 8: rc = launch_gemv_t<1>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual); break;
-    case 16: rc = launch_gemv_t<2>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual); break;
-    case 32: rc = launch_gemv_t<4>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual); break;
-    default: return set_error(DQ_ERR_SHAPE, "register-path token capacity must be 8/16/32 (got %d)", tok);
+  if (tok != 8 && tok != 16 && tok != 32)
+    return set_error(DQ_ERR_SHAPE, "register-path token capacity must be 8/16/32 (got %d)", tok);
+  if (grouped_sx) {
+    rc = (tok == 8) ? launch_gemv_t<1, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual)
+       : (tok == 16) ? launch_gemv_t<2, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual)
+                     : launch_gemv_t<4, true>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual);
+  } else {
+    rc = (tok == 8) ? launch_gemv_t<1, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual)
+       : (tok == 16) ? launch_gemv_t<2, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual)
+                     : launch_gemv_t<4, false>(codes, sx, w_packed, swp, r, M, N, K, y, y_dtype, split, stream, st, ar, residual);
   }
   if (rc == DQ_OK && ar.world > 1) {
     ar_bump_kernel<<<1, 1, 0, stream>>>(static_cast<uint32_t*>(ctx->seq));

@@ -186,6 +186,39 @@ def hadamard_f32(x: torch.Tensor, had: Hadamard) -> torch.Tensor:
     return out
 
 
+def quant_act_int4_grouped(x: torch.Tensor, a: Optional[torch.Tensor] = None, scale_fp16: bool = False,
+                           round_away: bool = False):
+    """bf16 [M,K] -> (codes int8 [M,K], scales fp32 [K/128, M]): one activation scale per (token,
+    group of 128), the quantiser of the reference's fused W4A4 Triton kernel."""
+    lib = _prep(x)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("quant_act_int4_grouped expects bf16 activations")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    M, K = x.shape
+    codes = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    sxg = torch.empty(K // GROUP, M, dtype=torch.float32, device=x.device)
+    _lib.check(lib.dq_quant_act_int4_grouped(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), M, K, GROUP,
+                                             _ptr(codes), _ptr(sxg), int(scale_fp16), int(round_away),
+                                             _stream(x.device)), "dq_quant_act_int4_grouped")
+    return codes, sxg
+
+
+def gemm_w4a4_int4_grouped(codes: torch.Tensor, sxg: torch.Tensor, pw: PackedInt4Weight,
+                           r: Optional[torch.Tensor] = None, out_dtype=torch.float32) -> torch.Tensor:
+    """The int4 GEMM with per-(token, group) activation scales sxg [K/128, M]."""
+    lib = _prep(codes)
+    M, K = codes.shape
+    if K != pw.K or tuple(sxg.shape) != (K // pw.group, M):
+        raise ValueError("shape mismatch between codes, group scales and weight")
+    out = torch.empty(M, pw.N, dtype=out_dtype, device=codes.device)
+    ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    _lib.check(lib.dq_gemm_w4a4_int4_grouped(_ptr(codes), _ptr(sxg.contiguous()), _ptr(pw.w_packed),
+                                             _ptr(pw.sw_t), _ptr(r), M, pw.N, K, pw.group, _ptr(out), ydt,
+                                             _stream(codes.device)), "dq_gemm_w4a4_int4_grouped")
+    return out
+
+
 def fakequant_act_int4_bf16(x: torch.Tensor) -> torch.Tensor:
     """bf16 [M,K] -> bf16 [M,K]: per-token int4 fake-quantisation in one pass (the
     quantize_bmm_input step of PermLinear)."""

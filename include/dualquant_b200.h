@@ -296,6 +296,24 @@ DQ_API int dq_gemm_w4a4_int4_residual(const int8_t* codes, const float* sx, cons
                                       const void* sw_t, const float* r, const void* residual, int M,
                                       int N, int K, int G, void* y, int y_dtype, void* stream);
 
+/*
+ * The variant of the reference's fused W4A4 Triton kernel that scales activations per (token,
+ * K tile) instead of per token (ablation/real_int4_kernel/fused_w4a4_kernel.py:93-100,119) and of
+ * the per-group activation quantiser of its nunchaku path
+ * (ablation/real_int4_kernel/full_model_nunchaku.py:81-114), with the activation group equal to
+ * the weight group of this library's artefact (128; the Triton kernel uses 64 for both):
+ *   s[m,g] = absmax_{k in g}(x[m,k]*a[k]) / 7 (1 if 0), q = clamp(round(x*a / s), -8, 7)
+ *   Y[m,n] = r[n] * sum_g (sw[n,g] * s[m,g]) * (sum_{k in g} qx[m,k] * qw[n,k])
+ * sx_groups is fp32 [K/128][M] (group-major).  round_away != 0 rounds halves away from zero like
+ * the Triton kernel's libdevice.round (:98); 0 rounds them to even like formats/rtn_int.py:67.
+ */
+DQ_API int dq_quant_act_int4_grouped(const void* x_bf16, int64_t ldx, const float* a, int M, int K,
+                                     int G, int8_t* codes, float* sx_groups, int scale_fp16,
+                                     int round_away, void* stream);
+DQ_API int dq_gemm_w4a4_int4_grouped(const int8_t* codes, const float* sx_groups,
+                                     const uint8_t* w_packed, const void* sw_t, const float* r, int M,
+                                     int N, int K, int G, void* y, int y_dtype, void* stream);
+
 /* As above with an explicit kernel choice; used by tuning sweeps and tests.  token_tile: 0 = auto,
  * 16/32/64/128 = tcgen05 kernel with that token tile (weights through tensor memory for tiles up
  * to 64, int8 weight tiles in shared memory for 128; 1000 + tile / 2000 + tile force the

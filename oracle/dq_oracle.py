@@ -159,6 +159,43 @@ def quant_act_int4(x: torch.Tensor, a=None, had=None, scale_fp16: bool = False):
     return q.to(torch.int8), s.reshape(-1).contiguous(), x32
 
 
+def quant_act_int4_grouped(x: torch.Tensor, a=None, group: int = GROUP, scale_fp16: bool = False,
+                           round_away: bool = False):
+    """Activation quantiser with one scale per (token, K tile): the in-kernel quantiser of the
+    reference's fused W4A4 Triton kernel (ablation/real_int4_kernel/fused_w4a4_kernel.py:93-100):
+    a = x * beta in fp32, scale = absmax/7 per (row, tile) (1 where the tile is zero),
+    q = clamp(round(a / scale), -8, 7) with libdevice.round (halves away from zero; round_away)
+    or torch.round (halves to even, formats/rtn_int.py:67).
+    Returns (codes int8 [M,K], scales fp32 [M, K/group])."""
+    x32 = x.to(torch.float32)
+    if a is not None:
+        x32 = x32 * a.to(torch.float32)
+    M, K = x32.shape
+    xg = x32.reshape(M, K // group, group)
+    amax = xg.abs().amax(dim=-1, keepdim=True)
+    s = amax / 7
+    s[amax == 0] = 1.0
+    if scale_fp16:
+        s = _round_scale_fp16(s)
+    t = xg / s
+    q = (torch.sign(t) * torch.floor(t.abs() + 0.5)) if round_away else t.round()
+    q = q.clamp(-8, 7)
+    return q.reshape(M, K).to(torch.int8), s.reshape(M, K // group).contiguous()
+
+
+def epilogue_grouped(acc: torch.Tensor, sw: torch.Tensor, r, sxg: torch.Tensor, dtype=torch.float32):
+    """fused_w4a4_kernel.py:119: acc += float(partial) * (a_scale * w_scale), groups in order;
+    sxg is [M, K/group]; r[n] multiplies the finished sum."""
+    M, N, G = acc.shape
+    y = torch.zeros(M, N, dtype=dtype)
+    for g in range(G):
+        p = sxg[:, g].to(dtype).reshape(M, 1) * sw[:, g].to(dtype).reshape(1, N)
+        y = y + acc[:, :, g].to(dtype) * p
+    if r is not None:
+        y = y * r.to(dtype).reshape(1, N)
+    return y
+
+
 def rmsnorm_bf16(x: torch.Tensor, weight=None, eps: float = 1e-5) -> torch.Tensor:
     """_RMSNbf16Safe.forward (quarot/llama_quarot.py:135-141): fp32 variance by .mean(-1),
     x * rsqrt(var + eps), cast back to the input dtype; with `weight` the HF LlamaRMSNorm form
