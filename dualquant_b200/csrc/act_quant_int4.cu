@@ -372,6 +372,84 @@ act_quant_had_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_
 }
 
 // ---------------------------------------------------------------------------------------------
+// full online Hadamard with a large +-1 factor (orders 36 ... 172 of the reference's table)
+// ---------------------------------------------------------------------------------------------
+// Same arithmetic as act_quant_had_kernel for had_k up to kMaxHadKBig: the row (as fp32) and a
+// second buffer of the same size sit in shared memory next to the factor stored as one byte per
+// entry.  Walsh-Hadamard stages over the contiguous segments in place, then one thread per output
+// element: out[i][c] = sum_j H[i][j] * (v[j][c] * scale), j ascending, fp32 - the order of the
+// stand-alone restatement, so codes stay bit-identical.  Used for decode-size batches of models
+// whose intermediate size is not 28 * 2^k (e.g. 11008 = 172 * 64); not a tuned path.
+constexpr int kMaxHadKBig = 172;
+
+template <int THREADS, typename XT>
+__global__ void __launch_bounds__(THREADS)
+act_quant_had_big_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_t ldx,
+                         const float* __restrict__ a, int K, int had_k, float had_scale,
+                         const float* __restrict__ had_mat, int8_t* __restrict__ codes,
+                         float* __restrict__ sx, float* __restrict__ out, int mode, int scale_fp16) {
+  extern __shared__ float sm_row[];
+  __shared__ float red[THREADS / 32];
+  float* row = sm_row;
+  float* res = sm_row + K;
+  signed char* hm = reinterpret_cast<signed char*>(sm_row + 2 * K);
+  grid_dep_launch_dependents();
+  grid_dep_wait();
+  const int r = blockIdx.x;
+  const XT* xr = x + static_cast<int64_t>(r) * ldx;
+  const XT* ur = (up != nullptr) ? up + static_cast<int64_t>(r) * ldx : nullptr;
+  for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
+    float v[8];
+    load8(xr + idx, v);
+    apply_gate(ur != nullptr ? ur + idx : nullptr, v);
+    if (a != nullptr) {
+      float av[8];
+      load8(a + idx, av);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) row[idx + e] = v[e];
+  }
+  for (int i = threadIdx.x; i < had_k * had_k; i += THREADS) hm[i] = had_mat[i] > 0.f ? 1 : -1;
+  __syncthreads();
+  const int P = K / had_k;
+  for (int h = 1; h < P; h <<= 1) {
+    wht_stage<THREADS>(row, K, h, 1);
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < K; i += THREADS) row[i] = __fmul_rn(row[i], had_scale);
+  __syncthreads();
+  for (int o = threadIdx.x; o < K; o += THREADS) {
+    const int i = o / P, c = o - i * P;
+    const signed char* hrow = hm + i * had_k;
+    float acc = 0.f;
+    for (int j = 0; j < had_k; ++j) {
+      const float v = row[j * P + c];
+      acc = __fadd_rn(acc, hrow[j] > 0 ? v : -v);
+    }
+    res[o] = acc;
+  }
+  __syncthreads();
+  float s = 1.f;
+  if (mode != MODE_RAW) {
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < K; i += THREADS) amax = fmaxf(amax, fabsf(res[i]));
+    amax = block_max(amax, red, THREADS / 32);
+    s = token_scale(amax, scale_fp16);
+    if (threadIdx.x == 0 && sx != nullptr) sx[r] = s;
+  }
+  int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(r) * K : nullptr;
+  float* orow = out_row_ptr(out, r, K, mode);
+  for (int idx = threadIdx.x * 8; idx < K; idx += THREADS * 8) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = res[idx + e];
+    emit8(v, s, mode, crow, orow, idx);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // fast online Hadamard: warp-shuffle butterflies inside segments, one thread per column across
 // ---------------------------------------------------------------------------------------------
 // The row is viewed as S segments of P contiguous elements (S <= 32, P = 32 * R).
@@ -596,6 +674,12 @@ int init_act_quant_kernels() {
   cudaError_t e = cudaFuncSetAttribute(act_quant_had_kernel<kHadThreads, __nv_bfloat16>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
   if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(act_quant_had_big_kernel<kHadThreads, __nv_bfloat16>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(act_quant_had_big_kernel<kHadThreads, float>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
+  if (e == cudaSuccess)
     e = cudaFuncSetAttribute(act_quant_had_kernel<kHadThreads, float>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
 #define DQ_HAD_ATTR(R, T)                                                                     \
@@ -621,8 +705,8 @@ static bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 static int check_had(const dq_hadamard_desc* had, int K) {
   if (had == nullptr || had->kind == DQ_HAD_NONE) return DQ_OK;
   if (had->kind == DQ_HAD_FULL) {
-    DQ_REQUIRE(had->had_k >= 1 && had->had_k <= kMaxHadK, DQ_ERR_UNSUPPORTED,
-               "had_k=%d outside [1,%d]", had->had_k, kMaxHadK);
+    DQ_REQUIRE(had->had_k >= 1 && had->had_k <= kMaxHadKBig, DQ_ERR_UNSUPPORTED,
+               "had_k=%d outside [1,%d]", had->had_k, kMaxHadKBig);
     DQ_REQUIRE(K % had->had_k == 0 && is_pow2(K / had->had_k), DQ_ERR_SHAPE,
                "K=%d is not had_k=%d times a power of two", K, had->had_k);
     DQ_REQUIRE(had->had_k == 1 || had->had_mat != nullptr, DQ_ERR_NULL, "had_mat is null");
@@ -660,6 +744,17 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
              DQ_ERR_UNSUPPORTED, "the fused RMSNorm covers plain rows of K <= 32768 without a Hadamard");
   if (use_had || mode == MODE_RAW || K > 32768 || up != nullptr) {  // longer rows than the register path holds
     const int hk = use_had ? had->had_k : 1;
+    if (use_had && had->kind == DQ_HAD_FULL && hk > kMaxHadK) {
+      // large +-1 factor: row + result buffer + the factor as bytes
+      const size_t big = static_cast<size_t>(K) * 8 + (static_cast<size_t>(hk) * hk + 15) / 16 * 16;
+      DQ_REQUIRE(big <= static_cast<size_t>(kHadMaxSmem), DQ_ERR_UNSUPPORTED,
+                 "row of K=%d with a Hadamard factor of order %d does not fit in shared memory", K, hk);
+      DQ_CHECK_CUDA(launch_pdl(act_quant_had_big_kernel<kHadThreads, XT>, dim3(M), dim3(kHadThreads), big,
+                               stream, x, up, ldx, a, K, hk, had->scale, had->had_mat, codes, sx, out, mode,
+                               scale_fp16));
+      DQ_CHECK_CUDA(cudaGetLastError());
+      return DQ_OK;
+    }
     const size_t smem = static_cast<size_t>(K) * 4 + (hk > 1 ? static_cast<size_t>(hk) * hk * 4 : 0);
     DQ_REQUIRE(smem <= static_cast<size_t>(kHadMaxSmem), DQ_ERR_UNSUPPORTED,
                "row of K=%d does not fit in shared memory", K);

@@ -57,14 +57,38 @@ def paley2_hadamard(q: int) -> torch.Tensor:
     return torch.cat([top, bot], dim=0).to(torch.float32)
 
 
+_REFERENCE_ORDERS = (172, 156, 140, 108, 60, 52, 36, 28, 40, 20, 12)
+_GOLDEN_HADAMARDS = {}
+
+
+def reference_hadamard(k: int) -> torch.Tensor:
+    """The k x k +-1 matrix of the reference's table (quarot/vendor/hadamard_utils.py:57-391), read
+    from the fixture that tests/golden/make_golden.py produced by calling the reference's own
+    get_had<k>() functions (one bit per entry)."""
+    if not _GOLDEN_HADAMARDS:
+        import os
+
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests", "golden",
+                            "reference_vectors.npz")
+        blob = np.load(path)
+        bits, off = blob["had_bits"], 0
+        for order in blob["had_orders"].tolist():
+            nbytes = (order * order + 7) // 8
+            m = np.unpackbits(bits[off:off + nbytes])[: order * order].reshape(order, order)
+            _GOLDEN_HADAMARDS[order] = torch.from_numpy(m.astype(np.float32) * 2 - 1)
+            off += nbytes
+    return _GOLDEN_HADAMARDS[k].clone()
+
+
 def get_hadK(n: int):
-    """(had_K, K) for a transform length n (quarot/vendor/hadamard_utils.py:5-55), restricted to
-    the orders this path needs: 28 * 2^k (Llama-3 intermediate sizes) and powers of two."""
-    if n % 28 == 0 and _is_pow2(n // 28):
-        return paley2_hadamard(13), 28
-    if _is_pow2(n):
-        return None, 1
-    raise NotImplementedError(f"no Hadamard decomposition restated for n={n}")
+    """(had_K, K) as the reference's get_hadK (quarot/vendor/hadamard_utils.py:5-55): the first order
+    of its table that divides n, else (None, 1) for a power of two."""
+    for k in _REFERENCE_ORDERS:
+        if n % k == 0:
+            assert _is_pow2(n // k)
+            return reference_hadamard(k), k
+    assert _is_pow2(n)
+    return None, 1
 
 
 def _is_pow2(n: int) -> bool:

@@ -76,6 +76,11 @@ def main(ref_root: str) -> None:
     out["had28"] = had28.numpy().astype(np.int8)
     _, k1 = hadamard_utils.get_hadK(32)
     assert k1 == 1
+    # every order of the reference's table (quarot/vendor/hadamard_utils.py:5-55), one bit per entry
+    orders = (12, 20, 28, 36, 40, 52, 60, 108, 140, 156, 172)
+    out["had_orders"] = np.array(orders, dtype=np.int32)
+    out["had_bits"] = np.concatenate([
+        np.packbits((getattr(hadamard_utils, f"get_had{k}")().numpy() > 0).reshape(-1)) for k in orders])
 
     # ---- per-token rtn_int4 cast (formats/rtn_int.py) ---------------------------------------
     fmt = make_format("rtn_int4", block_size=-1)

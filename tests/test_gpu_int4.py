@@ -144,6 +144,30 @@ def test_partial_hadamard_bit_exact(K, d):
     assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
 
 
+@pytest.mark.parametrize("K", [1536, 2560, 1152, 1664, 3840, 6912, 4480, 4992, 11008])
+def test_full_hadamard_other_orders_bit_exact(K):
+    """Every order of the reference's table (12, 40, 36, 52, 60, 108, 140, 156, 172) times a power of
+    two: transform and codes against the oracle, whose matrices are the reference's own."""
+    from dualquant_b200 import quarot
+
+    had, k = O.get_hadK(K)
+    hk, kk = quarot.get_hadK(K)
+    assert kk == k and torch.equal(hk, had)
+    hd = ops.Hadamard(_lib.HAD_FULL, k, 0, quarot.full_hadamard_scale(K), hk.to(DEV))
+    g = torch.Generator().manual_seed(K)
+    x = torch.randn(3, K, generator=g)
+    ref = O.hadamard_full(x, had, k)
+    got = ops.hadamard_f32(x.to(DEV), hd)
+    assert torch.equal(got.cpu(), ref)
+    xb = synthetic.make_x(3, K, 6)
+    _, c = synthetic.make_scales(8, K, 6)
+    a = 1.0 / c
+    qx, sx, _ = O.quant_act_int4(xb, a, ("full", had, k), False)
+    codes, sxg = ops.quant_act_int4(xb.to(DEV), a.to(DEV), hd, False)
+    assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
+    _status_ok()
+
+
 def test_hadamard_golden(golden):
     x = torch.from_numpy(golden["hadfull_in"])
     hd, _ = _full_had(896)

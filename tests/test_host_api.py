@@ -14,8 +14,8 @@ def test_get_hadK_matches_reference_matrix(golden):
     assert k == 28
     assert torch.equal(had, torch.from_numpy(golden["had28"]).float())
     assert quarot.get_hadK(4096) == (None, 1)
-    with pytest.raises(NotImplementedError):
-        quarot.get_hadK(12 * 64)
+    h12, k12 = quarot.get_hadK(12 * 64)
+    assert k12 == 12 and h12.shape == (12, 12)
     assert quarot.full_hadamard_scale(14336) == float((1.0 / torch.tensor(14336).sqrt()).item())
 
 
@@ -54,3 +54,29 @@ def test_perm_linear_attributes_and_install():
     assert parent.o_proj.online_partial_had and parent.o_proj.K == 1 and parent.o_proj.had_dim == 8
     with pytest.raises(RuntimeError):
         pl(torch.zeros(2, 256, dtype=torch.bfloat16))  # CPU tensor
+
+
+def test_hadamard_generators_reproduce_every_order_of_the_reference_table(golden):
+    """quarot.hadamard_of_order builds each matrix of quarot/vendor/hadamard_utils.py:57-391 from its
+    construction (Paley I / II, Sylvester doubling, Williamson); the fixture holds the reference's
+    own literals, one bit per entry."""
+    import numpy as np
+    import torch
+
+    from dualquant_b200 import quarot
+
+    bits, off = golden["had_bits"], 0
+    for k in golden["had_orders"].tolist():
+        nbytes = (k * k + 7) // 8
+        ref = np.unpackbits(bits[off:off + nbytes])[: k * k].reshape(k, k).astype(np.float32) * 2 - 1
+        off += nbytes
+        h = quarot.hadamard_of_order(k)
+        assert torch.equal(h, torch.from_numpy(ref)), k
+        assert torch.equal(h @ h.T, k * torch.eye(k))
+    # the decomposition get_hadK picks (first matching order of the reference's list)
+    for n, k in ((11008, 172), (14336, 28), (13824, 108), (6656, 52), (4096, 1), (15360, 60), (17920, 140),
+                 (1280, 40), (1536, 12), (1152, 36), (4992, 156)):
+        h, kk = quarot.get_hadK(n)
+        assert kk == k and (h is None) == (k == 1)
+    ht, _ = quarot.get_hadK(11008, transpose=True)
+    assert torch.equal(ht, quarot.hadamard_of_order(172).T)
