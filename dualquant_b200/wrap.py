@@ -10,7 +10,7 @@ the same on the GPU and hand the result to PermLinear.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -45,6 +45,50 @@ def load_wrap_cache(path: str) -> dict:
     return {"mat_q": blob["mat_q"], "beta": blob["beta"]}
 
 
+def load_column_scales(path: str) -> Dict[str, torch.Tensor]:
+    """Reads one of the scale files DualQuant's driver saves after calibration
+    (methods/dualquant.py:59-66, shipped under scales_dualquant_rtn_int4/): a dict
+    {"layer<idx>.<sublayer path>": column_scales [in_features] fp32} (keys built in main.py:201),
+    the vectors PermLinear multiplies into the activations."""
+    blob = torch.load(path, map_location="cpu")
+    if not isinstance(blob, dict) or not blob:
+        raise ValueError(f"{path}: not a DualQuant scale file (expected a non-empty dict)")
+    out = {}
+    for key, val in blob.items():
+        if not (isinstance(key, str) and key.startswith("layer") and "." in key):
+            raise ValueError(f"{path}: unexpected key {key!r} (expected 'layer<idx>.<sublayer path>')")
+        if not (torch.is_tensor(val) and val.dim() == 1):
+            raise ValueError(f"{path}: entry {key!r} is not a 1-D tensor")
+        out[key] = val.detach().to(torch.float32)
+    return out
+
+
+def install_column_scales(model: nn.Module, scales: Dict[str, torch.Tensor], strict: bool = True) -> int:
+    """Seeds the activation scale of every PermLinear named by a scale file: key
+    "layer<idx>.<path>" addresses model.model.layers[idx].<path> (the walk of main.py:196-207).
+    Returns the number of layers set; with strict=True a key that does not resolve to a PermLinear
+    of matching width raises."""
+    layers = model.model.layers
+    n = 0
+    for key, vec in scales.items():
+        head, _, path = key.partition(".")
+        mod = layers[int(head[len("layer"):])]
+        try:
+            for part in path.split("."):
+                mod = getattr(mod, part)
+        except AttributeError:
+            if strict:
+                raise KeyError(f"{key}: no such sublayer") from None
+            continue
+        if not isinstance(mod, PermLinear) or mod.layer.in_features != vec.numel():
+            if strict:
+                raise KeyError(f"{key}: not a PermLinear with {vec.numel()} input channels")
+            continue
+        mod.set_act_scale(vec.to(mod.layer.weight.device))
+        n += 1
+    return n
+
+
 def install_from_wrap(parent: nn.Module, attr_name: str, mat_q: torch.Tensor, beta: torch.Tensor,
                       act_fmt, quantize_bmm_input: bool = False) -> PermLinear:
     """Copies mat_q into parent.<attr_name>.weight (as wrap_cached does), wraps the layer with a
@@ -59,4 +103,5 @@ def install_from_wrap(parent: nn.Module, attr_name: str, mat_q: torch.Tensor, be
     return perm
 
 
-__all__ = ["pack_from_dualquant", "load_wrap_cache", "install_from_wrap"]
+__all__ = ["pack_from_dualquant", "load_wrap_cache", "install_from_wrap", "load_column_scales",
+           "install_column_scales"]

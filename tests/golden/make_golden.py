@@ -191,6 +191,16 @@ def main(ref_root: str) -> None:
     out["e4m3_scale_in"] = sgrid.numpy()
     out["e4m3_scale_out"] = scale_formats.quantize_scale_e4m3(sgrid.clone()).numpy()
 
+    # ---- format of the shipped column-scale files (scales_dualquant_rtn_int4/*.pt) -----------------
+    scale_file = os.path.join(ref_root, "scales_dualquant_rtn_int4",
+                              "DQ_Qwen_Qwen3-0.6B_iter15_scale_row_column_row_all_one_col_l1_norm_rtn_int4.pt")
+    blob = torch.load(scale_file, map_location="cpu")
+    keys = sorted(blob.keys())
+    out["beta_file_keys"] = np.array(keys[:14])
+    out["beta_file_count"] = np.array([len(keys)], dtype=np.int32)
+    out["beta_file_widths"] = np.array([blob[k].numel() for k in keys[:14]], dtype=np.int32)
+    out["beta_file_sample"] = blob["layer0.mlp.down_proj"][:32].numpy()
+
     path = os.path.join(here, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, {k: v.shape for k, v in out.items()})

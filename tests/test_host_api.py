@@ -80,3 +80,47 @@ def test_hadamard_generators_reproduce_every_order_of_the_reference_table(golden
         assert kk == k and (h is None) == (k == 1)
     ht, _ = quarot.get_hadK(11008, transpose=True)
     assert torch.equal(ht, quarot.hadamard_of_order(172).T)
+
+
+def test_column_scale_files_load_and_install(tmp_path, golden):
+    """wrap.load_column_scales / install_column_scales on a file with the layout of the reference's
+    shipped scale files (key names and widths of one of them are in the golden fixture)."""
+    import torch
+    import torch.nn as nn
+
+    from dualquant_b200 import formats, wrap
+    from dualquant_b200.activations import PermLinear
+
+    keys = [str(k) for k in golden["beta_file_keys"]]
+    widths = golden["beta_file_widths"].tolist()
+    assert "layer0.mlp.down_proj" in keys and int(golden["beta_file_count"][0]) % 7 == 0
+    blob = {k: torch.rand(w) + 0.5 for k, w in zip(keys, widths)}
+    path = tmp_path / "scales.pt"
+    torch.save(blob, path)
+    scales = wrap.load_column_scales(str(path))
+    assert sorted(scales) == sorted(keys) and all(v.dtype == torch.float32 for v in scales.values())
+
+    fmt = formats.make_format("rtn_int4", block_size=-1)
+
+    def block(idx):
+        layer = nn.Module()
+        for k, w in zip(keys, widths):
+            head, _, p = k.partition(".")
+            if head != f"layer{idx}":
+                continue
+            parent_name, leaf = p.split(".")
+            if not hasattr(layer, parent_name):
+                setattr(layer, parent_name, nn.Module())
+            setattr(getattr(layer, parent_name), leaf, PermLinear(nn.Linear(w, 8, bias=False), fmt))
+        return layer
+
+    n_layers = 1 + max(int(k.split(".")[0][5:]) for k in keys)
+    model = nn.Module()
+    model.model = nn.Module()
+    model.model.layers = nn.ModuleList([block(i) for i in range(n_layers)])
+    assert wrap.install_column_scales(model, scales) == len(keys)
+    got = model.model.layers[0].mlp.down_proj.act_scale
+    assert torch.equal(got, blob["layer0.mlp.down_proj"])
+    torch.save({"oops": torch.ones(3)}, path)
+    with pytest.raises(ValueError):
+        wrap.load_column_scales(str(path))
