@@ -89,7 +89,8 @@ enum {
   DQ_TUNE_FUSED_STAGES = 1,     // ring depth of the one-launch decode kernel
   DQ_TUNE_FUSED_SPLIT = 2,      // its split of K
   DQ_TUNE_FUSED_EXTRA_CTA = 3,  // CTAs' worth of shared memory left free per SM for the next launch
-  DQ_TUNE_COUNT = 4
+  DQ_TUNE_AR_WAIT_LOG2 = 4,     // fused all-reduce: a peer's flag is waited for 2^value SM cycles (0 = 30)
+  DQ_TUNE_COUNT = 5
 };
 int tuning(int key);
 

@@ -40,7 +40,7 @@ int set_error(int code, const char* fmt, ...) {
 
 EncodeTiledFn encode_tiled_fn() { return g_encode; }
 
-static int g_tuning[DQ_TUNE_COUNT] = {0, 0, 0, 1};
+static int g_tuning[DQ_TUNE_COUNT] = {0, 0, 0, 1, 0};
 int tuning(int key) { return (key >= 0 && key < DQ_TUNE_COUNT) ? g_tuning[key] : 0; }
 
 int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t row_bytes, uint64_t rows,
@@ -113,7 +113,7 @@ extern "C" int dq_abi_version(void) { return 2; }
 
 extern "C" int dq_set_tuning(const char* name, int value) {
   static const char* const names[DQ_TUNE_COUNT] = {"linear_fused", "fused_stages", "fused_split",
-                                                   "fused_extra_cta"};
+                                                   "fused_extra_cta", "ar_wait_log2"};
   DQ_REQUIRE(name != nullptr, DQ_ERR_NULL, "null tuning name");
   for (int i = 0; i < DQ_TUNE_COUNT; ++i) {
     if (strcmp(name, names[i]) == 0) {

@@ -71,6 +71,7 @@ struct ArDev {
   const uint32_t* seq;   // this rank's call counter
   int rank, world;
   uint32_t cap;          // floats per parity half
+  long long wait_cycles; // how long a peer's flag is waited for before the kernel gives up
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -388,7 +389,7 @@ gemv_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
           const uint32_t* f = ar.flags[ar.rank] + unit * 8u + tid;
           const long long t_start = clock64();
           while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
-            if (clock64() - t_start > (1ll << 30) || *abort_flag != 0) {
+            if (clock64() - t_start > ar.wait_cycles || *abort_flag != 0) {
               *abort_flag = VSITE_ALLREDUCE;
               break;
             }
@@ -529,6 +530,8 @@ int launch_gemv_int4(const int8_t* codes, const float* sx, const uint8_t* w_pack
     ar.rank = ctx->rank;
     ar.world = ctx->world;
     ar.cap = static_cast<uint32_t>(ctx->buf_capacity_floats);
+    const int wl = tuning(DQ_TUNE_AR_WAIT_LOG2);
+    ar.wait_cycles = 1ll << ((wl >= 10 && wl <= 40) ? wl : 30);  // default: about half a second
   }
   int rc;
   if (tok != 8 && tok != 16 && tok != 32)

@@ -87,7 +87,8 @@ DQ_API int dq_abi_version(void);
  * Triton kernels autotune instead: vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:26-53).
  * name (host string): "linear_fused" (1 = dq_linear_w4a4_int4 runs decode batches, M <= 16, as one
  * launch that quantises inside the GEMM kernel; 0 = quantiser + GEMM, the default), "fused_stages", "fused_split", "fused_extra_cta"
- * (0 = the library's own choice).  Process-wide, not thread-safe against concurrent launches. */
+ * (0 = the library's own choice), "ar_wait_log2" (the fused all-reduce waits 2^value SM cycles for a
+ * peer before it gives up with DQ_ERR_TIMEOUT; 0 = 30, about half a second).  Process-wide, not thread-safe against concurrent launches. */
 DQ_API int dq_set_tuning(const char* name, int value);
 
 /* Tensor-core ceiling probe: launches, on every SM, a loop of `iters` x 4 tcgen05.mma instructions

@@ -124,3 +124,15 @@ def test_column_scale_files_load_and_install(tmp_path, golden):
     torch.save({"oops": torch.ones(3)}, path)
     with pytest.raises(ValueError):
         wrap.load_column_scales(str(path))
+
+
+def test_status_word_decoding():
+    """dq_device_status packs DQ_ERR_TIMEOUT with the site code in the upper 16 bits; the binding
+    raises RuntimeError for it (not ValueError: it is not an argument error)."""
+    from dualquant_b200 import _lib
+
+    with pytest.raises(RuntimeError, match="DQ_ERR_TIMEOUT"):
+        _lib.check(_lib.DQ_ERR_TIMEOUT | (23 << 16), "dq_device_status")
+    with pytest.raises(ValueError, match="DQ_ERR_SHAPE"):
+        _lib.check(1, "dq_x")
+    _lib.check(0, "dq_x")
