@@ -133,6 +133,17 @@ class PermLinear(nn.Module):
             return None
         return _lib.FP4_MXFP4 if name == "mxfp4" else _lib.FP4_NVFP4
 
+    def _a16w4_ready(self) -> bool:
+        """True when the layer can run 16-bit activations against its packed int4 weight: no online
+        Hadamard, K a multiple of the group size, and the weight on the int4 grid (packs on demand)."""
+        if self.online_full_had or self.online_partial_had or self.layer.in_features % GROUP != 0:
+            return False
+        if not self.layer.weight.is_cuda:
+            return False
+        if self._packed is None and self._weight_on_grid is None:
+            self.pack()
+        return self._packed is not None
+
     def _int4_path(self) -> bool:
         return (self.act_quant_enabled and getattr(self.act_fmt, "name", None) == "rtn_int4"
                 and self.act_fmt.block_size == -1 and self.layer.in_features % GROUP == 0)
@@ -202,6 +213,16 @@ class PermLinear(nn.Module):
             if self.layer.bias is not None:
                 out = out + self.layer.bias
             out = out.reshape(x.shape[:-1] + (self._packed_fp4.N,))
+        elif (not self.act_quant_enabled and self._a16w4_ready()
+              and x.dtype == torch.bfloat16 and self.dtype == torch.bfloat16):
+            # activation cast switched off on a W4 layer: bf16(x * act_scale) against the packed int4
+            # weight on the bf16 tensor cores (the reference multiplies by its 16-bit fake-quant copy)
+            pw = self._packed
+            x2 = x.reshape(-1, x.shape[-1])
+            out = ops.linear_a16w4(x2, self.act_scale, pw, None, out_dtype=torch.bfloat16)
+            if self.layer.bias is not None:
+                out = out + self.layer.bias
+            out = out.reshape(x.shape[:-1] + (pw.N,))
         else:
             out = self.layer(self._quantise_act(x))
         if self.quantize_bmm_input:

@@ -25,6 +25,7 @@ SOURCES = [
     "gemm_fp4.cu",
     "linear_w4a4.cu",
     "mma_peak.cu",
+    "gemm_a16w4.cu",
 ]
 
 NVCC_FLAGS = [

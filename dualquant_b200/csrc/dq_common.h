@@ -102,6 +102,7 @@ int init_gemm_fp4_kernels();
 int init_act_quant_kernels();
 int init_gemv_fused_kernels();
 int init_mma_peak_kernels();
+int init_gemm_a16w4_kernels();
 
 // One-launch decode linear (quantiser inside the GEMM kernel), defined in gemv_w4a4_int4_fused.cu.
 bool gemv_fused_covers(int M, int N, int K, const DeviceState* st);

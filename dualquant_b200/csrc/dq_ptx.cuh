@@ -295,11 +295,12 @@ __device__ __forceinline__ void store_y(void* y, const void* residual, int y_bf1
     if (residual != nullptr) {
       const float lin = __uint_as_float(static_cast<uint32_t>(bits) << 16);
       const float res = __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(residual)[idx]) << 16);
-      asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(bits) : "f"(lin + res));
+      asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(bits) : "f"(__fadd_rn(lin, res)));
     }
     reinterpret_cast<unsigned short*>(y)[idx] = bits;
   } else {
-    if (residual != nullptr) val += reinterpret_cast<const float*>(residual)[idx];
+    // (an explicit add: the product that formed val must not be contracted into an FMA with it)
+    if (residual != nullptr) val = __fadd_rn(val, reinterpret_cast<const float*>(residual)[idx]);
     reinterpret_cast<float*>(y)[idx] = val;
   }
 }

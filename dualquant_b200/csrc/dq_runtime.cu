@@ -166,6 +166,8 @@ extern "C" int dq_init(int device) {
   if (rc != DQ_OK) return rc;
   rc = init_mma_peak_kernels();
   if (rc != DQ_OK) return rc;
+  rc = init_gemm_a16w4_kernels();
+  if (rc != DQ_OK) return rc;
   DQ_CHECK_CUDA(cudaDeviceSynchronize());
   st->ready = true;
   return DQ_OK;

@@ -362,6 +362,32 @@ def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[H
     return out
 
 
+def linear_a16w4(x: torch.Tensor, a: Optional[torch.Tensor], pw: PackedInt4Weight,
+                 r: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+                 scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 activations (times the column scale a, rounded to bf16) against the int4 weight
+    artefact on the bf16 tensor cores: Y = r * (bf16(x * a) @ bf16(codes * group scale)^T)."""
+    lib = _prep(x)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("linear_a16w4 expects bf16 activations")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    M, K = x.shape
+    if K != pw.K:
+        raise ValueError(f"K mismatch: activations {K}, weight {pw.K}")
+    need = int(lib.dq_linear_a16w4_scratch_bytes(M, pw.N, K)) if a is not None else 0
+    if a is not None and (scratch is None or scratch.numel() < need):
+        scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty(M, pw.N, dtype=out_dtype, device=x.device)
+    ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    _lib.check(lib.dq_linear_a16w4(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), _ptr(pw.w_packed), _ptr(r),
+                                   M, pw.N, K, pw.group, _ptr(out), ydt, _ptr(scratch),
+                                   0 if scratch is None else scratch.numel(), _stream(x.device)),
+               "dq_linear_a16w4")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 # block-scaled FP4
 # ---------------------------------------------------------------------------------------------

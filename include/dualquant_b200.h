@@ -369,6 +369,22 @@ DQ_API int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float* a,
                         int scale_fp16, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * A16W4: 16-bit activations against the int4 weight artefact - the reference's fused-beta kernel
+ * (vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:55-149, wrapper :220-262) and what
+ * PermLinear computes when its activation cast is switched off (activations/perm_linear.py:108-141
+ * with act_quant_enabled = False):
+ *   Y[m,n] = r[n] * sum_k bf16(x[m,k] * a[k]) * bf16(qw[n,k] * sw[n,k/128])
+ * on tcgen05 kind::f16 (bf16 operands, fp32 accumulation).  The group scale is rounded to bf16 before
+ * it multiplies the code, as in the reference kernel, whose scales are bf16 (:186).  a may be null
+ * (no scale pass, scratch unused); otherwise scratch holds bf16(x * a):
+ * dq_linear_a16w4_scratch_bytes(M,N,K) bytes, 256-byte aligned.
+ */
+DQ_API size_t dq_linear_a16w4_scratch_bytes(int M, int N, int K);
+DQ_API int dq_linear_a16w4(const void* x_bf16, int64_t ldx, const float* a, const uint8_t* w_packed,
+                           const float* r, int M, int N, int K, int G, void* y, int y_dtype,
+                           void* scratch, size_t scratch_bytes, void* stream);
+
+/*
  * dq_linear_w4a4_int4 for callers that cannot hand the library any scratch memory.  (No
  * counterpart in the reference: its real-kernel path keeps torch-allocated buffers on the
  * module, ablation/real_int4_kernel/full_model_nunchaku.py:95-104.)
