@@ -705,8 +705,15 @@ def run_prefill_suite(args, emit=True):
                                                        scratch=scratch, out=y), dev)
         ms_gemm = _time_loop(g_gemm.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
         ms_full = _time_loop(g_full.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        # the A16W4 variant (bf16 activations x int4 weights, tcgen05 kind::f16) on the same operands
+        yb = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        s16 = torch.empty(M * K * 2 + 256, dtype=torch.uint8, device=dev)
+        g_a16 = _capture(lambda: ops.linear_a16w4(x, a, pw, r, scratch=s16, out=yb), dev)
+        ms_a16 = _time_loop(g_a16.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        del g_a16, yb, s16
         ops_ = 2.0 * M * N * K
         rows.append({"shape": label, "M": M, "K": K, "N": N,
+                     "a16w4_linear_us": round(ms_a16 * 1e3, 1), "a16w4_TFLOPS": round(ops_ / ms_a16 / 1e9, 1),
 
                      "gemm_us": round(ms_gemm * 1e3, 1), "gemm_TOPS": round(ops_ / ms_gemm / 1e9, 1),
                      "linear_us": round(ms_full * 1e3, 1), "linear_TOPS": round(ops_ / ms_full / 1e9, 1),
@@ -1199,6 +1206,11 @@ def run_reference_gpu(args, emit=True):
         scratch = torch.empty(max(256, ops.linear_scratch_bytes(M, N, K)), dtype=torch.uint8, device=dev)
         g_own = _capture(lambda: ops.linear_w4a4_int4(x, a32, None, pw, None, scratch=scratch, out=y), dev)
         row["dualquant_b200_linear_us"] = round(_time_loop(g_own.replay, 20, 5, dev, lambda: None) / 20 * 1e3, 1)
+        yb = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        s16 = torch.empty(M * K * 2 + 256, dtype=torch.uint8, device=dev)
+        g_a16 = _capture(lambda: ops.linear_a16w4(x, a32, pw, None, scratch=s16, out=yb), dev)
+        row["dualquant_b200_a16w4_us"] = round(_time_loop(g_a16.replay, 20, 5, dev, lambda: None) / 20 * 1e3, 1)
+        del g_a16, yb, s16
         for kname, fn, gs, mod in (("triton_fused_w4a4_gemm_g64", "fused_w4a4_gemm", 64, fwk),
                                    ("triton_fused_beta_int4_gemm_g32", "fused_beta_int4_gemm", 32, fdk)):
             try:

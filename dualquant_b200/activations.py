@@ -133,6 +133,12 @@ class PermLinear(nn.Module):
             return None
         return _lib.FP4_MXFP4 if name == "mxfp4" else _lib.FP4_NVFP4
 
+    def _bf16_arith(self, x2: torch.Tensor) -> bool:
+        """The reference upcasts to fp32 only when an activation scale or an online Hadamard is
+        configured; otherwise a bf16 input is quantised in bf16 arithmetic (perm_linear.py:109-133)."""
+        return (x2.dtype == torch.bfloat16 and self.act_scale is None
+                and not (self.online_full_had or self.online_partial_had))
+
     def _a16w4_ready(self) -> bool:
         """True when the layer can run 16-bit activations against its packed int4 weight: no online
         Hadamard, K a multiple of the group size, and the weight on the int4 grid (packs on demand)."""
@@ -157,7 +163,8 @@ class PermLinear(nn.Module):
         if self.act_quant_enabled:
             if getattr(self.act_fmt, "name", None) == "rtn_int4" and self.act_fmt.block_size == -1:
                 xin = x2 if x2.dtype in (torch.bfloat16, torch.float32) else x2.float()
-                out = ops.fakequant_act_int4(xin.contiguous(), self.act_scale, had, scale_fp16=False)
+                out = ops.fakequant_act_int4(xin.contiguous(), self.act_scale, had, scale_fp16=False,
+                                             bf16_arith=self._bf16_arith(xin))
             else:
                 x32 = x2.float()
                 if self.act_scale is not None:
@@ -191,8 +198,11 @@ class PermLinear(nn.Module):
                 self._scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
             out_dtype = self.dtype if self.dtype in (torch.bfloat16, torch.float32) else torch.float32
             if x2.dtype == torch.bfloat16:
+                # without an activation scale and a Hadamard the reference quantises in the input
+                # dtype, i.e. in bf16 arithmetic (perm_linear.py:109-133); same here
                 out = ops.linear_w4a4_int4(x2, self.act_scale, self._hadamard(x.device), pw, None,
-                                           out_dtype=out_dtype, scale_fp16=False, scratch=self._scratch)
+                                           out_dtype=out_dtype, scale_fp16=False, scratch=self._scratch,
+                                           bf16_arith=self._bf16_arith(x2))
             else:
                 # the reference upcasts to fp32 before scaling and quantising (perm_linear.py:119-125):
                 # fp32 / fp16 inputs go through the fp32 quantiser, not through a bf16 rounding

@@ -120,8 +120,32 @@ struct Raw8<float> {
 };
 
 __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t* codes_row,
-                                      float* out_row, int idx) {
+                                      float* out_row, int idx, int smode = 0) {
   const float inv_s = __fdiv_rn(1.0f, s);
+  if (smode == 2 && mode != MODE_RAW) {
+    // bf16 arithmetic (see token_scale): codes, or the de-quantised value q * s as fp32 / bf16
+    float q[8];
+    quant_codes8_bf16(v, s, q);
+    if (mode == MODE_CODES) {
+      *reinterpret_cast<uint2*>(codes_row + idx) =
+          make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
+    } else if (mode == MODE_FAKE_BF16) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(q[2 * e], s), __fmul_rn(q[2 * e + 1], s));
+        w[e] = *reinterpret_cast<const uint32_t*>(&pr);
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out_row) + idx) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = round_to_bf16(__fmul_rn(q[e], s));
+      *reinterpret_cast<float4*>(out_row + idx) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4*>(out_row + idx + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+    return;
+  }
   if (mode == MODE_CODES) {
     float q[8];
     quant_codes8(v, s, inv_s, q);
@@ -250,12 +274,12 @@ act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __rest
     const int idx = (i * THREADS + threadIdx.x) * 8;
     if (idx < K) {
       if constexpr (KEEP) {
-        emit8(kept[i], s, mode, crow, orow, idx);
+        emit8(kept[i], s, mode, crow, orow, idx, scale_fp16);
       } else {
         float v[8];
         raw[i].expand(v);
         prologue(v, idx);
-        emit8(v, s, mode, crow, orow, idx);
+        emit8(v, s, mode, crow, orow, idx, scale_fp16);
       }
     }
   }
@@ -367,7 +391,7 @@ act_quant_had_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = row[idx + e];
-    emit8(v, s, mode, crow, orow, idx);
+    emit8(v, s, mode, crow, orow, idx, scale_fp16);
   }
 }
 
@@ -445,7 +469,7 @@ act_quant_had_big_kernel(const XT* __restrict__ x, const XT* __restrict__ up, in
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = res[idx + e];
-    emit8(v, s, mode, crow, orow, idx);
+    emit8(v, s, mode, crow, orow, idx, scale_fp16);
   }
 }
 
@@ -603,7 +627,7 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = row[idx + e];
-    emit8(v, s, mode, crow, orow, idx);
+    emit8(v, s, mode, crow, orow, idx, scale_fp16);
   }
 }
 

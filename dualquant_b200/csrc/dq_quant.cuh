@@ -7,10 +7,21 @@
 
 namespace dq {
 
+__device__ __forceinline__ float round_to_bf16(float v) {
+  unsigned short bits;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(bits) : "f"(v));
+  return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+}
+
+// scale_fp16: 0 = fp32 scale, 1 = scale rounded to fp16, 2 = "bf16 arithmetic": the quantiser as
+// torch evaluates it on a bf16 tensor (every intermediate rounded to bf16), which is what the
+// reference's PermLinear does when there is neither an activation scale nor an online Hadamard
+// (activations/perm_linear.py:131-133 with formats/rtn_int.py:62-67).
 __device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
   float s = __fdiv_rn(amax, 7.0f);
+  if (scale_fp16 == 2) s = round_to_bf16(s);
   if (amax == 0.f) s = 1.0f;
-  if (scale_fp16) {
+  if (scale_fp16 == 1) {
     s = __half2float(__float2half_rn(fminf(s, 65504.0f)));
     if (s == 0.f) s = 1.0f;
   }
@@ -45,6 +56,12 @@ __device__ __forceinline__ void quant_codes8(const float* v, float s, float inv_
 #pragma unroll
     for (int e = 0; e < 8; ++e) q[e] = fminf(fmaxf(rintf(__fdiv_rn(v[e], s)), -8.0f), 7.0f);
   }
+}
+// The same in bf16 arithmetic: the quotient is rounded to bf16 before it is rounded to an integer.
+__device__ __forceinline__ void quant_codes8_bf16(const float* v, float s, float* q) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    q[e] = fminf(fmaxf(rintf(round_to_bf16(__fdiv_rn(v[e], s))), -8.0f), 7.0f);
 }
 // four codes in [-8, 7] (as floats) -> four int8 in one word, first code in the low byte
 __device__ __forceinline__ uint32_t pack_codes4(float q0, float q1, float q2, float q3) {

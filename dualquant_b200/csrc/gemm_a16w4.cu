@@ -1,30 +1,34 @@
 // A16W4 dual-scale linear for sm_100a: 16-bit activations against the int4 weight artefact,
 //
-//   Y[m,n] = r[n] * sum_k bf16(x[m,k] * a[k]) * bf16(qw[n,k] * sw[n, k/128])
+//   Y[m,n] = r[n] * sum_k fp16(x[m,k] * a[k]) * fp16(qw[n,k] * sw[n, k/128])
 //
 // the computation of the reference's fused-beta Triton kernel
 // (vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:55-149: beta multiplied into the
 // activation tile on its way in, nibbles de-quantised with the group scale, floating-point dot
-// product) on the tensor cores of this GPU: tcgen05.mma kind::f16 with bf16 operands and ONE fp32
-// accumulator in tensor memory over the whole K (the group scale is folded into the bf16 weight,
-// so nothing has to be drained per group).
+// product) on the tensor cores of this GPU: tcgen05.mma kind::f16 with fp16 operands and ONE fp32
+// accumulator in tensor memory over the whole K (the group scale is folded into the fp16 weight,
+// so nothing has to be drained per group).  fp16 rather than bf16 operands: with 8-bit mantissas
+// the reference's own acceptance check (mean relative error below 1 % against the fp32 formulation,
+// fused_dual_scale_kernel.py:269-308) fails at 1.4-5.7 %, with 11-bit mantissas it passes at
+// 0.25-0.4 %; the group scales are fp16 already, so code * scale is one exactly rounded product.
+// Activations beyond the fp16 range saturate at +-65504.
 //
 // Orientation as in the int4 kernels: the CTA's 128 weight rows are the UMMA M dimension, the token
 // tile TN is UMMA N.  Per weight group (128 k, one pipeline step):
 //   producer warp   one bulk copy of the packed tile (8 KB codes + 256 B fp16 scales) and two tiled
-//                   copies of the activation tile (TN x 64 bf16 each, 128-byte swizzle);
-//   8 unpack warps  thread (row, half) expands 32 bytes of nibbles into 64 bf16 = code * scale and
+//                   copies of the activation tile (TN x 64 fp16 each, 128-byte swizzle);
+//   8 unpack warps  thread (row, half) expands 32 bytes of nibbles into 64 fp16 = code * scale and
 //                   writes them as eight 16-byte pieces into the 128B-swizzled K-major operand tile.
-//                   A nibble pair becomes bf16x2 by bit tricks: (w >> s) & 0x000F000F picks two
-//                   two's-complement nibbles, ^ 0x43084308 turns them into the bf16 numbers
-//                   136 + code, a packed subtract gives code exactly and a packed multiply by the
-//                   group scale (rounded to bf16, the reference kernel's own scale type) the weight;
+//                   A nibble pair becomes half2 by bit tricks: (w >> s) & 0x000F000F picks two
+//                   two's-complement nibbles, ^ 0x64086408 turns them into the fp16 numbers
+//                   1032 + code, a packed subtract gives code exactly and a packed multiply by the
+//                   fp16 group scale the weight;
 //   issuing warp    eight tcgen05.mma (K = 16) per group, tcgen05.commit frees the operand buffers.
 // After the last group the first four unpack warps read the accumulator (one weight row per
 // thread), multiply by r[n] and store bf16 or fp32.  Every wait is bounded.
 //
-// The activation scale runs as a small separate pass (xs = bf16(x * a), caller scratch) so that
-// the GEMM can stage activations with TMA.
+// The activation scale and the conversion to fp16 run as a small separate pass
+// (xs = fp16(x * a), caller scratch) so that the GEMM can stage activations with TMA.
 #include "dq_common.h"
 #include "dq_ptx.cuh"
 
@@ -39,7 +43,7 @@ constexpr int kUnpackWarps = 8;
 constexpr int kProducerWarp = kUnpackWarps;
 constexpr int kIssuerWarp = kUnpackWarps + 1;
 constexpr int kThreads = (kUnpackWarps + 2) * 32;
-constexpr int kWTile = kBN * kGroup * 2;  // bf16 weight tile of one group: 32 KB (two 16 KB atoms)
+constexpr int kWTile = kBN * kGroup * 2;  // fp16 weight tile of one group: 32 KB (two 16 KB atoms)
 constexpr int kAtom = kBN * 128;          // 128 rows x 128 B
 
 enum { ASITE_TMA = 51, ASITE_UNPACK = 52, ASITE_MMA = 53, ASITE_EPI = 54, ASITE_ALIGN = 55 };
@@ -49,7 +53,7 @@ struct Cfg {
   static constexpr int NB = 2;                      // unpacked weight buffers
   static constexpr int SP = 4;                      // packed-tile stages
   static constexpr int SX = (TN <= 64) ? 4 : 3;     // activation stages
-  static constexpr int kXStage = TN * kGroup * 2;   // TN x 128 bf16 = two atoms of TN x 128 B
+  static constexpr int kXStage = TN * kGroup * 2;   // TN x 128 fp16 = two atoms of TN x 128 B
   static constexpr int kXAtom = TN * 128;
   static constexpr int kOffW = 0;
   static constexpr int kOffX = kOffW + NB * kWTile;
@@ -63,12 +67,11 @@ struct Cfg {
   static_assert(kOffX % 1024 == 0 && kXStage % 1024 == 0 && kXAtom % 1024 == 0, "swizzle atoms on 1 KB boundaries");
 };
 
-// Instruction descriptor, kind::f16: bf16 A and B (both K-major), fp32 accumulator.
-//   [4,6) D format (1 = F32)  [7,10) A format (1 = BF16)  [10,13) B format (1 = BF16)
+// Instruction descriptor, kind::f16: fp16 A and B (both K-major), fp32 accumulator.
+//   [4,6) D format (1 = F32)  [7,10) A format (0 = F16)  [10,13) B format (0 = F16)
 //   [17,23) N >> 3  [24,29) M >> 4
-__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -83,23 +86,23 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
-// two two's-complement nibbles (bits 0-3 and 16-19 of t) -> bf16x2 (code * scale)
-__device__ __forceinline__ uint32_t nib2_to_bf16x2(uint32_t t, __nv_bfloat162 s2) {
-  const uint32_t biased = (t & 0x000F000Fu) ^ 0x43084308u;  // bf16 numbers 136 + code
-  __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&biased);
-  const uint32_t k136 = 0x43084308u;
-  v = __hsub2(v, *reinterpret_cast<const __nv_bfloat162*>(&k136));  // exact: small integers
-  v = __hmul2(v, s2);
+// two two's-complement nibbles (bits 0-3 and 16-19 of t) -> half2 (code * scale)
+__device__ __forceinline__ uint32_t nib2_to_f16x2(uint32_t t, __half2 s2) {
+  const uint32_t biased = (t & 0x000F000Fu) ^ 0x64086408u;  // fp16 numbers 1024 + 8 + code
+  __half2 v = *reinterpret_cast<const __half2*>(&biased);
+  const uint32_t k1032 = 0x64086408u;
+  v = __hsub2(v, *reinterpret_cast<const __half2*>(&k1032));  // exact: small integers
+  v = __hmul2(v, s2);                                          // one rounding: fp16(code * scale)
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // Eight consecutive k of one row: the low (HI = 0) or high (HI = 1) nibbles of packed words wa, wb.
 template <int HI>
-__device__ __forceinline__ uint4 expand8(uint32_t wa, uint32_t wb, __nv_bfloat162 s2) {
+__device__ __forceinline__ uint4 expand8(uint32_t wa, uint32_t wb, __half2 s2) {
   // byte b of a word: nibble of k = 4j + b (low) or 16 + 4j + b (high).  (w >> s) & 0x000F000F
   // picks bytes 0 and 2, (w >> (s + 8)) bytes 1 and 3.
-  const uint32_t a02 = nib2_to_bf16x2(wa >> (4 * HI), s2), a13 = nib2_to_bf16x2(wa >> (4 * HI + 8), s2);
-  const uint32_t b02 = nib2_to_bf16x2(wb >> (4 * HI), s2), b13 = nib2_to_bf16x2(wb >> (4 * HI + 8), s2);
+  const uint32_t a02 = nib2_to_f16x2(wa >> (4 * HI), s2), a13 = nib2_to_f16x2(wa >> (4 * HI + 8), s2);
+  const uint32_t b02 = nib2_to_f16x2(wb >> (4 * HI), s2), b13 = nib2_to_f16x2(wb >> (4 * HI + 8), s2);
   uint4 o;
   o.x = __byte_perm(a02, a13, 0x5410);  // (k0, k1)
   o.y = __byte_perm(a02, a13, 0x7632);  // (k2, k3)
@@ -189,7 +192,7 @@ gemm_a16w4_kernel(const uint8_t* __restrict__ w_packed, const __grid_constant__ 
   } else if (warp == kIssuerWarp) {
     // ------------------------------------------------------------------ UMMA issue
     if (lane == 0) {
-      const uint32_t idesc = idesc_bf16(kBN, TN);
+      const uint32_t idesc = idesc_f16(kBN, TN);
       for (int i = 0; i < ng; ++i) {
         const int b = i % C::NB, sx = i % C::SX;
         if (!mbar_wait(&w_ready[b], (i / C::NB) & 1, abort_flag, ASITE_MMA)) break;
@@ -220,7 +223,7 @@ gemm_a16w4_kernel(const uint8_t* __restrict__ w_packed, const __grid_constant__ 
       if (!mbar_wait(&w_free[b], ((i / C::NB) & 1) ^ 1, abort_flag, ASITE_UNPACK)) { ok = false; break; }
       const uint8_t* tile = smem + C::kOffP + sp * C::kPStage;
       const __half sc = reinterpret_cast<const __half*>(tile + kTileCodeBytes)[row];
-      const __nv_bfloat162 s2 = __float2bfloat162_rn(__half2float(sc));
+      const __half2 s2 = __half2half2(sc);
       uint8_t* dst = smem + C::kOffW + b * kWTile + half * kAtom + row * 128;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
@@ -271,10 +274,10 @@ gemm_a16w4_kernel(const uint8_t* __restrict__ w_packed, const __grid_constant__ 
   if (tid == 0 && *abort_flag != 0) atomicCAS(status, 0, *abort_flag);
 }
 
-// xs[m, k] = bf16(float(x[m, k]) * a[k])
-__global__ void __launch_bounds__(256) scale_cols_bf16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
-                                                              const float* __restrict__ a, int M, int K,
-                                                              __nv_bfloat16* __restrict__ xs) {
+// xs[m, k] = fp16(float(x[m, k]) * a[k]) (a may be null), saturating at the fp16 range
+__global__ void __launch_bounds__(256) scale_cols_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx,
+                                                             const float* __restrict__ a, int M, int K,
+                                                             __half* __restrict__ xs) {
   grid_dep_launch_dependents();
   grid_dep_wait();
   const int vec = K / 8;
@@ -283,16 +286,20 @@ __global__ void __launch_bounds__(256) scale_cols_bf16_kernel(const __nv_bfloat1
        u += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int m = static_cast<int>(u / vec), kv = static_cast<int>(u % vec);
     const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(m) * ldx + kv * 8);
-    const float4 a0 = *reinterpret_cast<const float4*>(a + kv * 8);
-    const float4 a1 = *reinterpret_cast<const float4*>(a + kv * 8 + 4);
+    float av[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+    if (a != nullptr) {
+      const float4 a0 = *reinterpret_cast<const float4*>(a + kv * 8);
+      const float4 a1 = *reinterpret_cast<const float4*>(a + kv * 8 + 4);
+      av[0] = a0.x; av[1] = a0.y; av[2] = a0.z; av[3] = a0.w;
+      av[4] = a1.x; av[5] = a1.y; av[6] = a1.z; av[7] = a1.w;
+    }
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
     uint32_t o[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float lo = __fmul_rn(__uint_as_float(w[i] << 16), av[2 * i]);
-      const float hi = __fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), av[2 * i + 1]);
-      const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+      const float lo = fminf(fmaxf(__fmul_rn(__uint_as_float(w[i] << 16), av[2 * i]), -65504.f), 65504.f);
+      const float hi = fminf(fmaxf(__fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), av[2 * i + 1]), -65504.f), 65504.f);
+      const __half2 p = __floats2half2_rn(lo, hi);
       o[i] = *reinterpret_cast<const uint32_t*>(&p);
     }
     *reinterpret_cast<uint4*>(xs + static_cast<int64_t>(m) * K + kv * 8) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -350,23 +357,19 @@ extern "C" int dq_linear_a16w4(const void* x_bf16, int64_t ldx, const float* a, 
   DQ_REQUIRE(aligned(x_bf16, 16) && aligned(w_packed, 16) && ldx % 8 == 0 && ldx >= K, DQ_ERR_ALIGN,
              "x and w_packed must be 16-byte aligned, ldx a multiple of 8 and >= K");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const void* xs = x_bf16;
-  int64_t ld = ldx;
-  if (a != nullptr) {
-    DQ_REQUIRE(aligned(a, 16), DQ_ERR_ALIGN, "a must be 16-byte aligned");
-    DQ_REQUIRE(scratch != nullptr && aligned(scratch, 256), DQ_ERR_ALIGN, "scratch must be non-null and 256-byte aligned");
-    DQ_REQUIRE(scratch_bytes >= dq_linear_a16w4_scratch_bytes(M, N, K), DQ_ERR_WORKSPACE,
-               "scratch of %zu bytes is smaller than the %zu required", scratch_bytes,
-               dq_linear_a16w4_scratch_bytes(M, N, K));
-    const int64_t vecs = static_cast<int64_t>(M) * (K / 8);
-    int blocks = static_cast<int>((vecs + 255) / 256);
-    if (blocks > st->sm_count * 8) blocks = st->sm_count * 8;
-    DQ_CHECK_CUDA(launch_pdl(a16::scale_cols_bf16_kernel, dim3(blocks), dim3(256), 0, s,
-                             static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, M, K,
-                             static_cast<__nv_bfloat16*>(scratch)));
-    xs = scratch;
-    ld = K;
-  }
+  DQ_REQUIRE(a == nullptr || aligned(a, 16), DQ_ERR_ALIGN, "a must be 16-byte aligned");
+  DQ_REQUIRE(scratch != nullptr && aligned(scratch, 256), DQ_ERR_ALIGN, "scratch must be non-null and 256-byte aligned");
+  DQ_REQUIRE(scratch_bytes >= dq_linear_a16w4_scratch_bytes(M, N, K), DQ_ERR_WORKSPACE,
+             "scratch of %zu bytes is smaller than the %zu required", scratch_bytes,
+             dq_linear_a16w4_scratch_bytes(M, N, K));
+  const int64_t vecs = static_cast<int64_t>(M) * (K / 8);
+  int blocks = static_cast<int>((vecs + 255) / 256);
+  if (blocks > st->sm_count * 8) blocks = st->sm_count * 8;
+  DQ_CHECK_CUDA(launch_pdl(a16::scale_cols_f16_kernel, dim3(blocks), dim3(256), 0, s,
+                           static_cast<const __nv_bfloat16*>(x_bf16), ldx, a, M, K,
+                           static_cast<__half*>(scratch)));
+  const void* xs = scratch;
+  const int64_t ld = K;
   if (M <= 32) return a16::launch<32>(xs, ld, w_packed, r, M, N, K, y, y_dtype, s, st);
   return a16::launch<128>(xs, ld, w_packed, r, M, N, K, y, y_dtype, s, st);
 }

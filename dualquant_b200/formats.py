@@ -37,7 +37,9 @@ def _rtn_int4_cast(W: torch.Tensor, block_size: int) -> torch.Tensor:
     x = W.reshape(-1, bs)
     if x.dtype not in (torch.float32, torch.bfloat16):
         x = x.to(torch.float32)
-    out = ops.fakequant_act_int4(x.contiguous(), None, None, scale_fp16=False)
+    # a bf16 tensor is cast in bf16 arithmetic, as torch evaluates the reference's expression on it
+    out = ops.fakequant_act_int4(x.contiguous(), None, None, scale_fp16=False,
+                                 bf16_arith=(x.dtype == torch.bfloat16))
     return out.reshape(orig_shape).to(orig_dtype)
 
 

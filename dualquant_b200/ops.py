@@ -103,8 +103,16 @@ def unpack_w_int4(pw: PackedInt4Weight) -> torch.Tensor:
     return codes
 
 
+def _scale_mode(scale_fp16: bool, bf16_arith: bool) -> int:
+    """The C ABI's scale_fp16 argument: 0 = fp32 token scale, 1 = rounded to fp16, 2 = the whole
+    quantiser in bf16 arithmetic (the reference's path without activation scale and Hadamard)."""
+    if bf16_arith and scale_fp16:
+        raise ValueError("bf16 arithmetic and an fp16 token scale exclude each other")
+    return 2 if bf16_arith else int(bool(scale_fp16))
+
+
 def quant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
-                   had: Optional[Hadamard] = None, scale_fp16: bool = False):
+                   had: Optional[Hadamard] = None, scale_fp16: bool = False, bf16_arith: bool = False):
     """bf16 or fp32 [M,K] -> (codes int8 [M,K], sx fp32 [M])."""
     lib = _prep(x)
     if x.dtype not in (torch.bfloat16, torch.float32):
@@ -118,7 +126,7 @@ def quant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
     fn, what = ((lib.dq_quant_act_int4, "dq_quant_act_int4") if x.dtype == torch.bfloat16
                 else (lib.dq_quant_act_int4_f32, "dq_quant_act_int4_f32"))
     _lib.check(fn(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), desc, M, K, _ptr(codes), _ptr(sx),
-                  int(scale_fp16), _stream(x.device)), what)
+                  _scale_mode(scale_fp16, bf16_arith), _stream(x.device)), what)
     return codes, sx
 
 
@@ -161,7 +169,8 @@ def quant_act_int4_rmsnorm(x: torch.Tensor, norm_weight: Optional[torch.Tensor],
 
 
 def fakequant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
-                       had: Optional[Hadamard] = None, scale_fp16: bool = False) -> torch.Tensor:
+                       had: Optional[Hadamard] = None, scale_fp16: bool = False,
+                       bf16_arith: bool = False) -> torch.Tensor:
     """[M,K] bf16 or fp32 -> de-quantised fp32 [M,K] (what FormatSpec.cast returns)."""
     lib = _prep(x)
     if x.dtype not in (torch.bfloat16, torch.float32):
@@ -171,7 +180,8 @@ def fakequant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
     out = torch.empty(M, K, dtype=torch.float32, device=x.device)
     desc = had.desc() if had is not None else None
     _lib.check(lib.dq_fakequant_act_int4(_ptr(x), int(x.dtype == torch.float32), K, _ptr(a), desc,
-                                         M, K, _ptr(out), int(scale_fp16), _stream(x.device)),
+                                         M, K, _ptr(out), _scale_mode(scale_fp16, bf16_arith),
+                                         _stream(x.device)),
                "dq_fakequant_act_int4")
     return out
 
@@ -339,7 +349,7 @@ def linear_scratch_bytes(M: int, N: int, K: int) -> int:
 def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[Hadamard],
                      pw: PackedInt4Weight, r: Optional[torch.Tensor], out_dtype=torch.float32,
                      scale_fp16: bool = False, scratch: Optional[torch.Tensor] = None,
-                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, bf16_arith: bool = False) -> torch.Tensor:
     """Whole PermLinear.forward on the int4 path in one C call."""
     lib = _prep(x)
     if x.dtype != torch.bfloat16:
@@ -357,16 +367,16 @@ def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[H
     desc = had.desc() if had is not None else None
     _lib.check(lib.dq_linear_w4a4_int4(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), desc,
                                        _ptr(pw.w_packed), _ptr(pw.sw_t), _ptr(r), M, pw.N, K, pw.group,
-                                       _ptr(out), ydt, int(scale_fp16), _ptr(scratch), scratch.numel(),
-                                       _stream(x.device)), "dq_linear_w4a4_int4")
+                                       _ptr(out), ydt, _scale_mode(scale_fp16, bf16_arith), _ptr(scratch),
+                                       scratch.numel(), _stream(x.device)), "dq_linear_w4a4_int4")
     return out
 
 
 def linear_a16w4(x: torch.Tensor, a: Optional[torch.Tensor], pw: PackedInt4Weight,
                  r: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
                  scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """bf16 activations (times the column scale a, rounded to bf16) against the int4 weight
-    artefact on the bf16 tensor cores: Y = r * (bf16(x * a) @ bf16(codes * group scale)^T)."""
+    """bf16 activations (times the column scale a, rounded to fp16) against the int4 weight
+    artefact on the 16-bit tensor cores: Y = r * (fp16(x * a) @ fp16(codes * group scale)^T)."""
     lib = _prep(x)
     if x.dtype != torch.bfloat16:
         raise ValueError("linear_a16w4 expects bf16 activations")
@@ -375,8 +385,8 @@ def linear_a16w4(x: torch.Tensor, a: Optional[torch.Tensor], pw: PackedInt4Weigh
     M, K = x.shape
     if K != pw.K:
         raise ValueError(f"K mismatch: activations {K}, weight {pw.K}")
-    need = int(lib.dq_linear_a16w4_scratch_bytes(M, pw.N, K)) if a is not None else 0
-    if a is not None and (scratch is None or scratch.numel() < need):
+    need = int(lib.dq_linear_a16w4_scratch_bytes(M, pw.N, K))
+    if scratch is None or scratch.numel() < need:
         scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
     if out is None:
         out = torch.empty(M, pw.N, dtype=out_dtype, device=x.device)

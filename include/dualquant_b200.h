@@ -139,6 +139,11 @@ DQ_API int dq_quant_w_int4(const void* w_bf16, int N, int K, int G, int8_t* code
  *   q   = clamp(round_half_even(x32/s), -8, 7)
  * x is bf16 [M,K] with leading dimension ldx (elements); codes int8 [M,K]; sx fp32 [M].
  * `a` is fp32 [K].  `had` is a host pointer.
+ * scale_fp16 (here and in every entry point that takes it): 0 = fp32 token scale (the reference's
+ * arithmetic when an activation scale or a Hadamard is configured), 1 = the scale rounded to fp16
+ * (storage format of the benchmark configurations), 2 = the whole quantiser in bf16 arithmetic
+ * (scale = bf16(absmax/7), q = round(bf16(x/s))): what the reference computes on a bf16 input with
+ * neither activation scale nor Hadamard (activations/perm_linear.py:109-133).
  */
 DQ_API int dq_quant_act_int4(const void* x_bf16, int64_t ldx, const float* a,
                       const dq_hadamard_desc* had, int M, int K, int8_t* codes, float* sx,
@@ -373,10 +378,10 @@ DQ_API int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float* a,
  * (vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py:55-149, wrapper :220-262) and what
  * PermLinear computes when its activation cast is switched off (activations/perm_linear.py:108-141
  * with act_quant_enabled = False):
- *   Y[m,n] = r[n] * sum_k bf16(x[m,k] * a[k]) * bf16(qw[n,k] * sw[n,k/128])
- * on tcgen05 kind::f16 (bf16 operands, fp32 accumulation).  The group scale is rounded to bf16 before
- * it multiplies the code, as in the reference kernel, whose scales are bf16 (:186).  a may be null
- * (no scale pass, scratch unused); otherwise scratch holds bf16(x * a):
+ *   Y[m,n] = r[n] * sum_k fp16(x[m,k] * a[k]) * fp16(qw[n,k] * sw[n,k/128])
+ * on tcgen05 kind::f16 (fp16 operands, fp32 accumulation; with bf16 operands the reference's own
+ * acceptance check, mean relative error < 1 % (:269-308), does not pass).  Activations beyond the fp16
+ * range saturate at +-65504.  a may be null.  scratch holds fp16(x * a):
  * dq_linear_a16w4_scratch_bytes(M,N,K) bytes, 256-byte aligned.
  */
 DQ_API size_t dq_linear_a16w4_scratch_bytes(int M, int N, int K);

@@ -183,6 +183,19 @@ def quant_act_int4(x: torch.Tensor, a=None, had=None, scale_fp16: bool = False):
     return q.to(torch.int8), s.reshape(-1).contiguous(), x32
 
 
+def quant_act_int4_bf16_arith(x_bf16: torch.Tensor):
+    """PermLinear._quantise_act without activation scale and Hadamard (activations/perm_linear.py:
+    131-133): act_fmt.cast on the bf16 tensor itself, i.e. formats/rtn_int.py:62-67 evaluated by
+    torch in bf16 (scale, quotient and product each rounded to bf16).
+    Returns (codes int8 [M,K], scale as fp32 [M], de-quantised bf16 [M,K])."""
+    assert x_bf16.dtype == torch.bfloat16
+    xmax = x_bf16.abs().amax(dim=1, keepdim=True)
+    s = xmax / 7
+    s[xmax == 0] = 1.0
+    q = (x_bf16 / s).round_().clamp_(-8, 7)
+    return q.to(torch.int8), s.float().reshape(-1).contiguous(), q * s
+
+
 def quant_act_int4_grouped(x: torch.Tensor, a=None, group: int = GROUP, scale_fp16: bool = False,
                            round_away: bool = False):
     """Activation quantiser with one scale per (token, K tile): the in-kernel quantiser of the

@@ -126,6 +126,19 @@ def main(ref_root: str) -> None:
             "y_bf16": y.view(torch.int16).numpy(),
         }
 
+    # PermLinear with neither activation scale nor Hadamard: the bf16-arithmetic branch
+    gg = torch.Generator().manual_seed(31)
+    lin0 = nn.Linear(512, 128, bias=False).to(torch.bfloat16)
+    lin0.weight.data = wfmt.cast((torch.randn(128, 512, generator=gg) * 0.02).to(torch.bfloat16).float()).to(torch.bfloat16)
+    pl0 = PermLinear(lin0, fmt)
+    x0 = _seeded_x(24, 512, 131)
+    x0[3] = 0
+    with torch.no_grad():
+        out["perm_noscale_x"] = x0.view(torch.int16).numpy()
+        out["perm_noscale_w_bf16"] = lin0.weight.data.view(torch.int16).numpy()
+        out["perm_noscale_xq_bf16"] = pl0._quantise_act(x0).view(torch.int16).numpy()
+        out["perm_noscale_y_bf16"] = pl0(x0).view(torch.int16).numpy()
+
     for tag, (K, N, M, mode) in {
         "plain": (512, 128, 20, "none"),
         "full": (896, 128, 12, "full"),  # 896 = 28 * 32

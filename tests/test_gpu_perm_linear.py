@@ -184,3 +184,32 @@ def test_fp4_forward_close_to_fakequant_reference(name):
         wd = O.quant_nvfp4(w.float(), float((w.float().abs().max() / 2688.0).item()))[3]
     ref = xd.double() @ wd.double().T
     assert ((y - ref).abs().max() / ref.abs().max()).item() < 8e-3  # bf16 output rounding
+
+
+def test_bf16_arithmetic_branch_bit_exact_against_the_reference(golden):
+    """No activation scale, no Hadamard, bf16 input: the reference quantises in bf16 arithmetic
+    (activations/perm_linear.py:131-133).  De-quantised activations equal the reference's tensor bit
+    for bit; codes and scales equal the oracle's; the int4 GEMM output agrees to bf16 accuracy."""
+    from dualquant_b200 import ops
+
+    w = _bf16(golden["perm_noscale_w_bf16"])
+    lin = nn.Linear(w.shape[1], w.shape[0], bias=False).to(torch.bfloat16)
+    lin.weight.data = w.clone()
+    pl = PermLinear(lin.to(DEV), formats.make_format("rtn_int4", block_size=-1))
+    x = _bf16(golden["perm_noscale_x"])
+    xq = pl._quantise_act(x.to(DEV)).cpu()
+    assert torch.equal(xq, _bf16(golden["perm_noscale_xq_bf16"]))
+    q, s, _ = O.quant_act_int4_bf16_arith(x)
+    codes, sx = ops.quant_act_int4(x.to(DEV), None, None, bf16_arith=True)
+    assert torch.equal(codes.cpu(), q) and torch.equal(sx.cpu(), s)
+    # the format object's cast on a bf16 tensor takes the same branch
+    f = formats.make_format("rtn_int4", block_size=-1)
+    assert torch.equal(f.cast(x.to(DEV)).cpu(), _bf16(golden["perm_noscale_xq_bf16"]))
+    y = pl(x.to(DEV)).float().cpu()
+    assert pl._packed is not None
+    ref = _bf16(golden["perm_noscale_y_bf16"]).float()
+    assert (y - ref).abs().max() / ref.abs().max() < 2e-2
+    # exact integer sums of exactly these codes
+    qw, sw = O.quant_w_int4(w)
+    exact = O.dequant_matmul(q, s, qw, sw)
+    assert ((y.double() - exact).abs().max() / exact.abs().max()) < 8e-3

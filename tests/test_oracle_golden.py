@@ -159,3 +159,14 @@ def test_nvfp4_block_scale_rounding_matches_quantize_scale_e4m3(golden):
     assert int(exact.sum()) > 500
     assert torch.equal(bs.reshape(-1)[exact], ref[exact])
     assert float(bs.min()) == 2.0 ** -6  # zero / tiny blocks are clamped to the smallest normal
+
+
+def test_bf16_arithmetic_branch_matches_reference(golden):
+    # PermLinear without activation scale / Hadamard quantises the bf16 tensor in bf16 arithmetic
+    x = _bf16(golden["perm_noscale_x"])
+    q, s, deq = O.quant_act_int4_bf16_arith(x)
+    assert torch.equal(deq, _bf16(golden["perm_noscale_xq_bf16"]))
+    assert s[3].item() == 1.0 and int(q[3].abs().max()) == 0
+    # and it is not the fp32 quantiser: some codes differ
+    q32, _, _ = O.quant_act_int4(x, None, None, False)
+    assert not torch.equal(q32, q)
