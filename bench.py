@@ -630,6 +630,46 @@ def run_case(args):
                           "TFLOPS": round(2.0 * M * N * K / ms / 1e9, 1), "algorithmic_bytes": nbytes,
                           "GBps": round(nbytes / ms / 1e6, 1)}), flush=True)
         return
+    if parts[0] in ("a16w4", "linear"):  # a16w4:NAME:M / linear:NAME:M - one whole linear alone
+        name, M = parts[1], int(parts[2])
+        K, N = {n: (k, nn) for n, k, nn in synthetic.LLAMA31_8B_LINEARS}[name]
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        g = torch.Generator(device=dev).manual_seed(0)
+        n_copies = max(2, int(300e6 // (N * K // 2)) + 1) if M <= 128 else 1
+        copies = []
+        for _ in range(n_copies):
+            w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            cw, sw = ops.quant_w_int4(w)
+            copies.append(ops.pack_w_int4(cw, sw))
+            del w, cw, sw
+        r, c = synthetic.make_scales(N, K, 0)
+        r, a = r.to(dev), (1.0 / c).to(dev)
+        x = synthetic.make_x(M, K, 0).to(dev)
+        if parts[0] == "a16w4":
+            y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            scratch = torch.empty(M * K * 2 + 256, dtype=torch.uint8, device=dev)
+            call = lambda pw: ops.linear_a16w4(x, a, pw, r, scratch=scratch, out=y)  # noqa: E731
+        else:
+            y = torch.empty(M, N, dtype=torch.float32, device=dev)
+            scratch = torch.empty(max(256, ops.linear_scratch_bytes(M, N, K)), dtype=torch.uint8, device=dev)
+            call = lambda pw: ops.linear_w4a4_int4(x, a, None, pw, r, scale_fp16=True, scratch=scratch, out=y)  # noqa: E731
+        for i in range(3):
+            call(copies[i % n_copies])
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.iters):
+            call(copies[i % n_copies])
+        e1.record()
+        torch.cuda.synchronize()
+        _lib.device_status(0)
+        ms = e0.elapsed_time(e1) / args.iters
+        print(json.dumps({"case": args.case, "iters": args.iters, "us_per_call": round(ms * 1e3, 2),
+                          "TOPS": round(2.0 * M * N * K / ms / 1e9, 1),
+                          "GBps": round(synthetic.int4_gemm_bytes(M, N, K) / ms / 1e6, 1)}), flush=True)
+        return
     name, M = parts[0], int(parts[1])
     tn = int(parts[2]) if len(parts) > 2 else 0
     split = int(parts[3]) if len(parts) > 3 else 0
@@ -902,6 +942,19 @@ def run_decoder_suite(args, emit=True, init_pg=True):
                 ok = t.item() == 0.0
             checks = {"graph_equals_eager": ok, "max_abs_logit_diff": diff}
         checks["prefill_logits_finite"] = bool(torch.isfinite(logits).all().item())
+        if fused:
+            # the decode step with the all-reduce inside the GEMM against the same step reduced by
+            # NCCL (eager launches): sums are formed in a different order, so agreement is to rounding
+            pos_t.fill_(S)
+            a_logits = model.decode_step(tok, pos_t).float()
+            saved, model.ar = model.ar, None
+            try:
+                b_logits = model.decode_step(tok, pos_t).float()
+            finally:
+                model.ar = saved
+            rel = ((a_logits - b_logits).abs().max() / b_logits.abs().max()).item()
+            checks["fused_allreduce_vs_nccl_max_rel_diff"] = round(rel, 5)
+            checks["fused_allreduce_matches_nccl"] = bool(rel < 5e-2)
 
         if graph is None:
             for _ in range(2):  # untimed eager warm-up steps (allocator, lazy NCCL channels)
