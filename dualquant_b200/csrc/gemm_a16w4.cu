@@ -17,8 +17,8 @@
 // tile TN is UMMA N.  Per weight group (128 k, one pipeline step):
 //   producer warp   one bulk copy of the packed tile (8 KB codes + 256 B fp16 scales) and two tiled
 //                   copies of the activation tile (TN x 64 fp16 each, 128-byte swizzle);
-//   8 unpack warps  thread (row, half) expands 32 bytes of nibbles into 64 fp16 = code * scale and
-//                   writes them as eight 16-byte pieces into the 128B-swizzled K-major operand tile.
+//   16 unpack warps thread (row, k chunk) expands 16 bytes of nibbles into 32 fp16 = code * scale and
+//                   writes them as four 16-byte pieces into the 128B-swizzled K-major operand tile.
 //                   A nibble pair becomes half2 by bit tricks: (w >> s) & 0x000F000F picks two
 //                   two's-complement nibbles, ^ 0x64086408 turns them into the fp16 numbers
 //                   1032 + code, a packed subtract gives code exactly and a packed multiply by the
@@ -39,7 +39,7 @@ namespace dq {
 namespace a16 {
 
 constexpr int kBN = 128;                 // weight rows per CTA (UMMA M)
-constexpr int kUnpackWarps = 8;
+constexpr int kUnpackWarps = 16;  // four threads per weight row: two resident warps per scheduler hid too little latency
 constexpr int kProducerWarp = kUnpackWarps;
 constexpr int kIssuerWarp = kUnpackWarps + 1;
 constexpr int kThreads = (kUnpackWarps + 2) * 32;
@@ -214,7 +214,7 @@ gemm_a16w4_kernel(const uint8_t* __restrict__ w_packed, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------------ unpack warps
     const int row = tid & 127;
-    const int half = tid >> 7;  // k half of the group: atom `half`, packed chunks 2*half, 2*half + 1
+    const int ch = tid >> 7;    // k chunk (32 k) of the group this thread expands: 0..3
     const int swz = row & 7;
     bool ok = true;
     for (int i = 0; i < ng && ok; ++i) {
@@ -224,20 +224,17 @@ gemm_a16w4_kernel(const uint8_t* __restrict__ w_packed, const __grid_constant__ 
       const uint8_t* tile = smem + C::kOffP + sp * C::kPStage;
       const __half sc = reinterpret_cast<const __half*>(tile + kTileCodeBytes)[row];
       const __half2 s2 = __half2half2(sc);
-      uint8_t* dst = smem + C::kOffW + b * kWTile + half * kAtom + row * 128;
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int ch = 2 * half + cc;                    // k chunk (32 k) of the group
-        const int pos = ch ^ ((row >> 1) & 3);           // its position in the packed row
-        const uint4 w = *reinterpret_cast<const uint4*>(tile + row * 64 + pos * 16);
-        // the chunk's 32 k as four 16-byte pieces of the atom: k 0-7, 8-15 (low nibbles of words
-        // 0,1 / 2,3), 16-23, 24-31 (high nibbles)
-        const int c0 = cc * 4;
-        *reinterpret_cast<uint4*>(dst + (((c0 + 0) ^ swz) << 4)) = expand8<0>(w.x, w.y, s2);
-        *reinterpret_cast<uint4*>(dst + (((c0 + 1) ^ swz) << 4)) = expand8<0>(w.z, w.w, s2);
-        *reinterpret_cast<uint4*>(dst + (((c0 + 2) ^ swz) << 4)) = expand8<1>(w.x, w.y, s2);
-        *reinterpret_cast<uint4*>(dst + (((c0 + 3) ^ swz) << 4)) = expand8<1>(w.z, w.w, s2);
-      }
+      // chunks 0, 1 -> atom 0 (k 0..63), chunks 2, 3 -> atom 1; inside the atom 16-byte pieces c0..c0+3
+      uint8_t* dst = smem + C::kOffW + b * kWTile + (ch >> 1) * kAtom + row * 128;
+      const int c0 = (ch & 1) * 4;
+      const int pos = ch ^ ((row >> 1) & 3);           // the chunk's position in the packed row
+      const uint4 w = *reinterpret_cast<const uint4*>(tile + row * 64 + pos * 16);
+      // the chunk's 32 k as four 16-byte pieces: k 0-7, 8-15 (low nibbles of words 0,1 / 2,3),
+      // 16-23, 24-31 (high nibbles)
+      *reinterpret_cast<uint4*>(dst + (((c0 + 0) ^ swz) << 4)) = expand8<0>(w.x, w.y, s2);
+      *reinterpret_cast<uint4*>(dst + (((c0 + 1) ^ swz) << 4)) = expand8<0>(w.z, w.w, s2);
+      *reinterpret_cast<uint4*>(dst + (((c0 + 2) ^ swz) << 4)) = expand8<1>(w.x, w.y, s2);
+      *reinterpret_cast<uint4*>(dst + (((c0 + 3) ^ swz) << 4)) = expand8<1>(w.z, w.w, s2);
       fence_proxy_async_smem();  // generic-proxy stores before the tensor core's reads
       __syncwarp();
       if (lane == 0) {
