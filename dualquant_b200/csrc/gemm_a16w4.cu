@@ -27,6 +27,14 @@
 // After the last group the first four unpack warps read the accumulator (one weight row per
 // thread), multiply by r[n] and store bf16 or fp32.  Every wait is bounded.
 //
+// Bound (ncu at gate+up, M = 4096: tensor pipe 31 % active, issue slots 45 %): the shared-memory port.
+// Per 128 x 128 x 128 block the tensor core reads 64 KB of operands (a 128 x 128 tile saturates the
+// port on its own: 8 KB per 68-cycle UMMA), the unpack warps write 32 KB and read 8 KB, the copy
+// engine writes 40 KB - 144 KB against the ~69 KB the port moves in the block's 542 UMMA cycles.  Tried
+// and not kept: a second issuing warp with its own accumulator (slower: one activation stage less).
+// The next step is the weight operand through tensor memory (tcgen05.st by the unpack warps, as
+// the int4 kernel for small token tiles does), which takes 64 KB per block off the port.
+//
 // The activation scale and the conversion to fp16 run as a small separate pass
 // (xs = fp16(x * a), caller scratch) so that the GEMM can stage activations with TMA.
 #include "dq_common.h"
