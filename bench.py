@@ -943,18 +943,20 @@ def run_decoder_suite(args, emit=True, init_pg=True):
             checks = {"graph_equals_eager": ok, "max_abs_logit_diff": diff}
         checks["prefill_logits_finite"] = bool(torch.isfinite(logits).all().item())
         if fused:
-            # the decode step with the all-reduce inside the GEMM against the same step reduced by
-            # NCCL (eager launches): sums are formed in a different order, so agreement is to rounding
-            pos_t.fill_(S)
-            a_logits = model.decode_step(tok, pos_t).float()
-            saved, model.ar = model.ar, None
-            try:
-                b_logits = model.decode_step(tok, pos_t).float()
-            finally:
-                model.ar = saved
-            rel = ((a_logits - b_logits).abs().max() / b_logits.abs().max()).item()
+            # One row-parallel linear (layer 0's o_proj) on the same decode-size input, reduced inside
+            # the GEMM and by NCCL.  The fused path sums the ranks' fp32 partials and rounds once;
+            # NCCL sums bf16 partials: agreement to bf16 rounding.  (Whole-stack logits are no
+            # yardstick: 32 layers of 4-bit activations amplify a last-bit difference into
+            # decorrelated codes, measured on the random-init stack.)
+            lin = model.layers[0].o
+            gx = torch.Generator(device=dev).manual_seed(1234 + rank)
+            xin = torch.randn(B, lin.K, generator=gx, device=dev).to(torch.bfloat16)
+            y_fused = lin(xin, ar=model.ar).float()
+            y_nccl = lin(xin)
+            dist.all_reduce(y_nccl, group=group)
+            rel = ((y_fused - y_nccl.float()).abs().max() / y_nccl.float().abs().max()).item()
             checks["fused_allreduce_vs_nccl_max_rel_diff"] = round(rel, 5)
-            checks["fused_allreduce_matches_nccl"] = bool(rel < 5e-2)
+            checks["fused_allreduce_matches_nccl"] = bool(rel < 3e-2)
 
         if graph is None:
             for _ in range(2):  # untimed eager warm-up steps (allocator, lazy NCCL channels)
