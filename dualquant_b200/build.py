@@ -26,6 +26,7 @@ SOURCES = [
     "linear_w4a4.cu",
     "mma_peak.cu",
     "gemm_a16w4.cu",
+    "decoder_ops.cu",
 ]
 
 NVCC_FLAGS = [

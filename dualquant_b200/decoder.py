@@ -160,13 +160,21 @@ class DecoderLayer:
         self.k_cache = torch.zeros(shape, dtype=torch.bfloat16, device=device)
         self.v_cache = torch.zeros(shape, dtype=torch.bfloat16, device=device)
 
-    def forward(self, x, cos, sin, pos0: int, pos_t: Optional[torch.Tensor], mask, group, ar=None):
+    def forward(self, x, cos, sin, pos0: int, pos_t: Optional[torch.Tensor], mask, group, ar=None,
+                rope_tabs=None):
         """x [B, S, hidden] bf16.  Prefill: pos0 = 0, pos_t None (causal).  Decode: S = 1, the
         cache position comes from the device tensor pos_t and `mask` hides the unwritten tail."""
         cfg = self.cfg
         B, S, Hd = x.shape
         hd = cfg.head_dim
         qkv = self.qkv.normed(x.reshape(B * S, Hd), self.ln1, cfg.rms_norm_eps)
+        if pos_t is not None and S == 1 and rope_tabs is not None:
+            # decode: RoPE + cache append in one launch, attention over the cache
+            q = ops.rope_kv_append(qkv, rope_tabs[0], rope_tabs[1], pos_t, self.hq, self.hkv,
+                                   self.k_cache, self.v_cache)
+            attn = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
+            attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
+            return self._after_attention(x, attn, group, ar)
         qkv = qkv.reshape(B, S, self.hq + 2 * self.hkv, hd)
         q = qkv[:, :, : self.hq].transpose(1, 2)
         k = qkv[:, :, self.hq : self.hq + self.hkv].transpose(1, 2)
@@ -184,6 +192,12 @@ class DecoderLayer:
             attn = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask,
                                                   enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
+        return self._after_attention(x, attn, group, ar)
+
+    def _after_attention(self, x, attn, group, ar):
+        """o_proj, residual, MLP, residual."""
+        cfg = self.cfg
+        B, S, Hd = x.shape
         fused = ar if (ar is not None and self.tp > 1 and B * S <= 16) else None
         if self.tp == 1:
             # one GPU: the residual additions ride in the epilogues of o_proj and down_proj
@@ -245,7 +259,7 @@ class Decoder:
         sin = self.sin.index_select(0, pos_t)
         mask = (torch.arange(self.max_len, device=self.device) <= pos_t).view(1, 1, 1, self.max_len)
         for layer in self.layers:
-            x = layer.forward(x, cos, sin, 0, pos_t, mask, self.group, self.ar)
+            x = layer.forward(x, cos, sin, 0, pos_t, mask, self.group, self.ar, rope_tabs=(self.cos, self.sin))
         x = _rms_norm(x[:, 0], self.norm, self.cfg.rms_norm_eps)
         return x @ self.lm_head.T
 

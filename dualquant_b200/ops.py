@@ -529,3 +529,23 @@ def mma_peak(kind: int, iters: int = 4096, device=None) -> float:
     e1.record()
     torch.cuda.synchronize(dev)
     return n_ops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12
+
+
+def rope_kv_append(qkv: torch.Tensor, cos_tab: torch.Tensor, sin_tab: torch.Tensor, pos_t: torch.Tensor,
+                   hq: int, hkv: int, k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
+    """One decode token per sequence: RoPE on the query and key heads of qkv [B, (hq + 2 hkv) * d]
+    (bf16), key / value heads appended to the caches [B, hkv, max_len, d] at position pos_t (int64
+    device tensor); returns the rotated queries [B, hq, 1, d]."""
+    lib = _prep(qkv)
+    B = qkv.shape[0]
+    hd = k_cache.shape[-1]
+    max_len = k_cache.shape[2]
+    if qkv.dtype != torch.bfloat16 or qkv.stride(-1) != 1 or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("rope_kv_append expects bf16 qkv rows and contiguous caches")
+    if cos_tab.shape[0] < max_len or cos_tab.shape[1] != hd or not cos_tab.is_contiguous() or not sin_tab.is_contiguous():
+        raise ValueError("cos / sin tables must be contiguous [>= max_len, head_dim]")
+    q = torch.empty(B, hq, 1, hd, dtype=torch.bfloat16, device=qkv.device)
+    _lib.check(lib.dq_rope_kv_append(_ptr(qkv), qkv.stride(0), _ptr(cos_tab), _ptr(sin_tab), _ptr(pos_t), B, hq, hkv,
+                                     hd, max_len, _ptr(q), _ptr(k_cache), _ptr(v_cache), _stream(qkv.device)),
+               "dq_rope_kv_append")
+    return q

@@ -210,3 +210,49 @@ def test_captured_decode_step_equals_eager():
             torch.cuda.synchronize()
             assert torch.equal(static_logits, eager)
             static_tok.copy_(eager.argmax(-1))
+
+
+def test_rope_kv_append_equals_the_torch_expression():
+    """One launch for RoPE + cache append against the bf16 tensor expression
+    x * cos + rotate_half(x) * sin and index_copy_ that it replaces: bit-identical."""
+    from dualquant_b200 import ops
+
+    B, hq, hkv, hd, max_len = 5, 8, 2, 64, 40
+    g = torch.Generator(device=DEV).manual_seed(5)
+    qkv = torch.randn(B, (hq + 2 * hkv) * hd, generator=g, device=DEV).to(torch.bfloat16)
+    cfg = decoder.DecoderConfig(head_dim=hd)
+    cos, sin = decoder._rope_tables(cfg, max_len, torch.device(DEV))
+    kc = torch.randn(B, hkv, max_len, hd, generator=g, device=DEV).to(torch.bfloat16)
+    vc = torch.randn(B, hkv, max_len, hd, generator=g, device=DEV).to(torch.bfloat16)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    for p in (0, 17, max_len - 1):
+        pos = torch.tensor([p], dtype=torch.int64, device=DEV)
+        q = ops.rope_kv_append(qkv, cos, sin, pos, hq, hkv, kc, vc)
+        x = qkv.reshape(B, 1, hq + 2 * hkv, hd)
+        c, s = cos.index_select(0, pos), sin.index_select(0, pos)
+        q_ref = decoder._apply_rope(x[:, :, :hq].transpose(1, 2), c, s)
+        k_ref = decoder._apply_rope(x[:, :, hq:hq + hkv].transpose(1, 2), c, s)
+        kc_ref.index_copy_(2, pos, k_ref)
+        vc_ref.index_copy_(2, pos, x[:, :, hq + hkv:].transpose(1, 2))
+        assert torch.equal(q, q_ref)
+        assert torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+
+
+def test_decode_step_with_fused_rope_equals_the_unfused_step():
+    cfg = _small_cfg()
+    model = _build(cfg)
+    B, S = 3, 10
+    model.alloc_cache(B, S + 3)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), device=DEV)
+    with torch.no_grad():
+        tok = model.prefill(ids).argmax(-1)
+        pos = torch.tensor([S], dtype=torch.int64, device=DEV)
+        fused = model.decode_step(tok, pos).clone()
+        # the same step through the element-wise torch ops (no rope tables handed to the layers)
+        x = model.embed[tok].unsqueeze(1)
+        cos, sin = model.cos.index_select(0, pos), model.sin.index_select(0, pos)
+        mask = (torch.arange(model.max_len, device=DEV) <= pos).view(1, 1, 1, model.max_len)
+        for layer in model.layers:
+            x = layer.forward(x, cos, sin, 0, pos, mask, None, None)
+        ref = torch.nn.functional.rms_norm(x[:, 0], (cfg.hidden_size,), model.norm, cfg.rms_norm_eps) @ model.lm_head.T
+    assert torch.equal(fused, ref)
