@@ -204,6 +204,39 @@ def main(ref_root: str) -> None:
     out["e4m3_scale_in"] = sgrid.numpy()
     out["e4m3_scale_out"] = scale_formats.quantize_scale_e4m3(sgrid.clone()).numpy()
 
+    # ---- QuaRot offline folds (quarot/llama_quarot.py:186-264) on a tiny random Llama ---------------
+    # The reference moves weights with .cuda() inside apply_exact_had_to_linear; there is no GPU where
+    # this script runs, so Tensor.cuda is the identity for the duration of the call.
+    import transformers
+    from quarot import llama_quarot
+
+    tiny = transformers.LlamaConfig(hidden_size=64, intermediate_size=112, num_hidden_layers=1,
+                                    num_attention_heads=4, num_key_value_heads=4, vocab_size=48,
+                                    max_position_embeddings=32, tie_word_embeddings=False)
+    torch.manual_seed(77)
+    hf = transformers.LlamaForCausalLM(tiny).to(torch.float32)
+    for prm in hf.parameters():  # norms away from 1 so that the fusion is visible
+        if prm.dim() == 1:
+            prm.data = torch.rand_like(prm) + 0.5
+    names = ["model.embed_tokens.weight", "lm_head.weight", "model.norm.weight",
+             "model.layers.0.input_layernorm.weight", "model.layers.0.post_attention_layernorm.weight"] + [
+        f"model.layers.0.self_attn.{n}_proj.weight" for n in "qkvo"] + [
+        f"model.layers.0.mlp.{n}_proj.weight" for n in ("gate", "up", "down")]
+    sd = hf.state_dict()
+    for nme in names:
+        out["r1_before__" + nme] = sd[nme].numpy().copy()
+    orig_cuda = torch.Tensor.cuda
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    try:
+        torch.manual_seed(78)  # random_hadamard_matrix draws its +-1 diagonal from the global generator
+        llama_quarot.apply_r1(hf, rotate_mode="hadamard", apply_r2_r4=True)
+    finally:
+        torch.Tensor.cuda = orig_cuda
+    sd = hf.state_dict()
+    for nme in names:
+        if nme in sd:
+            out["r1_after__" + nme] = sd[nme].numpy().copy()
+
     # ---- format of the shipped column-scale files (scales_dualquant_rtn_int4/*.pt) -----------------
     scale_file = os.path.join(ref_root, "scales_dualquant_rtn_int4",
                               "DQ_Qwen_Qwen3-0.6B_iter15_scale_row_column_row_all_one_col_l1_norm_rtn_int4.pt")
