@@ -86,7 +86,7 @@ SIGNATURES = {
     "dq_gemm_w4a4_int4_acc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "dq_linear_w4a4_int4_scratch_bytes": (_sz, [_i, _i, _i]),
     "dq_linear_w4a4_int4": (_i, [_vp, _i64, _vp, _hp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _sz, _vp]),
-    "dq_rope_kv_append": (_i, [_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "dq_rope_kv_append": (_i, [_vp, _i64, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "dq_linear_a16w4_scratch_bytes": (_sz, [_i, _i, _i]),
     "dq_linear_a16w4": (_i, [_vp, _i64, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "dq_linear_w4a4_int4_static_max_bytes": (_sz, []),

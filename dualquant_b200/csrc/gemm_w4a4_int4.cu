@@ -35,27 +35,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-// Optional timeline instrumentation (development builds only, -DDQ_GEMM_TRACE): CTA (0,0,0)
-// records clock64() at the hand-off points of each role for the first 64 stages.
-#ifdef DQ_GEMM_TRACE
-#define DQ_TR(role, i, k)                                                              \
-  do {                                                                                 \
-    if (trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64) \
-      trace[((role) * 64 + (i)) * 8 + (k)] = clock64();                                \
-  } while (0)
-#define DQ_TRACE_PARAM , long long* trace
-#define DQ_TRACE_ARG , dq::g_trace
-#else
-#define DQ_TR(role, i, k) do {} while (0)
-#define DQ_TRACE_PARAM
-#define DQ_TRACE_ARG
-#endif
-
 namespace dq {
-
-#ifdef DQ_GEMM_TRACE
-long long* g_trace = nullptr;
-#endif
 
 constexpr int kBN = 128;           // weight rows per CTA tile (UMMA M)
 
@@ -63,19 +43,7 @@ constexpr int kWpBytes = kBN * kGroup / 2;  // packed stage: 8 KB
 constexpr int kWaBytes = kBN * kGroup;      // unpacked stage: 16 KB
 
 // {SP, SX, XC} for token tiles 16 / 32 / 64 / 128
-#ifndef DQ_CFG_16
-#define DQ_CFG_16 4, 2, 4
-#endif
-#ifndef DQ_CFG_32
-#define DQ_CFG_32 4, 2, 2
-#endif
-#ifndef DQ_CFG_64
-#define DQ_CFG_64 4, 2, 1
-#endif
-#ifndef DQ_CFG_128
-#define DQ_CFG_128 12, 4, 1
-#endif
-constexpr int kCfgTab[4][3] = {{DQ_CFG_16}, {DQ_CFG_32}, {DQ_CFG_64}, {DQ_CFG_128}};
+constexpr int kCfgTab[4][3] = {{4, 2, 4}, {4, 2, 2}, {4, 2, 1}, {12, 4, 1}};
 constexpr int kUnpackWarps = 4;
 
 template <int TN>
@@ -147,7 +115,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
                       const __half* __restrict__ sw_t, const float* __restrict__ r,
                       const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
                       const void* __restrict__ residual, int M, int N, int K, int groups_per_split,
-                      int split_k, int w_stream_once, int* status DQ_TRACE_PARAM) {
+                      int split_k, int w_stream_once, int* status) {
   using C = Cfg<TN>;
   // The 128-byte swizzle of the UMMA operands needs the buffers on 1 KB boundaries.  The kernel has
   // no static shared memory, so the dynamic window starts on one; if it ever does not, every CTA
@@ -238,9 +206,7 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
     for (int i = warp; i < my_groups; i += kUnpackWarps) {  // i: global group index
       const int sp = i % C::SP, b = i % C::NB;
       if (!mbar_wait(&full_p[sp], (i / C::SP) & 1, abort_flag, SITE_UNPACK_FULL)) break;
-      if (lane == 0) DQ_TR(0, i, 0);
       if (!mbar_wait(&done[b], ((i / C::NB) & 1) ^ 1, abort_flag, SITE_UNPACK_FREE)) break;
-      if (lane == 0) DQ_TR(0, i, 1);
       const uint8_t* src = smem + C::kOffP + sp * kWpBytes;
       uint8_t* dst = smem + C::kOffA + b * kWaBytes;
 #pragma unroll
@@ -276,10 +242,8 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
           mbar_expect_tx(&full_p[sp], kWpBytes);
           bulk_load_1d(smem + C::kOffP + sp * kWpBytes, w_group(i + C::SP), kWpBytes,
                        &full_p[sp], pol_w);
-          DQ_TR(3, i + C::SP, 0);
         }
       }
-      if (lane == 0) DQ_TR(0, i, 2);
     }
   } else if (warp < C::kProducerWarp) {
     // ------------------------------------------------------------------ epilogue warps
@@ -330,7 +294,6 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         tc_fence_after();
         ld_chunk(b, 0, va);
       }
-      if (tid == 128) DQ_TR(1, gi, 0);
 #pragma unroll
       for (int c = 0; c < C::NCH; ++c) {  // chunk c lives in va (c even) or vb (c odd)
         uint32_t* cur = (c & 1) ? vb : va;
@@ -339,7 +302,6 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         if (c + 1 < C::NCH) {
           ld_chunk(b, (c + 1) * C::CH, nxt);
         } else {
-          if (tid == 128) DQ_TR(1, gi, 1);
           // accumulator b is free once its last column has been read
           tc_fence_before();
           __syncwarp();
@@ -359,7 +321,6 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         }
         consume(cur, c * C::CH, s);
       }
-      if (tid == 128) DQ_TR(1, gi, 2);
       return true;
     };
     bool ok = true;
@@ -448,7 +409,6 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
           mbar_expect_tx(&full_x[sxi], C::kXStageBytes);
           tma_load_3d(smem + C::kOffX + sxi * C::kXStageBytes, &tm_x, 0, t0, g_begin + ix * C::XC,
                       &full_x[sxi], pol_x);
-          DQ_TR(3, xs, 1);
         }
       }
     }
@@ -465,11 +425,9 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
         const int b = gi % C::NB;
         const int xs = it * nxs + i / C::XC, xj = i % C::XC, sxi = xs % C::SX;
         if (!mbar_wait(&ready[b], (gi / C::NB) & 1, abort_flag, SITE_MMA_READY)) break;
-        DQ_TR(2, gi, 0);
         if (xj == 0 || C::kIssuers > 1) {
           if (!mbar_wait(&full_x[sxi], (xs / C::SX) & 1, abort_flag, SITE_MMA_X)) break;
         }
-        DQ_TR(2, gi, 1);
         tc_fence_after();
         const uint64_t da = umma_desc_k_sw128(a_base + b * kWaBytes);
         const uint64_t db = umma_desc_k_sw128(x_base + sxi * C::kXStageBytes + xj * C::kXBytes);
@@ -477,10 +435,8 @@ gemm_w4a4_int4_kernel(const uint8_t* __restrict__ w_packed,
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // +32 bytes along K inside the swizzle atom = +2 (>>4)
           umma_i8(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk > 0 ? 1u : 0u);
-        DQ_TR(2, gi, 2);
         umma_commit(&done[b]);
         if (xj == C::XC - 1 || i == ng - 1) umma_commit(&empty_x[sxi]);
-        DQ_TR(2, gi, 3);
       }
     }
   }
@@ -611,7 +567,7 @@ static int launch(const int8_t* codes, const float* sx, const uint8_t* w_packed,
   const int w_stream_once = (tok_tiles == 1) ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_w4a4_int4_kernel<TN>, w_packed, tm_x, sw_t, r, sx,
                                      y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, M, N, K, gps,
-                                     split, w_stream_once, st->status_dev DQ_TRACE_ARG);
+                                     split, w_stream_once, st->status_dev);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_w4a4_int4 launch failed (TN=%d split=%d): %s", TN, split,
                      cudaGetErrorString(e));
@@ -631,12 +587,6 @@ static int check_gemm_args(const void* codes, const void* w_packed, int M, int N
 }  // namespace dq
 
 using namespace dq;
-
-#ifdef DQ_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) void dq_debug_set_trace(long long* p) {
-  dq::g_trace = p;
-}
-#endif
 
 extern "C" size_t dq_gemm_w4a4_int4_workspace_bytes(int, int, int) { return 0; }
 

@@ -168,11 +168,19 @@ class DecoderLayer:
         B, S, Hd = x.shape
         hd = cfg.head_dim
         qkv = self.qkv.normed(x.reshape(B * S, Hd), self.ln1, cfg.rms_norm_eps)
-        if pos_t is not None and S == 1 and rope_tabs is not None:
-            # decode: RoPE + cache append in one launch, attention over the cache
-            q = ops.rope_kv_append(qkv, rope_tabs[0], rope_tabs[1], pos_t, self.hq, self.hkv,
-                                   self.k_cache, self.v_cache)
-            attn = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask, enable_gqa=True)
+        if rope_tabs is not None:
+            # RoPE + cache write in one launch; attention reads K / V straight from the cache
+            if pos_t is not None:
+                q = ops.rope_kv_append(qkv, rope_tabs[0], rope_tabs[1], pos_t, self.hq, self.hkv,
+                                       self.k_cache, self.v_cache, S)
+                attn = F.scaled_dot_product_attention(q, self.k_cache, self.v_cache, attn_mask=mask,
+                                                      enable_gqa=True)
+            else:
+                q = ops.rope_kv_append(qkv, rope_tabs[0], rope_tabs[1], pos0, self.hq, self.hkv,
+                                       self.k_cache, self.v_cache, S)
+                attn = F.scaled_dot_product_attention(q, self.k_cache[:, :, pos0 : pos0 + S],
+                                                      self.v_cache[:, :, pos0 : pos0 + S], is_causal=True,
+                                                      enable_gqa=True)
             attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
             return self._after_attention(x, attn, group, ar)
         qkv = qkv.reshape(B, S, self.hq + 2 * self.hkv, hd)
@@ -247,7 +255,7 @@ class Decoder:
         x = self.embed[ids]
         cos, sin = self.cos[:S], self.sin[:S]
         for layer in self.layers:
-            x = layer.forward(x, cos, sin, 0, None, None, self.group)
+            x = layer.forward(x, cos, sin, 0, None, None, self.group, rope_tabs=(self.cos, self.sin))
         x = _rms_norm(x[:, -1], self.norm, self.cfg.rms_norm_eps)
         return x @ self.lm_head.T
 

@@ -531,21 +531,32 @@ def mma_peak(kind: int, iters: int = 4096, device=None) -> float:
     return n_ops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12
 
 
-def rope_kv_append(qkv: torch.Tensor, cos_tab: torch.Tensor, sin_tab: torch.Tensor, pos_t: torch.Tensor,
-                   hq: int, hkv: int, k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
-    """One decode token per sequence: RoPE on the query and key heads of qkv [B, (hq + 2 hkv) * d]
-    (bf16), key / value heads appended to the caches [B, hkv, max_len, d] at position pos_t (int64
-    device tensor); returns the rotated queries [B, hq, 1, d]."""
+def rope_kv_append(qkv: torch.Tensor, cos_tab: torch.Tensor, sin_tab: torch.Tensor, pos, hq: int, hkv: int,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor, tokens_per_seq: int = 1) -> torch.Tensor:
+    """RoPE on the query and key heads of qkv [B * S, (hq + 2 hkv) * d] (bf16, S = tokens_per_seq),
+    key / value heads written to the caches [B, hkv, max_len, d] at positions pos .. pos + S - 1.
+    pos: an int64 device tensor (read by the kernel, so the call can sit in a captured graph) or a
+    Python int.  Returns the rotated queries as [B, hq, S, d] (a view of [B, S, hq, d])."""
     lib = _prep(qkv)
-    B = qkv.shape[0]
+    S = int(tokens_per_seq)
+    if S < 1 or qkv.shape[0] % S:
+        raise ValueError("qkv rows must be a multiple of tokens_per_seq")
+    B = qkv.shape[0] // S
     hd = k_cache.shape[-1]
     max_len = k_cache.shape[2]
     if qkv.dtype != torch.bfloat16 or qkv.stride(-1) != 1 or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
         raise ValueError("rope_kv_append expects bf16 qkv rows and contiguous caches")
     if cos_tab.shape[0] < max_len or cos_tab.shape[1] != hd or not cos_tab.is_contiguous() or not sin_tab.is_contiguous():
         raise ValueError("cos / sin tables must be contiguous [>= max_len, head_dim]")
-    q = torch.empty(B, hq, 1, hd, dtype=torch.bfloat16, device=qkv.device)
-    _lib.check(lib.dq_rope_kv_append(_ptr(qkv), qkv.stride(0), _ptr(cos_tab), _ptr(sin_tab), _ptr(pos_t), B, hq, hkv,
-                                     hd, max_len, _ptr(q), _ptr(k_cache), _ptr(v_cache), _stream(qkv.device)),
+    q = torch.empty(B, S, hq, hd, dtype=torch.bfloat16, device=qkv.device)
+    if isinstance(pos, torch.Tensor):
+        if pos.dtype != torch.int64 or pos.device != qkv.device:
+            raise ValueError("pos must be an int64 tensor on the device of qkv")
+        pos_dev, pos_host = _ptr(pos), 0
+    else:
+        pos_dev, pos_host = None, int(pos)
+    _lib.check(lib.dq_rope_kv_append(_ptr(qkv), qkv.stride(0), _ptr(cos_tab), _ptr(sin_tab), pos_dev, pos_host, B, S,
+                                     hq, hkv, hd, max_len, _ptr(q), _ptr(k_cache), _ptr(v_cache),
+                                     _stream(qkv.device)),
                "dq_rope_kv_append")
-    return q
+    return q.transpose(1, 2)

@@ -390,19 +390,22 @@ DQ_API int dq_linear_a16w4(const void* x_bf16, int64_t ldx, const float* a, cons
                            void* scratch, size_t scratch_bytes, void* stream);
 
 /*
- * Decode-step glue of the end-to-end harness: rotary position embedding of the query and key heads
- * of one new token per sequence and the append of its key / value heads to the cache, in one launch.
- * qkv is the bf16 output of the fused q/k/v linear, [B, (hq + 2 hkv) * head_dim] with row stride
- * ld_qkv; cos / sin tables are bf16 [max_len, head_dim]; *pos (device int64) is the cache position;
- * q_out [B, hq, head_dim]; caches [B, hkv, max_len, head_dim].  Arithmetic: the bf16 tensor
- * expression x * cos + rotate_half(x) * sin of the HF Llama layer the reference's harness drives
- * (ablation/real_int4_kernel/graph_bench_all.py:72-157 times that layer unchanged, with a static
- * cache): both products rounded to bf16, then their sum.
+ * Attention glue of the end-to-end harness: rotary position embedding of the query and key heads
+ * of S new tokens per sequence (S = 1 in decode, the prompt length in prefill) and the write of
+ * their key / value heads into the cache, in one launch.
+ * qkv is the bf16 output of the fused q/k/v linear, [B * S, (hq + 2 hkv) * head_dim] with row
+ * stride ld_qkv, token (b, s) in row b * S + s; cos / sin tables are bf16 [max_len, head_dim];
+ * token s goes to cache position pos0 + s, pos0 = *pos_dev (device int64) when pos_dev is given,
+ * else pos_host; q_out [B, S, hq, head_dim]; caches [B, hkv, max_len, head_dim].  Arithmetic: the
+ * bf16 tensor expression x * cos + rotate_half(x) * sin of the HF Llama layer the reference's
+ * harness drives (ablation/real_int4_kernel/graph_bench_all.py:72-157 times that layer unchanged,
+ * with a static cache): both products rounded to bf16, then their sum.  Tokens whose position
+ * falls outside the cache are skipped.
  */
 DQ_API int dq_rope_kv_append(const void* qkv_bf16, int64_t ld_qkv, const void* cos_tab_bf16,
-                             const void* sin_tab_bf16, const int64_t* pos, int B, int hq, int hkv,
-                             int head_dim, int max_len, void* q_out_bf16, void* k_cache_bf16,
-                             void* v_cache_bf16, void* stream);
+                             const void* sin_tab_bf16, const int64_t* pos_dev, int64_t pos_host, int B,
+                             int S, int hq, int hkv, int head_dim, int max_len, void* q_out_bf16,
+                             void* k_cache_bf16, void* v_cache_bf16, void* stream);
 
 /*
  * dq_linear_w4a4_int4 for callers that cannot hand the library any scratch memory.  (No

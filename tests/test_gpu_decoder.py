@@ -256,3 +256,54 @@ def test_decode_step_with_fused_rope_equals_the_unfused_step():
             x = layer.forward(x, cos, sin, 0, pos, mask, None, None)
         ref = torch.nn.functional.rms_norm(x[:, 0], (cfg.hidden_size,), model.norm, cfg.rms_norm_eps) @ model.lm_head.T
     assert torch.equal(fused, ref)
+
+
+def test_rope_kv_append_prompt_tokens_equal_the_torch_expression():
+    """S tokens per sequence from a host start position: rotated queries, keys and values land
+    where x * cos + rotate_half(x) * sin and the slice assignment into the cache put them."""
+    from dualquant_b200 import ops
+
+    B, S, hq, hkv, hd, max_len, p0 = 3, 11, 8, 2, 64, 40, 5
+    g = torch.Generator(device=DEV).manual_seed(6)
+    qkv = torch.randn(B * S, (hq + 2 * hkv) * hd, generator=g, device=DEV).to(torch.bfloat16)
+    cfg = decoder.DecoderConfig(head_dim=hd)
+    cos, sin = decoder._rope_tables(cfg, max_len, torch.device(DEV))
+    kc = torch.randn(B, hkv, max_len, hd, generator=g, device=DEV).to(torch.bfloat16)
+    vc = torch.randn(B, hkv, max_len, hd, generator=g, device=DEV).to(torch.bfloat16)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    q = ops.rope_kv_append(qkv, cos, sin, p0, hq, hkv, kc, vc, tokens_per_seq=S)
+    x = qkv.reshape(B, S, hq + 2 * hkv, hd)
+    c, s = cos[p0:p0 + S], sin[p0:p0 + S]
+    q_ref = decoder._apply_rope(x[:, :, :hq].transpose(1, 2), c, s)
+    kc_ref[:, :, p0:p0 + S] = decoder._apply_rope(x[:, :, hq:hq + hkv].transpose(1, 2), c, s)
+    vc_ref[:, :, p0:p0 + S] = x[:, :, hq + hkv:].transpose(1, 2)
+    assert q.shape == q_ref.shape and torch.equal(q, q_ref)
+    assert torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+    with pytest.raises(ValueError):
+        ops.rope_kv_append(qkv, cos, sin, max_len - S + 1, hq, hkv, kc, vc, tokens_per_seq=S)
+
+
+def test_prefill_with_fused_rope_matches_the_unfused_prefill():
+    """Prefill through the one-launch RoPE + cache write and grouped-query attention on the cache
+    against the element-wise torch ops with expanded K / V heads: same caches bit for bit, logits
+    within the attention kernels' bf16 summation-order difference."""
+    cfg = _small_cfg()
+    model = _build(cfg)
+    B, S = 2, 24
+    model.alloc_cache(B, S + 2)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), device=DEV)
+    with torch.no_grad():
+        fused = model.prefill(ids).float()
+        k0 = model.layers[0].k_cache.clone()
+        v0 = model.layers[0].v_cache.clone()
+        for layer in model.layers:
+            layer.k_cache.zero_()
+            layer.v_cache.zero_()
+        x = model.embed[ids]
+        for layer in model.layers:
+            x = layer.forward(x, model.cos[:S], model.sin[:S], 0, None, None, None)
+        ref = (torch.nn.functional.rms_norm(x[:, -1], (cfg.hidden_size,), model.norm, cfg.rms_norm_eps)
+               @ model.lm_head.T).float()
+    assert torch.equal(k0, model.layers[0].k_cache) and torch.equal(v0, model.layers[0].v_cache)
+    cos_sim = torch.nn.functional.cosine_similarity(fused.flatten(), ref.flatten(), dim=0).item()
+    assert cos_sim > 0.9
