@@ -67,6 +67,77 @@ __global__ void rope_kv_append_kernel(const unsigned short* __restrict__ qkv, in
   dst[i + half] = float_to_bf16_bits(hi);
 }
 
+// The same step, eight elements per access: thread = (head, chunk of 8 elements of the first half
+// of the head); it also owns the matching chunk of the second half.  grid: (B * S, ceil(units /
+// blockDim.x)), units = heads * head_dim / 16.  Needs head_dim % 16 == 0 and 16-byte aligned rows.
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f[2 * j] = __uint_as_float(w[j] << 16);
+    f[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+  }
+}
+
+__global__ void __launch_bounds__(128)
+rope_kv_append_vec_kernel(const unsigned short* __restrict__ qkv, int64_t ld_qkv,
+                          const unsigned short* __restrict__ cos_tab,
+                          const unsigned short* __restrict__ sin_tab,
+                          const long long* __restrict__ pos_ptr, long long pos_host, int S, int hq,
+                          int hkv, int hd, int max_len, unsigned short* __restrict__ q_out,
+                          unsigned short* __restrict__ k_cache, unsigned short* __restrict__ v_cache) {
+  grid_dep_launch_dependents();
+  grid_dep_wait();
+  const int half = hd / 2, chunks = half / 8;
+  const int unit = blockIdx.y * blockDim.x + threadIdx.x;
+  if (unit >= (hq + 2 * hkv) * chunks) return;
+  const int head = unit / chunks, i = (unit - head * chunks) * 8;
+  const int row = blockIdx.x;
+  const int b = row / S, sidx = row - b * S;
+  const long long pos = ((pos_ptr != nullptr) ? *pos_ptr : pos_host) + sidx;
+  if (pos < 0 || pos >= max_len) return;
+  const unsigned short* x = qkv + static_cast<int64_t>(row) * ld_qkv + static_cast<int64_t>(head) * hd;
+  const uint4 lo_in = *reinterpret_cast<const uint4*>(x + i);
+  const uint4 hi_in = *reinterpret_cast<const uint4*>(x + i + half);
+  unsigned short* dst;
+  if (head >= hq + hkv) {
+    dst = v_cache + ((static_cast<int64_t>(b) * hkv + (head - hq - hkv)) * max_len + pos) * hd;
+    *reinterpret_cast<uint4*>(dst + i) = lo_in;
+    *reinterpret_cast<uint4*>(dst + i + half) = hi_in;
+    return;
+  }
+  float x1[8], x2[8], c1[8], c2[8], s1[8], s2[8];
+  unpack_bf16x8(lo_in, x1);
+  unpack_bf16x8(hi_in, x2);
+  const unsigned short* c = cos_tab + pos * hd;
+  const unsigned short* s = sin_tab + pos * hd;
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(c + i), c1);
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(c + i + half), c2);
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(s + i), s1);
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(s + i + half), s2);
+  uint32_t lo[4], hi[4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float l = __fadd_rn(round_to_bf16(__fmul_rn(x1[j], c1[j])), round_to_bf16(__fmul_rn(-x2[j], s1[j])));
+    const float h = __fadd_rn(round_to_bf16(__fmul_rn(x2[j], c2[j])), round_to_bf16(__fmul_rn(x1[j], s2[j])));
+    const uint32_t lb = float_to_bf16_bits(l), hb = float_to_bf16_bits(h);
+    if (j & 1) {
+      lo[j >> 1] |= lb << 16;
+      hi[j >> 1] |= hb << 16;
+    } else {
+      lo[j >> 1] = lb;
+      hi[j >> 1] = hb;
+    }
+  }
+  if (head < hq) {
+    dst = q_out + (static_cast<int64_t>(row) * hq + head) * hd;
+  } else {
+    dst = k_cache + ((static_cast<int64_t>(b) * hkv + (head - hq)) * max_len + pos) * hd;
+  }
+  *reinterpret_cast<uint4*>(dst + i) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  *reinterpret_cast<uint4*>(dst + i + half) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+}
+
 }  // namespace dq
 
 using namespace dq;
@@ -86,13 +157,24 @@ extern "C" int dq_rope_kv_append(const void* qkv_bf16, int64_t ld_qkv, const voi
   DQ_REQUIRE(ld_qkv >= static_cast<int64_t>(hq + 2 * hkv) * head_dim, DQ_ERR_SHAPE, "ld_qkv too small");
   DQ_REQUIRE(pos_dev != nullptr || (pos_host >= 0 && pos_host + S <= max_len), DQ_ERR_SHAPE,
              "positions %lld..%lld outside the cache of %d", (long long)pos_host, (long long)(pos_host + S), max_len);
-  DQ_CHECK_CUDA(launch_pdl(rope_kv_append_kernel, dim3(B * S, hq + 2 * hkv), dim3(head_dim / 2), 0,
-                           static_cast<cudaStream_t>(stream), static_cast<const unsigned short*>(qkv_bf16), ld_qkv,
-                           static_cast<const unsigned short*>(cos_tab_bf16),
-                           static_cast<const unsigned short*>(sin_tab_bf16),
-                           reinterpret_cast<const long long*>(pos_dev), static_cast<long long>(pos_host), S, hq, hkv,
-                           head_dim, max_len, static_cast<unsigned short*>(q_out_bf16),
-                           static_cast<unsigned short*>(k_cache_bf16), static_cast<unsigned short*>(v_cache_bf16)));
+  const cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  const auto* xq = static_cast<const unsigned short*>(qkv_bf16);
+  const auto* ct = static_cast<const unsigned short*>(cos_tab_bf16);
+  const auto* sn = static_cast<const unsigned short*>(sin_tab_bf16);
+  const auto* pp = reinterpret_cast<const long long*>(pos_dev);
+  auto* qo = static_cast<unsigned short*>(q_out_bf16);
+  auto* kc = static_cast<unsigned short*>(k_cache_bf16);
+  auto* vc = static_cast<unsigned short*>(v_cache_bf16);
+  const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (head_dim % 16 == 0 && ld_qkv % 8 == 0 && al16(xq) && al16(ct) && al16(sn) && al16(qo) && al16(kc) && al16(vc)) {
+    const int units = (hq + 2 * hkv) * (head_dim / 16);
+    DQ_CHECK_CUDA(launch_pdl(rope_kv_append_vec_kernel, dim3(B * S, (units + 127) / 128), dim3(128), 0, cs, xq,
+                             ld_qkv, ct, sn, pp, static_cast<long long>(pos_host), S, hq, hkv, head_dim, max_len, qo,
+                             kc, vc));
+  } else {
+    DQ_CHECK_CUDA(launch_pdl(rope_kv_append_kernel, dim3(B * S, hq + 2 * hkv), dim3(head_dim / 2), 0, cs, xq, ld_qkv,
+                             ct, sn, pp, static_cast<long long>(pos_host), S, hq, hkv, head_dim, max_len, qo, kc, vc));
+  }
   DQ_CHECK_CUDA(cudaGetLastError());
   return DQ_OK;
 }

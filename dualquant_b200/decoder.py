@@ -265,7 +265,11 @@ class Decoder:
         x = self.embed[ids].unsqueeze(1)
         cos = self.cos.index_select(0, pos_t)
         sin = self.sin.index_select(0, pos_t)
-        mask = (torch.arange(self.max_len, device=self.device) <= pos_t).view(1, 1, 1, self.max_len)
+        # additive mask over the unwritten tail of the cache, built once per step (a boolean mask
+        # would be converted by the attention call in every layer)
+        hidden = torch.arange(self.max_len, device=self.device) > pos_t
+        mask = torch.zeros(self.max_len, dtype=torch.bfloat16, device=self.device).masked_fill_(hidden, float("-inf"))
+        mask = mask.view(1, 1, 1, self.max_len)
         for layer in self.layers:
             x = layer.forward(x, cos, sin, 0, pos_t, mask, self.group, self.ar, rope_tabs=(self.cos, self.sin))
         x = _rms_norm(x[:, 0], self.norm, self.cfg.rms_norm_eps)

@@ -212,12 +212,13 @@ def test_captured_decode_step_equals_eager():
             static_tok.copy_(eager.argmax(-1))
 
 
-def test_rope_kv_append_equals_the_torch_expression():
+@pytest.mark.parametrize("hd", [64, 128, 40])  # 40: not a multiple of 16, the element-wise kernel
+def test_rope_kv_append_equals_the_torch_expression(hd):
     """One launch for RoPE + cache append against the bf16 tensor expression
     x * cos + rotate_half(x) * sin and index_copy_ that it replaces: bit-identical."""
     from dualquant_b200 import ops
 
-    B, hq, hkv, hd, max_len = 5, 8, 2, 64, 40
+    B, hq, hkv, max_len = 5, 8, 2, 40
     g = torch.Generator(device=DEV).manual_seed(5)
     qkv = torch.randn(B, (hq + 2 * hkv) * hd, generator=g, device=DEV).to(torch.bfloat16)
     cfg = decoder.DecoderConfig(head_dim=hd)
@@ -258,12 +259,13 @@ def test_decode_step_with_fused_rope_equals_the_unfused_step():
     assert torch.equal(fused, ref)
 
 
-def test_rope_kv_append_prompt_tokens_equal_the_torch_expression():
+@pytest.mark.parametrize("hd", [64, 40])
+def test_rope_kv_append_prompt_tokens_equal_the_torch_expression(hd):
     """S tokens per sequence from a host start position: rotated queries, keys and values land
     where x * cos + rotate_half(x) * sin and the slice assignment into the cache put them."""
     from dualquant_b200 import ops
 
-    B, S, hq, hkv, hd, max_len, p0 = 3, 11, 8, 2, 64, 40, 5
+    B, S, hq, hkv, max_len, p0 = 3, 11, 8, 2, 40, 5
     g = torch.Generator(device=DEV).manual_seed(6)
     qkv = torch.randn(B * S, (hq + 2 * hkv) * hd, generator=g, device=DEV).to(torch.bfloat16)
     cfg = decoder.DecoderConfig(head_dim=hd)
