@@ -80,6 +80,9 @@ SIGNATURES = {
     "dq_gemm_w4a4_int4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
     "dq_quant_act_int4_grouped": (_i, [_vp, _i64, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
     "dq_gemm_w4a4_int4_grouped": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
+    "dq_expand_w_int4_e4m3": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "dq_codes_to_e4m3": (_i, [_vp, _i64, _i, _i, _vp, _vp]),
+    "dq_gemm_w4a4_int4_e4m3": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
     "dq_gemm_w4a4_int4_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),
     "dq_gemm_w4a4_int4_ar": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),

@@ -27,6 +27,7 @@ SOURCES = [
     "mma_peak.cu",
     "gemm_a16w4.cu",
     "decoder_ops.cu",
+    "gemm_w4a4_int4_f8.cu",
 ]
 
 NVCC_FLAGS = [

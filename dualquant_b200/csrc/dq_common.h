@@ -103,6 +103,10 @@ int init_act_quant_kernels();
 int init_gemv_fused_kernels();
 int init_mma_peak_kernels();
 int init_gemm_a16w4_kernels();
+int init_gemm_int4_f8_kernels();
+int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t, const float* r,
+                          int M, int N, int K, void* y, int y_dtype, const void* residual, cudaStream_t stream,
+                          DeviceState* st);
 
 // One-launch decode linear (quantiser inside the GEMM kernel), defined in gemv_w4a4_int4_fused.cu.
 bool gemv_fused_covers(int M, int N, int K, const DeviceState* st);

@@ -168,6 +168,8 @@ extern "C" int dq_init(int device) {
   if (rc != DQ_OK) return rc;
   rc = init_gemm_a16w4_kernels();
   if (rc != DQ_OK) return rc;
+  rc = init_gemm_int4_f8_kernels();
+  if (rc != DQ_OK) return rc;
   DQ_CHECK_CUDA(cudaDeviceSynchronize());
   st->ready = true;
   return DQ_OK;

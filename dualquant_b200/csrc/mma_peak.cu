@@ -1,6 +1,6 @@
 // Tensor-pipe ceiling probe: tcgen05.mma issue loops on operands that never leave shared / tensor
 // memory.  Gives the denominator "what the tensor cores sustain with nothing else going on" for
-// kind::i8 (the int4-as-int8 path) and kind::mxf4nvf4.block_scale (MXFP4 / NVFP4), measured on the
+// kind::i8 and kind::f8f6f4 (the int4 paths) and kind::mxf4nvf4.block_scale (MXFP4 / NVFP4), measured on the
 // GPU at hand instead of scaled from a bf16 figure.  One CTA per SM; one thread issues UMMAs of
 // 128 x 256 x (32 bytes of K) back to back into one accumulator, commits once and waits (bounded).
 #include "dq_common.h"
@@ -39,7 +39,17 @@ __device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint6
   }
 }
 
-// KIND: 0 = kind::i8, 1 = MXFP4 (E8M0, scale_vec::2X), 2 = NVFP4 (E4M3, scale_vec::4X)
+__device__ __forceinline__ void umma_e4m3(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// KIND: 0 = kind::i8, 1 = MXFP4 (E8M0, scale_vec::2X), 2 = NVFP4 (E4M3, scale_vec::4X),
+//       3 = kind::f8f6f4 with E4M3 operands and an fp32 accumulator
 template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1) mma_peak_kernel(int iters, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -78,6 +88,13 @@ __global__ void __launch_bounds__(kThreads, 1) mma_peak_kernel(int iters, int* s
 #pragma unroll
         for (int j = 0; j < 4; ++j) umma_i8(tmem_base, da + 2 * j, db + 2 * j, idesc, (i | j) ? 1u : 0u);
       }
+    } else if constexpr (KIND == 3) {
+      // E4M3 A and B (format code 0), fp32 accumulator (D format 1)
+      const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(256 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+      for (int i = 0; i < iters; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) umma_e4m3(tmem_base, da + 2 * j, db + 2 * j, idesc, (i | j) ? 1u : 0u);
+      }
     } else {
       constexpr int NV = (KIND == 2) ? 1 : 0;
       const uint32_t sfa = tmem_base + 256;
@@ -109,6 +126,8 @@ int init_mma_peak_kernels() {
     e = cudaFuncSetAttribute(peak::mma_peak_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, peak::kSmem);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(peak::mma_peak_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, peak::kSmem);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(peak::mma_peak_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, peak::kSmem);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(mma_peak) failed: %s", cudaGetErrorString(e));
   return DQ_OK;
@@ -121,16 +140,17 @@ using namespace dq;
 extern "C" int dq_mma_peak_probe(int kind, int iters, double* ops_out, void* stream) {
   DeviceState* st = current_state();
   if (st == nullptr) return DQ_ERR_NOT_INIT;
-  DQ_REQUIRE(kind >= 0 && kind <= 2, DQ_ERR_SHAPE, "kind must be 0 (int8), 1 (MXFP4) or 2 (NVFP4)");
+  DQ_REQUIRE(kind >= 0 && kind <= 3, DQ_ERR_SHAPE, "kind must be 0 (int8), 1 (MXFP4), 2 (NVFP4) or 3 (E4M3)");
   DQ_REQUIRE(iters >= 1 && iters <= (1 << 20), DQ_ERR_SHAPE, "iters out of range");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(st->sm_count), block(peak::kThreads);
   if (kind == 0) peak::mma_peak_kernel<0><<<grid, block, peak::kSmem, s>>>(iters, st->status_dev);
   else if (kind == 1) peak::mma_peak_kernel<1><<<grid, block, peak::kSmem, s>>>(iters, st->status_dev);
-  else peak::mma_peak_kernel<2><<<grid, block, peak::kSmem, s>>>(iters, st->status_dev);
+  else if (kind == 2) peak::mma_peak_kernel<2><<<grid, block, peak::kSmem, s>>>(iters, st->status_dev);
+  else peak::mma_peak_kernel<3><<<grid, block, peak::kSmem, s>>>(iters, st->status_dev);
   DQ_CHECK_CUDA(cudaGetLastError());
   if (ops_out != nullptr) {
-    const double k_elems = (kind == 0) ? 32.0 : 64.0;  // K per instruction
+    const double k_elems = (kind == 0 || kind == 3) ? 32.0 : 64.0;  // K per instruction
     *ops_out = static_cast<double>(st->sm_count) * iters * 4.0 * 2.0 * 128.0 * 256.0 * k_elems;
   }
   return DQ_OK;

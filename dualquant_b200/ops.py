@@ -273,6 +273,46 @@ def gemm_w4a4_int4(codes: torch.Tensor, sx: torch.Tensor, pw: PackedInt4Weight,
     return out
 
 
+def expand_w_e4m3(pw: PackedInt4Weight) -> torch.Tensor:
+    """E4M3 byte copy [N, K] of the packed int4 weight (operand of gemm_w4a4_int4_e4m3)."""
+    lib = _prep(pw.w_packed)
+    w8 = torch.empty(pw.N, pw.K, dtype=torch.uint8, device=pw.w_packed.device)
+    _lib.check(lib.dq_expand_w_int4_e4m3(_ptr(pw.w_packed), pw.N, pw.K, pw.group, _ptr(w8),
+                                         _stream(w8.device)), "dq_expand_w_int4_e4m3")
+    return w8
+
+
+def codes_to_e4m3(codes: torch.Tensor) -> torch.Tensor:
+    """int8 activation codes [M, K] -> the same integers as E4M3 bytes."""
+    lib = _prep(codes)
+    M, K = codes.shape
+    x8 = torch.empty(M, K, dtype=torch.uint8, device=codes.device)
+    _lib.check(lib.dq_codes_to_e4m3(_ptr(codes), codes.stride(0), M, K, _ptr(x8), _stream(codes.device)),
+               "dq_codes_to_e4m3")
+    return x8
+
+
+def gemm_w4a4_int4_e4m3(x8: torch.Tensor, sx: torch.Tensor, w8: torch.Tensor, pw: PackedInt4Weight,
+                        r: Optional[torch.Tensor] = None, out_dtype=torch.float32,
+                        out: Optional[torch.Tensor] = None,
+                        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The int4 GEMM on the FP8 tensor-core path (prefill); same bits as gemm_w4a4_int4."""
+    lib = _prep(x8)
+    M, K = x8.shape
+    if K != pw.K or tuple(w8.shape) != (pw.N, pw.K) or not x8.is_contiguous() or not w8.is_contiguous():
+        raise ValueError("x8 [M, K] and w8 [N, K] must be contiguous and match the packed weight")
+    if out is None:
+        out = torch.empty(M, pw.N, dtype=residual.dtype if residual is not None else out_dtype, device=x8.device)
+    if residual is not None and (residual.dtype != out.dtype or tuple(residual.shape) != (M, pw.N)
+                                 or not residual.is_contiguous()):
+        raise ValueError("residual must be a contiguous [M, N] tensor of the output's dtype")
+    ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
+    _lib.check(lib.dq_gemm_w4a4_int4_e4m3(_ptr(x8), _ptr(sx), _ptr(w8), _ptr(pw.sw_t), _ptr(r), M, pw.N, K,
+                                          pw.group, _ptr(out), ydt, _ptr(residual), _stream(x8.device)),
+               "dq_gemm_w4a4_int4_e4m3")
+    return out
+
+
 class AllReduceContext:
     """Peer-mapped exchange buffers of the all-reduce fused into the decode GEMM
     (dq_gemm_w4a4_int4_ar).  Built once per process group from torch symmetric memory: one

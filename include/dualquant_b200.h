@@ -303,6 +303,23 @@ DQ_API int dq_gemm_w4a4_int4_residual(const int8_t* codes, const float* sx, cons
                                       int N, int K, int G, void* y, int y_dtype, void* stream);
 
 /*
+ * The same GEMM for token counts where it is compute-bound (prefill), on the FP8 tensor-core path:
+ * every int4 code is an exact E4M3 number and a group's 128 products sum to an integer below
+ * 2^24, so tcgen05.mma kind::f8f6f4 with an fp32 accumulator yields the group sums exactly and
+ * the result equals dq_gemm_w4a4_int4's bit for bit (same replacement target:
+ * ablation/real_int4_kernel/fused_w4a4_kernel.py:60-130 / activations/perm_linear.py:104-131).
+ * Operands are bytes: dq_expand_w_int4_e4m3 derives w8 [N,K] from the packed artefact (once, or
+ * per call into scratch), dq_codes_to_e4m3 converts the quantiser's int8 codes [M,K] (row stride
+ * ld) to x8 [M,K].  sw_t, r, sx, y, residual as in dq_gemm_w4a4_int4_residual (residual may be
+ * NULL).  Any M >= 1 is accepted; the kernel works on tiles of 256 tokens.
+ */
+DQ_API int dq_expand_w_int4_e4m3(const uint8_t* w_packed, int N, int K, int G, uint8_t* w8, void* stream);
+DQ_API int dq_codes_to_e4m3(const int8_t* codes, int64_t ld, int M, int K, uint8_t* x8, void* stream);
+DQ_API int dq_gemm_w4a4_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t,
+                                  const float* r, int M, int N, int K, int G, void* y, int y_dtype,
+                                  const void* residual, void* stream);
+
+/*
  * The variant of the reference's fused W4A4 Triton kernel that scales activations per (token,
  * K tile) instead of per token (ablation/real_int4_kernel/fused_w4a4_kernel.py:93-100,119) and of
  * the per-group activation quantiser of its nunchaku path
