@@ -31,29 +31,45 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <string.h>
 
 namespace dq {
 namespace f8 {
 
 constexpr int kBN = 128;    // weight rows per tile
 constexpr int kTN = 256;    // tokens per tile
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kABytes = kBN * kGroup;   // 16 KB
 constexpr int kBBytes = kTN * kGroup;   // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kEpiWarps = 8;
-constexpr int kProducerWarp = 8;
-constexpr int kIssuerWarp = 9;
-constexpr int kThreads = 384;
-constexpr int kOffBar = kStages * kStageBytes;
-constexpr int kNumBars = 2 * kStages + 4;
+// EW epilogue warps (8 or 16), then the producer warp, the issuing warp and two idle warps that
+// complete the last warpgroup (register re-balancing works on whole warpgroups).
+template <int EW, int CH>
+struct Shape {
+  static constexpr int kEpiWarps = EW;
+  static constexpr int kProducerWarp = EW;
+  static constexpr int kIssuerWarp = EW + 1;
+  static constexpr int kThreads = (EW + 4) * 32;
+  static constexpr int kCPW = kTN / (EW / 4);  // accumulator columns per epilogue warp
+  static constexpr int kCH = CH;                // columns per tcgen05.ld
+  // setmaxnreg.inc waits (without bound) until the CTA's pool holds the registers it asks for, and
+  // the pool is what the launch granted (threads x registers per thread) minus what the other warps
+  // keep: the two budgets below must fit into it or the kernel never starts.
+  static constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
+  static constexpr int kEpiRegs = (EW == 8) ? 232 : 104;
+  static constexpr int kAuxRegs = 40;
+  static_assert(EW * 32 * kEpiRegs + 128 * kAuxRegs <= kThreads * kLaunchRegs, "register pool of the CTA");
+};
+constexpr int kOffOut = kStages * kStageBytes;   // bf16 output tile [256 tokens][128 rows], source of the bulk store
+constexpr int kOutBytes = kTN * kBN * 2;
+constexpr int kOffSx = kOffOut + kOutBytes;      // token scales of the tile, double-buffered
+constexpr int kOffBar = kOffSx + 2 * kTN * 4;
+constexpr int kNumBars = 2 * kStages + 6;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kCPW = 128;   // accumulator columns per epilogue warp
-constexpr int kCH = 16;     // columns per tcgen05.ld
 static_assert(kSmemBytes + 1024 <= 227 * 1024, "shared memory");
 
-enum { FSITE_TMA = 61, FSITE_MMA_FULL = 62, FSITE_MMA_ACC = 63, FSITE_EPI = 64, FSITE_ALIGN = 65 };
+enum { FSITE_TMA = 61, FSITE_MMA_FULL = 62, FSITE_MMA_ACC = 63, FSITE_EPI = 64, FSITE_ALIGN = 65, FSITE_OUT = 66 };
 
 // Instruction descriptor, kind::f8f6f4: E4M3 A and B (format code 0, both K-major), fp32 accumulator.
 //   [4,6) D format (1 = F32)  [7,10) A format  [10,13) B format  [17,23) N >> 3  [24,29) M >> 4
@@ -138,12 +154,23 @@ __global__ void __launch_bounds__(256) codes_to_e4m3_kernel(const int8_t* __rest
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int EW, int CH>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t* v) {
+  if constexpr (CH == 8) tmem_ld_x8(taddr, v);
+  else if constexpr (CH == 16) tmem_ld_x16(taddr, v);
+  else tmem_ld_x32(taddr, v);
+}
+
+template <int EW, int CH>
+__global__ void __launch_bounds__(Shape<EW, CH>::kThreads, 1)
 gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                      const __half* __restrict__ sw_t, const float* __restrict__ r,
+                      const __grid_constant__ CUtensorMap tm_y, int bulk_out, const __half* __restrict__ sw_t, const float* __restrict__ r,
                       const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
                       const void* __restrict__ residual, int M, int N, int K, int row_tiles, int tok_tiles,
-                      int* status) {
+                      int tok_block, int* status) {
+  using S = Shape<EW, CH>;
+  constexpr int kEpiWarps = S::kEpiWarps, kProducerWarp = S::kProducerWarp, kIssuerWarp = S::kIssuerWarp;
+  constexpr int kCPW = S::kCPW, kCH = S::kCH;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicCAS(status, 0, FSITE_ALIGN);
@@ -154,7 +181,9 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   uint64_t* empty = full + kStages;
   uint64_t* acc_full = empty + kStages;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* out_free = acc_empty + 2;   // the output tile may be overwritten and the token scales are in place
+  uint64_t* out_ready = out_free + 1;   // the output tile is written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_ready + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
@@ -164,14 +193,22 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   const int total_tiles = row_tiles * tok_tiles;
   const int my_tiles = (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                        static_cast<int>(gridDim.x);
-  // tile order: tokens fastest, so the CTAs running at one time share a few weight tiles and the
-  // whole activation matrix stays in L2 from one row band to the next
-  auto tile_row = [&](int it) { return (static_cast<int>(blockIdx.x) + it * static_cast<int>(gridDim.x)) / tok_tiles; };
-  auto tile_tok = [&](int it) { return (static_cast<int>(blockIdx.x) + it * static_cast<int>(gridDim.x)) % tok_tiles; };
-
+  // Tile order: token tiles in blocks of tok_block; inside a block all row tiles, tokens fastest.  The
+  // CTAs running at one time then share a few weight tiles, and a block's activations (sized by the
+  // host to fit in L2 next to them) are read from HBM once.
+  const int full_block = tok_block * row_tiles;
+  auto tile_of = [&](int it, int& row, int& tok) {
+    const int t = static_cast<int>(blockIdx.x) + it * static_cast<int>(gridDim.x);
+    const int b = t / full_block, rem = t - b * full_block;
+    const int width = (tok_tiles - b * tok_block < tok_block) ? (tok_tiles - b * tok_block) : tok_block;
+    row = rem / width;
+    tok = b * tok_block + (rem - row * width);
+  };
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], kEpiWarps); }
+    mbar_init(out_free, kEpiWarps);
+    mbar_init(out_ready, kEpiWarps);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -182,6 +219,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
+    if (bulk_out) tma_prefetch_desc(&tm_y);
   }
   grid_dep_launch_dependents();
   tc_fence_before();
@@ -191,7 +229,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 
   if (warp < kEpiWarps) {
     // ------------------------------------------------------------------ epilogue
-    setmaxnreg_inc<232>();
+    setmaxnreg_inc<S::kEpiRegs>();
     const int q = warp & 3, h = warp >> 2;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(h * kCPW);
     float run[kCPW];
@@ -215,14 +253,14 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       if (!mbar_wait(&acc_full[b], (gi >> 1) & 1, abort_flag, FSITE_EPI)) return false;
       tc_fence_after();
       const uint32_t t0a = t_lane + static_cast<uint32_t>(b * kTN);
-      tmem_ld_x16(t0a, va);
+      tmem_ld_chunk<EW, CH>(t0a, va);
 #pragma unroll
       for (int c = 0; c < kCPW / kCH; ++c) {
         uint32_t* cur = (c & 1) ? vb : va;
         uint32_t* nxt = (c & 1) ? va : vb;
         tmem_ld_wait();
         if (c + 1 < kCPW / kCH) {
-          tmem_ld_x16(t0a + static_cast<uint32_t>((c + 1) * kCH), nxt);
+          tmem_ld_chunk<EW, CH>(t0a + static_cast<uint32_t>((c + 1) * kCH), nxt);
         } else {
           tc_fence_before();
           __syncwarp();
@@ -233,10 +271,15 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       return true;
     };
     bool ok = true;
+    unsigned short* out_sm = reinterpret_cast<unsigned short*>(smem + kOffOut);
+    float* sx_sm = reinterpret_cast<float*>(smem + kOffSx);
+    grid_dep_wait();  // the token scales come from the kernel before this one
     for (int it = 0; it < my_tiles && ok; ++it) {
-      const int row_tile = tile_row(it);
+      int row_tile, tok_tile;
+      tile_of(it, row_tile, tok_tile);
       const int n = row_tile * kBN + q * 32 + lane;
-      const int t0 = tile_tok(it) * kTN;
+      const int t0 = tok_tile * kTN;
+      if (bulk_out && tid < kTN) sx_sm[(it & 1) * kTN + tid] = (t0 + tid < M) ? __ldg(sx + t0 + tid) : 0.f;
 #pragma unroll
       for (int j = 0; j < kCPW; ++j) run[j] = 0.f;
       sw_row = reinterpret_cast<const unsigned short*>(sw_t) + static_cast<size_t>(row_tile) * ng * kBN + q * 32 + lane;
@@ -249,7 +292,38 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
       if (!ok) break;
-      if (n < N) {
+      if (bulk_out) {
+        // Y tile -> shared memory as [token][row] bf16 (a warp's 32 rows of one token are 64
+        // contiguous bytes), then one tiled bulk store; rows past N and tokens past M are clipped
+        // by the copy.  Two-byte global stores from here would cost more than two groups' UMMAs.
+        if (tid == 0) bulk_wait_group_read0();  // the previous tile's store has left the buffer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(out_free);
+        if (!mbar_wait(out_free, it & 1, abort_flag, FSITE_OUT)) break;
+        const float rn = (r != nullptr && n < N) ? r[n] : 1.f;
+        const float4* sx4 = reinterpret_cast<const float4*>(sx_sm + (it & 1) * kTN + h * kCPW);
+        unsigned short* dst = out_sm + (h * kCPW) * kBN + q * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < kCPW; j += 4) {
+          const float4 sv = sx4[j >> 2];
+          dst[(j + 0) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 0] * (rn * sv.x)));
+          dst[(j + 1) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 1] * (rn * sv.y)));
+          dst[(j + 2) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 2] * (rn * sv.z)));
+          dst[(j + 3) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 3] * (rn * sv.w)));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(out_ready);
+        bool stored = true;
+        if (tid == 0) {
+          stored = mbar_wait(out_ready, it & 1, abort_flag, FSITE_OUT);
+          if (stored) {
+            tma_store_2d(&tm_y, out_sm, row_tile * kBN, t0);
+            bulk_commit_group();
+          }
+        }
+        ok = __all_sync(0xffffffffu, stored ? 1 : 0) != 0;  // the warp leaves the loop together
+      } else if (n < N) {
         const float rn = (r != nullptr) ? r[n] : 1.f;
         const int m0 = t0 + h * kCPW;
         const int cnt = (M - m0 < kCPW) ? (M - m0) : kCPW;
@@ -278,8 +352,9 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
     }
+    if (bulk_out && tid == 0) bulk_wait_group_read0();
   } else {
-    setmaxnreg_dec<40>();
+    setmaxnreg_dec<S::kAuxRegs>();
     if (warp == kProducerWarp) {
       // ---------------------------------------------------------------- TMA producer
       if (lane == 0) {
@@ -288,7 +363,9 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         bool ok = true;
         int gi = 0;
         for (int it = 0; it < my_tiles && ok; ++it) {
-          const int n0 = tile_row(it) * kBN, t0 = tile_tok(it) * kTN;
+          int row_tile, tok_tile;
+          tile_of(it, row_tile, tok_tile);
+          const int n0 = row_tile * kBN, t0 = tok_tile * kTN;
           for (int i = 0; i < ng; ++i, ++gi) {
             const int s = gi % kStages;
             if (!mbar_wait(&empty[s], ((gi / kStages) & 1) ^ 1, abort_flag, FSITE_TMA)) { ok = false; break; }
@@ -335,7 +412,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 }  // namespace f8
 
 int init_gemm_int4_f8_kernels() {
-  cudaError_t e = cudaFuncSetAttribute(f8::gemm_w4a4_e4m3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(f8::gemm_w4a4_e4m3_kernel<16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        f8::kSmemBytes);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemm_w4a4_e4m3) failed: %s", cudaGetErrorString(e));
@@ -356,9 +433,25 @@ int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8,
   const int row_tiles = (N + f8::kBN - 1) / f8::kBN, tok_tiles = (M + f8::kTN - 1) / f8::kTN;
   const int64_t tiles = static_cast<int64_t>(row_tiles) * tok_tiles;
   const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
-  cudaError_t e = launch_pdl(f8::gemm_w4a4_e4m3_kernel, dim3(grid), dim3(f8::kThreads), f8::kSmemBytes, stream, tm_w,
-                             tm_x, static_cast<const __half*>(sw_t), r, sx, y, y_dtype == DQ_DTYPE_BF16 ? 1 : 0, residual, M, N, K, row_tiles,
-                             tok_tiles, st->status_dev);
+  // activations of one block of token tiles: about 40 MB, so that they stay in L2 (126 MB) beside
+  // the weight tiles in use while every row tile passes over them
+  int tok_block = static_cast<int>((40ll << 20) / (static_cast<int64_t>(f8::kTN) * K));
+  if (tok_block < 1) tok_block = 1;
+  if (tok_block > tok_tiles) tok_block = tok_tiles;
+  const __half* sw = static_cast<const __half*>(sw_t);
+  const int yb = y_dtype == DQ_DTYPE_BF16 ? 1 : 0;
+  // bf16 output without a residual leaves through a tiled bulk store (needs 16-byte aligned rows)
+  const int bulk_out = (yb && residual == nullptr && N % 8 == 0 && aligned(y, 16)) ? 1 : 0;
+  CUtensorMap tm_y;
+  memset(&tm_y, 0, sizeof(tm_y));
+  if (bulk_out) {
+    rc = make_tmap_2d_out(&tm_y, y, 2, static_cast<uint64_t>(N), static_cast<uint64_t>(M), f8::kBN, f8::kTN);
+    if (rc != DQ_OK) return rc;
+  }
+  using Sh = f8::Shape<16, 16>;
+  cudaError_t e = launch_pdl(f8::gemm_w4a4_e4m3_kernel<16, 16>, dim3(grid), dim3(Sh::kThreads), f8::kSmemBytes, stream,
+                             tm_w, tm_x, tm_y, bulk_out, sw, r, sx, y, yb, residual, M, N, K, row_tiles, tok_tiles,
+                             tok_block, st->status_dev);
   if (e != cudaSuccess) return set_error(DQ_ERR_CUDA, "gemm_w4a4_e4m3 launch failed: %s", cudaGetErrorString(e));
   return DQ_OK;
 }
