@@ -15,6 +15,7 @@ LIB_PATH = os.environ.get("DUALQUANT_B200_LIB", os.path.join(_PKG, "lib", "libdu
 DQ_OK = 0
 DQ_ERR_TIMEOUT = 9
 DTYPE_F32, DTYPE_BF16 = 0, 1
+CODES_E4M3 = 0x100  # or-ed into scale_fp16: the quantiser writes E4M3 code bytes
 HAD_NONE, HAD_FULL, HAD_PARTIAL = 0, 1, 2
 FP4_MXFP4, FP4_NVFP4 = 0, 1
 
@@ -88,6 +89,7 @@ SIGNATURES = {
     "dq_gemm_w4a4_int4_ar": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
     "dq_gemm_w4a4_int4_acc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "dq_linear_w4a4_int4_scratch_bytes": (_sz, [_i, _i, _i]),
+    "dq_linear_w4a4_int4_prefill_scratch_bytes": (_sz, [_i, _i, _i]),
     "dq_linear_w4a4_int4": (_i, [_vp, _i64, _vp, _hp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _sz, _vp]),
     "dq_rope_kv_append": (_i, [_vp, _i64, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "dq_linear_a16w4_scratch_bytes": (_sz, [_i, _i, _i]),

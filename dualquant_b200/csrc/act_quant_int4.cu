@@ -122,13 +122,16 @@ struct Raw8<float> {
 __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t* codes_row,
                                       float* out_row, int idx, int smode = 0) {
   const float inv_s = __fdiv_rn(1.0f, s);
+  const bool e4m3 = (smode & kCodesE4M3) != 0;
+  smode &= 0xFF;
   if (smode == 2 && mode != MODE_RAW) {
     // bf16 arithmetic (see token_scale): codes, or the de-quantised value q * s as fp32 / bf16
     float q[8];
     quant_codes8_bf16(v, s, q);
     if (mode == MODE_CODES) {
       *reinterpret_cast<uint2*>(codes_row + idx) =
-          make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
+          e4m3 ? make_uint2(pack_codes4_e4m3(q[0], q[1], q[2], q[3]), pack_codes4_e4m3(q[4], q[5], q[6], q[7]))
+               : make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
     } else if (mode == MODE_FAKE_BF16) {
       uint32_t w[4];
 #pragma unroll
@@ -149,8 +152,8 @@ __device__ __forceinline__ void emit8(const float* v, float s, int mode, int8_t*
   if (mode == MODE_CODES) {
     float q[8];
     quant_codes8(v, s, inv_s, q);
-    const uint32_t lo = pack_codes4(q[0], q[1], q[2], q[3]);
-    const uint32_t hi = pack_codes4(q[4], q[5], q[6], q[7]);
+    const uint32_t lo = e4m3 ? pack_codes4_e4m3(q[0], q[1], q[2], q[3]) : pack_codes4(q[0], q[1], q[2], q[3]);
+    const uint32_t hi = e4m3 ? pack_codes4_e4m3(q[4], q[5], q[6], q[7]) : pack_codes4(q[4], q[5], q[6], q[7]);
     *reinterpret_cast<uint2*>(codes_row + idx) = make_uint2(lo, hi);
   } else if (mode == MODE_FAKE_BF16) {
     float o[8];

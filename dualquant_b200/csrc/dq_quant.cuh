@@ -13,11 +13,16 @@ __device__ __forceinline__ float round_to_bf16(float v) {
   return __uint_as_float(static_cast<uint32_t>(bits) << 16);
 }
 
-// scale_fp16: 0 = fp32 scale, 1 = scale rounded to fp16, 2 = "bf16 arithmetic": the quantiser as
+// Flag in the scale_fp16 argument of the quantisers: codes are written as E4M3 bytes of the same
+// integers (the operand format of the FP8-path prefill GEMM) instead of int8.
+constexpr int kCodesE4M3 = 0x100;
+
+// scale_fp16 (low byte): 0 = fp32 scale, 1 = scale rounded to fp16, 2 = "bf16 arithmetic": the quantiser as
 // torch evaluates it on a bf16 tensor (every intermediate rounded to bf16), which is what the
 // reference's PermLinear does when there is neither an activation scale nor an online Hadamard
 // (activations/perm_linear.py:131-133 with formats/rtn_int.py:62-67).
 __device__ __forceinline__ float token_scale(float amax, int scale_fp16) {
+  scale_fp16 &= 0xFF;
   float s = __fdiv_rn(amax, 7.0f);
   if (scale_fp16 == 2) s = round_to_bf16(s);
   if (amax == 0.f) s = 1.0f;
@@ -71,6 +76,12 @@ __device__ __forceinline__ uint32_t pack_codes4(float q0, float q1, float q2, fl
   const uint32_t u3 = __float_as_uint(__fadd_rn(q3, kRoundMagic));
   return __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
 }
-
+// the same four codes as E4M3 bytes (integers up to 8 are exact in E4M3; -0 is stored as +0)
+__device__ __forceinline__ uint32_t pack_codes4_e4m3(float q0, float q1, float q2, float q3) {
+  unsigned short lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(__fadd_rn(q1, 0.f)), "f"(__fadd_rn(q0, 0.f)));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(__fadd_rn(q3, 0.f)), "f"(__fadd_rn(q2, 0.f)));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
 
 }  // namespace dq

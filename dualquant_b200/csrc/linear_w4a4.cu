@@ -1,6 +1,8 @@
 // One-call PermLinear.forward on the real int4 path.  Decode batches (M <= 16, no online Hadamard)
-// run as ONE kernel that quantises in its prologue; everything else is activation quantiser + GEMM
-// on the caller's stream with the intermediates in caller-provided scratch.
+// may run as ONE kernel that quantises in its prologue; everything else is activation quantiser +
+// GEMM on the caller's stream with the intermediates in caller-provided scratch.  Prefill batches
+// (M >= kPrefillTokens) take the FP8 tensor-core path when the caller's scratch also has room for
+// the byte form of the weight: quantiser (E4M3 codes) + weight expansion + GEMM.
 #include "dq_common.h"
 
 namespace {
@@ -12,6 +14,16 @@ extern "C" size_t dq_linear_w4a4_int4_scratch_bytes(int M, int N, int K) {
   if (M < 0 || K < 0) return 0;
   return round_up(static_cast<size_t>(M) * static_cast<size_t>(K), 256) +
          round_up(static_cast<size_t>(M) * sizeof(float), 256);
+}
+
+// From this many tokens on the FP8-path GEMM wins even with the weight expanded on every call
+// (the expansion moves 1.5 bytes per weight; measured on B200 it pays from about 1000 tokens).
+static constexpr int kPrefillTokens = 1024;
+
+extern "C" size_t dq_linear_w4a4_int4_prefill_scratch_bytes(int M, int N, int K) {
+  const size_t base = dq_linear_w4a4_int4_scratch_bytes(M, N, K);
+  if (M < kPrefillTokens || N < 1 || K < 1) return base;
+  return base + round_up(static_cast<size_t>(N) * static_cast<size_t>(K), 256);
 }
 
 extern "C" int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float* a,
@@ -41,6 +53,16 @@ extern "C" int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float*
   int8_t* codes = static_cast<int8_t*>(scratch);
   float* sx = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) +
                                        round_up(static_cast<size_t>(M) * K, 256));
+  if (M >= kPrefillTokens && G == dq::kGroup && (scale_fp16 & ~0xFF) == 0 &&
+      scratch_bytes >= dq_linear_w4a4_int4_prefill_scratch_bytes(M, N, K)) {
+    uint8_t* w8 = static_cast<uint8_t*>(scratch) + dq_linear_w4a4_int4_scratch_bytes(M, N, K);
+    int rc = dq_expand_w_int4_e4m3(w_packed, N, K, G, w8, stream);
+    if (rc != DQ_OK) return rc;
+    rc = dq_quant_act_int4(x_bf16, ldx, a, had, M, K, codes, sx, scale_fp16 | DQ_CODES_E4M3, stream);
+    if (rc != DQ_OK) return rc;
+    return dq_gemm_w4a4_int4_e4m3(reinterpret_cast<const uint8_t*>(codes), sx, w8, sw_t, r, M, N, K, G, y, y_dtype,
+                                  nullptr, stream);
+  }
   int rc = dq_quant_act_int4(x_bf16, ldx, a, had, M, K, codes, sx, scale_fp16, stream);
   if (rc != DQ_OK) return rc;
   return dq_gemm_w4a4_int4(codes, sx, w_packed, sw_t, r, M, N, K, G, y, y_dtype, nullptr, 0, stream);

@@ -74,11 +74,22 @@ class W4A4Linear:
             self._scratch[M] = buf
         return buf
 
+    # From this many tokens on the linears run on the FP8-path GEMM with the weight's byte form kept
+    # next to the 4-bit artefact (N * K bytes more per weight; same results bit for bit).
+    PREFILL_TOKENS = 512
+
+    def _gemm(self, codes, sx, out_dtype=torch.bfloat16, residual=None):
+        if codes.dtype == torch.uint8:
+            return ops.gemm_w4a4_int4_e4m3(codes, sx, self.pw.bytes_e4m3(), self.pw, self.r, out_dtype=out_dtype,
+                                           residual=residual)
+        return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype, residual=residual)
+
     def normed(self, x: torch.Tensor, norm_weight: torch.Tensor, eps: float,
                out_dtype=torch.bfloat16) -> torch.Tensor:
         """RMSNorm(x) -> this linear, the norm fused into the activation quantiser."""
-        codes, sx = ops.quant_act_int4_rmsnorm(x, norm_weight, eps, self.a, False)
-        return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype)
+        codes, sx = ops.quant_act_int4_rmsnorm(x, norm_weight, eps, self.a, False,
+                                               e4m3=x.shape[0] >= self.PREFILL_TOKENS)
+        return self._gemm(codes, sx, out_dtype)
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.bfloat16, ar=None, residual=None) -> torch.Tensor:
         """ar: an ops.AllReduceContext -> the cross-rank sum happens inside the GEMM (M <= 16).
@@ -86,18 +97,20 @@ class W4A4Linear:
         if ar is not None:
             codes, sx = ops.quant_act_int4(x, self.a, self.had, False)
             return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
-        if residual is not None:
-            codes, sx = ops.quant_act_int4(x, self.a, self.had, False)
-            return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, residual=residual)
+        big = x.shape[0] >= self.PREFILL_TOKENS
+        if residual is not None or big:
+            codes, sx = ops.quant_act_int4(x, self.a, self.had, False, e4m3=big)
+            return self._gemm(codes, sx, out_dtype, residual)
         return ops.linear_w4a4_int4(x, self.a, self.had, self.pw, self.r, out_dtype=out_dtype,
                                     scale_fp16=False, scratch=self._scratch_for(x.shape[0], x.device))
 
     def gated(self, gate: torch.Tensor, up: torch.Tensor, out_dtype=torch.bfloat16, ar=None,
               residual=None) -> torch.Tensor:
-        codes, sx = ops.quant_act_int4_gated(gate, up, self.a, self.had, False)
+        big = ar is None and gate.shape[0] >= self.PREFILL_TOKENS
+        codes, sx = ops.quant_act_int4_gated(gate, up, self.a, self.had, False, e4m3=big)
         if ar is not None:
             return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
-        return ops.gemm_w4a4_int4(codes, sx, self.pw, self.r, out_dtype=out_dtype, residual=residual)
+        return self._gemm(codes, sx, out_dtype, residual)
 
 
 def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:

@@ -60,9 +60,17 @@ class PackedInt4Weight:
     K: int
     group: int = GROUP
 
+    w8: Optional[torch.Tensor] = None  # derived E4M3 byte copy [N, K] for the prefill GEMM (not saved)
+
     def state(self):
         return {"w_packed": self.w_packed, "sw_t": self.sw_t, "N": self.N, "K": self.K,
                 "group": self.group, "layout_version": 2}
+
+    def bytes_e4m3(self) -> torch.Tensor:
+        """The E4M3 byte form of the weight, expanded on first use and kept (N * K bytes)."""
+        if self.w8 is None:
+            self.w8 = expand_w_e4m3(self)
+        return self.w8
 
 
 def quant_w_int4(w: torch.Tensor, group: int = GROUP):
@@ -112,26 +120,28 @@ def _scale_mode(scale_fp16: bool, bf16_arith: bool) -> int:
 
 
 def quant_act_int4(x: torch.Tensor, a: Optional[torch.Tensor] = None,
-                   had: Optional[Hadamard] = None, scale_fp16: bool = False, bf16_arith: bool = False):
-    """bf16 or fp32 [M,K] -> (codes int8 [M,K], sx fp32 [M])."""
+                   had: Optional[Hadamard] = None, scale_fp16: bool = False, bf16_arith: bool = False,
+                   e4m3: bool = False):
+    """bf16 or fp32 [M,K] -> (codes int8 [M,K], sx fp32 [M]); e4m3: the codes as E4M3 bytes (uint8),
+    the operand of gemm_w4a4_int4_e4m3."""
     lib = _prep(x)
     if x.dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("quant_act_int4 expects bf16 or fp32 activations")
     if x.stride(-1) != 1:
         x = x.contiguous()
     M, K = x.shape
-    codes = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    codes = torch.empty(M, K, dtype=torch.uint8 if e4m3 else torch.int8, device=x.device)
     sx = torch.empty(M, dtype=torch.float32, device=x.device)
     desc = had.desc() if had is not None else None
     fn, what = ((lib.dq_quant_act_int4, "dq_quant_act_int4") if x.dtype == torch.bfloat16
                 else (lib.dq_quant_act_int4_f32, "dq_quant_act_int4_f32"))
     _lib.check(fn(_ptr(x), x.stride(0) if M > 1 else K, _ptr(a), desc, M, K, _ptr(codes), _ptr(sx),
-                  _scale_mode(scale_fp16, bf16_arith), _stream(x.device)), what)
+                  _scale_mode(scale_fp16, bf16_arith) | (_lib.CODES_E4M3 if e4m3 else 0), _stream(x.device)), what)
     return codes, sx
 
 
 def quant_act_int4_gated(gate: torch.Tensor, up: torch.Tensor, a: Optional[torch.Tensor] = None,
-                         had: Optional[Hadamard] = None, scale_fp16: bool = False):
+                         had: Optional[Hadamard] = None, scale_fp16: bool = False, e4m3: bool = False):
     """codes/scales of bf16(bf16(SiLU(gate)) * up); gate and up are bf16 [M,K] views with the same
     row stride (typically the two halves of a fused gate+up projection output)."""
     lib = _prep(gate)
@@ -140,17 +150,18 @@ def quant_act_int4_gated(gate: torch.Tensor, up: torch.Tensor, a: Optional[torch
     if gate.shape != up.shape or gate.stride() != up.stride() or gate.stride(-1) != 1:
         raise ValueError("gate and up must have the same shape and strides (unit inner stride)")
     M, K = gate.shape
-    codes = torch.empty(M, K, dtype=torch.int8, device=gate.device)
+    codes = torch.empty(M, K, dtype=torch.uint8 if e4m3 else torch.int8, device=gate.device)
     sx = torch.empty(M, dtype=torch.float32, device=gate.device)
     desc = had.desc() if had is not None else None
     _lib.check(lib.dq_quant_act_int4_gated(_ptr(gate), _ptr(up), gate.stride(0) if M > 1 else K, _ptr(a),
-                                           desc, M, K, _ptr(codes), _ptr(sx), int(scale_fp16),
+                                           desc, M, K, _ptr(codes), _ptr(sx),
+                                           int(scale_fp16) | (_lib.CODES_E4M3 if e4m3 else 0),
                                            _stream(gate.device)), "dq_quant_act_int4_gated")
     return codes, sx
 
 
 def quant_act_int4_rmsnorm(x: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float,
-                           a: Optional[torch.Tensor] = None, scale_fp16: bool = False):
+                           a: Optional[torch.Tensor] = None, scale_fp16: bool = False, e4m3: bool = False):
     """RMSNorm (bf16 result, optional bf16 weight) + column scale + per-token int4 quantiser in
     one pass: bf16 [M,K] -> (codes int8 [M,K], sx fp32 [M])."""
     lib = _prep(x)
@@ -159,11 +170,11 @@ def quant_act_int4_rmsnorm(x: torch.Tensor, norm_weight: Optional[torch.Tensor],
     if norm_weight is not None and (norm_weight.dtype != torch.bfloat16 or norm_weight.numel() != x.shape[1]):
         raise ValueError("norm_weight must be bf16 with one entry per input channel")
     M, K = x.shape
-    codes = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    codes = torch.empty(M, K, dtype=torch.uint8 if e4m3 else torch.int8, device=x.device)
     sx = torch.empty(M, dtype=torch.float32, device=x.device)
     _lib.check(lib.dq_quant_act_int4_rmsnorm(_ptr(x), x.stride(0) if M > 1 else K, _ptr(norm_weight),
                                              float(eps), _ptr(a), M, K, _ptr(codes), _ptr(sx),
-                                             int(scale_fp16), _stream(x.device)),
+                                             int(scale_fp16) | (_lib.CODES_E4M3 if e4m3 else 0), _stream(x.device)),
                "dq_quant_act_int4_rmsnorm")
     return codes, sx
 
@@ -382,8 +393,13 @@ def gemm_w4a4_int4_acc(codes: torch.Tensor, pw: PackedInt4Weight) -> torch.Tenso
     return acc
 
 
-def linear_scratch_bytes(M: int, N: int, K: int) -> int:
-    return int(_lib.load().dq_linear_w4a4_int4_scratch_bytes(M, N, K))
+def linear_scratch_bytes(M: int, N: int, K: int, prefill: bool = True) -> int:
+    """Scratch of linear_w4a4_int4; prefill=True includes the room that lets batches of 1024 tokens
+    and more take the FP8-path GEMM (N * K bytes more for those, nothing for smaller batches)."""
+    lib = _lib.load()
+    if prefill:
+        return int(lib.dq_linear_w4a4_int4_prefill_scratch_bytes(M, N, K))
+    return int(lib.dq_linear_w4a4_int4_scratch_bytes(M, N, K))
 
 
 def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[Hadamard],
@@ -398,9 +414,10 @@ def linear_w4a4_int4(x: torch.Tensor, a: Optional[torch.Tensor], had: Optional[H
     if x.stride(-1) != 1:
         x = x.contiguous()
     M, K = x.shape
-    need = linear_scratch_bytes(M, pw.N, K)
-    if scratch is None or scratch.numel() < need:
-        scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+    # a caller's scratch is used as it is when it covers the plain path; the C side takes the
+    # FP8-path GEMM for prefill batches only if the scratch also has room for the weight's byte form
+    if scratch is None or scratch.numel() < linear_scratch_bytes(M, pw.N, K, prefill=False):
+        scratch = torch.empty(max(linear_scratch_bytes(M, pw.N, K), 256), dtype=torch.uint8, device=x.device)
     if out is None:
         out = torch.empty(M, pw.N, dtype=out_dtype, device=x.device)
     ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32

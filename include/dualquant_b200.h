@@ -312,7 +312,10 @@ DQ_API int dq_gemm_w4a4_int4_residual(const int8_t* codes, const float* sx, cons
  * per call into scratch), dq_codes_to_e4m3 converts the quantiser's int8 codes [M,K] (row stride
  * ld) to x8 [M,K].  sw_t, r, sx, y, residual as in dq_gemm_w4a4_int4_residual (residual may be
  * NULL).  Any M >= 1 is accepted; the kernel works on tiles of 256 tokens.
+ * The quantiser entries write their codes as E4M3 bytes directly when DQ_CODES_E4M3 is or-ed into
+ * their scale_fp16 argument (codes then has to be read as uint8).
  */
+#define DQ_CODES_E4M3 0x100
 DQ_API int dq_expand_w_int4_e4m3(const uint8_t* w_packed, int N, int K, int G, uint8_t* w8, void* stream);
 DQ_API int dq_codes_to_e4m3(const int8_t* codes, int64_t ld, int M, int K, uint8_t* x8, void* stream);
 DQ_API int dq_gemm_w4a4_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t,
@@ -383,8 +386,14 @@ DQ_API int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packed, i
  * One call for a whole PermLinear.forward (activations/perm_linear.py:136-141) on the real
  * int4 path: quantise x (as dq_quant_act_int4) into caller scratch, then the GEMM.
  * scratch must hold dq_linear_w4a4_int4_scratch_bytes(M,N,K) bytes.
+ * Prefill batches (1024 tokens and more) run on the FP8-path GEMM (dq_gemm_w4a4_int4_e4m3, same
+ * bits, about twice as fast) when the scratch also has room for the byte form of the weight:
+ * dq_linear_w4a4_int4_prefill_scratch_bytes(M,N,K) (equal to the plain figure for smaller M).
+ * The weight is expanded into the scratch on every call; callers that can keep N*K bytes per
+ * weight call dq_expand_w_int4_e4m3 once and dq_gemm_w4a4_int4_e4m3 directly.
  */
 DQ_API size_t dq_linear_w4a4_int4_scratch_bytes(int M, int N, int K);
+DQ_API size_t dq_linear_w4a4_int4_prefill_scratch_bytes(int M, int N, int K);
 DQ_API int dq_linear_w4a4_int4(const void* x_bf16, int64_t ldx, const float* a,
                         const dq_hadamard_desc* had, const uint8_t* w_packed, const void* sw_t,
                         const float* r, int M, int N, int K, int G, void* y, int y_dtype,
