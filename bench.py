@@ -720,7 +720,8 @@ PREFILL_SHAPES = (
 
 def run_prefill_suite(args, emit=True):
     """Prefill-shaped linears (tensor-core bound): TOPS = 2*M*N*K / time of the GEMM launch and of
-    quantiser + GEMM, against the dense int8 peak (nominal 4500 TOPS; 2x the measured bf16 peak)."""
+    quantiser + GEMM, against the dense 8-bit peak (nominal 4500 TOPS; 2x the measured bf16 peak;
+    the MMA-only ceiling measured by the probe kernel)."""
     from dualquant_b200 import _lib, ops
 
     dev = torch.device("cuda", 0)
@@ -738,12 +739,19 @@ def run_prefill_suite(args, emit=True):
         r, a = r.to(dev), (1.0 / c).to(dev)
         x = (torch.randn(M, K, generator=g, device=dev)).to(torch.bfloat16)
         qx, sx = ops.quant_act_int4(x, a, None, True)
-        y = torch.empty(M, N, dtype=torch.float32, device=dev)
+        x8, _ = ops.quant_act_int4(x, a, None, True, e4m3=True)
+        w8 = pw.bytes_e4m3()
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         scratch = torch.empty(ops.linear_scratch_bytes(M, N, K), dtype=torch.uint8, device=dev)
-        g_gemm = _capture(lambda: ops.gemm_w4a4_int4(qx, sx, pw, r, out=y), dev)
+        # gemm: the FP8-path kernel (E4M3 operands, the weight's byte form resident); gemm_i8: the
+        # kind::i8 kernel on the 4-bit artefact; linear: the one-call entry (quantiser + weight
+        # expansion into scratch + FP8-path GEMM from 1024 tokens on)
+        g_gemm = _capture(lambda: ops.gemm_w4a4_int4_e4m3(x8, sx, w8, pw, r, out=y), dev)
+        g_i8 = _capture(lambda: ops.gemm_w4a4_int4(qx, sx, pw, r, out=y), dev)
         g_full = _capture(lambda: ops.linear_w4a4_int4(x, a, None, pw, r, scale_fp16=True,
                                                        scratch=scratch, out=y), dev)
         ms_gemm = _time_loop(g_gemm.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
+        ms_i8 = _time_loop(g_i8.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
         ms_full = _time_loop(g_full.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
         # the A16W4 variant (bf16 activations x int4 weights, tcgen05 kind::f16) on the same operands
         yb = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
@@ -754,11 +762,13 @@ def run_prefill_suite(args, emit=True):
         ops_ = 2.0 * M * N * K
         rows.append({"shape": label, "M": M, "K": K, "N": N,
                      "a16w4_linear_us": round(ms_a16 * 1e3, 1), "a16w4_TFLOPS": round(ops_ / ms_a16 / 1e9, 1),
-
+                     "gemm_kernel": "gemm_w4a4_e4m3_kernel (tcgen05 kind::f8f6f4, E4M3 codes)",
                      "gemm_us": round(ms_gemm * 1e3, 1), "gemm_TOPS": round(ops_ / ms_gemm / 1e9, 1),
+                     "gemm_i8_us": round(ms_i8 * 1e3, 1), "gemm_i8_TOPS": round(ops_ / ms_i8 / 1e9, 1),
                      "linear_us": round(ms_full * 1e3, 1), "linear_TOPS": round(ops_ / ms_full / 1e9, 1),
                      "frac_int8_nominal": round(ops_ / ms_gemm / 1e9 / 4500.0, 4),
                      "frac_2x_measured_bf16": round(ops_ / ms_gemm / 1e9 / int8_measured, 4)})
+        del x8, w8, g_gemm, g_i8, g_full
         del pw, x, qx, sx, y, scratch
     _lib.device_status(0)
     # "reference on this box": what the reference's PermLinear ends in - a bf16 F.linear (cuBLAS) on
@@ -775,12 +785,16 @@ def run_prefill_suite(args, emit=True):
         row["bf16_matmul_TFLOPS"] = round(2.0 * M * N * K / ms_bf16 / 1e9, 1)
         del xb, wb, yb, g_bf16
     mma = _mma_peaks(args)
+    if mma is not None and mma.get("e4m3_TFLOPS"):
+        for row in rows:
+            row["frac_e4m3_mma_only_measured"] = round(row["gemm_TOPS"] / mma["e4m3_TFLOPS"], 4)
     if mma is not None and mma.get("int8_TOPS"):
         for row in rows:
-            row["frac_int8_mma_only_measured"] = round(row["gemm_TOPS"] / mma["int8_TOPS"], 4)
+            row["gemm_i8_frac_int8_mma_only_measured"] = round(row["gemm_i8_TOPS"] / mma["int8_TOPS"], 4)
     rec = {"suite": "prefill", "unit": "TOPS (2*M*N*K/s)",
            "peaks": {"int8_nominal": 4500.0, "int8_2x_bf16_" + kind: int8_measured,
-                     "int8_mma_only_measured": None if mma is None else mma.get("int8_TOPS")},
+                     "int8_mma_only_measured": None if mma is None else mma.get("int8_TOPS"),
+                     "e4m3_mma_only_measured": None if mma is None else mma.get("e4m3_TFLOPS")},
            "steps": args.steps, "rows": rows}
     if emit:
         print(json.dumps(rec), flush=True)
@@ -811,8 +825,9 @@ def run_mlp_suite(args, emit=True):
     had = ops.Hadamard(_lib.HAD_FULL, kk, 0, quarot.full_hadamard_scale(I), hk.to(dev))
     x = torch.randn(M, H, generator=g, device=dev).to(torch.bfloat16)
     gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=dev)
-    y = torch.empty(M, H, dtype=torch.float32, device=dev)
+    y = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     s1 = torch.empty(ops.linear_scratch_bytes(M, 2 * I, H), dtype=torch.uint8, device=dev)
+    w8_down = w_down.bytes_e4m3()  # the down projection runs on the FP8-path GEMM, byte form resident
     state = {}
 
     def st_gate_up():
@@ -822,13 +837,13 @@ def run_mlp_suite(args, emit=True):
         state["h"] = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
 
     def st_quant():
-        state["q"] = ops.quant_act_int4(state["h"], a_dn, had, True)
+        state["q"] = ops.quant_act_int4(state["h"], a_dn, had, True, e4m3=True)
 
     def st_down():
-        ops.gemm_w4a4_int4(state["q"][0], state["q"][1], w_down, r_dn, out=y)
+        ops.gemm_w4a4_int4_e4m3(state["q"][0], state["q"][1], w8_down, w_down, r_dn, out=y)
 
     def st_fused_quant():
-        state["q"] = ops.quant_act_int4_gated(gu[:, :I], gu[:, I:], a_dn, had, True)
+        state["q"] = ops.quant_act_int4_gated(gu[:, :I], gu[:, I:], a_dn, had, True, e4m3=True)
 
     def whole():
         st_gate_up(); st_act(); st_quant(); st_down()
@@ -1297,7 +1312,7 @@ _MMA_PEAKS = {}
 
 
 def _mma_peaks(args):
-    """Measured once per process: {"int8_TOPS", "mxfp4_TFLOPS", "nvfp4_TFLOPS"} or None."""
+    """Measured once per process: {"int8_TOPS", "e4m3_TFLOPS", "mxfp4_TFLOPS", "nvfp4_TFLOPS"} or None."""
     if "v" not in _MMA_PEAKS:
         try:
             _MMA_PEAKS["v"] = run_peak_suite(args, emit=False)
@@ -1319,7 +1334,7 @@ def run_peak_suite(args, emit=True):
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
         rec = {"suite": "peaks_mma_only"}
-        for key, kind in (("int8_TOPS", 0), ("mxfp4_TFLOPS", 1), ("nvfp4_TFLOPS", 2)):
+        for key, kind in (("int8_TOPS", 0), ("e4m3_TFLOPS", 3), ("mxfp4_TFLOPS", 1), ("nvfp4_TFLOPS", 2)):
             best = 0.0
             for _ in range(3):
                 best = max(best, ops.mma_peak(kind, iters=4096))
