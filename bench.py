@@ -541,7 +541,9 @@ def run_extras(args, world, rank, local_rank, dev):
 
 def run_case(args):
     """One (linear, M) pair alone, a handful of launches: the small case profilers capture.
-    --case NAME:M[:TN:SPLIT], e.g. gate_up:16 ; --iters launches after 3 warm-up launches."""
+    --case NAME:M[:TN:SPLIT], e.g. gate_up:16 ; --iters launches after 3 warm-up launches.
+    Other forms: e4m3:NAME:M, a16w4:NAME:M, linear:NAME:M, fp4:FMT:NAME:M, quant:M:K, quant_had:M:K,
+    quant_fp4:FMT:M:K."""
     from dualquant_b200 import _lib, ops
 
     parts = args.case.split(":")
@@ -629,6 +631,36 @@ def run_case(args):
         print(json.dumps({"case": args.case, "iters": args.iters, "us_per_launch": round(ms * 1e3, 2),
                           "TFLOPS": round(2.0 * M * N * K / ms / 1e9, 1), "algorithmic_bytes": nbytes,
                           "GBps": round(nbytes / ms / 1e6, 1)}), flush=True)
+        return
+    if parts[0] == "e4m3":  # e4m3:NAME:M - the FP8-path int4 GEMM alone (E4M3 codes, bf16 out)
+        name, M = parts[1], int(parts[2])
+        K, N = {n: (k, nn) for n, k, nn in synthetic.LLAMA31_8B_LINEARS}[name]
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        g = torch.Generator(device=dev).manual_seed(0)
+        w = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        cw, sw = ops.quant_w_int4(w)
+        pw = ops.pack_w_int4(cw, sw)
+        del w, cw, sw
+        r, c = synthetic.make_scales(N, K, 0)
+        x8, sx = ops.quant_act_int4(synthetic.make_x(M, K, 0).to(dev), (1.0 / c).to(dev), None, True, e4m3=True)
+        w8, rr = pw.bytes_e4m3(), r.to(dev)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            ops.gemm_w4a4_int4_e4m3(x8, sx, w8, pw, rr, out=y)
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            ops.gemm_w4a4_int4_e4m3(x8, sx, w8, pw, rr, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        _lib.device_status(0)
+        ms = e0.elapsed_time(e1) / args.iters
+        print(json.dumps({"case": args.case, "iters": args.iters, "us_per_launch": round(ms * 1e3, 2),
+                          "TOPS": round(2.0 * M * N * K / ms / 1e9, 1),
+                          "operand_bytes": N * K + M * K + 2 * M * N}), flush=True)
         return
     if parts[0] in ("a16w4", "linear"):  # a16w4:NAME:M / linear:NAME:M - one whole linear alone
         name, M = parts[1], int(parts[2])
@@ -1325,7 +1357,8 @@ def _mma_peaks(args):
 def run_peak_suite(args, emit=True):
     """tcgen05.mma issue loops on operands that never leave shared / tensor memory: the rate the
     tensor pipe sustains with nothing else going on, for kind::i8 (128x256x32 per instruction)
-    and kind::mxf4nvf4.block_scale (128x256x64, E8M0 block 32 and E4M3 block 16)."""
+    and kind::mxf4nvf4.block_scale (128x256x64, E8M0 block 32 and E4M3 block 16); and the E4M3 loop
+    once more with its operands refilled from L2, the ceiling of a K loop that has to feed itself."""
     from dualquant_b200 import _lib, ops
 
     if "v" in _MMA_PEAKS and _MMA_PEAKS["v"] is not None:
@@ -1334,14 +1367,16 @@ def run_peak_suite(args, emit=True):
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
         rec = {"suite": "peaks_mma_only"}
-        for key, kind in (("int8_TOPS", 0), ("e4m3_TFLOPS", 3), ("mxfp4_TFLOPS", 1), ("nvfp4_TFLOPS", 2)):
+        for key, kind in (("int8_TOPS", 0), ("e4m3_TFLOPS", 3), ("e4m3_refill_TFLOPS", 4), ("mxfp4_TFLOPS", 1),
+                          ("nvfp4_TFLOPS", 2)):
             best = 0.0
             for _ in range(3):
                 best = max(best, ops.mma_peak(kind, iters=4096))
             rec[key] = round(best, 1)
         rec["how"] = ("one CTA per SM, one thread issuing back-to-back tcgen05.mma (UMMA 128x256, K = 32 bytes "
-                      "per instruction for int8, 64 elements for FP4) on shared-memory operands that are never "
-                      "reloaded; CUDA events; best of 3")
+                      "per instruction for int8 / E4M3, 64 elements for FP4) on shared-memory operands that are "
+                      "never reloaded; e4m3_refill: the same loop with a fresh 16 KB + 32 KB operand pair copied "
+                      "in from L2 for every four instructions (three-stage ring); CUDA events; best of 3")
         _lib.device_status(0)
         _MMA_PEAKS["v"] = rec
     if emit:

@@ -93,7 +93,9 @@ DQ_API int dq_set_tuning(const char* name, int value);
 
 /* Tensor-core ceiling probe: launches, on every SM, a loop of `iters` x 4 tcgen05.mma instructions
  * (UMMA 128 x 256, 32 bytes of K each) on operands resident in shared / tensor memory; kind 0 =
- * kind::i8, 1 = kind::mxf4nvf4 with E8M0 block-32 scales, 2 = with E4M3 block-16 scales.  *ops_out
+ * kind::i8, 1 = kind::mxf4nvf4 with E8M0 block-32 scales, 2 = with E4M3 block-16 scales, 3 =
+ * kind::f8f6f4 on E4M3 operands, 4 = the same with the operands re-fetched from L2 by bulk copies for
+ * every four instructions (the K loop of the prefill GEMM without an epilogue).  *ops_out
  * (host, may be null) receives the arithmetic operations the launch performs (2 per multiply-add);
  * the caller times the launch with events.  Measurement helper in the spirit of the reference's
  * roofline estimate (ablation/real_int4_kernel/verification/ceiling_analysis.py:55-63), which
