@@ -522,13 +522,24 @@ __device__ __forceinline__ void wht_segment_warp(float* seg, int lane) {
 
 // The K x K +-1 matrix of the "full" transform, in constant memory so that an FMA takes its
 // coefficient as an immediate constant-bank operand (one instruction per term instead of a
-// shared-memory load plus an FMA).  Refreshed by the host when a call brings a different matrix.
-__constant__ float c_had_mat[32 * 32];
+// shared-memory load plus an FMA).  Every entry is stored twice, (h, h): the matrix stage works on
+// two columns at a time with packed fp32 FMAs, each half of which rounds like the scalar fmaf.
+// Refreshed by the host when a call brings a different matrix.
+__constant__ float2 c_had_mat2[32 * 32];
+__device__ float2 g_had_stage[32 * 32];  // the table is assembled here, then copied to the constant bank
+
+__global__ void __launch_bounds__(1024) had_table_kernel(const float* __restrict__ had_mat, int S) {
+  const int t = threadIdx.x, i = t >> 5, j = t & 31;
+  const float h = (i < S && j < S) ? had_mat[i * S + j] : 0.f;  // rows and columns padded to 32 with zeros
+  g_had_stage[t] = make_float2(h, h);
+}
 
 // THREADS = 512: one CTA per SM, the shortest time per row (decode batches, one row per SM at most).
 // THREADS = 256: three CTAs per SM; with many rows one row's load, barrier and store phases overlap
-// another row's arithmetic.
-template <int R, typename XT, int THREADS>
+// another row's arithmetic (two CTAs per SM with more registers each measured 30 % slower).
+// HS: order of the +-1 factor when it is one of the common ones (28: 14336 = 28 * 512 and
+// 28672 = 28 * 1024), so that the matrix stage has no padded terms; 0 = any order up to 32.
+template <int R, typename XT, int THREADS, int HS = 0>
 __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 3 : 1)
 act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_t ldx,
                           const float* __restrict__ a, int K,
@@ -570,27 +581,37 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
   }
 
   float amax = 0.f;
+  if (matrix) {
+    // two adjacent columns per thread (P is even): packed loads, packed FMAs
+    constexpr int HN = (HS > 0) ? HS : 32;  // factor order known at compile time, or padded to 32
+    for (int c = 2 * threadIdx.x; c < P; c += 2 * THREADS) {
+      float2 v[HN];
+#pragma unroll
+      for (int j = 0; j < HN; ++j) {
+        v[j] = (j < S) ? *reinterpret_cast<const float2*>(row + j * P + c) : make_float2(0.f, 0.f);
+        v[j].x = __fmul_rn(v[j].x, had_scale);
+        v[j].y = __fmul_rn(v[j].y, had_scale);
+      }
+      // fully unrolled so that every coefficient is a constant-bank operand of its FMA and the
+      // independent accumulation chains can be interleaved
+#pragma unroll
+      for (int i = 0; i < HN; ++i) {
+        if (i < S) {
+          float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < HN; ++j)  // H entries are +-1 (0 in the padding): same as acc + H*v, j ascending
+            acc = __ffma2_rn(c_had_mat2[i * 32 + j], v[j], acc);
+          *reinterpret_cast<float2*>(row + i * P + c) = acc;
+          amax = fmaxf(amax, fmaxf(fabsf(acc.x), fabsf(acc.y)));
+        }
+      }
+    }
+  } else {
   for (int c = threadIdx.x; c < P; c += THREADS) {
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = (j < S) ? row[j * P + c] : 0.f;
-    if (matrix) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], had_scale);
-      // fully unrolled so that every coefficient is a constant-bank immediate of its FMA and
-      // the S independent accumulation chains can be interleaved
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (i < S) {
-          float acc = 0.f;
-#pragma unroll
-          for (int j = 0; j < 32; ++j)  // rows of c_had_mat are padded to 32 with zeros
-            acc = fmaf(c_had_mat[i * 32 + j], v[j], acc);  // H entries are +-1: same as acc + H*v
-          row[i * P + c] = acc;
-          amax = fmaxf(amax, fabsf(acc));
-        }
-      }
-    } else {
+    {
 #pragma unroll
       for (int hb = 0; hb < 5; ++hb) {
         constexpr int kOne = 1;
@@ -616,6 +637,7 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
       }
     }
   }
+  }
   float s = 1.f;
   if (mode != MODE_RAW) {
     amax = block_max(amax, red, THREADS / 32);
@@ -634,7 +656,7 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
   }
 }
 
-// Copies a device-resident S x S matrix into c_had_mat (rows padded to 32) when it is not the
+// Copies a device-resident S x S matrix into c_had_mat2 (rows padded to 32) when it is not the
 // one already there.  The matrix behind a given pointer is assumed immutable (it is the constant
 // Hadamard factor of a layer); the copy is a stream-ordered device-to-device memcpy.
 static int upload_had_matrix(const float* had_mat, int S, cudaStream_t stream) {
@@ -656,10 +678,12 @@ static int upload_had_matrix(const float* had_mat, int S, cudaStream_t stream) {
   if (capturing) seen_capture[dev] = true;
   if (!seen_capture[dev] && cached[dev] == had_mat && cached_s[dev] == S) return DQ_OK;
   void* sym = nullptr;
-  DQ_CHECK_CUDA(cudaGetSymbolAddress(&sym, c_had_mat));
-  DQ_CHECK_CUDA(cudaMemsetAsync(sym, 0, sizeof(float) * 32 * 32, stream));
-  DQ_CHECK_CUDA(cudaMemcpy2DAsync(sym, 32 * sizeof(float), had_mat, S * sizeof(float), S * sizeof(float), S,
-                                  cudaMemcpyDeviceToDevice, stream));
+  void* stage = nullptr;
+  DQ_CHECK_CUDA(cudaGetSymbolAddress(&sym, c_had_mat2));
+  DQ_CHECK_CUDA(cudaGetSymbolAddress(&stage, g_had_stage));
+  had_table_kernel<<<1, 1024, 0, stream>>>(had_mat, S);
+  DQ_CHECK_CUDA(cudaGetLastError());
+  DQ_CHECK_CUDA(cudaMemcpyAsync(sym, stage, sizeof(float2) * 32 * 32, cudaMemcpyDeviceToDevice, stream));
   // a captured copy has not run yet: whatever is cached no longer describes the table
   cached[dev] = capturing ? nullptr : had_mat;
   cached_s[dev] = capturing ? 0 : S;
@@ -721,6 +745,15 @@ int init_act_quant_kernels() {
   DQ_HAD_ATTR(1, float) DQ_HAD_ATTR(2, float) DQ_HAD_ATTR(4, float)
   DQ_HAD_ATTR(8, float) DQ_HAD_ATTR(16, float) DQ_HAD_ATTR(32, float)
 #undef DQ_HAD_ATTR
+#define DQ_HAD_ATTR28(R, T)                                                                   \
+  if (e == cudaSuccess)                                                                       \
+    e = cudaFuncSetAttribute(act_quant_had_fast_kernel<R, T, 512, 28>,                          \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);        \
+  if (e == cudaSuccess)                                                                       \
+    e = cudaFuncSetAttribute(act_quant_had_fast_kernel<R, T, 256, 28>,                          \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
+  DQ_HAD_ATTR28(16, __nv_bfloat16) DQ_HAD_ATTR28(32, __nv_bfloat16) DQ_HAD_ATTR28(16, float) DQ_HAD_ATTR28(32, float)
+#undef DQ_HAD_ATTR28
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(act_quant_had) failed: %s",
                      cudaGetErrorString(e));
@@ -794,15 +827,19 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
       // many rows: smaller CTAs, several per SM (the row must leave room for three of them)
       const DeviceState* dst = current_state();
       const bool small_cta = dst != nullptr && M > 2 * dst->sm_count && smem <= 72 * 1024;
-#define DQ_HAD_FAST(RR)                                                                          \
-  if (small_cta)                                                                                 \
-    DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT, 256>, dim3(M), dim3(256), smem, stream, x, up, \
-                             ldx, a, K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes,   \
-                             sx, out, mode, scale_fp16));                                                    \
-  else                                                                                           \
-    DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT, 512>, dim3(M), dim3(512), smem, stream, x, up, \
-                             ldx, a, K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes,   \
-                             sx, out, mode, scale_fp16))
+#define DQ_HAD_FAST_T(RR, TT, HH)                                                                      \
+  DQ_CHECK_CUDA(launch_pdl(act_quant_had_fast_kernel<RR, XT, TT, HH>, dim3(M), dim3(TT), smem, stream, x, up, \
+                           ldx, a, K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes, sx,   \
+                           out, mode, scale_fp16))
+#define DQ_HAD_FAST(RR)                                            \
+  if (plan.matrix && plan.S == 28 && (RR == 16 || RR == 32)) {     \
+    if (small_cta) DQ_HAD_FAST_T(RR, 256, 28);                     \
+    else DQ_HAD_FAST_T(RR, 512, 28);                               \
+  } else if (small_cta) {                                          \
+    DQ_HAD_FAST_T(RR, 256, 0);                                     \
+  } else {                                                         \
+    DQ_HAD_FAST_T(RR, 512, 0);                                     \
+  }
       switch (plan.R) {
         case 1: DQ_HAD_FAST(1); break;
         case 2: DQ_HAD_FAST(2); break;
@@ -812,6 +849,7 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
         default: DQ_HAD_FAST(32); break;
       }
 #undef DQ_HAD_FAST
+#undef DQ_HAD_FAST_T
       return DQ_OK;
     }
     DQ_CHECK_CUDA(launch_pdl(act_quant_had_kernel<kHadThreads, XT>, dim3(M), dim3(kHadThreads), smem,
