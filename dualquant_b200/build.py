@@ -28,6 +28,7 @@ SOURCES = [
     "gemm_a16w4.cu",
     "decoder_ops.cu",
     "gemm_w4a4_int4_f8.cu",
+    "gemm_fp4_persist.cu",
 ]
 
 NVCC_FLAGS = [

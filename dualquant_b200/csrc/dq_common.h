@@ -104,6 +104,11 @@ int init_gemv_fused_kernels();
 int init_mma_peak_kernels();
 int init_gemm_a16w4_kernels();
 int init_gemm_int4_f8_kernels();
+int init_gemm_fp4_persist_kernels();
+int launch_gemm_fp4_persist(const uint8_t* x_codes, const uint8_t* x_sf_atoms, const float* x_scale,
+                            const uint8_t* w_codes, const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
+                            int M, int N, int K, int nvfp4, void* y, int y_dtype, cudaStream_t stream,
+                            DeviceState* st);
 int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t, const float* r,
                           int M, int N, int K, void* y, int y_dtype, const void* residual, cudaStream_t stream,
                           DeviceState* st);

@@ -170,6 +170,8 @@ extern "C" int dq_init(int device) {
   if (rc != DQ_OK) return rc;
   rc = init_gemm_int4_f8_kernels();
   if (rc != DQ_OK) return rc;
+  rc = init_gemm_fp4_persist_kernels();
+  if (rc != DQ_OK) return rc;
   DQ_CHECK_CUDA(cudaDeviceSynchronize());
   st->ready = true;
   return DQ_OK;

@@ -17,16 +17,13 @@
 // 192 threads: warp 0 TMA producer, warp 1 TMEM allocation + UMMA issue, warps 2-5 epilogue.
 #include "dq_common.h"
 #include "dq_ptx.cuh"
+#include "gemm_fp4.cuh"
 
 #include <cuda_bf16.h>
 
 namespace dq {
 
-constexpr int kFBN = 128;      // weight rows per CTA
-constexpr int kFTN = 128;      // tokens per CTA
-constexpr int kFKStage = 256;  // k per stage (128 bytes of packed fp4 per row)
 constexpr int kFp4DecodeTokens = 32;  // library's choice of the 32-token tile: M up to this
-constexpr int kFTileBytes = 128 * 128;  // one operand tile of 128 rows
 constexpr int kFThreads = 256;  // producer, UMMA issuer, 4 epilogue warps, 2 scale-factor copiers
 
 // NT = token blocks of 128 per CTA; NT = 0 is the decode tile of 32 tokens.
@@ -62,47 +59,6 @@ struct FCfg {
 };
 
 enum { FSITE_TMA = 31, FSITE_MMA = 32, FSITE_EPI = 33, FSITE_SF = 34 };
-
-// Shared-memory descriptor of one scale-factor atom for tcgen05.cp: 32 rows x 16 bytes, no
-// swizzle, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t sf_atom_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(128 >> 4) << 32;  // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;         // descriptor version
-  return d;
-}
-
-__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-// Instruction descriptor, kind::mxf4nvf4: E2M1 operands (format code 1), both K-major.
-//   [4,6) B scale id  [7,10) A format  [10,13) B format  [17,23) N >> 3  [23] scale format
-//   (0 = E4M3, 1 = E8M0)  [24,29) M >> 4  [29,31) A scale id  [31] K size (0 = 64)
-__device__ __forceinline__ uint32_t umma_idesc_fp4(int m, int n, int e8m0, uint32_t sf_id) {
-  return (sf_id << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(e8m0) << 23) | (static_cast<uint32_t>(m >> 4) << 24) | (sf_id << 29);
-}
-
-template <int NVFP4>
-__device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                         uint32_t idesc, uint32_t sfa, uint32_t sfb,
-                                         uint32_t accumulate) {
-  if constexpr (NVFP4) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::
-            "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::
-            "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
-        : "memory");
-  }
-}
 
 template <int NVFP4, int NT>
 __global__ void __launch_bounds__(kFThreads, FCfg<NT>::kMinCtas)
@@ -472,7 +428,20 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   DQ_REQUIRE(token_tile == 0 || token_tile == 32 || token_tile == 128 || token_tile == 256, DQ_ERR_SHAPE,
              "token_tile must be 0 (library's choice), 32, 128 or 256, got %d", token_tile);
   const int total_st = K / kFKStage;
-  // The library's own choice: 32-token tiles for decode batches, else 128.  The 256-token tile is
+  // Prefill-size batches (library's choice of tile, output addressable by the copy engine): the
+  // persistent kernel, when its 256-token tiles fill whole rounds of one tile per SM (a last round
+  // with few tiles costs a full tile time; measured on B200: gate+up and qkv of the Qwen2.5-7B shapes
+  // at M = 4096 run 1.2-1.3x faster persistent, o and down - 448 tiles on 148 SMs - do not).
+  {
+    const int esz0 = (y_dtype == DQ_DTYPE_BF16) ? 2 : 4;
+    const int64_t tiles256 = static_cast<int64_t>((N + kFBN - 1) / kFBN) * ((M + 255) / 256);
+    const int64_t rounds = (tiles256 + st->sm_count - 1) / st->sm_count;
+    const bool fills = tiles256 * 100 >= rounds * st->sm_count * 85;
+    if (token_tile == 0 && M >= 512 && fills && (static_cast<size_t>(N) * esz0) % 16 == 0 && aligned(y, 16))
+      return launch_gemm_fp4_persist(x_codes, x_sf_atoms, x_scale, w_codes, w_sf_atoms, w_scale, r, M, N, K,
+                                     fmt == DQ_FP4_NVFP4 ? 1 : 0, y, y_dtype, static_cast<cudaStream_t>(stream), st);
+  }
+  // The library's own choice otherwise: 32-token tiles for decode batches, else 128.  The 256-token tile is
   // not chosen: measured on the Qwen2.5-7B-architecture linears at M = 4096 it is 3 % faster on the
   // longest K loop and 2-15 % slower elsewhere (one CTA and one UMMA-issuing thread per SM).
   const int tile_tok = token_tile ? token_tile : (M <= kFp4DecodeTokens ? 32 : kFTN);
