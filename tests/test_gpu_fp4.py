@@ -214,6 +214,30 @@ def test_fp4_gemm_token_tiles_agree(fmt, M, N, K):
     assert err < 1e-3, err
 
 
+# Shapes the library sends to the persistent prefill kernel (at least 512 tokens, 256-token tiles
+# that fill whole rounds of one tile per SM): one tile per CTA and several, a last token tile of 216
+# tokens (two scale-factor blocks) and one of 100 (a single block), rows past N.
+@pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
+@pytest.mark.parametrize("M,N,K,dtype", [(728, 6272, 512, torch.float32), (612, 6260, 768, torch.bfloat16),
+                                         (2048, 9472, 256, torch.bfloat16)])
+def test_fp4_persistent_kernel_equals_the_one_tile_kernel(fmt, M, N, K, dtype):
+    x = synthetic.make_x(M, K, M + 1)
+    w = synthetic.make_w(N, K, N + 2)
+    r, c = synthetic.make_scales(N, K, 3)
+    a = (1.0 / c).to(DEV)
+    pw = ops.pack_w_fp4(w.to(DEV), fmt)
+    codes, sf, rs = ops.quant_fp4(x.to(DEV), fmt, a, None)
+    sfa = ops.fp4_sf_to_atoms(sf, K, fmt)
+    want = ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r.to(DEV), out_dtype=dtype, token_tile=128)
+    got = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
+    ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r.to(DEV), out=got)  # library's choice: the persistent kernel
+    _lib.device_status(0)
+    assert torch.equal(got, want)
+    ref = _fp4_reference(x, a.cpu(), w, r, fmt)
+    err = ((got.double().cpu() - ref).abs().max() / ref.abs().max()).item()
+    assert err < (1e-3 if dtype == torch.float32 else 1e-2), err
+
+
 @pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
 @pytest.mark.parametrize("M,N,K,dtype", [(130, 130, 768, torch.float32), (257, 204, 512, torch.bfloat16),
                                          (40, 136, 768, torch.bfloat16), (129, 200, 512, torch.bfloat16),
