@@ -1073,7 +1073,10 @@ def run_fp4_suite(args, emit=True):
                 x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
                 codes, sf, rs = ops.quant_fp4(x, fmt, a, None)
                 sfa = ops.fp4_sf_to_atoms(sf, K, fmt)
-                y = torch.empty(M, N, dtype=torch.float32, device=dev)
+                # prefill rows write bf16 (the model's activation type; at M = 4096 an fp32 gate+up output is
+                # 620 MB, a third of the GEMM's time in HBM writes alone), decode rows fp32
+                ydt = torch.bfloat16 if M > 128 else torch.float32
+                y = torch.empty(M, N, dtype=ydt, device=dev)
                 # Decode batches stream the weights: the graph walks enough copies of the packed
                 # weight (> 2x the 126 MB L2 in total) that every launch reads them from HBM.
                 # At M = 4096 operands + output exceed L2 on their own or the GEMM is tensor-bound.
@@ -1096,8 +1099,9 @@ def run_fp4_suite(args, emit=True):
                 ms_full = _time_loop(g_full.replay, args.steps, args.warmup, dev, lambda: None) / args.steps / n_copies
                 del pws, g_gemm, g_full
                 flops = 2.0 * M * N * K
-                nbytes = N * K // 2 + N * K // blk + 2 * N + 2 * K + 2 * M * K + 4 * M * N
+                nbytes = N * K // 2 + N * K // blk + 2 * N + 2 * K + 2 * M * K + y.element_size() * M * N
                 rows.append({"fmt": fmt_name, "linear": name, "M": M, "K": K, "N": N, "weight_copies": n_copies,
+                             "y_dtype": "bf16" if ydt == torch.bfloat16 else "fp32",
                              "gemm_us": round(ms_gemm * 1e3, 1), "linear_us": round(ms_full * 1e3, 1),
                              "gemm_TFLOPS": round(flops / ms_gemm / 1e9, 1),
                              "gemm_GBps": round(nbytes / ms_gemm / 1e6, 1),
