@@ -773,7 +773,9 @@ def run_prefill_suite(args, emit=True):
         qx, sx = ops.quant_act_int4(x, a, None, True)
         x8, _ = ops.quant_act_int4(x, a, None, True, e4m3=True)
         w8 = pw.bytes_e4m3()
-        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        # configuration 0 names an fp32 output; the other rows write bf16, the model's activation type
+        ydt = torch.float32 if label.startswith("config0") else torch.bfloat16
+        y = torch.empty(M, N, dtype=ydt, device=dev)
         scratch = torch.empty(ops.linear_scratch_bytes(M, N, K), dtype=torch.uint8, device=dev)
         # gemm: the FP8-path kernel (E4M3 operands, the weight's byte form resident); gemm_i8: the
         # kind::i8 kernel on the 4-bit artefact; linear: the one-call entry (quantiser + weight
@@ -792,7 +794,7 @@ def run_prefill_suite(args, emit=True):
         ms_a16 = _time_loop(g_a16.replay, args.steps, args.warmup, dev, lambda: None) / args.steps
         del g_a16, yb, s16
         ops_ = 2.0 * M * N * K
-        rows.append({"shape": label, "M": M, "K": K, "N": N,
+        rows.append({"shape": label, "M": M, "K": K, "N": N, "y_dtype": "fp32" if ydt == torch.float32 else "bf16",
                      "a16w4_linear_us": round(ms_a16 * 1e3, 1), "a16w4_TFLOPS": round(ops_ / ms_a16 / 1e9, 1),
                      "gemm_kernel": "gemm_w4a4_e4m3_kernel (tcgen05 kind::f8f6f4, E4M3 codes)",
                      "gemm_us": round(ms_gemm * 1e3, 1), "gemm_TOPS": round(ops_ / ms_gemm / 1e9, 1),

@@ -71,7 +71,7 @@ constexpr int kOffOut = kStages * kStageBytes;   // bf16 output tile [256 tokens
 constexpr int kOutBytes = kTN * kBN * 2;
 constexpr int kOffSx = kOffOut + kOutBytes;      // token scales of the tile, double-buffered
 constexpr int kOffBar = kOffSx + 2 * kTN * 4;
-constexpr int kNumBars = 2 * kStages + 7;
+constexpr int kNumBars = 2 * kStages + 9;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
 constexpr uint32_t kTmemCols = 512;
 static_assert(kSmemBytes + 1024 <= 227 * 1024, "shared memory");
@@ -168,15 +168,20 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t* v) {
   else tmem_ld_x32(taddr, v);
 }
 
-template <int EW, int CH, int NB, bool REBAL>
+// OUT: how the output tile leaves - 0 direct stores (any shape, fp32 or bf16, optional residual),
+// 1 bf16 through shared memory and one tiled bulk store, 3 the same with the residual added, 2 fp32
+// through shared memory in two halves.  A template parameter: with all three epilogues in one kernel the K loop's
+// code ran 20-25 % slower.
+template <int EW, int CH, int NB, bool REBAL, int OUT>
 __global__ void __launch_bounds__(Shape<EW, CH, NB, REBAL>::kThreads, 1)
 gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                      const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_res, int bulk_out,
+                      const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_res,
                       const __half* __restrict__ sw_t, const float* __restrict__ r,
                       const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
                       const void* __restrict__ residual, int M, int N, int K, int row_tiles, int tok_tiles,
                       int tok_block, int* status) {
   using S = Shape<EW, CH, NB, REBAL>;
+  constexpr int bulk_out = (OUT == 3) ? 1 : OUT;
   constexpr int kEpiWarps = S::kEpiWarps, kProducerWarp = S::kProducerWarp, kIssuerWarp = S::kIssuerWarp;
   constexpr int kCPW = S::kCPW, kCH = S::kCH, kNB = S::kNB;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -191,8 +196,10 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   uint64_t* acc_empty = acc_full + 2;
   uint64_t* out_free = acc_empty + 2;   // the output tile may be overwritten and the token scales are in place
   uint64_t* out_ready = out_free + 1;   // the output tile is written
-  uint64_t* res_full = out_ready + 1;   // the residual tile has landed in the output buffer
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_full + 1);
+  uint64_t* res_full = out_ready + 1;   // the residual tile has landed in the output buffer (bf16 output);
+                                        // fp32 output: the first half's store has left the buffer
+  uint64_t* half_ready = res_full + 1;  // [2]: fp32 output, tokens 0-127 / 128-255 of the tile are written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(half_ready + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
@@ -219,6 +226,8 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     mbar_init(out_free, kEpiWarps);
     mbar_init(out_ready, kEpiWarps);
     mbar_init(res_full, 1);
+    mbar_init(&half_ready[0], kEpiWarps / 2);
+    mbar_init(&half_ready[1], kEpiWarps / 2);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -230,7 +239,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
     if (bulk_out) tma_prefetch_desc(&tm_y);
-    if (bulk_out && residual != nullptr) tma_prefetch_desc(&tm_res);
+    if (OUT == 3) tma_prefetch_desc(&tm_res);
   }
   grid_dep_launch_dependents();
   tc_fence_before();
@@ -284,7 +293,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     bool ok = true;
     unsigned short* out_sm = reinterpret_cast<unsigned short*>(smem + kOffOut);
     float* sx_sm = reinterpret_cast<float*>(smem + kOffSx);
-    const bool bulk_res = bulk_out && residual != nullptr;
+    constexpr bool bulk_res = (OUT == 3);
     grid_dep_wait();  // the token scales come from the kernel before this one
     for (int it = 0; it < my_tiles && ok; ++it) {
       int row_tile, tok_tile;
@@ -311,7 +320,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
       if (!ok) break;
-      if (bulk_out) {
+      if constexpr (OUT == 1 || OUT == 3) {
         // Y tile -> shared memory as [token][row] bf16 (a warp's 32 rows of one token are 64
         // contiguous bytes), then one tiled bulk store; rows past N and tokens past M are clipped
         // by the copy.  With a residual, its tile was copied into the same buffer during the K loop.  Two-byte global stores from here would cost more than two groups' UMMAs.
@@ -353,7 +362,45 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           }
         }
         ok = __all_sync(0xffffffffu, stored ? 1 : 0) != 0;  // the warp leaves the loop together
-      } else if (n < N) {
+      } else if constexpr (OUT == 2) {
+        // fp32 output: the buffer holds half a tile, [128 tokens][128 rows] of fp32.  The four warps
+        // with tokens 0-127 stage and store first; the other four follow once that store has been
+        // read.  Each half is stored by a thread of its own team, which also waits for its copy
+        // before the buffer is reused.
+        static_assert(kCPW == 128 && kEpiWarps == 8, "one half of the tile per warp");
+        if (lane == 0 && (warp == 0 || warp == 4)) bulk_wait_group_read0();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(out_free);
+        if (!mbar_wait(out_free, it & 1, abort_flag, FSITE_OUT)) break;
+        if (h == 1 && !mbar_wait(res_full, it & 1, abort_flag, FSITE_OUT)) break;
+        const float rn = (r != nullptr && n < N) ? r[n] : 1.f;
+        const float4* sx4 = reinterpret_cast<const float4*>(sx_sm + (it & 1) * kTN + h * kCPW);
+        float* dst = reinterpret_cast<float*>(out_sm) + q * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < kCPW; j += 4) {
+          const float4 sv = sx4[j >> 2];
+          dst[(j + 0) * kBN] = run[j + 0] * (rn * sv.x);
+          dst[(j + 1) * kBN] = run[j + 1] * (rn * sv.y);
+          dst[(j + 2) * kBN] = run[j + 2] * (rn * sv.z);
+          dst[(j + 3) * kBN] = run[j + 3] * (rn * sv.w);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&half_ready[h]);
+        bool stored = true;
+        if (lane == 0 && (warp == 0 || warp == 4)) {
+          stored = mbar_wait(&half_ready[h], it & 1, abort_flag, FSITE_OUT);
+          if (stored) {
+            tma_store_2d(&tm_y, out_sm, row_tile * kBN, t0 + h * kCPW);
+            bulk_commit_group();
+            if (h == 0) {
+              bulk_wait_group_read0();
+              mbar_arrive(res_full);  // the second half may overwrite the buffer
+            }
+          }
+        }
+        ok = __all_sync(0xffffffffu, stored ? 1 : 0) != 0;
+      } else if (n < N) {  // OUT == 0
         const float rn = (r != nullptr) ? r[n] : 1.f;
         const int m0 = t0 + h * kCPW;
         const int cnt = (M - m0 < kCPW) ? (M - m0) : kCPW;
@@ -382,7 +429,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
     }
-    if (bulk_out && tid == 0) bulk_wait_group_read0();
+    if (bulk_out && lane == 0 && (warp == 0 || warp == 4)) bulk_wait_group_read0();
   } else {
     if constexpr (REBAL) setmaxnreg_dec<S::kAuxRegs>();
     if (warp == kProducerWarp) {
@@ -444,12 +491,19 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 // (0.46 us per group) sits at what the shared-memory port moves - 48 KB written by the copy engine
 // and 48 KB read by the tensor core per group.
 using KernelShape = Shape<8, 32, 2, true>;
-constexpr auto Kernel = gemm_w4a4_e4m3_kernel<8, 32, 2, true>;
+template <int OUT>
+constexpr auto Kernel = gemm_w4a4_e4m3_kernel<8, 32, 2, true, OUT>;
 
 }  // namespace f8
 
 int init_gemm_int4_f8_kernels() {
-  cudaError_t e = cudaFuncSetAttribute(f8::Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(f8::Kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(f8::Kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(f8::Kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(f8::Kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemm_w4a4_e4m3) failed: %s", cudaGetErrorString(e));
   return DQ_OK;
@@ -477,21 +531,34 @@ int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8,
   const __half* sw = static_cast<const __half*>(sw_t);
   const int yb = y_dtype == DQ_DTYPE_BF16 ? 1 : 0;
   // bf16 output without a residual leaves through a tiled bulk store (needs 16-byte aligned rows)
-  const int bulk_out = (yb && N % 8 == 0 && aligned(y, 16) && (residual == nullptr || aligned(residual, 16))) ? 1 : 0;
+  // bf16 output (optionally with a residual) and fp32 output without one leave through tiled bulk
+  // stores (16-byte aligned rows); anything else is stored directly
+  int bulk_out = 0;
+  if (yb && N % 8 == 0 && aligned(y, 16) && (residual == nullptr || aligned(residual, 16))) bulk_out = 1;
+  else if (!yb && residual == nullptr && N % 4 == 0 && aligned(y, 16)) bulk_out = 2;
   CUtensorMap tm_y, tm_res;
   memset(&tm_y, 0, sizeof(tm_y));
   memset(&tm_res, 0, sizeof(tm_res));
-  if (bulk_out) {
+  if (bulk_out == 1) {
     rc = make_tmap_2d_out(&tm_y, y, 2, static_cast<uint64_t>(N), static_cast<uint64_t>(M), f8::kBN, f8::kTN);
     if (rc != DQ_OK) return rc;
     if (residual != nullptr) {
       rc = make_tmap_2d_out(&tm_res, residual, 2, static_cast<uint64_t>(N), static_cast<uint64_t>(M), f8::kBN, f8::kTN);
       if (rc != DQ_OK) return rc;
     }
+  } else if (bulk_out == 2) {
+    rc = make_tmap_2d_out(&tm_y, y, 4, static_cast<uint64_t>(N), static_cast<uint64_t>(M), f8::kBN, f8::kTN / 2);
+    if (rc != DQ_OK) return rc;
   }
-  cudaError_t e = launch_pdl(f8::Kernel, dim3(grid), dim3(f8::KernelShape::kThreads), f8::kSmemBytes, stream, tm_w, tm_x,
-                             tm_y, tm_res, bulk_out, sw, r, sx, y, yb, residual, M, N, K, row_tiles, tok_tiles, tok_block,
-                             st->status_dev);
+  cudaError_t e;
+#define DQ_F8_LAUNCH(OUTV)                                                                                          \
+  e = launch_pdl(f8::Kernel<OUTV>, dim3(grid), dim3(f8::KernelShape::kThreads), f8::kSmemBytes, stream, tm_w, tm_x, \
+                 tm_y, tm_res, sw, r, sx, y, yb, residual, M, N, K, row_tiles, tok_tiles, tok_block, st->status_dev)
+  if (bulk_out == 1 && residual != nullptr) DQ_F8_LAUNCH(3);
+  else if (bulk_out == 1) DQ_F8_LAUNCH(1);
+  else if (bulk_out == 2) DQ_F8_LAUNCH(2);
+  else DQ_F8_LAUNCH(0);
+#undef DQ_F8_LAUNCH
   if (e != cudaSuccess) return set_error(DQ_ERR_CUDA, "gemm_w4a4_e4m3 launch failed: %s", cudaGetErrorString(e));
   return DQ_OK;
 }
