@@ -196,7 +196,9 @@ class Workload:
         self.y_all = torch.empty(y_elems, dtype=torch.float32, device=dev)
         off = 0
         self.x_chunk, self.y_chunk = {}, {}  # per M: (offset, elements) of its slice of x_all / y_all
+        self.x_off, self.y_off = {}, {}  # (M, K) / (M, linear): (offset, elements) in x_all / y_all
         for M, K in x_keys:
+            self.x_off[(M, K)] = (off, M * K)
             lo, n = self.x_chunk.get(M, (off, 0))
             self.x_chunk[M] = (lo, n + M * K)
             self.x_all_host[off:off + M * K].copy_(synthetic.make_x(M, K, seed).reshape(-1))
@@ -208,6 +210,7 @@ class Workload:
         for M in synthetic.DECODE_M:
             for lin in self.linears:
                 K, nl = lin["K"], lin["N"]
+                self.y_off[(M, lin["name"])] = (off, M * nl)
                 lo, n = self.y_chunk.get(M, (off, 0))
                 self.y_chunk[M] = (lo, n + M * nl)
                 self.y[(M, lin["name"])] = self.y_all[off:off + M * nl].view(M, nl)
@@ -225,6 +228,14 @@ class Workload:
             ops.linear_w4a4_int4(self.x[(M, lin["K"])], lin["a"], None, lin["w"][mi], lin["r"],
                                  scale_fp16=True, scratch=self.scratch[(M, lin["name"])],
                                  out=self.y[(M, lin["name"])])
+
+    def step_unit(self, mi, li):
+        """One (batch size, linear) pair."""
+        M = synthetic.DECODE_M[mi]
+        lin = self.linears[li]
+        self.ops.linear_w4a4_int4(self.x[(M, lin["K"])], lin["a"], None, lin["w"][mi], lin["r"],
+                                  scale_fp16=True, scratch=self.scratch[(M, lin["name"])],
+                                  out=self.y[(M, lin["name"])])
 
     def step(self):
         """Device-resident pass: quantiser + GEMM for all 24 (linear, M) pairs."""
@@ -245,37 +256,50 @@ class Workload:
                 codes, sx = self.q[(M, lin["name"])]
                 ops.gemm_w4a4_int4(codes, sx, lin["w"][mi], lin["r"], out=self.y[(M, lin["name"])])
 
-    def e2e_setup(self, run_m):
-        """run_m[mi]() launches the four linears of batch size DECODE_M[mi] on the current stream."""
-        self.run_m = run_m
+    def e2e_units(self):
+        """The step's (batch size, linear) pairs in end-to-end order: largest batch first and, inside
+        a batch, the linear with the largest output first, so that the downloads (the 42.8 MB of fp32
+        outputs are what bounds the step) start as early as possible and never pause."""
+        lins = sorted(range(len(self.linears)), key=lambda li: -self.linears[li]["N"])
+        return [(mi, li) for mi in reversed(range(len(synthetic.DECODE_M))) for li in lins]
+
+    def e2e_setup(self, run_unit):
+        """run_unit[(mi, li)]() launches one linear (quantiser + GEMM) on the current stream."""
+        self.run_unit = run_unit
+        self.units = self.e2e_units()
         self.s_in = torch.cuda.Stream(device=self.dev)
         self.s_out = torch.cuda.Stream(device=self.dev)
-        self.ev_in = [torch.cuda.Event() for _ in synthetic.DECODE_M]
-        self.ev_done = [torch.cuda.Event() for _ in synthetic.DECODE_M]
+        self.ev_in = {key: torch.cuda.Event() for key in self.x_off}
+        self.ev_done = {u: torch.cuda.Event() for u in self.units}
 
     def e2e_step(self):
-        """Host buffers in, host buffers out, every step: the activations of each batch size go
-        up from pinned host memory on a copy stream, its four linears run (through the C ABI) on
-        the compute stream as soon as they have landed, and its outputs go down to pinned host
-        memory on a second copy stream while the next batch size computes.  Largest batch first,
-        so that the largest download overlaps the rest of the step.  The step ends when the last
-        output byte is in host memory."""
+        """Host buffers in, host buffers out, every step: each activation matrix goes up from pinned
+        host memory on a copy stream, each linear runs (through the C ABI) on the compute stream as
+        soon as its input has landed, and its output goes down to pinned host memory on a second
+        copy stream while the following linears compute.  The step ends when the last output byte
+        is in host memory."""
         cur = torch.cuda.current_stream(self.dev)
         self.s_in.wait_stream(cur)   # not before the previous step has ended
         self.s_out.wait_stream(cur)
-        order = list(range(len(synthetic.DECODE_M)))[::-1]
         with torch.cuda.stream(self.s_in):
-            for mi in order:
-                lo, n = self.x_chunk[synthetic.DECODE_M[mi]]
+            seen = set()
+            for mi, li in self.units:
+                key = (synthetic.DECODE_M[mi], self.linears[li]["K"])
+                if key in seen:
+                    continue
+                seen.add(key)
+                lo, n = self.x_off[key]
                 self.x_all[lo:lo + n].copy_(self.x_all_host[lo:lo + n], non_blocking=True)
-                self.ev_in[mi].record(self.s_in)
-        for mi in order:
-            cur.wait_event(self.ev_in[mi])
-            self.run_m[mi]()
-            self.ev_done[mi].record(cur)
+                self.ev_in[key].record(self.s_in)
+        for u in self.units:
+            mi, li = u
+            M, lin = synthetic.DECODE_M[mi], self.linears[li]
+            cur.wait_event(self.ev_in[(M, lin["K"])])
+            self.run_unit[u]()
+            self.ev_done[u].record(cur)
             with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(self.ev_done[mi])
-                lo, n = self.y_chunk[synthetic.DECODE_M[mi]]
+                self.s_out.wait_event(self.ev_done[u])
+                lo, n = self.y_off[(M, lin["name"])]
                 self.y_all_host[lo:lo + n].copy_(self.y_all[lo:lo + n], non_blocking=True)
         cur.wait_stream(self.s_out)
 
@@ -457,18 +481,19 @@ def run_gpu(args):
     }
 
     # ---- end to end through the C ABI with host buffers -----------------------------------------
+    units = wl.e2e_units()
     if args.no_graph:
-        run_m = [(lambda mi=mi: wl.step_m(mi)) for mi in range(n_m)]
+        run_unit = {u: (lambda u=u: wl.step_unit(*u)) for u in units}
     else:
-        graphs_m = [_capture(lambda mi=mi: wl.step_m(mi), dev) for mi in range(n_m)]
-        run_m = [gm.replay for gm in graphs_m]
-    wl.e2e_setup(run_m)
+        graphs_u = {u: _capture(lambda u=u: wl.step_unit(*u), dev) for u in units}
+        run_unit = {u: g_.replay for u, g_ in graphs_u.items()}
+    wl.e2e_setup(run_unit)
     ms3 = max_over_ranks(_time_loop(wl.e2e_step, args.steps, args.warmup, dev, barrier)) / args.steps
     h2d, d2h = wl.e2e_bytes()
     e2e = {"value": round(step_bytes / (ms3 * 1e-3) / 1e9, 1), "unit": UNIT,
            "ms_per_step": round(ms3, 4), "h2d_bytes_per_step": h2d * world,
            "d2h_bytes_per_step": d2h * world,
-           "copies": "per batch size, on two copy streams, overlapped with the other batch sizes' linears"}
+           "copies": "per linear, on two copy streams, overlapped with the other linears; largest outputs first"}
     # clock samples cover the timed regions above
     clocks = sampler.stop() if sampler is not None else None
     _lib.device_status(local_rank)
