@@ -114,6 +114,14 @@ def test_config2_prefill_mlp_full_size():
     ref_d = O.epilogue(O.acc_int32(codes[rows.to(DEV)].cpu(), qw_d), sw_d, r_dn[cols_d], sxd[rows.to(DEV)].cpu())
     got_d = y[rows.to(DEV)][:, cols_d.to(DEV)].cpu()
     assert ((got_d.double() - ref_d.double()).abs().max() / ref_d.double().abs().max()).item() < 1e-5
+    # the same projection on the FP8 tensor-core path (the quantiser writes E4M3 code bytes, the
+    # weight's byte form is derived from the artefact): the whole [8192, 4096] output bit for bit
+    x8, sx8 = ops.quant_act_int4_gated(gu[:, :I], gu[:, I:], a_dn.to(DEV), had_dev, True, e4m3=True)
+    assert torch.equal(sx8, sxd)
+    y8 = ops.gemm_w4a4_int4_e4m3(x8, sx8, pw_dn.bytes_e4m3(), pw_dn, r_dn.to(DEV))
+    _lib.device_status(0)
+    assert torch.equal(y8, y)
+    del x8, y8
     # and the plain (ungated) Hadamard quantiser at this size, bit-exact
     hb = h.to(torch.bfloat16)
     c2, s2 = ops.quant_act_int4(hb.to(DEV), a_dn.to(DEV), had_dev, True)
