@@ -556,6 +556,7 @@ def run_extras(args, world, rank, local_rank, dev):
         guarded("mlp", lambda: run_mlp_suite(sub, emit=False))
         guarded("fp4", lambda: run_fp4_suite(sub, emit=False))
         guarded("reference_gpu_kernels", lambda: run_reference_gpu(sub, emit=False))
+        guarded("bcd", lambda: run_bcd_suite(sub, emit=False))
     sub.fused_allreduce = True
     try:
         out["decoder"] = run_decoder_suite(sub, emit=False, init_pg=False)
@@ -1297,6 +1298,66 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 # The reference's own GPU kernels (Triton) on this GPU: context rows, never on the product path
 # ------------------------------------------------------------------------------------------------
+def run_bcd_suite(args, emit=True):
+    """DualQuant's offline scale search + block quantisation of one 4096 x 4096 weight (32 column
+    blocks of 128, row_column scales, five iterations, E8M0 row scales): dualquant_b200.bcd on the
+    GPU (all blocks as one batch) next to the reference's wrap_dualquant_layer on the host cores
+    (block after block; timed on the first four blocks and scaled to 32 - the blocks are
+    independent and equally large)."""
+    from dualquant_b200 import bcd
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    R, C, bs, iters = 4096, 4096, 128, 5
+    cfg = dict(scale_option="row_column", row_init="max_abs", col_init="l1_norm", num_iter=iters, scale_format="e8m0")
+    g = torch.Generator(device=dev).manual_seed(0)
+    W = torch.randn(R, C, generator=g, device=dev) * 0.02
+    for _ in range(2):
+        bcd.dualquant_weight(W, block_size=bs, **cfg)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        mat_q, cs = bcd.dualquant_weight(W, block_size=bs, **cfg)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    gpu_ms = e0.elapsed_time(e1) / reps
+    W3 = W.reshape(R, C // bs, bs)
+    s = W3.abs().amax(dim=-1, keepdim=True) / 7.0
+    rtn = ((W3 / s).round().clamp(-8, 7) * s).reshape(R, C)
+    rec = {"suite": "bcd", "rows": R, "cols": C, "block_size": bs, "num_iter": iters, "scale_format": "e8m0",
+           "gpu_ms": round(gpu_ms, 2),
+           "mse_dualquant_over_rtn": round((((mat_q * cs - W) ** 2).mean() / ((rtn - W) ** 2).mean()).item(), 4)}
+    try:
+        from oracle import stage_reference as SR
+
+        SR.import_reference()
+        from layer_wrapper_dualquant import wrap_dualquant_layer
+
+        nb = 4
+        lin = torch.nn.Linear(nb * bs, R, bias=False)
+        lin.weight.data.copy_(W[:, :nb * bs].cpu())
+        ref_cfg = dict(num_splits=1, block_size=bs, dualquant_to_element_tensor=True, **cfg)
+        t0 = time.time()
+        ref_cs = wrap_dualquant_layer(lin, None, ref_cfg, "rtn_int4", act_quant_flag=True)
+        cpu_s = time.time() - t0
+        rec["reference_cpu"] = {"blocks_timed": nb, "seconds": round(cpu_s, 3),
+                                "scaled_to_all_blocks_ms": round(cpu_s * (C // bs) / nb * 1e3, 1),
+                                "threads": torch.get_num_threads()}
+        rec["speedup_vs_reference_cpu"] = round(cpu_s * (C // bs) / nb * 1e3 / gpu_ms, 1)
+        d = (mat_q[:, :nb * bs].cpu() - lin.weight.data).abs() / lin.weight.data.abs().max()
+        # fp32 sums in another order: ulp-level differences everywhere, a code step at a rounding boundary
+        rec["stored_weight_vs_reference"] = {"frac_elements_off_by_more_than_1e-5": round((d > 1e-5).float().mean().item(), 7),
+                                             "max_rel_diff": round(d.max().item(), 6)}
+        rec["max_rel_diff_column_scales"] = round(((cs[:nb * bs].cpu() - ref_cs).abs() / ref_cs.abs()).max().item(), 9)
+    except Exception as exc:  # noqa: BLE001
+        rec["reference_cpu"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    if emit:
+        print(json.dumps(rec), flush=True)
+    return rec
+
+
 def run_reference_gpu(args, emit=True):
     """Times the reference's two Triton kernels on the same GPU with the same CUDA-event harness:
     `fused_w4a4_gemm` (ablation/real_int4_kernel/fused_w4a4_kernel.py:129-161, group 64, autotuned)
@@ -1437,7 +1498,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="only the decode sweep (skip the prefill / MLP / FP4 / decoder sub-records)")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-(linear, M) GEMM table")
-    ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp", "decoder", "peaks", "reference_gpu"],
+    ap.add_argument("--suite", default=None, choices=["prefill", "fp4", "mlp", "decoder", "peaks", "reference_gpu", "bcd"],
                     help="one measurement suite alone")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
@@ -1459,6 +1520,8 @@ def main():
         run_peak_suite(args)
     elif args.suite == "reference_gpu":
         run_reference_gpu(args)
+    elif args.suite == "bcd":
+        run_bcd_suite(args)
     elif args.case:
         run_case(args)
     elif args.impl == "reference":

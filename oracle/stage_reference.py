@@ -11,6 +11,7 @@ Copied verbatim (files stay byte-identical; oracle/_ref/MANIFEST.txt lists them 
   blockfmt/           the indirection module that resolves the external block-format backend
   quarot/             online_had_install, the pure-torch Hadamard transform, vendored QuaRot utils
   legacy_vendor/torch_quant.py, scale_formats.py, _legacy_path.py
+  layer_wrapper_dualquant.py                                         (the offline scale search, CPU)
   vendor/dualscale_kernel_benchmark/fused_dual_scale_kernel.py      (Triton A16W4 kernel)
   ablation/real_int4_kernel/fused_w4a4_kernel.py                     (Triton W4A4 kernel)
 `import_reference()` installs the same three import shims tests/golden/make_golden.py uses
@@ -30,6 +31,7 @@ _TREES = ("activations", "formats", "quarot", "blockfmt")
 _FILES = (
     "_legacy_path.py",
     "scale_formats.py",
+    "layer_wrapper_dualquant.py",
     os.path.join("legacy_vendor", "torch_quant.py"),
     os.path.join("vendor", "dualscale_kernel_benchmark", "fused_dual_scale_kernel.py"),
     os.path.join("ablation", "real_int4_kernel", "fused_w4a4_kernel.py"),

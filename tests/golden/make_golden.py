@@ -247,6 +247,33 @@ def main(ref_root: str) -> None:
     out["beta_file_widths"] = np.array([blob[k].numel() for k in keys[:14]], dtype=np.int32)
     out["beta_file_sample"] = blob["layer0.mlp.down_proj"][:32].numpy()
 
+    # ---- DualQuant block-coordinate descent (layer_wrapper_dualquant.wrap_dualquant_layer) ----------
+    # rtn_int4, element-mode inner quantiser, act_quant_flag=True: the layer keeps mat_q, the call
+    # returns the column scales.  Configurations: 15 iterations of row_column with unrounded row
+    # scales (rows max_abs, columns l1_norm), a max_abs / l2_norm one with E4M3 row scales, an E8M0
+    # one, and column-only scales.  (The row_init="all_one" + col_init="l1_norm" combination in the
+    # name of the shipped scale files drives every code of this synthetic matrix to zero in the
+    # first step and the reference returns NaN; it is not recorded.)
+    from layer_wrapper_dualquant import wrap_dualquant_layer
+
+    g = torch.Generator().manual_seed(99)
+    wb = torch.randn(96, 256, generator=g) * 0.02
+    wb[:, torch.randperm(256, generator=g)[:4]] *= 12.0
+    out["bcd_w"] = wb.numpy().copy()
+    bcd_cfgs = {
+        "iter15": dict(scale_option="row_column", row_init="max_abs", col_init="l1_norm", num_iter=15, scale_format="none"),
+        "e4m3": dict(scale_option="row_column", row_init="max_abs", col_init="l2_norm", num_iter=5, scale_format="e4m3"),
+        "e8m0": dict(scale_option="row_column", row_init="max_abs", col_init="l1_norm", num_iter=5, scale_format="e8m0"),
+        "colonly": dict(scale_option="only_column", row_init="max_abs", col_init="l1_norm", num_iter=5, scale_format="none"),
+    }
+    for tag, c in bcd_cfgs.items():
+        lin = torch.nn.Linear(256, 96, bias=False)
+        lin.weight.data.copy_(wb)
+        cfg = dict(num_splits=1, block_size=128, dualquant_to_element_tensor=True, **c)
+        cs = wrap_dualquant_layer(lin, None, cfg, "rtn_int4", act_quant_flag=True)
+        out[f"bcd_{tag}_matq"] = lin.weight.data.numpy().copy()
+        out[f"bcd_{tag}_colscales"] = cs.numpy().copy()
+
     path = os.path.join(here, "reference_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, {k: v.shape for k, v in out.items()})
