@@ -656,6 +656,108 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// the same transform for a handful of rows: one thread-block cluster per row
+// ---------------------------------------------------------------------------------------------
+// At decode sizes (a few token rows) the fast kernel is one CTA per row on a few SMs and its phases
+// - load (+ SiLU * up), Walsh-Hadamard inside the segments, the S x S stage across them, absmax,
+// codes - are a serial chain.  Here four CTAs share a row: CTA c loads and transforms segments
+// [c S/4, (c+1) S/4), then computes the matrix stage for columns [c P/4, (c+1) P/4) of every
+// segment, reading the other CTAs' segments through distributed shared memory; the row absmax is
+// exchanged the same way.  Every sum is formed exactly as in the fast kernel (same Walsh-Hadamard
+// routine, j ascending fp32 FMAs with the factor's entry as coefficient), so scales and codes are
+// bit-identical.  Needs S % 4 == 0 and the factor in c_had_mat2.
+constexpr int kHadClusterCtas = 4;
+constexpr int kHadClusterThreads = 512;
+constexpr int kHadClusterMaxRows = 64;
+
+template <int R, typename XT>
+__global__ void __launch_bounds__(kHadClusterThreads, 1)
+act_quant_had_cluster_kernel(const XT* __restrict__ x, const XT* __restrict__ up, int64_t ldx,
+                             const float* __restrict__ a, int S, float had_scale, int8_t* __restrict__ codes,
+                             float* __restrict__ sx, float* __restrict__ out, int mode, int scale_fp16) {
+  constexpr int P = 32 * R;                   // segment length
+  constexpr int PC = P / kHadClusterCtas;     // columns of the matrix stage per CTA
+  constexpr int G = kHadClusterThreads / PC;  // threads per column: output rows i = qi, qi + G, ...
+  extern __shared__ float sm_row[];
+  __shared__ float red[kHadClusterThreads / 32];
+  __shared__ float pmax[kHadClusterCtas];
+  const int SQ = S / kHadClusterCtas;         // segments per CTA
+  const int K = S * P;
+  float* seg = sm_row;                        // [SQ][P]: this CTA's segments (read by its peers)
+  float* outv = sm_row + SQ * P;              // [S][PC]: this CTA's slice of the transformed row
+  grid_dep_launch_dependents();
+  grid_dep_wait();
+  const int rank = static_cast<int>(cluster_ctarank());
+  const int rr = blockIdx.x / kHadClusterCtas;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t base = static_cast<int64_t>(rr) * ldx + static_cast<int64_t>(rank) * SQ * P;
+  const XT* xr = x + base;
+  const XT* ur = (up != nullptr) ? up + base : nullptr;
+  const float* ar = (a != nullptr) ? a + static_cast<int64_t>(rank) * SQ * P : nullptr;
+  for (int idx = tid * 8; idx < SQ * P; idx += kHadClusterThreads * 8) {
+    float v[8];
+    load8(xr + idx, v);
+    apply_gate(ur != nullptr ? ur + idx : nullptr, v);
+    if (ar != nullptr) {
+      float av[8];
+      load8(ar + idx, av);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], av[e]);
+    }
+    *reinterpret_cast<float4*>(seg + idx) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(seg + idx + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+  __syncthreads();
+  for (int sgm = warp; sgm < SQ; sgm += kHadClusterThreads / 32) wht_segment_warp<R>(seg + sgm * P, lane);
+  cluster_sync_all();  // every CTA's segments are transformed and visible to its peers
+
+  const int col = tid % PC, qi = tid / PC;
+  float v[32];
+  {
+    const uint32_t seg_addr = smem_u32(seg);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      v[j] = 0.f;
+      if (j < S) {
+        const int owner = j / SQ, local = j - owner * SQ;
+        const uint32_t addr = dsmem_map(seg_addr + static_cast<uint32_t>((local * P + rank * PC + col) * 4),
+                                        static_cast<uint32_t>(owner));
+        v[j] = __fmul_rn(dsmem_ld_f32(addr), had_scale);
+      }
+    }
+  }
+  float amax = 0.f;
+  for (int i = qi; i < S; i += G) {  // i is the same for every lane of a warp
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc = fmaf(c_had_mat2[i * 32 + j].x, v[j], acc);  // padding entries are zero
+    outv[i * PC + col] = acc;
+    amax = fmaxf(amax, fabsf(acc));
+  }
+  float s = 1.f;
+  amax = block_max(amax, red, kHadClusterThreads / 32);  // (also orders the outv writes before their reads below)
+  if (tid < kHadClusterCtas)
+    dsmem_store_f32(dsmem_map(smem_u32(&pmax[rank]), static_cast<uint32_t>(tid)), amax);
+  cluster_sync_all();  // the four partial maxima have landed everywhere; no remote access after this point
+  if (mode != MODE_RAW) {
+    float full = pmax[0];
+#pragma unroll
+    for (int c = 1; c < kHadClusterCtas; ++c) full = fmaxf(full, pmax[c]);
+    s = token_scale(full, scale_fp16);
+    if (rank == 0 && tid == 0 && sx != nullptr) sx[rr] = s;
+  }
+  int8_t* crow = (codes != nullptr) ? codes + static_cast<int64_t>(rr) * K : nullptr;
+  float* orow = out_row_ptr(out, rr, K, mode);
+  for (int u = tid; u < S * (PC / 8); u += kHadClusterThreads) {
+    const int i = u / (PC / 8), piece = u - i * (PC / 8);
+    float e8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) e8[e] = outv[i * PC + piece * 8 + e];
+    emit8(e8, s, mode, crow, orow, i * P + rank * PC + piece * 8, scale_fp16);
+  }
+}
+
 // Copies a device-resident S x S matrix into c_had_mat2 (rows padded to 32) when it is not the
 // one already there.  The matrix behind a given pointer is assumed immutable (it is the constant
 // Hadamard factor of a layer); the copy is a stream-ordered device-to-device memcpy.
@@ -754,6 +856,14 @@ int init_act_quant_kernels() {
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
   DQ_HAD_ATTR28(16, __nv_bfloat16) DQ_HAD_ATTR28(32, __nv_bfloat16) DQ_HAD_ATTR28(16, float) DQ_HAD_ATTR28(32, float)
 #undef DQ_HAD_ATTR28
+#define DQ_HAD_ATTRC(R, T)                                                                    \
+  if (e == cudaSuccess)                                                                       \
+    e = cudaFuncSetAttribute(act_quant_had_cluster_kernel<R, T>,                                \
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+  DQ_HAD_ATTRC(4, __nv_bfloat16) DQ_HAD_ATTRC(8, __nv_bfloat16) DQ_HAD_ATTRC(16, __nv_bfloat16)
+  DQ_HAD_ATTRC(32, __nv_bfloat16) DQ_HAD_ATTRC(4, float) DQ_HAD_ATTRC(8, float) DQ_HAD_ATTRC(16, float)
+  DQ_HAD_ATTRC(32, float)
+#undef DQ_HAD_ATTRC
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(act_quant_had) failed: %s",
                      cudaGetErrorString(e));
@@ -823,6 +933,36 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
       if (plan.matrix) {
         int rc2 = upload_had_matrix(had->had_mat, plan.S, stream);
         if (rc2 != DQ_OK) return rc2;
+      }
+      // a handful of rows (decode): four CTAs per row
+      if (plan.matrix && plan.inner && plan.S % kHadClusterCtas == 0 && M <= kHadClusterMaxRows && plan.R >= 4) {
+        const int P = 32 * plan.R;
+        const size_t csmem = static_cast<size_t>(plan.S / kHadClusterCtas * P + plan.S * (P / kHadClusterCtas)) * 4;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kHadClusterCtas * M, 1, 1);
+        cfg.blockDim = dim3(kHadClusterThreads, 1, 1);
+        cfg.dynamicSmemBytes = csmem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kHadClusterCtas;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+#define DQ_HAD_CLUSTER(RR)                                                                                  \
+  DQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, act_quant_had_cluster_kernel<RR, XT>, x, up, ldx, a, plan.S, had->scale, \
+                                   codes, sx, out, mode, scale_fp16))
+        switch (plan.R) {
+          case 4: DQ_HAD_CLUSTER(4); break;
+          case 8: DQ_HAD_CLUSTER(8); break;
+          case 16: DQ_HAD_CLUSTER(16); break;
+          default: DQ_HAD_CLUSTER(32); break;
+        }
+#undef DQ_HAD_CLUSTER
+        return DQ_OK;
       }
       // many rows: smaller CTAs, several per SM (the row must leave room for three of them)
       const DeviceState* dst = current_state();
