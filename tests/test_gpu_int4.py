@@ -116,8 +116,11 @@ def _full_had(K):
                         None if had is None else had.to(DEV)), ("full", had, k)
 
 
+# (up to 64 rows with a factor order divisible by four and segments of 128 ... 1024 take the
+# four-CTA cluster kernel: 14336 = 28 x 512, 28672 = 28 x 1024, 7168 = 28 x 256, 3584 = 28 x 128;
+# 65 rows: the one-CTA kernel again)
 @pytest.mark.parametrize("M,K", [(3, 896), (2, 14336), (4, 1024), (2, 64), (3, 4096), (1, 2048), (2, 28 * 1024),
-                                 (2, 32768)])
+                                 (2, 32768), (2, 7168), (64, 3584), (65, 3584)])
 def test_full_hadamard_bit_exact(M, K):
     hd, ohad = _full_had(K)
     g = torch.Generator().manual_seed(2)
