@@ -107,7 +107,7 @@ int init_gemm_int4_f8_kernels();
 int init_gemm_fp4_persist_kernels();
 int launch_gemm_fp4_persist(const uint8_t* x_codes, const uint8_t* x_sf_atoms, const float* x_scale,
                             const uint8_t* w_codes, const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
-                            int M, int N, int K, int nvfp4, void* y, int y_dtype, cudaStream_t stream,
+                            int M, int N, int K, int nvfp4, void* y, int y_dtype, int row_tiles, cudaStream_t stream,
                             DeviceState* st);
 int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t, const float* r,
                           int M, int N, int K, void* y, int y_dtype, const void* residual, cudaStream_t stream,

@@ -67,7 +67,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx,
                 const float* __restrict__ r, const float* __restrict__ w_scale,
                 const float* __restrict__ x_scale, void* __restrict__ y, int y_bf16, int M, int N,
-                int K, int stages_per_split, int split_k, int tok_fast, int* status) {
+                int K, int stages_per_split, int split_k, int tok_fast, int row_tile0, int* status) {
   using C = FCfg<NT>;
   constexpr int kFStages = C::kStages;
   constexpr int kAtoms = NVFP4 ? 4 : 2;           // scale-factor atoms per operand per stage
@@ -85,7 +85,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // tok_fast: grid x walks the token tiles (CTAs that run together share one weight tile and the
   // whole, smaller, activation matrix stays in L2); otherwise grid x walks the row tiles
-  const int n0 = (tok_fast ? blockIdx.y : blockIdx.x) * kFBN;
+  const int n0 = (static_cast<int>(tok_fast ? blockIdx.y : blockIdx.x) + row_tile0) * kFBN;  // row_tile0: first row tile of this launch
   const int t0 = (tok_fast ? blockIdx.x : blockIdx.y) * C::kTok;
   // token blocks of this CTA that hold tokens (the last CTA of a ragged M may own only one)
   const int nblk = (NT == 2 && M - t0 > kFTN) ? 2 : 1;
@@ -429,17 +429,30 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
              "token_tile must be 0 (library's choice), 32, 128 or 256, got %d", token_tile);
   const int total_st = K / kFKStage;
   // Prefill-size batches (library's choice of tile, output addressable by the copy engine): the
-  // persistent kernel, when its 256-token tiles fill whole rounds of one tile per SM (a last round
-  // with few tiles costs a full tile time; measured on B200: gate+up and qkv of the Qwen2.5-7B shapes
-  // at M = 4096 run 1.2-1.3x faster persistent, o and down - 448 tiles on 148 SMs - do not).
+  // persistent kernel on as many row tiles as fill whole rounds of one 256-token tile per SM, the
+  // one-tile kernel (with split-K) on the row tiles that are left.  A last round with few tiles
+  // would cost a full tile time: down of the Qwen2.5-7B shapes at M = 4096 is 448 tiles on 148 SMs
+  // - 27 of its 28 row tiles go to the persistent kernel, the last to 256 split-K CTAs (measured
+  // 163 -> 147 us; the same split on o, K = 3584, does not pay for its second launch).
+  int row_tile0 = 0;  // first row tile of the one-tile launch below
   {
     const int esz0 = (y_dtype == DQ_DTYPE_BF16) ? 2 : 4;
-    const int64_t tiles256 = static_cast<int64_t>((N + kFBN - 1) / kFBN) * ((M + 255) / 256);
-    const int64_t rounds = (tiles256 + st->sm_count - 1) / st->sm_count;
-    const bool fills = tiles256 * 100 >= rounds * st->sm_count * 85;
-    if (token_tile == 0 && M >= 512 && fills && (static_cast<size_t>(N) * esz0) % 16 == 0 && aligned(y, 16))
-      return launch_gemm_fp4_persist(x_codes, x_sf_atoms, x_scale, w_codes, w_sf_atoms, w_scale, r, M, N, K,
-                                     fmt == DQ_FP4_NVFP4 ? 1 : 0, y, y_dtype, static_cast<cudaStream_t>(stream), st);
+    const int rt_all = (N + kFBN - 1) / kFBN, tok256 = (M + 255) / 256;
+    if (token_tile == 0 && M >= 512 && (static_cast<size_t>(N) * esz0) % 16 == 0 && aligned(y, 16)) {
+      const int64_t tiles256 = static_cast<int64_t>(rt_all) * tok256;
+      const int64_t rounds = (tiles256 + st->sm_count - 1) / st->sm_count;
+      int rt_p = 0;
+      if (tiles256 * 100 >= rounds * st->sm_count * 85) rt_p = rt_all;                      // fills its rounds
+      else if (tiles256 >= st->sm_count && K >= 8192)  // long K loops only: a second launch costs ~10 us
+        rt_p = static_cast<int>((tiles256 / st->sm_count) * st->sm_count / tok256);
+      if (rt_p > 0) {
+        int rc0 = launch_gemm_fp4_persist(x_codes, x_sf_atoms, x_scale, w_codes, w_sf_atoms, w_scale, r, M, N, K,
+                                          fmt == DQ_FP4_NVFP4 ? 1 : 0, y, y_dtype, rt_p,
+                                          static_cast<cudaStream_t>(stream), st);
+        if (rc0 != DQ_OK || rt_p == rt_all) return rc0;
+        row_tile0 = rt_p;
+      }
+    }
   }
   // The library's own choice otherwise: 32-token tiles for decode batches, else 128.  The 256-token tile is
   // not chosen: measured on the Qwen2.5-7B-architecture linears at M = 4096 it is 3 % faster on the
@@ -450,7 +463,7 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   int split = 1;
   {
     const int split_tok = (tile_tok == 32) ? 32 : kFTN;  // the 256-token tile never splits: judged as 128
-    const int tiles1 = ((N + kFBN - 1) / kFBN) * ((M + split_tok - 1) / split_tok);
+    const int tiles1 = ((N + kFBN - 1) / kFBN - row_tile0) * ((M + split_tok - 1) / split_tok);
     while (split < 8 && tiles1 * split * 6 < st->sm_count * 2 * 5 && total_st / (2 * split) >= 2) split *= 2;
   }
   DQ_REQUIRE(nt != 0 || M <= 32, DQ_ERR_UNSUPPORTED, "the 32-token tile covers batches of up to 32 tokens, got M=%d", M);
@@ -474,7 +487,7 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
   }
   const int sps = (total_st + split - 1) / split;
   cudaLaunchConfig_t cfg = {};
-  const int row_tiles = (N + kFBN - 1) / kFBN, tok_tiles = (M + tile_tok - 1) / tile_tok;
+  const int row_tiles = (N + kFBN - 1) / kFBN - row_tile0, tok_tiles = (M + tile_tok - 1) / tile_tok;
   // the smaller operand is the one every CTA wave re-reads; it stays in L2 when grid x walks its tiles
   const int tok_fast = (tok_tiles > 1 && M < N && row_tiles <= 65535) ? 1 : 0;
   cfg.gridDim = tok_fast ? dim3(tok_tiles, row_tiles, split) : dim3(row_tiles, tok_tiles, split);
@@ -494,7 +507,7 @@ extern "C" int dq_gemm_w4a4_fp4_tiled(const uint8_t* x_codes, const uint8_t* x_s
                   ? (nt == 2 ? gemm_fp4_kernel<1, 2> : nt == 1 ? gemm_fp4_kernel<1, 1> : gemm_fp4_kernel<1, 0>)
                   : (nt == 2 ? gemm_fp4_kernel<0, 2> : nt == 1 ? gemm_fp4_kernel<0, 1> : gemm_fp4_kernel<0, 0>);
   e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, tm_y, bulk_store, w_sf_atoms, x_sf_atoms, r, w_scale, x_scale, y, bf, M, N,
-                         K, sps, split, tok_fast, st->status_dev);
+                         K, sps, split, tok_fast, row_tile0, st->status_dev);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "gemm_fp4 launch failed (split=%d): %s", split, cudaGetErrorString(e));
   DQ_CHECK_CUDA(cudaGetLastError());

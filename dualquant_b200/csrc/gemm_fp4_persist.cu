@@ -303,9 +303,10 @@ int init_gemm_fp4_persist_kernels() {
 }
 
 // Prefill-size batches whose output the copy engine can address; the caller has validated the operands.
+// Processes row tiles [0, row_tiles) of the weight (the caller may give the rest to the one-tile kernel).
 int launch_gemm_fp4_persist(const uint8_t* x_codes, const uint8_t* x_sf_atoms, const float* x_scale,
                             const uint8_t* w_codes, const uint8_t* w_sf_atoms, const float* w_scale, const float* r,
-                            int M, int N, int K, int nvfp4, void* y, int y_dtype, cudaStream_t stream,
+                            int M, int N, int K, int nvfp4, void* y, int y_dtype, int row_tiles, cudaStream_t stream,
                             DeviceState* st) {
   CUtensorMap tm_w, tm_x, tm_y;
   int rc = make_tmap_2d_u8(&tm_w, w_codes, static_cast<uint64_t>(K) / 2, N, static_cast<uint64_t>(K) / 2, 128, kFBN,
@@ -317,7 +318,7 @@ int launch_gemm_fp4_persist(const uint8_t* x_codes, const uint8_t* x_sf_atoms, c
   const int esz = (y_dtype == DQ_DTYPE_BF16) ? 2 : 4;
   rc = make_tmap_2d_out(&tm_y, y, esz, static_cast<uint64_t>(N), static_cast<uint64_t>(M), kFBN, 32);
   if (rc != DQ_OK) return rc;
-  const int row_tiles = (N + kFBN - 1) / kFBN, tok_tiles = (M + fp4p::kTok - 1) / fp4p::kTok;
+  const int tok_tiles = (M + fp4p::kTok - 1) / fp4p::kTok;  // row_tiles: the first row tiles of the weight
   const int64_t tiles = static_cast<int64_t>(row_tiles) * tok_tiles;
   const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
   // a block of token tiles whose packed activations (K / 2 bytes per token) take about 40 MB of L2

@@ -218,8 +218,11 @@ def test_fp4_gemm_token_tiles_agree(fmt, M, N, K):
 # that fill whole rounds of one tile per SM): one tile per CTA and several, a last token tile of 216
 # tokens (two scale-factor blocks) and one of 100 (a single block), rows past N.
 @pytest.mark.parametrize("fmt", [_lib.FP4_MXFP4, _lib.FP4_NVFP4])
+# (1024 x 5120 and 1000 x 5104 are 160 tiles on 148 SMs: 37 row tiles go to the persistent kernel,
+# the last three to the one-tile kernel with split-K)
 @pytest.mark.parametrize("M,N,K,dtype", [(728, 6272, 512, torch.float32), (612, 6260, 768, torch.bfloat16),
-                                         (2048, 9472, 256, torch.bfloat16)])
+                                         (2048, 9472, 256, torch.bfloat16), (1024, 5120, 8192, torch.bfloat16),
+                                         (1000, 5104, 8192, torch.float32)])
 def test_fp4_persistent_kernel_equals_the_one_tile_kernel(fmt, M, N, K, dtype):
     x = synthetic.make_x(M, K, M + 1)
     w = synthetic.make_w(N, K, N + 2)
@@ -232,7 +235,10 @@ def test_fp4_persistent_kernel_equals_the_one_tile_kernel(fmt, M, N, K, dtype):
     got = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
     ops.gemm_w4a4_fp4(codes, sfa, rs, pw, r.to(DEV), out=got)  # library's choice: the persistent kernel
     _lib.device_status(0)
-    assert torch.equal(got, want)
+    # (rows finished by a split-K launch sum their fp32 partial sums in another order)
+    assert torch.allclose(got.float(), want.float(), rtol=2e-6 if dtype == torch.float32 else 2 ** -7, atol=1e-6)
+    if N in (6272, 6260, 9472):
+        assert torch.equal(got, want)
     ref = _fp4_reference(x, a.cpu(), w, r, fmt)
     err = ((got.double().cpu() - ref).abs().max() / ref.abs().max()).item()
     assert err < (1e-3 if dtype == torch.float32 else 1e-2), err
