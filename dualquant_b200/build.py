@@ -17,6 +17,8 @@ SOURCES = [
     "dq_runtime.cu",
     "weights_int4.cu",
     "act_quant_int4.cu",
+    "act_quant_had_bf16.cu",
+    "act_quant_had_f32.cu",
     "quant_fp4.cu",
     "gemm_w4a4_int4.cu",
     "gemm_w4a4_int4_tm.cu",
