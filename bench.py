@@ -1424,9 +1424,75 @@ def run_reference_gpu(args, emit=True):
             torch.cuda.empty_cache()
         rec["rows"].append(row)
         del w, x, pw
+    try:
+        rec["decode_sweep"] = _reference_gpu_decode_sweep(SR, fdk, fwk, dev)
+    except Exception as exc:  # noqa: BLE001
+        rec["decode_sweep"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if emit:
         print(json.dumps(rec), flush=True)
     return rec
+
+
+def _reference_gpu_decode_sweep(SR, fdk, fwk, dev, budget_s=90.0):
+    """The headline step (the 24 (linear, M) pairs of the decode sweep) through the reference's own GPU
+    code on this GPU: (a) its PermLinear - fake-quantised activations into a bf16 F.linear, the path the
+    reference runs by default - and (b) its Triton W4A4 kernel (fused_w4a4_gemm, group 64, autotuned per
+    shape; stops adding shapes once `budget_s` seconds are spent and says so).  One weight copy per
+    linear, eager launches, CUDA events around the whole step; GB/s counts the same algorithmic int4
+    bytes as the headline, so the figures compare like for like."""
+    ref = SR.import_reference()
+    g = torch.Generator(device=dev).manual_seed(0)
+    out = {"step_algorithmic_bytes": _step_bytes(1)}
+    lins = []
+    for name, K, N in synthetic.LLAMA31_8B_LINEARS:
+        w = torch.randn(N, K, generator=g, device=dev) * 0.02
+        _, c = synthetic.make_scales(N, K, 0)
+        lin = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+        lin.weight.data.copy_(w.to(torch.bfloat16))
+        pl = ref.PermLinear(lin, ref.make_format("rtn_int4", block_size=-1))
+        pl.set_act_scale((1.0 / c).to(dev))
+        lins.append((name, K, N, w, pl, (1.0 / c).to(dev).to(torch.bfloat16)))
+    xs = {(M, K): torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+          for M in synthetic.DECODE_M for K in {k for _, k, _ in synthetic.LLAMA31_8B_LINEARS}}
+
+    def step_permlinear():
+        for M in synthetic.DECODE_M:
+            for _name, K, _N, _w, pl, _b in lins:
+                pl(xs[(M, K)])
+
+    with torch.no_grad():
+        step_permlinear()
+        torch.cuda.synchronize(dev)
+        ms = _time_loop(step_permlinear, 10, 3, dev, lambda: None) / 10
+    out["reference_permlinear_bf16"] = {"ms_per_step": round(ms, 3),
+                                        "GBps": round(out["step_algorithmic_bytes"] / ms / 1e6, 1),
+                                        "what": "PermLinear.forward (fake-quant activations, bf16 F.linear), eager"}
+    # Triton W4A4 kernel: autotune every shape first (inside the time budget), then time the shapes done
+    t0 = time.time()
+    packed, done = {}, []
+    for name, K, N, w, _pl, beta in lins:
+        packed[name] = fdk.pack_int4_weights(w, 64)
+    for M in synthetic.DECODE_M:
+        for name, K, N, _w, _pl, beta in lins:
+            if time.time() - t0 > budget_s:
+                break
+            wp, s1 = packed[name]
+            fwk.fused_w4a4_gemm(xs[(M, K)], beta, wp, s1, group_size=64)  # compile / autotune
+            torch.cuda.synchronize(dev)
+            done.append((M, name, K, N, beta))
+
+    def step_triton():
+        for M, name, K, _N, beta in done:
+            wp, s1 = packed[name]
+            fwk.fused_w4a4_gemm(xs[(M, K)], beta, wp, s1, group_size=64)
+
+    if done:
+        ms_t = _time_loop(step_triton, 10, 3, dev, lambda: None) / 10
+        nbytes = sum(synthetic.int4_gemm_bytes(M, N, K) for M, _n, K, N, _b in done)
+        out["reference_triton_w4a4_g64"] = {"pairs_timed": len(done), "of": 24, "ms": round(ms_t, 3),
+                                            "GBps": round(nbytes / ms_t / 1e6, 1),
+                                            "what": "fused_w4a4_gemm (per-(row, K tile) activation scales, group 64), eager"}
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
