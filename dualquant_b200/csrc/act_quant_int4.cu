@@ -24,7 +24,7 @@ namespace dq {
 // shape, where the kernel is bound by instruction issue and registers are plentiful) instead of
 // being re-expanded from the raw row (few-rows shape, where occupancy hides latency).
 template <int THREADS, int VPT, typename XT, bool KEEP = false>
-__global__ void __launch_bounds__(THREADS, (THREADS >= 512 && VPT <= 2) ? 2048 / THREADS : 1)
+__global__ void __launch_bounds__(THREADS, (THREADS >= 512 && VPT <= 2) ? 2048 / THREADS : (VPT >= 4 && !KEEP) ? 1024 / THREADS : 1)
 act_quant_rows_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int K,
                       int8_t* __restrict__ codes, float* __restrict__ sx, float* __restrict__ out,
                       int mode, int scale_fp16, const __nv_bfloat16* __restrict__ norm_w,
@@ -426,7 +426,10 @@ static int launch_act(const XT* x, int64_t ldx, const float* a, const dq_hadamar
     // kernel is then bound by bytes in flight per SM, not by the per-row latency chain.
     if (M >= kBigM && vec > 128 && vec <= 512) DQ_ROWS_LAUNCH_K(128, 4, true);
     else if (M >= kBigM && vec > 512 && vec <= 1024) DQ_ROWS_LAUNCH_K(256, 4, true);
-    else if (M >= kBigM && vec > 1024 && vec <= 2048) DQ_ROWS_LAUNCH_K(512, 4, true);
+    // long rows (e.g. 14336): 256 threads with eight vectors each, re-expanded in the code pass, so
+    // that four CTAs (four rows) share an SM - 512 threads keeping their values held one row per SM
+    // and ran at 1.85 TB/s where this shape reaches 2.7
+    else if (M >= kBigM && vec > 1024 && vec <= 2048) DQ_ROWS_LAUNCH_K(256, 8, false);
     else if (vec <= 128) DQ_ROWS_LAUNCH(128, 1);
     else if (vec <= 256) DQ_ROWS_LAUNCH(256, 1);
     else if (vec <= 512) DQ_ROWS_LAUNCH(512, 1);
