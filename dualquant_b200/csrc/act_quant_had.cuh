@@ -118,6 +118,42 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
   if (matrix) {
     // two adjacent columns per thread (P is even): packed loads, packed FMAs
     constexpr int HN = (HS > 0) ? HS : 32;  // factor order known at compile time, or padded to 32
+    constexpr int pairs = 16 * R;  // P = 32 R
+    if constexpr (pairs < THREADS) {
+      // Short segments (rows of 28 * 64 ... 28 * 256 values, the shards of a row-parallel linear):
+      // fewer column pairs than threads.  G = THREADS / pairs threads share one pair, each holding
+      // its S inputs in registers and forming the output rows i = qi, qi + G, ...; every sum is the
+      // same j-ascending chain as below.  (pairs is a power of two, so G is whole; qi is the same for
+      // all lanes of a warp once a segment has 64 values, which keeps the coefficient loads uniform.)
+      constexpr int G = THREADS / pairs;
+      const int c = 2 * (static_cast<int>(threadIdx.x) & (pairs - 1)), qi = static_cast<int>(threadIdx.x) / pairs;
+      float2 v[HN];
+#pragma unroll
+      for (int j = 0; j < HN; ++j) {
+        v[j] = (j < S) ? *reinterpret_cast<const float2*>(row + j * P + c) : make_float2(0.f, 0.f);
+        v[j].x = __fmul_rn(v[j].x, had_scale);
+        v[j].y = __fmul_rn(v[j].y, had_scale);
+      }
+      __syncthreads();  // every thread holds its inputs before the first output row replaces them
+      for (int i = qi; i < S; i += 2 * G) {  // two independent chains in flight
+        const int i2 = i + G;
+        const bool second = i2 < S;
+        const float2* h0 = c_had_mat2 + i * 32;
+        const float2* h1 = c_had_mat2 + (second ? i2 : i) * 32;
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < HN; ++j) {
+          acc0 = __ffma2_rn(h0[j], v[j], acc0);
+          acc1 = __ffma2_rn(h1[j], v[j], acc1);
+        }
+        *reinterpret_cast<float2*>(row + i * P + c) = acc0;
+        amax = fmaxf(amax, fmaxf(fabsf(acc0.x), fabsf(acc0.y)));
+        if (second) {
+          *reinterpret_cast<float2*>(row + i2 * P + c) = acc1;
+          amax = fmaxf(amax, fmaxf(fabsf(acc1.x), fabsf(acc1.y)));
+        }
+      }
+    } else
     for (int c = 2 * threadIdx.x; c < P; c += 2 * THREADS) {
       float2 v[HN];
 #pragma unroll
@@ -295,6 +331,106 @@ act_quant_had_cluster_kernel(const XT* __restrict__ x, const XT* __restrict__ up
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// the across-heads transform (o_proj input) for many rows: registers only
+// ---------------------------------------------------------------------------------------------
+// Row = S heads of 128 values, Walsh-Hadamard over the head index for each of the 128 lanes of a
+// head.  The one-CTA-per-row kernel above spends its time waiting (load, barrier, 128 busy threads,
+// barrier, store); here a lane owns eight adjacent columns of min(S, 16) heads and keeps them in
+// registers from the load to the codes: 16 lanes cover a row (32 for S = 32, where the halves of
+// the warp hold heads 0-15 and 16-31 and the last stage is one shuffle per value), nothing goes
+// through shared memory and no barrier is needed.  Same stage order and operand order as above.
+// Codes only (int8 or E4M3, fp32 or fp16 scale), no gate: everything is unrolled over the heads, and
+// with the other output modes and the SiLU gate expanded sixteen times the code outgrew the
+// instruction cache (measured: 2.4x slower than the kernel above at 32 heads).
+constexpr int kHeadsKernelThreads = 128;
+constexpr int kHeadsKernelMinRows = 64;
+
+template <int S, typename XT, bool E4M3>
+__global__ void __launch_bounds__(kHeadsKernelThreads)
+act_quant_had_heads_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ a, int M,
+                           float had_scale, int8_t* __restrict__ codes, float* __restrict__ sx, int scale_fp16) {
+  constexpr int HL = (S < 16) ? S : 16;   // heads per lane
+  constexpr int L = (S == 32) ? 32 : 16;  // lanes per row
+  constexpr int K = S * 128;
+  grid_dep_launch_dependents();
+  grid_dep_wait();
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (L - 1);
+  const int64_t rr = (static_cast<int64_t>(blockIdx.x) * (kHeadsKernelThreads / 32) + (threadIdx.x >> 5)) * (32 / L) +
+                     lane / L;
+  const bool live = rr < M;  // lanes of a row past the end keep running (shuffles), but touch no memory
+  const int col = 8 * (sub & 15);
+  const int head0 = (S == 32 && sub >= 16) ? 16 : 0;
+  const XT* xr = x + (live ? rr : 0) * ldx;
+  float v[HL][8];
+#pragma unroll
+  for (int j = 0; j < HL; ++j) {
+    const int idx = (head0 + j) * 128 + col;
+    if (live) {
+      load8(xr + idx, v[j]);
+      if (a != nullptr) {
+        float av[8];
+        load8(a + idx, av);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] = __fmul_rn(v[j][e], av[e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[j][e] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int h = 1; h < HL; h <<= 1) {
+#pragma unroll
+    for (int j = 0; j < HL; ++j) {
+      if ((j & h) == 0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float u = v[j][e], w = v[j + h][e];
+          v[j][e] = __fadd_rn(u, w);
+          v[j + h][e] = __fsub_rn(u, w);
+        }
+      }
+    }
+  }
+  if constexpr (S == 32) {  // heads j and j + 16 sit in lanes l and l + 16
+    const bool upper = sub >= 16;
+#pragma unroll
+    for (int j = 0; j < HL; ++j) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j][e], 16);
+        v[j][e] = upper ? __fsub_rn(other, v[j][e]) : __fadd_rn(v[j][e], other);
+      }
+    }
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < HL; ++j) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[j][e] = __fmul_rn(v[j][e], had_scale);
+      amax = fmaxf(amax, fabsf(v[j][e]));
+    }
+  }
+#pragma unroll
+  for (int o = L / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (!live) return;
+  const float s = token_scale(amax, scale_fp16);
+  if (sub == 0 && sx != nullptr) sx[rr] = s;
+  const float inv_s = __fdiv_rn(1.0f, s);
+  int8_t* crow = codes + rr * K;
+#pragma unroll
+  for (int j = 0; j < HL; ++j) {
+    float q[8];
+    quant_codes8(v[j], s, inv_s, q);
+    const uint32_t lo = E4M3 ? pack_codes4_e4m3(q[0], q[1], q[2], q[3]) : pack_codes4(q[0], q[1], q[2], q[3]);
+    const uint32_t hi = E4M3 ? pack_codes4_e4m3(q[4], q[5], q[6], q[7]) : pack_codes4(q[4], q[5], q[6], q[7]);
+    *reinterpret_cast<uint2*>(crow + (head0 + j) * 128 + col) = make_uint2(lo, hi);
+  }
+}
+
 // Copies a device-resident S x S matrix into c_had_mat2 (rows padded to 32) when it is not the
 // one already there.  The matrix behind a given pointer is assumed immutable (it is the constant
 // Hadamard factor of a layer); the copy is a stream-ordered device-to-device memcpy.
@@ -377,7 +513,7 @@ int init_had_fast_t() {
   if (e == cudaSuccess)                                                                       \
     e = cudaFuncSetAttribute(act_quant_had_fast_kernel<R, XT, 256, 28>,                         \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kHadMaxSmem);
-  DQ_HAD_ATTR28(16) DQ_HAD_ATTR28(32)
+  DQ_HAD_ATTR28(2) DQ_HAD_ATTR28(4) DQ_HAD_ATTR28(8) DQ_HAD_ATTR28(16) DQ_HAD_ATTR28(32)
 #undef DQ_HAD_ATTR28
 #define DQ_HAD_ATTRC(R)                                                                       \
   if (e == cudaSuccess)                                                                       \
@@ -403,6 +539,28 @@ int launch_had_fast_t(const XT* x, const XT* up, int64_t ldx, const float* a, co
       if (plan.matrix) {
         int rc2 = upload_had_matrix(had->had_mat, plan.S, stream);
         if (rc2 != DQ_OK) return rc2;
+      }
+      // across 2 ... 32 heads of 128 values, many rows: the register-only kernel
+      if (had->kind == DQ_HAD_PARTIAL && had->had_dim == 128 && plan.S >= 2 && M >= kHeadsKernelMinRows &&
+          up == nullptr && mode == MODE_CODES && codes != nullptr && (scale_fp16 & 0xFF) != 2) {
+        const int rows_per_cta = (kHeadsKernelThreads / 32) * (plan.S == 32 ? 1 : 2);
+        const dim3 grid((M + rows_per_cta - 1) / rows_per_cta);
+#define DQ_HAD_HEADS(SS)                                                                                            \
+  if ((scale_fp16 & kCodesE4M3) != 0)                                                                               \
+    DQ_CHECK_CUDA(launch_pdl(act_quant_had_heads_kernel<SS, XT, true>, grid, dim3(kHeadsKernelThreads), 0, stream, x, \
+                             ldx, a, M, had->scale, codes, sx, scale_fp16));                                        \
+  else                                                                                                              \
+    DQ_CHECK_CUDA(launch_pdl(act_quant_had_heads_kernel<SS, XT, false>, grid, dim3(kHeadsKernelThreads), 0, stream, x, \
+                             ldx, a, M, had->scale, codes, sx, scale_fp16))
+        switch (plan.S) {
+          case 2: DQ_HAD_HEADS(2); break;
+          case 4: DQ_HAD_HEADS(4); break;
+          case 8: DQ_HAD_HEADS(8); break;
+          case 16: DQ_HAD_HEADS(16); break;
+          default: DQ_HAD_HEADS(32); break;
+        }
+#undef DQ_HAD_HEADS
+        return DQ_OK;
       }
       // a handful of rows (decode): four CTAs per row
       if (plan.matrix && plan.inner && plan.S % kHadClusterCtas == 0 && M <= kHadClusterMaxRows && plan.R >= 4) {
@@ -442,7 +600,7 @@ int launch_had_fast_t(const XT* x, const XT* up, int64_t ldx, const float* a, co
                            ldx, a, K, plan.S, plan.inner, plan.matrix, had->scale, had->had_mat, codes, sx,   \
                            out, mode, scale_fp16))
 #define DQ_HAD_FAST(RR)                                            \
-  if (plan.matrix && plan.S == 28 && (RR == 16 || RR == 32)) {     \
+  if (plan.matrix && plan.S == 28 && RR >= 2) {                    \
     if (small_cta) DQ_HAD_FAST_T(RR, 256, 28);                     \
     else DQ_HAD_FAST_T(RR, 512, 28);                               \
   } else if (small_cta) {                                          \

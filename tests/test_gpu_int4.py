@@ -135,6 +135,25 @@ def test_full_hadamard_bit_exact(M, K):
     _status_ok()
 
 
+# Row lengths of a row-parallel down_proj shard (14336 / 8, / 4, / 2) and other short segments: several
+# threads share a column pair of the matrix stage.  70 rows: one 512-thread CTA per row; 500 rows: three
+# 256-thread CTAs per SM.  1536 = 12 x 128 and 2560 = 40 x 64 -> 20 x 128 go through the generic order.
+@pytest.mark.parametrize("M,K", [(70, 1792), (500, 1792), (500, 3584), (70, 7168), (500, 7168), (70, 14336),
+                                 (500, 14336), (500, 896), (500, 1536), (70, 2560)])
+def test_full_hadamard_many_rows_bit_exact(M, K):
+    hd, ohad = _full_had(K)
+    xb = synthetic.make_x(M, K, 11)
+    _, c = synthetic.make_scales(8, K, 11)
+    a = 1.0 / c
+    qx, sx, _ = O.quant_act_int4(xb, a, ohad, False)
+    codes, sxg = ops.quant_act_int4(xb.to(DEV), a.to(DEV), hd, False)
+    assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
+    x32 = xb.float()
+    got = ops.hadamard_f32(x32.to(DEV), hd)
+    assert torch.equal(got.cpu(), O.hadamard_full(x32, ohad[1], ohad[2]))
+    _status_ok()
+
+
 @pytest.mark.parametrize("K,d", [(4096, 128), (256, 8), (1024, 64), (8192, 128)])
 def test_partial_hadamard_bit_exact(K, d):
     M = 5
@@ -145,6 +164,25 @@ def test_partial_hadamard_bit_exact(K, d):
     qx, sx, _ = O.quant_act_int4(xb, a, ("partial", d), False)
     codes, sxg = ops.quant_act_int4(xb.to(DEV), a.to(DEV), hd, False)
     assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
+
+
+# 64 rows and more of 2 ... 32 heads x 128 take the register-only kernel (16 or 32 lanes per row);
+# 63 rows and head sizes other than 128 stay on the one-CTA-per-row kernel.
+@pytest.mark.parametrize("M,K,d", [(64, 4096, 128), (333, 4096, 128), (300, 2048, 128), (301, 1024, 128),
+                                   (65, 512, 128), (1000, 256, 128), (63, 4096, 128), (300, 1024, 64)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_partial_hadamard_many_rows_bit_exact(M, K, d, dtype):
+    hd = ops.Hadamard(_lib.HAD_PARTIAL, 1, d, O.partial_hadamard_scale(K // d), None)
+    xb = synthetic.make_x(M, K, 12)
+    _, c = synthetic.make_scales(8, K, 12)
+    a = 1.0 / c
+    for fp16 in (False, True):
+        qx, sx, _ = O.quant_act_int4(xb, a, ("partial", d), fp16)
+        codes, sxg = ops.quant_act_int4(xb.to(DEV).to(dtype), a.to(DEV), hd, fp16)
+        assert torch.equal(codes.cpu(), qx) and torch.equal(sxg.cpu(), sx)
+    x8, sx8 = ops.quant_act_int4(xb.to(DEV).to(dtype), a.to(DEV), hd, True, e4m3=True)
+    assert torch.equal(x8, ops.codes_to_e4m3(codes)) and torch.equal(sx8, sxg)
+    _status_ok()
 
 
 @pytest.mark.parametrize("K", [1536, 2560, 1152, 1664, 3840, 6912, 4480, 4992, 11008])
@@ -384,6 +422,9 @@ def test_all_gemm_kernels_bit_identical_on_random_shapes():
         auto1 = ops.gemm_w4a4_int4(codes, sx, pw, r)
         auto2 = ops.gemm_w4a4_int4(codes, sx, pw, r)
         assert torch.equal(auto1, auto2), (M, N, K)
+        # the persistent FP8-path kernel (codes as E4M3 bytes, fp32 group sums): same bits again
+        y8 = ops.gemm_w4a4_int4_e4m3(ops.codes_to_e4m3(codes), sx, ops.expand_w_e4m3(pw), pw, r)
+        assert torch.equal(y8, outs[0]), (M, N, K, "e4m3")
     _status_ok()
 
 
