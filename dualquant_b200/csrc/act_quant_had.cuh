@@ -24,7 +24,7 @@ constexpr int kHadFastMaxSmem = 200 * 1024;
 // Full transform of size 28 * 512: A + matrix.  Full power-of-two size: A + butterflies.
 // Partial (across heads) transform: butterflies only, segments = heads.
 template <int R>
-__device__ __forceinline__ void wht_segment_warp(float* seg, int lane) {
+__device__ __forceinline__ void wht_segment_warp(float* seg, int lane, float post = 1.0f) {
   // lane l holds elements l + 32 r (r < R): conflict-free shared-memory access; stages h < 32
   // pair lanes (shuffle), stages h >= 32 pair registers r and r + h/32.  Stage order h = 1, 2, ...
   float v[R];
@@ -50,8 +50,10 @@ __device__ __forceinline__ void wht_segment_warp(float* seg, int lane) {
       }
     }
   }
+  // `post`: the transform's scale when a matrix stage follows (it multiplies every value once, here,
+  // instead of once per thread that reads the value there); 1 otherwise, an exact identity
 #pragma unroll
-  for (int r = 0; r < R; ++r) seg[lane + 32 * r] = v[r];
+  for (int r = 0; r < R; ++r) seg[lane + 32 * r] = __fmul_rn(v[r], post);
 }
 
 // The K x K +-1 matrix of the "full" transform, in constant memory so that an FMA takes its
@@ -66,6 +68,30 @@ __global__ void __launch_bounds__(1024) had_table_kernel(const float* __restrict
   const int t = threadIdx.x, i = t >> 5, j = t & 31;
   const float h = (i < S && j < S) ? had_mat[i * S + j] : 0.f;  // rows and columns padded to 32 with zeros
   g_had_stage[t] = make_float2(h, h);
+}
+
+// Output rows QI, QI + G, ... of the matrix stage for one column pair, fully unrolled (see the
+// call site); matrix_rows_dispatch selects the copy for a run-time qi in [0, G).
+template <int HN, int G, int QI>
+__device__ __forceinline__ void matrix_rows_static(const float2* v, float* row, int P, int c, int S, float& amax) {
+#pragma unroll
+  for (int i = QI; i < HN; i += G) {
+    if (i < S) {
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < HN; ++j) acc = __ffma2_rn(c_had_mat2[i * 32 + j], v[j], acc);
+      *reinterpret_cast<float2*>(row + i * P + c) = acc;
+      amax = fmaxf(amax, fmaxf(fabsf(acc.x), fabsf(acc.y)));
+    }
+  }
+}
+template <int HN, int G, int QI = 0>
+__device__ __forceinline__ void matrix_rows_dispatch(int qi, const float2* v, float* row, int P, int c, int S,
+                                                     float& amax) {
+  if constexpr (QI < G) {
+    if (qi == QI) matrix_rows_static<HN, G, QI>(v, row, P, c, S, amax);
+    else matrix_rows_dispatch<HN, G, QI + 1>(qi, v, row, P, c, S, amax);
+  }
 }
 
 // THREADS = 512: one CTA per SM, the shortest time per row (decode batches, one row per SM at most).
@@ -110,9 +136,11 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
   __syncthreads();
 
   if (inner) {
-    for (int sgm = warp; sgm < S; sgm += THREADS / 32) wht_segment_warp<R>(row + sgm * P, lane);
+    for (int sgm = warp; sgm < S; sgm += THREADS / 32)
+      wht_segment_warp<R>(row + sgm * P, lane, matrix ? had_scale : 1.0f);
     __syncthreads();
   }
+  const bool scale_here = !inner;  // no Walsh-Hadamard phase: the matrix stage scales its own inputs
 
   float amax = 0.f;
   if (matrix) {
@@ -129,12 +157,21 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
       const int c = 2 * (static_cast<int>(threadIdx.x) & (pairs - 1)), qi = static_cast<int>(threadIdx.x) / pairs;
       float2 v[HN];
 #pragma unroll
-      for (int j = 0; j < HN; ++j) {
+      for (int j = 0; j < HN; ++j)
         v[j] = (j < S) ? *reinterpret_cast<const float2*>(row + j * P + c) : make_float2(0.f, 0.f);
-        v[j].x = __fmul_rn(v[j].x, had_scale);
-        v[j].y = __fmul_rn(v[j].y, had_scale);
+      if (scale_here) {
+#pragma unroll
+        for (int j = 0; j < HN; ++j) {
+          v[j].x = __fmul_rn(v[j].x, had_scale);
+          v[j].y = __fmul_rn(v[j].y, had_scale);
+        }
       }
       __syncthreads();  // every thread holds its inputs before the first output row replaces them
+      if constexpr (G <= 8) {
+        // the thread's output rows are known once qi is: one fully unrolled copy per value of qi, so
+        // that every coefficient is a constant-bank operand of its FMA (HN x HN FMAs of code in all)
+        matrix_rows_dispatch<HN, G>(qi, v, row, P, c, S, amax);
+      } else
       for (int i = qi; i < S; i += 2 * G) {  // two independent chains in flight
         const int i2 = i + G;
         const bool second = i2 < S;
@@ -157,10 +194,14 @@ act_quant_had_fast_kernel(const XT* __restrict__ x, const XT* __restrict__ up, i
     for (int c = 2 * threadIdx.x; c < P; c += 2 * THREADS) {
       float2 v[HN];
 #pragma unroll
-      for (int j = 0; j < HN; ++j) {
+      for (int j = 0; j < HN; ++j)
         v[j] = (j < S) ? *reinterpret_cast<const float2*>(row + j * P + c) : make_float2(0.f, 0.f);
-        v[j].x = __fmul_rn(v[j].x, had_scale);
-        v[j].y = __fmul_rn(v[j].y, had_scale);
+      if (scale_here) {
+#pragma unroll
+        for (int j = 0; j < HN; ++j) {
+          v[j].x = __fmul_rn(v[j].x, had_scale);
+          v[j].y = __fmul_rn(v[j].y, had_scale);
+        }
       }
       // the known order is fully unrolled, so that every coefficient is a constant-bank operand of
       // its FMA and the independent accumulation chains can be interleaved; the generic form keeps

@@ -215,6 +215,39 @@ class DecoderLayer:
         attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
         return self._after_attention(x, attn, group, ar)
 
+    def forward_token_sharded(self, x, B: int, S: int, group, rope_tabs, codes, sx):
+        """Prompt pass under tensor parallelism with the residual stream sharded over tokens: x is
+        this rank's [B * S / tp, hidden] slice (ranks own consecutive blocks of tokens).  RMSNorm
+        and the activation quantiser run on the slice, the codes (one byte per element) and token
+        scales are all-gathered into `codes` [B * S, hidden] / `sx` [B * S], the column-parallel
+        linears and the attention of this rank's heads see every token, and the partial outputs of
+        the row-parallel linears come back through a reduce-scatter.  Against all-reduce + replicated
+        norms: three quarters of the bytes on the wire and 1/tp of the element-wise work."""
+        cfg = self.cfg
+        Tq, Hd = x.shape
+        T = B * S
+        hd = cfg.head_dim
+        e4m3 = codes.dtype == torch.uint8
+        c_sh, s_sh = ops.quant_act_int4_rmsnorm(x, self.ln1, cfg.rms_norm_eps, self.qkv.a, False, e4m3=e4m3)
+        dist.all_gather_into_tensor(codes, c_sh, group=group)
+        dist.all_gather_into_tensor(sx, s_sh, group=group)
+        qkv = self.qkv._gemm(codes, sx)
+        q = ops.rope_kv_append(qkv, rope_tabs[0], rope_tabs[1], 0, self.hq, self.hkv, self.k_cache, self.v_cache, S)
+        attn = F.scaled_dot_product_attention(q, self.k_cache[:, :, :S], self.v_cache[:, :, :S], is_causal=True,
+                                              enable_gqa=True)
+        o = self.o(attn.transpose(1, 2).reshape(T, self.hq * hd))
+        o_sh = torch.empty(Tq, Hd, dtype=o.dtype, device=o.device)
+        dist.reduce_scatter_tensor(o_sh, o, group=group)
+        x = x + o_sh
+        c_sh, s_sh = ops.quant_act_int4_rmsnorm(x, self.ln2, cfg.rms_norm_eps, self.gate_up.a, False, e4m3=e4m3)
+        dist.all_gather_into_tensor(codes, c_sh, group=group)
+        dist.all_gather_into_tensor(sx, s_sh, group=group)
+        gu = self.gate_up._gemm(codes, sx)
+        d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :])
+        d_sh = torch.empty(Tq, Hd, dtype=d.dtype, device=d.device)
+        dist.reduce_scatter_tensor(d_sh, d, group=group)
+        return x + d_sh
+
     def _after_attention(self, x, attn, group, ar):
         """o_proj, residual, MLP, residual."""
         cfg = self.cfg
@@ -239,11 +272,14 @@ class DecoderLayer:
 
 class Decoder:
     def __init__(self, cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, group=None,
-                 fused_allreduce: bool = False, keep_codes: bool = False):
+                 fused_allreduce: bool = False, keep_codes: bool = False, token_sharded_prefill: bool = True):
         """fused_allreduce: decode steps sum the row-parallel linears' partial outputs inside the
-        GEMM kernel over NVLink peer memory instead of calling NCCL (prefill keeps NCCL)."""
+        GEMM kernel over NVLink peer memory instead of calling NCCL (prefill keeps NCCL).
+        token_sharded_prefill: with tp > 1, prompts whose token count divides by tp keep the residual
+        stream sharded over tokens (reduce-scatter / all-gather of codes) instead of all-reducing it."""
         assert cfg.num_key_value_heads % tp == 0 and cfg.intermediate_size % (tp * 128) == 0
         self.cfg, self.tp, self.rank, self.group, self.device = cfg, tp, rank, group, device
+        self.token_sharded_prefill = token_sharded_prefill
         self.ar = None
         if fused_allreduce and tp > 1:
             self.ar = ops.AllReduceContext(group if group is not None else dist.group.WORLD, device,
@@ -265,12 +301,35 @@ class Decoder:
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [B, S] -> logits of the last position [B, vocab]."""
         B, S = ids.shape
+        if self.tp > 1 and self.token_sharded_prefill and (B * S) % self.tp == 0:
+            return self._prefill_token_sharded(ids)
         x = self.embed[ids]
         cos, sin = self.cos[:S], self.sin[:S]
         for layer in self.layers:
             x = layer.forward(x, cos, sin, 0, None, None, self.group, rope_tabs=(self.cos, self.sin))
         x = _rms_norm(x[:, -1], self.norm, self.cfg.rms_norm_eps)
         return x @ self.lm_head.T
+
+    def _prefill_token_sharded(self, ids: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        B, S = ids.shape
+        T, Hd = B * S, cfg.hidden_size
+        Tq = T // self.tp
+        lo = self.rank * Tq
+        x = self.embed[ids.reshape(-1)[lo : lo + Tq]]
+        e4m3 = T >= W4A4Linear.PREFILL_TOKENS
+        codes = torch.empty(T, Hd, dtype=torch.uint8 if e4m3 else torch.int8, device=self.device)
+        sx = torch.empty(T, dtype=torch.float32, device=self.device)
+        for layer in self.layers:
+            x = layer.forward_token_sharded(x, B, S, self.group, (self.cos, self.sin), codes, sx)
+        # the last position of every sequence lives on exactly one rank: the others contribute zeros
+        last = torch.zeros(B, Hd, dtype=torch.bfloat16, device=self.device)
+        mine = [b for b in range(B) if lo <= b * S + S - 1 < lo + Tq]
+        if mine:
+            rows = torch.tensor([b * S + S - 1 - lo for b in mine], device=self.device)
+            last[torch.tensor(mine, device=self.device)] = x[rows]
+        dist.all_reduce(last, group=self.group)
+        return _rms_norm(last, self.norm, cfg.rms_norm_eps) @ self.lm_head.T
 
     def decode_step(self, ids: torch.Tensor, pos_t: torch.Tensor) -> torch.Tensor:
         """ids [B] (one token per sequence), pos_t: int64 device tensor [1] with the cache position.
