@@ -1060,7 +1060,10 @@ def run_decoder_suite(args, emit=True, init_pg=True):
             "suite": "decoder", "n_gpus": world, "layers": cfg.num_hidden_layers, "batch": B, "seqlen": S,
             "decode_steps": steps, "parallelism": f"tp{world}: qkv/gate_up column-parallel, o/down row-parallel + "
                            + ("all-reduce fused into the decode GEMM over peer memory (NCCL in prefill)" if fused
-                              else "NCCL all-reduce"),
+                              else "NCCL all-reduce")
+                           + ("; prefill with the residual stream sharded over tokens (NCCL reduce-scatter of partial "
+                              "outputs, all-gather of activation codes)"
+                              if world > 1 and model.token_sharded_prefill and (B * S) % world == 0 else ""),
             "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(B * S / prefill_ms * 1e3, 1),
             "decode_ms_per_step": round(step_ms, 3) if checks.get("graph_equals_eager") is not False else None,
             "decode_tokens_per_s": round(B / step_ms * 1e3, 1),

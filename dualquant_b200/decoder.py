@@ -52,7 +52,9 @@ class W4A4Linear:
     """Packed int4 weight + DualQuant scales (+ optional online Hadamard) of one linear shard."""
 
     def __init__(self, N: int, K: int, device, gen: torch.Generator, had: Optional[ops.Hadamard] = None,
-                 keep_codes: bool = False):
+                 keep_codes: bool = False, gen_a: Optional[torch.Generator] = None):
+        """gen_a: generator of the input-channel scale; the shards of a column-parallel linear pass
+        one that is seeded alike on every rank (they share their input channels, hence the scale)."""
         w = (torch.randn(N, K, generator=gen, device=device) * 0.02).to(torch.bfloat16)
         codes, sw = ops.quant_w_int4(w)
         self.pw = ops.pack_w_int4(codes, sw)
@@ -60,7 +62,7 @@ class W4A4Linear:
         self.codes, self.sw = (codes, sw) if keep_codes else (None, None)
         del w, codes, sw
         self.r = torch.exp(torch.randn(N, generator=gen, device=device) * 0.3).half().float()
-        c = torch.exp(torch.randn(K, generator=gen, device=device) * 0.3).half().float()
+        c = torch.exp(torch.randn(K, generator=gen_a if gen_a is not None else gen, device=device) * 0.3).half().float()
         self.a = 1.0 / c
         self.had = had
         self.N, self.K = N, K
@@ -146,7 +148,8 @@ def _shared_hadamard_matrix(hk, kk: int, device):
 
 
 class DecoderLayer:
-    def __init__(self, cfg: DecoderConfig, tp: int, device, gen: torch.Generator, keep_codes: bool = False):
+    def __init__(self, cfg: DecoderConfig, tp: int, device, gen: torch.Generator, keep_codes: bool = False,
+                 shared: Optional[torch.Generator] = None):
         self.cfg, self.tp = cfg, tp
         hd = cfg.head_dim
         self.hq = cfg.num_attention_heads // tp
@@ -159,9 +162,9 @@ class DecoderLayer:
             hk, kk = quarot.get_hadK(inter)
             had_d = ops.Hadamard(_lib.HAD_FULL, kk, 0, quarot.full_hadamard_scale(inter),
                                  _shared_hadamard_matrix(hk, kk, device))
-        self.qkv = W4A4Linear((self.hq + 2 * self.hkv) * hd, cfg.hidden_size, device, gen, None, keep_codes)
+        self.qkv = W4A4Linear((self.hq + 2 * self.hkv) * hd, cfg.hidden_size, device, gen, None, keep_codes, shared)
         self.o = W4A4Linear(cfg.hidden_size, self.hq * hd, device, gen, had_o, keep_codes)
-        self.gate_up = W4A4Linear(2 * inter, cfg.hidden_size, device, gen, None, keep_codes)
+        self.gate_up = W4A4Linear(2 * inter, cfg.hidden_size, device, gen, None, keep_codes, shared)
         self.down = W4A4Linear(cfg.hidden_size, inter, device, gen, had_d, keep_codes)
         self.inter = inter
         self.ln1 = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
@@ -289,7 +292,7 @@ class Decoder:
         self.embed = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=shared, device=device) * 0.02).to(torch.bfloat16)
         self.lm_head = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=shared, device=device) * 0.02).to(torch.bfloat16)
         self.norm = torch.ones(cfg.hidden_size, dtype=torch.bfloat16, device=device)
-        self.layers = [DecoderLayer(cfg, tp, device, gen, keep_codes) for _ in range(cfg.num_hidden_layers)]
+        self.layers = [DecoderLayer(cfg, tp, device, gen, keep_codes, shared) for _ in range(cfg.num_hidden_layers)]
         self.max_len = 0
 
     def alloc_cache(self, batch: int, max_len: int):

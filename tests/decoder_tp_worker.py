@@ -35,8 +35,9 @@ def main():
     # 640 tokens: E4M3 codes and the FP8-path GEMM; 66 tokens: int8 codes, small-batch kernels;
     # 3 x 7 tokens with three ranks or more does not divide: the sharded path must step aside
     for B, S in ((4, 160), (2, 33 * world // 2 if world % 2 == 0 else 33 * world), (3, 7)):
-        g = torch.Generator(device=dev).manual_seed(B * 1000 + S)   # same ids on every rank
-        ids = torch.randint(0, cfg.vocab_size, (B, S), generator=g, device=dev)
+        g = torch.Generator().manual_seed(B * 1000 + S)   # CPU generator: the same prompt on every rank
+        ids = torch.randint(0, cfg.vocab_size, (B, S), generator=g).to(dev)
+        dist.broadcast(ids, src=0)
         outs = []
         with torch.no_grad():
             for m in models:
