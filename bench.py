@@ -951,7 +951,8 @@ def run_decoder_suite(args, emit=True, init_pg=True):
     cfg = decoder.DecoderConfig(num_hidden_layers=args.layers)
     B, S, steps = args.batch, args.seqlen, args.decode_steps
     fused = bool(args.fused_allreduce) and world > 1
-    model = decoder.Decoder(cfg, dev, tp=world, rank=rank, seed=0, group=group, fused_allreduce=fused)
+    model = decoder.Decoder(cfg, dev, tp=world, rank=rank, seed=0, group=group, fused_allreduce=fused,
+                            prefill_exchange=getattr(args, "prefill_exchange", "peer"))
     model.alloc_cache(B, S + steps)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab_size, (B, S), generator=g).to(dev)
@@ -1059,10 +1060,12 @@ def run_decoder_suite(args, emit=True, init_pg=True):
         rec = ({
             "suite": "decoder", "n_gpus": world, "layers": cfg.num_hidden_layers, "batch": B, "seqlen": S,
             "decode_steps": steps, "parallelism": f"tp{world}: qkv/gate_up column-parallel, o/down row-parallel + "
-                           + ("all-reduce fused into the decode GEMM over peer memory (NCCL in prefill)" if fused
+                           + ("all-reduce fused into the decode GEMM over peer memory" if fused
                               else "NCCL all-reduce")
-                           + ("; prefill with the residual stream sharded over tokens (NCCL reduce-scatter of partial "
-                              "outputs, all-gather of activation codes)"
+                           + (("; prefill with the residual stream sharded over tokens, "
+                               + ("partial output tiles pushed to their owners from the GEMM epilogue and codes pushed "
+                                  "to every rank over NVLink peer memory (no NCCL)" if model._exchange else
+                                  "NCCL reduce-scatter of partial outputs and all-gather of activation codes"))
                               if world > 1 and model.token_sharded_prefill and (B * S) % world == 0 else ""),
             "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(B * S / prefill_ms * 1e3, 1),
             "decode_ms_per_step": round(step_ms, 3) if checks.get("graph_equals_eager") is not False else None,
@@ -1560,6 +1563,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seqlen", type=int, default=2048)
     ap.add_argument("--decode-steps", type=int, default=128)
+    ap.add_argument("--prefill-exchange", choices=("peer", "nccl"), default="peer",
+                    help="decoder suite on several GPUs: how the token-sharded prompt pass exchanges data")
     ap.add_argument("--fused-allreduce", action="store_true",
                     help="decoder suite, N>1: sum row-parallel partial outputs inside the decode GEMM over peer memory")
     ap.add_argument("--tune", action="append", default=[], metavar="NAME=VALUE",

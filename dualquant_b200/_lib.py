@@ -51,6 +51,14 @@ class AllReduceCtx(ctypes.Structure):
                 ("flag_units", ctypes.c_uint64)]
 
 
+class ExchangeCtx(ctypes.Structure):
+    """dq_exchange_ctx of the header."""
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("part_ptrs", ctypes.c_void_p * 8), ("codes_ptrs", ctypes.c_void_p * 8),
+                ("sx_ptrs", ctypes.c_void_p * 8), ("flag_ptrs", ctypes.c_void_p * 8),
+                ("tokens_per_rank", ctypes.c_int64), ("hidden", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
 SIGNATURES = {
     "dq_init": (_i, [_i]),
     "dq_last_error_string": (_c.c_char_p, []),
@@ -88,6 +96,10 @@ SIGNATURES = {
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),
     "dq_gemm_w4a4_int4_ar": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
     "dq_gemm_w4a4_int4_acc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "dq_gemm_w4a4_int4_e4m3_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "dq_exchange_barrier": (_i, [_vp, _c.c_uint32, _vp]),
+    "dq_exchange_sum": (_i, [_vp, _vp, _vp]),
+    "dq_exchange_push": (_i, [_vp, _vp, _vp, _vp]),
     "dq_linear_w4a4_int4_scratch_bytes": (_sz, [_i, _i, _i]),
     "dq_linear_w4a4_int4_prefill_scratch_bytes": (_sz, [_i, _i, _i]),
     "dq_linear_w4a4_int4": (_i, [_vp, _i64, _vp, _hp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _sz, _vp]),

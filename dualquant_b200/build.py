@@ -31,6 +31,7 @@ SOURCES = [
     "decoder_ops.cu",
     "gemm_w4a4_int4_f8.cu",
     "gemm_fp4_persist.cu",
+    "exchange.cu",
 ]
 
 NVCC_FLAGS = [

@@ -168,10 +168,18 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t* v) {
   else tmem_ld_x32(taddr, v);
 }
 
+// Destinations of the scatter output mode (OUT = 4): the partial-output buffer of every rank,
+// [world][tq][N] bf16, where slot `rank` of the owner of a tile's tokens receives the tile.
+struct ScatterDst {
+  unsigned short* part[8];
+  int rank, tq, rot;  // rot: token tiles are visited starting at tile `rot`, so that the ranks start on different owners
+};
+
 // OUT: how the output tile leaves - 0 direct stores (any shape, fp32 or bf16, optional residual),
 // 1 bf16 through shared memory and one tiled bulk store, 3 the same with the residual added, 2 fp32
-// through shared memory in two halves.  A template parameter: with all three epilogues in one kernel the K loop's
-// code ran 20-25 % slower.
+// through shared memory in two halves, 4 bf16 through shared memory and then 16-byte stores into the partial
+// buffer of the rank that owns the tile's tokens (peer memory; tensor-parallel prompt pass).  A template
+// parameter: with all three epilogues in one kernel the K loop's code ran 20-25 % slower.
 template <int EW, int CH, int NB, bool REBAL, int OUT>
 __global__ void __launch_bounds__(Shape<EW, CH, NB, REBAL>::kThreads, 1)
 gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
@@ -179,9 +187,9 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
                       const __half* __restrict__ sw_t, const float* __restrict__ r,
                       const float* __restrict__ sx, void* __restrict__ y, int y_bf16,
                       const void* __restrict__ residual, int M, int N, int K, int row_tiles, int tok_tiles,
-                      int tok_block, int* status) {
+                      int tok_block, int* status, const __grid_constant__ ScatterDst sc) {
   using S = Shape<EW, CH, NB, REBAL>;
-  constexpr int bulk_out = (OUT == 3) ? 1 : OUT;
+  constexpr int bulk_out = (OUT == 3) ? 1 : OUT;  // non-zero: the tile is staged in shared memory
   constexpr int kEpiWarps = S::kEpiWarps, kProducerWarp = S::kProducerWarp, kIssuerWarp = S::kIssuerWarp;
   constexpr int kCPW = S::kCPW, kCH = S::kCH, kNB = S::kNB;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -219,6 +227,10 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     const int width = (tok_tiles - b * tok_block < tok_block) ? (tok_tiles - b * tok_block) : tok_block;
     row = rem / width;
     tok = b * tok_block + (rem - row * width);
+    if constexpr (OUT == 4) {
+      tok += sc.rot;
+      if (tok >= tok_tiles) tok -= tok_tiles;
+    }
   };
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
@@ -238,7 +250,7 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
-    if (bulk_out) tma_prefetch_desc(&tm_y);
+    if (bulk_out && OUT != 4) tma_prefetch_desc(&tm_y);
     if (OUT == 3) tma_prefetch_desc(&tm_res);
   }
   grid_dep_launch_dependents();
@@ -320,7 +332,39 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
       if (!ok) break;
-      if constexpr (OUT == 1 || OUT == 3) {
+      if constexpr (OUT == 4) {
+        // Y tile -> shared memory as [token][row] bf16, then every warp sends 32 tokens: 256 bytes per
+        // token (16 lanes x 16 bytes) into slot sc.rank of the owner's partial buffer.  The host
+        // guarantees whole tiles (N % 128 == 0, M % 256 == 0) and tiles that do not straddle owners.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(out_free);  // this warp has read its share of the previous tile
+        if (!mbar_wait(out_free, it & 1, abort_flag, FSITE_OUT)) break;
+        const float rn = (r != nullptr) ? r[n] : 1.f;
+        const float4* sx4 = reinterpret_cast<const float4*>(sx_sm + (it & 1) * kTN + h * kCPW);
+        unsigned short* dst = out_sm + (h * kCPW) * kBN + q * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < kCPW; j += 4) {
+          const float4 sv = sx4[j >> 2];
+          dst[(j + 0) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 0] * (rn * sv.x)));
+          dst[(j + 1) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 1] * (rn * sv.y)));
+          dst[(j + 2) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 2] * (rn * sv.z)));
+          dst[(j + 3) * kBN] = __bfloat16_as_ushort(__float2bfloat16_rn(run[j + 3] * (rn * sv.w)));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(out_ready);
+        if (!mbar_wait(out_ready, it & 1, abort_flag, FSITE_OUT)) break;
+        const int owner = t0 / sc.tq;
+        unsigned short* base = sc.part[owner] +
+                               (static_cast<size_t>(sc.rank) * sc.tq + (t0 - owner * sc.tq)) * static_cast<size_t>(N) +
+                               row_tile * kBN;
+        constexpr int kTokPerWarp = kTN / kEpiWarps;
+#pragma unroll 4
+        for (int u = 0; u < kTokPerWarp / 2; ++u) {
+          const int tok = warp * kTokPerWarp + 2 * u + (lane >> 4);
+          const uint4 v16 = *reinterpret_cast<const uint4*>(out_sm + tok * kBN + (lane & 15) * 8);
+          *reinterpret_cast<uint4*>(base + static_cast<size_t>(tok) * N + (lane & 15) * 8) = v16;
+        }
+      } else if constexpr (OUT == 1 || OUT == 3) {
         // Y tile -> shared memory as [token][row] bf16 (a warp's 32 rows of one token are 64
         // contiguous bytes), then one tiled bulk store; rows past N and tokens past M are clipped
         // by the copy.  With a residual, its tile was copied into the same buffer during the K loop.  Two-byte global stores from here would cost more than two groups' UMMAs.
@@ -429,7 +473,8 @@ gemm_w4a4_e4m3_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         }
       }
     }
-    if (bulk_out && lane == 0 && (warp == 0 || warp == 4)) bulk_wait_group_read0();
+    if constexpr (OUT == 4) __threadfence_system();  // this thread's stores to peers are performed before the kernel ends
+    if (bulk_out && OUT != 4 && lane == 0 && (warp == 0 || warp == 4)) bulk_wait_group_read0();
   } else {
     if constexpr (REBAL) setmaxnreg_dec<S::kAuxRegs>();
     if (warp == kProducerWarp) {
@@ -504,15 +549,17 @@ int init_gemm_int4_f8_kernels() {
     e = cudaFuncSetAttribute(f8::Kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(f8::Kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(f8::Kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, f8::kSmemBytes);
   if (e != cudaSuccess)
     return set_error(DQ_ERR_CUDA, "cudaFuncSetAttribute(gemm_w4a4_e4m3) failed: %s", cudaGetErrorString(e));
   return DQ_OK;
 }
 
 // w8 / x8: E4M3 bytes, row-major [N, K] / [M, K]
-int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t, const float* r,
-                          int M, int N, int K, void* y, int y_dtype, const void* residual, cudaStream_t stream,
-                          DeviceState* st) {
+static int launch_gemm_int4_e4m3_impl(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t,
+                                      const float* r, int M, int N, int K, void* y, int y_dtype, const void* residual,
+                                      cudaStream_t stream, DeviceState* st, const f8::ScatterDst* scatter) {
   CUtensorMap tm_w, tm_x;
   int rc = make_tmap_2d_u8(&tm_w, w8, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K),
                            128, f8::kBN, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -534,7 +581,11 @@ int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8,
   // bf16 output (optionally with a residual) and fp32 output without one leave through tiled bulk
   // stores (16-byte aligned rows); anything else is stored directly
   int bulk_out = 0;
-  if (yb && N % 8 == 0 && aligned(y, 16) && (residual == nullptr || aligned(residual, 16))) bulk_out = 1;
+  f8::ScatterDst sc;
+  memset(&sc, 0, sizeof(sc));
+  if (scatter != nullptr) sc = *scatter;
+  if (scatter != nullptr) bulk_out = 4;
+  else if (yb && N % 8 == 0 && aligned(y, 16) && (residual == nullptr || aligned(residual, 16))) bulk_out = 1;
   else if (!yb && residual == nullptr && N % 4 == 0 && aligned(y, 16)) bulk_out = 2;
   CUtensorMap tm_y, tm_res;
   memset(&tm_y, 0, sizeof(tm_y));
@@ -553,8 +604,9 @@ int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8,
   cudaError_t e;
 #define DQ_F8_LAUNCH(OUTV)                                                                                          \
   e = launch_pdl(f8::Kernel<OUTV>, dim3(grid), dim3(f8::KernelShape::kThreads), f8::kSmemBytes, stream, tm_w, tm_x, \
-                 tm_y, tm_res, sw, r, sx, y, yb, residual, M, N, K, row_tiles, tok_tiles, tok_block, st->status_dev)
-  if (bulk_out == 1 && residual != nullptr) DQ_F8_LAUNCH(3);
+                 tm_y, tm_res, sw, r, sx, y, yb, residual, M, N, K, row_tiles, tok_tiles, tok_block, st->status_dev, sc)
+  if (bulk_out == 4) DQ_F8_LAUNCH(4);
+  else if (bulk_out == 1 && residual != nullptr) DQ_F8_LAUNCH(3);
   else if (bulk_out == 1) DQ_F8_LAUNCH(1);
   else if (bulk_out == 2) DQ_F8_LAUNCH(2);
   else DQ_F8_LAUNCH(0);
@@ -563,9 +615,45 @@ int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8,
   return DQ_OK;
 }
 
+int launch_gemm_int4_e4m3(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t, const float* r,
+                          int M, int N, int K, void* y, int y_dtype, const void* residual, cudaStream_t stream,
+                          DeviceState* st) {
+  return launch_gemm_int4_e4m3_impl(x8, sx, w8, sw_t, r, M, N, K, y, y_dtype, residual, stream, st, nullptr);
+}
+
 }  // namespace dq
 
 using namespace dq;
+
+extern "C" int dq_gemm_w4a4_int4_e4m3_scatter(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t,
+                                              const float* r, int M, int N, int K, int G, const dq_exchange_ctx* ctx,
+                                              void* stream) {
+  DeviceState* st = current_state();
+  if (st == nullptr) return DQ_ERR_NOT_INIT;
+  DQ_REQUIRE(x8 != nullptr && sx != nullptr && w8 != nullptr && sw_t != nullptr && ctx != nullptr, DQ_ERR_NULL,
+             "null x8 / sx / w8 / sw_t / ctx");
+  DQ_REQUIRE(G == kGroup, DQ_ERR_UNSUPPORTED, "weight group size must be %d (got %d)", kGroup, G);
+  DQ_REQUIRE(ctx->world >= 1 && ctx->world <= 8 && ctx->rank >= 0 && ctx->rank < ctx->world, DQ_ERR_SHAPE,
+             "bad exchange context (world %d, rank %d)", ctx->world, ctx->rank);
+  DQ_REQUIRE(K >= kGroup && K % kGroup == 0 && N == ctx->hidden && N % f8::kBN == 0 &&
+                 ctx->tokens_per_rank % f8::kTN == 0 && static_cast<int64_t>(M) == ctx->world * ctx->tokens_per_rank,
+             DQ_ERR_SHAPE, "scatter GEMM needs N == hidden (%d), N %% 128 == 0, tokens_per_rank %% 256 == 0 and "
+             "M == world * tokens_per_rank (M=%d N=%d K=%d tokens_per_rank=%lld)", ctx->hidden, M, N, K,
+             static_cast<long long>(ctx->tokens_per_rank));
+  DQ_REQUIRE(aligned(x8, 16) && aligned(w8, 16), DQ_ERR_ALIGN, "x8 and w8 must be 16-byte aligned");
+  f8::ScatterDst sc;
+  memset(&sc, 0, sizeof(sc));
+  for (int p = 0; p < ctx->world; ++p) {
+    DQ_REQUIRE(ctx->part_ptrs[p] != nullptr && aligned(ctx->part_ptrs[p], 16), DQ_ERR_ALIGN,
+               "partial buffer of rank %d is null or not 16-byte aligned", p);
+    sc.part[p] = static_cast<unsigned short*>(ctx->part_ptrs[p]);
+  }
+  sc.rank = ctx->rank;
+  sc.tq = static_cast<int>(ctx->tokens_per_rank);
+  sc.rot = static_cast<int>(((ctx->rank + 1) % ctx->world) * (ctx->tokens_per_rank / f8::kTN));
+  return launch_gemm_int4_e4m3_impl(x8, sx, w8, sw_t, r, M, N, K, nullptr, DQ_DTYPE_BF16, nullptr,
+                                    static_cast<cudaStream_t>(stream), st, &sc);
+}
 
 extern "C" int dq_expand_w_int4_e4m3(const uint8_t* w_packed, int N, int K, int G, uint8_t* w8, void* stream) {
   DeviceState* st = current_state();

@@ -218,14 +218,19 @@ class DecoderLayer:
         attn = attn.transpose(1, 2).reshape(B * S, self.hq * hd)
         return self._after_attention(x, attn, group, ar)
 
-    def forward_token_sharded(self, x, B: int, S: int, group, rope_tabs, codes, sx):
+    def forward_token_sharded(self, x, B: int, S: int, group, rope_tabs, codes, sx, xc=None):
         """Prompt pass under tensor parallelism with the residual stream sharded over tokens: x is
         this rank's [B * S / tp, hidden] slice (ranks own consecutive blocks of tokens).  RMSNorm
         and the activation quantiser run on the slice, the codes (one byte per element) and token
         scales are all-gathered into `codes` [B * S, hidden] / `sx` [B * S], the column-parallel
         linears and the attention of this rank's heads see every token, and the partial outputs of
         the row-parallel linears come back through a reduce-scatter.  Against all-reduce + replicated
-        norms: three quarters of the bytes on the wire and 1/tp of the element-wise work."""
+        norms: three quarters of the bytes on the wire and 1/tp of the element-wise work.
+        xc: an ops.ExchangeContext -> the exchange runs over peer memory instead of NCCL: the
+        row-parallel GEMMs push their output tiles into the owners' partial buffers from their
+        epilogues, the owners add them onto x (in place) and push their codes to every rank."""
+        if xc is not None:
+            return self._forward_token_sharded_peer(x, B, S, rope_tabs, xc)
         cfg = self.cfg
         Tq, Hd = x.shape
         T = B * S
@@ -251,6 +256,32 @@ class DecoderLayer:
         dist.reduce_scatter_tensor(d_sh, d, group=group)
         return x + d_sh
 
+    def _forward_token_sharded_peer(self, x, B: int, S: int, rope_tabs, xc):
+        cfg = self.cfg
+        T = B * S
+        c_sh, s_sh = ops.quant_act_int4_rmsnorm(x, self.ln1, cfg.rms_norm_eps, self.qkv.a, False, e4m3=True)
+        xc.push(c_sh, s_sh)
+        xc.barrier()  # every rank's codes have landed here
+        qkv = self.qkv._gemm(xc.codes, xc.sx)
+        q = ops.rope_kv_append(qkv, rope_tabs[0], rope_tabs[1], 0, self.hq, self.hkv, self.k_cache, self.v_cache, S)
+        attn = F.scaled_dot_product_attention(q, self.k_cache[:, :, :S], self.v_cache[:, :, :S], is_causal=True,
+                                              enable_gqa=True)
+        attn = attn.transpose(1, 2).reshape(T, self.hq * cfg.head_dim)
+        c_o, s_o = ops.quant_act_int4(attn, self.o.a, self.o.had, False, e4m3=True)
+        ops.gemm_w4a4_int4_e4m3_scatter(c_o, s_o, self.o.pw.bytes_e4m3(), self.o.pw, self.o.r, xc)
+        xc.barrier()  # every rank's partial rows for this rank's tokens have landed
+        xc.add_partials(x)
+        c_sh, s_sh = ops.quant_act_int4_rmsnorm(x, self.ln2, cfg.rms_norm_eps, self.gate_up.a, False, e4m3=True)
+        xc.push(c_sh, s_sh)
+        xc.barrier()
+        gu = self.gate_up._gemm(xc.codes, xc.sx)
+        c_d, s_d = ops.quant_act_int4_gated(gu[:, : self.inter], gu[:, self.inter :], self.down.a, self.down.had,
+                                            False, e4m3=True)
+        ops.gemm_w4a4_int4_e4m3_scatter(c_d, s_d, self.down.pw.bytes_e4m3(), self.down.pw, self.down.r, xc)
+        xc.barrier()
+        xc.add_partials(x)
+        return x
+
     def _after_attention(self, x, attn, group, ar):
         """o_proj, residual, MLP, residual."""
         cfg = self.cfg
@@ -275,14 +306,21 @@ class DecoderLayer:
 
 class Decoder:
     def __init__(self, cfg: DecoderConfig, device, tp: int = 1, rank: int = 0, seed: int = 0, group=None,
-                 fused_allreduce: bool = False, keep_codes: bool = False, token_sharded_prefill: bool = True):
+                 fused_allreduce: bool = False, keep_codes: bool = False, token_sharded_prefill: bool = True,
+                 prefill_exchange: str = "peer"):
         """fused_allreduce: decode steps sum the row-parallel linears' partial outputs inside the
         GEMM kernel over NVLink peer memory instead of calling NCCL (prefill keeps NCCL).
         token_sharded_prefill: with tp > 1, prompts whose token count divides by tp keep the residual
-        stream sharded over tokens (reduce-scatter / all-gather of codes) instead of all-reducing it."""
+        stream sharded over tokens (reduce-scatter / all-gather of codes) instead of all-reducing it.
+        prefill_exchange: "peer" - that exchange runs in this library's kernels over NVLink peer memory
+        (needs tokens / tp a multiple of 256 and at least 512 tokens, else NCCL carries it); "nccl"."""
+        if prefill_exchange not in ("peer", "nccl"):
+            raise ValueError("prefill_exchange must be 'peer' or 'nccl'")
         assert cfg.num_key_value_heads % tp == 0 and cfg.intermediate_size % (tp * 128) == 0
         self.cfg, self.tp, self.rank, self.group, self.device = cfg, tp, rank, group, device
         self.token_sharded_prefill = token_sharded_prefill
+        self.prefill_exchange = prefill_exchange
+        self._exchange = {}
         self.ar = None
         if fused_allreduce and tp > 1:
             self.ar = ops.AllReduceContext(group if group is not None else dist.group.WORLD, device,
@@ -321,10 +359,20 @@ class Decoder:
         lo = self.rank * Tq
         x = self.embed[ids.reshape(-1)[lo : lo + Tq]]
         e4m3 = T >= W4A4Linear.PREFILL_TOKENS
-        codes = torch.empty(T, Hd, dtype=torch.uint8 if e4m3 else torch.int8, device=self.device)
-        sx = torch.empty(T, dtype=torch.float32, device=self.device)
+        xc = None
+        if self.prefill_exchange == "peer" and e4m3 and Tq % 256 == 0 and Hd % 128 == 0:
+            xc = self._exchange.get(Tq)
+            if xc is None:  # collective: every rank reaches this with the same Tq
+                xc = self._exchange[Tq] = ops.ExchangeContext(
+                    self.group if self.group is not None else dist.group.WORLD, self.device, Tq, Hd)
+            codes = sx = None
+        else:
+            codes = torch.empty(T, Hd, dtype=torch.uint8 if e4m3 else torch.int8, device=self.device)
+            sx = torch.empty(T, dtype=torch.float32, device=self.device)
         for layer in self.layers:
-            x = layer.forward_token_sharded(x, B, S, self.group, (self.cos, self.sin), codes, sx)
+            x = layer.forward_token_sharded(x, B, S, self.group, (self.cos, self.sin), codes, sx, xc)
+        if xc is not None:
+            _lib.device_status(self.device.index)  # a barrier that gave up must not pass as a result
         # the last position of every sequence lives on exactly one rank: the others contribute zeros
         last = torch.zeros(B, Hd, dtype=torch.bfloat16, device=self.device)
         mine = [b for b in range(B) if lo <= b * S + S - 1 < lo + Tq]

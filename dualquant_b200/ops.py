@@ -383,6 +383,89 @@ def gemm_w4a4_int4_ar(codes: torch.Tensor, sx: torch.Tensor, pw: PackedInt4Weigh
     return out
 
 
+class ExchangeContext:
+    """Peer-mapped buffers of the token-sharded prompt pass under tensor parallelism (one allocation
+    per rank in torch symmetric memory, every rank maps all of them): partial outputs
+    [world][tokens_per_rank][hidden] bf16, gathered activation codes [world * tokens_per_rank][hidden]
+    bytes, gathered token scales, barrier words.  Built collectively; afterwards all ranks must issue
+    the same sequence of exchange calls (the barrier epoch is counted on the host)."""
+
+    def __init__(self, group, device, tokens_per_rank: int, hidden: int):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the exchange covers one NVLink domain of at most 8 ranks")
+        if tokens_per_rank % 256 or hidden % 128:
+            raise ValueError("tokens_per_rank must be a multiple of 256 and hidden a multiple of 128")
+        self.tokens_per_rank, self.hidden = int(tokens_per_rank), int(hidden)
+        T = self.world * self.tokens_per_rank
+        part_b = T * hidden * 2
+        codes_b = T * hidden
+        sx_b = (T * 4 + 255) // 256 * 256
+        total = part_b + codes_b + sx_b + 256
+        self._mem = symm.empty(total, dtype=torch.uint8, device=device)
+        self._mem[part_b + codes_b + sx_b:].zero_()
+        self._handle = symm.rendezvous(self._mem, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group, device_ids=[device.index])  # every rank's barrier words are zero from here on
+        ctx = _lib.ExchangeCtx()
+        ctx.world, ctx.rank = self.world, self.rank
+        for p in range(self.world):
+            base = int(self._handle.buffer_ptrs[p])
+            ctx.part_ptrs[p] = base
+            ctx.codes_ptrs[p] = base + part_b
+            ctx.sx_ptrs[p] = base + part_b + codes_b
+            ctx.flag_ptrs[p] = base + part_b + codes_b + sx_b
+        ctx.tokens_per_rank, ctx.hidden = self.tokens_per_rank, self.hidden
+        self._ctx = ctx
+        self._ref = ctypes.byref(ctx)
+        self.epoch = 0
+        # this rank's views of its own buffers
+        self.part = self._mem[:part_b].view(torch.bfloat16).view(self.world, self.tokens_per_rank, hidden)
+        self.codes = self._mem[part_b:part_b + codes_b].view(T, hidden)
+        self.sx = self._mem[part_b + codes_b:part_b + codes_b + T * 4].view(torch.float32)
+
+    def barrier(self):
+        """Device-side barrier across the ranks on the current stream (bounded wait)."""
+        lib = _prep(self._mem)
+        self.epoch += 1
+        _lib.check(lib.dq_exchange_barrier(self._ref, self.epoch, _stream(self._mem.device)), "dq_exchange_barrier")
+
+    def add_partials(self, x: torch.Tensor):
+        """x [tokens_per_rank, hidden] bf16 += the ranks' partial rows for this rank's tokens."""
+        lib = _prep(x)
+        if x.dtype != torch.bfloat16 or tuple(x.shape) != (self.tokens_per_rank, self.hidden) or not x.is_contiguous():
+            raise ValueError("x must be a contiguous bf16 [tokens_per_rank, hidden] tensor")
+        _lib.check(lib.dq_exchange_sum(self._ref, _ptr(x), _stream(x.device)), "dq_exchange_sum")
+
+    def push(self, codes: torch.Tensor, sx: torch.Tensor):
+        """This rank's codes [tokens_per_rank, hidden] (E4M3 bytes) and token scales into every rank's
+        gathered buffers."""
+        lib = _prep(codes)
+        if (codes.dtype != torch.uint8 or tuple(codes.shape) != (self.tokens_per_rank, self.hidden)
+                or not codes.is_contiguous() or sx.dtype != torch.float32 or sx.numel() != self.tokens_per_rank):
+            raise ValueError("codes must be uint8 [tokens_per_rank, hidden], sx fp32 [tokens_per_rank]")
+        _lib.check(lib.dq_exchange_push(self._ref, _ptr(codes), _ptr(sx), _stream(codes.device)), "dq_exchange_push")
+
+
+def gemm_w4a4_int4_e4m3_scatter(x8: torch.Tensor, sx: torch.Tensor, w8: torch.Tensor, pw: PackedInt4Weight,
+                                r: Optional[torch.Tensor], ctx: ExchangeContext) -> None:
+    """Row-parallel int4 GEMM of the token-sharded prompt pass: this rank's K slice; the bf16 output
+    tiles go from the kernel's epilogue into the partial buffer of the rank that owns the tokens."""
+    lib = _prep(x8)
+    M, K = x8.shape
+    if K != pw.K or tuple(w8.shape) != (pw.N, pw.K) or not x8.is_contiguous() or not w8.is_contiguous():
+        raise ValueError("x8 [M, K] and w8 [N, K] must be contiguous and match the packed weight")
+    _lib.check(lib.dq_gemm_w4a4_int4_e4m3_scatter(_ptr(x8), _ptr(sx), _ptr(w8), _ptr(pw.sw_t), _ptr(r), M, pw.N, K,
+                                                  pw.group, ctx._ref, _stream(x8.device)),
+               "dq_gemm_w4a4_int4_e4m3_scatter")
+
+
 def gemm_w4a4_int4_acc(codes: torch.Tensor, pw: PackedInt4Weight) -> torch.Tensor:
     """Test hook: raw per-group int32 accumulators [M, N, K/G]."""
     lib = _prep(codes)

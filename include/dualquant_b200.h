@@ -380,6 +380,54 @@ DQ_API int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const uint
                                 const void* sw_t, const float* r, int M, int N, int K, int G,
                                 void* y, int y_dtype, void* stream, const dq_allreduce_ctx* ctx);
 
+/*
+ * Peer-memory context of the token-sharded prompt pass under tensor parallelism (host struct; every
+ * pointer is a device pointer valid in THIS process: rank p's buffers mapped here).  Rank p owns
+ * the tokens [p * tokens_per_rank, (p + 1) * tokens_per_rank) of the residual stream.
+ *   part_ptrs[p]:  [world][tokens_per_rank][hidden] bf16 - slot s receives rank s's partial output
+ *                  rows for rank p's tokens
+ *   codes_ptrs[p]: [world * tokens_per_rank][hidden] bytes - the gathered activation codes
+ *   sx_ptrs[p]:    [world * tokens_per_rank] fp32 - the gathered token scales
+ *   flag_ptrs[p]:  8 uint32 barrier words, zero-initialised once
+ * Replaces the all-reduce after a Megatron row-parallel linear plus the replicated norm in front of
+ * the next column-parallel one; the reference has no multi-GPU code.
+ */
+typedef struct dq_exchange_ctx {
+  int32_t world, rank;
+  void* part_ptrs[8];
+  void* codes_ptrs[8];
+  void* sx_ptrs[8];
+  void* flag_ptrs[8];
+  int64_t tokens_per_rank;
+  int32_t hidden;
+  int32_t reserved;
+} dq_exchange_ctx;
+
+/*
+ * Row-parallel int4 linear of the token-sharded prompt pass: dq_gemm_w4a4_int4_e4m3 whose bf16
+ * output tiles [256 tokens x 128 rows] go, from the kernel's epilogue and while the other tiles
+ * compute, into slot ctx->rank of the partial buffer of the rank that owns the tokens (plain
+ * 16-byte stores to peer memory).  Needs N == ctx->hidden, N % 128 == 0,
+ * M == world * tokens_per_rank and tokens_per_rank % 256 == 0.  Follow with dq_exchange_barrier,
+ * then dq_exchange_sum.
+ */
+DQ_API int dq_gemm_w4a4_int4_e4m3_scatter(const uint8_t* x8, const float* sx, const uint8_t* w8, const void* sw_t,
+                                          const float* r, int M, int N, int K, int G, const dq_exchange_ctx* ctx,
+                                          void* stream);
+/*
+ * Barrier across the ranks of ctx on the device: publishes everything this rank's stream has
+ * completed, then waits for every peer's word of the same epoch.  epoch: a counter the host
+ * increments identically on all ranks (first call 1).  The wait is bounded (2^34 SM cycles, about
+ * nine seconds; dq_set_tuning("ar_wait_log2", n) changes it): on expiry the kernel records site 24 in
+ * the device status word and returns, and while the word is set later barriers do not wait.
+ */
+DQ_API int dq_exchange_barrier(const dq_exchange_ctx* ctx, uint32_t epoch, void* stream);
+/* x [tokens_per_rank, hidden] bf16 += bf16(sum over ranks, in rank order, of this rank's partial slots). */
+DQ_API int dq_exchange_sum(const dq_exchange_ctx* ctx, void* x_bf16, void* stream);
+/* This rank's codes [tokens_per_rank, hidden] bytes and token scales [tokens_per_rank] into its slice of
+ * every rank's gathered buffers (its own included). */
+DQ_API int dq_exchange_push(const dq_exchange_ctx* ctx, const void* codes, const float* sx, void* stream);
+
 /* Test hook: the raw per-group int32 accumulators acc[M, N, K/G] (no scales applied). */
 DQ_API int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packed, int M, int N, int K,
                           int G, int32_t* acc, void* stream);

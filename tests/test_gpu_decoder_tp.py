@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.gpu
-def test_token_sharded_prefill_equals_allreduce_prefill_two_ranks():
+def test_token_sharded_prefill_paths_equal_allreduce_prefill_two_ranks():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
