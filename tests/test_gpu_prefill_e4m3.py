@@ -150,3 +150,100 @@ def test_decoder_linear_rows_do_not_depend_on_the_batch_they_arrive_in():
                           (lin.gated(x[:h], x.flip(0)[:h].contiguous()), lin.gated(x[h:], x.flip(0)[h:].contiguous())))):
         assert torch.equal(whole, torch.cat(parts))
     _lib.device_status(0)
+
+
+# ------------------------------------------------------------------------------------------
+# the exchange kernels of the token-sharded prompt pass, one rank at a time on one GPU: every
+# "peer" buffer is a local array, and no kernel waits for another
+# ------------------------------------------------------------------------------------------
+def _exchange_ctx(world, rank, tq, hidden, part, codes, sx, flags):
+    ctx = _lib.ExchangeCtx()
+    ctx.world, ctx.rank = world, rank
+    for p in range(world):
+        ctx.part_ptrs[p] = part[p].data_ptr()
+        ctx.codes_ptrs[p] = codes[p].data_ptr()
+        ctx.sx_ptrs[p] = sx[p].data_ptr()
+        ctx.flag_ptrs[p] = flags[p].data_ptr()
+    ctx.tokens_per_rank, ctx.hidden = tq, hidden
+    return ctx
+
+
+@pytest.mark.parametrize("world,tq,N,K", [(1, 512, 256, 512), (2, 256, 128, 1024), (4, 256, 384, 256), (8, 512, 256, 128)])
+def test_scatter_gemm_puts_every_tile_into_its_owners_slot(world, tq, N, K):
+    """dq_gemm_w4a4_int4_e4m3_scatter as each rank in turn: slot `rank` of owner p's partial buffer
+    must hold rows [p * tq, (p + 1) * tq) of the plain GEMM's bf16 output, and nothing else moves."""
+    import ctypes
+
+    M = world * tq
+    codes_w, sw, pw = _weights(N, K, 11)
+    r, _ = synthetic.make_scales(N, K, 11)
+    x8, sx = ops.quant_act_int4(synthetic.make_x(M, K, 13).to(DEV), None, None, False, e4m3=True)
+    want = ops.gemm_w4a4_int4_e4m3(x8, sx, pw.bytes_e4m3(), pw, r.to(DEV), out_dtype=torch.bfloat16)
+    lib = _lib.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for rank in range(world):
+        part = torch.full((world, world, tq, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        codes = torch.zeros(world, M, N, dtype=torch.uint8, device=DEV)
+        sxg = torch.zeros(world, M, dtype=torch.float32, device=DEV)
+        flags = torch.zeros(world, 8, dtype=torch.int32, device=DEV)
+        ctx = _exchange_ctx(world, rank, tq, N, part, codes, sxg, flags)
+        rc = lib.dq_gemm_w4a4_int4_e4m3_scatter(ctypes.c_void_p(x8.data_ptr()), ctypes.c_void_p(sx.data_ptr()),
+                                                ctypes.c_void_p(pw.bytes_e4m3().data_ptr()),
+                                                ctypes.c_void_p(pw.sw_t.data_ptr()), ctypes.c_void_p(r.to(DEV).data_ptr()),
+                                                M, N, K, 128, ctypes.byref(ctx), stream)
+        assert rc == 0, _lib.last_error()
+        _lib.device_status(0)
+        for p in range(world):
+            assert torch.equal(part[p, rank], want[p * tq:(p + 1) * tq]), (rank, p)
+            others = [s for s in range(world) if s != rank]
+            assert bool((part[p, others] == 7.0).all())
+
+
+def test_scatter_gemm_rejects_shapes_it_cannot_tile():
+    import ctypes
+
+    codes_w, sw, pw = _weights(128, 128, 1)
+    x8, sx = ops.quant_act_int4(synthetic.make_x(300, 128, 1).to(DEV), None, None, False, e4m3=True)
+    part = torch.zeros(1, 1, 300, 128, dtype=torch.bfloat16, device=DEV)
+    dummy = torch.zeros(1, 300 * 128, dtype=torch.uint8, device=DEV)
+    ctx = _exchange_ctx(1, 0, 300, 128, part, dummy, torch.zeros(1, 300, device=DEV),
+                        torch.zeros(1, 8, dtype=torch.int32, device=DEV))
+    rc = _lib.load().dq_gemm_w4a4_int4_e4m3_scatter(
+        ctypes.c_void_p(x8.data_ptr()), ctypes.c_void_p(sx.data_ptr()), ctypes.c_void_p(pw.bytes_e4m3().data_ptr()),
+        ctypes.c_void_p(pw.sw_t.data_ptr()), None, 300, 128, 128, 128, ctypes.byref(ctx),
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc != 0 and "tokens_per_rank" in _lib.last_error()
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_exchange_sum_and_push(world):
+    """Owner side: x += bf16(rank-ordered fp32 sum of the partial slots); then the owner's codes and
+    token scales land in its slice of every rank's gathered buffers."""
+    import ctypes
+
+    tq, H = 256, 128
+    g = torch.Generator(device=DEV).manual_seed(world)
+    part = torch.randn(world, world, tq, H, generator=g, device=DEV).to(torch.bfloat16)
+    codes = torch.zeros(world, world * tq, H, dtype=torch.uint8, device=DEV)
+    sxg = torch.zeros(world, world * tq, dtype=torch.float32, device=DEV)
+    flags = torch.zeros(world, 8, dtype=torch.int32, device=DEV)
+    lib = _lib.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rank = world - 1
+    ctx = _exchange_ctx(world, rank, tq, H, part, codes, sxg, flags)
+    x = torch.randn(tq, H, generator=g, device=DEV).to(torch.bfloat16)
+    acc = part[rank, 0].float()
+    for p in range(1, world):
+        acc = acc + part[rank, p].float()
+    want = (x.float() + acc.to(torch.bfloat16).float()).to(torch.bfloat16)
+    assert lib.dq_exchange_sum(ctypes.byref(ctx), ctypes.c_void_p(x.data_ptr()), stream) == 0
+    assert torch.equal(x, want)
+    mine = torch.randint(0, 256, (tq, H), generator=g, device=DEV, dtype=torch.uint8)
+    smine = torch.rand(tq, generator=g, device=DEV)
+    assert lib.dq_exchange_push(ctypes.byref(ctx), ctypes.c_void_p(mine.data_ptr()), ctypes.c_void_p(smine.data_ptr()),
+                                stream) == 0
+    for p in range(world):
+        assert torch.equal(codes[p, rank * tq:(rank + 1) * tq], mine)
+        assert torch.equal(sxg[p, rank * tq:(rank + 1) * tq], smine)
+        assert int(codes[p].sum().item()) == int(mine.sum().item())  # nothing outside the slice
+    _lib.device_status(0)

@@ -61,3 +61,43 @@ def test_missing_peer_times_out_and_reports_site():
     qx, sxo, _ = O.quant_act_int4(x, None, None, False)
     ref = O.dequant_matmul(qx, sxo, *O.quant_w_int4(w))
     assert ((y2.double().cpu() - ref).abs().max() / ref.abs().max()) < 1e-5
+
+
+def test_exchange_barrier_without_peer_times_out_once():
+    """The device-side barrier of the token-sharded prompt pass, same construction: the "peer" of a
+    world-2 context is a local array nobody writes.  The first barrier gives up after the (lowered)
+    limit and records site 24; a second barrier issued while the word is still set does not wait
+    again; the status call reports and clears the word; nothing faults."""
+    T, H = 512, 128
+    part = torch.zeros(2, 2, T // 2, H, dtype=torch.bfloat16, device=DEV)
+    codes = torch.zeros(2, T, H, dtype=torch.uint8, device=DEV)
+    sx = torch.zeros(2, T, dtype=torch.float32, device=DEV)
+    flags = torch.zeros(2, 8, dtype=torch.int32, device=DEV)
+    ctx = _lib.ExchangeCtx()
+    ctx.world, ctx.rank = 2, 0
+    for p in range(2):
+        ctx.part_ptrs[p] = part[p].data_ptr()
+        ctx.codes_ptrs[p] = codes[p].data_ptr()
+        ctx.sx_ptrs[p] = sx[p].data_ptr()
+        ctx.flag_ptrs[p] = flags[p].data_ptr()
+    ctx.tokens_per_rank, ctx.hidden = T // 2, H
+    lib = _lib.load()
+    _lib.ensure_init(0)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.set_tuning("ar_wait_log2", 26)  # about 35 ms
+    try:
+        t0, t1, t2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        t0.record()
+        assert lib.dq_exchange_barrier(ctypes.byref(ctx), 1, stream) == 0
+        t1.record()
+        assert lib.dq_exchange_barrier(ctypes.byref(ctx), 2, stream) == 0
+        t2.record()
+        with pytest.raises(RuntimeError, match="DQ_ERR_TIMEOUT.*site 24"):
+            _lib.device_status(0)
+        first, second = t0.elapsed_time(t1), t1.elapsed_time(t2)
+        assert 5.0 < first < 2000.0      # waited, but not for long
+        assert second < first / 4        # the second barrier saw the word and returned at once
+    finally:
+        _lib.set_tuning("ar_wait_log2", 0)
+    assert int(flags[1, 0].item()) == 2  # this rank's word did reach the "peer" both times
+    _lib.device_status(0)                # cleared
