@@ -30,13 +30,15 @@ __device__ __forceinline__ void wht_segment_warp(float* seg, int lane, float pos
   float v[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) v[r] = seg[lane + 32 * r];
+  // the lane with bit m clear keeps a + b, its partner a - b: other + sign * own, one FMA either
+  // way (the product with +-1 is exact, so the FMA rounds exactly like the addition / subtraction)
 #pragma unroll
   for (int m = 1; m < 32; m <<= 1) {
-    const bool upper = (lane & m) != 0;
+    const float sign = (lane & m) != 0 ? -1.0f : 1.0f;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const float other = __shfl_xor_sync(0xffffffffu, v[r], m);
-      v[r] = upper ? __fsub_rn(other, v[r]) : __fadd_rn(v[r], other);
+      v[r] = __fmaf_rn(v[r], sign, other);
     }
   }
 #pragma unroll
@@ -436,13 +438,13 @@ act_quant_had_heads_kernel(const XT* __restrict__ x, int64_t ldx, const float* _
     }
   }
   if constexpr (S == 32) {  // heads j and j + 16 sit in lanes l and l + 16
-    const bool upper = sub >= 16;
+    const float sign = sub >= 16 ? -1.0f : 1.0f;  // a + b below, a - b above: other + sign * own, rounded once
 #pragma unroll
     for (int j = 0; j < HL; ++j) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const float other = __shfl_xor_sync(0xffffffffu, v[j][e], 16);
-        v[j][e] = upper ? __fsub_rn(other, v[j][e]) : __fadd_rn(v[j][e], other);
+        v[j][e] = __fmaf_rn(v[j][e], sign, other);
       }
     }
   }

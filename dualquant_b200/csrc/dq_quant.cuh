@@ -53,8 +53,10 @@ __device__ __forceinline__ void quant_codes8(const float* v, float s, float inv_
     const float t = __fmul_rn(v[e], inv_s);
     const float qe = __fsub_rn(__fadd_rn(t, kRoundMagic), kRoundMagic);
     const float dist = fabsf(fabsf(__fsub_rn(t, qe)) - 0.5f);
-    // the negated comparisons also catch NaN / inf (1/s overflowed for a denormal scale)
-    exact |= !(dist >= 1e-5f) || !(fabsf(t) <= 16.0f);
+    // the negated comparison also catches a NaN or infinite estimate (1/s overflowed for a denormal
+    // scale): t - qe is then NaN.  A finite estimate of any size rounds correctly above (beyond 2^22
+    // it is an integer already) and is clamped below.
+    exact |= !(dist >= 1e-5f);
     q[e] = fminf(fmaxf(qe, -8.0f), 7.0f);
   }
   if (exact) {
