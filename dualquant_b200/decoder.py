@@ -28,7 +28,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import _lib, ops, quarot, synthetic
+from . import _lib, ops, quarot, sharding, synthetic
 
 
 @dataclass
@@ -355,12 +355,12 @@ class Decoder:
         cfg = self.cfg
         B, S = ids.shape
         T, Hd = B * S, cfg.hidden_size
-        Tq = T // self.tp
-        lo = self.rank * Tq
-        x = self.embed[ids.reshape(-1)[lo : lo + Tq]]
+        lo, hi = sharding.token_shard(T, self.tp, self.rank)
+        Tq = hi - lo
+        x = self.embed[ids.reshape(-1)[lo:hi]]
         e4m3 = T >= W4A4Linear.PREFILL_TOKENS
         xc = None
-        if self.prefill_exchange == "peer" and e4m3 and Tq % 256 == 0 and Hd % 128 == 0:
+        if self.prefill_exchange == "peer" and sharding.peer_exchange_fits(T, self.tp, Hd, W4A4Linear.PREFILL_TOKENS):
             xc = self._exchange.get(Tq)
             if xc is None:  # collective: every rank reaches this with the same Tq
                 xc = self._exchange[Tq] = ops.ExchangeContext(
@@ -375,10 +375,10 @@ class Decoder:
             _lib.device_status(self.device.index)  # a barrier that gave up must not pass as a result
         # the last position of every sequence lives on exactly one rank: the others contribute zeros
         last = torch.zeros(B, Hd, dtype=torch.bfloat16, device=self.device)
-        mine = [b for b in range(B) if lo <= b * S + S - 1 < lo + Tq]
+        mine = sharding.last_token_rows(B, S, self.tp, self.rank)
         if mine:
-            rows = torch.tensor([b * S + S - 1 - lo for b in mine], device=self.device)
-            last[torch.tensor(mine, device=self.device)] = x[rows]
+            rows = torch.tensor([row for _, row in mine], device=self.device)
+            last[torch.tensor([b for b, _ in mine], device=self.device)] = x[rows]
         dist.all_reduce(last, group=self.group)
         return _rms_norm(last, self.norm, cfg.rms_norm_eps) @ self.lm_head.T
 
