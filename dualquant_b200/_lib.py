@@ -56,7 +56,8 @@ class ExchangeCtx(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32),
                 ("part_ptrs", ctypes.c_void_p * 8), ("codes_ptrs", ctypes.c_void_p * 8),
                 ("sx_ptrs", ctypes.c_void_p * 8), ("flag_ptrs", ctypes.c_void_p * 8),
-                ("tokens_per_rank", ctypes.c_int64), ("hidden", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+                ("tokens_per_rank", ctypes.c_int64), ("hidden", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("barrier_count", ctypes.c_void_p)]
 
 
 SIGNATURES = {

@@ -34,7 +34,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 struct BarrierArgs {
   uint32_t* flags[8];  // flags[p]: rank p's flag words, one per source rank
   int rank, world;
-  uint32_t epoch;
+  uint32_t epoch;      // 0: take the epoch from *counter (device-side count of this rank's barriers)
+  uint32_t* counter;   // this rank's own barrier count; advanced by the kernel when epoch == 0
   long long wait_cycles;
 };
 
@@ -44,14 +45,20 @@ struct BarrierArgs {
 // A wait that runs out records its site in the device status word and returns; once the word is
 // set (by this or any earlier kernel) later barriers do not wait at all, so a lost rank costs one
 // limit, not one per barrier.
+// With epoch == 0 the epoch is this rank's own barrier count + 1, kept in device memory and advanced
+// here: the ranks issue the same sequence of barriers, so their counts agree, and the launch carries
+// no per-call value - a captured graph that holds barriers can be replayed.
 __global__ void __launch_bounds__(32) exchange_barrier_kernel(BarrierArgs a, int* status) {
   const int p = threadIdx.x;
+  const uint32_t epoch = (a.epoch != 0) ? a.epoch : *a.counter + 1u;
+  __syncwarp();  // every lane has read the count before lane 0 advances it
+  if (a.epoch == 0 && p == 0) *a.counter = epoch;
   if (p >= a.world || p == a.rank) return;
   __threadfence_system();
-  st_release_sys_u32(a.flags[p] + a.rank, a.epoch);
+  st_release_sys_u32(a.flags[p] + a.rank, epoch);
   const uint32_t* mine = a.flags[a.rank] + p;
   const long long t_start = clock64();
-  while (static_cast<int32_t>(ld_acquire_sys_u32(mine) - a.epoch) < 0) {
+  while (static_cast<int32_t>(ld_acquire_sys_u32(mine) - epoch) < 0) {
     if (*reinterpret_cast<volatile int*>(status) != 0) return;
     if (clock64() - t_start > a.wait_cycles) {
       atomicCAS(status, 0, XSITE_BARRIER);
@@ -143,6 +150,8 @@ extern "C" int dq_exchange_barrier(const dq_exchange_ctx* ctx, uint32_t epoch, v
   a.rank = ctx->rank;
   a.world = ctx->world;
   a.epoch = epoch;
+  a.counter = static_cast<uint32_t*>(ctx->barrier_count);
+  DQ_REQUIRE(epoch != 0 || a.counter != nullptr, DQ_ERR_NULL, "epoch 0 needs ctx->barrier_count");
   const int wl = tuning(DQ_TUNE_AR_WAIT_LOG2);
   // default: about nine seconds - the ranks' hosts enqueue a prompt pass with seconds of skew the
   // first time (lazy library set-up), and a peer that is merely late must not be taken for lost

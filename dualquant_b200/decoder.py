@@ -342,25 +342,35 @@ class Decoder:
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [B, S] -> logits of the last position [B, vocab]."""
         B, S = ids.shape
-        if self.tp > 1 and self.token_sharded_prefill and (B * S) % self.tp == 0:
-            return self._prefill_token_sharded(ids)
-        x = self.embed[ids]
-        cos, sin = self.cos[:S], self.sin[:S]
-        for layer in self.layers:
-            x = layer.forward(x, cos, sin, 0, None, None, self.group, rope_tabs=(self.cos, self.sin))
-        x = _rms_norm(x[:, -1], self.norm, self.cfg.rms_norm_eps)
-        return x @ self.lm_head.T
+        return self._prefill_tail(self._prefill_body(ids), B, S)
 
-    def _prefill_token_sharded(self, ids: torch.Tensor) -> torch.Tensor:
+    def _token_sharded(self, B: int, S: int) -> bool:
+        return self.tp > 1 and self.token_sharded_prefill and (B * S) % self.tp == 0
+
+    def _peer_exchange(self, B: int, S: int) -> bool:
+        return (self._token_sharded(B, S) and self.prefill_exchange == "peer" and
+                sharding.peer_exchange_fits(B * S, self.tp, self.cfg.hidden_size, W4A4Linear.PREFILL_TOKENS))
+
+    def _prefill_body(self, ids: torch.Tensor) -> torch.Tensor:
+        """The decoder layers of a prompt pass: kernels on the current stream only - no host
+        synchronisation and, on one GPU or with the peer-memory exchange, no library collective - so
+        that it can be captured in a CUDA graph.  Returns the last positions' hidden states [B, hidden]
+        or, token-sharded, this rank's slice of the residual stream."""
         cfg = self.cfg
         B, S = ids.shape
+        if not self._token_sharded(B, S):
+            x = self.embed[ids]
+            cos, sin = self.cos[:S], self.sin[:S]
+            for layer in self.layers:
+                x = layer.forward(x, cos, sin, 0, None, None, self.group, rope_tabs=(self.cos, self.sin))
+            return x[:, -1]
         T, Hd = B * S, cfg.hidden_size
         lo, hi = sharding.token_shard(T, self.tp, self.rank)
         Tq = hi - lo
         x = self.embed[ids.reshape(-1)[lo:hi]]
         e4m3 = T >= W4A4Linear.PREFILL_TOKENS
         xc = None
-        if self.prefill_exchange == "peer" and sharding.peer_exchange_fits(T, self.tp, Hd, W4A4Linear.PREFILL_TOKENS):
+        if self._peer_exchange(B, S):
             xc = self._exchange.get(Tq)
             if xc is None:  # collective: every rank reaches this with the same Tq
                 xc = self._exchange[Tq] = ops.ExchangeContext(
@@ -371,16 +381,57 @@ class Decoder:
             sx = torch.empty(T, dtype=torch.float32, device=self.device)
         for layer in self.layers:
             x = layer.forward_token_sharded(x, B, S, self.group, (self.cos, self.sin), codes, sx, xc)
-        if xc is not None:
-            _lib.device_status(self.device.index)  # a barrier that gave up must not pass as a result
-        # the last position of every sequence lives on exactly one rank: the others contribute zeros
-        last = torch.zeros(B, Hd, dtype=torch.bfloat16, device=self.device)
-        mine = sharding.last_token_rows(B, S, self.tp, self.rank)
-        if mine:
-            rows = torch.tensor([row for _, row in mine], device=self.device)
-            last[torch.tensor([b for b, _ in mine], device=self.device)] = x[rows]
-        dist.all_reduce(last, group=self.group)
-        return _rms_norm(last, self.norm, cfg.rms_norm_eps) @ self.lm_head.T
+        return x
+
+    def _prefill_tail(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        """Final norm and output projection of the last positions (collected from their owners first
+        when the residual stream is token-sharded)."""
+        cfg = self.cfg
+        if self._token_sharded(B, S):
+            if self._peer_exchange(B, S):
+                _lib.device_status(self.device.index)  # a barrier that gave up must not pass as a result
+            # the last position of every sequence lives on exactly one rank: the others contribute zeros
+            last = torch.zeros(B, cfg.hidden_size, dtype=torch.bfloat16, device=self.device)
+            mine = sharding.last_token_rows(B, S, self.tp, self.rank)
+            if mine:
+                rows = torch.tensor([row for _, row in mine], device=self.device)
+                last[torch.tensor([b for b, _ in mine], device=self.device)] = x[rows]
+            dist.all_reduce(last, group=self.group)
+            x = last
+        return _rms_norm(x, self.norm, cfg.rms_norm_eps) @ self.lm_head.T
+
+    def capture_prefill(self, ids: torch.Tensor):
+        """The prompt pass for prompts of ids' shape as a CUDA graph (the reference's harness times its
+        prompt pass the same way, ablation/real_int4_kernel/graph_bench_all.py:72-92): returns
+        run(new_ids=None) -> logits, which copies new_ids into the captured input, replays the layers
+        and finishes with the eager tail.  Where the layers hold a library collective (tensor
+        parallelism over NCCL) nothing is captured and run() is the eager prefill.  With the
+        peer-memory exchange all ranks must capture and replay together."""
+        B, S = ids.shape
+        if self.tp > 1 and not self._peer_exchange(B, S):
+            return lambda new_ids=None: self.prefill(ids if new_ids is None else new_ids)
+        static_ids = ids.clone()
+        cur = torch.cuda.current_stream(self.device)
+        side = torch.cuda.Stream(device=self.device)
+        with torch.no_grad():
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):  # lazy set-up (byte forms of the weights, exchange buffers) happens here
+                self._prefill_body(static_ids)
+            cur.wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self._prefill_body(static_ids)
+
+        def run(new_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+            if new_ids is not None:
+                static_ids.copy_(new_ids)
+            graph.replay()
+            with torch.no_grad():
+                return self._prefill_tail(out, B, S)
+
+        run.graph = graph
+        return run
 
     def decode_step(self, ids: torch.Tensor, pos_t: torch.Tensor) -> torch.Tensor:
         """ids [B] (one token per sequence), pos_t: int64 device tensor [1] with the cache position.

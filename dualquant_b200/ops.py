@@ -388,7 +388,7 @@ class ExchangeContext:
     per rank in torch symmetric memory, every rank maps all of them): partial outputs
     [world][tokens_per_rank][hidden] bf16, gathered activation codes [world * tokens_per_rank][hidden]
     bytes, gathered token scales, barrier words.  Built collectively; afterwards all ranks must issue
-    the same sequence of exchange calls (the barrier epoch is counted on the host)."""
+    the same sequence of exchange calls (every rank counts its barriers on the device)."""
 
     def __init__(self, group, device, tokens_per_rank: int, hidden: int):
         import ctypes
@@ -422,19 +422,20 @@ class ExchangeContext:
             ctx.sx_ptrs[p] = base + part_b + codes_b
             ctx.flag_ptrs[p] = base + part_b + codes_b + sx_b
         ctx.tokens_per_rank, ctx.hidden = self.tokens_per_rank, self.hidden
+        self._count = torch.zeros(1, dtype=torch.int32, device=device)  # this rank's barriers so far
+        ctx.barrier_count = self._count.data_ptr()
         self._ctx = ctx
         self._ref = ctypes.byref(ctx)
-        self.epoch = 0
         # this rank's views of its own buffers
         self.part = self._mem[:part_b].view(torch.bfloat16).view(self.world, self.tokens_per_rank, hidden)
         self.codes = self._mem[part_b:part_b + codes_b].view(T, hidden)
         self.sx = self._mem[part_b + codes_b:part_b + codes_b + T * 4].view(torch.float32)
 
     def barrier(self):
-        """Device-side barrier across the ranks on the current stream (bounded wait)."""
+        """Device-side barrier across the ranks on the current stream (bounded wait).  The epoch is
+        counted on the device, so the call can sit in a captured CUDA graph."""
         lib = _prep(self._mem)
-        self.epoch += 1
-        _lib.check(lib.dq_exchange_barrier(self._ref, self.epoch, _stream(self._mem.device)), "dq_exchange_barrier")
+        _lib.check(lib.dq_exchange_barrier(self._ref, 0, _stream(self._mem.device)), "dq_exchange_barrier")
 
     def add_partials(self, x: torch.Tensor):
         """x [tokens_per_rank, hidden] bf16 += the ranks' partial rows for this rank's tokens."""

@@ -389,6 +389,8 @@ DQ_API int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const uint
  *   codes_ptrs[p]: [world * tokens_per_rank][hidden] bytes - the gathered activation codes
  *   sx_ptrs[p]:    [world * tokens_per_rank] fp32 - the gathered token scales
  *   flag_ptrs[p]:  8 uint32 barrier words, zero-initialised once
+ *   barrier_count: this rank's own uint32 count of barriers, zero-initialised once (device memory;
+ *                  may be NULL if every barrier call passes its epoch)
  * Replaces the all-reduce after a Megatron row-parallel linear plus the replicated norm in front of
  * the next column-parallel one; the reference has no multi-GPU code.
  */
@@ -401,6 +403,7 @@ typedef struct dq_exchange_ctx {
   int64_t tokens_per_rank;
   int32_t hidden;
   int32_t reserved;
+  void* barrier_count;
 } dq_exchange_ctx;
 
 /*
@@ -417,7 +420,9 @@ DQ_API int dq_gemm_w4a4_int4_e4m3_scatter(const uint8_t* x8, const float* sx, co
 /*
  * Barrier across the ranks of ctx on the device: publishes everything this rank's stream has
  * completed, then waits for every peer's word of the same epoch.  epoch: a counter the host
- * increments identically on all ranks (first call 1).  The wait is bounded (2^34 SM cycles, about
+ * increments identically on all ranks (first call 1), or 0 - the kernel then counts in
+ * ctx->barrier_count itself, which makes the call replayable inside a captured CUDA graph (do not
+ * mix the two forms on one context).  The wait is bounded (2^34 SM cycles, about
  * nine seconds; dq_set_tuning("ar_wait_log2", n) changes it): on expiry the kernel records site 24 in
  * the device status word and returns, and while the word is set later barriers do not wait.
  */

@@ -74,6 +74,16 @@ def main():
                 step = m.decode_step(tok, pos)
                 torch.cuda.synchronize(dev)
                 outs.append((logits.float(), step.float(), m.layers[-1].k_cache[:, :, :S].float()))
+        # the peer-memory pass replayed from a CUDA graph (barrier epochs counted on the device)
+        if models[2]._peer_exchange(B, S):
+            with torch.no_grad():
+                run = models[2].capture_prefill(ids)
+                for _ in range(2):
+                    logits_g = run().float()
+                    torch.cuda.synchronize(dev)
+                    if not hasattr(run, "graph") or not torch.equal(logits_g, outs[2][0]):
+                        failures.append(("captured peer pass", B, S, float((logits_g - outs[2][0]).abs().max())))
+
         def diffs(a, b):
             return tuple(float((x - y).abs().max()) for x, y in zip(a, b))
 

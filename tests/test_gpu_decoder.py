@@ -309,3 +309,26 @@ def test_prefill_with_fused_rope_matches_the_unfused_prefill():
     assert torch.equal(k0, model.layers[0].k_cache) and torch.equal(v0, model.layers[0].v_cache)
     cos_sim = torch.nn.functional.cosine_similarity(fused.flatten(), ref.flatten(), dim=0).item()
     assert cos_sim > 0.9
+
+
+def test_captured_prompt_pass_equals_the_eager_one():
+    """The layers of a prompt pass replayed from a CUDA graph (new ids copied into the captured
+    input) against the eagerly launched pass: same logits, same cache."""
+    cfg = _small_cfg()
+    model = _build(cfg)
+    B, S = 2, 48
+    model.alloc_cache(B, S + 4)
+    g = torch.Generator(device=DEV).manual_seed(9)
+    ids0 = torch.randint(0, cfg.vocab_size, (B, S), generator=g, device=DEV)
+    ids1 = torch.randint(0, cfg.vocab_size, (B, S), generator=g, device=DEV)
+    with torch.no_grad():
+        run = model.capture_prefill(ids0)
+        assert hasattr(run, "graph")
+        for ids in (ids0, ids1, ids0):
+            want = model.prefill(ids)
+            k_want = model.layers[-1].k_cache[:, :, :S].clone()
+            model.layers[-1].k_cache.zero_()
+            got = run(ids)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want)
+            assert torch.equal(model.layers[-1].k_cache[:, :, :S], k_want)

@@ -101,3 +101,16 @@ def test_exchange_barrier_without_peer_times_out_once():
         _lib.set_tuning("ar_wait_log2", 0)
     assert int(flags[1, 0].item()) == 2  # this rank's word did reach the "peer" both times
     _lib.device_status(0)                # cleared
+    # epoch 0: the kernel counts this rank's barriers itself (the form a captured graph can replay)
+    count = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ctx.barrier_count = count.data_ptr()
+    flags.zero_()
+    _lib.set_tuning("ar_wait_log2", 22)
+    try:
+        for _ in range(3):
+            assert lib.dq_exchange_barrier(ctypes.byref(ctx), 0, stream) == 0
+        with pytest.raises(RuntimeError, match="DQ_ERR_TIMEOUT.*site 24"):
+            _lib.device_status(0)
+    finally:
+        _lib.set_tuning("ar_wait_log2", 0)
+    assert int(count.item()) == 3 and int(flags[1, 0].item()) == 3
