@@ -96,6 +96,7 @@ SIGNATURES = {
     "dq_gemm_w4a4_int4_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "dq_gemm_w4a4_int4_ex": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _sz, _vp, _i, _i]),
     "dq_gemm_w4a4_int4_ar": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
+    "dq_gemm_w4a4_int4_ar_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp]),
     "dq_gemm_w4a4_int4_acc": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "dq_gemm_w4a4_int4_e4m3_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "dq_exchange_barrier": (_i, [_vp, _c.c_uint32, _vp]),

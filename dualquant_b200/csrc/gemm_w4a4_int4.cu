@@ -698,10 +698,22 @@ extern "C" int dq_gemm_w4a4_int4_acc(const int8_t* codes, const uint8_t* w_packe
                              acc, M <= 16 ? 16 : 128, 1, s, st);
 }
 
+extern "C" int dq_gemm_w4a4_int4_ar_residual(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                             const void* sw_t, const float* r, const void* residual, int M, int N,
+                                             int K, int G, void* y, int y_dtype, void* stream,
+                                             const dq_allreduce_ctx* ctx);
+
 extern "C" int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                                     const void* sw_t, const float* r, int M, int N, int K, int G,
                                     void* y, int y_dtype, void* stream,
                                     const dq_allreduce_ctx* ctx) {
+  return dq_gemm_w4a4_int4_ar_residual(codes, sx, w_packed, sw_t, r, nullptr, M, N, K, G, y, y_dtype, stream, ctx);
+}
+
+extern "C" int dq_gemm_w4a4_int4_ar_residual(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                             const void* sw_t, const float* r, const void* residual, int M, int N,
+                                             int K, int G, void* y, int y_dtype, void* stream,
+                                             const dq_allreduce_ctx* ctx) {
   DeviceState* st = current_state();
   if (st == nullptr) return DQ_ERR_NOT_INIT;
   if (M == 0) return DQ_OK;
@@ -713,5 +725,5 @@ extern "C" int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const 
   const int total_groups = K / kGroup;
   const int split = gemv_pick_split((N + kBN - 1) / kBN, total_groups, tok, st->sm_count);
   return launch_gemv_int4(codes, sx, w_packed, sw_t, r, M, N, K, y, y_dtype, tok, split,
-                          static_cast<cudaStream_t>(stream), st, ctx);
+                          static_cast<cudaStream_t>(stream), st, ctx, residual);
 }

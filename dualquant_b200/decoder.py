@@ -98,7 +98,7 @@ class W4A4Linear:
         residual: [M, N] bf16 -> returns residual + linear, the sum formed in the GEMM epilogue."""
         if ar is not None:
             codes, sx = ops.quant_act_int4(x, self.a, self.had, False)
-            return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
+            return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype, residual=residual)
         big = x.shape[0] >= self.PREFILL_TOKENS
         if residual is not None or big:
             codes, sx = ops.quant_act_int4(x, self.a, self.had, False, e4m3=big)
@@ -111,7 +111,7 @@ class W4A4Linear:
         big = ar is None and gate.shape[0] >= self.PREFILL_TOKENS
         codes, sx = ops.quant_act_int4_gated(gate, up, self.a, self.had, False, e4m3=big)
         if ar is not None:
-            return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype)
+            return ops.gemm_w4a4_int4_ar(codes, sx, self.pw, self.r, ar, out_dtype=out_dtype, residual=residual)
         return self._gemm(codes, sx, out_dtype, residual)
 
 
@@ -293,14 +293,19 @@ class DecoderLayer:
             gu = self.gate_up.normed(x.reshape(B * S, Hd), self.ln2, cfg.rms_norm_eps)
             return self.down.gated(gu[:, : self.inter], gu[:, self.inter :],
                                    residual=x.reshape(B * S, Hd)).reshape(B, S, Hd)
-        o = self.o(attn, ar=fused)
-        if fused is None:
-            dist.all_reduce(o, group=group)
+        if fused is not None:
+            # decode batch: the cross-rank sum and the residual addition both happen as the row-parallel
+            # GEMM stores its rows
+            x2 = self.o(attn, ar=fused, residual=x.reshape(B * S, Hd).contiguous())
+            gu = self.gate_up.normed(x2, self.ln2, cfg.rms_norm_eps)
+            return self.down.gated(gu[:, : self.inter], gu[:, self.inter :], ar=fused,
+                                   residual=x2).reshape(B, S, Hd)
+        o = self.o(attn)
+        dist.all_reduce(o, group=group)
         x = x + o.reshape(B, S, Hd)
         gu = self.gate_up.normed(x.reshape(B * S, Hd), self.ln2, cfg.rms_norm_eps)
-        d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :], ar=fused)
-        if fused is None:
-            dist.all_reduce(d, group=group)
+        d = self.down.gated(gu[:, : self.inter], gu[:, self.inter :])
+        dist.all_reduce(d, group=group)
         return x + d.reshape(B, S, Hd)
 
 

@@ -367,19 +367,23 @@ class AllReduceContext:
 
 def gemm_w4a4_int4_ar(codes: torch.Tensor, sx: torch.Tensor, pw: PackedInt4Weight,
                       r: Optional[torch.Tensor], ctx: AllReduceContext, out_dtype=torch.float32,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Row-parallel int4 GEMM of a decode batch (M <= 16): this rank's K slice, summed over the
-    ranks of `ctx` inside the kernel; every rank gets the full [M, N] result."""
+    ranks of `ctx` inside the kernel; every rank gets the full [M, N] result (+ residual [M, N] of
+    the output's dtype, added as the sum is stored)."""
     lib = _prep(codes)
     M, K = codes.shape
     if K != pw.K:
         raise ValueError(f"K mismatch: activations {K}, weight {pw.K}")
     if out is None:
-        out = torch.empty(M, pw.N, dtype=out_dtype, device=codes.device)
+        out = torch.empty(M, pw.N, dtype=residual.dtype if residual is not None else out_dtype, device=codes.device)
+    if residual is not None and (residual.dtype != out.dtype or tuple(residual.shape) != (M, pw.N)
+                                 or not residual.is_contiguous()):
+        raise ValueError("residual must be a contiguous [M, N] tensor of the output's dtype")
     ydt = _lib.DTYPE_BF16 if out.dtype == torch.bfloat16 else _lib.DTYPE_F32
-    _lib.check(lib.dq_gemm_w4a4_int4_ar(_ptr(codes), _ptr(sx), _ptr(pw.w_packed), _ptr(pw.sw_t), _ptr(r),
-                                        M, pw.N, K, pw.group, _ptr(out), ydt, _stream(codes.device),
-                                        ctx._ref), "dq_gemm_w4a4_int4_ar")
+    _lib.check(lib.dq_gemm_w4a4_int4_ar_residual(_ptr(codes), _ptr(sx), _ptr(pw.w_packed), _ptr(pw.sw_t), _ptr(r),
+                                                 _ptr(residual), M, pw.N, K, pw.group, _ptr(out), ydt,
+                                                 _stream(codes.device), ctx._ref), "dq_gemm_w4a4_int4_ar_residual")
     return out
 
 

@@ -379,6 +379,12 @@ typedef struct dq_allreduce_ctx {
 DQ_API int dq_gemm_w4a4_int4_ar(const int8_t* codes, const float* sx, const uint8_t* w_packed,
                                 const void* sw_t, const float* r, int M, int N, int K, int G,
                                 void* y, int y_dtype, void* stream, const dq_allreduce_ctx* ctx);
+/* The same with the decoder's residual connection added to the cross-rank sum as it is stored:
+ * Y = residual + sum over ranks (residual [M, N] in y's dtype, may alias y; NULL = none). */
+DQ_API int dq_gemm_w4a4_int4_ar_residual(const int8_t* codes, const float* sx, const uint8_t* w_packed,
+                                         const void* sw_t, const float* r, const void* residual, int M, int N,
+                                         int K, int G, void* y, int y_dtype, void* stream,
+                                         const dq_allreduce_ctx* ctx);
 
 /*
  * Peer-memory context of the token-sharded prompt pass under tensor parallelism (host struct; every

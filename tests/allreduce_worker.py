@@ -47,6 +47,13 @@ def main():
             torch.cuda.synchronize(dev)
             if not torch.equal(got, want.to(dt)):
                 failures.append((it, M, N, K, str(dt), float((got.float() - want).abs().max())))
+            # with the residual connection added as the sum is stored (same tensor on every rank)
+            gr = torch.Generator(device=dev).manual_seed(7 + it)
+            res = torch.randn(M, N, generator=gr, device=dev).to(dt)
+            got = ops.gemm_w4a4_int4_ar(codes, sx, pw, r, ctx, residual=res)
+            torch.cuda.synchronize(dev)
+            if not torch.equal(got, (want.to(dt).float() + res.float()).to(dt)):
+                failures.append((it, M, N, K, str(dt), "residual"))
     status = _lib.device_status(local)
     # a CUDA graph holding several fused calls replays correctly
     M, N, K = 8, 4096, 2048
